@@ -1,0 +1,207 @@
+/*
+ * libsharplight_cuda: flat C ABI of the CUDA (sm_100a) execution provider for Sharplight's quantized MatMul operator.
+ *
+ * The managed provider (Sharplight.Cuda: CudaExecutionProvider / CudaDevice / CudaSegment) binds these entry points
+ * with [LibraryImport]; each comment names the reference interface the entry point serves (paths relative to the
+ * Sharplight source tree). The conventions follow the repository's own native ABI
+ * (native/sharplight_audio/include/sharplight_audio.h:1-47):
+ *  - every function returns an slc_result (0 = success, negative = failure) unless stated otherwise;
+ *  - handles are opaque pointers owned by the caller until their *_close / *_free / *_destroy function is called;
+ *  - strings are UTF-8, NUL terminated, in static or thread-local storage;
+ *  - no callbacks into managed code;
+ *  - a handle must not be destroyed while another thread is inside a call using it. An slc_device may be used from
+ *    several threads at once (one opened device serves every model on that GPU, src/Sharplight.Core/Runtime/
+ *    DevicePool.cs:3-8); an slc_matmul / slc_activation is used by one thread at a time (one Run at a time per
+ *    compiled model, src/Sharplight.Core/Runtime/CompiledModel.cs:223).
+ *
+ * Weights are the raw ggml blocks the GGUF importer hands out (src/Sharplight.Import.Gguf/GgufWeightSource.cs:6-38),
+ * row-major [N, K]; the library copies them and keeps a same-size device layout of its own.
+ * There is no CPU fallback: without a CUDA device every compute entry point fails with SLC_ERR_NO_DEVICE.
+ */
+#ifndef SHARPLIGHT_CUDA_H
+#define SHARPLIGHT_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(_WIN32)
+#define SLC_API __declspec(dllexport)
+#elif defined(__GNUC__) || defined(__clang__)
+#define SLC_API __attribute__((visibility("default")))
+#else
+#define SLC_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ABI version; incremented when an existing function or struct changes incompatibly. */
+#define SLC_ABI_VERSION 1
+
+typedef int32_t slc_result;
+
+enum
+{
+    SLC_OK = 0,
+    SLC_ERR_INVALID_ARGUMENT = -1,  /* -> ArgumentException */
+    SLC_ERR_OUT_OF_MEMORY = -2,     /* -> InsufficientMemoryException */
+    SLC_ERR_NO_DEVICE = -3,         /* no CUDA driver / no sm_100 device: the provider reports itself unavailable */
+    SLC_ERR_UNSUPPORTED = -4,       /* -> NotSupportedException (format, shape) */
+    SLC_ERR_CUDA = -5,              /* a CUDA runtime call failed; slc_last_error_message() has the text */
+    SLC_ERR_INVALID_STATE = -6,     /* -> InvalidOperationException (e.g. rows beyond the compiled bound) */
+    SLC_ERR_TIMEOUT = -7,           /* a bounded device-side wait ran out; the context stays usable */
+    SLC_ERR_BUFFER_TOO_SMALL = -8
+};
+
+/* Weight formats, numbered like ggml (src/Sharplight.Import.Gguf/GgmlTypes.cs:51-92); block sizes and bytes as in
+   src/Sharplight.Core/Tensors/DataType.cs:102,110,116,120. */
+typedef enum slc_format
+{
+    SLC_FMT_Q4_0 = 2,   /* 32 values, 18 bytes: f16 d; u8 qs[16] */
+    SLC_FMT_Q8_0 = 8,   /* 32 values, 34 bytes: f16 d; i8 q[32] */
+    SLC_FMT_Q4_K = 12,  /* 256 values, 144 bytes: f16 d; f16 dmin; u8 scales[12]; u8 qs[128] */
+    SLC_FMT_Q6_K = 14   /* 256 values, 210 bytes: u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d */
+} slc_format;
+
+/* Activation element types. */
+typedef enum slc_dtype
+{
+    SLC_F32 = 0,
+    SLC_BF16 = 1   /* widened to f32 (exact) before quantization */
+} slc_dtype;
+
+/* slc_matmul_create flags. */
+enum
+{
+    SLC_MATMUL_DEFAULT = 0,
+    /* every activation row is computed exactly as a single row would be, so a 2-4 row verification step gives the
+       logits of one-row decoding bit for bit (CompileOptions.RowInvariantRows, src/Sharplight.Core/Runtime/
+       CompileOptions.cs:52-60; src/Sharplight.Cpu/MatMulOp.cs:36-41) */
+    SLC_MATMUL_ROW_INVARIANT = 1
+};
+
+/* Kernel families, for slc_matmul_set_kernel / slc_matmul_last_kernel. */
+enum
+{
+    SLC_KERNEL_AUTO = 0,
+    SLC_KERNEL_MMVQ = 1,     /* dp4a mat-vec, weights streamed once for up to 8 activation rows */
+    SLC_KERNEL_SKINNY = 2,   /* int8 mma tiles with the weight as the streamed operand, 9..64 rows */
+    SLC_KERNEL_MMQ = 3       /* tcgen05 / TMEM int8 GEMM for prefill */
+};
+
+typedef struct slc_device slc_device;
+typedef struct slc_weight slc_weight;
+typedef struct slc_matmul slc_matmul;
+typedef struct slc_activation slc_activation;
+
+/* What DeviceInfo needs (src/Sharplight.Core/Runtime/DeviceInfo.cs:4-50). */
+typedef struct slc_device_info
+{
+    char name[256];
+    char driver[64];           /* "driver 12090 / runtime 12090" */
+    uint8_t uuid[16];          /* the GPU UUID, so the same GPU under two providers is recognised */
+    int64_t total_memory;
+    int64_t free_memory;
+    int32_t sm_count;
+    int32_t cc_major;
+    int32_t cc_minor;
+    int32_t max_shared_per_block;
+    int32_t l2_bytes;
+    int32_t concurrent_workgroups;  /* SM count x resident CTAs of the mat-vec kernel */
+    int32_t supported;              /* 1 when the device can run this library's kernels (compute capability 10.0) */
+    int32_t reserved;
+} slc_device_info;
+
+/* ---- library: the ABI probe the managed loader performs (cf. src/Sharplight.Audio/Native/NativeAudioLibrary.cs:47-59) */
+SLC_API int32_t slc_abi_version(void);
+SLC_API const char *slc_version_string(void);
+SLC_API const char *slc_error_string(slc_result code);
+/* Detail text of the calling thread's most recent failure ("" when none). */
+SLC_API const char *slc_last_error_message(void);
+
+/* ---- devices: IExecutionProvider.CheckAvailability / GetDevices / OpenDevice
+        (src/Sharplight.Core/Runtime/IExecutionProvider.cs:25-45) */
+SLC_API slc_result slc_device_count(int32_t *out_count);
+SLC_API slc_result slc_device_info_get(int32_t index, slc_device_info *out);
+SLC_API slc_result slc_device_open(int32_t index, slc_device **out);
+SLC_API void slc_device_close(slc_device *device);
+/* IComputeDevice.AvailableMemory / GetMemoryInfo (src/Sharplight.Core/Runtime/IComputeDevice.cs:12-24). */
+SLC_API slc_result slc_device_memory(slc_device *device, int64_t *out_free, int64_t *out_total);
+/* Waits for everything queued on the device's own stream: the point where ICompiledSegment.GetOutput may read
+   (src/Sharplight.Core/Runtime/ICompiledSegment.cs:11-19). */
+SLC_API slc_result slc_device_sync(slc_device *device);
+/* The device's own stream as a cudaStream_t, for callers that time or order work on it. */
+SLC_API void *slc_device_stream(slc_device *device);
+/* Device-side status word (0 = fine; SLC_ERR_TIMEOUT after a bounded wait ran out); reading clears it. */
+SLC_API slc_result slc_last_status(slc_device *device, int32_t *out_status);
+
+/* ---- device buffers: boundary values a segment keeps on the device (IDeviceForwardingSegment.TryForwardFrom,
+        src/Sharplight.Core/Runtime/IDeviceForwardingSegment.cs:10-18) and staging for SetInput / GetOutput */
+SLC_API slc_result slc_buffer_alloc(slc_device *device, int64_t bytes, void **out_device_ptr);
+SLC_API void slc_buffer_free(slc_device *device, void *device_ptr);
+SLC_API slc_result slc_buffer_upload(slc_device *device, void *device_ptr, const void *host, int64_t bytes);
+SLC_API slc_result slc_buffer_download(slc_device *device, void *host, const void *device_ptr, int64_t bytes);
+
+/* ---- weights: WeightInfo.Source -> device (src/Sharplight.Core/Models/IWeightSource.cs:4-40).
+        blocks: raw ggml blocks of an [n, k] weight, row-major, bytes == n * k / block_size * block_bytes.
+        The data is copied (the caller may unmap afterwards) and re-laid-out on the device at the same byte count,
+        as the reference does for Q8_0 at upload (src/Sharplight.Shaders/Lowering/WeightRepacker.cs:56-69). */
+SLC_API slc_result slc_weight_upload(slc_device *device, int32_t format, int64_t n, int64_t k, const void *blocks,
+                                     int64_t bytes, slc_weight **out);
+/* Like slc_weight_upload but keeps only the K range [k0, k1) of every row (block-aligned): the row-split shard of a
+   tensor-parallel o / down projection. */
+SLC_API slc_result slc_weight_upload_kslice(slc_device *device, int32_t format, int64_t n, int64_t k,
+                                            const void *blocks, int64_t bytes, int64_t k0, int64_t k1,
+                                            slc_weight **out);
+/* Writes the weight back as raw ggml blocks (inverse of the device layout; for verification). */
+SLC_API slc_result slc_weight_download(slc_weight *weight, void *blocks, int64_t bytes);
+SLC_API slc_result slc_weight_shape(slc_weight *weight, int32_t *format, int64_t *n, int64_t *k, int64_t *device_bytes);
+SLC_API void slc_weight_free(slc_weight *weight);
+
+/* ---- the operator: StandardOps.MatMul, y = x . W^T (src/Sharplight.Core/Graph/StandardOps.cs:144-163), lowered
+        like the CPU provider's MatMulOp on its integer-dot path (src/Sharplight.Cpu/MatMulOp.cs:88-115,174-213) */
+SLC_API slc_result slc_matmul_create(slc_device *device, slc_weight *weight, int64_t max_rows, uint32_t flags,
+                                     slc_matmul **out);
+SLC_API void slc_matmul_destroy(slc_matmul *op);
+/*
+ * y[rows][n] (f32, row stride y_stride elements) = x[rows][k] . W^T. x rows are x_stride elements apart.
+ * x_is_device / y_is_device: 0 = host memory (copied through the op's staging buffers on the stream, the call
+ * returns after the result is in y), 1 = device memory (asynchronous on the stream).
+ * stream: a cudaStream_t, or NULL for the device's own stream.
+ * rows == 0 is a no-op; rows > max_rows fails with SLC_ERR_INVALID_STATE.
+ */
+SLC_API slc_result slc_matmul_run(slc_matmul *op, const void *x, int32_t x_dtype, int64_t rows, int64_t x_stride,
+                                  int32_t x_is_device, float *y, int64_t y_stride, int32_t y_is_device,
+                                  void *stream);
+/* Forces a kernel family (SLC_KERNEL_*) for later runs; SLC_KERNEL_AUTO restores the row-count dispatch. */
+SLC_API slc_result slc_matmul_set_kernel(slc_matmul *op, int32_t kernel);
+/* The family the most recent run used, and the number of kernels it launched. */
+SLC_API slc_result slc_matmul_last_kernel(slc_matmul *op, int32_t *out_kernel, int32_t *out_launches);
+
+/* ---- shared quantized activations: one 8-bit copy of x serves every MatMul reading the same rows (Q/K/V, gate/up),
+        as the reference's lowering shares it (src/Sharplight.Shaders/Lowering/GraphLowerer.IntDot.cs:38-43) */
+SLC_API slc_result slc_activation_create(slc_device *device, int64_t max_rows, int64_t k, slc_activation **out);
+SLC_API void slc_activation_destroy(slc_activation *act);
+/* Quantizes device-resident x (rows x k, x_stride elements apart) per 32 values: d = max|x| / 127, round half away
+   from zero (src/Sharplight.Cpu/IntDot.cs:92-126). Asynchronous on the stream. */
+SLC_API slc_result slc_activation_quantize(slc_activation *act, const void *x_device, int32_t x_dtype, int64_t rows,
+                                           int64_t x_stride, void *stream);
+/* y (device, f32) = act . W^T with the rows last quantized into act. Asynchronous on the stream. */
+SLC_API slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act, float *y_device, int64_t y_stride,
+                                            void *stream);
+
+/* ---- parity exports (host buffers; synchronous): the quantities the bit-exactness checks compare */
+/* q[rows][k] int8, d[rows][k/32] f32 block scales, gs[rows][k/16] f32 group sums d * sum16(q), as IntDot.Quantize
+   lays them out logically (src/Sharplight.Cpu/Q8Row.cs:9-20). x is host memory. */
+SLC_API slc_result slc_debug_quantize(slc_device *device, const void *x, int32_t x_dtype, int64_t rows, int64_t k,
+                                      int8_t *q, float *d, float *gs);
+/* s32[rows][n][k/32]: per 32-value block, the int32 dot of the CPU decoder's unsigned weight codes
+   (src/Sharplight.Cpu/IntDot.Decode.cs:70-99,125-148,189-223) with the activation codes, computed by the kernel
+   family the op would run for this row count. x is host memory. */
+SLC_API slc_result slc_debug_block_dots(slc_matmul *op, const void *x, int32_t x_dtype, int64_t rows, int32_t *s32);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,128 @@
+"""Vectorised numpy restatement of the same arithmetic as oracle/sl_oracle.c. TEST INFRASTRUCTURE ONLY.
+
+A second, independently written statement of the reference's rules (paths relative to the Sharplight tree):
+src/Sharplight.Cpu/Quant.cs:371-405,504-545,585-618 (decode), src/Sharplight.Cpu/IntDot.cs:92-126 (activation
+quantization), src/Sharplight.Cpu/IntDot.Decode.cs:70-99,125-148,189-223 (unsigned codes). The tests hold the two
+restatements against each other and against the ggml golden fixtures.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
+BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}
+
+
+def _f16(b: np.ndarray) -> np.ndarray:
+    """Two little-endian bytes (last axis of size 2) -> f32."""
+    return np.ascontiguousarray(b).view("<f2")[..., 0].astype(np.float32)
+
+
+def _fma(a, b, c):
+    """fma in f32 for small-integer a: the product and sum are exact in double, one final rounding."""
+    return (a.astype(np.float64) * b.astype(np.float64) + c.astype(np.float64)).astype(np.float32)
+
+
+def scale_min(s: np.ndarray):
+    """12 scale bytes [..., 12] -> (sc [..., 8], m [..., 8]) 6-bit values."""
+    s = s.astype(np.int32)
+    sc = np.empty(s.shape[:-1] + (8,), np.int32)
+    m = np.empty_like(sc)
+    sc[..., :4] = s[..., 0:4] & 63
+    m[..., :4] = s[..., 4:8] & 63
+    sc[..., 4:] = (s[..., 8:12] & 15) | ((s[..., 0:4] >> 6) << 4)
+    m[..., 4:] = (s[..., 8:12] >> 4) | ((s[..., 4:8] >> 6) << 4)
+    return sc, m
+
+
+def codes(fmt: int, blocks: np.ndarray, n: int, k: int):
+    """Raw blocks -> (u int32 [n, k] unsigned codes, a f32 [n, k/16], b f32 [n, k/16])."""
+    bs, bb = BLOCK[fmt]
+    nb = k // bs
+    blk = np.ascontiguousarray(blocks, np.uint8).reshape(n, nb, bb)
+    if fmt == Q8_0:
+        d = _f16(blk[..., 0:2])
+        u = (blk[..., 2:34] ^ 0x80).astype(np.int32).reshape(n, k)
+        a = np.repeat(d, 2, axis=1)
+        b = np.float32(-128.0) * a
+    elif fmt == Q4_0:
+        d = _f16(blk[..., 0:2])
+        qs = blk[..., 2:18].astype(np.int32)
+        u = np.concatenate([qs & 15, qs >> 4], axis=-1).reshape(n, k)
+        a = np.repeat(d, 2, axis=1)
+        b = np.float32(-8.0) * a
+    elif fmt == Q4_K:
+        d = _f16(blk[..., 0:2])
+        dmin = _f16(blk[..., 2:4])
+        sc, m = scale_min(blk[..., 4:16])
+        qs = blk[..., 16:144].astype(np.int32).reshape(n, nb, 4, 32)
+        u = np.concatenate([qs & 15, qs >> 4], axis=-1).reshape(n, k)
+        a8 = d[..., None] * sc.astype(np.float32)
+        b8 = -dmin[..., None] * m.astype(np.float32)
+        a = np.repeat(a8.reshape(n, nb * 8), 2, axis=1)
+        b = np.repeat(b8.reshape(n, nb * 8), 2, axis=1)
+    elif fmt == Q6_K:
+        ql = blk[..., 0:128].astype(np.int32).reshape(n, nb, 2, 64)
+        qh = blk[..., 128:192].astype(np.int32).reshape(n, nb, 2, 32)
+        sc = blk[..., 192:208].view(np.int8).astype(np.float32)
+        d = _f16(blk[..., 208:210])
+        la, lb = ql[..., :32], ql[..., 32:]
+        v1 = (la & 15) | ((qh & 3) << 4)
+        v2 = (lb & 15) | (((qh >> 2) & 3) << 4)
+        v3 = (la >> 4) | (((qh >> 4) & 3) << 4)
+        v4 = (lb >> 4) | (((qh >> 6) & 3) << 4)
+        u = np.concatenate([v1, v2, v3, v4], axis=-1).reshape(n, k)
+        a = (d[..., None] * sc).reshape(n, nb * 16).astype(np.float32)
+        b = np.float32(-32.0) * a
+    else:
+        raise ValueError(fmt)
+    return u, a.astype(np.float32), b.astype(np.float32)
+
+
+def dequantize(fmt: int, blocks: np.ndarray, n: int, k: int) -> np.ndarray:
+    """w = fma(code, a, b) per value with the reference's signed code for Q8_0 (offset 0)."""
+    u, a, b = codes(fmt, blocks, n, k)
+    a16 = np.repeat(a, 16, axis=1)
+    if fmt == Q8_0:
+        return _fma((u - 128).astype(np.float32), a16, np.zeros_like(a16))
+    return _fma(u.astype(np.float32), a16, np.repeat(b, 16, axis=1))
+
+
+def quantize(x: np.ndarray):
+    """f32 [m, k] -> (q int8, d [m, k/32], gs [m, k/16]) by the scalar rule, all in f32 arithmetic."""
+    x = np.ascontiguousarray(x, np.float32)
+    m, k = x.shape
+    xb = x.reshape(m, k // 32, 32)
+    amax = np.abs(xb).max(axis=-1)
+    d = (amax / np.float32(127.0)).astype(np.float32)
+    with np.errstate(divide="ignore"):
+        inv = np.where(d != 0, np.float32(1.0) / d, np.float32(0.0)).astype(np.float32)
+    v = (xb * inv[..., None]).astype(np.float32)
+    r = np.trunc((v + np.copysign(np.float32(0.5), v)).astype(np.float32)).astype(np.int32)
+    q = r.astype(np.int8).reshape(m, k)
+    s16 = r.reshape(m, k // 16, 16).sum(axis=-1)
+    gs = (np.repeat(d, 2, axis=1) * s16.astype(np.float32)).astype(np.float32)
+    return q, d, gs
+
+
+def block_dots(u: np.ndarray, q: np.ndarray) -> np.ndarray:
+    """u int [n, k], q int8 [m, k] -> int32 [m, n, k/32] exact dots per 32-value block."""
+    n, k = u.shape
+    m = q.shape[0]
+    ub = u.astype(np.int64).reshape(n, k // 32, 32)
+    qb = q.astype(np.int64).reshape(m, k // 32, 32)
+    return np.einsum("nbi,mbi->mnb", ub, qb).astype(np.int32)
+
+
+def matmul_intdot_f64(fmt: int, blocks: np.ndarray, n: int, k: int, x: np.ndarray) -> np.ndarray:
+    """Sum of the integer-dot terms a*d*s + b*(d*sum q) per 16 values, in double."""
+    u, a, b = codes(fmt, blocks, n, k)
+    q, d, _ = quantize(x)
+    m = q.shape[0]
+    ug = u.astype(np.int64).reshape(n, k // 16, 16)
+    qg = q.astype(np.int64).reshape(m, k // 16, 16)
+    s = np.einsum("ngi,mgi->mng", ug, qg).astype(np.float64)
+    sq = qg.sum(axis=-1).astype(np.float64)
+    d16 = np.repeat(d, 2, axis=1).astype(np.float64)
+    return (s * a.astype(np.float64)[None] * d16[:, None, :]).sum(-1) + \
+        (b.astype(np.float64)[None] * (d16 * sq)[:, None, :]).sum(-1)

@@ -1,0 +1,685 @@
+// The C ABI of libsharplight_cuda (include/sharplight_cuda.h): handles, argument checks, kernel dispatch.
+// No CPU fallback lives here: every compute entry point needs a CUDA device and fails loudly without one.
+#include "../../include/sharplight_cuda.h"
+
+#include "internal.cuh"
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+using namespace slc;
+
+// ---- handles ---------------------------------------------------------------------------------------------------------
+
+struct slc_device
+{
+    int index = 0;
+    cudaStream_t stream = nullptr;
+    int *status_dev = nullptr;   // device-side status word (bounded waits report here)
+    cudaDeviceProp prop{};
+};
+
+struct slc_weight
+{
+    slc_device *dev = nullptr;
+    int fmt = 0;
+    long long n = 0, k = 0;
+    uint8_t *base = nullptr;
+    size_t bytes = 0;
+    WeightView view{};
+};
+
+struct slc_activation
+{
+    slc_device *dev = nullptr;
+    long long max_rows = 0, k = 0;
+    int k_pad = 0, cap_rows = 0;  // cap_rows: padded row capacity of the planes
+    uint8_t *base = nullptr;
+    size_t bytes = 0;
+    ActPlanes planes{};
+    int rows = 0, rows_pad = 0;   // what the last quantize call wrote
+};
+
+struct slc_matmul
+{
+    slc_device *dev = nullptr;
+    slc_weight *w = nullptr;
+    long long max_rows = 0;
+    uint32_t flags = 0;
+    int forced_kernel = SLC_KERNEL_AUTO;
+    int last_kernel = 0, last_launches = 0;
+    slc_activation *act = nullptr;  // the op's own quantized copy (slc_matmul_run)
+    void *x_stage = nullptr;        // device staging for host activations (max_rows x k, 4 bytes each)
+    float *y_stage = nullptr;       // device staging for host outputs (max_rows x n)
+};
+
+// ---- errors ----------------------------------------------------------------------------------------------------------
+
+static thread_local std::string t_last_error;
+
+static slc_result fail(slc_result code, const std::string &msg)
+{
+    t_last_error = msg;
+    return code;
+}
+
+static slc_result cuda_fail(cudaError_t e, const char *what)
+{
+    if (e == cudaErrorMemoryAllocation) {
+        cudaGetLastError();
+        return fail(SLC_ERR_OUT_OF_MEMORY, std::string(what) + ": out of device memory");
+    }
+    if (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver) {
+        cudaGetLastError();
+        return fail(SLC_ERR_NO_DEVICE, std::string(what) + ": " + cudaGetErrorString(e));
+    }
+    return fail(SLC_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+#define SLC_CUDA(call)                                          \
+    do {                                                        \
+        cudaError_t e_ = (call);                                \
+        if (e_ != cudaSuccess) return cuda_fail(e_, #call);     \
+    } while (0)
+
+// Rows are padded so that every token tile a kernel touches exists: 8, 16, 32, then multiples of 64.
+static int pad_rows(long long rows)
+{
+    if (rows <= 8) return 8;
+    if (rows <= 16) return 16;
+    if (rows <= 32) return 32;
+    return (int)((rows + 63) / 64 * 64);
+}
+
+extern "C" {
+
+int32_t slc_abi_version(void) { return SLC_ABI_VERSION; }
+
+const char *slc_version_string(void) { return "libsharplight_cuda 0.1 (sm_100a)"; }
+
+const char *slc_error_string(slc_result code)
+{
+    switch (code) {
+    case SLC_OK: return "ok";
+    case SLC_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case SLC_ERR_OUT_OF_MEMORY: return "out of memory";
+    case SLC_ERR_NO_DEVICE: return "no usable CUDA device";
+    case SLC_ERR_UNSUPPORTED: return "unsupported format or shape";
+    case SLC_ERR_CUDA: return "CUDA runtime error";
+    case SLC_ERR_INVALID_STATE: return "invalid state";
+    case SLC_ERR_TIMEOUT: return "device-side wait timed out";
+    case SLC_ERR_BUFFER_TOO_SMALL: return "buffer too small";
+    default: return "unknown error";
+    }
+}
+
+const char *slc_last_error_message(void) { return t_last_error.c_str(); }
+
+// ---- devices ---------------------------------------------------------------------------------------------------------
+
+slc_result slc_device_count(int32_t *out_count)
+{
+    if (!out_count) return fail(SLC_ERR_INVALID_ARGUMENT, "out_count is null");
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        *out_count = 0;
+        return fail(SLC_ERR_NO_DEVICE, std::string("cudaGetDeviceCount: ") + cudaGetErrorString(e));
+    }
+    *out_count = n;
+    return SLC_OK;
+}
+
+slc_result slc_device_info_get(int32_t index, slc_device_info *out)
+{
+    if (!out) return fail(SLC_ERR_INVALID_ARGUMENT, "out is null");
+    int32_t n = 0;
+    slc_result r = slc_device_count(&n);
+    if (r != SLC_OK) return r;
+    if (index < 0 || index >= n) return fail(SLC_ERR_INVALID_ARGUMENT, "device index out of range");
+    cudaDeviceProp p;
+    SLC_CUDA(cudaGetDeviceProperties(&p, index));
+    memset(out, 0, sizeof(*out));
+    snprintf(out->name, sizeof(out->name), "%s", p.name);
+    int drv = 0, rt = 0;
+    cudaDriverGetVersion(&drv);
+    cudaRuntimeGetVersion(&rt);
+    snprintf(out->driver, sizeof(out->driver), "driver %d / runtime %d", drv, rt);
+    memcpy(out->uuid, p.uuid.bytes, 16);
+    out->total_memory = (int64_t)p.totalGlobalMem;
+    out->sm_count = p.multiProcessorCount;
+    out->cc_major = p.major;
+    out->cc_minor = p.minor;
+    out->max_shared_per_block = (int32_t)p.sharedMemPerBlockOptin;
+    out->l2_bytes = p.l2CacheSize;
+    out->concurrent_workgroups = p.multiProcessorCount * 16;
+    out->supported = (p.major == 10 && p.minor == 0) ? 1 : 0;
+    size_t fr = 0, tot = 0;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    if (cudaSetDevice(index) == cudaSuccess && cudaMemGetInfo(&fr, &tot) == cudaSuccess) out->free_memory = (int64_t)fr;
+    cudaSetDevice(prev);
+    return SLC_OK;
+}
+
+slc_result slc_device_open(int32_t index, slc_device **out)
+{
+    if (!out) return fail(SLC_ERR_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    int32_t n = 0;
+    slc_result r = slc_device_count(&n);
+    if (r != SLC_OK) return r;
+    if (index < 0 || index >= n) return fail(SLC_ERR_INVALID_ARGUMENT, "device index out of range");
+    slc_device *d = new (std::nothrow) slc_device();
+    if (!d) return fail(SLC_ERR_OUT_OF_MEMORY, "host allocation failed");
+    d->index = index;
+    cudaError_t e = cudaGetDeviceProperties(&d->prop, index);
+    if (e == cudaSuccess && !(d->prop.major == 10 && d->prop.minor == 0)) {
+        delete d;
+        return fail(SLC_ERR_NO_DEVICE, "device is not compute capability 10.0 (sm_100a kernels only)");
+    }
+    if (e == cudaSuccess) e = cudaSetDevice(index);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaMalloc(&d->status_dev, 256);
+    if (e == cudaSuccess) e = cudaMemset(d->status_dev, 0, 256);
+    if (e != cudaSuccess) {
+        if (d->stream) cudaStreamDestroy(d->stream);
+        if (d->status_dev) cudaFree(d->status_dev);
+        delete d;
+        return cuda_fail(e, "slc_device_open");
+    }
+    *out = d;
+    return SLC_OK;
+}
+
+void slc_device_close(slc_device *d)
+{
+    if (!d) return;
+    cudaSetDevice(d->index);
+    cudaStreamSynchronize(d->stream);
+    cudaStreamDestroy(d->stream);
+    cudaFree(d->status_dev);
+    delete d;
+}
+
+slc_result slc_device_memory(slc_device *d, int64_t *out_free, int64_t *out_total)
+{
+    if (!d) return fail(SLC_ERR_INVALID_ARGUMENT, "device is null");
+    SLC_CUDA(cudaSetDevice(d->index));
+    size_t fr = 0, tot = 0;
+    SLC_CUDA(cudaMemGetInfo(&fr, &tot));
+    if (out_free) *out_free = (int64_t)fr;
+    if (out_total) *out_total = (int64_t)tot;
+    return SLC_OK;
+}
+
+slc_result slc_device_sync(slc_device *d)
+{
+    if (!d) return fail(SLC_ERR_INVALID_ARGUMENT, "device is null");
+    SLC_CUDA(cudaSetDevice(d->index));
+    SLC_CUDA(cudaStreamSynchronize(d->stream));
+    return SLC_OK;
+}
+
+void *slc_device_stream(slc_device *d) { return d ? (void *)d->stream : nullptr; }
+
+slc_result slc_last_status(slc_device *d, int32_t *out_status)
+{
+    if (!d || !out_status) return fail(SLC_ERR_INVALID_ARGUMENT, "null argument");
+    SLC_CUDA(cudaSetDevice(d->index));
+    int v = 0;
+    SLC_CUDA(cudaMemcpy(&v, d->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v != 0) SLC_CUDA(cudaMemset(d->status_dev, 0, sizeof(int)));
+    *out_status = v;
+    return SLC_OK;
+}
+
+// ---- buffers ---------------------------------------------------------------------------------------------------------
+
+slc_result slc_buffer_alloc(slc_device *d, int64_t bytes, void **out)
+{
+    if (!d || !out || bytes < 0) return fail(SLC_ERR_INVALID_ARGUMENT, "bad buffer request");
+    *out = nullptr;
+    SLC_CUDA(cudaSetDevice(d->index));
+    SLC_CUDA(cudaMalloc(out, bytes > 0 ? (size_t)bytes : 16));
+    return SLC_OK;
+}
+
+void slc_buffer_free(slc_device *d, void *p)
+{
+    if (!d || !p) return;
+    cudaSetDevice(d->index);
+    cudaFree(p);
+}
+
+slc_result slc_buffer_upload(slc_device *d, void *dst, const void *host, int64_t bytes)
+{
+    if (!d || bytes < 0 || (bytes > 0 && (!dst || !host))) return fail(SLC_ERR_INVALID_ARGUMENT, "bad upload");
+    if (bytes == 0) return SLC_OK;
+    SLC_CUDA(cudaSetDevice(d->index));
+    SLC_CUDA(cudaMemcpyAsync(dst, host, (size_t)bytes, cudaMemcpyHostToDevice, d->stream));
+    SLC_CUDA(cudaStreamSynchronize(d->stream));
+    return SLC_OK;
+}
+
+slc_result slc_buffer_download(slc_device *d, void *host, const void *src, int64_t bytes)
+{
+    if (!d || bytes < 0 || (bytes > 0 && (!src || !host))) return fail(SLC_ERR_INVALID_ARGUMENT, "bad download");
+    if (bytes == 0) return SLC_OK;
+    SLC_CUDA(cudaSetDevice(d->index));
+    SLC_CUDA(cudaMemcpyAsync(host, src, (size_t)bytes, cudaMemcpyDeviceToHost, d->stream));
+    SLC_CUDA(cudaStreamSynchronize(d->stream));
+    return SLC_OK;
+}
+
+// ---- weights ---------------------------------------------------------------------------------------------------------
+
+static slc_result check_weight_args(slc_device *d, int32_t fmt, int64_t n, int64_t k, const void *blocks, int64_t bytes)
+{
+    if (!d) return fail(SLC_ERR_INVALID_ARGUMENT, "device is null");
+    const int bs = block_size(fmt);
+    if (bs == 0) return fail(SLC_ERR_UNSUPPORTED, "weight format is not one of Q4_0, Q8_0, Q4_K, Q6_K");
+    if (n < 0 || k <= 0) return fail(SLC_ERR_INVALID_ARGUMENT, "bad weight shape");
+    if (k % bs != 0) {
+        char msg[96];
+        snprintf(msg, sizeof(msg), "K=%lld is not a multiple of the block size %d", (long long)k, bs);
+        return fail(SLC_ERR_INVALID_ARGUMENT, msg);
+    }
+    if (n > (1 << 30) || k > (1 << 30)) return fail(SLC_ERR_UNSUPPORTED, "weight dimension too large");
+    if (bytes != n * (k / bs) * block_bytes(fmt)) return fail(SLC_ERR_INVALID_ARGUMENT, "bytes != n * k / block_size * block_bytes");
+    if (bytes > 0 && !blocks) return fail(SLC_ERR_INVALID_ARGUMENT, "blocks is null");
+    return SLC_OK;
+}
+
+slc_result slc_weight_upload(slc_device *d, int32_t fmt, int64_t n, int64_t k, const void *blocks, int64_t bytes,
+                             slc_weight **out)
+{
+    if (!out) return fail(SLC_ERR_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    slc_result r = check_weight_args(d, fmt, n, k, blocks, bytes);
+    if (r != SLC_OK) return r;
+    SLC_CUDA(cudaSetDevice(d->index));
+    slc_weight *w = new (std::nothrow) slc_weight();
+    if (!w) return fail(SLC_ERR_OUT_OF_MEMORY, "host allocation failed");
+    w->dev = d; w->fmt = fmt; w->n = n; w->k = k;
+    const int n_pad = (int)round_up((size_t)n, 16), k_pad = (int)round_up((size_t)k, 256);
+    const size_t qs_b = round_up(weight_qs_bytes(fmt, n_pad, k_pad), 256);
+    const size_t sc_b = round_up(weight_sc_bytes(fmt, n_pad, k_pad), 256);
+    const size_t d6_b = weight_d6_bytes(fmt, n_pad, k_pad);
+    w->bytes = qs_b + sc_b + d6_b + 256;
+    uint8_t *raw = nullptr;
+    cudaError_t e = cudaMalloc(&w->base, w->bytes);
+    if (e == cudaSuccess && bytes > 0) e = cudaMalloc(&raw, (size_t)bytes);
+    if (e == cudaSuccess && bytes > 0) e = cudaMemcpyAsync(raw, blocks, (size_t)bytes, cudaMemcpyHostToDevice, d->stream);
+    if (e == cudaSuccess) {
+        e = launch_repack(fmt, (int)n, (int)k, n_pad, k_pad, raw, w->base, w->base + qs_b, w->base + qs_b + sc_b, false,
+                          d->stream);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);
+    if (raw) cudaFree(raw);
+    if (e != cudaSuccess) {
+        if (w->base) cudaFree(w->base);
+        delete w;
+        return cuda_fail(e, "slc_weight_upload");
+    }
+    w->view.fmt = fmt; w->view.n = (int)n; w->view.k = (int)k; w->view.n_pad = n_pad; w->view.k_pad = k_pad;
+    w->view.qs = reinterpret_cast<const uint4 *>(w->base);
+    w->view.sc = w->base + qs_b;
+    w->view.d6 = reinterpret_cast<const __half *>(w->base + qs_b + sc_b);
+    *out = w;
+    return SLC_OK;
+}
+
+slc_result slc_weight_upload_kslice(slc_device *d, int32_t fmt, int64_t n, int64_t k, const void *blocks, int64_t bytes,
+                                    int64_t k0, int64_t k1, slc_weight **out)
+{
+    if (!out) return fail(SLC_ERR_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    slc_result r = check_weight_args(d, fmt, n, k, blocks, bytes);
+    if (r != SLC_OK) return r;
+    const int bs = block_size(fmt), bb = block_bytes(fmt);
+    if (k0 < 0 || k1 <= k0 || k1 > k || k0 % bs != 0 || k1 % bs != 0) {
+        return fail(SLC_ERR_INVALID_ARGUMENT, "K slice must be non-empty and aligned to the block size");
+    }
+    const size_t row_full = (size_t)(k / bs) * bb, row_slice = (size_t)((k1 - k0) / bs) * bb, off = (size_t)(k0 / bs) * bb;
+    std::vector<uint8_t> packed;
+    try { packed.resize((size_t)n * row_slice); } catch (...) { return fail(SLC_ERR_OUT_OF_MEMORY, "host allocation failed"); }
+    for (int64_t row = 0; row < n; row++) {
+        memcpy(packed.data() + (size_t)row * row_slice, (const uint8_t *)blocks + (size_t)row * row_full + off, row_slice);
+    }
+    return slc_weight_upload(d, fmt, n, k1 - k0, packed.data(), (int64_t)packed.size(), out);
+}
+
+slc_result slc_weight_download(slc_weight *w, void *blocks, int64_t bytes)
+{
+    if (!w) return fail(SLC_ERR_INVALID_ARGUMENT, "weight is null");
+    const long long want = w->n * (w->k / block_size(w->fmt)) * block_bytes(w->fmt);
+    if (bytes != want) return fail(SLC_ERR_BUFFER_TOO_SMALL, "bytes != n * k / block_size * block_bytes");
+    if (bytes == 0) return SLC_OK;
+    if (!blocks) return fail(SLC_ERR_INVALID_ARGUMENT, "blocks is null");
+    slc_device *d = w->dev;
+    SLC_CUDA(cudaSetDevice(d->index));
+    uint8_t *raw = nullptr;
+    SLC_CUDA(cudaMalloc(&raw, (size_t)bytes));
+    cudaError_t e = cudaMemsetAsync(raw, 0, (size_t)bytes, d->stream);
+    const size_t qs_b = (const uint8_t *)w->view.sc - w->base;
+    if (e == cudaSuccess) {
+        e = launch_repack(w->fmt, (int)w->n, (int)w->k, w->view.n_pad, w->view.k_pad, raw, w->base, w->base + qs_b,
+                          (uint8_t *)w->view.d6, true, d->stream);
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(blocks, raw, (size_t)bytes, cudaMemcpyDeviceToHost, d->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);
+    cudaFree(raw);
+    if (e != cudaSuccess) return cuda_fail(e, "slc_weight_download");
+    return SLC_OK;
+}
+
+slc_result slc_weight_shape(slc_weight *w, int32_t *format, int64_t *n, int64_t *k, int64_t *device_bytes)
+{
+    if (!w) return fail(SLC_ERR_INVALID_ARGUMENT, "weight is null");
+    if (format) *format = w->fmt;
+    if (n) *n = w->n;
+    if (k) *k = w->k;
+    if (device_bytes) *device_bytes = (int64_t)w->bytes;
+    return SLC_OK;
+}
+
+void slc_weight_free(slc_weight *w)
+{
+    if (!w) return;
+    cudaSetDevice(w->dev->index);
+    cudaFree(w->base);
+    delete w;
+}
+
+// ---- activations -----------------------------------------------------------------------------------------------------
+
+slc_result slc_activation_create(slc_device *d, int64_t max_rows, int64_t k, slc_activation **out)
+{
+    if (!out) return fail(SLC_ERR_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    if (!d || max_rows < 1 || k < 32 || k % 32 != 0 || k > (1 << 30) || max_rows > (1 << 24)) {
+        return fail(SLC_ERR_INVALID_ARGUMENT, "activation shape: max_rows >= 1, K a positive multiple of 32");
+    }
+    SLC_CUDA(cudaSetDevice(d->index));
+    slc_activation *a = new (std::nothrow) slc_activation();
+    if (!a) return fail(SLC_ERR_OUT_OF_MEMORY, "host allocation failed");
+    a->dev = d; a->max_rows = max_rows; a->k = k;
+    a->k_pad = (int)round_up((size_t)k, 256);
+    a->cap_rows = pad_rows(max_rows);
+    const size_t cap = (size_t)a->cap_rows, kp = (size_t)a->k_pad;
+    const size_t q_b = round_up(cap * kp, 256), ds_b = round_up(cap * (kp / 32) * 8, 256);
+    const size_t gs_b = round_up(cap * (kp / 16) * 4, 256), is_b = round_up(cap * (kp / 32) * 4, 256);
+    a->bytes = q_b + ds_b + gs_b + is_b;
+    cudaError_t e = cudaMalloc(&a->base, a->bytes);
+    if (e == cudaSuccess) e = cudaMemset(a->base, 0, a->bytes);
+    if (e != cudaSuccess) {
+        if (a->base) cudaFree(a->base);
+        delete a;
+        return cuda_fail(e, "slc_activation_create");
+    }
+    a->planes.q = reinterpret_cast<int8_t *>(a->base);
+    a->planes.ds = reinterpret_cast<float2 *>(a->base + q_b);
+    a->planes.gs = reinterpret_cast<float *>(a->base + q_b + ds_b);
+    a->planes.isum = reinterpret_cast<int *>(a->base + q_b + ds_b + gs_b);
+    *out = a;
+    return SLC_OK;
+}
+
+void slc_activation_destroy(slc_activation *a)
+{
+    if (!a) return;
+    cudaSetDevice(a->dev->index);
+    cudaFree(a->base);
+    delete a;
+}
+
+slc_result slc_activation_quantize(slc_activation *a, const void *x, int32_t x_dtype, int64_t rows, int64_t x_stride,
+                                   void *stream)
+{
+    if (!a) return fail(SLC_ERR_INVALID_ARGUMENT, "activation is null");
+    if (x_dtype != SLC_F32 && x_dtype != SLC_BF16) return fail(SLC_ERR_UNSUPPORTED, "activation dtype must be f32 or bf16");
+    if (rows < 0) return fail(SLC_ERR_INVALID_ARGUMENT, "rows < 0");
+    if (rows > a->max_rows) return fail(SLC_ERR_INVALID_STATE, "rows exceed the bound the activation was created with");
+    if (rows > 0 && !x) return fail(SLC_ERR_INVALID_ARGUMENT, "x is null");
+    if (rows > 0 && x_stride < a->k) return fail(SLC_ERR_INVALID_ARGUMENT, "x_stride < K");
+    a->rows = (int)rows;
+    a->rows_pad = rows > 0 ? pad_rows(rows) : 0;
+    if (rows == 0) return SLC_OK;
+    SLC_CUDA(cudaSetDevice(a->dev->index));
+    cudaStream_t s = stream ? (cudaStream_t)stream : a->dev->stream;
+    SLC_CUDA(launch_quantize(x, x_dtype, a->rows, a->rows_pad, (int)a->k, a->k_pad, x_stride, a->planes, s));
+    return SLC_OK;
+}
+
+static ActView view_of(const slc_activation *a)
+{
+    ActView v;
+    v.rows = a->rows; v.rows_pad = a->rows_pad; v.k = (int)a->k; v.k_pad = a->k_pad;
+    v.q = a->planes.q; v.ds = a->planes.ds; v.gs = a->planes.gs; v.isum = a->planes.isum;
+    return v;
+}
+
+// ---- the operator ----------------------------------------------------------------------------------------------------
+
+slc_result slc_matmul_create(slc_device *d, slc_weight *w, int64_t max_rows, uint32_t flags, slc_matmul **out)
+{
+    if (!out) return fail(SLC_ERR_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    if (!d || !w) return fail(SLC_ERR_INVALID_ARGUMENT, "null device or weight");
+    if (w->dev != d) return fail(SLC_ERR_INVALID_ARGUMENT, "the weight lives on another device");
+    if (max_rows < 1 || max_rows > (1 << 24)) return fail(SLC_ERR_INVALID_ARGUMENT, "max_rows out of range");
+    if (flags & ~(uint32_t)SLC_MATMUL_ROW_INVARIANT) return fail(SLC_ERR_INVALID_ARGUMENT, "unknown flags");
+    slc_matmul *op = new (std::nothrow) slc_matmul();
+    if (!op) return fail(SLC_ERR_OUT_OF_MEMORY, "host allocation failed");
+    op->dev = d; op->w = w; op->max_rows = max_rows; op->flags = flags;
+    *out = op;
+    return SLC_OK;
+}
+
+void slc_matmul_destroy(slc_matmul *op)
+{
+    if (!op) return;
+    cudaSetDevice(op->dev->index);
+    if (op->act) slc_activation_destroy(op->act);
+    if (op->x_stage) cudaFree(op->x_stage);
+    if (op->y_stage) cudaFree(op->y_stage);
+    delete op;
+}
+
+slc_result slc_matmul_set_kernel(slc_matmul *op, int32_t kernel)
+{
+    if (!op) return fail(SLC_ERR_INVALID_ARGUMENT, "op is null");
+    if (kernel < SLC_KERNEL_AUTO || kernel > SLC_KERNEL_MMQ) return fail(SLC_ERR_INVALID_ARGUMENT, "unknown kernel family");
+    if (kernel == SLC_KERNEL_MMQ && !mmq_supports(op->w->fmt)) {
+        return fail(SLC_ERR_UNSUPPORTED, "the tensor-core GEMM does not take this weight format");
+    }
+    op->forced_kernel = kernel;
+    return SLC_OK;
+}
+
+slc_result slc_matmul_last_kernel(slc_matmul *op, int32_t *out_kernel, int32_t *out_launches)
+{
+    if (!op) return fail(SLC_ERR_INVALID_ARGUMENT, "op is null");
+    if (out_kernel) *out_kernel = op->last_kernel;
+    if (out_launches) *out_launches = op->last_launches;
+    return SLC_OK;
+}
+
+// Row-count dispatch. The reference's own GPU policy switches at 8 / 16 / 33 rows
+// (src/Sharplight.Shaders/Lowering/GraphLowerer.IntDot.cs:18-19, GraphLowerer.Mmq.cs:16-52 of the Sharplight tree);
+// these thresholds are the measured crossovers of this library's kernels on B200.
+static int choose_kernel(const slc_matmul *op, int rows)
+{
+    if (op->forced_kernel != SLC_KERNEL_AUTO) return op->forced_kernel;
+    if ((op->flags & SLC_MATMUL_ROW_INVARIANT) && rows <= 8) return SLC_KERNEL_MMVQ;
+    if (rows <= 2) return SLC_KERNEL_MMVQ;
+    if (rows <= 64 || !mmq_supports(op->w->fmt)) return SLC_KERNEL_SKINNY;
+    return SLC_KERNEL_MMQ;
+}
+
+static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, long long y_stride, int *dump,
+                              cudaStream_t s)
+{
+    const ActView av = view_of(act);
+    const WeightView &wv = op->w->view;
+    const int rows = act->rows;
+    const int kernel = choose_kernel(op, rows);
+    const long long dump_row = (long long)wv.n * (wv.k >> 5);
+    op->last_kernel = kernel;
+    op->last_launches = 0;
+    if (kernel == SLC_KERNEL_MMVQ) {
+        for (int r0 = 0; r0 < rows; r0 += 8) {
+            const int m = rows - r0 < 8 ? rows - r0 : 8;
+            SLC_CUDA(launch_mmvq(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, s));
+            op->last_launches++;
+        }
+    } else if (kernel == SLC_KERNEL_SKINNY) {
+        for (int r0 = 0; r0 < rows; r0 += 64) {
+            const int m = rows - r0 < 64 ? rows - r0 : 64;
+            SLC_CUDA(launch_skinny(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, s));
+            op->last_launches++;
+        }
+    } else {
+        SLC_CUDA(launch_mmq(wv, av, rows, y, y_stride, dump, op->dev->status_dev, s));
+        op->last_launches++;
+    }
+    return SLC_OK;
+}
+
+slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act, float *y, int64_t y_stride, void *stream)
+{
+    if (!op || !act) return fail(SLC_ERR_INVALID_ARGUMENT, "null op or activation");
+    if (act->dev != op->dev) return fail(SLC_ERR_INVALID_ARGUMENT, "the activation lives on another device");
+    if (act->k != op->w->k) return fail(SLC_ERR_INVALID_ARGUMENT, "activation K differs from the weight's K");
+    if (act->rows > op->max_rows) return fail(SLC_ERR_INVALID_STATE, "rows exceed the op's compiled bound");
+    if (act->rows == 0 || op->w->n == 0) return SLC_OK;
+    if (!y || y_stride < op->w->n) return fail(SLC_ERR_INVALID_ARGUMENT, "bad output buffer or stride");
+    SLC_CUDA(cudaSetDevice(op->dev->index));
+    cudaStream_t s = stream ? (cudaStream_t)stream : op->dev->stream;
+    return run_kernels(op, act, y, y_stride, nullptr, s);
+}
+
+static slc_result ensure_op_buffers(slc_matmul *op, bool need_x_stage, bool need_y_stage)
+{
+    if (!op->act) {
+        slc_result r = slc_activation_create(op->dev, op->max_rows, op->w->k, &op->act);
+        if (r != SLC_OK) return r;
+    }
+    if (need_x_stage && !op->x_stage) SLC_CUDA(cudaMalloc(&op->x_stage, (size_t)op->max_rows * op->w->k * 4));
+    if (need_y_stage && !op->y_stage) {
+        SLC_CUDA(cudaMalloc(&op->y_stage, (size_t)op->max_rows * (op->w->n > 0 ? op->w->n : 1) * 4));
+    }
+    return SLC_OK;
+}
+
+slc_result slc_matmul_run(slc_matmul *op, const void *x, int32_t x_dtype, int64_t rows, int64_t x_stride,
+                          int32_t x_is_device, float *y, int64_t y_stride, int32_t y_is_device, void *stream)
+{
+    if (!op) return fail(SLC_ERR_INVALID_ARGUMENT, "op is null");
+    if (x_dtype != SLC_F32 && x_dtype != SLC_BF16) return fail(SLC_ERR_UNSUPPORTED, "activation dtype must be f32 or bf16");
+    if (rows < 0) return fail(SLC_ERR_INVALID_ARGUMENT, "rows < 0");
+    if (rows > op->max_rows) return fail(SLC_ERR_INVALID_STATE, "rows exceed the op's compiled bound");
+    if (rows == 0) return SLC_OK;
+    const long long n = op->w->n, k = op->w->k;
+    if (!x || x_stride < k) return fail(SLC_ERR_INVALID_ARGUMENT, "bad activation buffer or stride");
+    if (n > 0 && (!y || y_stride < n)) return fail(SLC_ERR_INVALID_ARGUMENT, "bad output buffer or stride");
+    SLC_CUDA(cudaSetDevice(op->dev->index));
+    cudaStream_t s = stream ? (cudaStream_t)stream : op->dev->stream;
+    slc_result r = ensure_op_buffers(op, !x_is_device, !y_is_device);
+    if (r != SLC_OK) return r;
+    const size_t esz = x_dtype == SLC_F32 ? 4 : 2;
+    const void *x_dev = x;
+    long long xs = x_stride;
+    if (!x_is_device) {
+        SLC_CUDA(cudaMemcpy2DAsync(op->x_stage, (size_t)k * esz, x, (size_t)x_stride * esz, (size_t)k * esz, (size_t)rows,
+                                   cudaMemcpyHostToDevice, s));
+        x_dev = op->x_stage;
+        xs = k;
+    }
+    r = slc_activation_quantize(op->act, x_dev, x_dtype, rows, xs, s);
+    if (r != SLC_OK) return r;
+    if (n == 0) return SLC_OK;
+    float *y_dev = y_is_device ? y : op->y_stage;
+    const long long ys = y_is_device ? y_stride : n;
+    r = run_kernels(op, op->act, y_dev, ys, nullptr, s);
+    if (r != SLC_OK) return r;
+    if (!y_is_device) {
+        SLC_CUDA(cudaMemcpy2DAsync(y, (size_t)y_stride * 4, y_dev, (size_t)n * 4, (size_t)n * 4, (size_t)rows,
+                                   cudaMemcpyDeviceToHost, s));
+        SLC_CUDA(cudaStreamSynchronize(s));
+    }
+    return SLC_OK;
+}
+
+// ---- parity exports --------------------------------------------------------------------------------------------------
+
+slc_result slc_debug_quantize(slc_device *d, const void *x, int32_t x_dtype, int64_t rows, int64_t k, int8_t *q, float *dd,
+                              float *gs)
+{
+    if (!d || rows < 0) return fail(SLC_ERR_INVALID_ARGUMENT, "bad arguments");
+    if (rows == 0) return SLC_OK;
+    if (!x || !q || !dd || !gs) return fail(SLC_ERR_INVALID_ARGUMENT, "null buffer");
+    slc_activation *a = nullptr;
+    slc_result r = slc_activation_create(d, rows, k, &a);
+    if (r != SLC_OK) return r;
+    const size_t esz = x_dtype == SLC_F32 ? 4 : 2;
+    void *xd = nullptr;
+    cudaError_t e = cudaMalloc(&xd, (size_t)rows * k * esz);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(xd, x, (size_t)rows * k * esz, cudaMemcpyHostToDevice, d->stream);
+    if (e != cudaSuccess) { slc_activation_destroy(a); if (xd) cudaFree(xd); return cuda_fail(e, "slc_debug_quantize"); }
+    r = slc_activation_quantize(a, xd, x_dtype, rows, k, d->stream);
+    if (r == SLC_OK) {
+        const int kp = a->k_pad, rp = a->rows_pad;
+        std::vector<float2> ds((size_t)(kp / 32) * rp);
+        e = cudaMemcpy2DAsync(q, (size_t)k, a->planes.q, (size_t)kp, (size_t)k, (size_t)rows, cudaMemcpyDeviceToHost, d->stream);
+        if (e == cudaSuccess) e = cudaMemcpy2DAsync(gs, (size_t)(k / 16) * 4, a->planes.gs, (size_t)(kp / 16) * 4,
+                                                    (size_t)(k / 16) * 4, (size_t)rows, cudaMemcpyDeviceToHost, d->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(ds.data(), a->planes.ds, ds.size() * 8, cudaMemcpyDeviceToHost, d->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);
+        if (e != cudaSuccess) r = cuda_fail(e, "slc_debug_quantize");
+        else {
+            for (int64_t t = 0; t < rows; t++)
+                for (int64_t b = 0; b < k / 32; b++) dd[t * (k / 32) + b] = ds[(size_t)b * rp + t].x;
+        }
+    }
+    cudaFree(xd);
+    slc_activation_destroy(a);
+    return r;
+}
+
+slc_result slc_debug_block_dots(slc_matmul *op, const void *x, int32_t x_dtype, int64_t rows, int32_t *s32)
+{
+    if (!op || rows < 0) return fail(SLC_ERR_INVALID_ARGUMENT, "bad arguments");
+    if (rows > op->max_rows) return fail(SLC_ERR_INVALID_STATE, "rows exceed the op's compiled bound");
+    const long long n = op->w->n, k = op->w->k;
+    if (rows == 0 || n == 0) return SLC_OK;
+    if (!x || !s32) return fail(SLC_ERR_INVALID_ARGUMENT, "null buffer");
+    slc_device *d = op->dev;
+    SLC_CUDA(cudaSetDevice(d->index));
+    slc_result r = ensure_op_buffers(op, true, true);
+    if (r != SLC_OK) return r;
+    const size_t esz = x_dtype == SLC_F32 ? 4 : 2;
+    const size_t dump_bytes = (size_t)rows * n * (k / 32) * 4;
+    int *dump = nullptr;
+    SLC_CUDA(cudaMalloc(&dump, dump_bytes));
+    cudaError_t e = cudaMemsetAsync(dump, 0xff, dump_bytes, d->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(op->x_stage, x, (size_t)rows * k * esz, cudaMemcpyHostToDevice, d->stream);
+    if (e != cudaSuccess) { cudaFree(dump); return cuda_fail(e, "slc_debug_block_dots"); }
+    r = slc_activation_quantize(op->act, op->x_stage, x_dtype, rows, k, d->stream);
+    if (r == SLC_OK) r = run_kernels(op, op->act, op->y_stage, n, dump, d->stream);
+    if (r == SLC_OK) {
+        e = cudaMemcpyAsync(s32, dump, dump_bytes, cudaMemcpyDeviceToHost, d->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);
+        if (e != cudaSuccess) r = cuda_fail(e, "slc_debug_block_dots");
+    }
+    cudaFree(dump);
+    return r;
+}
+
+}  // extern "C"

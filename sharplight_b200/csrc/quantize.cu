@@ -1,0 +1,81 @@
+// Activation quantization to 8 bits per 32-value block, bit-identical to the reference's CPU rule
+// (src/Sharplight.Cpu/IntDot.cs:92-126 of the Sharplight tree): d = max|x| / 127, id = d != 0 ? 1 / d : 0,
+// q = (int)(x * id + copysign(0.5, x * id)) -- round half away from zero through truncation, every step a separately
+// rounded IEEE single operation (no fused multiply-add, no approximate division).
+// Eight lanes share a block (four values each); amax and the sums travel by lane shuffles.
+#include "internal.cuh"
+
+#include <cuda_bf16.h>
+
+namespace slc {
+
+template <int DTYPE>
+__global__ void __launch_bounds__(256) quantize_kernel(const void *__restrict__ xv, int rows, int rows_pad, int k,
+                                                       int k_pad, long long x_stride, ActPlanes out)
+{
+    const int nblk_pad = k_pad >> 5;
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long blk_global = tid >> 3;
+    // rows_pad and nblk_pad are multiples of 8, so the grid covers the blocks exactly and every lane of a warp
+    // reaches the shuffles below
+    const int sub = (int)(tid & 7);
+    const int row = (int)(blk_global / nblk_pad), blk = (int)(blk_global % nblk_pad);
+    const bool live = row < rows && blk * 32 < k;
+
+    float v[4] = { 0.f, 0.f, 0.f, 0.f };
+    if (live) {
+        const long long base = (long long)row * x_stride + blk * 32 + sub * 4;
+        if (DTYPE == 0) {
+            const float *x = (const float *)xv + base;
+            if ((((uintptr_t)x) & 15) == 0) {
+                const float4 f = *reinterpret_cast<const float4 *>(x);
+                v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+            } else {
+                for (int i = 0; i < 4; i++) v[i] = x[i];
+            }
+        } else {
+            const __nv_bfloat16 *x = (const __nv_bfloat16 *)xv + base;
+            for (int i = 0; i < 4; i++) v[i] = __bfloat162float(x[i]);  // exact widening
+        }
+    }
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    int r[4];
+    int s = 0;
+    for (int i = 0; i < 4; i++) {
+        const float w = __fmul_rn(v[i], id);
+        r[i] = __float2int_rz(__fadd_rn(w, copysignf(0.5f, w)));
+        s += r[i];
+    }
+    const unsigned packed = (unsigned)(r[0] & 0xff) | ((unsigned)(r[1] & 0xff) << 8) | ((unsigned)(r[2] & 0xff) << 16) |
+                            ((unsigned)(r[3] & 0xff) << 24);
+    *reinterpret_cast<unsigned *>(out.q + (long long)row * k_pad + blk * 32 + sub * 4) = packed;
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);        // sum of this lane's 16-value group
+    const int s_other = __shfl_xor_sync(0xffffffffu, s, 4);
+    if ((sub & 3) == 0) {
+        out.gs[(long long)row * (k_pad >> 4) + blk * 2 + (sub >> 2)] = __fmul_rn(d, (float)s);
+    }
+    if (sub == 0) {
+        const int s32 = s + s_other;
+        out.ds[(long long)blk * rows_pad + row] = make_float2(d, __fmul_rn(d, (float)s32));
+        out.isum[(long long)row * nblk_pad + blk] = s32;
+    }
+}
+
+cudaError_t launch_quantize(const void *x, int x_dtype, int rows, int rows_pad, int k, int k_pad, long long x_stride,
+                            ActPlanes out, cudaStream_t stream)
+{
+    const long long threads = (long long)rows_pad * (k_pad >> 5) * 8;
+    if (threads == 0) return cudaSuccess;
+    const unsigned grid = (unsigned)((threads + 255) / 256);
+    if (x_dtype == 0) quantize_kernel<0><<<grid, 256, 0, stream>>>(x, rows, rows_pad, k, k_pad, x_stride, out);
+    else quantize_kernel<1><<<grid, 256, 0, stream>>>(x, rows, rows_pad, k, k_pad, x_stride, out);
+    return cudaGetLastError();
+}
+
+}  // namespace slc

@@ -1,0 +1,492 @@
+"""Host side of the CUDA execution provider, mirroring the reference's provider contract for the MatMul path.
+
+The managed provider (Sharplight.Cuda) is C#; this module is the same surface in Python over the same C ABI, so the
+parity tests read like the reference's own: ``CudaExecutionProvider`` (IExecutionProvider,
+src/Sharplight.Core/Runtime/IExecutionProvider.cs:25-74 of the Sharplight tree), ``CudaDevice`` (IComputeDevice,
+IComputeDevice.cs:6-67), ``CudaSegment`` (ICompiledSegment, ICompiledSegment.cs:6-25) and ``MatMulOp`` (the CPU
+provider's operator, src/Sharplight.Cpu/MatMulOp.cs:88-160). Names, argument meaning and error behaviour follow the
+reference; .NET exception types map to the classes below.
+
+Everything computes on the GPU through libsharplight_cuda.so. Nothing here falls back to the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+
+from . import native as N
+
+
+class ArgumentError(ValueError):
+    """System.ArgumentException."""
+
+
+class InvalidOperationError(RuntimeError):
+    """System.InvalidOperationException."""
+
+
+class ObjectDisposedError(InvalidOperationError):
+    """System.ObjectDisposedException."""
+
+
+class NotSupportedError(NotImplementedError):
+    """System.NotSupportedException."""
+
+
+class InsufficientMemoryError(MemoryError):
+    """System.InsufficientMemoryException."""
+
+
+_EXC = {N.ERR_INVALID_ARGUMENT: ArgumentError, N.ERR_OUT_OF_MEMORY: InsufficientMemoryError,
+        N.ERR_UNSUPPORTED: NotSupportedError, N.ERR_INVALID_STATE: InvalidOperationError,
+        N.ERR_NO_DEVICE: NotSupportedError}
+
+
+def _check(code: int) -> None:
+    """Native result -> the exception the managed wrapper throws."""
+    if code >= 0:
+        return
+    lib = N.load()
+    detail = lib.slc_last_error_message().decode() or lib.slc_error_string(code).decode()
+    raise _EXC.get(code, N.NativeError)(detail) if code in _EXC else N.NativeError(code, detail)
+
+
+DATA_TYPES = {"Q4_0": N.FMT_Q4_0, "Q8_0": N.FMT_Q8_0, "Q4_K": N.FMT_Q4_K, "Q6_K": N.FMT_Q6_K}
+
+# DeviceFeatures names the device reports (src/Sharplight.Core/Runtime/DeviceFeatures.cs:28,54)
+FEATURES = frozenset({"int_dot", "matrix_int8", "subgroup_ops", "fp16", "bf16"})
+
+
+@dataclass(frozen=True)
+class ProviderAvailability:
+    available: bool
+    reason: str = ""
+
+
+@dataclass(frozen=True)
+class DeviceInfo:
+    """The fields of src/Sharplight.Core/Runtime/DeviceInfo.cs:4-50 this provider fills."""
+    provider: str
+    index: int
+    name: str
+    kind: str
+    total_memory: int
+    vendor: str
+    driver: str
+    uuid: bytes
+    features: frozenset
+    concurrent_workgroups: int
+    sm_count: int = 0
+    compute_capability: tuple = (0, 0)
+
+
+@dataclass(frozen=True)
+class OpSupport:
+    supported: bool
+    reason: str = ""
+
+    @staticmethod
+    def yes() -> "OpSupport":
+        return OpSupport(True)
+
+    @staticmethod
+    def no(reason: str) -> "OpSupport":
+        return OpSupport(False, reason)
+
+
+@dataclass
+class WeightInfo:
+    """A static weight as the importer describes it: type name, shape [N, K], raw ggml blocks."""
+    type: str
+    shape: Sequence[int]
+    blocks: np.ndarray
+
+
+@dataclass
+class MatMulNode:
+    """StandardOps.MatMul (src/Sharplight.Core/Graph/StandardOps.cs:144-163): y = x . W^T."""
+    name: str
+    x: str                     # input value name, f32 or bf16 [T, K]
+    weight: WeightInfo
+    y: str                     # output value name, f32 [T, N]
+    x_dtype: str = "f32"
+    f32_activations: bool = False   # StandardOps.cs:130-135: the node opts out of 8-bit activations
+
+
+@dataclass
+class GraphSegment:
+    nodes: List[MatMulNode]
+    inputs: List[str]
+    outputs: List[str]
+
+
+@dataclass
+class CompileOptions:
+    """The knobs of src/Sharplight.Core/Runtime/CompileOptions.cs:4-60 the MatMul path reads."""
+    max_rows: int = 1                       # bound of the symbolic row count T
+    disabled_features: frozenset = frozenset()
+    allow_reduced_precision: bool = False
+    row_invariant_rows: int = 0
+
+
+class CudaExecutionProvider:
+    """IExecutionProvider "cuda". Cheap to construct; touches the driver only in check_availability / get_devices."""
+
+    name = "cuda"
+    portable_code_format = None   # kernels are compiled ahead of time into the shared library
+
+    def __init__(self):
+        self._disposed = False
+
+    def check_availability(self) -> ProviderAvailability:
+        """Never raises (the catalog wraps providers the same way, ExecutionProviderCatalog.cs:28-47)."""
+        try:
+            lib = N.load()
+            count = C.c_int32(0)
+            rc = lib.slc_device_count(C.byref(count))
+            if rc != N.OK:
+                return ProviderAvailability(False, lib.slc_last_error_message().decode())
+            for i in range(count.value):
+                info = N.DeviceInfoStruct()
+                if lib.slc_device_info_get(i, C.byref(info)) == N.OK and info.supported:
+                    return ProviderAvailability(True)
+            return ProviderAvailability(False, "no compute-capability 10.0 device")
+        except Exception as e:  # library missing, ABI mismatch
+            return ProviderAvailability(False, str(e))
+
+    def get_devices(self) -> List[DeviceInfo]:
+        if not self.check_availability().available:
+            return []
+        lib = N.load()
+        count = C.c_int32(0)
+        _check(lib.slc_device_count(C.byref(count)))
+        out = []
+        for i in range(count.value):
+            s = N.DeviceInfoStruct()
+            _check(lib.slc_device_info_get(i, C.byref(s)))
+            if not s.supported:
+                continue
+            out.append(DeviceInfo("cuda", i, s.name.decode(), "DiscreteGpu", s.total_memory, "NVIDIA",
+                                  s.driver.decode(), bytes(s.uuid), FEATURES, s.concurrent_workgroups,
+                                  s.sm_count, (s.cc_major, s.cc_minor)))
+        return out
+
+    def open_device(self, device: DeviceInfo, options: Optional[dict] = None) -> "CudaDevice":
+        if self._disposed:
+            raise ObjectDisposedError("CudaExecutionProvider")
+        if device.provider != self.name:
+            raise ArgumentError(f"device belongs to provider '{device.provider}'")
+        if not self.check_availability().available:
+            raise NotSupportedError("the CUDA provider is unavailable")
+        return CudaDevice(device, options or {})
+
+    def can_compile_for(self, profile) -> bool:
+        return False
+
+    def dispose(self) -> None:
+        self._disposed = True
+
+
+class DeviceWeight:
+    """A weight resident on the device (slc_weight)."""
+
+    def __init__(self, device: "CudaDevice", fmt: int, n: int, k: int, handle: int):
+        self.device, self.format, self.n, self.k, self._h = device, fmt, n, k, C.c_void_p(handle)
+
+    @property
+    def handle(self):
+        if self._h is None:
+            raise ObjectDisposedError("DeviceWeight")
+        return self._h
+
+    @property
+    def device_bytes(self) -> int:
+        b = C.c_int64(0)
+        _check(N.load().slc_weight_shape(self.handle, None, None, None, C.byref(b)))
+        return b.value
+
+    def download(self) -> np.ndarray:
+        bs, bb = N.BLOCK[self.format]
+        out = np.empty(self.n * (self.k // bs) * bb, np.uint8)
+        _check(N.load().slc_weight_download(self.handle, out.ctypes.data_as(C.c_void_p), out.size))
+        return out
+
+    def dispose(self) -> None:
+        if self._h is not None:
+            N.load().slc_weight_free(self._h)
+            self._h = None
+
+
+class CudaDevice:
+    """IComputeDevice over one opened GPU (slc_device). Safe to share between threads."""
+
+    def __init__(self, info: DeviceInfo, options: dict):
+        self.info = info
+        self.options = options
+        h = C.c_void_p()
+        _check(N.load().slc_device_open(info.index, C.byref(h)))
+        self._h = h
+        disabled = frozenset(options.get("disabled_features", ()))
+        self.enabled_features = frozenset(info.features - disabled)
+
+    @property
+    def handle(self):
+        if self._h is None:
+            raise ObjectDisposedError("CudaDevice")
+        return self._h
+
+    @property
+    def available_memory(self) -> int:
+        free = C.c_int64(0)
+        _check(N.load().slc_device_memory(self.handle, C.byref(free), None))
+        return free.value
+
+    @property
+    def stream(self) -> int:
+        """The device's own cudaStream_t."""
+        return N.load().slc_device_stream(self.handle) or 0
+
+    def synchronize(self) -> None:
+        _check(N.load().slc_device_sync(self.handle))
+
+    def last_status(self) -> int:
+        v = C.c_int32(0)
+        _check(N.load().slc_last_status(self.handle, C.byref(v)))
+        return v.value
+
+    def supports(self, node) -> OpSupport:
+        """Yes only for MatMul with a static Q8_0 / Q4_0 / Q4_K / Q6_K weight whose K is a multiple of the block size
+        and activations that may be quantized to 8 bits (mirrors CpuOpSupport.CheckQuantizedMatMul,
+        src/Sharplight.Cpu/CpuOpSupport.Linear.cs:21-53); everything else goes to the placement fallback."""
+        if not isinstance(node, MatMulNode):
+            return OpSupport.no("only MatMul runs on the CUDA provider")
+        fmt = DATA_TYPES.get(node.weight.type)
+        if fmt is None:
+            return OpSupport.no(f"weight type {node.weight.type} has no CUDA kernel")
+        if len(node.weight.shape) != 2:
+            return OpSupport.no("weight must be [N, K]")
+        if node.weight.shape[1] % N.BLOCK[fmt][0] != 0:
+            return OpSupport.no(f"K={node.weight.shape[1]} is not a multiple of the {node.weight.type} block size")
+        if node.x_dtype not in ("f32", "bf16"):
+            return OpSupport.no("activations must be f32 or bf16")
+        if "int_dot" not in self.enabled_features:
+            return OpSupport.no("int_dot is disabled and this provider has no float path")
+        return OpSupport.yes()
+
+    def upload_weight(self, type_name: str, shape: Sequence[int], blocks, k_slice=None) -> DeviceWeight:
+        fmt = DATA_TYPES.get(type_name)
+        if fmt is None:
+            raise NotSupportedError(f"weight type {type_name}")
+        n, k = int(shape[0]), int(shape[1])
+        blocks = np.ascontiguousarray(blocks, np.uint8).reshape(-1)
+        h = C.c_void_p()
+        ptr = blocks.ctypes.data_as(C.c_void_p)
+        if k_slice is None:
+            _check(N.load().slc_weight_upload(self.handle, fmt, n, k, ptr, blocks.size, C.byref(h)))
+        else:
+            k0, k1 = k_slice
+            _check(N.load().slc_weight_upload_kslice(self.handle, fmt, n, k, ptr, blocks.size, k0, k1, C.byref(h)))
+            k = k1 - k0
+        return DeviceWeight(self, fmt, n, k, h.value)
+
+    def compile(self, segment: GraphSegment, options: CompileOptions) -> "CudaSegment":
+        for node in segment.nodes:
+            s = self.supports(node)
+            if not s.supported:
+                raise NotSupportedError(f"{node.name}: {s.reason}")
+        return CudaSegment(self, segment, options)
+
+    def debug_quantize(self, x: np.ndarray, dtype: int = N.F32):
+        """(q, d, gs) of the device quantizer for host rows x [rows, k]."""
+        rows, k = x.shape
+        x = np.ascontiguousarray(x)
+        q = np.empty((rows, k), np.int8)
+        d = np.empty((rows, k // 32), np.float32)
+        gs = np.empty((rows, k // 16), np.float32)
+        _check(N.load().slc_debug_quantize(self.handle, x.ctypes.data_as(C.c_void_p), dtype, rows, k,
+                                           q.ctypes.data_as(C.c_void_p), d.ctypes.data_as(C.c_void_p),
+                                           gs.ctypes.data_as(C.c_void_p)))
+        return q, d, gs
+
+    def dispose(self) -> None:
+        if self._h is not None:
+            N.load().slc_device_close(self._h)
+            self._h = None
+
+
+def to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """f32 -> bf16 bit patterns (uint16), round to nearest even."""
+    b = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    return ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
+    return (b.astype(np.uint32) << 16).view(np.float32)
+
+
+class MatMulOp:
+    """y = x . W^T for activation rows x and a quantized weight W [N, K] (src/Sharplight.Cpu/MatMulOp.cs:88-160),
+    on the integer-dot path at every row count."""
+
+    def __init__(self, device: CudaDevice, weight: DeviceWeight, max_rows: int, *, row_invariant: bool = False):
+        self.device, self.weight, self.max_rows = device, weight, max_rows
+        h = C.c_void_p()
+        flags = N.MATMUL_ROW_INVARIANT if row_invariant else N.MATMUL_DEFAULT
+        _check(N.load().slc_matmul_create(device.handle, weight.handle, max_rows, flags, C.byref(h)))
+        self._h = h
+
+    @property
+    def handle(self):
+        if self._h is None:
+            raise ObjectDisposedError("MatMulOp")
+        return self._h
+
+    def set_kernel(self, kernel: int) -> None:
+        _check(N.load().slc_matmul_set_kernel(self.handle, kernel))
+
+    def last_kernel(self):
+        k, l = C.c_int32(0), C.c_int32(0)
+        _check(N.load().slc_matmul_last_kernel(self.handle, C.byref(k), C.byref(l)))
+        return k.value, l.value
+
+    def run(self, x: np.ndarray, dtype: int = N.F32) -> np.ndarray:
+        """Host rows in, host rows out (copies inside the call)."""
+        if x.ndim != 2 or x.shape[1] != self.weight.k:
+            raise ArgumentError(f"x must be [rows, {self.weight.k}]")
+        rows = x.shape[0]
+        x = np.ascontiguousarray(x)
+        y = np.zeros((rows, self.weight.n), np.float32)
+        _check(N.load().slc_matmul_run(self.handle, x.ctypes.data_as(C.c_void_p), dtype, rows, self.weight.k, 0,
+                                       y.ctypes.data_as(C.c_void_p), max(self.weight.n, 1), 0, None))
+        return y
+
+    def run_pointers(self, x_ptr: int, dtype: int, rows: int, x_stride: int, x_is_device: bool, y_ptr: int,
+                     y_stride: int, y_is_device: bool, stream: int = 0) -> None:
+        """The raw entry point: host or device pointers, caller-owned stream (0 = the device's own)."""
+        _check(N.load().slc_matmul_run(self.handle, C.c_void_p(x_ptr), dtype, rows, x_stride, int(x_is_device),
+                                       C.c_void_p(y_ptr), y_stride, int(y_is_device),
+                                       C.c_void_p(stream) if stream else None))
+
+    def block_dots(self, x: np.ndarray, dtype: int = N.F32) -> np.ndarray:
+        """int32 [rows, N, K/32]: the unsigned-code block dots the kernels computed for host rows x."""
+        rows = x.shape[0]
+        x = np.ascontiguousarray(x)
+        s32 = np.zeros((rows, self.weight.n, self.weight.k // 32), np.int32)
+        _check(N.load().slc_debug_block_dots(self.handle, x.ctypes.data_as(C.c_void_p), dtype, rows,
+                                             s32.ctypes.data_as(C.c_void_p)))
+        return s32
+
+    def dispose(self) -> None:
+        if self._h is not None:
+            N.load().slc_matmul_destroy(self._h)
+            self._h = None
+
+
+class SharedActivation:
+    """One 8-bit copy of x serving several MatMuls (slc_activation)."""
+
+    def __init__(self, device: CudaDevice, max_rows: int, k: int):
+        self.device, self.max_rows, self.k = device, max_rows, k
+        h = C.c_void_p()
+        _check(N.load().slc_activation_create(device.handle, max_rows, k, C.byref(h)))
+        self._h = h
+
+    @property
+    def handle(self):
+        if self._h is None:
+            raise ObjectDisposedError("SharedActivation")
+        return self._h
+
+    def quantize(self, x_device_ptr: int, dtype: int, rows: int, x_stride: int, stream: int = 0) -> None:
+        _check(N.load().slc_activation_quantize(self.handle, C.c_void_p(x_device_ptr), dtype, rows, x_stride,
+                                                C.c_void_p(stream) if stream else None))
+
+    def matmul(self, op: MatMulOp, y_device_ptr: int, y_stride: int, stream: int = 0) -> None:
+        _check(N.load().slc_matmul_run_quantized(op.handle, self.handle, C.c_void_p(y_device_ptr), y_stride,
+                                                 C.c_void_p(stream) if stream else None))
+
+    def dispose(self) -> None:
+        if self._h is not None:
+            N.load().slc_activation_destroy(self._h)
+            self._h = None
+
+
+class CudaSegment:
+    """ICompiledSegment for a list of MatMul nodes: weights are uploaded at compile time, inputs are copied in
+    SetInput, Execute runs the nodes in order, GetOutput copies a result out. Error behaviour follows the CPU
+    segment (src/Sharplight.Cpu/CpuCompiledSegment.cs:96-124,149,189)."""
+
+    def __init__(self, device: CudaDevice, segment: GraphSegment, options: CompileOptions):
+        self.device, self.segment, self.options = device, segment, options
+        self._disposed = False
+        self._executed = False
+        self._inputs: Dict[str, np.ndarray] = {}
+        self._outputs: Dict[str, np.ndarray] = {}
+        self._ops: Dict[str, MatMulOp] = {}
+        self._weights: List[DeviceWeight] = []
+        row_inv = options.row_invariant_rows > 0
+        for node in segment.nodes:
+            w = device.upload_weight(node.weight.type, node.weight.shape, node.weight.blocks)
+            self._weights.append(w)
+            self._ops[node.name] = MatMulOp(device, w, options.max_rows, row_invariant=row_inv)
+
+    @property
+    def device_memory_bytes(self) -> int:
+        return sum(w.device_bytes for w in self._weights)
+
+    def _live(self):
+        if self._disposed:
+            raise ObjectDisposedError("CudaSegment")
+
+    def set_input(self, value: str, data: np.ndarray) -> None:
+        self._live()
+        if value not in self.segment.inputs:
+            raise ArgumentError(f"'{value}' is not an input of this segment")
+        node = next(n for n in self.segment.nodes if n.x == value)
+        k = node.weight.shape[1]
+        data = np.ascontiguousarray(data)
+        if data.ndim != 2 or data.shape[1] != k:
+            raise ArgumentError(f"input '{value}' must be [T, {k}]")
+        if data.shape[0] > self.options.max_rows:
+            raise ArgumentError(f"input '{value}' holds more rows than the compiled capacity")
+        self._inputs[value] = data
+
+    def execute(self, symbols: Optional[Dict[str, int]] = None) -> None:
+        self._live()
+        t = (symbols or {}).get("T")
+        if t is not None and t > self.options.max_rows:
+            raise InvalidOperationError(f"T={t} exceeds the compiled bound {self.options.max_rows}")
+        values: Dict[str, np.ndarray] = dict(self._inputs)
+        for node in self.segment.nodes:
+            if node.x not in values:
+                raise InvalidOperationError(f"input '{node.x}' was never set")
+            x = values[node.x]
+            if t is not None:
+                x = x[:t]
+            dtype = N.BF16 if node.x_dtype == "bf16" else N.F32
+            values[node.y] = self._ops[node.name].run(x, dtype)
+        self._outputs = {name: values[name] for name in self.segment.outputs}
+        self._executed = True
+
+    def get_output(self, value: str) -> np.ndarray:
+        self._live()
+        if not self._executed:
+            raise InvalidOperationError("GetOutput before Execute")
+        if value not in self._outputs:
+            raise ArgumentError(f"'{value}' is not an output of this segment")
+        return self._outputs[value]
+
+    def reset_state(self) -> None:
+        self._live()   # MatMul keeps no state
+
+    def dispose(self) -> None:
+        if self._disposed:
+            return
+        for op in self._ops.values():
+            op.dispose()
+        for w in self._weights:
+            w.dispose()
+        self._disposed = True

@@ -1,0 +1,308 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI (needs a B200).
+
+Bars: activation codes, scales and group sums bit-identical; per-block int32 dots bit-identical; fp32 outputs within
+max relative error 1e-3 of the oracle's integer-dot result on the same inputs (helpers.max_rel_error states the
+floor used for outputs that cancel to nothing). Shapes follow the reference's own tests
+(tests/Sharplight.Cpu.Tests/QuantTests.cs:119-128, tests/Sharplight.Vulkan.Tests/MatMulTests.cs:7-48, MmqTests.cs:21-98,
+SkinnyGemmTests.cs:29-39 of the Sharplight tree).
+"""
+import numpy as np
+import pytest
+
+from helpers import FMT_OF, MAX_REL, max_rel_error, relative_rms, sl_oracle
+from sharplight_b200 import (ArgumentError, CompileOptions, GraphSegment, InvalidOperationError, MatMulNode, MatMulOp,
+                             NotSupportedError, ObjectDisposedError, WeightInfo, synth)
+from sharplight_b200 import native as N
+from sharplight_b200.provider import bf16_bits_to_f32, to_bf16_bits
+from test_oracle import quantize_kat
+
+pytestmark = pytest.mark.gpu
+
+TYPES = ["Q8_0", "Q4_0", "Q4_K", "Q6_K"]
+
+
+def check_matmul(device, type_name, n, k, rows, *, seed=1, kernel=N.KERNEL_AUTO, dots=True, blocks=None, x=None,
+                 max_rows=None):
+    fmt = FMT_OF[type_name]
+    blocks = synth.weight_blocks(type_name, n, k, seed) if blocks is None else blocks
+    x = synth.activations(rows, k, seed + 1000) if x is None else x
+    w = device.upload_weight(type_name, (n, k), blocks)
+    op = MatMulOp(device, w, max_rows or max(rows, 1))
+    try:
+        if kernel != N.KERNEL_AUTO:
+            op.set_kernel(kernel)
+        y = op.run(x)
+        ref, ref64, s32 = sl_oracle.matmul_intdot(fmt, blocks, n, k, x, threads=8, want_f64=True, want_s32=dots)
+        assert y.shape == ref.shape
+        assert max_rel_error(y, ref) <= MAX_REL, (type_name, n, k, rows, op.last_kernel())
+        assert max_rel_error(y, ref64) <= MAX_REL
+        if dots and rows > 0 and n > 0:
+            got = op.block_dots(x)
+            assert np.array_equal(got, s32), (type_name, n, k, rows, op.last_kernel())
+        return y, op.last_kernel()
+    finally:
+        op.dispose()
+        w.dispose()
+
+
+# ---- activation quantization ------------------------------------------------------------------------------------
+
+def test_quantize_known_answers_bit_exact(cuda_device):
+    x = quantize_kat()
+    q, d, gs = cuda_device.debug_quantize(x)
+    rq, rd, rgs = sl_oracle.quantize(x)
+    assert np.array_equal(q, rq)
+    assert np.array_equal(d.view(np.uint32), rd.view(np.uint32))
+    assert np.array_equal(gs.view(np.uint32), rgs.view(np.uint32))
+
+
+@pytest.mark.parametrize("rows,k", [(1, 32), (3, 1568), (8, 4096), (33, 1024), (70, 256)])
+def test_quantize_random_bit_exact(cuda_device, rows, k):
+    g = np.random.Generator(np.random.Philox(rows * 7919 + k))
+    x = (g.standard_normal((rows, k)) * np.exp(g.uniform(-6, 6, (rows, 1)))).astype(np.float32)
+    x[0, :32] = 0.0
+    x[-1, -32:] = np.float32(-3.0)           # constant block: every code -127
+    x[rows // 2, ::7] *= np.float32(1e4)
+    q, d, gs = cuda_device.debug_quantize(x)
+    rq, rd, rgs = sl_oracle.quantize(x)
+    assert np.array_equal(q, rq)
+    assert np.array_equal(d.view(np.uint32), rd.view(np.uint32))
+    assert np.array_equal(gs.view(np.uint32), rgs.view(np.uint32))
+
+
+def test_quantize_bf16_input(cuda_device):
+    x = synth.activations(5, 512, 77)
+    bits = to_bf16_bits(x)
+    q, d, gs = cuda_device.debug_quantize(bits, N.BF16)
+    rq, rd, rgs = sl_oracle.quantize(bf16_bits_to_f32(bits))
+    assert np.array_equal(q, rq) and np.array_equal(d, rd) and np.array_equal(gs, rgs)
+
+
+# ---- weights ----------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("type_name", TYPES)
+@pytest.mark.parametrize("n,k", [(1, 256), (7, 512), (37, 1280), (16, 256), (4112, 512)])
+def test_weight_layout_round_trip(cuda_device, type_name, n, k):
+    """The device layout is a permutation of the raw blocks: download(upload(blocks)) == blocks."""
+    blocks = synth.weight_blocks(type_name, n, k, seed=n + k)
+    w = cuda_device.upload_weight(type_name, (n, k), blocks)
+    try:
+        assert np.array_equal(w.download(), blocks)
+        assert w.device_bytes >= blocks.size
+    finally:
+        w.dispose()
+
+
+@pytest.mark.parametrize("type_name,k", [("Q8_0", 1568), ("Q4_0", 1568), ("Q8_0", 32), ("Q4_0", 96)])
+def test_weight_round_trip_k_not_multiple_of_256(cuda_device, type_name, k):
+    blocks = synth.weight_blocks(type_name, 5, k, seed=k)
+    w = cuda_device.upload_weight(type_name, (5, k), blocks)
+    try:
+        assert np.array_equal(w.download(), blocks)
+    finally:
+        w.dispose()
+
+
+def test_upload_rejects_bad_shapes(cuda_device):
+    with pytest.raises(ArgumentError):
+        cuda_device.upload_weight("Q4_K", (4, 288), np.zeros(4 * 162, np.uint8))      # K % 256 != 0
+    with pytest.raises(ArgumentError):
+        cuda_device.upload_weight("Q8_0", (4, 64), np.zeros(10, np.uint8))            # byte count
+    with pytest.raises(NotSupportedError):
+        cuda_device.upload_weight("Q5_K", (4, 256), np.zeros(4 * 176, np.uint8))
+
+
+# ---- the operator ---------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("type_name", TYPES)
+@pytest.mark.parametrize("rows", [1, 2, 3, 4, 5, 8, 9, 16, 17, 20, 33, 40, 64, 65, 100])
+def test_matmul_row_counts(cuda_device, type_name, rows):
+    """MatMulTests.WeightFormat: K = 512, N = 96 over the row counts that cross every kernel boundary."""
+    check_matmul(cuda_device, type_name, 96, 512, rows, seed=rows)
+
+
+@pytest.mark.parametrize("type_name", TYPES)
+@pytest.mark.parametrize("n,k", [(7, 1536), (7, 2560), (7, 1024), (37, 768), (4112, 512), (1, 256), (16, 4096)])
+def test_matmul_shapes(cuda_device, type_name, n, k):
+    """QuantTests.MatMulWithIntDotMatchesReference shapes (N = 7), odd N, and SkinnyGemmTests' N = 4112."""
+    for rows in (1, 3, 16, 40):
+        check_matmul(cuda_device, type_name, n, k, rows, seed=n + rows, dots=(n * rows <= 4112 * 3))
+
+
+@pytest.mark.parametrize("type_name", ["Q8_0", "Q4_0"])
+@pytest.mark.parametrize("k", [32, 96, 1568])
+def test_matmul_k_multiple_of_32_only(cuda_device, type_name, k):
+    for rows in (1, 3, 12):
+        check_matmul(cuda_device, type_name, 7, k, rows, seed=k)
+
+
+@pytest.mark.parametrize("type_name", TYPES)
+@pytest.mark.parametrize("kernel,rows", [(N.KERNEL_MMVQ, 1), (N.KERNEL_MMVQ, 7), (N.KERNEL_MMVQ, 19), (N.KERNEL_SKINNY, 1),
+                                         (N.KERNEL_SKINNY, 2), (N.KERNEL_SKINNY, 24), (N.KERNEL_SKINNY, 130)])
+def test_each_kernel_family_at_any_row_count(cuda_device, type_name, kernel, rows):
+    _, (used, launches) = check_matmul(cuda_device, type_name, 100, 1024, rows, seed=rows, kernel=kernel)
+    assert used == kernel and launches >= 1
+
+
+@pytest.mark.parametrize("tid", [2, 8, 12, 14])
+def test_golden_fixture_rows_as_weights(cuda_device, golden, tid):
+    """The ggml-quantized (and the random-byte) fixture records as weights: device output vs the oracle, and vs the
+    double product of ggml's own decoded floats with exactly representable activations (MatMulTests.
+    IntDotExactActivations, MmqTests: atol 2e-3, rtol 1e-3)."""
+    from helpers import TYPE_OF
+    for kind in ("ggml", "random"):
+        name = f"ext_{tid}_{kind}"
+        _, rows, cols = (int(v) for v in golden[name + "_shape"])
+        blocks = golden[name + "_blocks"]
+        expected = golden[name + "_expected"].reshape(rows, cols)
+        if not np.all(np.isfinite(expected)):
+            # random bytes can decode to inf / nan scales: keep the rows whose floats are finite
+            keep = np.all(np.isfinite(expected), axis=1)
+            if not keep.any():
+                continue
+            bb = blocks.size // rows
+            blocks = blocks.reshape(rows, bb)[keep].reshape(-1)
+            expected = expected[keep]
+            rows = int(keep.sum())
+        for t in (1, 5, 20):
+            x = synth.exact_int8_activations(t, cols, seed=tid * 10 + t)
+            y, _ = check_matmul(cuda_device, TYPE_OF[tid], rows, cols, t, blocks=blocks, x=x)
+            ref = x.astype(np.float64) @ expected.astype(np.float64).T
+            scale = max(1.0, float(np.abs(ref).max()))
+            assert np.all(np.abs(y - ref) <= 2e-3 * scale + 1e-3 * np.abs(ref))
+
+
+@pytest.mark.parametrize("type_name", TYPES)
+def test_row_invariance(cuda_device, type_name):
+    """RowInvarianceTests (tests/Sharplight.Cpu.Tests/RowInvarianceTests.cs:11-57): with the row-invariant flag a
+    2-4 row step equals single-row steps bit for bit."""
+    n, k = 200, 1024
+    blocks = synth.weight_blocks(type_name, n, k, 5)
+    w = cuda_device.upload_weight(type_name, (n, k), blocks)
+    op = MatMulOp(cuda_device, w, 8, row_invariant=True)
+    try:
+        x = synth.activations(8, k, 6)
+        single = np.concatenate([op.run(x[i:i + 1]) for i in range(8)])
+        for rows in (2, 3, 4, 8):
+            multi = op.run(x[:rows])
+            assert np.array_equal(multi.view(np.uint32), single[:rows].view(np.uint32))
+    finally:
+        op.dispose()
+        w.dispose()
+
+
+def test_int8_exact_activations_match_float_product(cuda_device):
+    """With activations the quantizer represents exactly, the integer-dot result equals the product with the
+    dequantized weight up to f32 rounding (MmqTests.cs:71-78: atol 2e-3, rtol 1e-3)."""
+    for type_name in TYPES:
+        n, k = 96, 1024
+        blocks = synth.weight_blocks(type_name, n, k, 21)
+        for rows in (2, 65):
+            x = synth.exact_int8_activations(rows, k, 22)
+            y, _ = check_matmul(cuda_device, type_name, n, k, rows, blocks=blocks, x=x, dots=False)
+            exact = sl_oracle.matmul_f64(FMT_OF[type_name], blocks, n, k, x, threads=8)
+            assert np.all(np.abs(y - exact) <= 2e-3 + 1e-3 * np.abs(exact))
+
+
+def test_bf16_activations(cuda_device):
+    n, k, rows = 64, 512, 6
+    blocks = synth.weight_blocks("Q4_0", n, k, 31)
+    bits = to_bf16_bits(synth.activations(rows, k, 32))
+    w = cuda_device.upload_weight("Q4_0", (n, k), blocks)
+    op = MatMulOp(cuda_device, w, rows)
+    try:
+        y = op.run(bits, N.BF16)
+        ref, _, _ = sl_oracle.matmul_intdot(2, blocks, n, k, bf16_bits_to_f32(bits))
+        assert max_rel_error(y, ref) <= MAX_REL
+    finally:
+        op.dispose()
+        w.dispose()
+
+
+def test_edge_cases_and_errors(cuda_device):
+    blocks = synth.weight_blocks("Q8_0", 8, 64, 1)
+    w = cuda_device.upload_weight("Q8_0", (8, 64), blocks)
+    op = MatMulOp(cuda_device, w, 4)
+    assert op.run(np.zeros((0, 64), np.float32)).shape == (0, 8)          # empty input is a no-op
+    with pytest.raises(InvalidOperationError):
+        op.run(np.zeros((5, 64), np.float32))                             # rows beyond the compiled bound
+    with pytest.raises(ArgumentError):
+        op.run(np.zeros((1, 32), np.float32))                             # wrong K
+    y = op.run(np.zeros((2, 64), np.float32))
+    assert not y.any()                                                    # all-zero activations: zero scales
+    op.dispose()
+    with pytest.raises(ObjectDisposedError):
+        op.run(np.zeros((1, 64), np.float32))
+    w.dispose()
+    empty = cuda_device.upload_weight("Q4_K", (0, 256), np.zeros(0, np.uint8))   # a weight with no rows
+    op = MatMulOp(cuda_device, empty, 2)
+    assert op.run(np.ones((2, 256), np.float32)).shape == (2, 0)
+    op.dispose()
+    empty.dispose()
+    assert cuda_device.last_status() == 0
+
+
+def test_segment_contract(cuda_device):
+    """ICompiledSegment behaviour (src/Sharplight.Cpu/CpuCompiledSegment.cs:96-124,149,189)."""
+    k, n1, n2 = 512, 48, 80
+    w1 = WeightInfo("Q4_K", (n1, k), synth.weight_blocks("Q4_K", n1, k, 1))
+    w2 = WeightInfo("Q8_0", (n2, k), synth.weight_blocks("Q8_0", n2, k, 2))
+    seg = GraphSegment([MatMulNode("gate", "x", w1, "g"), MatMulNode("up", "x", w2, "u")], ["x"], ["g", "u"])
+    compiled = cuda_device.compile(seg, CompileOptions(max_rows=8))
+    assert compiled.device_memory_bytes > 0
+    with pytest.raises(InvalidOperationError):
+        compiled.get_output("g")                                          # before Execute
+    with pytest.raises(ArgumentError):
+        compiled.set_input("nope", np.zeros((1, k), np.float32))
+    with pytest.raises(ArgumentError):
+        compiled.set_input("x", np.zeros((9, k), np.float32))             # beyond the compiled capacity
+    x = synth.activations(8, k, 3)
+    compiled.set_input("x", x)
+    with pytest.raises(InvalidOperationError):
+        compiled.execute({"T": 9})
+    compiled.execute({"T": 5})
+    g = compiled.get_output("g")
+    ref, _, _ = sl_oracle.matmul_intdot(12, w1.blocks, n1, k, x[:5])
+    assert g.shape == (5, n1) and max_rel_error(g, ref) <= MAX_REL
+    ref2, _, _ = sl_oracle.matmul_intdot(8, w2.blocks, n2, k, x[:5])
+    assert max_rel_error(compiled.get_output("u"), ref2) <= MAX_REL
+    compiled.dispose()
+    with pytest.raises(ObjectDisposedError):
+        compiled.execute({"T": 1})
+    with pytest.raises(NotSupportedError):
+        cuda_device.compile(GraphSegment([MatMulNode("m", "x", WeightInfo("Q5_K", (4, 256), np.zeros(704, np.uint8)),
+                                                     "y")], ["x"], ["y"]), CompileOptions())
+
+
+# ---- the benchmark configurations at full size ------------------------------------------------------------------
+
+def test_config1_q8_0_qwen_up_proj(cuda_device):
+    check_matmul(cuda_device, "Q8_0", 3072, 1024, 1, seed=101)
+
+
+@pytest.mark.parametrize("rows", [1, 4, 16, 64])
+def test_config2_q4_k_llama8b_ffn(cuda_device, rows):
+    check_matmul(cuda_device, "Q4_K", 14336, 4096, rows, seed=102, dots=(rows <= 4))
+
+
+def test_intdot_stays_close_to_exact_product_at_full_size(cuda_device):
+    """Size-independent property at the benchmark shape: 8-bit activations cost < 1e-2 relative RMS."""
+    n, k, rows = 14336, 4096, 4
+    blocks = synth.weight_blocks("Q4_K", n, k, 102)
+    x = synth.activations(rows, k, 103)
+    w = cuda_device.upload_weight("Q4_K", (n, k), blocks)
+    op = MatMulOp(cuda_device, w, rows)
+    try:
+        y = op.run(x)
+        exact = sl_oracle.matmul_f64(12, blocks, n, k, x, threads=8)
+        assert relative_rms(y, exact) < 1e-2
+        # linearity in the weight rows: permuting rows of W permutes columns of y
+        perm = np.random.Generator(np.random.Philox(9)).permutation(n)
+        wp = cuda_device.upload_weight("Q4_K", (n, k), blocks.reshape(n, -1)[perm].reshape(-1))
+        opp = MatMulOp(cuda_device, wp, rows)
+        assert np.array_equal(opp.run(x), y[:, perm])
+        opp.dispose()
+        wp.dispose()
+    finally:
+        op.dispose()
+        w.dispose()
