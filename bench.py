@@ -1,0 +1,293 @@
+"""Benchmark of the quantized MatMul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--rows M]
+
+One JSON line on stdout (rank 0). Metric: quantized mat-vec HBM GB/s = weight bytes streamed per second, the figure the
+reference's own benchmark reports (tests/Sharplight.Cpu.Tests/BenchTests.cs:82-99 of the Sharplight tree).
+
+Workload at N = 1: BASELINE config 2, the Llama-3-8B FFN shape -- Q4_K weight [14336, 4096], f32 activations ~N(0,1),
+M = 1 row. One step = the MatMul (8-bit activation quantization + mat-vec) over each of COPIES independent weight
+matrices of that shape (COPIES x 33 MB is far larger than the 126 MB L2, so every weight byte comes from HBM).
+  value : device-resident inputs and outputs, timed with CUDA events on the launching stream.
+  e2e   : the same step through the provider API with HOST buffers (pinned): host->device copy of x, kernels,
+          device->host copy of y inside the timed region.
+  roofline : the mat-vec kernel alone (activations already quantized), algorithmic bytes / measured launch time.
+  cpu_baseline : the CPU restatement of the reference's integer-dot MatMul (oracle/) on the host cores, bounded sample.
+With --impl reference the CPU arm is the measured one (the reference's managed CPU provider cannot be built here: no
+.NET toolchain; the restatement is labelled "port").
+For N > 1 every rank streams its own COPIES matrices (weak scaling, no data-path collective for this workload).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+TYPE, N_ROWS_W, K_COLS = "Q4_K", 14336, 4096
+COPIES = 32
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _once(self):
+        nv = self._nv
+        self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+        try:
+            bits = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+        except Exception:
+            bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+                 0x80: "hw_power_brake"}
+        for bit, name in names.items():
+            if bits & bit:
+                self.reasons.add(name)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self._once()
+            except Exception:
+                return
+            self._stop.wait(0.01)
+
+    def start(self):
+        if self._nv:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def cpu_arm(rows: int, seconds: float = 12.0):
+    """The reference's CPU integer-dot MatMul (restated in oracle/) on all host cores; bounded sample."""
+    from oracle import sl_oracle
+    from sharplight_b200 import synth
+    threads = os.cpu_count() or 1
+    copies = 8   # 264 MB of distinct weights, so the sample does not sit in the last-level cache
+    blocks = [synth.weight_blocks(TYPE, N_ROWS_W, K_COLS, seed=200 + i) for i in range(copies)]
+    x = synth.activations(rows, K_COLS, seed=300)
+    wbytes = synth.weight_bytes(TYPE, N_ROWS_W, K_COLS)
+    for i in range(2):
+        sl_oracle.matmul_intdot(12, blocks[i], N_ROWS_W, K_COLS, x, threads=threads, tier=1)
+    t0 = time.perf_counter()
+    done = 0
+    while True:
+        sl_oracle.matmul_intdot(12, blocks[done % copies], N_ROWS_W, K_COLS, x, threads=threads, tier=1)
+        done += 1
+        el = time.perf_counter() - t0
+        if el > seconds or done >= 4000:
+            break
+    return {"value": wbytes * done / el / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "tier": sl_oracle.fast_tier_name(),
+            "sample": f"{done} mat-vecs of the {TYPE} [{N_ROWS_W},{K_COLS}] weight at M={rows} over {copies} rotating "
+                      f"copies, {el:.1f} s, {threads} threads"}, el / done
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    seconds = max(3.0, min(60.0, 0.25 * (args.steps + args.warmup)))
+    base, per_matvec = cpu_arm(args.rows, seconds)
+    line = {"impl": "reference", "metric": "quant mat-vec HBM GB/s", "value": base["value"], "unit": "GB/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_matvec * COPIES * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int8 -> int32, f32 scales",
+            "data": "synthetic",
+            "config": {"workload": f"configs[1]: {TYPE} [{N_ROWS_W},{K_COLS}] mat-vec, M={args.rows}; bounded sample, "
+                                   f"step time extrapolated to {COPIES} matrices"},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "CPU restatement (oracle/) of the reference's Sharplight.Cpu integer-dot MatMul; the managed "
+                    "reference cannot be built here (no .NET toolchain)"}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from sharplight_b200 import CudaExecutionProvider, MatMulOp, SharedActivation, synth
+    from sharplight_b200 import native as N
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    provider = CudaExecutionProvider()
+    av = provider.check_availability()
+    if not av.available:
+        raise RuntimeError("CUDA provider unavailable (no CPU fallback): " + av.reason)
+    device = provider.open_device([d for d in provider.get_devices() if d.index == local][0])
+    rows, n, k = args.rows, N_ROWS_W, K_COLS
+    wbytes = synth.weight_bytes(TYPE, n, k)
+
+    base_blocks = synth.weight_blocks(TYPE, n, k, seed=100 + rank)
+    weights, ops = [], []
+    for i in range(COPIES):
+        blocks = np.roll(base_blocks.reshape(n, -1), i * 37, axis=0).reshape(-1)   # distinct matrices, cheap to make
+        w = device.upload_weight(TYPE, (n, k), blocks)
+        weights.append(w)
+        ops.append(MatMulOp(device, w, max(rows, 1)))
+    x_host = torch.from_numpy(synth.activations(rows, k, seed=7)).pin_memory()
+    y_host = torch.empty((COPIES, rows, n), dtype=torch.float32).pin_memory()
+    x_dev = x_host.cuda()
+    y_dev = torch.empty((COPIES, rows, n), dtype=torch.float32, device="cuda")
+    stream = torch.cuda.current_stream()
+    sptr = stream.cuda_stream
+    act = SharedActivation(device, max(rows, 1), k)
+
+    def step_device():
+        for i, op in enumerate(ops):
+            op.run_pointers(x_dev.data_ptr(), N.F32, rows, k, True, y_dev[i].data_ptr(), n, True, sptr)
+
+    def step_kernel_only():
+        for i, op in enumerate(ops):
+            act.matmul(op, y_dev[i].data_ptr(), n, sptr)
+
+    def step_host():
+        for i, op in enumerate(ops):
+            op.run_pointers(x_host.data_ptr(), N.F32, rows, k, False, y_host[i].data_ptr(), n, False, sptr)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms_step = timed(step_device, args.steps, max(args.warmup, 3))
+    clocks = sampler.stop()
+    kernel_family, launches_per_call = ops[0].last_kernel()   # launches of one MatMul call, quantization included
+    if launches_per_call == 1:
+        # quantization is fused into the mat-vec kernel: the device-timed step is the kernel
+        ms_kernel_step, main_launches = ms_step, 1
+    else:
+        # kernel-only pass for the roofline: activations quantized once, only the MatMul kernel in the loop
+        act.quantize(x_dev.data_ptr(), N.F32, rows, k, sptr)
+        ms_kernel_step = timed(step_kernel_only, args.steps, 3)
+        main_launches = launches_per_call - 1
+    # end to end through host buffers
+    t_wall0 = time.perf_counter()
+    ms_e2e = timed(step_host, max(3, args.steps // 4), 3) if not args.no_e2e else float("nan")
+    _ = time.perf_counter() - t_wall0
+
+    # a last correctness look at what was timed: device result == host-path result
+    torch.cuda.synchronize()
+    same = bool(torch.equal(y_dev.cpu(), y_host)) if not args.no_e2e else None
+
+    peak, peak_kind = measured_peaks()
+    algo_bytes = wbytes + rows * k + rows * (k // 32) * 8 + rows * n * 4
+    sec_per_launch = ms_kernel_step * 1e-3 / (COPIES * main_launches)
+    achieved = algo_bytes / sec_per_launch / 1e9
+    value = world * COPIES * wbytes / (ms_step * 1e-3) / 1e9
+    e2e = world * COPIES * wbytes / (ms_e2e * 1e-3) / 1e9
+
+    if rank == 0:
+        base = None
+        if world == 1 and not args.no_cpu:
+            base, _ = cpu_arm(rows)
+        line = {"metric": "quant mat-vec HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
+                "config": {"workload": f"configs[1]: {TYPE} [{n},{k}] mat-vec (quantize + kernel), M={rows}, "
+                                       f"{COPIES} weight matrices per step per GPU",
+                           "l2": f"inputs larger than L2: {COPIES * wbytes / 1e6:.0f} MB of weights per step vs 126 MB",
+                           "kernel_family": {1: "mmvq (dp4a)", 2: "skinny (int8 mma)", 3: "mmq (tcgen05)"}[kernel_family]},
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                             "traffic": None, "peak_source": peak_kind, "kernel_us": sec_per_launch * 1e6,
+                             "algorithmic_bytes_per_launch": algo_bytes, "frac_of_nominal_8000": achieved / 8000.0},
+                "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": COPIES * rows * k * 4,
+                        "d2h_bytes_per_step": COPIES * rows * n * 4, "ms_per_step": ms_e2e},
+                "gpu_launches": args.steps * COPIES * launches_per_call,
+                "clocks": clocks, "device_equals_host_path": same}
+        if base is not None:
+            line["cpu_baseline"] = base
+        print(json.dumps(line), flush=True)
+    for op in ops:
+        op.dispose()
+    for w in weights:
+        w.dispose()
+    act.dispose()
+    device.dispose()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    global COPIES
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--copies", type=int, default=COPIES, help="weight matrices per step (profiling runs use fewer)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    args = ap.parse_args()
+    COPIES = args.copies
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

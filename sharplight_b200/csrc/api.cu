@@ -52,6 +52,7 @@ struct slc_matmul
     uint32_t flags = 0;
     int forced_kernel = SLC_KERNEL_AUTO;
     int last_kernel = 0, last_launches = 0;
+    int last_launches_total = 0;    // including the activation quantization, when it was a launch of its own
     slc_activation *act = nullptr;  // the op's own quantized copy (slc_matmul_run)
     void *x_stage = nullptr;        // device staging for host activations (max_rows x k, 4 bytes each)
     float *y_stage = nullptr;       // device staging for host outputs (max_rows x n)
@@ -507,7 +508,7 @@ slc_result slc_matmul_last_kernel(slc_matmul *op, int32_t *out_kernel, int32_t *
 {
     if (!op) return fail(SLC_ERR_INVALID_ARGUMENT, "op is null");
     if (out_kernel) *out_kernel = op->last_kernel;
-    if (out_launches) *out_launches = op->last_launches;
+    if (out_launches) *out_launches = op->last_launches_total > 0 ? op->last_launches_total : op->last_launches;
     return SLC_OK;
 }
 
@@ -523,6 +524,36 @@ static int choose_kernel(const slc_matmul *op, int rows)
     return SLC_KERNEL_MMQ;
 }
 
+// Whether the rows of this call go through the fused quantize + dp4a kernel (matvec_fused.cu) straight from x.
+static bool use_fused(const slc_matmul *op, int rows)
+{
+    if (choose_kernel(op, rows) != SLC_KERNEL_MMVQ) return false;
+    const int k_pad = op->w->view.k_pad;
+    if (op->flags & SLC_MATMUL_ROW_INVARIANT) return rows <= 8 && fused_matvec_fits(1, k_pad);
+    return fused_matvec_fits(rows, k_pad);
+}
+
+// Fused path: chunks of up to 4 rows (one row at a time under the row-invariant flag would give the same bits; a
+// chunk's rows are computed independently of each other, so chunks of 4 keep the guarantee).
+static slc_result run_fused(slc_matmul *op, const void *x, int x_dtype, long long x_stride, int rows, float *y,
+                            long long y_stride, int *dump, cudaStream_t s)
+{
+    const WeightView &wv = op->w->view;
+    const size_t esz = x_dtype == SLC_F32 ? 4 : 2;
+    const long long dump_row = (long long)wv.n * (wv.k >> 5);
+    op->last_kernel = SLC_KERNEL_MMVQ;
+    op->last_launches = 0;
+    int chunk = 4;
+    while (chunk > 1 && !fused_matvec_fits(chunk, wv.k_pad)) chunk--;
+    for (int r0 = 0; r0 < rows; r0 += chunk) {
+        const int m = rows - r0 < chunk ? rows - r0 : chunk;
+        SLC_CUDA(launch_fused_matvec(wv, (const uint8_t *)x + (size_t)r0 * x_stride * esz, x_dtype, x_stride, m,
+                                     y + r0 * y_stride, y_stride, dump ? dump + r0 * dump_row : nullptr, s));
+        op->last_launches++;
+    }
+    return SLC_OK;
+}
+
 static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, long long y_stride, int *dump,
                               cudaStream_t s)
 {
@@ -533,6 +564,7 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
     const long long dump_row = (long long)wv.n * (wv.k >> 5);
     op->last_kernel = kernel;
     op->last_launches = 0;
+    op->last_launches_total = 0;
     if (kernel == SLC_KERNEL_MMVQ) {
         for (int r0 = 0; r0 < rows; r0 += 8) {
             const int m = rows - r0 < 8 ? rows - r0 : 8;
@@ -602,13 +634,20 @@ slc_result slc_matmul_run(slc_matmul *op, const void *x, int32_t x_dtype, int64_
         x_dev = op->x_stage;
         xs = k;
     }
-    r = slc_activation_quantize(op->act, x_dev, x_dtype, rows, xs, s);
-    if (r != SLC_OK) return r;
     if (n == 0) return SLC_OK;
     float *y_dev = y_is_device ? y : op->y_stage;
     const long long ys = y_is_device ? y_stride : n;
-    r = run_kernels(op, op->act, y_dev, ys, nullptr, s);
-    if (r != SLC_OK) return r;
+    if (use_fused(op, (int)rows)) {
+        r = run_fused(op, x_dev, x_dtype, xs, (int)rows, y_dev, ys, nullptr, s);
+        if (r != SLC_OK) return r;
+        op->last_launches_total = op->last_launches;
+    } else {
+        r = slc_activation_quantize(op->act, x_dev, x_dtype, rows, xs, s);
+        if (r != SLC_OK) return r;
+        r = run_kernels(op, op->act, y_dev, ys, nullptr, s);
+        if (r != SLC_OK) return r;
+        op->last_launches_total = op->last_launches + 1;
+    }
     if (!y_is_device) {
         SLC_CUDA(cudaMemcpy2DAsync(y, (size_t)y_stride * 4, y_dev, (size_t)n * 4, (size_t)n * 4, (size_t)rows,
                                    cudaMemcpyDeviceToHost, s));
@@ -671,8 +710,12 @@ slc_result slc_debug_block_dots(slc_matmul *op, const void *x, int32_t x_dtype, 
     cudaError_t e = cudaMemsetAsync(dump, 0xff, dump_bytes, d->stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(op->x_stage, x, (size_t)rows * k * esz, cudaMemcpyHostToDevice, d->stream);
     if (e != cudaSuccess) { cudaFree(dump); return cuda_fail(e, "slc_debug_block_dots"); }
-    r = slc_activation_quantize(op->act, op->x_stage, x_dtype, rows, k, d->stream);
-    if (r == SLC_OK) r = run_kernels(op, op->act, op->y_stage, n, dump, d->stream);
+    if (use_fused(op, (int)rows)) {
+        r = run_fused(op, op->x_stage, x_dtype, k, (int)rows, op->y_stage, n, dump, d->stream);
+    } else {
+        r = slc_activation_quantize(op->act, op->x_stage, x_dtype, rows, k, d->stream);
+        if (r == SLC_OK) r = run_kernels(op, op->act, op->y_stage, n, dump, d->stream);
+    }
     if (r == SLC_OK) {
         e = cudaMemcpyAsync(s32, dump, dump_bytes, cudaMemcpyDeviceToHost, d->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);

@@ -25,6 +25,12 @@ cudaError_t launch_quantize(const void *x, int x_dtype, int rows, int rows_pad, 
 cudaError_t launch_mmvq(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
                         int *dump, cudaStream_t stream);
 
+// matvec_fused.cu: quantization fused into the dp4a mat-vec, 1..4 activation rows of device-resident x
+// (f32 or bf16, rows x_stride elements apart); y rows y_stride apart. dump as for launch_mmvq.
+bool fused_matvec_fits(int rows, int k_pad);
+cudaError_t launch_fused_matvec(const WeightView &w, const void *x, int x_dtype, long long x_stride, int rows, float *y,
+                                long long y_stride, int *dump, cudaStream_t stream);
+
 // skinny.cu: int8 mma tiles, 1..64 activation rows per launch.
 cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
                           int *dump, cudaStream_t stream);
