@@ -309,18 +309,12 @@ slc_result slc_weight_upload(slc_device *d, int32_t fmt, int64_t n, int64_t k, c
     if (!w) return fail(SLC_ERR_OUT_OF_MEMORY, "host allocation failed");
     w->dev = d; w->fmt = fmt; w->n = n; w->k = k;
     const int n_pad = (int)round_up((size_t)n, 16), k_pad = (int)round_up((size_t)k, 256);
-    const size_t qs_b = round_up(weight_qs_bytes(fmt, n_pad, k_pad), 256);
-    const size_t sc_b = round_up(weight_sc_bytes(fmt, n_pad, k_pad), 256);
-    const size_t d6_b = weight_d6_bytes(fmt, n_pad, k_pad);
-    w->bytes = qs_b + sc_b + d6_b + 256;
+    w->bytes = round_up(weight_bytes(fmt, n_pad, k_pad), 256) + 256;
     uint8_t *raw = nullptr;
     cudaError_t e = cudaMalloc(&w->base, w->bytes);
     if (e == cudaSuccess && bytes > 0) e = cudaMalloc(&raw, (size_t)bytes);
     if (e == cudaSuccess && bytes > 0) e = cudaMemcpyAsync(raw, blocks, (size_t)bytes, cudaMemcpyHostToDevice, d->stream);
-    if (e == cudaSuccess) {
-        e = launch_repack(fmt, (int)n, (int)k, n_pad, k_pad, raw, w->base, w->base + qs_b, w->base + qs_b + sc_b, false,
-                          d->stream);
-    }
+    if (e == cudaSuccess) e = launch_repack(fmt, (int)n, (int)k, n_pad, k_pad, raw, w->base, false, d->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);
     if (raw) cudaFree(raw);
     if (e != cudaSuccess) {
@@ -329,9 +323,7 @@ slc_result slc_weight_upload(slc_device *d, int32_t fmt, int64_t n, int64_t k, c
         return cuda_fail(e, "slc_weight_upload");
     }
     w->view.fmt = fmt; w->view.n = (int)n; w->view.k = (int)k; w->view.n_pad = n_pad; w->view.k_pad = k_pad;
-    w->view.qs = reinterpret_cast<const uint4 *>(w->base);
-    w->view.sc = w->base + qs_b;
-    w->view.d6 = reinterpret_cast<const __half *>(w->base + qs_b + sc_b);
+    w->view.data = w->base;
     *out = w;
     return SLC_OK;
 }
@@ -368,10 +360,8 @@ slc_result slc_weight_download(slc_weight *w, void *blocks, int64_t bytes)
     uint8_t *raw = nullptr;
     SLC_CUDA(cudaMalloc(&raw, (size_t)bytes));
     cudaError_t e = cudaMemsetAsync(raw, 0, (size_t)bytes, d->stream);
-    const size_t qs_b = (const uint8_t *)w->view.sc - w->base;
     if (e == cudaSuccess) {
-        e = launch_repack(w->fmt, (int)w->n, (int)w->k, w->view.n_pad, w->view.k_pad, raw, w->base, w->base + qs_b,
-                          (uint8_t *)w->view.d6, true, d->stream);
+        e = launch_repack(w->fmt, (int)w->n, (int)w->k, w->view.n_pad, w->view.k_pad, raw, w->base, true, d->stream);
     }
     if (e == cudaSuccess) e = cudaMemcpyAsync(blocks, raw, (size_t)bytes, cudaMemcpyDeviceToHost, d->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);
@@ -524,36 +514,6 @@ static int choose_kernel(const slc_matmul *op, int rows)
     return SLC_KERNEL_MMQ;
 }
 
-// Whether the rows of this call go through the fused quantize + dp4a kernel (matvec_fused.cu) straight from x.
-static bool use_fused(const slc_matmul *op, int rows)
-{
-    if (choose_kernel(op, rows) != SLC_KERNEL_MMVQ) return false;
-    const int k_pad = op->w->view.k_pad;
-    if (op->flags & SLC_MATMUL_ROW_INVARIANT) return rows <= 8 && fused_matvec_fits(1, k_pad);
-    return fused_matvec_fits(rows, k_pad);
-}
-
-// Fused path: chunks of up to 4 rows (one row at a time under the row-invariant flag would give the same bits; a
-// chunk's rows are computed independently of each other, so chunks of 4 keep the guarantee).
-static slc_result run_fused(slc_matmul *op, const void *x, int x_dtype, long long x_stride, int rows, float *y,
-                            long long y_stride, int *dump, cudaStream_t s)
-{
-    const WeightView &wv = op->w->view;
-    const size_t esz = x_dtype == SLC_F32 ? 4 : 2;
-    const long long dump_row = (long long)wv.n * (wv.k >> 5);
-    op->last_kernel = SLC_KERNEL_MMVQ;
-    op->last_launches = 0;
-    int chunk = 4;
-    while (chunk > 1 && !fused_matvec_fits(chunk, wv.k_pad)) chunk--;
-    for (int r0 = 0; r0 < rows; r0 += chunk) {
-        const int m = rows - r0 < chunk ? rows - r0 : chunk;
-        SLC_CUDA(launch_fused_matvec(wv, (const uint8_t *)x + (size_t)r0 * x_stride * esz, x_dtype, x_stride, m,
-                                     y + r0 * y_stride, y_stride, dump ? dump + r0 * dump_row : nullptr, s));
-        op->last_launches++;
-    }
-    return SLC_OK;
-}
-
 static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, long long y_stride, int *dump,
                               cudaStream_t s)
 {
@@ -566,9 +526,14 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
     op->last_launches = 0;
     op->last_launches_total = 0;
     if (kernel == SLC_KERNEL_MMVQ) {
-        for (int r0 = 0; r0 < rows; r0 += 8) {
-            const int m = rows - r0 < 8 ? rows - r0 : 8;
-            SLC_CUDA(launch_mmvq(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, s));
+        // chunks of up to 4 rows; every row of a chunk is computed exactly as a single row is, so the row-invariant
+        // guarantee holds for any chunking
+        int chunk = 4;
+        while (chunk > 1 && !matvec_fits(chunk, wv.k_pad)) chunk--;
+        if (!matvec_fits(chunk, wv.k_pad)) return fail(SLC_ERR_UNSUPPORTED, "K is too large for the mat-vec kernel's shared memory");
+        for (int r0 = 0; r0 < rows; r0 += chunk) {
+            const int m = rows - r0 < chunk ? rows - r0 : chunk;
+            SLC_CUDA(launch_matvec(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, s));
             op->last_launches++;
         }
     } else if (kernel == SLC_KERNEL_SKINNY) {
@@ -637,17 +602,11 @@ slc_result slc_matmul_run(slc_matmul *op, const void *x, int32_t x_dtype, int64_
     if (n == 0) return SLC_OK;
     float *y_dev = y_is_device ? y : op->y_stage;
     const long long ys = y_is_device ? y_stride : n;
-    if (use_fused(op, (int)rows)) {
-        r = run_fused(op, x_dev, x_dtype, xs, (int)rows, y_dev, ys, nullptr, s);
-        if (r != SLC_OK) return r;
-        op->last_launches_total = op->last_launches;
-    } else {
-        r = slc_activation_quantize(op->act, x_dev, x_dtype, rows, xs, s);
-        if (r != SLC_OK) return r;
-        r = run_kernels(op, op->act, y_dev, ys, nullptr, s);
-        if (r != SLC_OK) return r;
-        op->last_launches_total = op->last_launches + 1;
-    }
+    r = slc_activation_quantize(op->act, x_dev, x_dtype, rows, xs, s);
+    if (r != SLC_OK) return r;
+    r = run_kernels(op, op->act, y_dev, ys, nullptr, s);
+    if (r != SLC_OK) return r;
+    op->last_launches_total = op->last_launches + 1;
     if (!y_is_device) {
         SLC_CUDA(cudaMemcpy2DAsync(y, (size_t)y_stride * 4, y_dev, (size_t)n * 4, (size_t)n * 4, (size_t)rows,
                                    cudaMemcpyDeviceToHost, s));
@@ -710,12 +669,8 @@ slc_result slc_debug_block_dots(slc_matmul *op, const void *x, int32_t x_dtype, 
     cudaError_t e = cudaMemsetAsync(dump, 0xff, dump_bytes, d->stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(op->x_stage, x, (size_t)rows * k * esz, cudaMemcpyHostToDevice, d->stream);
     if (e != cudaSuccess) { cudaFree(dump); return cuda_fail(e, "slc_debug_block_dots"); }
-    if (use_fused(op, (int)rows)) {
-        r = run_fused(op, op->x_stage, x_dtype, k, (int)rows, op->y_stage, n, dump, d->stream);
-    } else {
-        r = slc_activation_quantize(op->act, op->x_stage, x_dtype, rows, k, d->stream);
-        if (r == SLC_OK) r = run_kernels(op, op->act, op->y_stage, n, dump, d->stream);
-    }
+    r = slc_activation_quantize(op->act, op->x_stage, x_dtype, rows, k, d->stream);
+    if (r == SLC_OK) r = run_kernels(op, op->act, op->y_stage, n, dump, d->stream);
     if (r == SLC_OK) {
         e = cudaMemcpyAsync(s32, dump, dump_bytes, cudaMemcpyDeviceToHost, d->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);

@@ -5,9 +5,33 @@
 
 namespace slc {
 
+// Programmatic dependent launch. Every kernel of this library is launched with the attribute below and calls
+// pdl_wait() before its first read of data an earlier kernel may have produced and before its first global write, so
+// consecutive kernels on a stream overlap only where that is safe: a kernel's independent prologue (weight loads)
+// runs while its predecessor drains.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // repack.cu
-cudaError_t launch_repack(int fmt, int n, int k, int n_pad, int k_pad, uint8_t *raw, uint8_t *qs, uint8_t *sc,
-                          uint8_t *d6, bool to_raw, cudaStream_t stream);
+cudaError_t launch_repack(int fmt, int n, int k, int n_pad, int k_pad, uint8_t *raw, uint8_t *data, bool to_raw,
+                          cudaStream_t stream);
 
 // quantize.cu: x (f32 or bf16, device) -> ActView planes. x_dtype: 0 = f32, 1 = bf16.
 struct ActPlanes
@@ -20,16 +44,11 @@ struct ActPlanes
 cudaError_t launch_quantize(const void *x, int x_dtype, int rows, int rows_pad, int k, int k_pad, long long x_stride,
                             ActPlanes out, cudaStream_t stream);
 
-// mmvq.cu: dp4a mat-vec for 1..8 activation rows. dump (optional) receives unsigned-code block dots
-// [rows][n][k/32].
-cudaError_t launch_mmvq(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                        int *dump, cudaStream_t stream);
-
-// matvec_fused.cu: quantization fused into the dp4a mat-vec, 1..4 activation rows of device-resident x
-// (f32 or bf16, rows x_stride elements apart); y rows y_stride apart. dump as for launch_mmvq.
-bool fused_matvec_fits(int rows, int k_pad);
-cudaError_t launch_fused_matvec(const WeightView &w, const void *x, int x_dtype, long long x_stride, int rows, float *y,
-                                long long y_stride, int *dump, cudaStream_t stream);
+// matvec.cu: dp4a mat-vec for 1..4 activation rows (rows row0 .. row0+rows-1 of the quantized activations). dump
+// (optional) receives unsigned-code block dots [rows][n][k/32]; status: device word raised when a bounded wait runs out.
+bool matvec_fits(int rows, int k_pad);
+cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
+                          int *dump, int *status, cudaStream_t stream);
 
 // skinny.cu: int8 mma tiles, 1..64 activation rows per launch.
 cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,

@@ -2,42 +2,48 @@
 //
 // Weights arrive as raw ggml blocks (block layouts: src/Sharplight.Core/Tensors/DataType.cs:102,110,116,120 of the
 // Sharplight tree) and are re-laid-out once at upload, at the same byte count apart from padding, the way the reference
-// repacks Q8_0 at upload (src/Sharplight.Shaders/Lowering/WeightRepacker.cs:56-69). The layout is "fragment-major":
+// repacks Q8_0 at upload (src/Sharplight.Shaders/Lowering/WeightRepacker.cs:56-69). The layout is a sequence of
+// "records": rows are grouped 16 at a time (row group rg = n / 16; N is padded to a multiple of 16 with zero rows),
+// K is cut in 256-value super-tiles (K is padded to a multiple of 256 with zero blocks: zero scale, zero codes), and
+// the record of (rg, st) holds everything the 16 rows need for those 256 values, contiguously:
 //
-//   rows are grouped 16 at a time (row group rg = n / 16; N is padded to a multiple of 16 with zero rows),
-//   K is padded to a multiple of 256 with zero blocks (zero scale, zero codes),
-//   the 4/6/8-bit codes of a 16-row x KT-value tile are stored as 32 lanes x 16 bytes = 512 contiguous bytes, lane
-//   (g, t) = (lane / 4, lane % 4) holding exactly the bytes that lane needs of rows g and g + 8 -- the operand
-//   fragment of an int8 m16n8k32 tensor-core tile, which is also what a dp4a lane wants -- so every weight byte is
-//   fetched by one coalesced 128-bit load straight into the register that consumes it, with no shared-memory staging.
+//     record(rg, st) at byte ((rg * k_pad/256) + st) * record_bytes(fmt)
+//     [ codes: "fragment-major" 16-byte units ][ scales: 16 rows x 16 bytes ][ Q6_K only: d, 16 rows x 2 bytes ]
 //
-// Within a 32-value block the K order of a lane's bytes may differ from the natural order (a dot product does not care
-// as long as the activation bytes are fetched in the same order); the per-format order is given below.
+// record_bytes = 16 rows x the raw bytes of 256 values: Q4_0 / Q4_K 2304, Q8_0 4352, Q6_K 3360 (all multiples of 16,
+// so one record, or a run of records of one row group, is one bulk async copy into shared memory).
 //
-//   Q8_0  tile = 32 values (one block).      lane: [row g: q[8t..8t+7]] [row g+8: q[8t..8t+7]]
-//         scales: f16 [n_pad][k_pad/32]
-//   Q4_0  tile = 64 values (two blocks).     lane words: w0 = row g   blk 2kt   qs[4t..4t+3]
-//                                                        w1 = row g+8 blk 2kt   qs[4t..4t+3]
-//                                                        w2 = row g   blk 2kt+1 qs[4t..4t+3]
-//                                                        w3 = row g+8 blk 2kt+1 qs[4t..4t+3]
+// Codes: the 4/6/8-bit codes of a 16-row x KT-value tile are 32 lanes x 16 bytes = 512 contiguous bytes, lane
+// (g, t) = (lane / 4, lane % 4) holding exactly the bytes that lane needs of rows g and g + 8 -- the operand fragment
+// of an int8 m16n8k32 tensor-core tile, which is also what a dp4a lane wants -- so every weight byte travels by a
+// 128-bit access straight into the register that consumes it. Within a 32-value block the K order of a lane's bytes
+// may differ from the natural order (a dot product does not care as long as the activation bytes are fetched in the
+// same order); the per-format order:
+//
+//   Q8_0  8 tiles of 32 values (one block).  lane: [row g: q[8t..8t+7]] [row g+8: q[8t..8t+7]]
+//         scales entry of a row: f16 d of its 8 blocks
+//   Q4_0  4 tiles of 64 values (two blocks). lane words: w0 = row g   blk 2i   qs[4t..4t+3]
+//                                                        w1 = row g+8 blk 2i   qs[4t..4t+3]
+//                                                        w2 = row g   blk 2i+1 qs[4t..4t+3]
+//                                                        w3 = row g+8 blk 2i+1 qs[4t..4t+3]
 //         (low nibbles = values 4t..4t+3, high nibbles = values 16+4t..16+4t+3 of the block)
-//         scales: f16 [n_pad][k_pad/32]
-//   Q4_K  tile = 64 values (chunk c of a super-block: sub-blocks 2c in the low, 2c+1 in the high nibbles).
+//         scales entry of a row: f16 d of its 8 blocks
+//   Q4_K  4 tiles of 64 values (chunk c of the super-block: sub-block 2c in the low, 2c+1 in the high nibbles).
 //                                            lane: [row g: qs[32c+8t..+7]] [row g+8: qs[32c+8t..+7]]
-//         headers: 16 bytes [n_pad][k_pad/256]: f16 d, f16 dmin, u8 scales[12] (verbatim)
-//   Q6_K  tile = 128 values (half h of a super-block), three 512-byte planes; with L = ql + 64h, H = qh + 32h,
-//         l0 = 4t, l1 = 16 + 4t:
+//         scales entry of a row: f16 d, f16 dmin, u8 scales[12] (the block header, verbatim)
+//   Q6_K  2 tiles of 128 values (half h of the super-block), three 512-byte planes each; with L = ql + 64h,
+//         H = qh + 32h, l0 = 4t, l1 = 16 + 4t:
 //           plane 0 lane: row g:   L[l0..+3], L[32+l0..+3], L[l1..+3], L[32+l1..+3]
 //           plane 1 lane: row g+8: the same
 //           plane 2 lane: H[l0..+3] (row g), H[l1..+3] (row g), H[l0..+3] (row g+8), H[l1..+3] (row g+8)
-//         scales: i8 [n_pad][k_pad/256][16] (verbatim), d: f16 [n_pad][k_pad/256]
+//         scales entry of a row: i8 scales[16] (verbatim); then d: f16 per row
 //
 // Quantized activations (the reference's Q8Row, src/Sharplight.Cpu/Q8Row.cs:9-20, in a GPU-friendly arrangement):
 //   q    int8   [rows_pad][k_pad]        codes, zero beyond K
 //   ds   float2 [k_pad/32][rows_pad]     (d, d * sum32(q)) per block, token-minor so neighbouring tokens share a load
 //   gs   float  [rows_pad][k_pad/16]     d * sum16(q), the reference's group sums (parity export)
 //   isum int32  [rows_pad][k_pad/32]     sum32(q) (parity export: converts signed block dots to unsigned-code dots)
-// rows_pad = rows rounded up to 8.
+// rows_pad = rows rounded up to 8, 16, 32 or a multiple of 64.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -58,11 +64,19 @@ __host__ __device__ inline int block_bytes(int fmt)
     return fmt == FMT_Q4_0 ? 18 : fmt == FMT_Q8_0 ? 34 : fmt == FMT_Q4_K ? 144 : fmt == FMT_Q6_K ? 210 : 0;
 }
 
-// 16-byte units of codes per 256-value super-tile of one row group (all formats: a multiple of 32 lanes).
-__host__ __device__ inline int qs_units_per_supertile(int fmt)
+// 16-byte units of codes per record (all formats: a multiple of 32 lanes).
+__host__ __device__ constexpr int code_units(int fmt)
 {
     // Q8_0: 8 tiles, Q4_0 / Q4_K: 4 tiles, Q6_K: 2 tiles x 3 planes; 32 lanes each
     return (fmt == FMT_Q8_0 ? 8 : fmt == FMT_Q6_K ? 6 : 4) * 32;
+}
+
+__host__ __device__ constexpr int code_bytes(int fmt) { return code_units(fmt) * 16; }
+
+// Bytes of one record: codes, 16 scale entries of 16 bytes, and for Q6_K the 16 f16 super-block scales.
+__host__ __device__ constexpr int record_bytes(int fmt)
+{
+    return code_bytes(fmt) + 256 + (fmt == FMT_Q6_K ? 32 : 0);
 }
 
 struct WeightView
@@ -70,9 +84,12 @@ struct WeightView
     int fmt;
     int n, k;          // logical shape
     int n_pad, k_pad;  // multiples of 16 / 256
-    const uint4 *qs;   // fragment-major codes: [n_pad/16][k_pad/256][qs_units_per_supertile]
-    const void *sc;    // Q8_0/Q4_0: __half [n_pad][k_pad/32]; Q4_K: uint4 [n_pad][k_pad/256]; Q6_K: uint4 (i8 x16)
-    const __half *d6;  // Q6_K only: [n_pad][k_pad/256]
+    const uint8_t *data;  // records: [n_pad/16][k_pad/256][record_bytes(fmt)]
+
+    __host__ __device__ const uint8_t *record(int rg, int st) const
+    {
+        return data + ((long long)rg * (k_pad >> 8) + st) * record_bytes(fmt);
+    }
 };
 
 struct ActView
@@ -87,21 +104,9 @@ struct ActView
 
 inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Byte sizes of the planes of a device weight.
-inline size_t weight_qs_bytes(int fmt, int n_pad, int k_pad)
+inline size_t weight_bytes(int fmt, int n_pad, int k_pad)
 {
-    return (size_t)(n_pad / 16) * (k_pad / 256) * qs_units_per_supertile(fmt) * 16;
-}
-
-inline size_t weight_sc_bytes(int fmt, int n_pad, int k_pad)
-{
-    if (fmt == FMT_Q8_0 || fmt == FMT_Q4_0) return (size_t)n_pad * (k_pad / 32) * 2;
-    return (size_t)n_pad * (k_pad / 256) * 16;
-}
-
-inline size_t weight_d6_bytes(int fmt, int n_pad, int k_pad)
-{
-    return fmt == FMT_Q6_K ? round_up((size_t)n_pad * (k_pad / 256) * 2, 256) : 0;
+    return (size_t)(n_pad / 16) * (k_pad / 256) * record_bytes(fmt);
 }
 
 // 128-bit read-only load that does not allocate in L1: weight bytes are used exactly once.

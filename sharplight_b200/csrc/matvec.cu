@@ -1,21 +1,27 @@
-// Decode mat-vec with the activation quantization fused in: one launch per MatMul for 1..4 activation rows.
+// Dequant-fused integer-dot mat-vec (decode), 1..4 activation rows per launch: the dp4a kernel family.
 //
-// Arithmetic: the reference's integer-dot MatMul (src/Sharplight.Cpu/IntDot.cs:92-126 for the 8-bit activation rule,
-// src/Sharplight.Cpu/IntDot.Kernels.cs:12-29 and src/Sharplight.Shaders/Kernels/mmvq.slang:92-173,319-424 of the
-// Sharplight tree for the block sums): exact int32 dots per 32-value block, f32 scaling.
+// Arithmetic: the reference's integer-dot MatMul (src/Sharplight.Cpu/IntDot.Kernels.cs:12-29 and the GPU form in
+// src/Sharplight.Shaders/Kernels/mmvq.slang:92-173,319-424 of the Sharplight tree): per 32-value block an exact int32
+// sum of weight code x activation code, scaled in f32 by (weight scale x activation scale), minus
+// (weight min x d_x * sum q) for the formats with an offset.
 //
-// Shape of the kernel: one CTA owns 16 weight rows; its warps split K in 256-value super-tiles. Each lane first puts
-// two super-tiles of weight loads in flight (128-bit streaming loads from the fragment-major layout, layout.cuh), and
-// while those travel the CTA quantizes the activation rows into shared memory (8 lanes per 32-value block, bit-identical
-// to quantize.cu). The dot loop then runs dp4a on registers against shared memory, with the next super-tile's loads
-// always in flight. Integer sub-block scales (Q4_K, Q6_K) are applied in int32 before the single int->float conversion.
+// Shape of the kernel (not the shader's): one CTA owns 16 weight rows; its warps split K in 256-value super-tiles.
+// Every warp streams its records (layout.cuh) into a private two-slot ring in shared memory with bulk async copies
+// (cp.async.bulk + mbarrier, the TMA engine, no registers held by loads in flight). The first copies are issued before
+// the kernel waits for its predecessor on the stream (programmatic dependent launch): weights never depend on earlier
+// kernels, the quantized activations do, so the weight stream of this MatMul overlaps the tail of the previous kernel
+// and the activation quantization. The activation codes and scales are copied to shared memory once per CTA; the dot
+// loop reads a record from its slot (one 128-bit shared load per lane per tile), runs dp4a against the activations,
+// and re-arms the slot with the warp's next record. Integer sub-block scales (Q4_K, Q6_K) are applied in int32 before
+// the one int->float conversion per block. Every mbarrier wait is bounded: when it runs out the kernel raises the
+// device status word and leaves.
 #include "internal.cuh"
-
-#include <cuda_bf16.h>
 
 namespace slc {
 
-constexpr int FV_WARPS = 4;
+constexpr int FV_MAX_WARPS = 8;
+constexpr int FV_STAGES = 2;
+constexpr unsigned FV_WAIT_LIMIT = 1u << 22;
 constexpr int FV_MAX_SMEM = 100 * 1024;
 
 template <int FMT> struct FTile;
@@ -24,29 +30,55 @@ template <> struct FTile<FMT_Q4_0> { uint4 q[4]; uint4 s[2]; };
 template <> struct FTile<FMT_Q4_K> { uint4 q[4]; uint4 s[2]; };
 template <> struct FTile<FMT_Q6_K> { uint4 q[6]; uint4 s[2]; unsigned short d[2]; };
 
+// ---- mbarrier / bulk-copy primitives ------------------------------------------------------------------------------
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, unsigned count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+// Arms the barrier with the byte count and starts the bulk copy global -> shared that completes it.
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, unsigned bytes, uint64_t *bar)
+{
+    const unsigned b = smem_u32(bar);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(b) : "memory");
+}
+
+// Bounded wait for the phase with the given parity. Returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity)
+{
+    const unsigned b = smem_u32(bar);
+    for (unsigned i = 0; i < FV_WAIT_LIMIT; i++) {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(b), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// One record of this lane: code units and the scale entries of rows g and g + 8, from a shared-memory slot.
 template <int FMT>
-__device__ __forceinline__ void load_tile(FTile<FMT> &tl, const WeightView &w, int rg, int st, int lane)
+__device__ __forceinline__ void load_tile(FTile<FMT> &tl, const uint8_t *slot, int lane)
 {
     const int g = lane >> 2;
-    const int nst = w.k_pad >> 8;
-    constexpr int NQ = FMT == FMT_Q8_0 ? 8 : FMT == FMT_Q6_K ? 6 : 4;
-    const uint4 *qp = w.qs + ((long long)rg * nst + st) * (NQ * 32) + lane;
+    constexpr int NQ = code_units(FMT) / 32;
+    const uint4 *qp = reinterpret_cast<const uint4 *>(slot) + lane;
 #pragma unroll
-    for (int i = 0; i < NQ; i++) tl.q[i] = ld_stream(qp + 32 * i);
-    const long long r0 = (long long)(rg * 16 + g), r1 = r0 + 8;
-    if (FMT == FMT_Q8_0 || FMT == FMT_Q4_0) {
-        const __half *sp = reinterpret_cast<const __half *>(w.sc);
-        const int nblk_pad = w.k_pad >> 5;
-        tl.s[0] = __ldg(reinterpret_cast<const uint4 *>(sp + r0 * nblk_pad + st * 8));
-        tl.s[1] = __ldg(reinterpret_cast<const uint4 *>(sp + r1 * nblk_pad + st * 8));
-    } else {
-        const uint4 *hp = reinterpret_cast<const uint4 *>(w.sc);
-        tl.s[0] = __ldg(hp + r0 * nst + st);
-        tl.s[1] = __ldg(hp + r1 * nst + st);
-    }
+    for (int i = 0; i < NQ; i++) tl.q[i] = qp[32 * i];
+    const uint4 *sp = reinterpret_cast<const uint4 *>(slot + code_bytes(FMT));
+    tl.s[0] = sp[g];
+    tl.s[1] = sp[g + 8];
     if constexpr (FMT == FMT_Q6_K) {
-        tl.d[0] = __ldg(reinterpret_cast<const unsigned short *>(w.d6) + r0 * nst + st);
-        tl.d[1] = __ldg(reinterpret_cast<const unsigned short *>(w.d6) + r1 * nst + st);
+        const unsigned short *dp = reinterpret_cast<const unsigned short *>(slot + code_bytes(FMT) + 256);
+        tl.d[0] = dp[g];
+        tl.d[1] = dp[g + 8];
     }
 }
 
@@ -232,78 +264,53 @@ __device__ __forceinline__ void compute_tile(const FTile<FMT> &tl, const SmemAct
     }
 }
 
-// Quantizes x[M][k] into shared memory; the same operations, in the same order, as quantize.cu.
-template <int M>
-__device__ __forceinline__ void quantize_to_smem(const void *xv, int x_dtype, long long x_stride, int k, int k_pad,
-                                                 int8_t *sq, float2 *sds, int *sisum)
-{
-    const int nblk_pad = k_pad >> 5;
-    const int sub = threadIdx.x & 7;
-    for (int b = threadIdx.x >> 3; b < M * nblk_pad; b += (FV_WARPS * 32) >> 3) {
-        const int m = b / nblk_pad, blk = b - m * nblk_pad;
-        float v[4] = { 0.f, 0.f, 0.f, 0.f };
-        if (blk * 32 < k) {
-            const long long base = (long long)m * x_stride + blk * 32 + sub * 4;
-            if (x_dtype == 0) {
-                const float *x = (const float *)xv + base;
-                if ((((uintptr_t)x) & 15) == 0) {
-                    const float4 f = __ldg(reinterpret_cast<const float4 *>(x));
-                    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
-                } else {
-                    for (int i = 0; i < 4; i++) v[i] = __ldg(x + i);
-                }
-            } else {
-                const __nv_bfloat16 *x = (const __nv_bfloat16 *)xv + base;
-                for (int i = 0; i < 4; i++) v[i] = __bfloat162float(x[i]);
-            }
-        }
-        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-        const float d = __fdiv_rn(amax, 127.0f);
-        const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-        int r[4], s = 0;
-        for (int i = 0; i < 4; i++) {
-            const float wv = __fmul_rn(v[i], id);
-            r[i] = __float2int_rz(__fadd_rn(wv, copysignf(0.5f, wv)));
-            s += r[i];
-        }
-        *reinterpret_cast<unsigned *>(sq + m * k_pad + blk * 32 + sub * 4) =
-            (unsigned)(r[0] & 0xff) | ((unsigned)(r[1] & 0xff) << 8) | ((unsigned)(r[2] & 0xff) << 16) |
-            ((unsigned)(r[3] & 0xff) << 24);
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        if (sub == 0) {
-            sds[m * nblk_pad + blk] = make_float2(d, __fmul_rn(d, (float)s));
-            sisum[m * nblk_pad + blk] = s;
-        }
-    }
-}
-
 template <int FMT, int M, bool DUMP>
-__global__ void __launch_bounds__(FV_WARPS * 32)
-fused_matvec_kernel(const WeightView w, const void *__restrict__ x, int x_dtype, long long x_stride,
-                    float *__restrict__ y, long long y_stride, int *dump)
+__global__ void __launch_bounds__(FV_MAX_WARPS * 32)
+matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__ y, long long y_stride, int *dump,
+              int *status)
 {
-    extern __shared__ __align__(16) unsigned char smem[];
-    __shared__ float red[FV_WARPS][16][M];
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ __align__(8) uint64_t bars[FV_MAX_WARPS][FV_STAGES];
+    __shared__ float red[FV_MAX_WARPS][16][M];
+    constexpr int REC = record_bytes(FMT);
+    const int warps = blockDim.x >> 5;
     const int nblk_pad = w.k_pad >> 5, nst = w.k_pad >> 8;
-    int8_t *sq = reinterpret_cast<int8_t *>(smem);
-    float2 *sds = reinterpret_cast<float2 *>(smem + (size_t)M * w.k_pad);
-    int *sisum = reinterpret_cast<int *>(smem + (size_t)M * w.k_pad + (size_t)M * nblk_pad * 8);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, t = lane & 3, g = lane >> 2;
     const int rg = blockIdx.x;
+    uint8_t *ring = smem + (size_t)warp * FV_STAGES * REC;
+    unsigned char *act_base = smem + (size_t)warps * FV_STAGES * REC;
+    int8_t *sq = reinterpret_cast<int8_t *>(act_base);
+    float2 *sds = reinterpret_cast<float2 *>(act_base + (size_t)M * w.k_pad);
+    int *sisum = reinterpret_cast<int *>(act_base + (size_t)M * w.k_pad + (size_t)M * nblk_pad * 8);
 
-    // weight loads first: they are in flight while the activations are quantized
-    FTile<FMT> ta, tb;
-    int st = warp;
-    if (st < nst) load_tile<FMT>(ta, w, rg, st, lane);
-    if (st + FV_WARPS < nst) load_tile<FMT>(tb, w, rg, st + FV_WARPS, lane);
+    // this warp's records: super-tiles warp, warp + warps, ...; the first FV_STAGES copies start right away
+    const int count = nst > warp ? (nst - warp + warps - 1) / warps : 0;
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < FV_STAGES; s++) mbar_init(&bars[warp][s], 1);
+        fence_mbar_init();
+#pragma unroll
+        for (int s = 0; s < FV_STAGES; s++) {
+            if (s < count) bulk_load(ring + s * REC, w.record(rg, warp + s * warps), REC, &bars[warp][s]);
+        }
+    }
 
-    // M * nblk_pad is a multiple of 8 and the stride below keeps the 8 lanes of a block together
-    quantize_to_smem<M>(x, x_dtype, x_stride, w.k, w.k_pad, sq, sds, sisum);
+    pdl_launch_dependents();
+    pdl_wait();   // the activations (and the previous use of y) are complete from here on
+
+    // quantized activations -> shared memory
+    {
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.q + (long long)row0 * a.k_pad);
+        uint4 *dst = reinterpret_cast<uint4 *>(sq);
+        for (int i = threadIdx.x; i < M * (w.k_pad >> 4); i += blockDim.x) dst[i] = __ldg(src + i);
+        for (int blk = threadIdx.x; blk < nblk_pad; blk += blockDim.x) {
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                sds[m * nblk_pad + blk] = __ldg(&a.ds[(long long)blk * a.rows_pad + row0 + m]);
+                if (DUMP) sisum[m * nblk_pad + blk] = __ldg(&a.isum[(long long)(row0 + m) * nblk_pad + blk]);
+            }
+        }
+    }
     __syncthreads();
 
     const SmemAct act{ sq, sds, sisum, w.k_pad, nblk_pad };
@@ -314,12 +321,23 @@ fused_matvec_kernel(const WeightView w, const void *__restrict__ x, int x_dtype,
 #pragma unroll
         for (int m = 0; m < M; m++) acc[r][m] = 0.0f;
 
-    for (; st < nst; st += 2 * FV_WARPS) {
-        compute_tile<FMT, M, DUMP>(ta, act, st, t, acc, dc);
-        if (st + 2 * FV_WARPS < nst) load_tile<FMT>(ta, w, rg, st + 2 * FV_WARPS, lane);
-        if (st + FV_WARPS < nst) {
-            compute_tile<FMT, M, DUMP>(tb, act, st + FV_WARPS, t, acc, dc);
-            if (st + 3 * FV_WARPS < nst) load_tile<FMT>(tb, w, rg, st + 3 * FV_WARPS, lane);
+    bool alive = true;
+    for (int i = 0; i < count; i++) {
+        const int s = i % FV_STAGES;
+        const uint8_t *slot = ring + s * REC;
+        if (!mbar_wait(&bars[warp][s], (unsigned)(i / FV_STAGES) & 1u)) {
+            // the copy never landed: report, stop computing, but still drain what else is in flight (bounded)
+            if (lane == 0) atomicExch(status, -7);
+            alive = false;
+        }
+        if (alive) {
+            FTile<FMT> tl;
+            load_tile<FMT>(tl, slot, lane);
+            __syncwarp();   // every lane has its copy of the record: the slot may be refilled
+            if (lane == 0 && i + FV_STAGES < count) {
+                bulk_load(ring + s * REC, w.record(rg, warp + (i + FV_STAGES) * warps), REC, &bars[warp][s]);
+            }
+            compute_tile<FMT, M, DUMP>(tl, act, warp + i * warps, t, acc, dc);
         }
     }
 
@@ -337,43 +355,57 @@ fused_matvec_kernel(const WeightView w, const void *__restrict__ x, int x_dtype,
     if (threadIdx.x < 16 * M) {
         const int m = threadIdx.x / 16, rr = threadIdx.x % 16;
         float v = 0.0f;
-#pragma unroll
-        for (int wi = 0; wi < FV_WARPS; wi++) v += red[wi][rr][m];
+        for (int wi = 0; wi < warps; wi++) v += red[wi][rr][m];
         const int row = blockIdx.x * 16 + rr;
-        if (row < w.n) y[(long long)m * y_stride + row] = v;
+        if (row < w.n) y[(long long)(row0 + m) * y_stride + row] = v;
     }
 }
 
-size_t fused_matvec_smem(int rows, int k_pad) { return (size_t)rows * (k_pad + (k_pad >> 5) * 12); }
+// Warps per CTA: four split K by default; eight when there are few row groups and K is long (the down projections),
+// never more than there are super-tiles.
+static int matvec_warps(const WeightView &w)
+{
+    const int nst = w.k_pad >> 8, rgs = w.n_pad / 16;
+    int warps = (rgs < 444 && nst >= 8) ? 8 : 4;
+    return warps < nst ? warps : nst;
+}
 
-bool fused_matvec_fits(int rows, int k_pad) { return rows >= 1 && rows <= 4 && fused_matvec_smem(rows, k_pad) <= FV_MAX_SMEM; }
+static size_t matvec_smem(int fmt, int warps, int rows, int k_pad)
+{
+    return (size_t)warps * FV_STAGES * record_bytes(fmt) + (size_t)rows * (k_pad + (k_pad >> 5) * 12);
+}
+
+bool matvec_fits(int rows, int k_pad)
+{
+    return rows >= 1 && rows <= 4 && matvec_smem(FMT_Q8_0, FV_MAX_WARPS, rows, k_pad) <= FV_MAX_SMEM;
+}
 
 template <int FMT, int M, bool DUMP>
-static cudaError_t launch_one(const WeightView &w, const void *x, int x_dtype, long long x_stride, float *y,
-                              long long y_stride, int *dump, cudaStream_t stream)
+static cudaError_t launch_one(const WeightView &w, const ActView &a, int row0, float *y, long long y_stride, int *dump,
+                              int *status, cudaStream_t stream)
 {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kernel = fused_matvec_kernel<FMT, M, DUMP>;
+    auto kernel = matvec_kernel<FMT, M, DUMP>;
     if (dev < 64 && !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FV_MAX_SMEM);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    const size_t smem = fused_matvec_smem(M, w.k_pad);
-    kernel<<<w.n_pad / 16, FV_WARPS * 32, smem, stream>>>(w, x, x_dtype, x_stride, y, y_stride, dump);
-    return cudaGetLastError();
+    const int warps = matvec_warps(w);
+    return launch_pdl(kernel, dim3(w.n_pad / 16), dim3(warps * 32), matvec_smem(FMT, warps, M, w.k_pad), stream, w, a,
+                      row0, y, y_stride, dump, status);
 }
 
 template <int FMT>
-static cudaError_t launch_fmt(const WeightView &w, const void *x, int x_dtype, long long x_stride, int rows, float *y,
-                              long long y_stride, int *dump, cudaStream_t stream)
+static cudaError_t launch_fmt(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
+                              int *dump, int *status, cudaStream_t stream)
 {
-#define SLC_ROWS(MM)                                                                                     \
-    case MM:                                                                                             \
-        return dump ? launch_one<FMT, MM, true>(w, x, x_dtype, x_stride, y, y_stride, dump, stream)      \
-                    : launch_one<FMT, MM, false>(w, x, x_dtype, x_stride, y, y_stride, nullptr, stream);
+#define SLC_ROWS(MM)                                                                        \
+    case MM:                                                                                \
+        return dump ? launch_one<FMT, MM, true>(w, a, row0, y, y_stride, dump, status, stream)      \
+                    : launch_one<FMT, MM, false>(w, a, row0, y, y_stride, nullptr, status, stream);
     switch (rows) {
         SLC_ROWS(1) SLC_ROWS(2) SLC_ROWS(3) SLC_ROWS(4)
     default: return cudaErrorInvalidValue;
@@ -381,15 +413,16 @@ static cudaError_t launch_fmt(const WeightView &w, const void *x, int x_dtype, l
 #undef SLC_ROWS
 }
 
-cudaError_t launch_fused_matvec(const WeightView &w, const void *x, int x_dtype, long long x_stride, int rows, float *y,
-                                long long y_stride, int *dump, cudaStream_t stream)
+// rows 1..4 starting at activation row row0; dump (optional) receives [rows][n][k/32] block dots.
+cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
+                          int *dump, int *status, cudaStream_t stream)
 {
     if (w.n_pad == 0 || rows == 0) return cudaSuccess;
     switch (w.fmt) {
-    case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(w, x, x_dtype, x_stride, rows, y, y_stride, dump, stream);
-    case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(w, x, x_dtype, x_stride, rows, y, y_stride, dump, stream);
-    case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(w, x, x_dtype, x_stride, rows, y, y_stride, dump, stream);
-    case FMT_Q6_K: return launch_fmt<FMT_Q6_K>(w, x, x_dtype, x_stride, rows, y, y_stride, dump, stream);
+    case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(w, a, row0, rows, y, y_stride, dump, status, stream);
+    case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(w, a, row0, rows, y, y_stride, dump, status, stream);
+    case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(w, a, row0, rows, y, y_stride, dump, status, stream);
+    case FMT_Q6_K: return launch_fmt<FMT_Q6_K>(w, a, row0, rows, y, y_stride, dump, status, stream);
     default: return cudaErrorInvalidValue;
     }
 }

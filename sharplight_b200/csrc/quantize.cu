@@ -22,6 +22,9 @@ __global__ void __launch_bounds__(256) quantize_kernel(const void *__restrict__ 
     const int row = (int)(blk_global / nblk_pad), blk = (int)(blk_global % nblk_pad);
     const bool live = row < rows && blk * 32 < k;
 
+    pdl_wait();                // x may come from the kernel before this one
+    pdl_launch_dependents();   // the MatMul that follows may start fetching its weights
+
     float v[4] = { 0.f, 0.f, 0.f, 0.f };
     if (live) {
         const long long base = (long long)row * x_stride + blk * 32 + sub * 4;
@@ -73,9 +76,8 @@ cudaError_t launch_quantize(const void *x, int x_dtype, int rows, int rows_pad, 
     const long long threads = (long long)rows_pad * (k_pad >> 5) * 8;
     if (threads == 0) return cudaSuccess;
     const unsigned grid = (unsigned)((threads + 255) / 256);
-    if (x_dtype == 0) quantize_kernel<0><<<grid, 256, 0, stream>>>(x, rows, rows_pad, k, k_pad, x_stride, out);
-    else quantize_kernel<1><<<grid, 256, 0, stream>>>(x, rows, rows_pad, k, k_pad, x_stride, out);
-    return cudaGetLastError();
+    if (x_dtype == 0) return launch_pdl(quantize_kernel<0>, dim3(grid), dim3(256), 0, stream, x, rows, rows_pad, k, k_pad, x_stride, out);
+    return launch_pdl(quantize_kernel<1>, dim3(grid), dim3(256), 0, stream, x, rows, rows_pad, k, k_pad, x_stride, out);
 }
 
 }  // namespace slc

@@ -1,5 +1,5 @@
-// Upload-time re-layout of raw ggml blocks into the fragment-major device layout (layout.cuh), and its inverse.
-// One thread per 16-byte unit of the code plane, one thread per scale entry. Runs once per weight.
+// Upload-time re-layout of raw ggml blocks into the record layout (layout.cuh), and its inverse.
+// One thread per 16-byte unit. Runs once per weight.
 #include "internal.cuh"
 
 namespace slc {
@@ -47,21 +47,42 @@ __device__ __forceinline__ RawPos code_source(int fmt, int n, int nblk, int rg, 
     return p;
 }
 
-__global__ void repack_codes_kernel(int fmt, int n, int k, int n_pad, int k_pad, uint8_t *raw, uint8_t *qs, int to_raw)
+// One thread per 16-byte unit of a record: code units first, then the 16 scale entries, then (Q6_K) two units of d.
+__global__ void repack_kernel(int fmt, int n, int k, int n_pad, int k_pad, uint8_t *raw, uint8_t *data, int to_raw)
 {
-    const int per_st = qs_units_per_supertile(fmt);
+    const int rec = record_bytes(fmt), units_per_rec = rec / 16, ncode = code_units(fmt);
     const int nst = k_pad >> 8;
-    const long long units = (long long)(n_pad / 16) * nst * per_st;
+    const long long units = (long long)(n_pad / 16) * nst * units_per_rec;
     const long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (u >= units) return;
-    const int r2 = (int)(u % per_st);
-    const long long v = u / per_st;
+    const int r2 = (int)(u % units_per_rec);
+    const long long v = u / units_per_rec;
     const int st = (int)(v % nst), rg = (int)(v / nst);
-    const int nblk = k / block_size(fmt);
-    const long long row_bytes = (long long)nblk * block_bytes(fmt);
-    uint8_t *unit = qs + u * 16;
+    const int bs = block_size(fmt), bb = block_bytes(fmt);
+    const int nblk = k / bs;
+    const long long row_bytes = (long long)nblk * bb;
+    uint8_t *unit = data + u * 16;
     for (int i = 0; i < 16; i++) {
-        RawPos p = code_source(fmt, n, nblk, rg, st, r2, i);
+        RawPos p;
+        if (r2 < ncode) {
+            p = code_source(fmt, n, nblk, rg, st, r2, i);
+        } else if (r2 < ncode + 16) {
+            // scale entry of row r2 - ncode
+            p.row = rg * 16 + (r2 - ncode);
+            if (fmt == FMT_Q8_0 || fmt == FMT_Q4_0) {
+                const int blk = st * 8 + (i >> 1);
+                p.off = blk * bb + (i & 1);
+                p.valid = p.row < n && blk < nblk;
+            } else {
+                p.off = st * bb + (fmt == FMT_Q4_K ? 0 : 192) + i;
+                p.valid = p.row < n && st < nblk;
+            }
+        } else {
+            // Q6_K super-block scales: two units, 8 rows x f16 each
+            p.row = rg * 16 + (r2 - ncode - 16) * 8 + (i >> 1);
+            p.off = st * bb + 208 + (i & 1);
+            p.valid = p.row < n && st < nblk;
+        }
         if (to_raw) {
             if (p.valid) raw[p.row * row_bytes + p.off] = unit[i];
         } else {
@@ -70,46 +91,13 @@ __global__ void repack_codes_kernel(int fmt, int n, int k, int n_pad, int k_pad,
     }
 }
 
-__global__ void repack_scales_kernel(int fmt, int n, int k, int n_pad, int k_pad, uint8_t *raw, uint8_t *sc,
-                                     uint8_t *d6, int to_raw)
+cudaError_t launch_repack(int fmt, int n, int k, int n_pad, int k_pad, uint8_t *raw, uint8_t *data, bool to_raw,
+                          cudaStream_t stream)
 {
-    const int bs = block_size(fmt), bb = block_bytes(fmt);
-    const int nblk = k / bs, nblk_pad = k_pad / bs;
-    const long long total = (long long)n_pad * nblk_pad;
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= total) return;
-    const int blk = (int)(idx % nblk_pad), row = (int)(idx / nblk_pad);
-    const bool valid = row < n && blk < nblk;
-    uint8_t *src = raw + ((long long)row * nblk + blk) * bb;
-    int entry_bytes, src_off;
-    if (fmt == FMT_Q8_0 || fmt == FMT_Q4_0) { entry_bytes = 2; src_off = 0; }
-    else if (fmt == FMT_Q4_K) { entry_bytes = 16; src_off = 0; }
-    else { entry_bytes = 16; src_off = 192; }
-    uint8_t *dst = sc + idx * entry_bytes;
-    for (int i = 0; i < entry_bytes; i++) {
-        if (to_raw) { if (valid) src[src_off + i] = dst[i]; }
-        else dst[i] = valid ? src[src_off + i] : (uint8_t)0;
-    }
-    if (fmt == FMT_Q6_K) {
-        for (int i = 0; i < 2; i++) {
-            if (to_raw) { if (valid) src[208 + i] = d6[idx * 2 + i]; }
-            else d6[idx * 2 + i] = valid ? src[208 + i] : (uint8_t)0;
-        }
-    }
-}
-
-cudaError_t launch_repack(int fmt, int n, int k, int n_pad, int k_pad, uint8_t *raw, uint8_t *qs, uint8_t *sc,
-                          uint8_t *d6, bool to_raw, cudaStream_t stream)
-{
-    const long long units = (long long)(n_pad / 16) * (k_pad >> 8) * qs_units_per_supertile(fmt);
-    const long long entries = (long long)n_pad * (k_pad / block_size(fmt));
+    const long long units = (long long)(n_pad / 16) * (k_pad >> 8) * (record_bytes(fmt) / 16);
     if (units > 0) {
-        repack_codes_kernel<<<(unsigned)((units + 255) / 256), 256, 0, stream>>>(fmt, n, k, n_pad, k_pad, raw, qs,
-                                                                                  to_raw ? 1 : 0);
-    }
-    if (entries > 0) {
-        repack_scales_kernel<<<(unsigned)((entries + 255) / 256), 256, 0, stream>>>(fmt, n, k, n_pad, k_pad, raw, sc,
-                                                                                    d6, to_raw ? 1 : 0);
+        repack_kernel<<<(unsigned)((units + 255) / 256), 256, 0, stream>>>(fmt, n, k, n_pad, k_pad, raw, data,
+                                                                           to_raw ? 1 : 0);
     }
     return cudaGetLastError();
 }

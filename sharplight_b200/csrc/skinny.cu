@@ -1,6 +1,6 @@
 // Skinny integer-dot GEMM for 3..64 activation rows (batched decode, speculative verification, short prefill).
 //
-// Same arithmetic as mmvq.cu -- exact int32 block dots scaled in f32 (src/Sharplight.Cpu/IntDot.Kernels.cs:12-29,
+// Same arithmetic as matvec.cu -- exact int32 block dots scaled in f32 (src/Sharplight.Cpu/IntDot.Kernels.cs:12-29,
 // src/Sharplight.Shaders/Kernels/mmq.slang:224-233 of the Sharplight tree) -- but the int32 dots come from int8
 // tensor-core tiles: the 16 weight rows of a CTA are the M operand of m16n8k32 (m16n8k16 for Q6_K, whose scales
 // change every 16 values), eight activation rows are the N operand, one 32-value block is one K step. The weight
@@ -88,14 +88,13 @@ __device__ __forceinline__ float half_of(unsigned word, int which)
 template <int NT, bool DUMP>
 __device__ __forceinline__ void sk_q8_0(SkCtx<NT, DUMP> &c, int st, int lane)
 {
-    const int nst = c.w.k_pad >> 8, nblk_pad = c.w.k_pad >> 5;
-    const uint4 *qp = c.w.qs + ((long long)c.rg * nst + st) * 256 + lane;
+    const uint8_t *rec = c.w.record(c.rg, st);
+    const uint4 *qp = reinterpret_cast<const uint4 *>(rec) + lane;
     uint4 q[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) q[i] = ld_stream(qp + 32 * i);
-    const __half *sp = reinterpret_cast<const __half *>(c.w.sc);
-    const uint4 sc0 = __ldg(reinterpret_cast<const uint4 *>(sp + (long long)(c.rg * 16 + c.g) * nblk_pad + st * 8));
-    const uint4 sc1 = __ldg(reinterpret_cast<const uint4 *>(sp + (long long)(c.rg * 16 + c.g + 8) * nblk_pad + st * 8));
+    const uint4 *sp = reinterpret_cast<const uint4 *>(rec + code_bytes(FMT_Q8_0));
+    const uint4 sc0 = ld_stream(sp + c.g), sc1 = ld_stream(sp + c.g + 8);
     const unsigned s0w[4] = { sc0.x, sc0.y, sc0.z, sc0.w }, s1w[4] = { sc1.x, sc1.y, sc1.z, sc1.w };
 #pragma unroll
     for (int i = 0; i < 8; i++) {
@@ -117,14 +116,13 @@ __device__ __forceinline__ void sk_q8_0(SkCtx<NT, DUMP> &c, int st, int lane)
 template <int NT, bool DUMP>
 __device__ __forceinline__ void sk_q4_0(SkCtx<NT, DUMP> &c, int st, int lane)
 {
-    const int nst = c.w.k_pad >> 8, nblk_pad = c.w.k_pad >> 5;
-    const uint4 *qp = c.w.qs + ((long long)c.rg * nst + st) * 128 + lane;
+    const uint8_t *rec = c.w.record(c.rg, st);
+    const uint4 *qp = reinterpret_cast<const uint4 *>(rec) + lane;
     uint4 q[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) q[i] = ld_stream(qp + 32 * i);
-    const __half *sp = reinterpret_cast<const __half *>(c.w.sc);
-    const uint4 sc0 = __ldg(reinterpret_cast<const uint4 *>(sp + (long long)(c.rg * 16 + c.g) * nblk_pad + st * 8));
-    const uint4 sc1 = __ldg(reinterpret_cast<const uint4 *>(sp + (long long)(c.rg * 16 + c.g + 8) * nblk_pad + st * 8));
+    const uint4 *sp = reinterpret_cast<const uint4 *>(rec + code_bytes(FMT_Q4_0));
+    const uint4 sc0 = ld_stream(sp + c.g), sc1 = ld_stream(sp + c.g + 8);
     const unsigned s0w[4] = { sc0.x, sc0.y, sc0.z, sc0.w }, s1w[4] = { sc1.x, sc1.y, sc1.z, sc1.w };
 #pragma unroll
     for (int i = 0; i < 8; i++) {
@@ -150,14 +148,13 @@ __device__ __forceinline__ void sk_q4_0(SkCtx<NT, DUMP> &c, int st, int lane)
 template <int NT, bool DUMP>
 __device__ __forceinline__ void sk_q4_k(SkCtx<NT, DUMP> &c, int st, int lane)
 {
-    const int nst = c.w.k_pad >> 8;
-    const uint4 *qp = c.w.qs + ((long long)c.rg * nst + st) * 128 + lane;
+    const uint8_t *rec = c.w.record(c.rg, st);
+    const uint4 *qp = reinterpret_cast<const uint4 *>(rec) + lane;
     uint4 q[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) q[i] = ld_stream(qp + 32 * i);
-    const uint4 *hp = reinterpret_cast<const uint4 *>(c.w.sc);
-    const uint4 h[2] = { __ldg(hp + (long long)(c.rg * 16 + c.g) * nst + st),
-                         __ldg(hp + (long long)(c.rg * 16 + c.g + 8) * nst + st) };
+    const uint4 *hp = reinterpret_cast<const uint4 *>(rec + code_bytes(FMT_Q4_K));
+    const uint4 h[2] = { ld_stream(hp + c.g), ld_stream(hp + c.g + 8) };
     float d[2], dmin[2];
     unsigned sc[2][2], mn[2][2];
 #pragma unroll
@@ -195,12 +192,12 @@ __device__ __forceinline__ void sk_q4_k(SkCtx<NT, DUMP> &c, int st, int lane)
 template <int NT, bool DUMP>
 __device__ __forceinline__ void sk_q6_k(SkCtx<NT, DUMP> &c, int st, int lane)
 {
-    const int nst = c.w.k_pad >> 8;
-    const uint4 *qp = c.w.qs + ((long long)c.rg * nst + st) * 192 + lane;
-    const uint4 *scp = reinterpret_cast<const uint4 *>(c.w.sc);
-    const long long e0 = (long long)(c.rg * 16 + c.g) * nst + st, e1 = (long long)(c.rg * 16 + c.g + 8) * nst + st;
-    const uint4 scv[2] = { __ldg(scp + e0), __ldg(scp + e1) };
-    const float d[2] = { __half2float(__ldg(c.w.d6 + e0)), __half2float(__ldg(c.w.d6 + e1)) };
+    const uint8_t *rec = c.w.record(c.rg, st);
+    const uint4 *qp = reinterpret_cast<const uint4 *>(rec) + lane;
+    const uint4 *scp = reinterpret_cast<const uint4 *>(rec + code_bytes(FMT_Q6_K));
+    const __half *dp = reinterpret_cast<const __half *>(rec + code_bytes(FMT_Q6_K) + 256);
+    const uint4 scv[2] = { ld_stream(scp + c.g), ld_stream(scp + c.g + 8) };
+    const float d[2] = { __half2float(__ldg(dp + c.g)), __half2float(__ldg(dp + c.g + 8)) };
     const unsigned scw[2][4] = { { scv[0].x, scv[0].y, scv[0].z, scv[0].w }, { scv[1].x, scv[1].y, scv[1].z, scv[1].w } };
 #pragma unroll
     for (int h = 0; h < 2; h++) {
@@ -259,6 +256,9 @@ skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__
 #pragma unroll
         for (int e = 0; e < 4; e++) c.acc[nt][e] = 0.0f;
 
+    pdl_launch_dependents();
+    pdl_wait();   // quantized activations come from the kernel before this one
+
     const int nst = w.k_pad >> 8;
     for (int st = warp; st < nst; st += SK_WARPS) {
         if (FMT == FMT_Q8_0) sk_q8_0<NT, DUMP>(c, st, lane);
@@ -287,12 +287,11 @@ static cudaError_t launch_nt(const WeightView &w, const ActView &a, int row0, in
                              int *dump, cudaStream_t stream)
 {
     const dim3 grid(w.n_pad / 16), block(SK_WARPS * 32);
-    if (rows <= 8) skinny_kernel<FMT, 1, DUMP><<<grid, block, 0, stream>>>(w, a, row0, rows, y, y_stride, dump);
-    else if (rows <= 16) skinny_kernel<FMT, 2, DUMP><<<grid, block, 0, stream>>>(w, a, row0, rows, y, y_stride, dump);
-    else if (rows <= 32) skinny_kernel<FMT, 4, DUMP><<<grid, block, 0, stream>>>(w, a, row0, rows, y, y_stride, dump);
-    else if (rows <= 64) skinny_kernel<FMT, 8, DUMP><<<grid, block, 0, stream>>>(w, a, row0, rows, y, y_stride, dump);
-    else return cudaErrorInvalidValue;
-    return cudaGetLastError();
+    if (rows <= 8) return launch_pdl(skinny_kernel<FMT, 1, DUMP>, grid, block, 0, stream, w, a, row0, rows, y, y_stride, dump);
+    if (rows <= 16) return launch_pdl(skinny_kernel<FMT, 2, DUMP>, grid, block, 0, stream, w, a, row0, rows, y, y_stride, dump);
+    if (rows <= 32) return launch_pdl(skinny_kernel<FMT, 4, DUMP>, grid, block, 0, stream, w, a, row0, rows, y, y_stride, dump);
+    if (rows <= 64) return launch_pdl(skinny_kernel<FMT, 8, DUMP>, grid, block, 0, stream, w, a, row0, rows, y, y_stride, dump);
+    return cudaErrorInvalidValue;
 }
 
 // row0 must be a multiple of 8 (activation scale pairs are fetched with aligned 128-bit loads).
