@@ -41,6 +41,7 @@ struct slc_activation
     uint8_t *base = nullptr;
     size_t bytes = 0;
     ActPlanes planes{};
+    uint8_t *q_tiled = nullptr;   // present when the capacity allows GEMM-sized row counts
     int rows = 0, rows_pad = 0;   // what the last quantize call wrote
 };
 
@@ -87,13 +88,14 @@ static slc_result cuda_fail(cudaError_t e, const char *what)
         if (e_ != cudaSuccess) return cuda_fail(e_, #call);     \
     } while (0)
 
-// Rows are padded so that every token tile a kernel touches exists: 8, 16, 32, then multiples of 64.
+// Rows are padded so that every token tile a kernel touches exists: 8, 16, 32, 64, then multiples of 128.
 static int pad_rows(long long rows)
 {
     if (rows <= 8) return 8;
     if (rows <= 16) return 16;
     if (rows <= 32) return 32;
-    return (int)((rows + 63) / 64 * 64);
+    if (rows <= 64) return 64;
+    return (int)((rows + 127) / 128 * 128);
 }
 
 extern "C" {
@@ -406,7 +408,8 @@ slc_result slc_activation_create(slc_device *d, int64_t max_rows, int64_t k, slc
     const size_t cap = (size_t)a->cap_rows, kp = (size_t)a->k_pad;
     const size_t q_b = round_up(cap * kp, 256), ds_b = round_up(cap * (kp / 32) * 8, 256);
     const size_t gs_b = round_up(cap * (kp / 16) * 4, 256), is_b = round_up(cap * (kp / 32) * 4, 256);
-    a->bytes = q_b + ds_b + gs_b + is_b;
+    const size_t qt_b = a->cap_rows > 64 ? q_b : 0;   // core-matrix copy for the tensor-core GEMM
+    a->bytes = q_b + ds_b + gs_b + is_b + qt_b;
     cudaError_t e = cudaMalloc(&a->base, a->bytes);
     if (e == cudaSuccess) e = cudaMemset(a->base, 0, a->bytes);
     if (e != cudaSuccess) {
@@ -418,6 +421,7 @@ slc_result slc_activation_create(slc_device *d, int64_t max_rows, int64_t k, slc
     a->planes.ds = reinterpret_cast<float2 *>(a->base + q_b);
     a->planes.gs = reinterpret_cast<float *>(a->base + q_b + ds_b);
     a->planes.isum = reinterpret_cast<int *>(a->base + q_b + ds_b + gs_b);
+    a->q_tiled = qt_b ? a->base + q_b + ds_b + gs_b + is_b : nullptr;
     *out = a;
     return SLC_OK;
 }
@@ -444,6 +448,7 @@ slc_result slc_activation_quantize(slc_activation *a, const void *x, int32_t x_d
     if (rows == 0) return SLC_OK;
     SLC_CUDA(cudaSetDevice(a->dev->index));
     cudaStream_t s = stream ? (cudaStream_t)stream : a->dev->stream;
+    a->planes.q_tiled = rows > 64 ? a->q_tiled : nullptr;
     SLC_CUDA(launch_quantize(x, x_dtype, a->rows, a->rows_pad, (int)a->k, a->k_pad, x_stride, a->planes, s));
     return SLC_OK;
 }
@@ -543,7 +548,8 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
             op->last_launches++;
         }
     } else {
-        SLC_CUDA(launch_mmq(wv, av, rows, y, y_stride, dump, op->dev->status_dev, s));
+        if (!act->planes.q_tiled) return fail(SLC_ERR_INVALID_STATE, "the tensor-core GEMM needs more than 64 rows");
+        SLC_CUDA(launch_mmq(wv, av, act->planes.q_tiled, y, y_stride, dump, op->dev->status_dev, s));
         op->last_launches++;
     }
     return SLC_OK;

@@ -36,6 +36,7 @@ cudaError_t launch_repack(int fmt, int n, int k, int n_pad, int k_pad, uint8_t *
 // quantize.cu: x (f32 or bf16, device) -> ActView planes. x_dtype: 0 = f32, 1 = bf16.
 struct ActPlanes
 {
+    uint8_t *q_tiled;   // optional second copy of the codes in tensor-core core-matrix order (mmq.cu), or null
     int8_t *q;
     float2 *ds;
     float *gs;
@@ -57,7 +58,7 @@ cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int r
 // mmq.cu: tcgen05 / TMEM int8 GEMM for many rows (Q4_0, Q8_0, Q4_K). status: device word set to a negative code when
 // a bounded wait runs out.
 bool mmq_supports(int fmt);
-cudaError_t launch_mmq(const WeightView &w, const ActView &a, int rows, float *y, long long y_stride, int *dump,
-                       int *status, cudaStream_t stream);
+cudaError_t launch_mmq(const WeightView &w, const ActView &a, const uint8_t *q_tiled, float *y, long long y_stride,
+                       int *dump, int *status, cudaStream_t stream);
 
 }  // namespace slc

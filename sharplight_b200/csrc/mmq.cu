@@ -1,13 +1,416 @@
-// Prefill GEMM on the int8 tensor cores (tcgen05 / TMEM). Placeholder translation unit until the kernel lands.
+// Prefill GEMM on the 5th-generation tensor cores: y[t][n] = sum over 32-value blocks of d_w[n,b] * d_x[t,b] * S[n,t,b],
+// S = the exact int32 dot of weight codes and 8-bit activation codes of block b -- the integer-dot arithmetic of
+// src/Sharplight.Cpu/IntDot.Kernels.cs:12-29 applied to many rows, scaled per block as the reference's int8 GEMM does
+// (src/Sharplight.Shaders/Kernels/mmq.slang:224-233 of the Sharplight tree: acc += float(C) * (d_x * d_w) - s_x * m_w).
+//
+// One CTA computes a 128 (weight rows) x 128 (tokens) tile. Roles, warp-specialised:
+//   warps 0-7   epilogue: read each block's int32 tile from tensor memory (tcgen05.ld), scale, accumulate in f32
+//               registers; warp w owns TMEM lanes 32*(w%4).. and columns 64*(w/4)..
+//   warps 8-11  producers: stream the weight records (layout.cuh) with 128-bit loads, expand 4-bit codes to int8 in
+//               registers and store them in the K-major core-matrix layout the tensor core reads; lane 0 of warp 8 also
+//               starts the bulk async copies (TMA engine) of the activation tile, which the quantizer already wrote in
+//               that layout, and of the activation scales
+//   warp 12     allocates tensor memory; its lane 0 issues tcgen05.mma kind::i8 (M=128, N=128, K=32: one quantization
+//               block per instruction, into a fresh accumulator: per-block scales forbid accumulating across blocks in
+//               int32) and commits to mbarriers
+// Pipelines: 2 shared-memory stages of 256 K-values (8 blocks), 4 TMEM accumulator buffers of 128 columns.
+// Every mbarrier wait is bounded; when one runs out the kernel raises the device status word, and every role leaves
+// through the common exit that frees tensor memory.
 #include "internal.cuh"
 
 namespace slc {
 
-bool mmq_supports(int) { return false; }
+constexpr int MQ_TILE_N = 128;     // weight rows per CTA (UMMA M)
+constexpr int MQ_TILE_T = 128;     // tokens per CTA (UMMA N)
+constexpr int MQ_STAGES = 2;
+constexpr int MQ_DBUF = 4;
+constexpr int MQ_EPI_WARPS = 8, MQ_PROD_WARPS = 4;
+constexpr int MQ_THREADS = (MQ_EPI_WARPS + MQ_PROD_WARPS + 1) * 32;
+constexpr unsigned MQ_WAIT_LIMIT = 1u << 22;
 
-cudaError_t launch_mmq(const WeightView &, const ActView &, int, float *, long long, int *, int *, cudaStream_t)
+constexpr int MQ_A_BYTES = MQ_TILE_N * 256;          // int8 codes of one stage
+constexpr int MQ_B_BYTES = MQ_TILE_T * 256;
+constexpr int MQ_DX_BYTES = 8 * MQ_TILE_T * 8;       // (d, d*sum q) per block and token
+constexpr int MQ_DW_BYTES = MQ_TILE_N * 8 * 4;       // weight scale per row and block
+constexpr int MQ_STAGE_BYTES = MQ_A_BYTES + MQ_B_BYTES + MQ_DX_BYTES + 2 * MQ_DW_BYTES;
+constexpr int MQ_SMEM_BYTES = MQ_STAGES * MQ_STAGE_BYTES + 1024;
+
+// ---- PTX wrappers ----------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ unsigned mq_smem(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mq_bar_init(uint64_t *bar, unsigned count)
 {
-    return cudaErrorNotSupported;
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mq_smem(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mq_bar_arrive(uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mq_smem(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mq_bar_expect_tx(uint64_t *bar, unsigned bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mq_smem(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mq_bulk_load(void *dst, const void *src, unsigned bytes, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(mq_smem(dst)), "l"(src), "r"(bytes), "r"(mq_smem(bar)) : "memory");
+}
+
+// Bounded wait on a phase parity. Returns false when the limit ran out.
+__device__ __forceinline__ bool mq_bar_wait(uint64_t *bar, unsigned parity)
+{
+    const unsigned b = mq_smem(bar);
+    for (unsigned i = 0; i < MQ_WAIT_LIMIT; i++) {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(b), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void mq_fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mq_tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void mq_tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] = A[smem] * B[smem], int8 x int8 -> int32, fresh accumulator.
+__device__ __forceinline__ void mq_umma_i8(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(0u), "r"(0u) : "memory");
+}
+
+__device__ __forceinline__ void mq_umma_commit(uint64_t *bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mq_smem(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mq_tmem_ld32(unsigned taddr, int (&r)[32])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+
+__device__ __forceinline__ void mq_tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major, no swizzle: 8-row x 16-byte core matrices of 128 contiguous bytes;
+// the two core matrices of one K=32 step are lbo bytes apart, groups of 8 rows sbo bytes apart.
+__device__ __forceinline__ uint64_t mq_desc(unsigned smem_addr, unsigned lbo, unsigned sbo)
+{
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+}
+
+// Instruction descriptor of kind::i8: int32 accumulator, A signed or unsigned 8-bit, B signed, both K-major.
+__host__ __device__ constexpr unsigned mq_idesc(bool a_signed, int m, int n)
+{
+    return (2u << 4) | ((a_signed ? 1u : 0u) << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ float mq_h2f(unsigned bits) { return __half2float(__ushort_as_half((unsigned short)bits)); }
+
+struct MqSmem
+{
+    uint64_t a_full[MQ_STAGES], b_full[MQ_STAGES], mma_done[MQ_STAGES], epi_done[MQ_STAGES];
+    uint64_t d_full[MQ_DBUF], d_empty[MQ_DBUF];
+    unsigned tmem_base;
+    int abort;
+};
+
+// ---- producer: one row group (16 rows) of one stage -> int8 codes in the A tile, scales in the tables ------------------
+
+template <int FMT>
+__device__ __forceinline__ void mq_expand(const WeightView &w, int rg, int rgl, int st, int lane, uint8_t *a_tile,
+                                          float *dws, float *dms)
+{
+    const int g = lane >> 2, t = lane & 3;
+    const bool live = rg * 16 < w.n_pad;
+    const uint8_t *rec = w.record(live ? rg : 0, st);
+    const uint4 *qp = reinterpret_cast<const uint4 *>(rec) + lane;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    uint8_t *row_lo = a_tile + (2 * rgl) * 2048 + g * 16, *row_hi = row_lo + 2048;   // rows g and g + 8
+    const uint4 *sp = reinterpret_cast<const uint4 *>(rec + code_bytes(FMT));
+    const uint4 s0 = live ? ld_stream(sp + g) : zero, s1 = live ? ld_stream(sp + g + 8) : zero;
+    float *dw_lo = dws + (rgl * 16 + g) * 8, *dw_hi = dw_lo + 64;
+
+    if constexpr (FMT == FMT_Q8_0) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint4 q = live ? ld_stream(qp + 32 * i) : zero;
+            const int off = (2 * i + (t >> 1)) * 128 + 8 * (t & 1);
+            *reinterpret_cast<uint2 *>(row_lo + off) = make_uint2(q.x, q.y);
+            *reinterpret_cast<uint2 *>(row_hi + off) = make_uint2(q.z, q.w);
+        }
+    } else if constexpr (FMT == FMT_Q4_0) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint4 q = live ? ld_stream(qp + 32 * i) : zero;
+            const unsigned wv[4] = { q.x, q.y, q.z, q.w };
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                // codes minus 8 as signed bytes: the block dot needs no offset term
+                const unsigned lo = __vsub4(wv[j] & 0x0F0F0F0Fu, 0x08080808u);
+                const unsigned hi = __vsub4((wv[j] >> 4) & 0x0F0F0F0Fu, 0x08080808u);
+                const int blk = 2 * i + (j >> 1);
+                uint8_t *dst = ((j & 1) ? row_hi : row_lo) + (2 * blk) * 128 + 4 * t;
+                *reinterpret_cast<unsigned *>(dst) = lo;
+                *reinterpret_cast<unsigned *>(dst + 128) = hi;
+            }
+        }
+    } else {  // Q4_K: unsigned nibbles, the mins go through the offset table
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const uint4 q = live ? ld_stream(qp + 32 * c) : zero;
+            const int off = (4 * c + (t >> 1)) * 128 + 8 * (t & 1);
+            *reinterpret_cast<uint2 *>(row_lo + off) = make_uint2(q.x & 0x0F0F0F0Fu, q.y & 0x0F0F0F0Fu);
+            *reinterpret_cast<uint2 *>(row_lo + off + 256) = make_uint2((q.x >> 4) & 0x0F0F0F0Fu, (q.y >> 4) & 0x0F0F0F0Fu);
+            *reinterpret_cast<uint2 *>(row_hi + off) = make_uint2(q.z & 0x0F0F0F0Fu, q.w & 0x0F0F0F0Fu);
+            *reinterpret_cast<uint2 *>(row_hi + off + 256) = make_uint2((q.z >> 4) & 0x0F0F0F0Fu, (q.w >> 4) & 0x0F0F0F0Fu);
+        }
+    }
+
+    // scale tables: lane t converts blocks 2t and 2t + 1 of rows g and g + 8
+    if constexpr (FMT == FMT_Q8_0 || FMT == FMT_Q4_0) {
+        const unsigned w0 = t == 0 ? s0.x : t == 1 ? s0.y : t == 2 ? s0.z : s0.w;
+        const unsigned w1 = t == 0 ? s1.x : t == 1 ? s1.y : t == 2 ? s1.z : s1.w;
+        *reinterpret_cast<float2 *>(dw_lo + 2 * t) = make_float2(mq_h2f(w0 & 0xffffu), mq_h2f(w0 >> 16));
+        *reinterpret_cast<float2 *>(dw_hi + 2 * t) = make_float2(mq_h2f(w1 & 0xffffu), mq_h2f(w1 >> 16));
+    } else {
+        float *dm_lo = dms + (rgl * 16 + g) * 8, *dm_hi = dm_lo + 64;
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const uint4 h = r ? s1 : s0;
+            const float d = mq_h2f(h.x & 0xffffu), dmin = mq_h2f(h.x >> 16);
+            const unsigned sc_lo = h.y & 0x3F3F3F3Fu, mn_lo = h.z & 0x3F3F3F3Fu;
+            const unsigned sc_hi = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
+            const unsigned mn_hi = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+            const unsigned scw = t < 2 ? sc_lo : sc_hi, mnw = t < 2 ? mn_lo : mn_hi;
+            const int sh = 16 * (t & 1);
+            const float2 sc = make_float2(d * (float)((scw >> sh) & 0xffu), d * (float)((scw >> (sh + 8)) & 0xffu));
+            const float2 mn = make_float2(dmin * (float)((mnw >> sh) & 0xffu), dmin * (float)((mnw >> (sh + 8)) & 0xffu));
+            *reinterpret_cast<float2 *>((r ? dw_hi : dw_lo) + 2 * t) = sc;
+            *reinterpret_cast<float2 *>((r ? dm_hi : dm_lo) + 2 * t) = mn;
+        }
+    }
+}
+
+// ---- the kernel ------------------------------------------------------------------------------------------------------
+
+template <int FMT, bool DUMP>
+__global__ void __launch_bounds__(MQ_THREADS, 1)
+mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_tiled, float *__restrict__ y,
+           long long y_stride, int *dump, int *status)
+{
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ MqSmem sh;
+    // 1024-byte alignment of the tiles
+    unsigned char *smem = smem_raw + ((1024 - (mq_smem(smem_raw) & 1023)) & 1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * MQ_TILE_N, t0 = blockIdx.y * MQ_TILE_T;
+    const int nst = w.k_pad >> 8;
+    constexpr bool HAS_MIN = FMT == FMT_Q4_K;
+
+    auto stage_a = [&](int s) { return smem + s * MQ_STAGE_BYTES; };
+    auto stage_b = [&](int s) { return smem + s * MQ_STAGE_BYTES + MQ_A_BYTES; };
+    auto stage_dx = [&](int s) { return reinterpret_cast<float2 *>(smem + s * MQ_STAGE_BYTES + MQ_A_BYTES + MQ_B_BYTES); };
+    auto stage_dw = [&](int s) { return reinterpret_cast<float *>(smem + s * MQ_STAGE_BYTES + MQ_A_BYTES + MQ_B_BYTES + MQ_DX_BYTES); };
+    auto stage_dm = [&](int s) { return stage_dw(s) + MQ_TILE_N * 8; };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < MQ_STAGES; s++) {
+            mq_bar_init(&sh.a_full[s], MQ_PROD_WARPS);
+            mq_bar_init(&sh.b_full[s], 1);
+            mq_bar_init(&sh.mma_done[s], 1);
+            mq_bar_init(&sh.epi_done[s], MQ_EPI_WARPS);
+        }
+        for (int b = 0; b < MQ_DBUF; b++) {
+            mq_bar_init(&sh.d_full[b], 1);
+            mq_bar_init(&sh.d_empty[b], MQ_EPI_WARPS);
+        }
+        sh.abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == MQ_EPI_WARPS + MQ_PROD_WARPS) {
+        // all 512 columns: four 128-column accumulators (one CTA per SM: the shared-memory footprint guarantees it)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(mq_smem(&sh.tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    mq_tc_fence_before();
+    __syncthreads();
+    mq_tc_fence_after();
+    const unsigned tmem = sh.tmem_base;
+
+    pdl_launch_dependents();
+    pdl_wait();   // quantized activations come from the kernel before this one; y may still be read by it
+
+    if (warp < MQ_EPI_WARPS) {
+        // ===== epilogue =====
+        const int q4 = warp & 3, half = warp >> 2;
+        const int r = q4 * 32 + lane;                 // weight row inside the tile = TMEM lane
+        const int c0 = half * 64;                     // first token column of this warp
+        float acc[64];
+#pragma unroll
+        for (int j = 0; j < 64; j++) acc[j] = 0.0f;
+        bool alive = true;
+        for (int it = 0; it < nst && alive; it++) {
+            const int s = it % MQ_STAGES;
+            const float2 *dxs = stage_dx(s);
+            const float *dws = stage_dw(s), *dms = stage_dm(s);
+            // the stage's scale tables: weight scales come from the producers, activation scales from a bulk copy
+            const unsigned spar = (unsigned)(it / MQ_STAGES) & 1u;
+            if (!mq_bar_wait(&sh.a_full[s], spar) || !mq_bar_wait(&sh.b_full[s], spar)) { alive = false; break; }
+#pragma unroll 1
+            for (int b = 0; b < 8; b++) {
+                const int i = it * 8 + b, buf = i % MQ_DBUF;
+                if (!mq_bar_wait(&sh.d_full[buf], (unsigned)(i / MQ_DBUF) & 1u)) { alive = false; break; }
+                mq_tc_fence_after();
+                const float dwv = dws[r * 8 + b];
+                const float dmv = HAS_MIN ? dms[r * 8 + b] : 0.0f;
+#pragma unroll
+                for (int cc = 0; cc < 2; cc++) {
+                    int sv[32];
+                    mq_tmem_ld32(tmem + ((unsigned)(q4 * 32) << 16) + (unsigned)(buf * MQ_TILE_T + c0 + cc * 32), sv);
+                    mq_tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float2 dx = dxs[b * MQ_TILE_T + c0 + cc * 32 + j];
+                        float v = acc[cc * 32 + j];
+                        v = fmaf((float)sv[j] * dwv, dx.x, v);
+                        if (HAS_MIN) v = fmaf(-dmv, dx.y, v);
+                        acc[cc * 32 + j] = v;
+                        if (DUMP) {
+                            const int tok = t0 + c0 + cc * 32 + j, row = n0 + r, blk = i;
+                            if (tok < a.rows && row < w.n && blk * 32 < w.k) {
+                                const int cexp = FMT == FMT_Q8_0 ? 128 : FMT == FMT_Q4_0 ? 8 : 0;
+                                const int add = cexp ? cexp * __ldg(&a.isum[(long long)tok * (a.k_pad >> 5) + blk]) : 0;
+                                dump[((long long)tok * w.n + row) * (w.k >> 5) + blk] = sv[j] + add;
+                            }
+                        }
+                    }
+                }
+                mq_tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mq_bar_arrive(&sh.d_empty[buf]);
+            }
+            __syncwarp();
+            if (lane == 0) mq_bar_arrive(&sh.epi_done[s]);   // the stage's scale tables are free
+        }
+        if (!alive) {
+            if (lane == 0) atomicExch(status, -7);
+        } else {
+            const int row = n0 + r;
+            if (row < w.n) {
+#pragma unroll
+                for (int j = 0; j < 64; j++) {
+                    const int tok = t0 + c0 + j;
+                    if (tok < a.rows) y[(long long)tok * y_stride + row] = acc[j];
+                }
+            }
+        }
+    } else if (warp < MQ_EPI_WARPS + MQ_PROD_WARPS) {
+        // ===== producers =====
+        const int pw = warp - MQ_EPI_WARPS;
+        bool alive = true;
+        for (int it = 0; it < nst && alive; it++) {
+            const int s = it % MQ_STAGES;
+            const unsigned par = ((unsigned)(it / MQ_STAGES) & 1u) ^ 1u;   // first use of a stage passes at once
+            if (!mq_bar_wait(&sh.mma_done[s], par) || !mq_bar_wait(&sh.epi_done[s], par)) { alive = false; break; }
+            if (pw == 0 && lane == 0) {
+                // activation codes (already in core-matrix order) and scales of this stage, by bulk async copy
+                mq_bar_expect_tx(&sh.b_full[s], MQ_B_BYTES + MQ_DX_BYTES);
+                const uint8_t *src = q_tiled + ((long long)it * (a.rows_pad >> 3) + (t0 >> 3)) * 2048;
+                mq_bulk_load(stage_b(s), src, MQ_B_BYTES, &sh.b_full[s]);
+                for (int b = 0; b < 8; b++) {
+                    mq_bulk_load(stage_dx(s) + b * MQ_TILE_T, a.ds + (long long)(it * 8 + b) * a.rows_pad + t0,
+                                 MQ_TILE_T * 8, &sh.b_full[s]);
+                }
+            }
+            uint8_t *at = stage_a(s);
+            mq_expand<FMT>(w, (n0 >> 4) + 2 * pw, 2 * pw, it, lane, at, stage_dw(s), stage_dm(s));
+            mq_expand<FMT>(w, (n0 >> 4) + 2 * pw + 1, 2 * pw + 1, it, lane, at, stage_dw(s), stage_dm(s));
+            mq_fence_proxy_async();   // generic-proxy stores -> visible to the tensor core's reads
+            __syncwarp();
+            if (lane == 0) mq_bar_arrive(&sh.a_full[s]);
+        }
+        if (!alive && lane == 0) atomicExch(status, -7);
+    } else {
+        // ===== MMA issuer =====
+        if (lane == 0) {
+            constexpr unsigned idesc = mq_idesc(FMT != FMT_Q4_K, MQ_TILE_N, MQ_TILE_T);
+            bool alive = true;
+            for (int it = 0; it < nst && alive; it++) {
+                const int s = it % MQ_STAGES;
+                const unsigned par = (unsigned)(it / MQ_STAGES) & 1u;
+                if (!mq_bar_wait(&sh.a_full[s], par) || !mq_bar_wait(&sh.b_full[s], par)) { alive = false; break; }
+                mq_tc_fence_after();
+                const unsigned a_addr = mq_smem(stage_a(s)), b_addr = mq_smem(stage_b(s));
+                for (int b = 0; b < 8; b++) {
+                    const int i = it * 8 + b, buf = i % MQ_DBUF;
+                    if (!mq_bar_wait(&sh.d_empty[buf], ((unsigned)(i / MQ_DBUF) & 1u) ^ 1u)) { alive = false; break; }
+                    mq_tc_fence_after();
+                    mq_umma_i8(tmem + (unsigned)(buf * MQ_TILE_T), mq_desc(a_addr + b * 256, 128, 2048),
+                               mq_desc(b_addr + b * 256, 128, 2048), idesc);
+                    mq_umma_commit(&sh.d_full[buf]);
+                }
+                if (alive) mq_umma_commit(&sh.mma_done[s]);
+            }
+            if (!alive) atomicExch(status, -7);
+        }
+        __syncwarp();
+    }
+
+    mq_tc_fence_before();
+    __syncthreads();
+    if (warp == MQ_EPI_WARPS + MQ_PROD_WARPS) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+bool mmq_supports(int fmt) { return fmt == FMT_Q4_0 || fmt == FMT_Q8_0 || fmt == FMT_Q4_K; }
+
+template <int FMT, bool DUMP>
+static cudaError_t mmq_launch_one(const WeightView &w, const ActView &a, const uint8_t *q_tiled, float *y,
+                                  long long y_stride, int *dump, int *status, cudaStream_t stream)
+{
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto kernel = mmq_kernel<FMT, DUMP>;
+    if (dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MQ_SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    const dim3 grid((w.n_pad + MQ_TILE_N - 1) / MQ_TILE_N, (a.rows + MQ_TILE_T - 1) / MQ_TILE_T);
+    return launch_pdl(kernel, grid, dim3(MQ_THREADS), MQ_SMEM_BYTES, stream, w, a, q_tiled, y, y_stride, dump, status);
+}
+
+// a.rows_pad must be a multiple of 128 and q_tiled the core-matrix copy of the activation codes (quantize.cu).
+cudaError_t launch_mmq(const WeightView &w, const ActView &a, const uint8_t *q_tiled, float *y, long long y_stride,
+                       int *dump, int *status, cudaStream_t stream)
+{
+    if (w.n_pad == 0 || a.rows == 0) return cudaSuccess;
+    if ((a.rows_pad % MQ_TILE_T) != 0 || !q_tiled) return cudaErrorInvalidValue;
+#define SLC_FMT(F)                                                                                 \
+    case F:                                                                                        \
+        return dump ? mmq_launch_one<F, true>(w, a, q_tiled, y, y_stride, dump, status, stream)    \
+                    : mmq_launch_one<F, false>(w, a, q_tiled, y, y_stride, nullptr, status, stream);
+    switch (w.fmt) {
+        SLC_FMT(FMT_Q4_0) SLC_FMT(FMT_Q8_0) SLC_FMT(FMT_Q4_K)
+    default: return cudaErrorInvalidValue;
+    }
+#undef SLC_FMT
 }
 
 }  // namespace slc

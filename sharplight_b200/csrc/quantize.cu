@@ -57,6 +57,15 @@ __global__ void __launch_bounds__(256) quantize_kernel(const void *__restrict__ 
     const unsigned packed = (unsigned)(r[0] & 0xff) | ((unsigned)(r[1] & 0xff) << 8) | ((unsigned)(r[2] & 0xff) << 16) |
                             ((unsigned)(r[3] & 0xff) << 24);
     *reinterpret_cast<unsigned *>(out.q + (long long)row * k_pad + blk * 32 + sub * 4) = packed;
+    if (out.q_tiled) {
+        // the same codes as 8-token x 16-byte core matrices, [super-tile][token / 8][16-byte K chunk][token % 8][16]:
+        // a 128-token x 256-value tile is then 32 KB of contiguous bytes, ready for one bulk copy into the layout the
+        // tensor core reads
+        const int kk = blk * 32 + sub * 4;
+        const long long off = ((long long)(kk >> 8) * (rows_pad >> 3) + (row >> 3)) * 2048 + ((kk & 255) >> 4) * 128 +
+                              (row & 7) * 16 + (kk & 15);
+        *reinterpret_cast<unsigned *>(out.q_tiled + off) = packed;
+    }
     s += __shfl_xor_sync(0xffffffffu, s, 1);
     s += __shfl_xor_sync(0xffffffffu, s, 2);        // sum of this lane's 16-value group
     const int s_other = __shfl_xor_sync(0xffffffffu, s, 4);

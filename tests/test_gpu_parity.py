@@ -306,3 +306,47 @@ def test_intdot_stays_close_to_exact_product_at_full_size(cuda_device):
     finally:
         op.dispose()
         w.dispose()
+
+
+# ---- prefill: the tensor-core GEMM ------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("type_name", ["Q4_0", "Q8_0", "Q4_K"])
+@pytest.mark.parametrize("rows,n,k", [(65, 96, 512), (200, 100, 512), (300, 520, 512), (129, 128, 256), (1000, 3000, 256)])
+def test_mmq_shapes(cuda_device, type_name, rows, n, k):
+    """MmqTests (tests/Sharplight.Vulkan.Tests/MmqTests.cs:21-98): (T, N) in {(65, 96), (200, 100), (300, 520)} at
+    K = 512 and the large grid T = 1000, N = 3000, K = 256; here every block dot is also compared bit for bit."""
+    _, (used, launches) = check_matmul(cuda_device, type_name, n, k, rows, seed=rows + n, kernel=N.KERNEL_MMQ,
+                                       dots=(rows * n <= 300 * 520))
+    assert used == N.KERNEL_MMQ and launches >= 1
+
+
+@pytest.mark.parametrize("type_name", ["Q4_0", "Q8_0", "Q4_K"])
+def test_mmq_exact_int8_activations(cuda_device, type_name):
+    """MmqTests' exact-activation case (K = 1024): atol 2e-3, rtol 1e-3 against the product with the dequantized weight."""
+    n, k, rows = 520, 1024, 300
+    blocks = synth.weight_blocks(type_name, n, k, 41)
+    x = synth.exact_int8_activations(rows, k, 42)
+    y, _ = check_matmul(cuda_device, type_name, n, k, rows, blocks=blocks, x=x, dots=False, kernel=N.KERNEL_MMQ)
+    exact = sl_oracle.matmul_f64(FMT_OF[type_name], blocks, n, k, x, threads=8)
+    assert np.all(np.abs(y - exact) <= 2e-3 + 1e-3 * np.abs(exact))
+
+
+def test_config3_q4_0_prefill_bf16(cuda_device):
+    """BASELINE config 3 at full size: Q4_0 [4096, 4096], bf16 activations [2048, 4096]. The oracle checks a sample of
+    the token rows (rows are independent), every weight row; the block dots of a second, smaller sample bit for bit."""
+    n, k, rows = 4096, 4096, 2048
+    blocks = synth.weight_blocks("Q4_0", n, k, 103)
+    bits = to_bf16_bits(synth.activations(rows, k, 104))
+    w = cuda_device.upload_weight("Q4_0", (n, k), blocks)
+    op = MatMulOp(cuda_device, w, rows)
+    try:
+        y = op.run(bits, N.BF16)
+        assert op.last_kernel()[0] == N.KERNEL_MMQ
+        sample = np.random.Generator(np.random.Philox(5)).choice(rows, 24, replace=False)
+        xs = bf16_bits_to_f32(bits[sample])
+        ref, ref64, _ = sl_oracle.matmul_intdot(2, blocks, n, k, xs, threads=8, want_f64=True)
+        assert max_rel_error(y[sample], ref) <= MAX_REL
+        assert max_rel_error(y[sample], ref64) <= MAX_REL
+    finally:
+        op.dispose()
+        w.dispose()
