@@ -141,6 +141,67 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def prefill_leg(device, torch, N, synth, stream, steps):
+    """BASELINE config 3: Q4_0 [4096, 4096], bf16 activations [2048, 4096] on the tcgen05 int8 GEMM.
+    Operator time = quantization + GEMM (what the reference's published TFLOPS include,
+    tests/Sharplight.Vulkan.Tests/BenchTests.cs:28-46); kernel time = the GEMM alone on quantized activations."""
+    from sharplight_b200 import MatMulOp, SharedActivation
+    from sharplight_b200.provider import to_bf16_bits
+    n, k, m, copies = 4096, 4096, 2048, 8
+    base = synth.weight_blocks("Q4_0", n, k, seed=300)
+    ws = [device.upload_weight("Q4_0", (n, k), np.roll(base.reshape(n, -1), 11 * i, axis=0).reshape(-1))
+          for i in range(copies)]
+    ops = [MatMulOp(device, w, m) for w in ws]
+    x = torch.from_numpy(to_bf16_bits(synth.activations(m, k, seed=301)).view(np.int16)).cuda()
+    y = torch.empty((copies, m, n), dtype=torch.float32, device="cuda")
+    act = SharedActivation(device, m, k)
+    sp = stream.cuda_stream
+
+    def op_step(p=sp):
+        for i, op in enumerate(ops):
+            op.run_pointers(x.data_ptr(), N.BF16, m, k, True, y[i].data_ptr(), n, True, p)
+
+    def gemm_step(p=sp):
+        for i, op in enumerate(ops):
+            act.matmul(op, y[i].data_ptr(), n, p)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=torch.cuda.Stream()):
+            fn(torch.cuda.current_stream().cuda_stream)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            g.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / (steps * copies)
+
+    t_op = timed(op_step)
+    act.quantize(x.data_ptr(), N.BF16, m, k, sp)
+    t_gemm = timed(gemm_step)
+    family, _ = ops[0].last_kernel()
+    ops_count = 2.0 * m * n * k
+    out = {"workload": "configs[2]: Q4_0 [4096,4096] x bf16 [2048,4096], 8 rotating weight copies",
+           "operator_tops": ops_count / t_op / 1e12, "gemm_kernel_tops": ops_count / t_gemm / 1e12,
+           "operator_us": t_op * 1e6, "gemm_kernel_us": t_gemm * 1e6,
+           "frac_of_nominal_int8_4500": ops_count / t_gemm / 4.5e15,
+           "kernel_family": {1: "mmvq (dp4a)", 2: "skinny (int8 mma)", 3: "mmq (tcgen05)"}[family],
+           "block_scale_fmas": m * n * (k // 32)}
+    for op in ops:
+        op.dispose()
+    for w in ws:
+        w.dispose()
+    act.dispose()
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -252,6 +313,10 @@ def run_ours(args):
     torch.cuda.synchronize()
     same = bool(torch.equal(y_dev.cpu(), y_host)) if not args.no_e2e else None
 
+    prefill = None
+    if world == 1 and not args.no_prefill:
+        prefill = prefill_leg(device, torch, N, synth, stream, max(5, args.steps // 10))
+
     peak, peak_kind = measured_peaks()
     algo_bytes = wbytes + rows * k + rows * (k // 32) * 8 + rows * n * 4
     sec_per_launch = ms_kernel_step * 1e-3 / (COPIES * main_launches)
@@ -280,6 +345,8 @@ def run_ours(args):
                 "clocks": clocks, "device_equals_host_path": same}
         if base is not None:
             line["cpu_baseline"] = base
+        if prefill is not None:
+            line["prefill"] = prefill
         print(json.dumps(line), flush=True)
     for op in ops:
         op.dispose()
@@ -302,6 +369,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--copies", type=int, default=COPIES, help="weight matrices per step (profiling runs use fewer)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM leg")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of a CUDA graph")
     args = ap.parse_args()
     COPIES = args.copies

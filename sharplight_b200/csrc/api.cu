@@ -409,7 +409,7 @@ slc_result slc_activation_create(slc_device *d, int64_t max_rows, int64_t k, slc
     const size_t q_b = round_up(cap * kp, 256), ds_b = round_up(cap * (kp / 32) * 8, 256);
     const size_t gs_b = round_up(cap * (kp / 16) * 4, 256), is_b = round_up(cap * (kp / 32) * 4, 256);
     const size_t qt_b = a->cap_rows > 64 ? q_b : 0;   // core-matrix copy for the tensor-core GEMM
-    a->bytes = q_b + ds_b + gs_b + is_b + qt_b;
+    a->bytes = q_b + 2 * ds_b + gs_b + is_b + qt_b;
     cudaError_t e = cudaMalloc(&a->base, a->bytes);
     if (e == cudaSuccess) e = cudaMemset(a->base, 0, a->bytes);
     if (e != cudaSuccess) {
@@ -419,9 +419,11 @@ slc_result slc_activation_create(slc_device *d, int64_t max_rows, int64_t k, slc
     }
     a->planes.q = reinterpret_cast<int8_t *>(a->base);
     a->planes.ds = reinterpret_cast<float2 *>(a->base + q_b);
-    a->planes.gs = reinterpret_cast<float *>(a->base + q_b + ds_b);
-    a->planes.isum = reinterpret_cast<int *>(a->base + q_b + ds_b + gs_b);
-    a->q_tiled = qt_b ? a->base + q_b + ds_b + gs_b + is_b : nullptr;
+    a->planes.dx = reinterpret_cast<float *>(a->base + q_b + ds_b);
+    a->planes.sx = reinterpret_cast<float *>(a->base + q_b + ds_b + ds_b / 2);
+    a->planes.gs = reinterpret_cast<float *>(a->base + q_b + 2 * ds_b);
+    a->planes.isum = reinterpret_cast<int *>(a->base + q_b + 2 * ds_b + gs_b);
+    a->q_tiled = qt_b ? a->base + q_b + 2 * ds_b + gs_b + is_b : nullptr;
     *out = a;
     return SLC_OK;
 }
@@ -457,7 +459,8 @@ static ActView view_of(const slc_activation *a)
 {
     ActView v;
     v.rows = a->rows; v.rows_pad = a->rows_pad; v.k = (int)a->k; v.k_pad = a->k_pad;
-    v.q = a->planes.q; v.ds = a->planes.ds; v.gs = a->planes.gs; v.isum = a->planes.isum;
+    v.q = a->planes.q; v.ds = a->planes.ds; v.dx = a->planes.dx; v.sx = a->planes.sx; v.gs = a->planes.gs;
+    v.isum = a->planes.isum;
     return v;
 }
 
@@ -685,5 +688,17 @@ slc_result slc_debug_block_dots(slc_matmul *op, const void *x, int32_t x_dtype, 
     cudaFree(dump);
     return r;
 }
+
+#ifdef MQ_TIMING
+// Measurement builds only: the cycle counters the GEMM kernel adds up behind the status word.
+__attribute__((visibility("default"))) slc_result slc_debug_timing(slc_device *d, int32_t *out48, int32_t clear)
+{
+    cudaSetDevice(d->index);
+    cudaDeviceSynchronize();
+    cudaMemcpy(out48, d->status_dev + 16, 48 * sizeof(int), cudaMemcpyDeviceToHost);
+    if (clear) cudaMemset(d->status_dev + 16, 0, 48 * sizeof(int));
+    return SLC_OK;
+}
+#endif
 
 }  // extern "C"

@@ -39,6 +39,7 @@ struct ActPlanes
     uint8_t *q_tiled;   // optional second copy of the codes in tensor-core core-matrix order (mmq.cu), or null
     int8_t *q;
     float2 *ds;
+    float *dx, *sx;
     float *gs;
     int *isum;
 };

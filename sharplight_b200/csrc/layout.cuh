@@ -41,6 +41,7 @@
 // Quantized activations (the reference's Q8Row, src/Sharplight.Cpu/Q8Row.cs:9-20, in a GPU-friendly arrangement):
 //   q    int8   [rows_pad][k_pad]        codes, zero beyond K
 //   ds   float2 [k_pad/32][rows_pad]     (d, d * sum32(q)) per block, token-minor so neighbouring tokens share a load
+//   dx, sx float [k_pad/32][rows_pad]    the two halves of ds as planes of their own (GEMM scale tables)
 //   gs   float  [rows_pad][k_pad/16]     d * sum16(q), the reference's group sums (parity export)
 //   isum int32  [rows_pad][k_pad/32]     sum32(q) (parity export: converts signed block dots to unsigned-code dots)
 // rows_pad = rows rounded up to 8, 16, 32 or a multiple of 64.
@@ -98,6 +99,8 @@ struct ActView
     int k, k_pad;
     const int8_t *q;     // [rows_pad][k_pad]
     const float2 *ds;    // [k_pad/32][rows_pad]
+    const float *dx;     // [k_pad/32][rows_pad] d alone, and
+    const float *sx;     // [k_pad/32][rows_pad] d * sum32(q) alone: the planes the tensor-core GEMM bulk-copies
     const float *gs;     // [rows_pad][k_pad/16]
     const int *isum;     // [rows_pad][k_pad/32]
 };

@@ -21,7 +21,7 @@ namespace slc {
 
 constexpr int FV_MAX_WARPS = 8;
 constexpr int FV_STAGES = 2;
-constexpr unsigned FV_WAIT_LIMIT = 1u << 22;
+constexpr unsigned FV_WAIT_LIMIT = 100000;   // attempts of up to ~20 us each (suspend-time hint): about two seconds
 constexpr int FV_MAX_SMEM = 100 * 1024;
 
 template <int FMT> struct FTile;
@@ -56,8 +56,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity)
     const unsigned b = smem_u32(bar);
     for (unsigned i = 0; i < FV_WAIT_LIMIT; i++) {
         unsigned ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(b), "r"(parity) : "memory");
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(b), "r"(parity), "r"(20000u) : "memory");
         if (ok) return true;
     }
     return false;

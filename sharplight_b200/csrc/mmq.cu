@@ -11,9 +11,10 @@
 //               starts the bulk async copies (TMA engine) of the activation tile, which the quantizer already wrote in
 //               that layout, and of the activation scales
 //   warp 12     allocates tensor memory; its lane 0 issues tcgen05.mma kind::i8 (M=128, N=128, K=32: one quantization
-//               block per instruction, into a fresh accumulator: per-block scales forbid accumulating across blocks in
-//               int32) and commits to mbarriers
-// Pipelines: 2 shared-memory stages of 256 K-values (8 blocks), 4 TMEM accumulator buffers of 128 columns.
+//               block per instruction, each into its own accumulator buffer: per-block scales forbid accumulating
+//               across blocks in int32) and commits to mbarriers
+// Pipelines: 3 shared-memory stages of 256 K-values (8 blocks), 4 TMEM accumulator buffers of 128 columns; the
+// producers keep the next stage's weight records in registers while the current one is expanded.
 // Every mbarrier wait is bounded; when one runs out the kernel raises the device status word, and every role leaves
 // through the common exit that frees tensor memory.
 #include "internal.cuh"
@@ -22,18 +23,25 @@ namespace slc {
 
 constexpr int MQ_TILE_N = 128;     // weight rows per CTA (UMMA M)
 constexpr int MQ_TILE_T = 128;     // tokens per CTA (UMMA N)
-constexpr int MQ_STAGES = 2;
+// shared-memory stages: three, or two for the format with an offset table (Q4_K), whose stage is 8 KB larger
+__host__ __device__ constexpr int mq_stages(int fmt) { return fmt == FMT_Q4_K ? 2 : 3; }
+constexpr int MQ_MAX_STAGES = 3;
 constexpr int MQ_DBUF = 4;
 constexpr int MQ_EPI_WARPS = 8, MQ_PROD_WARPS = 4;
-constexpr int MQ_THREADS = (MQ_EPI_WARPS + MQ_PROD_WARPS + 1) * 32;
-constexpr unsigned MQ_WAIT_LIMIT = 1u << 22;
+constexpr int MQ_THREADS = 512;   // warps 0-7 epilogue, 8-11 producers, 12 MMA issuer, 13-15 idle (they fill the warpgroup)
+// a wait suspends in hardware for up to ~20 us per attempt (the hint below) instead of spinning on issue slots the
+// epilogue needs; 100000 attempts bound it at about two seconds
+constexpr unsigned MQ_WAIT_LIMIT = 100000;
 
 constexpr int MQ_A_BYTES = MQ_TILE_N * 256;          // int8 codes of one stage
 constexpr int MQ_B_BYTES = MQ_TILE_T * 256;
-constexpr int MQ_DX_BYTES = 8 * MQ_TILE_T * 8;       // (d, d*sum q) per block and token
-constexpr int MQ_DW_BYTES = MQ_TILE_N * 8 * 4;       // weight scale per row and block
-constexpr int MQ_STAGE_BYTES = MQ_A_BYTES + MQ_B_BYTES + MQ_DX_BYTES + 2 * MQ_DW_BYTES;
-constexpr int MQ_SMEM_BYTES = MQ_STAGES * MQ_STAGE_BYTES + 1024;
+constexpr int MQ_DX_BYTES = 8 * MQ_TILE_T * 4;       // d per block and token (a second table of d * sum32(q) for Q4_K)
+constexpr int MQ_DW_BYTES = MQ_TILE_N * 8 * 4;       // weight scale per row and block (a second table of mins for Q4_K)
+__host__ __device__ constexpr int mq_stage_bytes(int fmt)
+{
+    return MQ_A_BYTES + MQ_B_BYTES + (fmt == FMT_Q4_K ? 2 : 1) * (MQ_DX_BYTES + MQ_DW_BYTES);
+}
+__host__ __device__ constexpr int mq_smem_bytes(int fmt) { return mq_stages(fmt) * mq_stage_bytes(fmt) + 1024; }
 
 // ---- PTX wrappers ----------------------------------------------------------------------------------------------------
 
@@ -66,8 +74,8 @@ __device__ __forceinline__ bool mq_bar_wait(uint64_t *bar, unsigned parity)
     const unsigned b = mq_smem(bar);
     for (unsigned i = 0; i < MQ_WAIT_LIMIT; i++) {
         unsigned ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(b), "r"(parity) : "memory");
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(b), "r"(parity), "r"(20000u) : "memory");
         if (ok) return true;
     }
     return false;
@@ -77,12 +85,13 @@ __device__ __forceinline__ void mq_fence_proxy_async() { asm volatile("fence.pro
 __device__ __forceinline__ void mq_tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void mq_tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// D[tmem] = A[smem] * B[smem], int8 x int8 -> int32, fresh accumulator.
+// D[tmem] += A[smem] * B[smem], int8 x int8 -> int32. The accumulator holds MQ_BIAS when the instruction starts (the
+// epilogue re-arms it), so the result is MQ_BIAS + block dot: the bit pattern of the float 12582912 + dot.
 __device__ __forceinline__ void mq_umma_i8(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc)
 {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(0u), "r"(0u) : "memory");
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(1u), "r"(0u) : "memory");
 }
 
 __device__ __forceinline__ void mq_umma_commit(uint64_t *bar)
@@ -102,6 +111,30 @@ __device__ __forceinline__ void mq_tmem_ld32(unsigned taddr, int (&r)[32])
                  : "r"(taddr) : "memory");
 }
 
+__device__ __forceinline__ void mq_tmem_ld16(unsigned taddr, int (&r)[16])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
+
+// int32 -> f32 without a conversion instruction (the conversion unit delivers 16 results per clock per SM, which alone
+// would cost ~1000 cycles per 128x128 block): for |s| < 2^22 the bit pattern 0x4B400000 + s is the float 12582912 + s.
+// The tensor core does the integer add: every accumulator buffer is pre-loaded with the pattern.
+constexpr int MQ_BIAS = 0x4B400000;
+constexpr float MQ_BIAS_F = 12582912.0f;
+
+__device__ __forceinline__ void mq_tmem_st16_const(unsigned taddr, int v)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                 "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+                 ::"r"(taddr), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void mq_tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ void mq_tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, K-major, no swizzle: 8-row x 16-byte core matrices of 128 contiguous bytes;
@@ -120,9 +153,19 @@ __host__ __device__ constexpr unsigned mq_idesc(bool a_signed, int m, int n)
 
 __device__ __forceinline__ float mq_h2f(unsigned bits) { return __half2float(__ushort_as_half((unsigned short)bits)); }
 
+// Optional cycle accounting of the wait sites (a measurement build only: -DMQ_TIMING). CTA (0, 0) adds its cycles, in
+// units of 16, to status[16 + slot].
+#ifdef MQ_TIMING
+#define MQ_T0() const long long mq_t0_ = clock64()
+#define MQ_T1(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) atomicAdd(status + 16 + (slot), (int)((clock64() - mq_t0_) >> 4)); } while (0)
+#else
+#define MQ_T0() do { } while (0)
+#define MQ_T1(slot) do { } while (0)
+#endif
+
 struct MqSmem
 {
-    uint64_t a_full[MQ_STAGES], b_full[MQ_STAGES], mma_done[MQ_STAGES], epi_done[MQ_STAGES];
+    uint64_t a_full[MQ_MAX_STAGES], b_full[MQ_MAX_STAGES], mma_done[MQ_MAX_STAGES], epi_done[MQ_MAX_STAGES];
     uint64_t d_full[MQ_DBUF], d_empty[MQ_DBUF];
     unsigned tmem_base;
     int abort;
@@ -131,23 +174,41 @@ struct MqSmem
 // ---- producer: one row group (16 rows) of one stage -> int8 codes in the A tile, scales in the tables ------------------
 
 template <int FMT>
-__device__ __forceinline__ void mq_expand(const WeightView &w, int rg, int rgl, int st, int lane, uint8_t *a_tile,
-                                          float *dws, float *dms)
+struct MqRegs
 {
-    const int g = lane >> 2, t = lane & 3;
+    uint4 q[code_units(FMT) / 32];
+    uint4 s0, s1;
+};
+
+// The record of (rg, st) into registers (zeros for row groups beyond the weight).
+template <int FMT>
+__device__ __forceinline__ void mq_load(MqRegs<FMT> &rr, const WeightView &w, int rg, int st, int lane)
+{
+    const int g = lane >> 2;
     const bool live = rg * 16 < w.n_pad;
     const uint8_t *rec = w.record(live ? rg : 0, st);
     const uint4 *qp = reinterpret_cast<const uint4 *>(rec) + lane;
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    uint8_t *row_lo = a_tile + (2 * rgl) * 2048 + g * 16, *row_hi = row_lo + 2048;   // rows g and g + 8
+#pragma unroll
+    for (int i = 0; i < code_units(FMT) / 32; i++) rr.q[i] = live ? ld_stream(qp + 32 * i) : zero;
     const uint4 *sp = reinterpret_cast<const uint4 *>(rec + code_bytes(FMT));
-    const uint4 s0 = live ? ld_stream(sp + g) : zero, s1 = live ? ld_stream(sp + g + 8) : zero;
+    rr.s0 = live ? ld_stream(sp + g) : zero;
+    rr.s1 = live ? ld_stream(sp + g + 8) : zero;
+}
+
+// Registers -> int8 codes in the A tile (rows rgl*16 .. +15), scales in the tables.
+template <int FMT>
+__device__ __forceinline__ void mq_store(const MqRegs<FMT> &rr, int rgl, int lane, uint8_t *a_tile, float *dws, float *dms)
+{
+    const int g = lane >> 2, t = lane & 3;
+    uint8_t *row_lo = a_tile + (2 * rgl) * 2048 + g * 16, *row_hi = row_lo + 2048;   // rows g and g + 8
+    const uint4 s0 = rr.s0, s1 = rr.s1;
     float *dw_lo = dws + (rgl * 16 + g) * 8, *dw_hi = dw_lo + 64;
 
     if constexpr (FMT == FMT_Q8_0) {
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            const uint4 q = live ? ld_stream(qp + 32 * i) : zero;
+            const uint4 q = rr.q[i];
             const int off = (2 * i + (t >> 1)) * 128 + 8 * (t & 1);
             *reinterpret_cast<uint2 *>(row_lo + off) = make_uint2(q.x, q.y);
             *reinterpret_cast<uint2 *>(row_hi + off) = make_uint2(q.z, q.w);
@@ -155,7 +216,7 @@ __device__ __forceinline__ void mq_expand(const WeightView &w, int rg, int rgl, 
     } else if constexpr (FMT == FMT_Q4_0) {
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const uint4 q = live ? ld_stream(qp + 32 * i) : zero;
+            const uint4 q = rr.q[i];
             const unsigned wv[4] = { q.x, q.y, q.z, q.w };
 #pragma unroll
             for (int j = 0; j < 4; j++) {
@@ -171,7 +232,7 @@ __device__ __forceinline__ void mq_expand(const WeightView &w, int rg, int rgl, 
     } else {  // Q4_K: unsigned nibbles, the mins go through the offset table
 #pragma unroll
         for (int c = 0; c < 4; c++) {
-            const uint4 q = live ? ld_stream(qp + 32 * c) : zero;
+            const uint4 q = rr.q[c];
             const int off = (4 * c + (t >> 1)) * 128 + 8 * (t & 1);
             *reinterpret_cast<uint2 *>(row_lo + off) = make_uint2(q.x & 0x0F0F0F0Fu, q.y & 0x0F0F0F0Fu);
             *reinterpret_cast<uint2 *>(row_lo + off + 256) = make_uint2((q.x >> 4) & 0x0F0F0F0Fu, (q.y >> 4) & 0x0F0F0F0Fu);
@@ -220,12 +281,15 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
     const int n0 = blockIdx.x * MQ_TILE_N, t0 = blockIdx.y * MQ_TILE_T;
     const int nst = w.k_pad >> 8;
     constexpr bool HAS_MIN = FMT == FMT_Q4_K;
+    constexpr int MQ_STAGES = mq_stages(FMT), MQ_STAGE_BYTES = mq_stage_bytes(FMT);
 
+    // stage layout: A codes, B codes, d_x table, d_w table, then (Q4_K) the d_x * sum q table and the mins table
     auto stage_a = [&](int s) { return smem + s * MQ_STAGE_BYTES; };
     auto stage_b = [&](int s) { return smem + s * MQ_STAGE_BYTES + MQ_A_BYTES; };
-    auto stage_dx = [&](int s) { return reinterpret_cast<float2 *>(smem + s * MQ_STAGE_BYTES + MQ_A_BYTES + MQ_B_BYTES); };
-    auto stage_dw = [&](int s) { return reinterpret_cast<float *>(smem + s * MQ_STAGE_BYTES + MQ_A_BYTES + MQ_B_BYTES + MQ_DX_BYTES); };
-    auto stage_dm = [&](int s) { return stage_dw(s) + MQ_TILE_N * 8; };
+    auto stage_dx = [&](int s) { return reinterpret_cast<float *>(smem + s * MQ_STAGE_BYTES + MQ_A_BYTES + MQ_B_BYTES); };
+    auto stage_dw = [&](int s) { return stage_dx(s) + 8 * MQ_TILE_T; };
+    auto stage_sx = [&](int s) { return stage_dw(s) + MQ_TILE_N * 8; };
+    auto stage_dm = [&](int s) { return stage_sx(s) + 8 * MQ_TILE_T; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < MQ_STAGES; s++) {
@@ -253,58 +317,153 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
 
     pdl_launch_dependents();
     pdl_wait();   // quantized activations come from the kernel before this one; y may still be read by it
+#ifdef MQ_TIMING
+    const long long mq_kernel_t0 = clock64();
+#endif
+
+    // Register budget: launched at 128 per thread; the two epilogue warpgroups take more and the other two give back
+    // (256 x 168 + 256 x 88 = 256 x 152 + 256 x 104 = 65536). Q8_0's producers hold the larger records in registers.
+    if constexpr (FMT == FMT_Q8_0) {
+        if (warp < MQ_EPI_WARPS) asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+        else asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+    } else {
+        if (warp < MQ_EPI_WARPS) asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
+        else asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+    }
 
     if (warp < MQ_EPI_WARPS) {
         // ===== epilogue =====
         const int q4 = warp & 3, half = warp >> 2;
         const int r = q4 * 32 + lane;                 // weight row inside the tile = TMEM lane
         const int c0 = half * 64;                     // first token column of this warp
+        const unsigned tlane = tmem + ((unsigned)(q4 * 32) << 16) + (unsigned)c0;
         float acc[64];
 #pragma unroll
         for (int j = 0; j < 64; j++) acc[j] = 0.0f;
         bool alive = true;
-        for (int it = 0; it < nst && alive; it++) {
-            const int s = it % MQ_STAGES;
-            const float2 *dxs = stage_dx(s);
-            const float *dws = stage_dw(s), *dms = stage_dm(s);
-            // the stage's scale tables: weight scales come from the producers, activation scales from a bulk copy
-            const unsigned spar = (unsigned)(it / MQ_STAGES) & 1u;
-            if (!mq_bar_wait(&sh.a_full[s], spar) || !mq_bar_wait(&sh.b_full[s], spar)) { alive = false; break; }
-#pragma unroll 1
-            for (int b = 0; b < 8; b++) {
-                const int i = it * 8 + b, buf = i % MQ_DBUF;
-                if (!mq_bar_wait(&sh.d_full[buf], (unsigned)(i / MQ_DBUF) & 1u)) { alive = false; break; }
-                mq_tc_fence_after();
-                const float dwv = dws[r * 8 + b];
-                const float dmv = HAS_MIN ? dms[r * 8 + b] : 0.0f;
+        const int total = nst * 8;
+        int sa[32], sb[32];
+
+        // arm this warp's part of every accumulator buffer with the bias, then open the buffers for the MMA issuer
 #pragma unroll
-                for (int cc = 0; cc < 2; cc++) {
-                    int sv[32];
-                    mq_tmem_ld32(tmem + ((unsigned)(q4 * 32) << 16) + (unsigned)(buf * MQ_TILE_T + c0 + cc * 32), sv);
-                    mq_tmem_wait_ld();
+        for (int buf = 0; buf < MQ_DBUF; buf++) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) mq_tmem_st16_const(tlane + (unsigned)(buf * MQ_TILE_T + q * 16), MQ_BIAS);
+        }
+        mq_tmem_wait_st();
+        mq_tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+            for (int buf = 0; buf < MQ_DBUF; buf++) mq_bar_arrive(&sh.d_empty[buf]);
+        }
+
+        // Tensor-memory loads take a few hundred cycles: both halves of a block are requested together, and the
+        // next block's halves are requested as soon as the registers of the current ones have been consumed.
+        if (total > 0) {
+            if (mq_bar_wait(&sh.d_full[0], 0)) {
+                mq_tc_fence_after();
+                mq_tmem_ld32(tlane, sa);
+                mq_tmem_ld32(tlane + 32, sb);
+            } else {
+                alive = false;
+            }
+        }
+        for (int i = 0; i < total && alive; i++) {
+            const int it = i >> 3, b = i & 7, s = it % MQ_STAGES, buf = i % MQ_DBUF;
+            if (b == 0) {
+                // the stage's scale tables: weight scales come from the producers, activation scales from a bulk copy
+                const unsigned spar = (unsigned)(it / MQ_STAGES) & 1u;
+                MQ_T0();
+                if (!mq_bar_wait(&sh.a_full[s], spar) || !mq_bar_wait(&sh.b_full[s], spar)) { alive = false; break; }
+                if (warp == 0) MQ_T1(1);
+            }
+            const float *dxs = stage_dx(s) + b * MQ_TILE_T + c0, *sxs = stage_sx(s) + b * MQ_TILE_T + c0;
+            const float dwv = stage_dw(s)[r * 8 + b];
+            const float dmv = HAS_MIN ? -stage_dm(s)[r * 8 + b] : 0.0f;
+            // (biased - 12582912) * d_w as one FMA: the constant -12582912 * d_w is exact when d_w comes from an f16
+            const float cw = -MQ_BIAS_F * dwv;
+            const unsigned tcol = tlane + (unsigned)(buf * MQ_TILE_T);
+
+            auto scale32 = [&](const int (&sv)[32], int q) {
+#pragma unroll
+                for (int j4 = 0; j4 < 8; j4++) {
+                    const float4 dx = *reinterpret_cast<const float4 *>(dxs + q * 32 + j4 * 4);
+                    const float dxv[4] = { dx.x, dx.y, dx.z, dx.w };
+                    float sxv[4] = { 0.f, 0.f, 0.f, 0.f };
+                    if (HAS_MIN) {
+                        const float4 sx = *reinterpret_cast<const float4 *>(sxs + q * 32 + j4 * 4);
+                        sxv[0] = sx.x; sxv[1] = sx.y; sxv[2] = sx.z; sxv[3] = sx.w;
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float f = __int_as_float(sv[j4 * 4 + e]);
+                        float v = acc[q * 32 + j4 * 4 + e];
+                        if (HAS_MIN) {
+                            // d_w = d * sc is a rounded product: keep the subtraction exact, then scale
+                            v = fmaf((f - MQ_BIAS_F) * dwv, dxv[e], v);
+                            v = fmaf(dmv, sxv[e], v);
+                        } else {
+                            v = fmaf(fmaf(f, dwv, cw), dxv[e], v);
+                        }
+                        acc[q * 32 + j4 * 4 + e] = v;
+                    }
+                }
+                if (DUMP) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
-                        const float2 dx = dxs[b * MQ_TILE_T + c0 + cc * 32 + j];
-                        float v = acc[cc * 32 + j];
-                        v = fmaf((float)sv[j] * dwv, dx.x, v);
-                        if (HAS_MIN) v = fmaf(-dmv, dx.y, v);
-                        acc[cc * 32 + j] = v;
-                        if (DUMP) {
-                            const int tok = t0 + c0 + cc * 32 + j, row = n0 + r, blk = i;
-                            if (tok < a.rows && row < w.n && blk * 32 < w.k) {
-                                const int cexp = FMT == FMT_Q8_0 ? 128 : FMT == FMT_Q4_0 ? 8 : 0;
-                                const int add = cexp ? cexp * __ldg(&a.isum[(long long)tok * (a.k_pad >> 5) + blk]) : 0;
-                                dump[((long long)tok * w.n + row) * (w.k >> 5) + blk] = sv[j] + add;
-                            }
+                        const int tok = t0 + c0 + q * 32 + j, row = n0 + r;
+                        if (tok < a.rows && row < w.n && i * 32 < w.k) {
+                            const int cexp = FMT == FMT_Q8_0 ? 128 : FMT == FMT_Q4_0 ? 8 : 0;
+                            const int add = cexp ? cexp * __ldg(&a.isum[(long long)tok * (a.k_pad >> 5) + i]) : 0;
+                            dump[((long long)tok * w.n + row) * (w.k >> 5) + i] = sv[j] - MQ_BIAS + add;
                         }
                     }
                 }
+            };
+
+            {
+                MQ_T0();
+                mq_tmem_wait_ld();   // both halves of block i are in registers
+                if (warp == 0) MQ_T1(2);
+            }
+            // every column of this buffer has been read: re-arm it with the bias (asynchronously)
+#pragma unroll
+            for (int q = 0; q < 4; q++) mq_tmem_st16_const(tcol + (unsigned)(q * 16), MQ_BIAS);
+            {
+                MQ_T0();
+                scale32(sa, 0);
+                if (warp == 0) MQ_T1(3);
+            }
+            bool next_ready = false;
+            if (i + 1 < total) {
+                const int nb = (i + 1) % MQ_DBUF;
+                MQ_T0();
+                if (!mq_bar_wait(&sh.d_full[nb], (unsigned)((i + 1) / MQ_DBUF) & 1u)) { alive = false; break; }
+                if (warp == 0) MQ_T1(0);
+                mq_tc_fence_after();
+                mq_tmem_ld32(tlane + (unsigned)(nb * MQ_TILE_T), sa);
+                next_ready = true;
+            }
+            // the bias stores have landed by now: hand the buffer back to the MMA issuer
+            {
+                MQ_T0();
+                mq_tmem_wait_st();
                 mq_tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mq_bar_arrive(&sh.d_empty[buf]);
+                if (warp == 0) MQ_T1(6);
             }
-            __syncwarp();
-            if (lane == 0) mq_bar_arrive(&sh.epi_done[s]);   // the stage's scale tables are free
+            {
+                MQ_T0();
+                scale32(sb, 1);
+                if (warp == 0) MQ_T1(7);
+            }
+            if (next_ready) mq_tmem_ld32(tlane + (unsigned)(((i + 1) % MQ_DBUF) * MQ_TILE_T + 32), sb);
+            if (b == 7) {
+                __syncwarp();
+                if (lane == 0) mq_bar_arrive(&sh.epi_done[s]);   // the stage's scale tables are free
+            }
         }
         if (!alive) {
             if (lane == 0) atomicExch(status, -7);
@@ -321,30 +480,51 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
     } else if (warp < MQ_EPI_WARPS + MQ_PROD_WARPS) {
         // ===== producers =====
         const int pw = warp - MQ_EPI_WARPS;
+        const int rg0 = (n0 >> 4) + 2 * pw;
         bool alive = true;
+        MqRegs<FMT> ra, rb;
+        if (nst > 0) {
+            mq_load<FMT>(ra, w, rg0, 0, lane);
+            mq_load<FMT>(rb, w, rg0 + 1, 0, lane);
+        }
         for (int it = 0; it < nst && alive; it++) {
             const int s = it % MQ_STAGES;
             const unsigned par = ((unsigned)(it / MQ_STAGES) & 1u) ^ 1u;   // first use of a stage passes at once
-            if (!mq_bar_wait(&sh.mma_done[s], par) || !mq_bar_wait(&sh.epi_done[s], par)) { alive = false; break; }
+            {
+                MQ_T0();
+                if (!mq_bar_wait(&sh.mma_done[s], par)) { alive = false; break; }
+                if (pw == 0) MQ_T1(4);
+            }
+            {
+                MQ_T0();
+                if (!mq_bar_wait(&sh.epi_done[s], par)) { alive = false; break; }
+                if (pw == 0) MQ_T1(5);
+            }
             if (pw == 0 && lane == 0) {
                 // activation codes (already in core-matrix order) and scales of this stage, by bulk async copy
-                mq_bar_expect_tx(&sh.b_full[s], MQ_B_BYTES + MQ_DX_BYTES);
+                mq_bar_expect_tx(&sh.b_full[s], MQ_B_BYTES + (HAS_MIN ? 2 : 1) * MQ_DX_BYTES);
                 const uint8_t *src = q_tiled + ((long long)it * (a.rows_pad >> 3) + (t0 >> 3)) * 2048;
                 mq_bulk_load(stage_b(s), src, MQ_B_BYTES, &sh.b_full[s]);
                 for (int b = 0; b < 8; b++) {
-                    mq_bulk_load(stage_dx(s) + b * MQ_TILE_T, a.ds + (long long)(it * 8 + b) * a.rows_pad + t0,
-                                 MQ_TILE_T * 8, &sh.b_full[s]);
+                    const long long off = (long long)(it * 8 + b) * a.rows_pad + t0;
+                    mq_bulk_load(stage_dx(s) + b * MQ_TILE_T, a.dx + off, MQ_TILE_T * 4, &sh.b_full[s]);
+                    if (HAS_MIN) mq_bulk_load(stage_sx(s) + b * MQ_TILE_T, a.sx + off, MQ_TILE_T * 4, &sh.b_full[s]);
                 }
             }
             uint8_t *at = stage_a(s);
-            mq_expand<FMT>(w, (n0 >> 4) + 2 * pw, 2 * pw, it, lane, at, stage_dw(s), stage_dm(s));
-            mq_expand<FMT>(w, (n0 >> 4) + 2 * pw + 1, 2 * pw + 1, it, lane, at, stage_dw(s), stage_dm(s));
+            mq_store<FMT>(ra, 2 * pw, lane, at, stage_dw(s), stage_dm(s));
+            mq_store<FMT>(rb, 2 * pw + 1, lane, at, stage_dw(s), stage_dm(s));
+            if (it + 1 < nst) {
+                // the next stage's records travel while this stage is multiplied
+                mq_load<FMT>(ra, w, rg0, it + 1, lane);
+                mq_load<FMT>(rb, w, rg0 + 1, it + 1, lane);
+            }
             mq_fence_proxy_async();   // generic-proxy stores -> visible to the tensor core's reads
             __syncwarp();
             if (lane == 0) mq_bar_arrive(&sh.a_full[s]);
         }
         if (!alive && lane == 0) atomicExch(status, -7);
-    } else {
+    } else if (warp == MQ_EPI_WARPS + MQ_PROD_WARPS) {
         // ===== MMA issuer =====
         if (lane == 0) {
             constexpr unsigned idesc = mq_idesc(FMT != FMT_Q4_K, MQ_TILE_N, MQ_TILE_T);
@@ -352,12 +532,25 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
             for (int it = 0; it < nst && alive; it++) {
                 const int s = it % MQ_STAGES;
                 const unsigned par = (unsigned)(it / MQ_STAGES) & 1u;
-                if (!mq_bar_wait(&sh.a_full[s], par) || !mq_bar_wait(&sh.b_full[s], par)) { alive = false; break; }
+                {
+                    MQ_T0();
+                    if (!mq_bar_wait(&sh.a_full[s], par)) { alive = false; break; }
+                    MQ_T1(8);
+                }
+                {
+                    MQ_T0();
+                    if (!mq_bar_wait(&sh.b_full[s], par)) { alive = false; break; }
+                    MQ_T1(9);
+                }
                 mq_tc_fence_after();
                 const unsigned a_addr = mq_smem(stage_a(s)), b_addr = mq_smem(stage_b(s));
                 for (int b = 0; b < 8; b++) {
                     const int i = it * 8 + b, buf = i % MQ_DBUF;
-                    if (!mq_bar_wait(&sh.d_empty[buf], ((unsigned)(i / MQ_DBUF) & 1u) ^ 1u)) { alive = false; break; }
+                    {
+                        MQ_T0();
+                        if (!mq_bar_wait(&sh.d_empty[buf], (unsigned)(i / MQ_DBUF) & 1u)) { alive = false; break; }
+                        MQ_T1(10);
+                    }
                     mq_tc_fence_after();
                     mq_umma_i8(tmem + (unsigned)(buf * MQ_TILE_T), mq_desc(a_addr + b * 256, 128, 2048),
                                mq_desc(b_addr + b * 256, 128, 2048), idesc);
@@ -370,6 +563,9 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
         __syncwarp();
     }
 
+#ifdef MQ_TIMING
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) atomicAdd(status + 16 + 12, (int)((clock64() - mq_kernel_t0) >> 4));
+#endif
     mq_tc_fence_before();
     __syncthreads();
     if (warp == MQ_EPI_WARPS + MQ_PROD_WARPS) {
@@ -388,12 +584,12 @@ static cudaError_t mmq_launch_one(const WeightView &w, const ActView &a, const u
     cudaGetDevice(&dev);
     auto kernel = mmq_kernel<FMT, DUMP>;
     if (dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MQ_SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mq_smem_bytes(FMT));
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
     const dim3 grid((w.n_pad + MQ_TILE_N - 1) / MQ_TILE_N, (a.rows + MQ_TILE_T - 1) / MQ_TILE_T);
-    return launch_pdl(kernel, grid, dim3(MQ_THREADS), MQ_SMEM_BYTES, stream, w, a, q_tiled, y, y_stride, dump, status);
+    return launch_pdl(kernel, grid, dim3(MQ_THREADS), mq_smem_bytes(FMT), stream, w, a, q_tiled, y, y_stride, dump, status);
 }
 
 // a.rows_pad must be a multiple of 128 and q_tiled the core-matrix copy of the activation codes (quantize.cu).

@@ -74,7 +74,10 @@ __global__ void __launch_bounds__(256) quantize_kernel(const void *__restrict__ 
     }
     if (sub == 0) {
         const int s32 = s + s_other;
-        out.ds[(long long)blk * rows_pad + row] = make_float2(d, __fmul_rn(d, (float)s32));
+        const float sxv = __fmul_rn(d, (float)s32);
+        out.ds[(long long)blk * rows_pad + row] = make_float2(d, sxv);
+        out.dx[(long long)blk * rows_pad + row] = d;
+        out.sx[(long long)blk * rows_pad + row] = sxv;
         out.isum[(long long)row * nblk_pad + blk] = s32;
     }
 }
