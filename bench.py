@@ -202,6 +202,118 @@ def prefill_leg(device, torch, N, synth, stream, steps):
     return out
 
 
+class TpStack:
+    """BASELINE config 5: the quantized MatMuls of a Llama-3-70B-shaped layer stack, tensor-parallel over the ranks:
+    q / k / v / gate / up column-split, o / down row-split with an all-reduce (sum) of the f32 partial outputs.
+    Attention, norms and the activation function are not on the path: the inputs of o and down are fresh synthetic
+    activations of the sharded shape. One step = every MatMul of every layer once, for `rows` activation rows."""
+
+    def __init__(self, device, torch, dist, N, synth, rank, world, rows, layers, arch, type_name="Q4_K"):
+        from sharplight_b200 import MatMulOp, SharedActivation, tp
+        self.torch, self.dist, self.N, self.world, self.rows = torch, dist, N, world, rows
+        self.layers, self.arch = layers, arch
+        self.specs = tp.layer_matmuls(arch)
+        self.total_weight_bytes = tp.layer_weight_bytes(arch, type_name) * layers
+        h, f = arch["hidden"], arch["ffn"]
+        self.weights, self.ops = [], []
+        shard_blocks = {}
+        for name, n, k, split, _ in self.specs:
+            nl, kl = tp.shard_shape(n, k, split, rank, world, type_name, arch["head_dim"])
+            shard_blocks[name] = (synth.weight_blocks(type_name, nl, kl, seed=500 + 7 * rank + len(shard_blocks)), nl, kl)
+        for _ in range(layers):
+            layer_ops = {}
+            for name, (blocks, nl, kl) in shard_blocks.items():
+                w = device.upload_weight(type_name, (nl, kl), blocks)
+                self.weights.append(w)
+                layer_ops[name] = MatMulOp(device, w, rows)
+            self.ops.append(layer_ops)
+        dims = {name: (nl, kl) for name, (_, nl, kl) in shard_blocks.items()}
+        self.dims = dims
+        g = torch.Generator(device="cuda").manual_seed(1234 + rank)
+        mk = lambda r, c: torch.randn((r, c), generator=g, device="cuda", dtype=torch.float32)
+        self.x = {"x_attn": mk(rows, h), "x_ffn": mk(rows, h), "x_o": mk(rows, dims["o"][1]), "x_down": mk(rows, dims["down"][1])}
+        self.y = {name: torch.empty((rows, dims[name][0]), device="cuda", dtype=torch.float32) for name in dims}
+        self.act = {key: SharedActivation(device, rows, v.shape[1]) for key, v in self.x.items()}
+        self.launches_per_step = 0
+
+    def step(self, sp):
+        N, rows = self.N, self.rows
+        launches = 0
+        for layer_ops in self.ops:
+            for key in ("x_attn", "x_o", "x_ffn", "x_down"):
+                x = self.x[key]
+                self.act[key].quantize(x.data_ptr(), N.F32, rows, x.shape[1], sp)
+                launches += 1
+                for name, _, _, split, inp in self.specs:
+                    if inp != key:
+                        continue
+                    y = self.y[name]
+                    self.act[key].matmul(layer_ops[name], y.data_ptr(), y.shape[1], sp)
+                    launches += layer_ops[name].last_kernel()[1]
+                    if split == "row" and self.world > 1:
+                        self.dist.all_reduce(y)
+        self.launches_per_step = launches
+
+    def dispose(self):
+        for layer_ops in self.ops:
+            for op in layer_ops.values():
+                op.dispose()
+        for w in self.weights:
+            w.dispose()
+        for a in self.act.values():
+            a.dispose()
+
+
+def time_graphed(torch, dist, world, stream, fn, steps, warmup, use_graph=True):
+    """fn(stream_ptr) captured into a CUDA graph and replayed; returns ms per step (max over ranks)."""
+    for _ in range(2):
+        fn(stream.cuda_stream)
+    torch.cuda.synchronize()
+    run = lambda: fn(stream.cuda_stream)
+    if use_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=torch.cuda.Stream()):
+            fn(torch.cuda.current_stream().cuda_stream)
+        run = graph.replay
+    for _ in range(warmup):
+        run()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        run()
+    e1.record(stream)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def run_tp(args, torch, dist, device, N, synth, stream, world, rank, local):
+    """The N > 1 workload (and the "tp_stack" object of the N = 1 line)."""
+    from sharplight_b200 import tp
+    arch = tp.LLAMA70B
+    layers = args.layers or arch["layers"]
+    out = {}
+    for rows in ([args.rows] if world > 1 and not args.tp_all_rows else [1, 8, 64]):
+        stack = TpStack(device, torch, dist, N, synth, rank, world, rows, layers, arch)
+        steps = max(3, min(args.steps, 20))
+        ms = time_graphed(torch, dist, world, stream, stack.step, steps, 3, use_graph=not args.no_graph)
+        out[rows] = {"ms_per_step": ms, "weight_gbs": stack.total_weight_bytes / (ms * 1e-3) / 1e9,
+                     "launches_per_step": stack.launches_per_step, "allreduces_per_step": 2 * layers if world > 1 else 0}
+        stack.dispose()
+        torch.cuda.synchronize()
+    return {"workload": f"configs[4]: Llama-3-70B-shaped stack, {layers} layers, Q4_K, tensor parallel x{world}",
+            "weight_bytes_per_step": tp.layer_weight_bytes(arch) * layers, "by_rows": out}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -221,6 +333,33 @@ def run_ours(args):
     device = provider.open_device([d for d in provider.get_devices() if d.index == local][0])
     rows, n, k = args.rows, N_ROWS_W, K_COLS
     wbytes = synth.weight_bytes(TYPE, n, k)
+
+    if world > 1:
+        stream = torch.cuda.Stream()
+        torch.cuda.set_stream(stream)
+        sampler = ClockSampler(local)
+        sampler.start()
+        tpr = run_tp(args, torch, dist, device, N, synth, stream, world, rank, local)
+        clocks = sampler.stop()
+        if rank == 0:
+            main = tpr["by_rows"][rows]
+            line = {"metric": "quant mat-vec HBM GB/s", "value": main["weight_gbs"], "unit": "GB/s", "n_gpus": world,
+                    "steps": max(3, min(args.steps, 20)), "warmup": 3, "ms_per_step": main["ms_per_step"],
+                    "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                    "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
+                    "config": {"workload": tpr["workload"] + f", decode M={rows}: column-split q/k/v/gate/up, row-split "
+                                           "o/down + NCCL all-reduce of f32 partials",
+                               "l2": f"inputs larger than L2: {tpr['weight_bytes_per_step'] / world / 1e9:.1f} GB of weights per GPU per step",
+                               "launch": "host launches" if args.no_graph else "CUDA graph replay of the step"},
+                    "gpu_launches": main["launches_per_step"] * max(3, min(args.steps, 20)),
+                    "tp_stack": tpr, "clocks": clocks,
+                    "e2e": {"value": main["weight_gbs"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                            "note": "activations of this workload are device-resident by construction (they come from the "
+                                    "preceding layer); the host-buffer figure is reported by the N=1 run"}}
+            print(json.dumps(line), flush=True)
+        device.dispose()
+        dist.destroy_process_group()
+        return
 
     base_blocks = synth.weight_blocks(TYPE, n, k, seed=100 + rank)
     weights, ops = [], []
@@ -313,6 +452,9 @@ def run_ours(args):
     torch.cuda.synchronize()
     same = bool(torch.equal(y_dev.cpu(), y_host)) if not args.no_e2e else None
 
+    tp_stack = None
+    if world == 1 and args.tp_stack:
+        tp_stack = run_tp(args, torch, dist, device, N, synth, stream, 1, 0, local)
     prefill = None
     if world == 1 and not args.no_prefill:
         prefill = prefill_leg(device, torch, N, synth, stream, max(5, args.steps // 10))
@@ -347,6 +489,8 @@ def run_ours(args):
             line["cpu_baseline"] = base
         if prefill is not None:
             line["prefill"] = prefill
+        if tp_stack is not None:
+            line["tp_stack"] = tp_stack
         print(json.dumps(line), flush=True)
     for op in ops:
         op.dispose()
@@ -369,6 +513,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--copies", type=int, default=COPIES, help="weight matrices per step (profiling runs use fewer)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--layers", type=int, default=0, help="layers of the tensor-parallel stack (default: the architecture's 80)")
+    ap.add_argument("--tp-stack", action="store_true", help="N=1: also time the 70B-shaped stack at tensor-parallel degree 1")
+    ap.add_argument("--tp-all-rows", action="store_true", help="N>1: time decode batches 1, 8 and 64 instead of --rows only")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM leg")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of a CUDA graph")
     args = ap.parse_args()
