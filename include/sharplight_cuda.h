@@ -191,6 +191,20 @@ SLC_API slc_result slc_activation_quantize(slc_activation *act, const void *x_de
 SLC_API slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act, float *y_device, int64_t y_stride,
                                             void *stream);
 
+/* ---- no device allocation: this entry point has no counterpart in the reference. It serves hosts that may not call
+        cudaMalloc while they run (a serving loop with a fixed memory budget, a framework that owns the allocator, a
+        phase where an allocation would stall the device). Same result as slc_matmul_run with device pointers, for
+        1..4 rows and K <= 32768, but the quantized activations go to a fixed SLC_STATIC_SCRATCH_BYTES array inside the
+        library's device image (held by every GPU that loads the library until exit) instead of allocated planes.
+        Limits are rejected with SLC_ERR_UNSUPPORTED (text: slc_static_last_error). All calls on a device share the
+        array: calls that overlap on the GPU race, serialise them. The first call on a device resolves the array's
+        address and should happen before any stream capture begins. x and y are device memory; asynchronous on the
+        stream (NULL = the device's own). */
+#define SLC_STATIC_SCRATCH_BYTES 491520
+SLC_API slc_result slc_matmul_run_static(slc_weight *weight, const void *x_device, int32_t x_dtype, int64_t rows,
+                                         int64_t x_stride, float *y_device, int64_t y_stride, void *stream);
+SLC_API const char *slc_static_last_error(void);
+
 /* ---- parity exports (host buffers; synchronous): the quantities the bit-exactness checks compare */
 /* q[rows][k] int8, d[rows][k/32] f32 block scales, gs[rows][k/16] f32 group sums d * sum16(q), as IntDot.Quantize
    lays them out logically (src/Sharplight.Cpu/Q8Row.cs:9-20). x is host memory. */

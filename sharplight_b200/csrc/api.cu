@@ -13,51 +13,7 @@
 
 using namespace slc;
 
-// ---- handles ---------------------------------------------------------------------------------------------------------
-
-struct slc_device
-{
-    int index = 0;
-    cudaStream_t stream = nullptr;
-    int *status_dev = nullptr;   // device-side status word (bounded waits report here)
-    cudaDeviceProp prop{};
-};
-
-struct slc_weight
-{
-    slc_device *dev = nullptr;
-    int fmt = 0;
-    long long n = 0, k = 0;
-    uint8_t *base = nullptr;
-    size_t bytes = 0;
-    WeightView view{};
-};
-
-struct slc_activation
-{
-    slc_device *dev = nullptr;
-    long long max_rows = 0, k = 0;
-    int k_pad = 0, cap_rows = 0;  // cap_rows: padded row capacity of the planes
-    uint8_t *base = nullptr;
-    size_t bytes = 0;
-    ActPlanes planes{};
-    uint8_t *q_tiled = nullptr;   // present when the capacity allows GEMM-sized row counts
-    int rows = 0, rows_pad = 0;   // what the last quantize call wrote
-};
-
-struct slc_matmul
-{
-    slc_device *dev = nullptr;
-    slc_weight *w = nullptr;
-    long long max_rows = 0;
-    uint32_t flags = 0;
-    int forced_kernel = SLC_KERNEL_AUTO;
-    int last_kernel = 0, last_launches = 0;
-    int last_launches_total = 0;    // including the activation quantization, when it was a launch of its own
-    slc_activation *act = nullptr;  // the op's own quantized copy (slc_matmul_run)
-    void *x_stage = nullptr;        // device staging for host activations (max_rows x k, 4 bytes each)
-    float *y_stage = nullptr;       // device staging for host outputs (max_rows x n)
-};
+#include "handles.cuh"
 
 // ---- errors ----------------------------------------------------------------------------------------------------------
 

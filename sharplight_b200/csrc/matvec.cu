@@ -264,6 +264,173 @@ __device__ __forceinline__ void compute_tile(const FTile<FMT> &tl, const SmemAct
     }
 }
 
+// ---- whole-block lane mapping (Q4_K, Q8_0, Q4_0) -----------------------------------------------------------------
+// The record sits in shared memory, so a lane is free to read other lanes' code units: lane (g, t) takes, for rows g
+// and g + 8, the whole 32-value blocks of quarter t of the super-tile (four 128-bit shared loads, visited in an order
+// rotated by t so the four lanes of a group hit different banks). A lane then owns complete block dots: the per-block
+// scaling is done once per (row, block) instead of once per quarter block in each of four lanes.
+
+// unsigned bytes x signed bytes: high nibbles are used in place (value * 16), the sum is shifted down afterwards
+__device__ __forceinline__ int dp4a_us(unsigned a, int b, int c)
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+template <bool DUMP>
+__device__ __forceinline__ void export_block(const DumpCtx &dc, const SmemAct &a, int blk, int m, int r, int dot, int c_export)
+{
+    if (!DUMP) return;
+    const int row = dc.rg * 16 + dc.g + 8 * r;
+    if (row < dc.n && blk * 32 < dc.k) {
+        dc.out[((long long)m * dc.n + row) * (dc.k >> 5) + blk] = dot + c_export * a.isum[m * a.nblk_pad + blk];
+    }
+}
+
+template <int FMT, int M, bool DUMP>
+__device__ __forceinline__ void compute_slot(const uint8_t *slot, const SmemAct &a, int st, int lane, float acc[2][M],
+                                             const DumpCtx &dc)
+{
+    const int g = lane >> 2, t = lane & 3;
+    const int8_t *xq = a.q + st * 256;
+    const float2 *xs = a.ds + st * 8;
+    const uint4 *sp = reinterpret_cast<const uint4 *>(slot + code_bytes(FMT));
+    const uint4 h0 = sp[g], h1 = sp[g + 8];
+
+    if constexpr (FMT == FMT_Q4_K) {
+        // chunk t = sub-blocks 2t (low nibbles) and 2t + 1 (high nibbles)
+        const uint4 *tile = reinterpret_cast<const uint4 *>(slot + t * 512) + g * 4;
+        int s[2][2][M];
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+#pragma unroll
+            for (int b = 0; b < 2; b++)
+#pragma unroll
+                for (int m = 0; m < M; m++) s[r][b][m] = 0;
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) {
+            const int j = (jj + t) & 3;
+            const uint4 q = tile[j];
+            const int l0 = (int)(q.x & 0x0F0F0F0Fu), l1 = (int)(q.y & 0x0F0F0F0Fu);
+            const int l2 = (int)(q.z & 0x0F0F0F0Fu), l3 = (int)(q.w & 0x0F0F0F0Fu);
+            const unsigned u0 = q.x & 0xF0F0F0F0u, u1 = q.y & 0xF0F0F0F0u, u2 = q.z & 0xF0F0F0F0u, u3 = q.w & 0xF0F0F0F0u;
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                const int8_t *xp = xq + m * a.k_pad + 64 * t + 8 * j;
+                const int2 xl = *reinterpret_cast<const int2 *>(xp), xh = *reinterpret_cast<const int2 *>(xp + 32);
+                s[0][0][m] = __dp4a(l0, xl.x, __dp4a(l1, xl.y, s[0][0][m]));
+                s[1][0][m] = __dp4a(l2, xl.x, __dp4a(l3, xl.y, s[1][0][m]));
+                s[0][1][m] = dp4a_us(u0, xh.x, dp4a_us(u1, xh.y, s[0][1][m]));
+                s[1][1][m] = dp4a_us(u2, xh.x, dp4a_us(u3, xh.y, s[1][1][m]));
+            }
+        }
+        const int sh = 16 * (t & 1);
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const uint4 h = r ? h1 : h0;
+            const float d = h2f(h.x & 0xffffu), dmin = h2f(h.x >> 16);
+            // 6-bit scales / mins of sub-blocks 2t, 2t + 1 (src/Sharplight.Cpu/Quant.cs:504-516 of the Sharplight tree)
+            const unsigned scw = t < 2 ? (h.y & 0x3F3F3F3Fu) : ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u));
+            const unsigned mnw = t < 2 ? (h.z & 0x3F3F3F3Fu) : (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u));
+            const int sc0 = (int)((scw >> sh) & 0xffu), sc1 = (int)((scw >> (sh + 8)) & 0xffu);
+            const float mn0 = (float)((mnw >> sh) & 0xffu), mn1 = (float)((mnw >> (sh + 8)) & 0xffu);
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                const float2 ds0 = xs[m * a.nblk_pad + 2 * t], ds1 = xs[m * a.nblk_pad + 2 * t + 1];
+                const int d0 = s[r][0][m], d1 = s[r][1][m] >> 4;     // the high-nibble sum carries a factor 16
+                // integer sub-block scale first: |dot * sc| <= 60960 * 63 < 2^22, exact in f32
+                const float part = fmaf((float)(d0 * sc0), ds0.x, (float)(d1 * sc1) * ds1.x);
+                const float mpart = fmaf(mn0, ds0.y, mn1 * ds1.y);
+                acc[r][m] += fmaf(d, part, -dmin * mpart);
+                export_block<DUMP>(dc, a, st * 8 + 2 * t, m, r, d0, 0);
+                export_block<DUMP>(dc, a, st * 8 + 2 * t + 1, m, r, d1, 0);
+            }
+        }
+    } else if constexpr (FMT == FMT_Q8_0) {
+        // blocks 2t and 2t + 1, one 512-byte tile each
+#pragma unroll
+        for (int bl = 0; bl < 2; bl++) {
+            const int blk = 2 * t + bl;
+            const uint4 *tile = reinterpret_cast<const uint4 *>(slot + blk * 512) + g * 4;
+            int s[2][M];
+#pragma unroll
+            for (int r = 0; r < 2; r++)
+#pragma unroll
+                for (int m = 0; m < M; m++) s[r][m] = 0;
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+                const int j = (jj + t) & 3;
+                const uint4 q = tile[j];
+#pragma unroll
+                for (int m = 0; m < M; m++) {
+                    const int2 x = *reinterpret_cast<const int2 *>(xq + m * a.k_pad + blk * 32 + 8 * j);
+                    s[0][m] = __dp4a((int)q.x, x.x, __dp4a((int)q.y, x.y, s[0][m]));
+                    s[1][m] = __dp4a((int)q.z, x.x, __dp4a((int)q.w, x.y, s[1][m]));
+                }
+            }
+            const unsigned w0 = t == 0 ? h0.x : t == 1 ? h0.y : t == 2 ? h0.z : h0.w;
+            const unsigned w1 = t == 0 ? h1.x : t == 1 ? h1.y : t == 2 ? h1.z : h1.w;
+            const float dw[2] = { h2f((w0 >> (16 * bl)) & 0xffffu), h2f((w1 >> (16 * bl)) & 0xffffu) };
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                const float dx = xs[m * a.nblk_pad + blk].x;
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    acc[r][m] = fmaf(dw[r] * dx, (float)s[r][m], acc[r][m]);
+                    export_block<DUMP>(dc, a, st * 8 + blk, m, r, s[r][m], 128);
+                }
+            }
+        }
+    } else {  // Q4_0: tile t holds blocks 2t and 2t + 1
+        const uint4 *tile = reinterpret_cast<const uint4 *>(slot + t * 512) + g * 4;
+        int lo[2][2][M], hi[2][2][M];   // [row][block][m]
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+#pragma unroll
+            for (int b = 0; b < 2; b++)
+#pragma unroll
+                for (int m = 0; m < M; m++) { lo[r][b][m] = 0; hi[r][b][m] = 0; }
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) {
+            const int j = (jj + t) & 3;
+            const uint4 q = tile[j];
+            const unsigned wv[4] = { q.x, q.y, q.z, q.w };   // row g blk 0, row g+8 blk 0, row g blk 1, row g+8 blk 1
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+#pragma unroll
+                for (int b = 0; b < 2; b++) {
+                    const int8_t *xp = xq + m * a.k_pad + (2 * t + b) * 32 + 4 * j;
+                    const int xl = *reinterpret_cast<const int *>(xp), xh = *reinterpret_cast<const int *>(xp + 16);
+#pragma unroll
+                    for (int r = 0; r < 2; r++) {
+                        const unsigned wq = wv[2 * b + r];
+                        lo[r][b][m] = __dp4a((int)(wq & 0x0F0F0F0Fu), xl, lo[r][b][m]);
+                        hi[r][b][m] = dp4a_us(wq & 0xF0F0F0F0u, xh, hi[r][b][m]);
+                    }
+                }
+            }
+        }
+        const unsigned w0 = t == 0 ? h0.x : t == 1 ? h0.y : t == 2 ? h0.z : h0.w;
+        const unsigned w1 = t == 0 ? h1.x : t == 1 ? h1.y : t == 2 ? h1.z : h1.w;
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            const float dw[2] = { h2f((w0 >> (16 * b)) & 0xffffu), h2f((w1 >> (16 * b)) & 0xffffu) };
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                const float2 ds = xs[m * a.nblk_pad + 2 * t + b];
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    const int dot = lo[r][b][m] + (hi[r][b][m] >> 4);
+                    // codes are value + 8: d_w * (d_x * dot - 8 * d_x * sum q)
+                    acc[r][m] = fmaf(dw[r], fmaf(ds.x, (float)dot, -8.0f * ds.y), acc[r][m]);
+                    export_block<DUMP>(dc, a, st * 8 + 2 * t + b, m, r, dot, 0);
+                }
+            }
+        }
+    }
+}
+
 template <int FMT, int M, bool DUMP>
 __global__ void __launch_bounds__(FV_MAX_WARPS * 32)
 matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__ y, long long y_stride, int *dump,
@@ -331,13 +498,21 @@ matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__
             alive = false;
         }
         if (alive) {
-            FTile<FMT> tl;
-            load_tile<FMT>(tl, slot, lane);
-            __syncwarp();   // every lane has its copy of the record: the slot may be refilled
-            if (lane == 0 && i + FV_STAGES < count) {
-                bulk_load(ring + s * REC, w.record(rg, warp + (i + FV_STAGES) * warps), REC, &bars[warp][s]);
+            if constexpr (FMT == FMT_Q6_K) {
+                FTile<FMT> tl;
+                load_tile<FMT>(tl, slot, lane);
+                __syncwarp();   // every lane has its copy of the record: the slot may be refilled
+                if (lane == 0 && i + FV_STAGES < count) {
+                    bulk_load(ring + s * REC, w.record(rg, warp + (i + FV_STAGES) * warps), REC, &bars[warp][s]);
+                }
+                compute_tile<FMT, M, DUMP>(tl, act, warp + i * warps, t, acc, dc);
+            } else {
+                compute_slot<FMT, M, DUMP>(slot, act, warp + i * warps, lane, acc, dc);
+                __syncwarp();   // every lane is done reading the slot: it may be refilled
+                if (lane == 0 && i + FV_STAGES < count) {
+                    bulk_load(ring + s * REC, w.record(rg, warp + (i + FV_STAGES) * warps), REC, &bars[warp][s]);
+                }
             }
-            compute_tile<FMT, M, DUMP>(tl, act, warp + i * warps, t, acc, dc);
         }
     }
 

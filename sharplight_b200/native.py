@@ -76,6 +76,8 @@ SIGNATURES = {
     "slc_activation_destroy": (None, [_vp]),
     "slc_activation_quantize": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp]),
     "slc_matmul_run_quantized": (_i32, [_vp, _vp, _vp, _i64, _vp]),
+    "slc_matmul_run_static": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp, _i64, _vp]),
+    "slc_static_last_error": (C.c_char_p, []),
     "slc_debug_quantize": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp, _vp, _vp]),
     "slc_debug_block_dots": (_i32, [_vp, _vp, _i32, _i64, _vp]),
 }
