@@ -142,6 +142,13 @@ SLC_API slc_result slc_buffer_alloc(slc_device *device, int64_t bytes, void **ou
 SLC_API void slc_buffer_free(slc_device *device, void *device_ptr);
 SLC_API slc_result slc_buffer_upload(slc_device *device, void *device_ptr, const void *host, int64_t bytes);
 SLC_API slc_result slc_buffer_download(slc_device *device, void *host, const void *device_ptr, int64_t bytes);
+/* Page-locked host staging and asynchronous copies on a stream (NULL = the device's own): what lets a segment's
+   Execute return before its outputs have arrived ("Implementations may run asynchronously until an output is read",
+   src/Sharplight.Core/Runtime/ICompiledSegment.cs:11-12). direction: 0 host->device, 1 device->host, 2 device->device. */
+SLC_API slc_result slc_host_alloc(int64_t bytes, void **out_host_ptr);
+SLC_API void slc_host_free(void *host_ptr);
+SLC_API slc_result slc_buffer_copy_async(slc_device *device, void *dst, const void *src, int64_t bytes, int32_t direction,
+                                         void *stream);
 
 /* ---- weights: WeightInfo.Source -> device (src/Sharplight.Core/Models/IWeightSource.cs:4-40).
         blocks: raw ggml blocks of an [n, k] weight, row-major, bytes == n * k / block_size * block_bytes.
@@ -187,7 +194,8 @@ SLC_API void slc_activation_destroy(slc_activation *act);
    from zero (src/Sharplight.Cpu/IntDot.cs:92-126). Asynchronous on the stream. */
 SLC_API slc_result slc_activation_quantize(slc_activation *act, const void *x_device, int32_t x_dtype, int64_t rows,
                                            int64_t x_stride, void *stream);
-/* y (device, f32) = act . W^T with the rows last quantized into act. Asynchronous on the stream. */
+/* y (device, f32) = act . W^T with the rows last quantized into act. Asynchronous on the stream. Consecutive calls that
+   read the same quantized rows may execute side by side on the device: their outputs must not overlap in memory. */
 SLC_API slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act, float *y_device, int64_t y_stride,
                                             void *stream);
 

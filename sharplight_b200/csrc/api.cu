@@ -236,6 +236,31 @@ slc_result slc_buffer_download(slc_device *d, void *host, const void *src, int64
     return SLC_OK;
 }
 
+slc_result slc_host_alloc(int64_t bytes, void **out)
+{
+    if (!out || bytes < 0) return fail(SLC_ERR_INVALID_ARGUMENT, "bad host allocation request");
+    *out = nullptr;
+    SLC_CUDA(cudaHostAlloc(out, bytes > 0 ? (size_t)bytes : 16, cudaHostAllocDefault));
+    return SLC_OK;
+}
+
+void slc_host_free(void *p)
+{
+    if (p) cudaFreeHost(p);
+}
+
+slc_result slc_buffer_copy_async(slc_device *d, void *dst, const void *src, int64_t bytes, int32_t direction, void *stream)
+{
+    if (!d || bytes < 0 || direction < 0 || direction > 2) return fail(SLC_ERR_INVALID_ARGUMENT, "bad copy request");
+    if (bytes == 0) return SLC_OK;
+    if (!dst || !src) return fail(SLC_ERR_INVALID_ARGUMENT, "null copy pointer");
+    SLC_CUDA(cudaSetDevice(d->index));
+    const cudaMemcpyKind kind = direction == 0 ? cudaMemcpyHostToDevice : direction == 1 ? cudaMemcpyDeviceToHost
+                                                                                         : cudaMemcpyDeviceToDevice;
+    SLC_CUDA(cudaMemcpyAsync(dst, src, (size_t)bytes, kind, stream ? (cudaStream_t)stream : d->stream));
+    return SLC_OK;
+}
+
 // ---- weights ---------------------------------------------------------------------------------------------------------
 
 static slc_result check_weight_args(slc_device *d, int32_t fmt, int64_t n, int64_t k, const void *blocks, int64_t bytes)
@@ -407,6 +432,8 @@ slc_result slc_activation_quantize(slc_activation *a, const void *x, int32_t x_d
     SLC_CUDA(cudaSetDevice(a->dev->index));
     cudaStream_t s = stream ? (cudaStream_t)stream : a->dev->stream;
     a->planes.q_tiled = rows > 64 ? a->q_tiled : nullptr;
+    a->reads_since_quantize = 0;
+    a->quantize_stream = stream ? (cudaStream_t)stream : a->dev->stream;
     SLC_CUDA(launch_quantize(x, x_dtype, a->rows, a->rows_pad, (int)a->k, a->k_pad, x_stride, a->planes, s));
     return SLC_OK;
 }
@@ -489,6 +516,9 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
     op->last_kernel = kernel;
     op->last_launches = 0;
     op->last_launches_total = 0;
+    // A launch may run beside its predecessor when an earlier launch on this stream has already read these
+    // activations: they were complete before that launch started, and MatMul outputs do not alias each other.
+    auto early = [&]() { return act->reads_since_quantize > 0 ? 1 : 0; };
     if (kernel == SLC_KERNEL_MMVQ) {
         // chunks of up to 4 rows; every row of a chunk is computed exactly as a single row is, so the row-invariant
         // guarantee holds for any chunking
@@ -497,18 +527,21 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
         if (!matvec_fits(chunk, wv.k_pad)) return fail(SLC_ERR_UNSUPPORTED, "K is too large for the mat-vec kernel's shared memory");
         for (int r0 = 0; r0 < rows; r0 += chunk) {
             const int m = rows - r0 < chunk ? rows - r0 : chunk;
-            SLC_CUDA(launch_matvec(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, s));
+            SLC_CUDA(launch_matvec(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, early(), s));
+            act->reads_since_quantize++;
             op->last_launches++;
         }
     } else if (kernel == SLC_KERNEL_SKINNY) {
         for (int r0 = 0; r0 < rows; r0 += 64) {
             const int m = rows - r0 < 64 ? rows - r0 : 64;
-            SLC_CUDA(launch_skinny(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, s));
+            SLC_CUDA(launch_skinny(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, early(), s));
+            act->reads_since_quantize++;
             op->last_launches++;
         }
     } else {
         if (!act->planes.q_tiled) return fail(SLC_ERR_INVALID_STATE, "the tensor-core GEMM needs more than 64 rows");
-        SLC_CUDA(launch_mmq(wv, av, act->planes.q_tiled, y, y_stride, dump, op->dev->status_dev, s));
+        SLC_CUDA(launch_mmq(wv, av, act->planes.q_tiled, y, y_stride, dump, op->dev->status_dev, early(), s));
+        act->reads_since_quantize++;
         op->last_launches++;
     }
     return SLC_OK;

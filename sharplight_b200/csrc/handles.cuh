@@ -31,6 +31,8 @@ struct slc_activation
     slc::ActPlanes planes{};
     uint8_t *q_tiled = nullptr;   // present when the capacity allows GEMM-sized row counts
     int rows = 0, rows_pad = 0;   // what the last quantize call wrote
+    int reads_since_quantize = 0;       // MatMul launches that have read the current contents ...
+    cudaStream_t quantize_stream = nullptr;   // ... and the stream they were quantized on
 };
 
 struct slc_matmul

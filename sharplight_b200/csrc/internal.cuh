@@ -8,9 +8,25 @@ namespace slc {
 // Programmatic dependent launch. Every kernel of this library is launched with the attribute below and calls
 // pdl_wait() before its first read of data an earlier kernel may have produced and before its first global write, so
 // consecutive kernels on a stream overlap only where that is safe: a kernel's independent prologue (weight loads)
-// runs while its predecessor drains.
+// runs while its predecessor drains. `early` (launchers below): the launch reads quantized activations that an earlier
+// launch on the same stream has already read, and writes nothing the preceding kernel touches.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// The two ways a kernel joins the chain. Ordinary: wait for the preceding kernel (which may have produced this one's
+// input), and only then let the next kernel start -- so whatever starts after a kernel's trigger knows that everything
+// before that kernel is complete. Early: the input was complete before the preceding kernel even started (the preceding
+// kernel reads the same quantized activations), so run beside it; the wait moves to the exit, which keeps completion in
+// stream order for whoever waits on this kernel.
+__device__ __forceinline__ void pdl_enter(int early)
+{
+    if (!early) pdl_wait();
+    pdl_launch_dependents();
+}
+__device__ __forceinline__ void pdl_exit(int early)
+{
+    if (early) pdl_wait();
+}
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -50,16 +66,16 @@ cudaError_t launch_quantize(const void *x, int x_dtype, int rows, int rows_pad, 
 // (optional) receives unsigned-code block dots [rows][n][k/32]; status: device word raised when a bounded wait runs out.
 bool matvec_fits(int rows, int k_pad);
 cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                          int *dump, int *status, cudaStream_t stream);
+                          int *dump, int *status, int early, cudaStream_t stream);
 
 // skinny.cu: int8 mma tiles, 1..64 activation rows per launch.
 cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                          int *dump, cudaStream_t stream);
+                          int *dump, int early, cudaStream_t stream);
 
 // mmq.cu: tcgen05 / TMEM int8 GEMM for many rows (Q4_0, Q8_0, Q4_K). status: device word set to a negative code when
 // a bounded wait runs out.
 bool mmq_supports(int fmt);
 cudaError_t launch_mmq(const WeightView &w, const ActView &a, const uint8_t *q_tiled, float *y, long long y_stride,
-                       int *dump, int *status, cudaStream_t stream);
+                       int *dump, int *status, int early, cudaStream_t stream);
 
 }  // namespace slc

@@ -434,7 +434,7 @@ __device__ __forceinline__ void compute_slot(const uint8_t *slot, const SmemAct 
 template <int FMT, int M, bool DUMP>
 __global__ void __launch_bounds__(FV_MAX_WARPS * 32)
 matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__ y, long long y_stride, int *dump,
-              int *status)
+              int *status, int early)
 {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) uint64_t bars[FV_MAX_WARPS][FV_STAGES];
@@ -462,8 +462,9 @@ matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__
         }
     }
 
-    pdl_launch_dependents();
-    pdl_wait();   // the activations (and the previous use of y) are complete from here on
+    // early: the activations were complete before the preceding kernel began (it reads the same ones), so this kernel
+    // may run beside it; otherwise wait for the preceding kernel, which produced them
+    pdl_enter(early);
 
     // quantized activations -> shared memory
     {
@@ -534,6 +535,7 @@ matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__
         const int row = blockIdx.x * 16 + rr;
         if (row < w.n) y[(long long)(row0 + m) * y_stride + row] = v;
     }
+    pdl_exit(early);
 }
 
 // Warps per CTA: four split K by default; eight when there are few row groups and K is long (the down projections),
@@ -557,7 +559,7 @@ bool matvec_fits(int rows, int k_pad)
 
 template <int FMT, int M, bool DUMP>
 static cudaError_t launch_one(const WeightView &w, const ActView &a, int row0, float *y, long long y_stride, int *dump,
-                              int *status, cudaStream_t stream)
+                              int *status, int early, cudaStream_t stream)
 {
     static bool configured[64] = {};
     int dev = 0;
@@ -570,17 +572,17 @@ static cudaError_t launch_one(const WeightView &w, const ActView &a, int row0, f
     }
     const int warps = matvec_warps(w);
     return launch_pdl(kernel, dim3(w.n_pad / 16), dim3(warps * 32), matvec_smem(FMT, warps, M, w.k_pad), stream, w, a,
-                      row0, y, y_stride, dump, status);
+                      row0, y, y_stride, dump, status, early);
 }
 
 template <int FMT>
 static cudaError_t launch_fmt(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                              int *dump, int *status, cudaStream_t stream)
+                              int *dump, int *status, int early, cudaStream_t stream)
 {
 #define SLC_ROWS(MM)                                                                        \
     case MM:                                                                                \
-        return dump ? launch_one<FMT, MM, true>(w, a, row0, y, y_stride, dump, status, stream)      \
-                    : launch_one<FMT, MM, false>(w, a, row0, y, y_stride, nullptr, status, stream);
+        return dump ? launch_one<FMT, MM, true>(w, a, row0, y, y_stride, dump, status, early, stream)      \
+                    : launch_one<FMT, MM, false>(w, a, row0, y, y_stride, nullptr, status, early, stream);
     switch (rows) {
         SLC_ROWS(1) SLC_ROWS(2) SLC_ROWS(3) SLC_ROWS(4)
     default: return cudaErrorInvalidValue;
@@ -590,14 +592,14 @@ static cudaError_t launch_fmt(const WeightView &w, const ActView &a, int row0, i
 
 // rows 1..4 starting at activation row row0; dump (optional) receives [rows][n][k/32] block dots.
 cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                          int *dump, int *status, cudaStream_t stream)
+                          int *dump, int *status, int early, cudaStream_t stream)
 {
     if (w.n_pad == 0 || rows == 0) return cudaSuccess;
     switch (w.fmt) {
-    case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(w, a, row0, rows, y, y_stride, dump, status, stream);
-    case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(w, a, row0, rows, y, y_stride, dump, status, stream);
-    case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(w, a, row0, rows, y, y_stride, dump, status, stream);
-    case FMT_Q6_K: return launch_fmt<FMT_Q6_K>(w, a, row0, rows, y, y_stride, dump, status, stream);
+    case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(w, a, row0, rows, y, y_stride, dump, status, early, stream);
+    case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(w, a, row0, rows, y, y_stride, dump, status, early, stream);
+    case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(w, a, row0, rows, y, y_stride, dump, status, early, stream);
+    case FMT_Q6_K: return launch_fmt<FMT_Q6_K>(w, a, row0, rows, y, y_stride, dump, status, early, stream);
     default: return cudaErrorInvalidValue;
     }
 }

@@ -271,7 +271,7 @@ __device__ __forceinline__ void mq_store(const MqRegs<FMT> &rr, int rgl, int lan
 template <int FMT, bool DUMP>
 __global__ void __launch_bounds__(MQ_THREADS, 1)
 mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_tiled, float *__restrict__ y,
-           long long y_stride, int *dump, int *status)
+           long long y_stride, int *dump, int *status, int early)
 {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ MqSmem sh;
@@ -315,8 +315,7 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
     mq_tc_fence_after();
     const unsigned tmem = sh.tmem_base;
 
-    pdl_launch_dependents();
-    pdl_wait();   // quantized activations come from the kernel before this one; y may still be read by it
+    pdl_enter(early);   // waits for the kernel that produced the activations unless they were complete before it
 #ifdef MQ_TIMING
     const long long mq_kernel_t0 = clock64();
 #endif
@@ -566,6 +565,7 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
 #ifdef MQ_TIMING
     if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) atomicAdd(status + 16 + 12, (int)((clock64() - mq_kernel_t0) >> 4));
 #endif
+    pdl_exit(early);
     mq_tc_fence_before();
     __syncthreads();
     if (warp == MQ_EPI_WARPS + MQ_PROD_WARPS) {
@@ -577,7 +577,7 @@ bool mmq_supports(int fmt) { return fmt == FMT_Q4_0 || fmt == FMT_Q8_0 || fmt ==
 
 template <int FMT, bool DUMP>
 static cudaError_t mmq_launch_one(const WeightView &w, const ActView &a, const uint8_t *q_tiled, float *y,
-                                  long long y_stride, int *dump, int *status, cudaStream_t stream)
+                                  long long y_stride, int *dump, int *status, int early, cudaStream_t stream)
 {
     static bool configured[64] = {};
     int dev = 0;
@@ -589,19 +589,19 @@ static cudaError_t mmq_launch_one(const WeightView &w, const ActView &a, const u
         configured[dev] = true;
     }
     const dim3 grid((w.n_pad + MQ_TILE_N - 1) / MQ_TILE_N, (a.rows + MQ_TILE_T - 1) / MQ_TILE_T);
-    return launch_pdl(kernel, grid, dim3(MQ_THREADS), mq_smem_bytes(FMT), stream, w, a, q_tiled, y, y_stride, dump, status);
+    return launch_pdl(kernel, grid, dim3(MQ_THREADS), mq_smem_bytes(FMT), stream, w, a, q_tiled, y, y_stride, dump, status, early);
 }
 
 // a.rows_pad must be a multiple of 128 and q_tiled the core-matrix copy of the activation codes (quantize.cu).
 cudaError_t launch_mmq(const WeightView &w, const ActView &a, const uint8_t *q_tiled, float *y, long long y_stride,
-                       int *dump, int *status, cudaStream_t stream)
+                       int *dump, int *status, int early, cudaStream_t stream)
 {
     if (w.n_pad == 0 || a.rows == 0) return cudaSuccess;
     if ((a.rows_pad % MQ_TILE_T) != 0 || !q_tiled) return cudaErrorInvalidValue;
 #define SLC_FMT(F)                                                                                 \
     case F:                                                                                        \
-        return dump ? mmq_launch_one<F, true>(w, a, q_tiled, y, y_stride, dump, status, stream)    \
-                    : mmq_launch_one<F, false>(w, a, q_tiled, y, y_stride, nullptr, status, stream);
+        return dump ? mmq_launch_one<F, true>(w, a, q_tiled, y, y_stride, dump, status, early, stream)    \
+                    : mmq_launch_one<F, false>(w, a, q_tiled, y, y_stride, nullptr, status, early, stream);
     switch (w.fmt) {
         SLC_FMT(FMT_Q4_0) SLC_FMT(FMT_Q8_0) SLC_FMT(FMT_Q4_K)
     default: return cudaErrorInvalidValue;

@@ -246,7 +246,7 @@ __device__ __forceinline__ void sk_q6_k(SkCtx<NT, DUMP> &c, int st, int lane)
 template <int FMT, int NT, bool DUMP>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__restrict__ y, long long y_stride,
-              int *dump)
+              int *dump, int early)
 {
     __shared__ float red[SK_WARPS][16][NT * 8 + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -256,8 +256,7 @@ skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__
 #pragma unroll
         for (int e = 0; e < 4; e++) c.acc[nt][e] = 0.0f;
 
-    pdl_launch_dependents();
-    pdl_wait();   // quantized activations come from the kernel before this one
+    pdl_enter(early);   // waits for the kernel that produced the activations unless they were complete before it
 
     const int nst = w.k_pad >> 8;
     for (int st = warp; st < nst; st += SK_WARPS) {
@@ -280,29 +279,30 @@ skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__
         const int row = blockIdx.x * 16 + rr;
         if (row < w.n && m < rows) y[(long long)(row0 + m) * y_stride + row] = v;
     }
+    pdl_exit(early);
 }
 
 template <int FMT, bool DUMP>
 static cudaError_t launch_nt(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                             int *dump, cudaStream_t stream)
+                             int *dump, int early, cudaStream_t stream)
 {
     const dim3 grid(w.n_pad / 16), block(SK_WARPS * 32);
-    if (rows <= 8) return launch_pdl(skinny_kernel<FMT, 1, DUMP>, grid, block, 0, stream, w, a, row0, rows, y, y_stride, dump);
-    if (rows <= 16) return launch_pdl(skinny_kernel<FMT, 2, DUMP>, grid, block, 0, stream, w, a, row0, rows, y, y_stride, dump);
-    if (rows <= 32) return launch_pdl(skinny_kernel<FMT, 4, DUMP>, grid, block, 0, stream, w, a, row0, rows, y, y_stride, dump);
-    if (rows <= 64) return launch_pdl(skinny_kernel<FMT, 8, DUMP>, grid, block, 0, stream, w, a, row0, rows, y, y_stride, dump);
+    if (rows <= 8) return launch_pdl(skinny_kernel<FMT, 1, DUMP>, grid, block, 0, stream, w, a, row0, rows, y, y_stride, dump, early);
+    if (rows <= 16) return launch_pdl(skinny_kernel<FMT, 2, DUMP>, grid, block, 0, stream, w, a, row0, rows, y, y_stride, dump, early);
+    if (rows <= 32) return launch_pdl(skinny_kernel<FMT, 4, DUMP>, grid, block, 0, stream, w, a, row0, rows, y, y_stride, dump, early);
+    if (rows <= 64) return launch_pdl(skinny_kernel<FMT, 8, DUMP>, grid, block, 0, stream, w, a, row0, rows, y, y_stride, dump, early);
     return cudaErrorInvalidValue;
 }
 
 // row0 must be a multiple of 8 (activation scale pairs are fetched with aligned 128-bit loads).
 cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                          int *dump, cudaStream_t stream)
+                          int *dump, int early, cudaStream_t stream)
 {
     if (w.n_pad == 0 || rows == 0) return cudaSuccess;
     if (row0 & 7) return cudaErrorInvalidValue;
 #define SLC_FMT(F) \
-    case F: return dump ? launch_nt<F, true>(w, a, row0, rows, y, y_stride, dump, stream) \
-                        : launch_nt<F, false>(w, a, row0, rows, y, y_stride, nullptr, stream);
+    case F: return dump ? launch_nt<F, true>(w, a, row0, rows, y, y_stride, dump, early, stream) \
+                        : launch_nt<F, false>(w, a, row0, rows, y, y_stride, nullptr, early, stream);
     switch (w.fmt) {
         SLC_FMT(FMT_Q8_0) SLC_FMT(FMT_Q4_0) SLC_FMT(FMT_Q4_K) SLC_FMT(FMT_Q6_K)
     default: return cudaErrorInvalidValue;

@@ -101,7 +101,7 @@ slc_result slc_matmul_run_static(slc_weight *weight, const void *x_device, int32
     ActView av;
     av.rows = (int)rows; av.rows_pad = NA_ROWS_PAD; av.k = (int)weight->k; av.k_pad = k_pad;
     av.q = planes.q; av.ds = planes.ds; av.dx = planes.dx; av.sx = planes.sx; av.gs = planes.gs; av.isum = planes.isum;
-    e = launch_matvec(wv, av, 0, (int)rows, y_device, y_stride, nullptr, dev->status_dev, s);
+    e = launch_matvec(wv, av, 0, (int)rows, y_device, y_stride, nullptr, dev->status_dev, 0, s);
     if (e != cudaSuccess) return na_fail(SLC_ERR_CUDA, std::string("mat-vec: ") + cudaGetErrorString(e));
     return SLC_OK;
 }

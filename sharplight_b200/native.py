@@ -62,6 +62,9 @@ SIGNATURES = {
     "slc_buffer_free": (None, [_vp, _vp]),
     "slc_buffer_upload": (_i32, [_vp, _vp, _vp, _i64]),
     "slc_buffer_download": (_i32, [_vp, _vp, _vp, _i64]),
+    "slc_host_alloc": (_i32, [_i64, _P(_vp)]),
+    "slc_host_free": (None, [_vp]),
+    "slc_buffer_copy_async": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
     "slc_weight_upload": (_i32, [_vp, _i32, _i64, _i64, _vp, _i64, _P(_vp)]),
     "slc_weight_upload_kslice": (_i32, [_vp, _i32, _i64, _i64, _vp, _i64, _i64, _i64, _P(_vp)]),
     "slc_weight_download": (_i32, [_vp, _vp, _i64]),

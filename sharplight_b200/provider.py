@@ -414,28 +414,68 @@ class SharedActivation:
             self._h = None
 
 
+class _Pinned:
+    """Page-locked host staging exposed as a numpy array."""
+
+    def __init__(self, nbytes: int):
+        p = C.c_void_p()
+        _check(N.load().slc_host_alloc(max(nbytes, 16), C.byref(p)))
+        self.ptr, self.nbytes = p, nbytes
+        self.array = np.ctypeslib.as_array((C.c_uint8 * max(nbytes, 16)).from_address(p.value))
+
+    def free(self):
+        if self.ptr is not None:
+            self.array = None
+            N.load().slc_host_free(self.ptr)
+            self.ptr = None
+
+
 class CudaSegment:
-    """ICompiledSegment for a list of MatMul nodes: weights are uploaded at compile time, inputs are copied in
-    SetInput, Execute runs the nodes in order, GetOutput copies a result out. Error behaviour follows the CPU
-    segment (src/Sharplight.Cpu/CpuCompiledSegment.cs:96-124,149,189)."""
+    """ICompiledSegment for a list of MatMul nodes. Weights are uploaded at compile time; SetInput copies the host
+    bytes (into page-locked staging, then to the device); Execute quantizes every distinct input once and runs all
+    nodes that read it from that one 8-bit copy (as the reference's lowering shares it,
+    src/Sharplight.Shaders/Lowering/GraphLowerer.IntDot.cs:38-43), then starts the copy of the outputs back to the
+    host -- all asynchronous; GetOutput waits for the device once and reads the staged result. Error behaviour follows
+    the CPU segment (src/Sharplight.Cpu/CpuCompiledSegment.cs:96-124,149,189). A node's input may also be the output
+    of an earlier node of the segment (it then stays on the device)."""
 
     def __init__(self, device: CudaDevice, segment: GraphSegment, options: CompileOptions):
         self.device, self.segment, self.options = device, segment, options
         self._disposed = False
         self._executed = False
-        self._inputs: Dict[str, np.ndarray] = {}
-        self._outputs: Dict[str, np.ndarray] = {}
+        self._synced = False
+        self._rows: Dict[str, int] = {}
         self._ops: Dict[str, MatMulOp] = {}
         self._weights: List[DeviceWeight] = []
+        lib = N.load()
+        mr = options.max_rows
         row_inv = options.row_invariant_rows > 0
+        # value name -> (columns, element bytes)
+        self._shape: Dict[str, tuple] = {}
         for node in segment.nodes:
             w = device.upload_weight(node.weight.type, node.weight.shape, node.weight.blocks)
             self._weights.append(w)
-            self._ops[node.name] = MatMulOp(device, w, options.max_rows, row_invariant=row_inv)
+            self._ops[node.name] = MatMulOp(device, w, mr, row_invariant=row_inv)
+            self._shape.setdefault(node.x, (w.k, 2 if node.x_dtype == "bf16" else 4))
+            self._shape[node.y] = (w.n, 4)
+        # device buffers for every value; page-locked staging for inputs and outputs
+        self._dev: Dict[str, C.c_void_p] = {}
+        for name, (cols, esz) in self._shape.items():
+            p = C.c_void_p()
+            _check(lib.slc_buffer_alloc(device.handle, mr * cols * esz, C.byref(p)))
+            self._dev[name] = p
+        self._in_stage = {v: _Pinned(mr * self._shape[v][0] * self._shape[v][1]) for v in segment.inputs}
+        self._out_offset, off = {}, 0
+        for v in segment.outputs:
+            self._out_offset[v] = off
+            off += mr * self._shape[v][0] * 4
+        self._out_stage = _Pinned(off)
+        self._acts = {v: SharedActivation(device, mr, self._shape[v][0]) for v in {n.x for n in segment.nodes}}
 
     @property
     def device_memory_bytes(self) -> int:
-        return sum(w.device_bytes for w in self._weights)
+        return sum(w.device_bytes for w in self._weights) + \
+            sum(self.options.max_rows * c * e for c, e in self._shape.values())
 
     def _live(self):
         if self._disposed:
@@ -445,39 +485,58 @@ class CudaSegment:
         self._live()
         if value not in self.segment.inputs:
             raise ArgumentError(f"'{value}' is not an input of this segment")
-        node = next(n for n in self.segment.nodes if n.x == value)
-        k = node.weight.shape[1]
+        cols, esz = self._shape[value]
         data = np.ascontiguousarray(data)
-        if data.ndim != 2 or data.shape[1] != k:
-            raise ArgumentError(f"input '{value}' must be [T, {k}]")
+        if data.ndim != 2 or data.shape[1] != cols or data.dtype.itemsize != esz:
+            raise ArgumentError(f"input '{value}' must be [T, {cols}] of {esz}-byte elements")
         if data.shape[0] > self.options.max_rows:
             raise ArgumentError(f"input '{value}' holds more rows than the compiled capacity")
-        self._inputs[value] = data
+        nbytes = data.nbytes
+        stage = self._in_stage[value]
+        stage.array[:nbytes] = data.reshape(-1).view(np.uint8)
+        _check(N.load().slc_buffer_copy_async(self.device.handle, self._dev[value], stage.ptr, nbytes, 0, None))
+        self._rows[value] = data.shape[0]
 
     def execute(self, symbols: Optional[Dict[str, int]] = None) -> None:
         self._live()
         t = (symbols or {}).get("T")
         if t is not None and t > self.options.max_rows:
             raise InvalidOperationError(f"T={t} exceeds the compiled bound {self.options.max_rows}")
-        values: Dict[str, np.ndarray] = dict(self._inputs)
+        lib = N.load()
+        quantized = set()
+        rows_of: Dict[str, int] = dict(self._rows)
         for node in self.segment.nodes:
-            if node.x not in values:
+            if node.x not in rows_of:
                 raise InvalidOperationError(f"input '{node.x}' was never set")
-            x = values[node.x]
-            if t is not None:
-                x = x[:t]
-            dtype = N.BF16 if node.x_dtype == "bf16" else N.F32
-            values[node.y] = self._ops[node.name].run(x, dtype)
-        self._outputs = {name: values[name] for name in self.segment.outputs}
-        self._executed = True
+            rows = rows_of[node.x] if t is None else min(t, rows_of[node.x])
+            cols, _ = self._shape[node.x]
+            if node.x not in quantized:
+                dtype = N.BF16 if node.x_dtype == "bf16" else N.F32
+                self._acts[node.x].quantize(self._dev[node.x].value, dtype, rows, cols, 0)
+                quantized.add(node.x)
+            self._acts[node.x].matmul(self._ops[node.name], self._dev[node.y].value, self._shape[node.y][0], 0)
+            rows_of[node.y] = rows
+            quantized.discard(node.y)
+        self._out_rows = {v: rows_of[v] for v in self.segment.outputs}
+        for v in self.segment.outputs:
+            nbytes = self._out_rows[v] * self._shape[v][0] * 4
+            dst = C.c_void_p(self._out_stage.ptr.value + self._out_offset[v])
+            _check(lib.slc_buffer_copy_async(self.device.handle, dst, self._dev[v], nbytes, 1, None))
+        self._executed, self._synced = True, False
 
-    def get_output(self, value: str) -> np.ndarray:
+    def get_output(self, value: str, copy: bool = True) -> np.ndarray:
         self._live()
         if not self._executed:
             raise InvalidOperationError("GetOutput before Execute")
-        if value not in self._outputs:
+        if value not in self._out_offset:
             raise ArgumentError(f"'{value}' is not an output of this segment")
-        return self._outputs[value]
+        if not self._synced:
+            self.device.synchronize()
+            self._synced = True
+        rows, cols = self._out_rows[value], self._shape[value][0]
+        off = self._out_offset[value]
+        out = self._out_stage.array[off:off + rows * cols * 4].view(np.float32).reshape(rows, cols)
+        return out.copy() if copy else out
 
     def reset_state(self) -> None:
         self._live()   # MatMul keeps no state
@@ -485,8 +544,16 @@ class CudaSegment:
     def dispose(self) -> None:
         if self._disposed:
             return
+        self.device.synchronize()
         for op in self._ops.values():
             op.dispose()
+        for a in self._acts.values():
+            a.dispose()
         for w in self._weights:
             w.dispose()
+        for p in self._dev.values():
+            N.load().slc_buffer_free(self.device.handle, p)
+        for st in self._in_stage.values():
+            st.free()
+        self._out_stage.free()
         self._disposed = True
