@@ -534,7 +534,7 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
     } else if (kernel == SLC_KERNEL_SKINNY) {
         for (int r0 = 0; r0 < rows; r0 += 64) {
             const int m = rows - r0 < 64 ? rows - r0 : 64;
-            SLC_CUDA(launch_skinny(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, early(), s));
+            SLC_CUDA(launch_skinny(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, early(), s));
             act->reads_since_quantize++;
             op->last_launches++;
         }

@@ -45,6 +45,41 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+constexpr unsigned SLC_WAIT_LIMIT = 100000;   // attempts of up to ~20 us each (suspend-time hint): about two seconds
+
+// ---- mbarrier / bulk-copy primitives ------------------------------------------------------------------------------
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, unsigned count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+// Arms the barrier with the byte count and starts the bulk copy global -> shared that completes it.
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, unsigned bytes, uint64_t *bar)
+{
+    const unsigned b = smem_u32(bar);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(b) : "memory");
+}
+
+// Bounded wait for the phase with the given parity. Returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity)
+{
+    const unsigned b = smem_u32(bar);
+    for (unsigned i = 0; i < SLC_WAIT_LIMIT; i++) {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(b), "r"(parity), "r"(20000u) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 // repack.cu
 cudaError_t launch_repack(int fmt, int n, int k, int n_pad, int k_pad, uint8_t *raw, uint8_t *data, bool to_raw,
                           cudaStream_t stream);
@@ -70,7 +105,7 @@ cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int r
 
 // skinny.cu: int8 mma tiles, 1..64 activation rows per launch.
 cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                          int *dump, int early, cudaStream_t stream);
+                          int *dump, int *status, int early, cudaStream_t stream);
 
 // mmq.cu: tcgen05 / TMEM int8 GEMM for many rows (Q4_0, Q8_0, Q4_K). status: device word set to a negative code when
 // a bounded wait runs out.

@@ -21,7 +21,6 @@ namespace slc {
 
 constexpr int FV_MAX_WARPS = 8;
 constexpr int FV_STAGES = 2;
-constexpr unsigned FV_WAIT_LIMIT = 100000;   // attempts of up to ~20 us each (suspend-time hint): about two seconds
 constexpr int FV_MAX_SMEM = 100 * 1024;
 
 template <int FMT> struct FTile;
@@ -29,39 +28,6 @@ template <> struct FTile<FMT_Q8_0> { uint4 q[8]; uint4 s[2]; };
 template <> struct FTile<FMT_Q4_0> { uint4 q[4]; uint4 s[2]; };
 template <> struct FTile<FMT_Q4_K> { uint4 q[4]; uint4 s[2]; };
 template <> struct FTile<FMT_Q6_K> { uint4 q[6]; uint4 s[2]; unsigned short d[2]; };
-
-// ---- mbarrier / bulk-copy primitives ------------------------------------------------------------------------------
-
-__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, unsigned count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-
-// Arms the barrier with the byte count and starts the bulk copy global -> shared that completes it.
-__device__ __forceinline__ void bulk_load(void *dst, const void *src, unsigned bytes, uint64_t *bar)
-{
-    const unsigned b = smem_u32(bar);
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(bytes) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(b) : "memory");
-}
-
-// Bounded wait for the phase with the given parity. Returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity)
-{
-    const unsigned b = smem_u32(bar);
-    for (unsigned i = 0; i < FV_WAIT_LIMIT; i++) {
-        unsigned ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(b), "r"(parity), "r"(20000u) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
 
 // One record of this lane: code units and the scale entries of rows g and g + 8, from a shared-memory slot.
 template <int FMT>
