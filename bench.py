@@ -204,21 +204,25 @@ def prefill_leg(device, torch, N, synth, stream, steps):
 
 class TpStack:
     """BASELINE config 5: the quantized MatMuls of a Llama-3-70B-shaped layer stack, tensor-parallel over the ranks:
-    q / k / v / gate / up column-split, o / down row-split with an all-reduce (sum) of the f32 partial outputs.
+    q / k / v / gate / up column-split (stacked into one qkv and one gate_up MatMul per layer), o / down row-split with
+    an all-reduce (sum) of the f32 partial outputs.
     Attention, norms and the activation function are not on the path: the inputs of o and down are fresh synthetic
-    activations of the sharded shape. One step = every MatMul of every layer once, for `rows` activation rows."""
+    activations of the sharded shape. One step = every MatMul of every layer once, for `rows` activation rows (any
+    count up to max_rows: decode batches and the prefill run on the same stack)."""
 
-    def __init__(self, device, torch, dist, N, synth, rank, world, rows, layers, arch, type_name="Q4_K"):
+    def __init__(self, device, torch, dist, N, synth, rank, world, max_rows, layers, arch, type_name="Q4_K"):
         from sharplight_b200 import MatMulOp, SharedActivation, tp
-        self.torch, self.dist, self.N, self.world, self.rows = torch, dist, N, world, rows
+        self.torch, self.dist, self.N, self.world = torch, dist, N, world
+        rows = max_rows
         self.layers, self.arch = layers, arch
-        self.specs = tp.layer_matmuls(arch)
+        # q / k / v and gate / up are stacked along N (one MatMul each), as a runtime stores them
+        self.specs = [(name, sum(parts), k, split, inp) for name, parts, k, split, inp in tp.fused_layer_matmuls(arch)]
         self.total_weight_bytes = tp.layer_weight_bytes(arch, type_name) * layers
         h, f = arch["hidden"], arch["ffn"]
         self.weights, self.ops = [], []
         shard_blocks = {}
-        for name, n, k, split, _ in self.specs:
-            nl, kl = tp.shard_shape(n, k, split, rank, world, type_name, arch["head_dim"])
+        for name, parts, k, split, _ in tp.fused_layer_matmuls(arch):
+            nl, kl = tp.fused_shard_shape(parts, k, split, rank, world, type_name, arch["head_dim"])
             shard_blocks[name] = (synth.weight_blocks(type_name, nl, kl, seed=500 + 7 * rank + len(shard_blocks)), nl, kl)
         for _ in range(layers):
             layer_ops = {}
@@ -236,8 +240,8 @@ class TpStack:
         self.act = {key: SharedActivation(device, rows, v.shape[1]) for key, v in self.x.items()}
         self.launches_per_step = 0
 
-    def step(self, sp):
-        N, rows = self.N, self.rows
+    def step(self, rows, sp):
+        N = self.N
         launches = 0
         for layer_ops in self.ops:
             for key in ("x_attn", "x_o", "x_ffn", "x_down"):
@@ -251,7 +255,7 @@ class TpStack:
                     self.act[key].matmul(layer_ops[name], y.data_ptr(), y.shape[1], sp)
                     launches += layer_ops[name].last_kernel()[1]
                     if split == "row" and self.world > 1:
-                        self.dist.all_reduce(y)
+                        self.dist.all_reduce(y[:rows])
         self.launches_per_step = launches
 
     def dispose(self):
@@ -302,14 +306,18 @@ def run_tp(args, torch, dist, device, N, synth, stream, world, rank, local):
     arch = tp.LLAMA70B
     layers = args.layers or arch["layers"]
     out = {}
-    for rows in ([args.rows] if world > 1 and not args.tp_all_rows else [1, 8, 64]):
-        stack = TpStack(device, torch, dist, N, synth, rank, world, rows, layers, arch)
-        steps = max(3, min(args.steps, 20))
-        ms = time_graphed(torch, dist, world, stream, stack.step, steps, 3, use_graph=not args.no_graph)
+    row_counts = sorted(set([args.rows] + ([] if args.tp_main_only else [1, 8, 64, 2048])))
+    stack = TpStack(device, torch, dist, N, synth, rank, world, max(row_counts), layers, arch)
+    flops_per_row = 2.0 * sum(n * k for _, n, k, _, _ in stack.specs) * layers
+    for rows in row_counts:
+        steps = max(3, min(args.steps, 20 if rows <= 64 else 5))
+        ms = time_graphed(torch, dist, world, stream, lambda sp, r=rows: stack.step(r, sp), steps, 3,
+                          use_graph=not args.no_graph)
         out[rows] = {"ms_per_step": ms, "weight_gbs": stack.total_weight_bytes / (ms * 1e-3) / 1e9,
+                     "tops": flops_per_row * rows / (ms * 1e-3) / 1e12, "steps": steps,
                      "launches_per_step": stack.launches_per_step, "allreduces_per_step": 2 * layers if world > 1 else 0}
-        stack.dispose()
-        torch.cuda.synchronize()
+    stack.dispose()
+    torch.cuda.synchronize()
     return {"workload": f"configs[4]: Llama-3-70B-shaped stack, {layers} layers, Q4_K, tensor parallel x{world}",
             "weight_bytes_per_step": tp.layer_weight_bytes(arch) * layers, "by_rows": out}
 
@@ -481,7 +489,7 @@ def run_ours(args):
         same = bool(all(np.array_equal(yd[i], e2e_out[i]) for i in range(COPIES)))
 
     tp_stack = None
-    if world == 1 and args.tp_stack:
+    if world == 1 and not args.no_tp_stack:
         tp_stack = run_tp(args, torch, dist, device, N, synth, stream, 1, 0, local)
     prefill = None
     if world == 1 and not args.no_prefill:
@@ -544,8 +552,8 @@ def main():
     ap.add_argument("--copies", type=int, default=COPIES, help="weight matrices per step (profiling runs use fewer)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--layers", type=int, default=0, help="layers of the tensor-parallel stack (default: the architecture's 80)")
-    ap.add_argument("--tp-stack", action="store_true", help="N=1: also time the 70B-shaped stack at tensor-parallel degree 1")
-    ap.add_argument("--tp-all-rows", action="store_true", help="N>1: time decode batches 1, 8 and 64 instead of --rows only")
+    ap.add_argument("--no-tp-stack", action="store_true", help="N=1: skip the 70B-shaped stack at tensor-parallel degree 1")
+    ap.add_argument("--tp-main-only", action="store_true", help="time the stack at --rows only, not at 1, 8, 64 and 2048 rows")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM leg")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of a CUDA graph")
     args = ap.parse_args()

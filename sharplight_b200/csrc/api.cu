@@ -499,8 +499,10 @@ slc_result slc_matmul_last_kernel(slc_matmul *op, int32_t *out_kernel, int32_t *
 static int choose_kernel(const slc_matmul *op, int rows)
 {
     if (op->forced_kernel != SLC_KERNEL_AUTO) return op->forced_kernel;
-    if ((op->flags & SLC_MATMUL_ROW_INVARIANT) && rows <= 8) return SLC_KERNEL_MMVQ;
-    if (rows <= 2) return SLC_KERNEL_MMVQ;
+    // the mat-vec keeps a row's quantized activations whole in shared memory; a K beyond that goes to the tiled kernel
+    const bool mv = matvec_fits(1, op->w->view.k_pad);
+    if (mv && (op->flags & SLC_MATMUL_ROW_INVARIANT) && rows <= 8) return SLC_KERNEL_MMVQ;
+    if (mv && rows <= 2) return SLC_KERNEL_MMVQ;
     if (rows <= 64 || !mmq_supports(op->w->fmt)) return SLC_KERNEL_SKINNY;
     return SLC_KERNEL_MMQ;
 }

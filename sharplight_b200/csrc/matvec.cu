@@ -21,7 +21,7 @@ namespace slc {
 
 constexpr int FV_MAX_WARPS = 8;
 constexpr int FV_STAGES = 2;
-constexpr int FV_MAX_SMEM = 100 * 1024;
+constexpr int FV_MAX_SMEM = 200 * 1024;   // what a launch may ask for; typical launches take 25-60 KB
 
 template <int FMT> struct FTile;
 template <> struct FTile<FMT_Q8_0> { uint4 q[8]; uint4 s[2]; };

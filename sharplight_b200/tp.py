@@ -77,3 +77,34 @@ def shard_shape(n: int, k: int, split: str, rank: int, tp: int, type_name: str =
 def layer_weight_bytes(arch: dict, type_name: str = "Q4_K") -> int:
     bs, bb = BLOCK[type_name]
     return sum(n * (k // bs) * bb for _, n, k, _, _ in layer_matmuls(arch))
+
+
+# The same layer with the MatMuls that share an input stacked along N, the way a runtime stores them: one MatMul for
+# q / k / v and one for gate / up. A stacked weight is column-split part by part (rank r keeps its rows of q, its rows of
+# k and its rows of v), so its local rows are exactly the local rows of the separate MatMuls, in the same order.
+def fused_layer_matmuls(arch: dict):
+    """(name, [N of every stacked part], K, split, input) per MatMul of a layer."""
+    h, f = arch["hidden"], arch["ffn"]
+    kv = arch["kv_heads"] * arch["head_dim"]
+    return [("qkv", [h, kv, kv], h, "column", "x_attn"), ("o", [h], h, "row", "x_o"),
+            ("gate_up", [f, f], h, "column", "x_ffn"), ("down", [h], f, "row", "x_down")]
+
+
+def fused_shard_shape(parts, k: int, split: str, rank: int, tp: int, type_name: str = "Q4_K", head_dim: int = 128):
+    """(n_local, k_local) of rank's shard of a stacked weight."""
+    shapes = [shard_shape(n, k, split, rank, tp, type_name, head_dim) for n in parts]
+    return sum(s[0] for s in shapes), shapes[0][1]
+
+
+def fused_column_shard(blocks: np.ndarray, type_name: str, parts, k: int, rank: int, tp: int, align: int = 1):
+    """Rank's rows of every part of a stacked [sum(parts), k] weight, concatenated: (blocks, n_local, k)."""
+    bs, bb = BLOCK[type_name]
+    row_bytes = k // bs * bb
+    flat = np.ascontiguousarray(blocks, np.uint8).reshape(sum(parts), row_bytes)
+    out, base = [], 0
+    for n in parts:
+        n0, n1 = shard_range(n, rank, tp, align if n % (align * tp) == 0 else 1)
+        out.append(flat[base + n0:base + n1])
+        base += n
+    cat = np.concatenate(out, axis=0)
+    return cat.reshape(-1), cat.shape[0], k

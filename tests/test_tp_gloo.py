@@ -84,3 +84,30 @@ def test_shard_ranges_cover_everything():
     assert tp.shard_shape(28672, 8192, "column", 3, 8) == (3584, 8192)
     assert tp.shard_shape(8192, 28672, "row", 3, 8) == (8192, 3584)
     assert tp.shard_shape(1024, 8192, "column", 0, 8) == (128, 8192)
+
+
+def test_stacked_column_split_equals_separate_splits():
+    """A stacked q/k/v weight split part by part holds exactly the rows the separate MatMuls would hold."""
+    parts, k, world = [64, 16, 16], 512, 2
+    blocks = synth.weight_blocks("Q4_K", sum(parts), k, seed=21)
+    x = synth.activations(2, k, seed=22)
+    fmt = FMT_OF["Q4_K"]
+    full, _, _ = sl_oracle.matmul_intdot(fmt, blocks, sum(parts), k, x)
+    row_bytes = k // 256 * 144
+    flat = blocks.reshape(sum(parts), row_bytes)
+    for rank in range(world):
+        sb, sn, sk = tp.fused_column_shard(blocks, "Q4_K", parts, k, rank, world, align=8)
+        assert (sn, sk) == tp.fused_shard_shape(parts, k, "column", rank, world, "Q4_K", head_dim=8)
+        y, _, _ = sl_oracle.matmul_intdot(fmt, sb, sn, sk, x)
+        base, cols = 0, []
+        for n in parts:
+            n0, n1 = tp.shard_range(n, rank, world, 8)
+            cols.append(full[:, base + n0:base + n1])
+            separate, _, _ = tp.column_shard(flat[base:base + n].reshape(-1), "Q4_K", n, k, rank, world, align=8)
+            assert separate.tobytes() in sb.tobytes()
+            base += n
+        assert np.array_equal(y, np.concatenate(cols, axis=1))
+    names = [m[0] for m in tp.fused_layer_matmuls(tp.LLAMA70B)]
+    assert names == ["qkv", "o", "gate_up", "down"]
+    assert sum(sum(p) * k_ for _, p, k_, _, _ in tp.fused_layer_matmuls(tp.LLAMA70B)) == \
+        sum(n * k_ for _, n, k_, _, _ in tp.layer_matmuls(tp.LLAMA70B))
