@@ -199,6 +199,31 @@ SLC_API slc_result slc_activation_quantize(slc_activation *act, const void *x_de
 SLC_API slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act, float *y_device, int64_t y_stride,
                                             void *stream);
 
+/* ---- tensor parallelism: the reference has none (its multi-device story is layer placement,
+        src/Sharplight.Core/Runtime/PlacementPlanner.cs:7-13), so these entry points have no counterpart there. One
+        process per GPU. A row-split MatMul (o, down) leaves every rank with a partial output; with an exchange the
+        MatMul kernel itself sums the partial outputs of all ranks, through receive areas that the ranks map into each
+        other's address space (CUDA IPC, plain peer stores over NVLink, bounded waits), and y receives the total, the
+        bit-identical value on every rank. For up to SLC_TP_MAX_ROWS rows per call; larger row counts go through
+        slc_matmul_run_quantized and the caller's all-reduce.
+        Set-up: every rank creates its exchange (same world, max_rows, n everywhere) and gets a 64-byte handle; the
+        host exchanges the handles by any means and passes all of them, in rank order, to connect. All ranks must
+        issue the same sequence of allreduce calls on an exchange. A peer that never arrives (it died, or its stream is
+        stuck) ends the wait after about a second: the call's kernel raises the device status to SLC_ERR_TIMEOUT
+        (slc_last_status) and y is not meaningful. Destroy only when no rank has a launch in flight. */
+typedef struct slc_tp_exchange slc_tp_exchange;
+#define SLC_TP_MAX_RANKS 8
+#define SLC_TP_MAX_ROWS 64
+#define SLC_TP_HANDLE_BYTES 64
+SLC_API slc_result slc_tp_exchange_create(slc_device *device, int32_t rank, int32_t world, int64_t max_rows, int64_t n,
+                                          slc_tp_exchange **out, uint8_t *out_handle /* [SLC_TP_HANDLE_BYTES] */);
+SLC_API slc_result slc_tp_exchange_connect(slc_tp_exchange *exchange, const uint8_t *handles /* [world][64] */);
+SLC_API void slc_tp_exchange_destroy(slc_tp_exchange *exchange);
+/* y (device, f32) = sum over ranks of (act . W^T), W being this rank's K range of the weight and act this rank's
+   matching slice of the activations. Asynchronous on the stream. */
+SLC_API slc_result slc_matmul_run_quantized_allreduce(slc_matmul *op, slc_activation *act, slc_tp_exchange *exchange,
+                                                      float *y_device, int64_t y_stride, void *stream);
+
 /* ---- no device allocation: this entry point has no counterpart in the reference. It serves hosts that may not call
         cudaMalloc while they run (a serving loop with a fixed memory budget, a framework that owns the allocator, a
         phase where an allocation would stall the device). Same result as slc_matmul_run with device pointers, for

@@ -507,8 +507,9 @@ static int choose_kernel(const slc_matmul *op, int rows)
     return SLC_KERNEL_MMQ;
 }
 
+// ex (optional): the MatMul is the row-split part of a tensor-parallel group and its kernel sums over the ranks.
 static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, long long y_stride, int *dump,
-                              cudaStream_t s)
+                              cudaStream_t s, const Exchange *ex = nullptr)
 {
     const ActView av = view_of(act);
     const WeightView &wv = op->w->view;
@@ -520,7 +521,7 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
     op->last_launches_total = 0;
     // A launch may run beside its predecessor when an earlier launch on this stream has already read these
     // activations: they were complete before that launch started, and MatMul outputs do not alias each other.
-    auto early = [&]() { return act->reads_since_quantize > 0 ? 1 : 0; };
+    auto early = [&]() { return !ex && act->reads_since_quantize > 0 ? 1 : 0; };
     if (kernel == SLC_KERNEL_MMVQ) {
         // chunks of up to 4 rows; every row of a chunk is computed exactly as a single row is, so the row-invariant
         // guarantee holds for any chunking
@@ -529,17 +530,19 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
         if (!matvec_fits(chunk, wv.k_pad)) return fail(SLC_ERR_UNSUPPORTED, "K is too large for the mat-vec kernel's shared memory");
         for (int r0 = 0; r0 < rows; r0 += chunk) {
             const int m = rows - r0 < chunk ? rows - r0 : chunk;
-            SLC_CUDA(launch_matvec(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, early(), s));
+            SLC_CUDA(launch_matvec(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, early(), s, ex));
             act->reads_since_quantize++;
             op->last_launches++;
         }
     } else if (kernel == SLC_KERNEL_SKINNY) {
         for (int r0 = 0; r0 < rows; r0 += 64) {
             const int m = rows - r0 < 64 ? rows - r0 : 64;
-            SLC_CUDA(launch_skinny(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, early(), s));
+            SLC_CUDA(launch_skinny(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, early(), s, ex));
             act->reads_since_quantize++;
             op->last_launches++;
         }
+    } else if (ex) {
+        return fail(SLC_ERR_UNSUPPORTED, "the in-kernel all-reduce serves the mat-vec and skinny kernels (up to 64 rows)");
     } else {
         if (!act->planes.q_tiled) return fail(SLC_ERR_INVALID_STATE, "the tensor-core GEMM needs more than 64 rows");
         SLC_CUDA(launch_mmq(wv, av, act->planes.q_tiled, y, y_stride, dump, op->dev->status_dev, early(), s));
@@ -560,6 +563,108 @@ slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act, float *
     SLC_CUDA(cudaSetDevice(op->dev->index));
     cudaStream_t s = stream ? (cudaStream_t)stream : op->dev->stream;
     return run_kernels(op, act, y, y_stride, nullptr, s);
+}
+
+// ---- tensor-parallel exchange ---------------------------------------------------------------------------------------
+
+slc_result slc_tp_exchange_create(slc_device *d, int32_t rank, int32_t world, int64_t max_rows, int64_t n,
+                                  slc_tp_exchange **out, uint8_t *out_handle)
+{
+    if (!out || !out_handle) return fail(SLC_ERR_INVALID_ARGUMENT, "out or out_handle is null");
+    *out = nullptr;
+    if (!d || world < 1 || world > SLC_TP_MAX_RANKS || rank < 0 || rank >= world) {
+        return fail(SLC_ERR_INVALID_ARGUMENT, "exchange: 1 <= world <= 8, 0 <= rank < world");
+    }
+    if (max_rows < 1 || max_rows > SLC_TP_MAX_ROWS || n < 1 || n > (1 << 24)) {
+        return fail(SLC_ERR_INVALID_ARGUMENT, "exchange: 1 <= max_rows <= 64, 1 <= n <= 2^24");
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == SLC_TP_HANDLE_BYTES, "IPC handle size");
+    SLC_CUDA(cudaSetDevice(d->index));
+    slc_tp_exchange *x = new (std::nothrow) slc_tp_exchange();
+    if (!x) return fail(SLC_ERR_OUT_OF_MEMORY, "host allocation failed");
+    x->dev = d; x->rank = rank; x->world = world; x->max_rows = max_rows; x->n = n;
+    const int n_stride = (int)round_up((size_t)n, 64), groups = n_stride / 16;
+    const size_t recv_b = round_up((size_t)2 * world * max_rows * n_stride * 4, 256);
+    const size_t flag_b = round_up((size_t)2 * world * groups * 4, 256);
+    x->flags_off = recv_b; x->ctl_off = recv_b + flag_b; x->bytes = recv_b + flag_b + 256;
+    cudaError_t e = cudaMalloc(&x->base, x->bytes);
+    if (e == cudaSuccess) e = cudaMemset(x->base, 0, x->bytes);
+    cudaIpcMemHandle_t h;
+    memset(&h, 0, sizeof h);
+    if (e == cudaSuccess && world > 1) e = cudaIpcGetMemHandle(&h, x->base);
+    if (e != cudaSuccess) {
+        if (x->base) cudaFree(x->base);
+        delete x;
+        return cuda_fail(e, "slc_tp_exchange_create");
+    }
+    memcpy(out_handle, &h, sizeof h);
+    Exchange &v = x->view;
+    v.world = world; v.rank = rank; v.max_rows = (int)max_rows; v.n_stride = n_stride; v.groups = groups;
+    v.wait_ms = 1000;
+    v.epoch = reinterpret_cast<int *>(x->base + x->ctl_off);
+    v.done = v.epoch + 1;
+    x->peer[rank] = x->base;
+    x->connected = world == 1;
+    if (x->connected) {
+        v.recv[0] = reinterpret_cast<float *>(x->base);
+        v.flags[0] = reinterpret_cast<int *>(x->base + x->flags_off);
+    }
+    *out = x;
+    return SLC_OK;
+}
+
+slc_result slc_tp_exchange_connect(slc_tp_exchange *x, const uint8_t *handles)
+{
+    if (!x || !handles) return fail(SLC_ERR_INVALID_ARGUMENT, "exchange or handles is null");
+    if (x->connected) return x->world == 1 ? SLC_OK : fail(SLC_ERR_INVALID_STATE, "the exchange is already connected");
+    SLC_CUDA(cudaSetDevice(x->dev->index));
+    for (int p = 0; p < x->world; p++) {
+        if (p == x->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)p * SLC_TP_HANDLE_BYTES, sizeof h);
+        cudaError_t e = cudaIpcOpenMemHandle(&x->peer[p], h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            for (int q = 0; q < p; q++) {
+                if (q != x->rank && x->peer[q]) { cudaIpcCloseMemHandle(x->peer[q]); x->peer[q] = nullptr; }
+            }
+            return cuda_fail(e, "cudaIpcOpenMemHandle (peer receive area)");
+        }
+    }
+    for (int p = 0; p < x->world; p++) {
+        x->view.recv[p] = reinterpret_cast<float *>(x->peer[p]);
+        x->view.flags[p] = reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(x->peer[p]) + x->flags_off);
+    }
+    x->connected = true;
+    return SLC_OK;
+}
+
+void slc_tp_exchange_destroy(slc_tp_exchange *x)
+{
+    if (!x) return;
+    cudaSetDevice(x->dev->index);
+    cudaDeviceSynchronize();
+    for (int p = 0; p < x->world; p++) {
+        if (p != x->rank && x->peer[p]) cudaIpcCloseMemHandle(x->peer[p]);
+    }
+    cudaFree(x->base);
+    delete x;
+}
+
+slc_result slc_matmul_run_quantized_allreduce(slc_matmul *op, slc_activation *act, slc_tp_exchange *x, float *y,
+                                              int64_t y_stride, void *stream)
+{
+    if (!op || !act || !x) return fail(SLC_ERR_INVALID_ARGUMENT, "null op, activation or exchange");
+    if (act->dev != op->dev || x->dev != op->dev) return fail(SLC_ERR_INVALID_ARGUMENT, "op, activation and exchange live on different devices");
+    if (!x->connected) return fail(SLC_ERR_INVALID_STATE, "the exchange is not connected");
+    if (act->k != op->w->k) return fail(SLC_ERR_INVALID_ARGUMENT, "activation K differs from the weight's K");
+    if (act->rows > op->max_rows) return fail(SLC_ERR_INVALID_STATE, "rows exceed the op's compiled bound");
+    if (act->rows > x->max_rows) return fail(SLC_ERR_UNSUPPORTED, "rows exceed the exchange's bound");
+    if (op->w->n > x->n) return fail(SLC_ERR_INVALID_ARGUMENT, "the weight has more rows than the exchange was created for");
+    if (act->rows == 0 || op->w->n == 0) return SLC_OK;
+    if (!y || y_stride < op->w->n) return fail(SLC_ERR_INVALID_ARGUMENT, "bad output buffer or stride");
+    SLC_CUDA(cudaSetDevice(op->dev->index));
+    cudaStream_t s = stream ? (cudaStream_t)stream : op->dev->stream;
+    return run_kernels(op, act, y, y_stride, nullptr, s, &x->view);
 }
 
 static slc_result ensure_op_buffers(slc_matmul *op, bool need_x_stage, bool need_y_stage)

@@ -2,6 +2,7 @@
 #pragma once
 
 #include "internal.cuh"
+#include "exchange.cuh"
 
 struct slc_device
 {
@@ -49,3 +50,15 @@ struct slc_matmul
     float *y_stage = nullptr;       // device staging for host outputs (max_rows x n)
 };
 
+
+struct slc_tp_exchange
+{
+    slc_device *dev = nullptr;
+    int rank = 0, world = 0;
+    long long max_rows = 0, n = 0;
+    uint8_t *base = nullptr;              // this rank's receive area, arrival words and counters (one allocation)
+    size_t bytes = 0, flags_off = 0, ctl_off = 0;
+    void *peer[slc::SLC_MAX_RANKS] = {};  // the peers' allocations as mapped here (own entry = base)
+    bool connected = false;
+    slc::Exchange view{};
+};

@@ -100,12 +100,15 @@ cudaError_t launch_quantize(const void *x, int x_dtype, int rows, int rows_pad, 
 // matvec.cu: dp4a mat-vec for 1..4 activation rows (rows row0 .. row0+rows-1 of the quantized activations). dump
 // (optional) receives unsigned-code block dots [rows][n][k/32]; status: device word raised when a bounded wait runs out.
 bool matvec_fits(int rows, int k_pad);
+// exchange (optional, both kernels): the MatMul is the row-split part of a tensor-parallel group; the kernel sums the
+// partial outputs of all ranks itself (exchange.cuh) and y receives the total. Such a launch is never early.
+struct Exchange;
 cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                          int *dump, int *status, int early, cudaStream_t stream);
+                          int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange = nullptr);
 
 // skinny.cu: int8 mma tiles, 1..64 activation rows per launch.
 cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                          int *dump, int *status, int early, cudaStream_t stream);
+                          int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange = nullptr);
 
 // mmq.cu: tcgen05 / TMEM int8 GEMM for many rows (Q4_0, Q8_0, Q4_K). status: device word set to a negative code when
 // a bounded wait runs out.

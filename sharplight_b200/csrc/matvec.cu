@@ -16,6 +16,7 @@
 // the one int->float conversion per block. Every mbarrier wait is bounded: when it runs out the kernel raises the
 // device status word and leaves.
 #include "internal.cuh"
+#include "exchange.cuh"
 
 namespace slc {
 
@@ -400,7 +401,7 @@ __device__ __forceinline__ void compute_slot(const uint8_t *slot, const SmemAct 
 template <int FMT, int M, bool DUMP>
 __global__ void __launch_bounds__(FV_MAX_WARPS * 32)
 matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__ y, long long y_stride, int *dump,
-              int *status, int early)
+              int *status, int early, const Exchange ex)
 {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) uint64_t bars[FV_MAX_WARPS][FV_STAGES];
@@ -494,12 +495,26 @@ matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__
         }
     }
     __syncthreads();
-    if (threadIdx.x < 16 * M) {
+    {
+        const bool own = threadIdx.x < 16 * M;   // one thread per output value of the CTA
         const int m = threadIdx.x / 16, rr = threadIdx.x % 16;
-        float v = 0.0f;
-        for (int wi = 0; wi < warps; wi++) v += red[wi][rr][m];
         const int row = blockIdx.x * 16 + rr;
-        if (row < w.n) y[(long long)(row0 + m) * y_stride + row] = v;
+        float v = 0.0f;
+        if (own) {
+            for (int wi = 0; wi < warps; wi++) v += red[wi][rr][m];
+        }
+        if (ex.world == 0) {
+            if (own && row < w.n) y[(long long)(row0 + m) * y_stride + row] = v;
+        } else {
+            // row-split MatMul of a tensor-parallel group: v is this rank's partial value (exchange.cuh)
+            const int epoch = ex_epoch(ex), slot = epoch & 1;
+            if (own) {
+                for (int p = 0; p < ex.world; p++) ex.recv[p][ex_index(ex, slot, ex.rank, m, row)] = v;
+            }
+            if (!ex_publish_and_wait(ex, slot, epoch, blockIdx.x) && threadIdx.x == 0) atomicExch(status, -7);
+            if (own && row < w.n) y[(long long)(row0 + m) * y_stride + row] = ex_sum(ex, slot, m, row);
+            ex_finish(ex, epoch);
+        }
     }
     pdl_exit(early);
 }
@@ -525,7 +540,7 @@ bool matvec_fits(int rows, int k_pad)
 
 template <int FMT, int M, bool DUMP>
 static cudaError_t launch_one(const WeightView &w, const ActView &a, int row0, float *y, long long y_stride, int *dump,
-                              int *status, int early, cudaStream_t stream)
+                              int *status, int early, cudaStream_t stream, const Exchange &ex)
 {
     static bool configured[64] = {};
     int dev = 0;
@@ -538,17 +553,17 @@ static cudaError_t launch_one(const WeightView &w, const ActView &a, int row0, f
     }
     const int warps = matvec_warps(w);
     return launch_pdl(kernel, dim3(w.n_pad / 16), dim3(warps * 32), matvec_smem(FMT, warps, M, w.k_pad), stream, w, a,
-                      row0, y, y_stride, dump, status, early);
+                      row0, y, y_stride, dump, status, early, ex);
 }
 
 template <int FMT>
 static cudaError_t launch_fmt(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                              int *dump, int *status, int early, cudaStream_t stream)
+                              int *dump, int *status, int early, cudaStream_t stream, const Exchange &ex)
 {
 #define SLC_ROWS(MM)                                                                        \
     case MM:                                                                                \
-        return dump ? launch_one<FMT, MM, true>(w, a, row0, y, y_stride, dump, status, early, stream)      \
-                    : launch_one<FMT, MM, false>(w, a, row0, y, y_stride, nullptr, status, early, stream);
+        return dump ? launch_one<FMT, MM, true>(w, a, row0, y, y_stride, dump, status, early, stream, ex)      \
+                    : launch_one<FMT, MM, false>(w, a, row0, y, y_stride, nullptr, status, early, stream, ex);
     switch (rows) {
         SLC_ROWS(1) SLC_ROWS(2) SLC_ROWS(3) SLC_ROWS(4)
     default: return cudaErrorInvalidValue;
@@ -558,14 +573,20 @@ static cudaError_t launch_fmt(const WeightView &w, const ActView &a, int row0, i
 
 // rows 1..4 starting at activation row row0; dump (optional) receives [rows][n][k/32] block dots.
 cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                          int *dump, int *status, int early, cudaStream_t stream)
+                          int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange)
 {
     if (w.n_pad == 0 || rows == 0) return cudaSuccess;
+    Exchange ex{};
+    if (exchange) {
+        ex = *exchange;
+        // a launch that exchanges waits for its predecessor before anything else, and needs room for its tile
+        if (early || rows > ex.max_rows || w.n_pad > ex.n_stride || w.n_pad / 16 > ex.groups) return cudaErrorInvalidValue;
+    }
     switch (w.fmt) {
-    case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(w, a, row0, rows, y, y_stride, dump, status, early, stream);
-    case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(w, a, row0, rows, y, y_stride, dump, status, early, stream);
-    case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(w, a, row0, rows, y, y_stride, dump, status, early, stream);
-    case FMT_Q6_K: return launch_fmt<FMT_Q6_K>(w, a, row0, rows, y, y_stride, dump, status, early, stream);
+    case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
+    case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
+    case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
+    case FMT_Q6_K: return launch_fmt<FMT_Q6_K>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
     default: return cudaErrorInvalidValue;
     }
 }

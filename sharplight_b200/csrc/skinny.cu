@@ -14,6 +14,7 @@
 // 12582912 + dot: int->float costs no instruction (the conversion unit would be the bottleneck), and the integer
 // sub-block scale is applied by one exact FMA, fma(f, sc, -12582912 * sc).
 #include "internal.cuh"
+#include "exchange.cuh"
 
 namespace slc {
 
@@ -286,7 +287,7 @@ __host__ __device__ constexpr int sk_wdepth(int nt) { return nt == 8 ? 1 : sk_de
 template <int FMT, int NT, bool DUMP>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__restrict__ y, long long y_stride,
-              int *dump, int *status, int early)
+              int *dump, int *status, int early, const Exchange ex)
 {
     extern __shared__ __align__(128) unsigned char sk_smem[];
     __shared__ __align__(8) uint64_t bars[SK_WARPS][4];
@@ -378,31 +379,70 @@ skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__
             for (int e = 0; e < 4; e++) red[((rgl * NT + nt) * 4 + e) * 32 + lane] = acc[nt][e];
     }
     __syncthreads();
-    if (ks == 0 && rg_live) {
+    if (ex.world == 0) {
+        if (ks == 0 && rg_live) {
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
+            for (int nt = 0; nt < NT; nt++) {
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const float v = acc[nt][e] + red[((rgl * NT + nt) * 4 + e) * 32 + lane];
-                const int row = rg * 16 + c.g + 8 * (e >> 1);
-                const int m = nt * 8 + 2 * c.t + (e & 1);
-                if (row < w.n && m < rows) y[(long long)(row0 + m) * y_stride + row] = v;
+                for (int e = 0; e < 4; e++) {
+                    const float v = acc[nt][e] + red[((rgl * NT + nt) * 4 + e) * 32 + lane];
+                    const int row = rg * 16 + c.g + 8 * (e >> 1);
+                    const int m = nt * 8 + 2 * c.t + (e & 1);
+                    if (row < w.n && m < rows) y[(long long)(row0 + m) * y_stride + row] = v;
+                }
             }
         }
+    } else {
+        // Row-split MatMul of a tensor-parallel group (exchange.cuh). The CTA's partial tile is first laid out in
+        // shared memory as [token][64 columns], so that it leaves for the peers in 16-byte stores along the columns.
+        float *tile = red + SK_RGS * NT * 4 * 32;
+        if (ks == 0) {
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float v = acc[nt][e] + red[((rgl * NT + nt) * 4 + e) * 32 + lane];   // zero for absent row groups
+                    tile[(nt * 8 + 2 * c.t + (e & 1)) * 64 + rgl * 16 + c.g + 8 * (e >> 1)] = v;
+                }
+            }
+        }
+        __syncthreads();
+        const int epoch = ex_epoch(ex), slot = epoch & 1;
+        const int col0 = blockIdx.x * 64;
+        for (int idx = threadIdx.x; idx < rows * 16; idx += SK_WARPS * 32) {
+            const int m = idx >> 4, c4 = (idx & 15) * 4;
+            const float4 v = *reinterpret_cast<const float4 *>(tile + m * 64 + c4);
+            for (int p = 0; p < ex.world; p++) {
+                *reinterpret_cast<float4 *>(ex.recv[p] + ex_index(ex, slot, ex.rank, m, col0 + c4)) = v;
+            }
+        }
+        if (!ex_publish_and_wait(ex, slot, epoch, blockIdx.x) && threadIdx.x == 0) atomicExch(status, -7);
+        for (int idx = threadIdx.x; idx < rows * 16; idx += SK_WARPS * 32) {
+            const int m = idx >> 4, c4 = (idx & 15) * 4;
+            const float4 sum = ex_sum4(ex, slot, m, col0 + c4);
+            const float sv[4] = { sum.x, sum.y, sum.z, sum.w };
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                if (col0 + c4 + j < w.n) y[(long long)(row0 + m) * y_stride + col0 + c4 + j] = sv[j];
+            }
+        }
+        ex_finish(ex, epoch);
     }
     pdl_exit(early);
 }
 
 template <int FMT, int NT, bool DUMP>
 static cudaError_t launch_cfg(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                              int *dump, int *status, int early, cudaStream_t stream)
+                              int *dump, int *status, int early, cudaStream_t stream, const Exchange &ex)
 {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     auto kernel = skinny_kernel<FMT, NT, DUMP>;
-    // activation ring (depth x two K halves) + one weight-record ring per warp
-    const size_t smem = (size_t)sk_depth(NT) * SK_KS * SkTile<NT>::BYTES + (size_t)SK_WARPS * sk_wdepth(NT) * record_bytes(FMT);
+    // activation ring (depth x two K halves) + one weight-record ring per warp; the epilogue reuses the front of it
+    // for the K-half reduction (NT x 2 KB) and, when exchanging, the outgoing tile (NT x 2 KB)
+    size_t smem = (size_t)sk_depth(NT) * SK_KS * SkTile<NT>::BYTES + (size_t)SK_WARPS * sk_wdepth(NT) * record_bytes(FMT);
+    if (smem < (size_t)NT * 4096) smem = (size_t)NT * 4096;
     if (dev < 64 && !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
@@ -410,30 +450,36 @@ static cudaError_t launch_cfg(const WeightView &w, const ActView &a, int row0, i
     }
     const int rg_count = w.n_pad >> 4;
     return launch_pdl(kernel, dim3((rg_count + SK_RGS - 1) / SK_RGS), dim3(SK_WARPS * 32), smem, stream, w, a, row0, rows,
-                      y, y_stride, dump, status, early);
+                      y, y_stride, dump, status, early, ex);
 }
 
 template <int FMT, bool DUMP>
 static cudaError_t launch_nt(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                             int *dump, int *status, int early, cudaStream_t stream)
+                             int *dump, int *status, int early, cudaStream_t stream, const Exchange &ex)
 {
-    if (rows <= 8) return launch_cfg<FMT, 1, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream);
-    if (rows <= 16) return launch_cfg<FMT, 2, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream);
-    if (rows <= 32) return launch_cfg<FMT, 4, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream);
-    if (rows <= 64) return launch_cfg<FMT, 8, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream);
+    if (rows <= 8) return launch_cfg<FMT, 1, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
+    if (rows <= 16) return launch_cfg<FMT, 2, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
+    if (rows <= 32) return launch_cfg<FMT, 4, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
+    if (rows <= 64) return launch_cfg<FMT, 8, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
     return cudaErrorInvalidValue;
 }
 
 // row0 must be a multiple of 8 (activation scale pairs are fetched with aligned 128-bit accesses), and the quantized
 // activations must be padded to the token tile (8, 16, 32 or 64 rows).
 cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                          int *dump, int *status, int early, cudaStream_t stream)
+                          int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange)
 {
     if (w.n_pad == 0 || rows == 0) return cudaSuccess;
     if (row0 & 7) return cudaErrorInvalidValue;
+    Exchange ex{};
+    if (exchange) {
+        ex = *exchange;
+        const int ctas = ((w.n_pad >> 4) + SK_RGS - 1) / SK_RGS;
+        if (early || rows > ex.max_rows || ctas * 64 > ex.n_stride || ctas > ex.groups) return cudaErrorInvalidValue;
+    }
 #define SLC_FMT(F) \
-    case F: return dump ? launch_nt<F, true>(w, a, row0, rows, y, y_stride, dump, status, early, stream) \
-                        : launch_nt<F, false>(w, a, row0, rows, y, y_stride, nullptr, status, early, stream);
+    case F: return dump ? launch_nt<F, true>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex) \
+                        : launch_nt<F, false>(w, a, row0, rows, y, y_stride, nullptr, status, early, stream, ex);
     switch (w.fmt) {
         SLC_FMT(FMT_Q8_0) SLC_FMT(FMT_Q4_0) SLC_FMT(FMT_Q4_K) SLC_FMT(FMT_Q6_K)
     default: return cudaErrorInvalidValue;

@@ -22,6 +22,7 @@ FMT_Q4_0, FMT_Q8_0, FMT_Q4_K, FMT_Q6_K = 2, 8, 12, 14
 F32, BF16 = 0, 1
 MATMUL_DEFAULT, MATMUL_ROW_INVARIANT = 0, 1
 KERNEL_AUTO, KERNEL_MMVQ, KERNEL_SKINNY, KERNEL_MMQ = 0, 1, 2, 3
+TP_MAX_RANKS, TP_MAX_ROWS, TP_HANDLE_BYTES = 8, 64, 64
 
 BLOCK = {FMT_Q4_0: (32, 18), FMT_Q8_0: (32, 34), FMT_Q4_K: (256, 144), FMT_Q6_K: (256, 210)}
 
@@ -79,6 +80,10 @@ SIGNATURES = {
     "slc_activation_destroy": (None, [_vp]),
     "slc_activation_quantize": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp]),
     "slc_matmul_run_quantized": (_i32, [_vp, _vp, _vp, _i64, _vp]),
+    "slc_tp_exchange_create": (_i32, [_vp, _i32, _i32, _i64, _i64, _P(_vp), _vp]),
+    "slc_tp_exchange_connect": (_i32, [_vp, _vp]),
+    "slc_tp_exchange_destroy": (None, [_vp]),
+    "slc_matmul_run_quantized_allreduce": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp]),
     "slc_matmul_run_static": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp, _i64, _vp]),
     "slc_static_last_error": (C.c_char_p, []),
     "slc_debug_quantize": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp, _vp, _vp]),

@@ -414,6 +414,47 @@ class SharedActivation:
             self._h = None
 
 
+class TpExchange:
+    """The receive area through which a row-split MatMul's kernel sums its output over the ranks of a tensor-parallel
+    group (slc_tp_exchange). One per rank; ``handle_bytes`` of every rank, in rank order, go to ``connect``."""
+
+    def __init__(self, device: CudaDevice, rank: int, world: int, max_rows: int, n: int):
+        self.device, self.rank, self.world, self.max_rows, self.n = device, rank, world, max_rows, n
+        h = C.c_void_p()
+        buf = (C.c_uint8 * N.TP_HANDLE_BYTES)()
+        _check(N.load().slc_tp_exchange_create(device.handle, rank, world, max_rows, n, C.byref(h), buf))
+        self._h = h
+        self.handle_bytes = bytes(buf)
+
+    @property
+    def handle(self):
+        if self._h is None:
+            raise ObjectDisposedError("TpExchange")
+        return self._h
+
+    def connect(self, handles: Sequence[bytes]) -> None:
+        if len(handles) != self.world or any(len(b) != N.TP_HANDLE_BYTES for b in handles):
+            raise ArgumentError("connect needs one 64-byte handle per rank, in rank order")
+        blob = (C.c_uint8 * (N.TP_HANDLE_BYTES * self.world)).from_buffer_copy(b"".join(handles))
+        _check(N.load().slc_tp_exchange_connect(self.handle, blob))
+
+    def connect_group(self, dist) -> None:
+        """Exchanges the handles over an initialised torch.distributed group and connects."""
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.handle_bytes)
+        self.connect(handles)
+
+    def matmul(self, op: MatMulOp, act: "SharedActivation", y_device_ptr: int, y_stride: int, stream: int = 0) -> None:
+        """y = sum over ranks of act . W^T (every rank calls it with its shard)."""
+        _check(N.load().slc_matmul_run_quantized_allreduce(op.handle, act.handle, self.handle, C.c_void_p(y_device_ptr),
+                                                           y_stride, C.c_void_p(stream) if stream else None))
+
+    def dispose(self) -> None:
+        if self._h is not None:
+            N.load().slc_tp_exchange_destroy(self._h)
+            self._h = None
+
+
 class _Pinned:
     """Page-locked host staging exposed as a numpy array."""
 

@@ -1,0 +1,176 @@
+"""The in-kernel all-reduce of a row-split MatMul (slc_tp_exchange, slc_matmul_run_quantized_allreduce).
+
+One GPU: a group of one rank runs the whole exchange machinery (stores into its own receive area, arrival words, wait,
+sum, counters, slot alternation) and must give the bits of the plain MatMul. Two GPUs (skipped with fewer): two
+processes, each with its K range of the weight, sum through each other's memory; the total must match the oracle on
+the unsharded weight, the NCCL all-reduce of the plain partial outputs, and be bit-identical on both ranks.
+"""
+import ctypes as C
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from helpers import FMT_OF, MAX_REL, max_rel_error, sl_oracle
+from sharplight_b200 import MatMulOp, NotSupportedError, InvalidOperationError, SharedActivation, TpExchange, synth, tp
+from sharplight_b200 import native as N
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(lib, device, host: np.ndarray):
+    p = C.c_void_p()
+    assert lib.slc_buffer_alloc(device.handle, host.nbytes, C.byref(p)) == N.OK
+    assert lib.slc_buffer_upload(device.handle, p, host.ctypes.data_as(C.c_void_p), host.nbytes) == N.OK
+    return p
+
+
+def _read(lib, device, p, shape):
+    out = np.empty(shape, np.float32)
+    assert lib.slc_device_sync(device.handle) == N.OK
+    assert lib.slc_buffer_download(device.handle, out.ctypes.data_as(C.c_void_p), p, out.nbytes) == N.OK
+    return out
+
+
+@pytest.mark.parametrize("type_name,n,k", [("Q4_K", 200, 2048), ("Q8_0", 100, 1568), ("Q4_0", 72, 512), ("Q6_K", 64, 1024)])
+def test_group_of_one_gives_the_plain_result(cuda_device, type_name, n, k):
+    lib = N.load()
+    w = cuda_device.upload_weight(type_name, (n, k), synth.weight_blocks(type_name, n, k, seed=31))
+    op = MatMulOp(cuda_device, w, 64)
+    act = SharedActivation(cuda_device, 64, k)
+    ex = TpExchange(cuda_device, 0, 1, 64, n)
+    try:
+        for call, rows in enumerate((1, 2, 4, 8, 17, 64, 3, 1)):      # both kernel families, both slots, several epochs
+            x = synth.activations(rows, k, seed=40 + call)
+            xd = _dev(lib, cuda_device, x)
+            y0 = _dev(lib, cuda_device, np.full((rows, n), np.nan, np.float32))
+            y1 = _dev(lib, cuda_device, np.full((rows, n), np.nan, np.float32))
+            act.quantize(xd.value, N.F32, rows, k)
+            act.matmul(op, y0.value, n)
+            ex.matmul(op, act, y1.value, n)
+            plain, summed = _read(lib, cuda_device, y0, (rows, n)), _read(lib, cuda_device, y1, (rows, n))
+            assert np.array_equal(plain.view(np.uint32), summed.view(np.uint32)), (rows, op.last_kernel())
+            for p in (xd, y0, y1):
+                lib.slc_buffer_free(cuda_device.handle, p)
+        assert cuda_device.last_status() == 0
+    finally:
+        ex.dispose(); act.dispose(); op.dispose(); w.dispose()
+
+
+def test_exchange_limits(cuda_device):
+    lib = N.load()
+    n, k = 64, 512
+    w = cuda_device.upload_weight("Q8_0", (n, k), synth.weight_blocks("Q8_0", n, k, seed=1))
+    op = MatMulOp(cuda_device, w, 128)
+    act = SharedActivation(cuda_device, 128, k)
+    xd = _dev(lib, cuda_device, synth.activations(128, k, seed=2))
+    yd = _dev(lib, cuda_device, np.zeros((128, n), np.float32))
+    ex = TpExchange(cuda_device, 0, 1, 64, n)
+    lonely = TpExchange(cuda_device, 0, 2, 8, n)          # a group of two that nobody connected
+    narrow = TpExchange(cuda_device, 0, 1, 64, 32)        # created for fewer output columns
+    try:
+        act.quantize(xd.value, N.F32, 128, k)
+        with pytest.raises(NotSupportedError):
+            ex.matmul(op, act, yd.value, n)               # 128 rows: beyond the exchange
+        act.quantize(xd.value, N.F32, 4, k)
+        with pytest.raises(InvalidOperationError):
+            lonely.matmul(op, act, yd.value, n)
+        with pytest.raises(ValueError):
+            narrow.matmul(op, act, yd.value, n)
+        with pytest.raises(ValueError):
+            TpExchange(cuda_device, 2, 2, 8, n)           # rank outside the group
+        with pytest.raises(ValueError):
+            TpExchange(cuda_device, 0, 1, 65, n)          # more rows than an exchange carries
+        assert cuda_device.last_status() == 0
+    finally:
+        for e in (ex, lonely, narrow):
+            e.dispose()
+        act.dispose(); op.dispose(); w.dispose()
+        lib.slc_buffer_free(cuda_device.handle, xd)
+        lib.slc_buffer_free(cuda_device.handle, yd)
+
+
+# ---- two GPUs ----------------------------------------------------------------------------------------------------
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _two_gpu_worker(rank, world, port, out):
+    import torch
+    import torch.distributed as dist
+    from sharplight_b200 import CudaExecutionProvider
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    provider = CudaExecutionProvider()
+    device = provider.open_device([d for d in provider.get_devices() if d.index == rank][0])
+    failures = []
+    try:
+        stream = torch.cuda.Stream()
+        torch.cuda.set_stream(stream)
+        sp = stream.cuda_stream
+        for type_name, n, k in (("Q4_K", 520, 4096), ("Q8_0", 136, 1024)):
+            fmt = FMT_OF[type_name]
+            blocks = synth.weight_blocks(type_name, n, k, seed=61)
+            sb, sn, sk, k0 = tp.row_shard(blocks, type_name, n, k, rank, world)
+            w = device.upload_weight(type_name, (sn, sk), sb)
+            op = MatMulOp(device, w, 64)
+            act = SharedActivation(device, 64, sk)
+            ex = TpExchange(device, rank, world, 64, n)
+            ex.connect_group(dist)
+            dist.barrier()
+            for call, rows in enumerate((1, 4, 8, 33, 64, 2)):
+                x_full = synth.activations(rows, k, seed=70 + call)
+                ref, _, _ = sl_oracle.matmul_intdot(fmt, blocks, n, k, x_full)
+                x = torch.from_numpy(np.ascontiguousarray(x_full[:, k0:k0 + sk])).cuda()
+                y_part = torch.full((rows, n), float("nan"), device="cuda")
+                y_sum = torch.full((rows, n), float("nan"), device="cuda")
+                torch.cuda.synchronize()
+                act.quantize(x.data_ptr(), N.F32, rows, sk, sp)
+                act.matmul(op, y_part.data_ptr(), n, sp)
+                ex.matmul(op, act, y_sum.data_ptr(), n, sp)
+                stream.synchronize()
+                dist.all_reduce(y_part)                           # the collective-library way, for comparison
+                mine = y_sum.cpu().numpy()
+                if max_rel_error(mine, ref) > MAX_REL:
+                    failures.append(f"{type_name} rows={rows}: differs from the oracle by {max_rel_error(mine, ref):.2e}")
+                if max_rel_error(mine, y_part.cpu().numpy()) > 1e-5:
+                    failures.append(f"{type_name} rows={rows}: differs from the NCCL all-reduce")
+                both = [torch.empty_like(y_sum) for _ in range(world)]
+                dist.all_gather(both, y_sum)
+                if not all(torch.equal(both[0], b) for b in both[1:]):
+                    failures.append(f"{type_name} rows={rows}: the ranks hold different sums")
+            if device.last_status() != 0:
+                failures.append(f"{type_name}: device status {device.last_status()}")
+            dist.barrier()
+            torch.cuda.synchronize()
+            ex.dispose(); act.dispose(); op.dispose(); w.dispose()
+        out.put((rank, failures))
+    except Exception as exc:  # the parent reports it
+        out.put((rank, [f"exception: {exc!r}"]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpus_sum_through_peer_memory():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_two_gpu_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(60)
+    for rank, failures in results:
+        assert not failures, (rank, failures)
