@@ -211,8 +211,14 @@ class TpStack:
     count up to max_rows: decode batches and the prefill run on the same stack)."""
 
     def __init__(self, device, torch, dist, N, synth, rank, world, max_rows, layers, arch, type_name="Q4_K"):
-        from sharplight_b200 import MatMulOp, SharedActivation, tp
+        from sharplight_b200 import MatMulOp, SharedActivation, TpExchange, tp
         self.torch, self.dist, self.N, self.world = torch, dist, N, world
+        # the receive area of the in-kernel all-reduce (one serves o and down of every layer: same output width)
+        self.exchange = None
+        if world > 1:
+            self.exchange = TpExchange(device, rank, world, N.TP_MAX_ROWS, arch["hidden"])
+            self.exchange.connect_group(dist)
+            dist.barrier()
         rows = max_rows
         self.layers, self.arch = layers, arch
         # q / k / v and gate / up are stacked along N (one MatMul each), as a runtime stores them
@@ -240,9 +246,12 @@ class TpStack:
         self.act = {key: SharedActivation(device, rows, v.shape[1]) for key, v in self.x.items()}
         self.launches_per_step = 0
 
-    def step(self, rows, sp):
+    def step(self, rows, sp, fused=True):
+        """fused: row-split MatMuls of up to 64 rows sum over the ranks inside their kernel (peer stores over NVLink);
+        otherwise, and for the prefill, the partial outputs go through an NCCL all-reduce."""
         N = self.N
         launches = 0
+        in_kernel = fused and self.exchange is not None and rows <= N.TP_MAX_ROWS
         for layer_ops in self.ops:
             for key in ("x_attn", "x_o", "x_ffn", "x_down"):
                 x = self.x[key]
@@ -252,13 +261,20 @@ class TpStack:
                     if inp != key:
                         continue
                     y = self.y[name]
-                    self.act[key].matmul(layer_ops[name], y.data_ptr(), y.shape[1], sp)
+                    if split == "row" and in_kernel:
+                        self.exchange.matmul(layer_ops[name], self.act[key], y.data_ptr(), y.shape[1], sp)
+                    else:
+                        self.act[key].matmul(layer_ops[name], y.data_ptr(), y.shape[1], sp)
+                        if split == "row" and self.world > 1:
+                            self.dist.all_reduce(y[:rows])
                     launches += layer_ops[name].last_kernel()[1]
-                    if split == "row" and self.world > 1:
-                        self.dist.all_reduce(y[:rows])
         self.launches_per_step = launches
 
     def dispose(self):
+        if self.exchange is not None:
+            self.torch.cuda.synchronize()
+            self.dist.barrier()
+            self.exchange.dispose()
         for layer_ops in self.ops:
             for op in layer_ops.values():
                 op.dispose()
@@ -313,9 +329,17 @@ def run_tp(args, torch, dist, device, N, synth, stream, world, rank, local):
         steps = max(3, min(args.steps, 20 if rows <= 64 else 5))
         ms = time_graphed(torch, dist, world, stream, lambda sp, r=rows: stack.step(r, sp), steps, 3,
                           use_graph=not args.no_graph)
+        in_kernel = world > 1 and rows <= N.TP_MAX_ROWS
         out[rows] = {"ms_per_step": ms, "weight_gbs": stack.total_weight_bytes / (ms * 1e-3) / 1e9,
                      "tops": flops_per_row * rows / (ms * 1e-3) / 1e12, "steps": steps,
-                     "launches_per_step": stack.launches_per_step, "allreduces_per_step": 2 * layers if world > 1 else 0}
+                     "launches_per_step": stack.launches_per_step,
+                     "allreduce": "none" if world == 1 else "in the MatMul kernel (peer stores)" if in_kernel else "NCCL",
+                     "allreduces_per_step": 2 * layers if world > 1 else 0}
+        if in_kernel:
+            # the same step with the collective library doing the sum, for comparison
+            out[rows]["ms_per_step_nccl"] = time_graphed(torch, dist, world, stream,
+                                                         lambda sp, r=rows: stack.step(r, sp, fused=False), steps, 3,
+                                                         use_graph=not args.no_graph)
     stack.dispose()
     torch.cuda.synchronize()
     return {"workload": f"configs[4]: Llama-3-70B-shaped stack, {layers} layers, Q4_K, tensor parallel x{world}",
@@ -356,7 +380,8 @@ def run_ours(args):
                     "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                     "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
                     "config": {"workload": tpr["workload"] + f", decode M={rows}: column-split q/k/v/gate/up, row-split "
-                                           "o/down + NCCL all-reduce of f32 partials",
+                                           "o/down, f32 partial outputs summed inside the MatMul kernel over NVLink peer memory "
+                                           "(NCCL all-reduce for the 2048-row prefill)",
                                "l2": f"inputs larger than L2: {tpr['weight_bytes_per_step'] / world / 1e9:.1f} GB of weights per GPU per step",
                                "launch": "host launches" if args.no_graph else "CUDA graph replay of the step"},
                     "gpu_launches": main["launches_per_step"] * max(3, min(args.steps, 20)),

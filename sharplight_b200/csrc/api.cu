@@ -586,7 +586,9 @@ slc_result slc_tp_exchange_create(slc_device *d, int32_t rank, int32_t world, in
     const int n_stride = (int)round_up((size_t)n, 64), groups = n_stride / 16;
     const size_t recv_b = round_up((size_t)2 * world * max_rows * n_stride * 4, 256);
     const size_t flag_b = round_up((size_t)2 * world * groups * 4, 256);
-    x->flags_off = recv_b; x->ctl_off = recv_b + flag_b; x->bytes = recv_b + flag_b + 256;
+    const size_t ll_b = round_up((size_t)2 * world * SLC_LL_ROWS * n_stride * 8, 256);
+    x->flags_off = recv_b; x->ll_off = recv_b + flag_b; x->ctl_off = recv_b + flag_b + ll_b;
+    x->bytes = x->ctl_off + 256;
     cudaError_t e = cudaMalloc(&x->base, x->bytes);
     if (e == cudaSuccess) e = cudaMemset(x->base, 0, x->bytes);
     cudaIpcMemHandle_t h;
@@ -608,6 +610,7 @@ slc_result slc_tp_exchange_create(slc_device *d, int32_t rank, int32_t world, in
     if (x->connected) {
         v.recv[0] = reinterpret_cast<float *>(x->base);
         v.flags[0] = reinterpret_cast<int *>(x->base + x->flags_off);
+        v.ll[0] = reinterpret_cast<unsigned long long *>(x->base + x->ll_off);
     }
     *out = x;
     return SLC_OK;
@@ -633,6 +636,7 @@ slc_result slc_tp_exchange_connect(slc_tp_exchange *x, const uint8_t *handles)
     for (int p = 0; p < x->world; p++) {
         x->view.recv[p] = reinterpret_cast<float *>(x->peer[p]);
         x->view.flags[p] = reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(x->peer[p]) + x->flags_off);
+        x->view.ll[p] = reinterpret_cast<unsigned long long *>(reinterpret_cast<uint8_t *>(x->peer[p]) + x->ll_off);
     }
     x->connected = true;
     return SLC_OK;

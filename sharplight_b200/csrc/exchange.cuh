@@ -15,6 +15,11 @@
 // completes exchange e only after it has seen every peer's arrival for e, which the peer published after its own
 // exchange e - 1 was over: when exchange e + 1 starts storing into a slot, nobody is still reading exchange e - 1 there.
 //
+// Launches of up to SLC_LL_ROWS rows (where latency is everything) use a lighter protocol in the same spirit, without fences or arrival words:
+// every partial value travels as one 8-byte word {value, exchange number + 1}, written with a single store, which
+// arrives whole or not at all; the receiving thread polls the word itself until it carries the current number. One
+// NVLink crossing, no round trip. The same two-slot rule applies.
+//
 // Nothing here uses multicast objects or multimem: a rank that dies leaves its peers with a wait that runs out
 // (status word, SLC_ERR_TIMEOUT), not with a fault.
 #pragma once
@@ -24,11 +29,13 @@
 namespace slc {
 
 constexpr int SLC_MAX_RANKS = 8;
+constexpr int SLC_LL_ROWS = 16;  // launches of up to this many rows use the word protocol
 
 struct Exchange
 {
     float *recv[SLC_MAX_RANKS];   // rank p's receive area as this process sees it: [2][world][max_rows][n_stride]
     int *flags[SLC_MAX_RANKS];    // rank p's arrival words: [2][world][groups]
+    unsigned long long *ll[SLC_MAX_RANKS];   // rank p's {value, tag} words: [2][world][SLC_LL_ROWS][n_stride]
     int *epoch;                   // this rank's exchange counter
     int *done;                    // CTAs of the running launch that are through
     int world, rank;              // world == 0: no exchange, the kernel writes y directly
@@ -50,6 +57,46 @@ __device__ __forceinline__ unsigned long long ex_now()
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
+}
+
+__device__ __forceinline__ long long ex_ll_index(const Exchange &x, int slot, int src, int m, int col)
+{
+    return (((long long)slot * x.world + src) * SLC_LL_ROWS + m) * x.n_stride + col;
+}
+
+// The word protocol for one value owned by the calling thread, in two halves so that a thread with several values
+// sends them all before it waits for any: ex_ll_send stores {v, tag} into every peer's area; ex_ll_collect waits for
+// the peers' words for the same value and returns the sum in rank order (ok turns false when a word never came).
+__device__ __forceinline__ void ex_ll_send(const Exchange &x, int slot, int epoch, int m, int col, float v)
+{
+    const unsigned tag = (unsigned)epoch + 1u;
+    const unsigned long long word = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+    const long long at = ex_ll_index(x, slot, x.rank, m, col);
+    for (int p = 0; p < x.world; p++) {
+        if (p != x.rank) asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(x.ll[p] + at), "l"(word) : "memory");
+    }
+}
+
+__device__ __forceinline__ float ex_ll_collect(const Exchange &x, int slot, int epoch, int m, int col, float v, bool &ok)
+{
+    const unsigned tag = (unsigned)epoch + 1u;
+    const unsigned long long t0 = ex_now(), limit = (unsigned long long)x.wait_ms * 1000000ull;
+    float s = 0.0f;
+    for (int p = 0; p < x.world; p++) {
+        float val = v;
+        if (p != x.rank) {
+            const unsigned long long *src = x.ll[x.rank] + ex_ll_index(x, slot, p, m, col);
+            unsigned long long got;
+            for (;;) {
+                asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(got) : "l"(src) : "memory");
+                if ((unsigned)(got >> 32) == tag) break;
+                if (ex_now() - t0 > limit) { ok = false; break; }
+            }
+            val = __uint_as_float((unsigned)got);
+        }
+        s = p == 0 ? val : s + val;
+    }
+    return s;
 }
 
 // Steps 2 and 3. Every thread of the CTA calls it after its stores of step 1; returns false when a peer never arrived.

@@ -57,7 +57,7 @@ struct slc_tp_exchange
     int rank = 0, world = 0;
     long long max_rows = 0, n = 0;
     uint8_t *base = nullptr;              // this rank's receive area, arrival words and counters (one allocation)
-    size_t bytes = 0, flags_off = 0, ctl_off = 0;
+    size_t bytes = 0, flags_off = 0, ll_off = 0, ctl_off = 0;
     void *peer[slc::SLC_MAX_RANKS] = {};  // the peers' allocations as mapped here (own entry = base)
     bool connected = false;
     slc::Exchange view{};

@@ -506,13 +506,16 @@ matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__
         if (ex.world == 0) {
             if (own && row < w.n) y[(long long)(row0 + m) * y_stride + row] = v;
         } else {
-            // row-split MatMul of a tensor-parallel group: v is this rank's partial value (exchange.cuh)
+            // row-split MatMul of a tensor-parallel group: v is this rank's partial value; every thread trades its own
+            // value with the peers as {value, tag} words (exchange.cuh)
             const int epoch = ex_epoch(ex), slot = epoch & 1;
             if (own) {
-                for (int p = 0; p < ex.world; p++) ex.recv[p][ex_index(ex, slot, ex.rank, m, row)] = v;
+                bool ok = true;
+                ex_ll_send(ex, slot, epoch, m, row, v);
+                const float total = ex_ll_collect(ex, slot, epoch, m, row, v, ok);
+                if (!ok) atomicExch(status, -7);
+                if (row < w.n) y[(long long)(row0 + m) * y_stride + row] = total;
             }
-            if (!ex_publish_and_wait(ex, slot, epoch, blockIdx.x) && threadIdx.x == 0) atomicExch(status, -7);
-            if (own && row < w.n) y[(long long)(row0 + m) * y_stride + row] = ex_sum(ex, slot, m, row);
             ex_finish(ex, epoch);
         }
     }
@@ -580,7 +583,7 @@ cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int r
     if (exchange) {
         ex = *exchange;
         // a launch that exchanges waits for its predecessor before anything else, and needs room for its tile
-        if (early || rows > ex.max_rows || w.n_pad > ex.n_stride || w.n_pad / 16 > ex.groups) return cudaErrorInvalidValue;
+        if (early || rows > SLC_LL_ROWS || w.n_pad > ex.n_stride) return cudaErrorInvalidValue;
     }
     switch (w.fmt) {
     case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);

@@ -409,21 +409,35 @@ skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__
         __syncthreads();
         const int epoch = ex_epoch(ex), slot = epoch & 1;
         const int col0 = blockIdx.x * 64;
-        for (int idx = threadIdx.x; idx < rows * 16; idx += SK_WARPS * 32) {
-            const int m = idx >> 4, c4 = (idx & 15) * 4;
-            const float4 v = *reinterpret_cast<const float4 *>(tile + m * 64 + c4);
-            for (int p = 0; p < ex.world; p++) {
-                *reinterpret_cast<float4 *>(ex.recv[p] + ex_index(ex, slot, ex.rank, m, col0 + c4)) = v;
+        if (NT * 8 <= SLC_LL_ROWS) {
+            // few rows: every value travels as one {value, tag} word and is awaited by the thread that owns it
+            for (int idx = threadIdx.x; idx < rows * 64; idx += SK_WARPS * 32) {
+                ex_ll_send(ex, slot, epoch, idx >> 6, col0 + (idx & 63), tile[idx]);
             }
-        }
-        if (!ex_publish_and_wait(ex, slot, epoch, blockIdx.x) && threadIdx.x == 0) atomicExch(status, -7);
-        for (int idx = threadIdx.x; idx < rows * 16; idx += SK_WARPS * 32) {
-            const int m = idx >> 4, c4 = (idx & 15) * 4;
-            const float4 sum = ex_sum4(ex, slot, m, col0 + c4);
-            const float sv[4] = { sum.x, sum.y, sum.z, sum.w };
+            bool ok = true;
+            for (int idx = threadIdx.x; idx < rows * 64; idx += SK_WARPS * 32) {
+                const int m = idx >> 6, col = col0 + (idx & 63);
+                const float total = ex_ll_collect(ex, slot, epoch, m, col, tile[idx], ok);
+                if (col < w.n) y[(long long)(row0 + m) * y_stride + col] = total;
+            }
+            if (!ok) atomicExch(status, -7);
+        } else {
+            for (int idx = threadIdx.x; idx < rows * 16; idx += SK_WARPS * 32) {
+                const int m = idx >> 4, c4 = (idx & 15) * 4;
+                const float4 v = *reinterpret_cast<const float4 *>(tile + m * 64 + c4);
+                for (int p = 0; p < ex.world; p++) {
+                    *reinterpret_cast<float4 *>(ex.recv[p] + ex_index(ex, slot, ex.rank, m, col0 + c4)) = v;
+                }
+            }
+            if (!ex_publish_and_wait(ex, slot, epoch, blockIdx.x) && threadIdx.x == 0) atomicExch(status, -7);
+            for (int idx = threadIdx.x; idx < rows * 16; idx += SK_WARPS * 32) {
+                const int m = idx >> 4, c4 = (idx & 15) * 4;
+                const float4 sum = ex_sum4(ex, slot, m, col0 + c4);
+                const float sv[4] = { sum.x, sum.y, sum.z, sum.w };
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                if (col0 + c4 + j < w.n) y[(long long)(row0 + m) * y_stride + col0 + c4 + j] = sv[j];
+                for (int j = 0; j < 4; j++) {
+                    if (col0 + c4 + j < w.n) y[(long long)(row0 + m) * y_stride + col0 + c4 + j] = sv[j];
+                }
             }
         }
         ex_finish(ex, epoch);
