@@ -34,6 +34,9 @@ import numpy as np  # noqa: E402
 
 TYPE, N_ROWS_W, K_COLS = "Q4_K", 14336, 4096
 COPIES = 32
+# dram__bytes_read.sum + dram__bytes_write.sum of one matvec_kernel launch on this workload at M = 1, from the ncu capture
+# summarised in profiles/matvec_q4k_m1_14336x4096.md (the algorithmic bytes are 33 092 608)
+CONFIG2_M1_DRAM_BYTES = 33062656
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -544,7 +547,8 @@ def run_ours(args):
                            "kernel_family": {1: "mmvq (dp4a)", 2: "skinny (int8 mma)", 3: "mmq (tcgen05)"}[kernel_family],
                            "launch": "host launches" if args.no_graph else "CUDA graph replay of the step"},
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                             "traffic": None, "peak_source": peak_kind, "kernel_us": sec_per_launch * 1e6,
+                             "traffic": CONFIG2_M1_DRAM_BYTES if (rows, n, k, TYPE) == (1, 14336, 4096, "Q4_K") else None,
+                             "peak_source": peak_kind, "kernel_us": sec_per_launch * 1e6,
                              "algorithmic_bytes_per_launch": algo_bytes, "frac_of_nominal_8000": achieved / 8000.0},
                 "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": rows * k * 4,
                         "d2h_bytes_per_step": COPIES * rows * n * 4, "ms_per_step": ms_e2e},
