@@ -4,13 +4,13 @@
 // (src/Sharplight.Shaders/Kernels/mmq.slang:224-233 of the Sharplight tree: acc += float(C) * (d_x * d_w) - s_x * m_w).
 //
 // One CTA computes a 128 (weight rows) x 128 (tokens) tile. Roles, warp-specialised:
-//   warps 0-7   epilogue: read each block's int32 tile from tensor memory (tcgen05.ld), scale, accumulate in f32
-//               registers; warp w owns TMEM lanes 32*(w%4).. and columns 64*(w/4)..
-//   warps 8-11  producers: stream the weight records (layout.cuh) with 128-bit loads, expand 4-bit codes to int8 in
-//               registers and store them in the K-major core-matrix layout the tensor core reads; lane 0 of warp 8 also
-//               starts the bulk async copies (TMA engine) of the activation tile, which the quantizer already wrote in
-//               that layout, and of the activation scales
-//   warp 12     allocates tensor memory; its lane 0 issues tcgen05.mma kind::i8 (M=128, N=128, K=32: one quantization
+//   warps 0-15  epilogue, four per scheduler: read each block's tile from tensor memory (tcgen05.ld, 16 columns at a
+//               time), scale, accumulate in f32 registers; warp w owns TMEM lanes 32*(w%4).. and columns 32*(w/4)..
+//   warps 16-19 producers: stream the weight records (layout.cuh) with 128-bit loads, expand 4-bit codes to int8 in
+//               registers and store them in the K-major core-matrix layout the tensor core reads; lane 0 of warp 16
+//               also starts the bulk async copies (TMA engine) of the activation tile, which the quantizer already
+//               wrote in that layout, and of the activation scales
+//   warp 20     allocates tensor memory; its lane 0 issues tcgen05.mma kind::i8 (M=128, N=128, K=32: one quantization
 //               block per instruction, each into its own accumulator buffer: per-block scales forbid accumulating
 //               across blocks in int32) and commits to mbarriers
 // Pipelines: 3 shared-memory stages of 256 K-values (8 blocks), 4 TMEM accumulator buffers of 128 columns; the
@@ -27,8 +27,8 @@ constexpr int MQ_TILE_T = 128;     // tokens per CTA (UMMA N)
 __host__ __device__ constexpr int mq_stages(int fmt) { return fmt == FMT_Q4_K ? 2 : 3; }
 constexpr int MQ_MAX_STAGES = 3;
 constexpr int MQ_DBUF = 4;
-constexpr int MQ_EPI_WARPS = 8, MQ_PROD_WARPS = 4;
-constexpr int MQ_THREADS = 512;   // warps 0-7 epilogue, 8-11 producers, 12 MMA issuer, 13-15 idle (they fill the warpgroup)
+constexpr int MQ_EPI_WARPS = 16, MQ_PROD_WARPS = 4;
+constexpr int MQ_THREADS = 768;   // warps 0-15 epilogue, 16-19 producers, 20 MMA issuer, 21-23 idle (they fill the warpgroup)
 // a wait suspends in hardware for up to ~20 us per attempt (the hint below) instead of spinning on issue slots the
 // epilogue needs; 100000 attempts bound it at about two seconds
 constexpr unsigned MQ_WAIT_LIMIT = 100000;
@@ -99,24 +99,26 @@ __device__ __forceinline__ void mq_umma_commit(uint64_t *bar)
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mq_smem(bar)) : "memory");
 }
 
-__device__ __forceinline__ void mq_tmem_ld32(unsigned taddr, int (&r)[32])
+// The 32-bit results are declared as f32 registers: the values are used as floats (biased accumulators), and typing them
+// so from the start leaves no integer-to-float register moves behind.
+__device__ __forceinline__ void mq_tmem_ld32(unsigned taddr, float (&r)[32])
 {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
                  "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]),
+                   "=f"(r[8]), "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15]),
+                   "=f"(r[16]), "=f"(r[17]), "=f"(r[18]), "=f"(r[19]), "=f"(r[20]), "=f"(r[21]), "=f"(r[22]), "=f"(r[23]),
+                   "=f"(r[24]), "=f"(r[25]), "=f"(r[26]), "=f"(r[27]), "=f"(r[28]), "=f"(r[29]), "=f"(r[30]), "=f"(r[31])
                  : "r"(taddr) : "memory");
 }
 
-__device__ __forceinline__ void mq_tmem_ld16(unsigned taddr, int (&r)[16])
+__device__ __forceinline__ void mq_tmem_ld16(unsigned taddr, float (&r)[16])
 {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]),
+                   "=f"(r[8]), "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15])
                  : "r"(taddr) : "memory");
 }
 
@@ -126,11 +128,26 @@ __device__ __forceinline__ void mq_tmem_ld16(unsigned taddr, int (&r)[16])
 constexpr int MQ_BIAS = 0x4B400000;
 constexpr float MQ_BIAS_F = 12582912.0f;
 
-__device__ __forceinline__ void mq_tmem_st16_const(unsigned taddr, int v)
+// Sixteen registers that hold the bias pattern for the whole kernel. tcgen05.st takes sixteen distinct registers: fed
+// from one value, the compiler copies it into sixteen registers before every store (one move per accumulator column
+// per block, as many instructions as half the scaling itself); an array that is opaque to it stays in place.
+struct MqBias16
+{
+    int v[16];
+    __device__ __forceinline__ void init()
+    {
+#pragma unroll
+        for (int j = 0; j < 16; j++) asm volatile("mov.b32 %0, %1;" : "=r"(v[j]) : "r"(MQ_BIAS));
+    }
+};
+
+__device__ __forceinline__ void mq_tmem_st16(unsigned taddr, const MqBias16 &b)
 {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-                 "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
-                 ::"r"(taddr), "r"(v) : "memory");
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 ::"r"(taddr), "r"(b.v[0]), "r"(b.v[1]), "r"(b.v[2]), "r"(b.v[3]), "r"(b.v[4]), "r"(b.v[5]), "r"(b.v[6]),
+                   "r"(b.v[7]), "r"(b.v[8]), "r"(b.v[9]), "r"(b.v[10]), "r"(b.v[11]), "r"(b.v[12]), "r"(b.v[13]),
+                   "r"(b.v[14]), "r"(b.v[15]) : "memory");
 }
 
 __device__ __forceinline__ void mq_tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -203,7 +220,8 @@ __device__ __forceinline__ void mq_store(const MqRegs<FMT> &rr, int rgl, int lan
     const int g = lane >> 2, t = lane & 3;
     uint8_t *row_lo = a_tile + (2 * rgl) * 2048 + g * 16, *row_hi = row_lo + 2048;   // rows g and g + 8
     const uint4 s0 = rr.s0, s1 = rr.s1;
-    float *dw_lo = dws + (rgl * 16 + g) * 8, *dw_hi = dw_lo + 64;
+    // scale tables are [block][row of the tile]: the epilogue's lanes (one row each) read them without bank conflicts
+    float *dw_lo = dws + rgl * 16 + g, *dw_hi = dw_lo + 8;
 
     if constexpr (FMT == FMT_Q8_0) {
 #pragma unroll
@@ -245,10 +263,12 @@ __device__ __forceinline__ void mq_store(const MqRegs<FMT> &rr, int rgl, int lan
     if constexpr (FMT == FMT_Q8_0 || FMT == FMT_Q4_0) {
         const unsigned w0 = t == 0 ? s0.x : t == 1 ? s0.y : t == 2 ? s0.z : s0.w;
         const unsigned w1 = t == 0 ? s1.x : t == 1 ? s1.y : t == 2 ? s1.z : s1.w;
-        *reinterpret_cast<float2 *>(dw_lo + 2 * t) = make_float2(mq_h2f(w0 & 0xffffu), mq_h2f(w0 >> 16));
-        *reinterpret_cast<float2 *>(dw_hi + 2 * t) = make_float2(mq_h2f(w1 & 0xffffu), mq_h2f(w1 >> 16));
+        dw_lo[(2 * t) * MQ_TILE_N] = mq_h2f(w0 & 0xffffu);
+        dw_lo[(2 * t + 1) * MQ_TILE_N] = mq_h2f(w0 >> 16);
+        dw_hi[(2 * t) * MQ_TILE_N] = mq_h2f(w1 & 0xffffu);
+        dw_hi[(2 * t + 1) * MQ_TILE_N] = mq_h2f(w1 >> 16);
     } else {
-        float *dm_lo = dms + (rgl * 16 + g) * 8, *dm_hi = dm_lo + 64;
+        float *dm_lo = dms + rgl * 16 + g, *dm_hi = dm_lo + 8;
 #pragma unroll
         for (int r = 0; r < 2; r++) {
             const uint4 h = r ? s1 : s0;
@@ -260,8 +280,10 @@ __device__ __forceinline__ void mq_store(const MqRegs<FMT> &rr, int rgl, int lan
             const int sh = 16 * (t & 1);
             const float2 sc = make_float2(d * (float)((scw >> sh) & 0xffu), d * (float)((scw >> (sh + 8)) & 0xffu));
             const float2 mn = make_float2(dmin * (float)((mnw >> sh) & 0xffu), dmin * (float)((mnw >> (sh + 8)) & 0xffu));
-            *reinterpret_cast<float2 *>((r ? dw_hi : dw_lo) + 2 * t) = sc;
-            *reinterpret_cast<float2 *>((r ? dm_hi : dm_lo) + 2 * t) = mn;
+            (r ? dw_hi : dw_lo)[(2 * t) * MQ_TILE_N] = sc.x;
+            (r ? dw_hi : dw_lo)[(2 * t + 1) * MQ_TILE_N] = sc.y;
+            (r ? dm_hi : dm_lo)[(2 * t) * MQ_TILE_N] = mn.x;
+            (r ? dm_hi : dm_lo)[(2 * t + 1) * MQ_TILE_N] = mn.y;
         }
     }
 }
@@ -320,34 +342,34 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
     const long long mq_kernel_t0 = clock64();
 #endif
 
-    // Register budget: launched at 128 per thread; the two epilogue warpgroups take more and the other two give back
-    // (256 x 168 + 256 x 88 = 256 x 152 + 256 x 104 = 65536). Q8_0's producers hold the larger records in registers.
-    if constexpr (FMT == FMT_Q8_0) {
-        if (warp < MQ_EPI_WARPS) asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
-        else asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
-    } else {
-        if (warp < MQ_EPI_WARPS) asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
-        else asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
-    }
+    // Register budget: 80 per thread at launch (768 threads). The MMA issuer's warpgroup gives back all but 24; the
+    // epilogue takes 88 and the producers (two weight records in registers) 104: 4 x 88 + 104 + 24 = 6 x 80.
+    if (warp >= MQ_EPI_WARPS + MQ_PROD_WARPS) asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
+    else if (warp >= MQ_EPI_WARPS) asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+    else asm volatile("setmaxnreg.inc.sync.aligned.u32 88;");
 
     if (warp < MQ_EPI_WARPS) {
-        // ===== epilogue =====
-        const int q4 = warp & 3, half = warp >> 2;
+        // ===== epilogue: 16 warps, four per scheduler; warp = (TMEM lane quarter, 32-column slice) =====
+        // A warp requests its 32 columns of a block, waits, scales, and goes on to the next block; the other three
+        // warps of its scheduler cover the tensor-memory and shared-memory latencies, so nothing is carried in
+        // registers from one block to the next.
+        const int q4 = warp & 3, cs = warp >> 2;
         const int r = q4 * 32 + lane;                 // weight row inside the tile = TMEM lane
-        const int c0 = half * 64;                     // first token column of this warp
+        const int c0 = cs * 32;                       // first token column of this warp
         const unsigned tlane = tmem + ((unsigned)(q4 * 32) << 16) + (unsigned)c0;
-        float acc[64];
+        float acc[32];
 #pragma unroll
-        for (int j = 0; j < 64; j++) acc[j] = 0.0f;
+        for (int j = 0; j < 32; j++) acc[j] = 0.0f;
         bool alive = true;
         const int total = nst * 8;
-        int sa[32], sb[32];
+        MqBias16 bias;
+        bias.init();
 
         // arm this warp's part of every accumulator buffer with the bias, then open the buffers for the MMA issuer
 #pragma unroll
         for (int buf = 0; buf < MQ_DBUF; buf++) {
-#pragma unroll
-            for (int q = 0; q < 4; q++) mq_tmem_st16_const(tlane + (unsigned)(buf * MQ_TILE_T + q * 16), MQ_BIAS);
+            mq_tmem_st16(tlane + (unsigned)(buf * MQ_TILE_T), bias);
+            mq_tmem_st16(tlane + (unsigned)(buf * MQ_TILE_T + 16), bias);
         }
         mq_tmem_wait_st();
         mq_tc_fence_before();
@@ -357,17 +379,6 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
             for (int buf = 0; buf < MQ_DBUF; buf++) mq_bar_arrive(&sh.d_empty[buf]);
         }
 
-        // Tensor-memory loads take a few hundred cycles: both halves of a block are requested together, and the
-        // next block's halves are requested as soon as the registers of the current ones have been consumed.
-        if (total > 0) {
-            if (mq_bar_wait(&sh.d_full[0], 0)) {
-                mq_tc_fence_after();
-                mq_tmem_ld32(tlane, sa);
-                mq_tmem_ld32(tlane + 32, sb);
-            } else {
-                alive = false;
-            }
-        }
         for (int i = 0; i < total && alive; i++) {
             const int it = i >> 3, b = i & 7, s = it % MQ_STAGES, buf = i % MQ_DBUF;
             if (b == 0) {
@@ -377,27 +388,44 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
                 if (!mq_bar_wait(&sh.a_full[s], spar) || !mq_bar_wait(&sh.b_full[s], spar)) { alive = false; break; }
                 if (warp == 0) MQ_T1(1);
             }
+            const unsigned tcol = tlane + (unsigned)(buf * MQ_TILE_T);
+            {
+                MQ_T0();
+                if (!mq_bar_wait(&sh.d_full[buf], (unsigned)(i / MQ_DBUF) & 1u)) { alive = false; break; }
+                if (warp == 0) MQ_T1(0);
+            }
+            mq_tc_fence_after();
             const float *dxs = stage_dx(s) + b * MQ_TILE_T + c0, *sxs = stage_sx(s) + b * MQ_TILE_T + c0;
-            const float dwv = stage_dw(s)[r * 8 + b];
-            const float dmv = HAS_MIN ? -stage_dm(s)[r * 8 + b] : 0.0f;
+            const float dwv = stage_dw(s)[b * MQ_TILE_N + r];
+            const float dmv = HAS_MIN ? -stage_dm(s)[b * MQ_TILE_N + r] : 0.0f;
             // (biased - 12582912) * d_w as one FMA: the constant -12582912 * d_w is exact when d_w comes from an f16
             const float cw = -MQ_BIAS_F * dwv;
-            const unsigned tcol = tlane + (unsigned)(buf * MQ_TILE_T);
-
-            auto scale32 = [&](const int (&sv)[32], int q) {
+            // the slice in two halves of 16 columns: 16 result registers live at a time
 #pragma unroll
-                for (int j4 = 0; j4 < 8; j4++) {
-                    const float4 dx = *reinterpret_cast<const float4 *>(dxs + q * 32 + j4 * 4);
+            for (int h = 0; h < 2; h++) {
+                float sv[16];
+                mq_tmem_ld16(tcol + (unsigned)(h * 16), sv);
+                {
+                    MQ_T0();
+                    mq_tmem_wait_ld();
+                    if (warp == 0) MQ_T1(2);
+                }
+                // these columns have been read: re-arm them with the bias (asynchronously)
+                mq_tmem_st16(tcol + (unsigned)(h * 16), bias);
+                MQ_T0();
+#pragma unroll
+                for (int j4 = 0; j4 < 4; j4++) {
+                    const float4 dx = *reinterpret_cast<const float4 *>(dxs + h * 16 + j4 * 4);
                     const float dxv[4] = { dx.x, dx.y, dx.z, dx.w };
                     float sxv[4] = { 0.f, 0.f, 0.f, 0.f };
                     if (HAS_MIN) {
-                        const float4 sx = *reinterpret_cast<const float4 *>(sxs + q * 32 + j4 * 4);
+                        const float4 sx = *reinterpret_cast<const float4 *>(sxs + h * 16 + j4 * 4);
                         sxv[0] = sx.x; sxv[1] = sx.y; sxv[2] = sx.z; sxv[3] = sx.w;
                     }
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
-                        const float f = __int_as_float(sv[j4 * 4 + e]);
-                        float v = acc[q * 32 + j4 * 4 + e];
+                        const float f = sv[j4 * 4 + e];
+                        float v = acc[h * 16 + j4 * 4 + e];
                         if (HAS_MIN) {
                             // d_w = d * sc is a rounded product: keep the subtraction exact, then scale
                             v = fmaf((f - MQ_BIAS_F) * dwv, dxv[e], v);
@@ -405,44 +433,21 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
                         } else {
                             v = fmaf(fmaf(f, dwv, cw), dxv[e], v);
                         }
-                        acc[q * 32 + j4 * 4 + e] = v;
+                        acc[h * 16 + j4 * 4 + e] = v;
                     }
                 }
+                if (warp == 0) MQ_T1(3);
                 if (DUMP) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int tok = t0 + c0 + q * 32 + j, row = n0 + r;
+                    for (int j = 0; j < 16; j++) {
+                        const int tok = t0 + c0 + h * 16 + j, row = n0 + r;
                         if (tok < a.rows && row < w.n && i * 32 < w.k) {
                             const int cexp = FMT == FMT_Q8_0 ? 128 : FMT == FMT_Q4_0 ? 8 : 0;
                             const int add = cexp ? cexp * __ldg(&a.isum[(long long)tok * (a.k_pad >> 5) + i]) : 0;
-                            dump[((long long)tok * w.n + row) * (w.k >> 5) + i] = sv[j] - MQ_BIAS + add;
+                            dump[((long long)tok * w.n + row) * (w.k >> 5) + i] = __float_as_int(sv[j]) - MQ_BIAS + add;
                         }
                     }
                 }
-            };
-
-            {
-                MQ_T0();
-                mq_tmem_wait_ld();   // both halves of block i are in registers
-                if (warp == 0) MQ_T1(2);
-            }
-            // every column of this buffer has been read: re-arm it with the bias (asynchronously)
-#pragma unroll
-            for (int q = 0; q < 4; q++) mq_tmem_st16_const(tcol + (unsigned)(q * 16), MQ_BIAS);
-            {
-                MQ_T0();
-                scale32(sa, 0);
-                if (warp == 0) MQ_T1(3);
-            }
-            bool next_ready = false;
-            if (i + 1 < total) {
-                const int nb = (i + 1) % MQ_DBUF;
-                MQ_T0();
-                if (!mq_bar_wait(&sh.d_full[nb], (unsigned)((i + 1) / MQ_DBUF) & 1u)) { alive = false; break; }
-                if (warp == 0) MQ_T1(0);
-                mq_tc_fence_after();
-                mq_tmem_ld32(tlane + (unsigned)(nb * MQ_TILE_T), sa);
-                next_ready = true;
             }
             // the bias stores have landed by now: hand the buffer back to the MMA issuer
             {
@@ -453,12 +458,6 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
                 if (lane == 0) mq_bar_arrive(&sh.d_empty[buf]);
                 if (warp == 0) MQ_T1(6);
             }
-            {
-                MQ_T0();
-                scale32(sb, 1);
-                if (warp == 0) MQ_T1(7);
-            }
-            if (next_ready) mq_tmem_ld32(tlane + (unsigned)(((i + 1) % MQ_DBUF) * MQ_TILE_T + 32), sb);
             if (b == 7) {
                 __syncwarp();
                 if (lane == 0) mq_bar_arrive(&sh.epi_done[s]);   // the stage's scale tables are free
@@ -470,7 +469,7 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
             const int row = n0 + r;
             if (row < w.n) {
 #pragma unroll
-                for (int j = 0; j < 64; j++) {
+                for (int j = 0; j < 32; j++) {
                     const int tok = t0 + c0 + j;
                     if (tok < a.rows) y[(long long)tok * y_stride + row] = acc[j];
                 }
