@@ -323,6 +323,36 @@ def time_graphed(torch, dist, world, stream, fn, steps, warmup, use_graph=True):
     return ms
 
 
+def decode_step_leg(args, torch, dist, device, N, synth, stream):
+    """BASELINE config 4: every quantized MatMul of one decode step of a Llama-3-8B-shaped model on one GPU, a
+    continuous batch of 32 sequences: 32 layers of Q4_K weights (qkv, o, gate_up, down) and the Q6_K lm_head
+    [128256, 4096]. Attention, norms and sampling are not on the path."""
+    from sharplight_b200 import MatMulOp, SharedActivation, tp
+    arch, rows = tp.LLAMA8B, 32
+    stack = TpStack(device, torch, dist, N, synth, 0, 1, rows, arch["layers"], arch)
+    vocab, h = 128256, arch["hidden"]
+    head_w = device.upload_weight("Q6_K", (vocab, h), synth.weight_blocks("Q6_K", vocab, h, seed=900))
+    head = MatMulOp(device, head_w, rows)
+    head_act = SharedActivation(device, rows, h)
+    x = torch.randn((rows, h), device="cuda", dtype=torch.float32)
+    logits = torch.empty((rows, vocab), device="cuda", dtype=torch.float32)
+
+    def step(sp):
+        stack.step(rows, sp)
+        head_act.quantize(x.data_ptr(), N.F32, rows, h, sp)
+        head_act.matmul(head, logits.data_ptr(), vocab, sp)
+
+    steps = max(3, min(args.steps, 20))
+    ms = time_graphed(torch, dist, 1, stream, step, steps, 3, use_graph=not args.no_graph)
+    wbytes = stack.total_weight_bytes + synth.weight_bytes("Q6_K", vocab, h)
+    out = {"workload": "configs[3]: Llama-3-8B-shaped decode step, 32 layers Q4_K + Q6_K lm_head, batch 32, one GPU",
+           "ms_per_step": ms, "weight_gbs": wbytes / (ms * 1e-3) / 1e9, "weight_bytes_per_step": wbytes,
+           "sequences_per_s": rows / (ms * 1e-3), "launches_per_step": stack.launches_per_step + 2, "steps": steps}
+    head_act.dispose(); head.dispose(); head_w.dispose(); stack.dispose()
+    torch.cuda.synchronize()
+    return out
+
+
 def run_tp(args, torch, dist, device, N, synth, stream, world, rank, local):
     """The N > 1 workload (and the "tp_stack" object of the N = 1 line)."""
     from sharplight_b200 import tp
@@ -523,6 +553,9 @@ def run_ours(args):
     tp_stack = None
     if world == 1 and not args.no_tp_stack:
         tp_stack = run_tp(args, torch, dist, device, N, synth, stream, 1, 0, local)
+    decode_step = None
+    if world == 1 and not args.no_tp_stack:
+        decode_step = decode_step_leg(args, torch, dist, device, N, synth, stream)
     prefill = None
     if world == 1 and not args.no_prefill:
         prefill = prefill_leg(device, torch, N, synth, stream, max(5, args.steps // 10))
@@ -560,6 +593,8 @@ def run_ours(args):
             line["prefill"] = prefill
         if tp_stack is not None:
             line["tp_stack"] = tp_stack
+        if decode_step is not None:
+            line["decode_step_8b"] = decode_step
         print(json.dumps(line), flush=True)
     if segment is not None:
         segment.dispose()
@@ -585,7 +620,7 @@ def main():
     ap.add_argument("--copies", type=int, default=COPIES, help="weight matrices per step (profiling runs use fewer)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--layers", type=int, default=0, help="layers of the tensor-parallel stack (default: the architecture's 80)")
-    ap.add_argument("--no-tp-stack", action="store_true", help="N=1: skip the 70B-shaped stack at tensor-parallel degree 1")
+    ap.add_argument("--no-tp-stack", action="store_true", help="N=1: skip the 70B-shaped stack at tensor-parallel degree 1 and the 8B decode step")
     ap.add_argument("--tp-main-only", action="store_true", help="time the stack at --rows only, not at 1, 8, 64 and 2048 rows")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM leg")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of a CUDA graph")

@@ -219,6 +219,8 @@ SLC_API slc_result slc_tp_exchange_create(slc_device *device, int32_t rank, int3
                                           slc_tp_exchange **out, uint8_t *out_handle /* [SLC_TP_HANDLE_BYTES] */);
 SLC_API slc_result slc_tp_exchange_connect(slc_tp_exchange *exchange, const uint8_t *handles /* [world][64] */);
 SLC_API void slc_tp_exchange_destroy(slc_tp_exchange *exchange);
+/* How long a kernel waits for its peers before it gives up (default 1000 ms; 1..60000). */
+SLC_API slc_result slc_tp_exchange_set_wait_ms(slc_tp_exchange *exchange, int32_t milliseconds);
 /* y (device, f32) = sum over ranks of (act . W^T), W being this rank's K range of the weight and act this rank's
    matching slice of the activations. Asynchronous on the stream. */
 SLC_API slc_result slc_matmul_run_quantized_allreduce(slc_matmul *op, slc_activation *act, slc_tp_exchange *exchange,

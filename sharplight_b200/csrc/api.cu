@@ -642,6 +642,14 @@ slc_result slc_tp_exchange_connect(slc_tp_exchange *x, const uint8_t *handles)
     return SLC_OK;
 }
 
+slc_result slc_tp_exchange_set_wait_ms(slc_tp_exchange *x, int32_t milliseconds)
+{
+    if (!x) return fail(SLC_ERR_INVALID_ARGUMENT, "exchange is null");
+    if (milliseconds < 1 || milliseconds > 60000) return fail(SLC_ERR_INVALID_ARGUMENT, "wait limit: 1..60000 ms");
+    x->view.wait_ms = (unsigned)milliseconds;
+    return SLC_OK;
+}
+
 void slc_tp_exchange_destroy(slc_tp_exchange *x)
 {
     if (!x) return;

@@ -83,6 +83,7 @@ SIGNATURES = {
     "slc_tp_exchange_create": (_i32, [_vp, _i32, _i32, _i64, _i64, _P(_vp), _vp]),
     "slc_tp_exchange_connect": (_i32, [_vp, _vp]),
     "slc_tp_exchange_destroy": (None, [_vp]),
+    "slc_tp_exchange_set_wait_ms": (_i32, [_vp, _i32]),
     "slc_matmul_run_quantized_allreduce": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp]),
     "slc_matmul_run_static": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp, _i64, _vp]),
     "slc_static_last_error": (C.c_char_p, []),

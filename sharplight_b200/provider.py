@@ -438,6 +438,10 @@ class TpExchange:
         blob = (C.c_uint8 * (N.TP_HANDLE_BYTES * self.world)).from_buffer_copy(b"".join(handles))
         _check(N.load().slc_tp_exchange_connect(self.handle, blob))
 
+    def set_wait_ms(self, milliseconds: int) -> None:
+        """How long a kernel waits for its peers before it raises the device status to ERR_TIMEOUT."""
+        _check(N.load().slc_tp_exchange_set_wait_ms(self.handle, milliseconds))
+
     def connect_group(self, dist) -> None:
         """Exchanges the handles over an initialised torch.distributed group and connects."""
         handles = [None] * self.world

@@ -3,7 +3,8 @@
 One GPU: a group of one rank runs the whole exchange machinery (stores into its own receive area, arrival words, wait,
 sum, counters, slot alternation) and must give the bits of the plain MatMul. Two GPUs (skipped with fewer): two
 processes, each with its K range of the weight, sum through each other's memory; the total must match the oracle on
-the unsharded weight, the NCCL all-reduce of the plain partial outputs, and be bit-identical on both ranks.
+the unsharded weight, the NCCL all-reduce of the plain partial outputs, and be bit-identical on both ranks; and a
+peer that never arrives must end in a timeout status, not a hang.
 """
 import ctypes as C
 import os
@@ -146,10 +147,30 @@ def _two_gpu_worker(rank, world, port, out):
                 dist.all_gather(both, y_sum)
                 if not all(torch.equal(both[0], b) for b in both[1:]):
                     failures.append(f"{type_name} rows={rows}: the ranks hold different sums")
-            if device.last_status() != 0:
-                failures.append(f"{type_name}: device status {device.last_status()}")
+            status = device.last_status()
+            if status != 0:
+                failures.append(f"{type_name}: device status {status}")
             dist.barrier()
             torch.cuda.synchronize()
+            if type_name == "Q8_0":
+                # A peer that never shows up: rank 1 sits this exchange out (it has nothing in flight), rank 0's
+                # kernel gives up after the limit, reports through the status word and leaves the context usable.
+                ex.set_wait_ms(200)
+                if rank == 0:
+                    x = torch.from_numpy(np.ascontiguousarray(synth.activations(1, k, seed=99)[:, k0:k0 + sk])).cuda()
+                    y_sum = torch.zeros((1, n), device="cuda")
+                    act.quantize(x.data_ptr(), N.F32, 1, sk, sp)
+                    ex.matmul(op, act, y_sum.data_ptr(), n, sp)
+                    stream.synchronize()
+                    status = device.last_status()
+                    if status != N.ERR_TIMEOUT:
+                        failures.append(f"abandoned exchange: status {status}, expected {N.ERR_TIMEOUT}")
+                    act.matmul(op, y_sum.data_ptr(), n, sp)          # the device still works
+                    stream.synchronize()
+                    if device.last_status() != 0 or not bool(torch.isfinite(y_sum).all()):
+                        failures.append("the device did not recover after the abandoned exchange")
+                dist.barrier()
+                torch.cuda.synchronize()
             ex.dispose(); act.dispose(); op.dispose(); w.dispose()
         out.put((rank, failures))
     except Exception as exc:  # the parent reports it
