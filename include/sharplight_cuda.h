@@ -150,6 +150,24 @@ SLC_API void slc_host_free(void *host_ptr);
 SLC_API slc_result slc_buffer_copy_async(slc_device *device, void *dst, const void *src, int64_t bytes, int32_t direction,
                                          void *stream);
 
+/* ---- side streams and captured step graphs: a segment's Execute captured once per row count and replayed with one
+        call, its output copies on a second stream beside the kernels (the CUDA form of a command buffer that is
+        recorded once and re-submitted; ICompiledSegment.cs:11-12 allows asynchronous execution until an output is
+        read). slc_stream_wait makes `waiter` wait for everything queued so far on `signal` (NULL = the device's own
+        stream); between slc_graph_begin and slc_graph_end on a stream, launches and copies issued to it -- and to
+        streams made to wait on it, which must be joined back before the end -- are recorded instead of executed. Make
+        every call that will be captured once outside a capture first (first launches configure kernels). Errors of
+        this group: slc_graph_last_error. */
+typedef struct slc_graph slc_graph;
+SLC_API slc_result slc_stream_create(slc_device *device, void **out_stream);
+SLC_API void slc_stream_destroy(slc_device *device, void *stream);
+SLC_API slc_result slc_stream_wait(slc_device *device, void *waiter, void *signal);
+SLC_API slc_result slc_graph_begin(slc_device *device, void *stream);
+SLC_API slc_result slc_graph_end(slc_device *device, void *stream, slc_graph **out_graph);
+SLC_API slc_result slc_graph_launch(slc_graph *graph, void *stream);
+SLC_API void slc_graph_destroy(slc_graph *graph);
+SLC_API const char *slc_graph_last_error(void);
+
 /* ---- weights: WeightInfo.Source -> device (src/Sharplight.Core/Models/IWeightSource.cs:4-40).
         blocks: raw ggml blocks of an [n, k] weight, row-major, bytes == n * k / block_size * block_bytes.
         The data is copied (the caller may unmap afterwards) and re-laid-out on the device at the same byte count,

@@ -161,6 +161,7 @@ void slc_device_close(slc_device *d)
     if (!d) return;
     cudaSetDevice(d->index);
     cudaStreamSynchronize(d->stream);
+    for (cudaEvent_t ev : d->events) cudaEventDestroy(ev);
     cudaStreamDestroy(d->stream);
     cudaFree(d->status_dev);
     delete d;

@@ -4,12 +4,15 @@
 #include "internal.cuh"
 #include "exchange.cuh"
 
+#include <vector>
+
 struct slc_device
 {
     int index = 0;
     cudaStream_t stream = nullptr;
     int *status_dev = nullptr;   // device-side status word (bounded waits report here)
     cudaDeviceProp prop{};
+    std::vector<cudaEvent_t> events;   // made by slc_stream_wait (some live on inside captured graphs); freed at close
 };
 
 struct slc_weight

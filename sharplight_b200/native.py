@@ -66,6 +66,14 @@ SIGNATURES = {
     "slc_host_alloc": (_i32, [_i64, _P(_vp)]),
     "slc_host_free": (None, [_vp]),
     "slc_buffer_copy_async": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
+    "slc_stream_create": (_i32, [_vp, _P(_vp)]),
+    "slc_stream_destroy": (None, [_vp, _vp]),
+    "slc_stream_wait": (_i32, [_vp, _vp, _vp]),
+    "slc_graph_begin": (_i32, [_vp, _vp]),
+    "slc_graph_end": (_i32, [_vp, _vp, _P(_vp)]),
+    "slc_graph_launch": (_i32, [_vp, _vp]),
+    "slc_graph_destroy": (None, [_vp]),
+    "slc_graph_last_error": (C.c_char_p, []),
     "slc_weight_upload": (_i32, [_vp, _i32, _i64, _i64, _vp, _i64, _P(_vp)]),
     "slc_weight_upload_kslice": (_i32, [_vp, _i32, _i64, _i64, _vp, _i64, _i64, _i64, _P(_vp)]),
     "slc_weight_download": (_i32, [_vp, _vp, _i64]),

@@ -45,6 +45,12 @@ _EXC = {N.ERR_INVALID_ARGUMENT: ArgumentError, N.ERR_OUT_OF_MEMORY: Insufficient
         N.ERR_NO_DEVICE: NotSupportedError}
 
 
+def _check_graph(code: int) -> None:
+    """Result check for the stream / graph group, which reports through slc_graph_last_error."""
+    if code < 0:
+        raise N.NativeError(code, N.load().slc_graph_last_error().decode() or "stream / graph call failed")
+
+
 def _check(code: int) -> None:
     """Native result -> the exception the managed wrapper throws."""
     if code >= 0:
@@ -130,6 +136,7 @@ class CompileOptions:
     disabled_features: frozenset = frozenset()
     allow_reduced_precision: bool = False
     row_invariant_rows: int = 0
+    capture_steps: bool = True              # replay Execute as a captured CUDA graph from the third call per row count
 
 
 class CudaExecutionProvider:
@@ -516,6 +523,11 @@ class CudaSegment:
             off += mr * self._shape[v][0] * 4
         self._out_stage = _Pinned(off)
         self._acts = {v: SharedActivation(device, mr, self._shape[v][0]) for v in {n.x for n in segment.nodes}}
+        # output copies travel on a second stream beside the kernels; per row-count signature: None -> issued once
+        # from the host, 1 -> issued twice (every kernel configured), then the captured graph
+        self._copy_stream = C.c_void_p()
+        _check_graph(lib.slc_stream_create(device.handle, C.byref(self._copy_stream)))
+        self._graphs: Dict[tuple, object] = {}
 
     @property
     def device_memory_bytes(self) -> int:
@@ -548,26 +560,61 @@ class CudaSegment:
         if t is not None and t > self.options.max_rows:
             raise InvalidOperationError(f"T={t} exceeds the compiled bound {self.options.max_rows}")
         lib = N.load()
-        quantized = set()
+        # the step as a list of launches (host logic only), then issued directly or through its captured graph
+        plan, quantized = [], set()
         rows_of: Dict[str, int] = dict(self._rows)
         for node in self.segment.nodes:
             if node.x not in rows_of:
                 raise InvalidOperationError(f"input '{node.x}' was never set")
             rows = rows_of[node.x] if t is None else min(t, rows_of[node.x])
-            cols, _ = self._shape[node.x]
             if node.x not in quantized:
-                dtype = N.BF16 if node.x_dtype == "bf16" else N.F32
-                self._acts[node.x].quantize(self._dev[node.x].value, dtype, rows, cols, 0)
+                plan.append(("quantize", node, rows))
                 quantized.add(node.x)
-            self._acts[node.x].matmul(self._ops[node.name], self._dev[node.y].value, self._shape[node.y][0], 0)
+            plan.append(("matmul", node, rows))
             rows_of[node.y] = rows
             quantized.discard(node.y)
         self._out_rows = {v: rows_of[v] for v in self.segment.outputs}
-        for v in self.segment.outputs:
-            nbytes = self._out_rows[v] * self._shape[v][0] * 4
-            dst = C.c_void_p(self._out_stage.ptr.value + self._out_offset[v])
-            _check(lib.slc_buffer_copy_async(self.device.handle, dst, self._dev[v], nbytes, 1, None))
+        key = tuple(sorted(self._out_rows.items())) + tuple(sorted((v, r) for v, r in self._rows.items()))
+        state = self._graphs.get(key)
+        if not self.options.capture_steps or (state is None and len(self._graphs) >= 32):
+            self._issue(plan)
+        elif state is None or state == 1:
+            self._issue(plan)
+            self._graphs[key] = 1 if state is None else 2
+        elif state == 2:
+            _check_graph(lib.slc_graph_begin(self.device.handle, None))
+            try:
+                self._issue(plan)
+            finally:
+                g = C.c_void_p()
+                code = lib.slc_graph_end(self.device.handle, None, C.byref(g))
+            _check_graph(code)
+            self._graphs[key] = g
+            _check_graph(lib.slc_graph_launch(g, None))
+        else:
+            _check_graph(lib.slc_graph_launch(state, None))
         self._executed, self._synced = True, False
+
+    def _issue(self, plan) -> None:
+        """The step's launches on the device's stream; every output leaves on the copy stream as soon as the kernel
+        that produced it is queued, and the copy stream is joined back at the end."""
+        lib = N.load()
+        outputs = set(self.segment.outputs)
+        copied = False
+        for kind, node, rows in plan:
+            if kind == "quantize":
+                dtype = N.BF16 if node.x_dtype == "bf16" else N.F32
+                self._acts[node.x].quantize(self._dev[node.x].value, dtype, rows, self._shape[node.x][0], 0)
+                continue
+            self._acts[node.x].matmul(self._ops[node.name], self._dev[node.y].value, self._shape[node.y][0], 0)
+            if node.y in outputs:
+                nbytes = rows * self._shape[node.y][0] * 4
+                dst = C.c_void_p(self._out_stage.ptr.value + self._out_offset[node.y])
+                _check_graph(lib.slc_stream_wait(self.device.handle, self._copy_stream, None))
+                _check(lib.slc_buffer_copy_async(self.device.handle, dst, self._dev[node.y], nbytes, 1, self._copy_stream))
+                copied = True
+        if copied:
+            _check_graph(lib.slc_stream_wait(self.device.handle, None, self._copy_stream))
 
     def get_output(self, value: str, copy: bool = True) -> np.ndarray:
         self._live()
@@ -590,6 +637,11 @@ class CudaSegment:
         if self._disposed:
             return
         self.device.synchronize()
+        for g in self._graphs.values():
+            if not isinstance(g, int):
+                N.load().slc_graph_destroy(g)
+        self._graphs.clear()
+        N.load().slc_stream_destroy(self.device.handle, self._copy_stream)
         for op in self._ops.values():
             op.dispose()
         for a in self._acts.values():

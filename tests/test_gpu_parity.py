@@ -274,6 +274,35 @@ def test_segment_contract(cuda_device):
                                                      "y")], ["x"], ["y"]), CompileOptions())
 
 
+def test_segment_replays_a_captured_step(cuda_device):
+    """From the third Execute with the same row counts the step is a captured graph (outputs copied on a side stream):
+    every call, before and after the capture, must return what a fresh MatMul of that call's input gives; a different
+    row count in between gets its own steps; a chained node (y of one MatMul feeding the next) stays on the device."""
+    k, n1, n2 = 512, 64, 96
+    w1 = WeightInfo("Q4_K", (n1, k), synth.weight_blocks("Q4_K", n1, k, 4))
+    w2 = WeightInfo("Q8_0", (n2, k), synth.weight_blocks("Q8_0", n2, k, 5))
+    w3 = WeightInfo("Q8_0", (32, n2), synth.weight_blocks("Q8_0", 32, n2, 6))
+    seg = GraphSegment([MatMulNode("a", "x", w1, "ya"), MatMulNode("b", "x", w2, "yb"), MatMulNode("c", "yb", w3, "yc")],
+                       ["x"], ["ya", "yc"])
+    compiled = cuda_device.compile(seg, CompileOptions(max_rows=4))
+    eager = cuda_device.compile(seg, CompileOptions(max_rows=4, capture_steps=False))
+    try:
+        for call, rows in enumerate((1, 1, 1, 1, 3, 1, 3, 3, 3, 1)):
+            x = synth.activations(rows, k, 50 + call) * np.float32(1 + call)
+            for c in (compiled, eager):
+                c.set_input("x", x)
+                c.execute({"T": rows})
+            ya, yc = compiled.get_output("ya"), compiled.get_output("yc")
+            assert ya.shape == (rows, n1) and yc.shape == (rows, 32)
+            assert np.array_equal(ya, eager.get_output("ya")) and np.array_equal(yc, eager.get_output("yc")), call
+            ref, _, _ = sl_oracle.matmul_intdot(12, w1.blocks, n1, k, x)
+            assert max_rel_error(ya, ref) <= MAX_REL
+        assert cuda_device.last_status() == 0
+    finally:
+        compiled.dispose()
+        eager.dispose()
+
+
 # ---- the benchmark configurations at full size ------------------------------------------------------------------
 
 def test_config1_q8_0_qwen_up_proj(cuda_device):
