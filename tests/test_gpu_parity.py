@@ -379,3 +379,38 @@ def test_config3_q4_0_prefill_bf16(cuda_device):
     finally:
         op.dispose()
         w.dispose()
+
+
+def _check_sampled_rows(device, type_name, n, k, rows, seed, sample_n):
+    """Full-size weight on the GPU; the oracle recomputes a sample of the weight rows (rows of W are independent)."""
+    fmt = FMT_OF[type_name]
+    blocks = synth.weight_blocks(type_name, n, k, seed)
+    x = synth.activations(rows, k, seed + 1)
+    w = device.upload_weight(type_name, (n, k), blocks)
+    op = MatMulOp(device, w, rows)
+    try:
+        y = op.run(x)
+        pick = np.sort(np.random.Generator(np.random.Philox(seed)).choice(n, sample_n, replace=False))
+        row_bytes = blocks.size // n
+        sub = np.ascontiguousarray(blocks.reshape(n, row_bytes)[pick]).reshape(-1)
+        ref, ref64, _ = sl_oracle.matmul_intdot(fmt, sub, sample_n, k, x, threads=8, want_f64=True)
+        assert max_rel_error(y[:, pick], ref) <= MAX_REL, (type_name, n, k, rows, op.last_kernel())
+        assert max_rel_error(y[:, pick], ref64) <= MAX_REL
+        assert device.last_status() == 0
+        return op.last_kernel()[0]
+    finally:
+        op.dispose()
+        w.dispose()
+
+
+def test_config4_q6_k_lm_head_batch32(cuda_device):
+    """BASELINE config 4's largest MatMul at full size: the Q6_K lm_head [128256, 4096] for a batch of 32 sequences."""
+    assert _check_sampled_rows(cuda_device, "Q6_K", 128256, 4096, 32, 201, 512) == N.KERNEL_SKINNY
+
+
+@pytest.mark.parametrize("n,k,rows", [(8192, 28672, 1), (8192, 28672, 64), (10240, 8192, 8), (57344, 8192, 1),
+                                      (8192, 3584, 1), (1280, 8192, 64)])
+def test_config5_llama70b_shapes(cuda_device, n, k, rows):
+    """BASELINE config 5: the Q4_K MatMuls of a Llama-3-70B-shaped layer at full size, whole (down [8192, 28672],
+    stacked qkv [10240, 8192], stacked gate_up [57344, 8192]) and as 8-way tensor-parallel shards."""
+    _check_sampled_rows(cuda_device, "Q4_K", n, k, rows, 300 + rows, 256)
