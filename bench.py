@@ -125,11 +125,55 @@ def cpu_arm(rows: int, seconds: float = 12.0):
                       f"copies, {el:.1f} s, {threads} threads"}, el / done
 
 
+def cpu_arm_stack(rows: int, seconds: float):
+    """The N > 1 workload on the host cores: the four MatMuls of a Llama-3-70B-shaped layer (stacked qkv, o, stacked
+    gate_up, down), an eighth of the output rows of each (60 MB of Q4_K blocks), in rotation; weight GB/s."""
+    from oracle import sl_oracle
+    from sharplight_b200 import synth, tp
+    threads = os.cpu_count() or 1
+    mats = []
+    for i, (name, parts, k, _, _) in enumerate(tp.fused_layer_matmuls(tp.LLAMA70B)):
+        n = sum(parts) // 8
+        mats.append((synth.weight_blocks("Q4_K", n, k, seed=400 + i), n, k, synth.activations(rows, k, seed=410 + i)))
+    layer_bytes = sum(synth.weight_bytes("Q4_K", n, k) for _, n, k, _ in mats)
+    for b, n, k, x in mats:
+        sl_oracle.matmul_intdot(12, b, n, k, x, threads=threads, tier=1)
+    t0, done = time.perf_counter(), 0
+    while True:
+        for b, n, k, x in mats:
+            sl_oracle.matmul_intdot(12, b, n, k, x, threads=threads, tier=1)
+        done += 1
+        el = time.perf_counter() - t0
+        if el > seconds or done >= 2000:
+            break
+    gbs = layer_bytes * done / el / 1e9
+    return {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "tier": sl_oracle.fast_tier_name(),
+            "sample": f"{done} passes over one layer's four MatMuls at an eighth of their output rows "
+                      f"({layer_bytes / 1e6:.0f} MB of Q4_K blocks) at M={rows}, {el:.1f} s, {threads} threads"}, gbs
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     seconds = max(3.0, min(60.0, 0.25 * (args.steps + args.warmup)))
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.gpus > 1:
+        # the N > 1 arm's workload: the 70B-shaped stack (the CPU has no tensor parallelism: one socket, all threads)
+        from sharplight_b200 import tp
+        base, gbs = cpu_arm_stack(args.rows, seconds)
+        total = tp.layer_weight_bytes(tp.LLAMA70B) * tp.LLAMA70B["layers"]
+        line = {"impl": "reference", "metric": "quant mat-vec HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / (gbs * 1e9) * 1e3,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
+                "config": {"workload": f"configs[4]: Llama-3-70B-shaped stack, 80 layers, Q4_K, decode M={args.rows}, on the "
+                                       "host cores; bounded sample, step time extrapolated to the 38.5 GB stack"},
+                "cpu_baseline": base,
+                "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "note": "CPU restatement (oracle/) of the reference's Sharplight.Cpu integer-dot MatMul; the managed "
+                        "reference cannot be built here (no .NET toolchain)"}
+        print(json.dumps(line), flush=True)
+        return
     base, per_matvec = cpu_arm(args.rows, seconds)
     line = {"impl": "reference", "metric": "quant mat-vec HBM GB/s", "value": base["value"], "unit": "GB/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_matvec * COPIES * 1e3,
