@@ -217,6 +217,18 @@ SLC_API slc_result slc_activation_quantize(slc_activation *act, const void *x_de
 SLC_API slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act, float *y_device, int64_t y_stride,
                                             void *stream);
 
+/* The MatMul with the elementwise tail the reference's lowering folds into the kernel
+   (src/Sharplight.Shaders/Lowering/GraphLowerer.MatMul.cs:199-243, MatMulEpilogue): y[t][n] = (act . W^T + bias[n]) +
+   residual[t][n], f32 adds in that order -- the sums the separate Add nodes would give, one launch and one dependency
+   level less. bias (device, f32 [N]) and residual (device, f32, rows residual_stride apart, may be y itself) are each
+   optional; exchange (optional) as in slc_matmul_run_quantized_allreduce below: the additions then follow the sum over
+   the ranks. */
+typedef struct slc_tp_exchange slc_tp_exchange;
+SLC_API slc_result slc_matmul_run_quantized_epilogue(slc_matmul *op, slc_activation *act, slc_tp_exchange *exchange,
+                                                     const float *bias_device, const float *residual_device,
+                                                     int64_t residual_stride, float *y_device, int64_t y_stride,
+                                                     void *stream);
+
 /* ---- tensor parallelism: the reference has none (its multi-device story is layer placement,
         src/Sharplight.Core/Runtime/PlacementPlanner.cs:7-13), so these entry points have no counterpart there. One
         process per GPU. A row-split MatMul (o, down) leaves every rank with a partial output; with an exchange the
@@ -229,7 +241,6 @@ SLC_API slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act,
         issue the same sequence of allreduce calls on an exchange. A peer that never arrives (it died, or its stream is
         stuck) ends the wait after about a second: the call's kernel raises the device status to SLC_ERR_TIMEOUT
         (slc_last_status) and y is not meaningful. Destroy only when no rank has a launch in flight. */
-typedef struct slc_tp_exchange slc_tp_exchange;
 #define SLC_TP_MAX_RANKS 8
 #define SLC_TP_MAX_ROWS 64
 #define SLC_TP_HANDLE_BYTES 64

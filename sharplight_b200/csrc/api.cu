@@ -509,8 +509,9 @@ static int choose_kernel(const slc_matmul *op, int rows)
 }
 
 // ex (optional): the MatMul is the row-split part of a tensor-parallel group and its kernel sums over the ranks.
+// ep (optional): bias and residual added before the store.
 static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, long long y_stride, int *dump,
-                              cudaStream_t s, const Exchange *ex = nullptr)
+                              cudaStream_t s, const Exchange *ex = nullptr, const Epilogue *ep = nullptr)
 {
     const ActView av = view_of(act);
     const WeightView &wv = op->w->view;
@@ -531,14 +532,14 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
         if (!matvec_fits(chunk, wv.k_pad)) return fail(SLC_ERR_UNSUPPORTED, "K is too large for the mat-vec kernel's shared memory");
         for (int r0 = 0; r0 < rows; r0 += chunk) {
             const int m = rows - r0 < chunk ? rows - r0 : chunk;
-            SLC_CUDA(launch_matvec(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, early(), s, ex));
+            SLC_CUDA(launch_matvec(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, early(), s, ex, ep));
             act->reads_since_quantize++;
             op->last_launches++;
         }
     } else if (kernel == SLC_KERNEL_SKINNY) {
         for (int r0 = 0; r0 < rows; r0 += 64) {
             const int m = rows - r0 < 64 ? rows - r0 : 64;
-            SLC_CUDA(launch_skinny(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, early(), s, ex));
+            SLC_CUDA(launch_skinny(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, early(), s, ex, ep));
             act->reads_since_quantize++;
             op->last_launches++;
         }
@@ -546,7 +547,7 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
         return fail(SLC_ERR_UNSUPPORTED, "the in-kernel all-reduce serves the mat-vec and skinny kernels (up to 64 rows)");
     } else {
         if (!act->planes.q_tiled) return fail(SLC_ERR_INVALID_STATE, "the tensor-core GEMM needs more than 64 rows");
-        SLC_CUDA(launch_mmq(wv, av, act->planes.q_tiled, y, y_stride, dump, op->dev->status_dev, early(), s));
+        SLC_CUDA(launch_mmq(wv, av, act->planes.q_tiled, y, y_stride, dump, op->dev->status_dev, early(), s, ep));
         act->reads_since_quantize++;
         op->last_launches++;
     }
@@ -564,6 +565,28 @@ slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act, float *
     SLC_CUDA(cudaSetDevice(op->dev->index));
     cudaStream_t s = stream ? (cudaStream_t)stream : op->dev->stream;
     return run_kernels(op, act, y, y_stride, nullptr, s);
+}
+
+slc_result slc_matmul_run_quantized_epilogue(slc_matmul *op, slc_activation *act, slc_tp_exchange *x, const float *bias,
+                                             const float *residual, int64_t residual_stride, float *y, int64_t y_stride,
+                                             void *stream)
+{
+    if (!op || !act) return fail(SLC_ERR_INVALID_ARGUMENT, "null op or activation");
+    if (act->dev != op->dev || (x && x->dev != op->dev)) return fail(SLC_ERR_INVALID_ARGUMENT, "op, activation and exchange live on different devices");
+    if (act->k != op->w->k) return fail(SLC_ERR_INVALID_ARGUMENT, "activation K differs from the weight's K");
+    if (act->rows > op->max_rows) return fail(SLC_ERR_INVALID_STATE, "rows exceed the op's compiled bound");
+    if (x) {
+        if (!x->connected) return fail(SLC_ERR_INVALID_STATE, "the exchange is not connected");
+        if (act->rows > x->max_rows) return fail(SLC_ERR_UNSUPPORTED, "rows exceed the exchange's bound");
+        if (op->w->n > x->n) return fail(SLC_ERR_INVALID_ARGUMENT, "the weight has more rows than the exchange was created for");
+    }
+    if (act->rows == 0 || op->w->n == 0) return SLC_OK;
+    if (!y || y_stride < op->w->n) return fail(SLC_ERR_INVALID_ARGUMENT, "bad output buffer or stride");
+    if (residual && residual_stride < op->w->n) return fail(SLC_ERR_INVALID_ARGUMENT, "residual_stride < N");
+    SLC_CUDA(cudaSetDevice(op->dev->index));
+    cudaStream_t s = stream ? (cudaStream_t)stream : op->dev->stream;
+    const Epilogue ep{ bias, residual, residual_stride };
+    return run_kernels(op, act, y, y_stride, nullptr, s, x ? &x->view : nullptr, (bias || residual) ? &ep : nullptr);
 }
 
 // ---- tensor-parallel exchange ---------------------------------------------------------------------------------------

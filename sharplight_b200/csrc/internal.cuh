@@ -104,16 +104,18 @@ bool matvec_fits(int rows, int k_pad);
 // partial outputs of all ranks itself (exchange.cuh) and y receives the total. Such a launch is never early.
 struct Exchange;
 cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                          int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange = nullptr);
+                          int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange = nullptr,
+                          const Epilogue *epilogue = nullptr);
 
 // skinny.cu: int8 mma tiles, 1..64 activation rows per launch.
 cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                          int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange = nullptr);
+                          int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange = nullptr,
+                          const Epilogue *epilogue = nullptr);
 
 // mmq.cu: tcgen05 / TMEM int8 GEMM for many rows (Q4_0, Q8_0, Q4_K). status: device word set to a negative code when
 // a bounded wait runs out.
 bool mmq_supports(int fmt);
 cudaError_t launch_mmq(const WeightView &w, const ActView &a, const uint8_t *q_tiled, float *y, long long y_stride,
-                       int *dump, int *status, int early, cudaStream_t stream);
+                       int *dump, int *status, int early, cudaStream_t stream, const Epilogue *epilogue = nullptr);
 
 }  // namespace slc

@@ -105,6 +105,25 @@ struct ActView
     const int *isum;     // [rows_pad][k_pad/32]
 };
 
+// What a MatMul adds to its result before the store, the elementwise tail the reference's lowering folds into the
+// kernel (src/Sharplight.Shaders/Lowering/GraphLowerer.MatMul.cs:199-243: a bias row vector, then further adds such as
+// the residual): y[t][n] = (dot + bias[n]) + residual[t][n], each an f32 add in that order, the same sums the
+// stand-alone Add kernels would compute. Null pointers: nothing is added.
+struct Epilogue
+{
+    const float *bias;          // [n]
+    const float *residual;      // [rows][residual_stride], indexed like y
+    long long residual_stride;
+#ifdef __CUDACC__
+    __device__ __forceinline__ float apply(float v, long long tok, int col) const
+    {
+        if (bias) v = __fadd_rn(v, bias[col]);
+        if (residual) v = __fadd_rn(v, residual[tok * residual_stride + col]);
+        return v;
+    }
+#endif
+};
+
 inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 inline size_t weight_bytes(int fmt, int n_pad, int k_pad)

@@ -401,7 +401,7 @@ __device__ __forceinline__ void compute_slot(const uint8_t *slot, const SmemAct 
 template <int FMT, int M, bool DUMP>
 __global__ void __launch_bounds__(FV_MAX_WARPS * 32)
 matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__ y, long long y_stride, int *dump,
-              int *status, int early, const Exchange ex)
+              int *status, int early, const Exchange ex, const Epilogue ep)
 {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) uint64_t bars[FV_MAX_WARPS][FV_STAGES];
@@ -504,7 +504,7 @@ matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__
             for (int wi = 0; wi < warps; wi++) v += red[wi][rr][m];
         }
         if (ex.world == 0) {
-            if (own && row < w.n) y[(long long)(row0 + m) * y_stride + row] = v;
+            if (own && row < w.n) y[(long long)(row0 + m) * y_stride + row] = ep.apply(v, row0 + m, row);
         } else {
             // row-split MatMul of a tensor-parallel group: v is this rank's partial value; every thread trades its own
             // value with the peers as {value, tag} words (exchange.cuh)
@@ -514,7 +514,7 @@ matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__
                 ex_ll_send(ex, slot, epoch, m, row, v);
                 const float total = ex_ll_collect(ex, slot, epoch, m, row, v, ok);
                 if (!ok) atomicExch(status, -7);
-                if (row < w.n) y[(long long)(row0 + m) * y_stride + row] = total;
+                if (row < w.n) y[(long long)(row0 + m) * y_stride + row] = ep.apply(total, row0 + m, row);
             }
             ex_finish(ex, epoch);
         }
@@ -543,7 +543,7 @@ bool matvec_fits(int rows, int k_pad)
 
 template <int FMT, int M, bool DUMP>
 static cudaError_t launch_one(const WeightView &w, const ActView &a, int row0, float *y, long long y_stride, int *dump,
-                              int *status, int early, cudaStream_t stream, const Exchange &ex)
+                              int *status, int early, cudaStream_t stream, const Exchange &ex, const Epilogue &ep)
 {
     static bool configured[64] = {};
     int dev = 0;
@@ -556,17 +556,17 @@ static cudaError_t launch_one(const WeightView &w, const ActView &a, int row0, f
     }
     const int warps = matvec_warps(w);
     return launch_pdl(kernel, dim3(w.n_pad / 16), dim3(warps * 32), matvec_smem(FMT, warps, M, w.k_pad), stream, w, a,
-                      row0, y, y_stride, dump, status, early, ex);
+                      row0, y, y_stride, dump, status, early, ex, ep);
 }
 
 template <int FMT>
 static cudaError_t launch_fmt(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                              int *dump, int *status, int early, cudaStream_t stream, const Exchange &ex)
+                              int *dump, int *status, int early, cudaStream_t stream, const Exchange &ex, const Epilogue &ep)
 {
 #define SLC_ROWS(MM)                                                                        \
     case MM:                                                                                \
-        return dump ? launch_one<FMT, MM, true>(w, a, row0, y, y_stride, dump, status, early, stream, ex)      \
-                    : launch_one<FMT, MM, false>(w, a, row0, y, y_stride, nullptr, status, early, stream, ex);
+        return dump ? launch_one<FMT, MM, true>(w, a, row0, y, y_stride, dump, status, early, stream, ex, ep)      \
+                    : launch_one<FMT, MM, false>(w, a, row0, y, y_stride, nullptr, status, early, stream, ex, ep);
     switch (rows) {
         SLC_ROWS(1) SLC_ROWS(2) SLC_ROWS(3) SLC_ROWS(4)
     default: return cudaErrorInvalidValue;
@@ -576,9 +576,11 @@ static cudaError_t launch_fmt(const WeightView &w, const ActView &a, int row0, i
 
 // rows 1..4 starting at activation row row0; dump (optional) receives [rows][n][k/32] block dots.
 cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                          int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange)
+                          int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange,
+                          const Epilogue *epilogue)
 {
     if (w.n_pad == 0 || rows == 0) return cudaSuccess;
+    const Epilogue ep = epilogue ? *epilogue : Epilogue{ nullptr, nullptr, 0 };
     Exchange ex{};
     if (exchange) {
         ex = *exchange;
@@ -586,10 +588,10 @@ cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int r
         if (early || rows > SLC_LL_ROWS || w.n_pad > ex.n_stride) return cudaErrorInvalidValue;
     }
     switch (w.fmt) {
-    case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
-    case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
-    case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
-    case FMT_Q6_K: return launch_fmt<FMT_Q6_K>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
+    case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
+    case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
+    case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
+    case FMT_Q6_K: return launch_fmt<FMT_Q6_K>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
     default: return cudaErrorInvalidValue;
     }
 }

@@ -293,7 +293,7 @@ __device__ __forceinline__ void mq_store(const MqRegs<FMT> &rr, int rgl, int lan
 template <int FMT, bool DUMP>
 __global__ void __launch_bounds__(MQ_THREADS, 1)
 mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_tiled, float *__restrict__ y,
-           long long y_stride, int *dump, int *status, int early)
+           long long y_stride, int *dump, int *status, int early, const Epilogue ep)
 {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ MqSmem sh;
@@ -471,7 +471,7 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
                     const int tok = t0 + c0 + j;
-                    if (tok < a.rows) y[(long long)tok * y_stride + row] = acc[j];
+                    if (tok < a.rows) y[(long long)tok * y_stride + row] = ep.apply(acc[j], tok, row);
                 }
             }
         }
@@ -576,7 +576,7 @@ bool mmq_supports(int fmt) { return fmt == FMT_Q4_0 || fmt == FMT_Q8_0 || fmt ==
 
 template <int FMT, bool DUMP>
 static cudaError_t mmq_launch_one(const WeightView &w, const ActView &a, const uint8_t *q_tiled, float *y,
-                                  long long y_stride, int *dump, int *status, int early, cudaStream_t stream)
+                                  long long y_stride, int *dump, int *status, int early, cudaStream_t stream, const Epilogue &ep)
 {
     static bool configured[64] = {};
     int dev = 0;
@@ -588,19 +588,20 @@ static cudaError_t mmq_launch_one(const WeightView &w, const ActView &a, const u
         configured[dev] = true;
     }
     const dim3 grid((w.n_pad + MQ_TILE_N - 1) / MQ_TILE_N, (a.rows + MQ_TILE_T - 1) / MQ_TILE_T);
-    return launch_pdl(kernel, grid, dim3(MQ_THREADS), mq_smem_bytes(FMT), stream, w, a, q_tiled, y, y_stride, dump, status, early);
+    return launch_pdl(kernel, grid, dim3(MQ_THREADS), mq_smem_bytes(FMT), stream, w, a, q_tiled, y, y_stride, dump, status, early, ep);
 }
 
 // a.rows_pad must be a multiple of 128 and q_tiled the core-matrix copy of the activation codes (quantize.cu).
 cudaError_t launch_mmq(const WeightView &w, const ActView &a, const uint8_t *q_tiled, float *y, long long y_stride,
-                       int *dump, int *status, int early, cudaStream_t stream)
+                       int *dump, int *status, int early, cudaStream_t stream, const Epilogue *epilogue)
 {
     if (w.n_pad == 0 || a.rows == 0) return cudaSuccess;
+    const Epilogue ep = epilogue ? *epilogue : Epilogue{ nullptr, nullptr, 0 };
     if ((a.rows_pad % MQ_TILE_T) != 0 || !q_tiled) return cudaErrorInvalidValue;
 #define SLC_FMT(F)                                                                                 \
     case F:                                                                                        \
-        return dump ? mmq_launch_one<F, true>(w, a, q_tiled, y, y_stride, dump, status, early, stream)    \
-                    : mmq_launch_one<F, false>(w, a, q_tiled, y, y_stride, nullptr, status, early, stream);
+        return dump ? mmq_launch_one<F, true>(w, a, q_tiled, y, y_stride, dump, status, early, stream, ep)    \
+                    : mmq_launch_one<F, false>(w, a, q_tiled, y, y_stride, nullptr, status, early, stream, ep);
     switch (w.fmt) {
         SLC_FMT(FMT_Q4_0) SLC_FMT(FMT_Q8_0) SLC_FMT(FMT_Q4_K)
     default: return cudaErrorInvalidValue;

@@ -287,7 +287,7 @@ __host__ __device__ constexpr int sk_wdepth(int nt) { return nt == 8 ? 1 : sk_de
 template <int FMT, int NT, bool DUMP>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__restrict__ y, long long y_stride,
-              int *dump, int *status, int early, const Exchange ex)
+              int *dump, int *status, int early, const Exchange ex, const Epilogue ep)
 {
     extern __shared__ __align__(128) unsigned char sk_smem[];
     __shared__ __align__(8) uint64_t bars[SK_WARPS][4];
@@ -388,7 +388,7 @@ skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__
                     const float v = acc[nt][e] + red[((rgl * NT + nt) * 4 + e) * 32 + lane];
                     const int row = rg * 16 + c.g + 8 * (e >> 1);
                     const int m = nt * 8 + 2 * c.t + (e & 1);
-                    if (row < w.n && m < rows) y[(long long)(row0 + m) * y_stride + row] = v;
+                    if (row < w.n && m < rows) y[(long long)(row0 + m) * y_stride + row] = ep.apply(v, row0 + m, row);
                 }
             }
         }
@@ -418,7 +418,7 @@ skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__
             for (int idx = threadIdx.x; idx < rows * 64; idx += SK_WARPS * 32) {
                 const int m = idx >> 6, col = col0 + (idx & 63);
                 const float total = ex_ll_collect(ex, slot, epoch, m, col, tile[idx], ok);
-                if (col < w.n) y[(long long)(row0 + m) * y_stride + col] = total;
+                if (col < w.n) y[(long long)(row0 + m) * y_stride + col] = ep.apply(total, row0 + m, col);
             }
             if (!ok) atomicExch(status, -7);
         } else {
@@ -436,7 +436,7 @@ skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__
                 const float sv[4] = { sum.x, sum.y, sum.z, sum.w };
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    if (col0 + c4 + j < w.n) y[(long long)(row0 + m) * y_stride + col0 + c4 + j] = sv[j];
+                    if (col0 + c4 + j < w.n) y[(long long)(row0 + m) * y_stride + col0 + c4 + j] = ep.apply(sv[j], row0 + m, col0 + c4 + j);
                 }
             }
         }
@@ -447,7 +447,7 @@ skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__
 
 template <int FMT, int NT, bool DUMP>
 static cudaError_t launch_cfg(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                              int *dump, int *status, int early, cudaStream_t stream, const Exchange &ex)
+                              int *dump, int *status, int early, cudaStream_t stream, const Exchange &ex, const Epilogue &ep)
 {
     static bool configured[64] = {};
     int dev = 0;
@@ -464,26 +464,28 @@ static cudaError_t launch_cfg(const WeightView &w, const ActView &a, int row0, i
     }
     const int rg_count = w.n_pad >> 4;
     return launch_pdl(kernel, dim3((rg_count + SK_RGS - 1) / SK_RGS), dim3(SK_WARPS * 32), smem, stream, w, a, row0, rows,
-                      y, y_stride, dump, status, early, ex);
+                      y, y_stride, dump, status, early, ex, ep);
 }
 
 template <int FMT, bool DUMP>
 static cudaError_t launch_nt(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                             int *dump, int *status, int early, cudaStream_t stream, const Exchange &ex)
+                             int *dump, int *status, int early, cudaStream_t stream, const Exchange &ex, const Epilogue &ep)
 {
-    if (rows <= 8) return launch_cfg<FMT, 1, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
-    if (rows <= 16) return launch_cfg<FMT, 2, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
-    if (rows <= 32) return launch_cfg<FMT, 4, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
-    if (rows <= 64) return launch_cfg<FMT, 8, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex);
+    if (rows <= 8) return launch_cfg<FMT, 1, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
+    if (rows <= 16) return launch_cfg<FMT, 2, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
+    if (rows <= 32) return launch_cfg<FMT, 4, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
+    if (rows <= 64) return launch_cfg<FMT, 8, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
     return cudaErrorInvalidValue;
 }
 
 // row0 must be a multiple of 8 (activation scale pairs are fetched with aligned 128-bit accesses), and the quantized
 // activations must be padded to the token tile (8, 16, 32 or 64 rows).
 cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                          int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange)
+                          int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange,
+                          const Epilogue *epilogue)
 {
     if (w.n_pad == 0 || rows == 0) return cudaSuccess;
+    const Epilogue ep = epilogue ? *epilogue : Epilogue{ nullptr, nullptr, 0 };
     if (row0 & 7) return cudaErrorInvalidValue;
     Exchange ex{};
     if (exchange) {
@@ -492,8 +494,8 @@ cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int r
         if (early || rows > ex.max_rows || ctas * 64 > ex.n_stride || ctas > ex.groups) return cudaErrorInvalidValue;
     }
 #define SLC_FMT(F) \
-    case F: return dump ? launch_nt<F, true>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex) \
-                        : launch_nt<F, false>(w, a, row0, rows, y, y_stride, nullptr, status, early, stream, ex);
+    case F: return dump ? launch_nt<F, true>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep) \
+                        : launch_nt<F, false>(w, a, row0, rows, y, y_stride, nullptr, status, early, stream, ex, ep);
     switch (w.fmt) {
         SLC_FMT(FMT_Q8_0) SLC_FMT(FMT_Q4_0) SLC_FMT(FMT_Q4_K) SLC_FMT(FMT_Q6_K)
     default: return cudaErrorInvalidValue;

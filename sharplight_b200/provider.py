@@ -415,6 +415,14 @@ class SharedActivation:
         _check(N.load().slc_matmul_run_quantized(op.handle, self.handle, C.c_void_p(y_device_ptr), y_stride,
                                                  C.c_void_p(stream) if stream else None))
 
+    def matmul_epilogue(self, op: MatMulOp, y_device_ptr: int, y_stride: int, *, bias_ptr: int = 0, residual_ptr: int = 0,
+                        residual_stride: int = 0, stream: int = 0, exchange: "TpExchange" = None) -> None:
+        """y = (act . W^T + bias) + residual in the MatMul's own launch (slc_matmul_run_quantized_epilogue)."""
+        _check(N.load().slc_matmul_run_quantized_epilogue(
+            op.handle, self.handle, exchange.handle if exchange is not None else None,
+            C.c_void_p(bias_ptr) if bias_ptr else None, C.c_void_p(residual_ptr) if residual_ptr else None,
+            residual_stride, C.c_void_p(y_device_ptr), y_stride, C.c_void_p(stream) if stream else None))
+
     def dispose(self) -> None:
         if self._h is not None:
             N.load().slc_activation_destroy(self._h)
@@ -528,6 +536,8 @@ class CudaSegment:
         self._copy_stream = C.c_void_p()
         _check_graph(lib.slc_stream_create(device.handle, C.byref(self._copy_stream)))
         self._graphs: Dict[tuple, object] = {}
+        self._forward: Dict[str, "CudaSegment"] = {}   # input value -> the segment whose output it is read from
+        self._device_only: set = set()                 # outputs nobody reads on the host: not copied back
 
     @property
     def device_memory_bytes(self) -> int:
@@ -538,10 +548,45 @@ class CudaSegment:
         if self._disposed:
             raise ObjectDisposedError("CudaSegment")
 
+    def try_forward_from(self, value: str, producer) -> bool:
+        """IDeviceForwardingSegment.TryForwardFrom (src/Sharplight.Core/Runtime/IDeviceForwardingSegment.cs:10-21):
+        from now on input ``value`` is read straight from ``producer``'s output of the same name in device memory.
+        False when that output is not reachable from here (another provider or device, another shape)."""
+        self._live()
+        if not isinstance(producer, CudaSegment) or producer._disposed or producer.device is not self.device:
+            return False
+        if value not in self.segment.inputs or value not in producer.segment.outputs:
+            return False
+        if producer._shape[value] != self._shape[value] or producer.options.max_rows > self.options.max_rows:
+            return False
+        if value not in self._forward:
+            N.load().slc_buffer_free(self.device.handle, self._dev[value])
+        self._dev[value] = producer._dev[value]
+        self._forward[value] = producer
+        self._graphs_clear()
+        return True
+
+    def keep_on_device(self, value: str) -> None:
+        """No host consumer reads output ``value`` (a later segment takes it by try_forward_from): skip its copy back."""
+        self._live()
+        if value not in self._out_offset:
+            raise ArgumentError(f"'{value}' is not an output of this segment")
+        self._device_only.add(value)
+        self._graphs_clear()
+
+    def _graphs_clear(self) -> None:
+        self.device.synchronize()
+        for g in self._graphs.values():
+            if not isinstance(g, int):
+                N.load().slc_graph_destroy(g)
+        self._graphs.clear()
+
     def set_input(self, value: str, data: np.ndarray) -> None:
         self._live()
         if value not in self.segment.inputs:
             raise ArgumentError(f"'{value}' is not an input of this segment")
+        if value in self._forward:
+            raise InvalidOperationError(f"input '{value}' is forwarded from another segment's output")
         cols, esz = self._shape[value]
         data = np.ascontiguousarray(data)
         if data.ndim != 2 or data.shape[1] != cols or data.dtype.itemsize != esz:
@@ -563,6 +608,10 @@ class CudaSegment:
         # the step as a list of launches (host logic only), then issued directly or through its captured graph
         plan, quantized = [], set()
         rows_of: Dict[str, int] = dict(self._rows)
+        for value, producer in self._forward.items():
+            if not producer._executed:
+                raise InvalidOperationError(f"the segment that produces '{value}' has not executed")
+            rows_of[value] = producer._out_rows[value]
         for node in self.segment.nodes:
             if node.x not in rows_of:
                 raise InvalidOperationError(f"input '{node.x}' was never set")
@@ -574,7 +623,7 @@ class CudaSegment:
             rows_of[node.y] = rows
             quantized.discard(node.y)
         self._out_rows = {v: rows_of[v] for v in self.segment.outputs}
-        key = tuple(sorted(self._out_rows.items())) + tuple(sorted((v, r) for v, r in self._rows.items()))
+        key = tuple(sorted(self._out_rows.items())) + tuple(sorted((v, rows_of[v]) for v in self.segment.inputs))
         state = self._graphs.get(key)
         if not self.options.capture_steps or (state is None and len(self._graphs) >= 32):
             self._issue(plan)
@@ -607,7 +656,7 @@ class CudaSegment:
                 self._acts[node.x].quantize(self._dev[node.x].value, dtype, rows, self._shape[node.x][0], 0)
                 continue
             self._acts[node.x].matmul(self._ops[node.name], self._dev[node.y].value, self._shape[node.y][0], 0)
-            if node.y in outputs:
+            if node.y in outputs and node.y not in self._device_only:
                 nbytes = rows * self._shape[node.y][0] * 4
                 dst = C.c_void_p(self._out_stage.ptr.value + self._out_offset[node.y])
                 _check_graph(lib.slc_stream_wait(self.device.handle, self._copy_stream, None))
@@ -622,6 +671,8 @@ class CudaSegment:
             raise InvalidOperationError("GetOutput before Execute")
         if value not in self._out_offset:
             raise ArgumentError(f"'{value}' is not an output of this segment")
+        if value in self._device_only:
+            raise InvalidOperationError(f"output '{value}' stays on the device (keep_on_device)")
         if not self._synced:
             self.device.synchronize()
             self._synced = True
@@ -636,11 +687,7 @@ class CudaSegment:
     def dispose(self) -> None:
         if self._disposed:
             return
-        self.device.synchronize()
-        for g in self._graphs.values():
-            if not isinstance(g, int):
-                N.load().slc_graph_destroy(g)
-        self._graphs.clear()
+        self._graphs_clear()
         N.load().slc_stream_destroy(self.device.handle, self._copy_stream)
         for op in self._ops.values():
             op.dispose()
@@ -648,8 +695,9 @@ class CudaSegment:
             a.dispose()
         for w in self._weights:
             w.dispose()
-        for p in self._dev.values():
-            N.load().slc_buffer_free(self.device.handle, p)
+        for name, p in self._dev.items():
+            if name not in self._forward:    # a forwarded input's buffer belongs to the producing segment
+                N.load().slc_buffer_free(self.device.handle, p)
         for st in self._in_stage.values():
             st.free()
         self._out_stage.free()

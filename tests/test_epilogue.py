@@ -1,0 +1,65 @@
+"""slc_matmul_run_quantized_epilogue: bias and residual added inside the MatMul's launch. The fused store must give the
+bits of the plain MatMul followed by the two f32 additions, in every kernel family, also when the residual is y itself
+and when the output is summed over a (one-rank) tensor-parallel group."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from sharplight_b200 import MatMulOp, SharedActivation, TpExchange, synth
+from sharplight_b200 import native as N
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(lib, device, host: np.ndarray):
+    p = C.c_void_p()
+    assert lib.slc_buffer_alloc(device.handle, host.nbytes, C.byref(p)) == N.OK
+    assert lib.slc_buffer_upload(device.handle, p, host.ctypes.data_as(C.c_void_p), host.nbytes) == N.OK
+    return p
+
+
+def _read(lib, device, p, shape):
+    out = np.empty(shape, np.float32)
+    assert lib.slc_device_sync(device.handle) == N.OK
+    assert lib.slc_buffer_download(device.handle, out.ctypes.data_as(C.c_void_p), p, out.nbytes) == N.OK
+    return out
+
+
+@pytest.mark.parametrize("type_name,n,k,rows", [("Q4_K", 200, 1024, 1), ("Q8_0", 100, 1568, 2), ("Q6_K", 72, 512, 8),
+                                                ("Q4_0", 40, 512, 33), ("Q4_0", 300, 512, 130), ("Q4_K", 136, 256, 200)])
+def test_fused_additions_equal_separate_additions(cuda_device, type_name, n, k, rows):
+    lib = N.load()
+    rng = np.random.Generator(np.random.Philox(77))
+    w = cuda_device.upload_weight(type_name, (n, k), synth.weight_blocks(type_name, n, k, seed=3))
+    op = MatMulOp(cuda_device, w, rows)
+    act = SharedActivation(cuda_device, rows, k)
+    ex = TpExchange(cuda_device, 0, 1, 64, n)
+    x = synth.activations(rows, k, seed=4)
+    bias = rng.standard_normal(n).astype(np.float32)
+    res = rng.standard_normal((rows, n + 5)).astype(np.float32)           # a residual with its own row stride
+    xd, bd, rd = _dev(lib, cuda_device, x), _dev(lib, cuda_device, bias), _dev(lib, cuda_device, res)
+    ys = [_dev(lib, cuda_device, np.full((rows, n), np.nan, np.float32)) for _ in range(5)]
+    try:
+        act.quantize(xd.value, N.F32, rows, k)
+        act.matmul(op, ys[0].value, n)
+        act.matmul_epilogue(op, ys[1].value, n, bias_ptr=bd.value)
+        act.matmul_epilogue(op, ys[2].value, n, bias_ptr=bd.value, residual_ptr=rd.value, residual_stride=n + 5)
+        plain = _read(lib, cuda_device, ys[0], (rows, n))
+        with_bias = plain + bias[None, :]
+        assert np.array_equal(_read(lib, cuda_device, ys[1], (rows, n)).view(np.uint32), with_bias.view(np.uint32))
+        both = with_bias + res[:, :n]
+        assert np.array_equal(_read(lib, cuda_device, ys[2], (rows, n)).view(np.uint32), both.view(np.uint32))
+        # residual in place: y += act . W^T
+        start = rng.standard_normal((rows, n)).astype(np.float32)
+        assert lib.slc_buffer_upload(cuda_device.handle, ys[3], start.ctypes.data_as(C.c_void_p), start.nbytes) == N.OK
+        act.matmul_epilogue(op, ys[3].value, n, residual_ptr=ys[3].value, residual_stride=n)
+        assert np.array_equal(_read(lib, cuda_device, ys[3], (rows, n)).view(np.uint32), (plain + start).view(np.uint32))
+        if rows <= 64:      # with the sum over a tensor-parallel group (one rank) in front of the additions
+            act.matmul_epilogue(op, ys[4].value, n, bias_ptr=bd.value, residual_ptr=rd.value, residual_stride=n + 5, exchange=ex)
+            assert np.array_equal(_read(lib, cuda_device, ys[4], (rows, n)).view(np.uint32), both.view(np.uint32))
+        assert cuda_device.last_status() == 0
+    finally:
+        for p in [xd, bd, rd] + ys:
+            lib.slc_buffer_free(cuda_device.handle, p)
+        ex.dispose(); act.dispose(); op.dispose(); w.dispose()

@@ -303,6 +303,42 @@ def test_segment_replays_a_captured_step(cuda_device):
         eager.dispose()
 
 
+def test_segment_forwards_an_output_on_the_device(cuda_device):
+    """IDeviceForwardingSegment.TryForwardFrom: the second segment reads the first one's output in device memory; the
+    value is neither downloaded nor uploaded, and the result equals the two MatMuls chained through the host."""
+    k, n1, n2 = 512, 256, 48
+    w1 = WeightInfo("Q4_K", (n1, k), synth.weight_blocks("Q4_K", n1, k, 7))
+    w2 = WeightInfo("Q4_K", (n2, n1), synth.weight_blocks("Q4_K", n2, n1, 8))
+    first = cuda_device.compile(GraphSegment([MatMulNode("a", "x", w1, "h")], ["x"], ["h"]), CompileOptions(max_rows=4))
+    second = cuda_device.compile(GraphSegment([MatMulNode("b", "h", w2, "y")], ["h"], ["y"]), CompileOptions(max_rows=4))
+    host_a = cuda_device.compile(GraphSegment([MatMulNode("a", "x", w1, "h")], ["x"], ["h"]), CompileOptions(max_rows=4))
+    host_b = cuda_device.compile(GraphSegment([MatMulNode("b", "h", w2, "y")], ["h"], ["y"]), CompileOptions(max_rows=4))
+    other = cuda_device.compile(GraphSegment([MatMulNode("c", "x", w1, "z")], ["x"], ["z"]), CompileOptions(max_rows=4))
+    try:
+        assert not second.try_forward_from("h", other)        # that segment has no output of this name
+        assert not second.try_forward_from("y", first)        # not an input of this segment
+        assert second.try_forward_from("h", first)
+        first.keep_on_device("h")
+        with pytest.raises(InvalidOperationError):
+            second.set_input("h", np.zeros((1, n1), np.float32))
+        for call, rows in enumerate((1, 1, 1, 1, 3, 3, 3, 3)):    # long enough for both segments to switch to their graphs
+            x = synth.activations(rows, k, 60 + call)
+            first.set_input("x", x)
+            first.execute({"T": rows})
+            second.execute({"T": rows})
+            host_a.set_input("x", x)
+            host_a.execute({"T": rows})
+            host_b.set_input("h", host_a.get_output("h"))
+            host_b.execute({"T": rows})
+            assert np.array_equal(second.get_output("y"), host_b.get_output("y")), call
+        with pytest.raises(InvalidOperationError):
+            first.get_output("h")
+        assert cuda_device.last_status() == 0
+    finally:
+        for seg in (second, first, host_a, host_b, other):
+            seg.dispose()
+
+
 # ---- the benchmark configurations at full size ------------------------------------------------------------------
 
 def test_config1_q8_0_qwen_up_proj(cuda_device):
