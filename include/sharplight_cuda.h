@@ -188,6 +188,12 @@ SLC_API void slc_weight_free(slc_weight *weight);
         like the CPU provider's MatMulOp on its integer-dot path (src/Sharplight.Cpu/MatMulOp.cs:88-115,174-213) */
 SLC_API slc_result slc_matmul_create(slc_device *device, slc_weight *weight, int64_t max_rows, uint32_t flags,
                                      slc_matmul **out);
+/* Two weights of one shape that read the same activations and only feed silu(a) * b -- the gate and up projections of
+   a gated FFN (the reference's dual MatMul, src/Sharplight.Shaders/Lowering/GraphLowerer.MatMul.cs:128-198). The op
+   runs through the same entry points; y receives silu(x . gate^T) * (x . up^T), silu(v) = v / (1 + exp(-v)). For the
+   mat-vec row counts it is one launch that streams both weights; above, the two MatMuls and an element-wise kernel. */
+SLC_API slc_result slc_matmul_create_dual(slc_device *device, slc_weight *gate, slc_weight *up, int64_t max_rows,
+                                          uint32_t flags, slc_matmul **out);
 SLC_API void slc_matmul_destroy(slc_matmul *op);
 /*
  * y[rows][n] (f32, row stride y_stride elements) = x[rows][k] . W^T. x rows are x_stride elements apart.

@@ -465,10 +465,34 @@ slc_result slc_matmul_create(slc_device *d, slc_weight *w, int64_t max_rows, uin
     return SLC_OK;
 }
 
+slc_result slc_matmul_create_dual(slc_device *d, slc_weight *gate, slc_weight *up, int64_t max_rows, uint32_t flags,
+                                  slc_matmul **out)
+{
+    if (!out) return fail(SLC_ERR_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    if (!gate || !up) return fail(SLC_ERR_INVALID_ARGUMENT, "null weight");
+    if (gate->dev != up->dev || gate->fmt != up->fmt || gate->n != up->n || gate->k != up->k) {
+        return fail(SLC_ERR_INVALID_ARGUMENT, "gate and up must share device, format and shape");
+    }
+    slc_matmul *op = nullptr;
+    slc_result r = slc_matmul_create(d, gate, max_rows, flags, &op);
+    if (r != SLC_OK) return r;
+    op->w2 = up;
+    SLC_CUDA(cudaSetDevice(d->index));
+    cudaError_t e = cudaMalloc(&op->dual_tmp, (size_t)max_rows * (gate->n > 0 ? gate->n : 1) * 4);
+    if (e != cudaSuccess) {
+        delete op;
+        return cuda_fail(e, "slc_matmul_create_dual");
+    }
+    *out = op;
+    return SLC_OK;
+}
+
 void slc_matmul_destroy(slc_matmul *op)
 {
     if (!op) return;
     cudaSetDevice(op->dev->index);
+    if (op->dual_tmp) cudaFree(op->dual_tmp);
     if (op->act) slc_activation_destroy(op->act);
     if (op->x_stage) cudaFree(op->x_stage);
     if (op->y_stage) cudaFree(op->y_stage);
@@ -501,12 +525,16 @@ static int choose_kernel(const slc_matmul *op, int rows)
 {
     if (op->forced_kernel != SLC_KERNEL_AUTO) return op->forced_kernel;
     // the mat-vec keeps a row's quantized activations whole in shared memory; a K beyond that goes to the tiled kernel
-    const bool mv = matvec_fits(1, op->w->view.k_pad);
+    const bool mv = matvec_fits(1, op->w->view.k_pad, op->w2 != nullptr);
     if (mv && (op->flags & SLC_MATMUL_ROW_INVARIANT) && rows <= 8) return SLC_KERNEL_MMVQ;
     if (mv && rows <= 2) return SLC_KERNEL_MMVQ;
     if (rows <= 64 || !mmq_supports(op->w->fmt)) return SLC_KERNEL_SKINNY;
     return SLC_KERNEL_MMQ;
 }
+
+static slc_result run_family(slc_matmul *op, const WeightView &wv, const WeightView *w2, slc_activation *act, const ActView &av,
+                             int kernel, float *y, long long y_stride, int *dump, cudaStream_t s, const Exchange *ex,
+                             const Epilogue *ep);
 
 // ex (optional): the MatMul is the row-split part of a tensor-parallel group and its kernel sums over the ranks.
 // ep (optional): bias and residual added before the store.
@@ -514,13 +542,34 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
                               cudaStream_t s, const Exchange *ex = nullptr, const Epilogue *ep = nullptr)
 {
     const ActView av = view_of(act);
-    const WeightView &wv = op->w->view;
     const int rows = act->rows;
     const int kernel = choose_kernel(op, rows);
-    const long long dump_row = (long long)wv.n * (wv.k >> 5);
     op->last_kernel = kernel;
     op->last_launches = 0;
     op->last_launches_total = 0;
+    if (op->w2) {
+        // gate / up pair: one dual mat-vec launch where that kernel serves the row count, else gate -> scratch,
+        // up -> y, and the element-wise tail
+        if (dump || ex || ep) return fail(SLC_ERR_UNSUPPORTED, "a dual MatMul takes no block-dot export, exchange or epilogue");
+        if (kernel == SLC_KERNEL_MMVQ) return run_family(op, op->w->view, &op->w2->view, act, av, kernel, y, y_stride, nullptr, s, nullptr, nullptr);
+        const long long n = op->w->n;
+        slc_result r = run_family(op, op->w->view, nullptr, act, av, kernel, op->dual_tmp, n, nullptr, s, nullptr, nullptr);
+        if (r == SLC_OK) r = run_family(op, op->w2->view, nullptr, act, av, kernel, y, y_stride, nullptr, s, nullptr, nullptr);
+        if (r != SLC_OK) return r;
+        SLC_CUDA(launch_gate_mul(op->dual_tmp, n, y, y_stride, rows, (int)n, s));
+        op->last_launches++;
+        return SLC_OK;
+    }
+    return run_family(op, op->w->view, nullptr, act, av, kernel, y, y_stride, dump, s, ex, ep);
+}
+
+// The launches of one weight (two for the dual mat-vec) in the chosen kernel family.
+static slc_result run_family(slc_matmul *op, const WeightView &wv, const WeightView *w2, slc_activation *act, const ActView &av,
+                             int kernel, float *y, long long y_stride, int *dump, cudaStream_t s, const Exchange *ex,
+                             const Epilogue *ep)
+{
+    const int rows = act->rows;
+    const long long dump_row = (long long)wv.n * (wv.k >> 5);
     // A launch may run beside its predecessor when an earlier launch on this stream has already read these
     // activations: they were complete before that launch started, and MatMul outputs do not alias each other.
     auto early = [&]() { return !ex && act->reads_since_quantize > 0 ? 1 : 0; };
@@ -528,11 +577,11 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
         // chunks of up to 4 rows; every row of a chunk is computed exactly as a single row is, so the row-invariant
         // guarantee holds for any chunking
         int chunk = 4;
-        while (chunk > 1 && !matvec_fits(chunk, wv.k_pad)) chunk--;
-        if (!matvec_fits(chunk, wv.k_pad)) return fail(SLC_ERR_UNSUPPORTED, "K is too large for the mat-vec kernel's shared memory");
+        while (chunk > 1 && !matvec_fits(chunk, wv.k_pad, w2 != nullptr)) chunk--;
+        if (!matvec_fits(chunk, wv.k_pad, w2 != nullptr)) return fail(SLC_ERR_UNSUPPORTED, "K is too large for the mat-vec kernel's shared memory");
         for (int r0 = 0; r0 < rows; r0 += chunk) {
             const int m = rows - r0 < chunk ? rows - r0 : chunk;
-            SLC_CUDA(launch_matvec(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, early(), s, ex, ep));
+            SLC_CUDA(launch_matvec(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, early(), s, ex, ep, w2));
             act->reads_since_quantize++;
             op->last_launches++;
         }

@@ -43,6 +43,8 @@ struct slc_matmul
 {
     slc_device *dev = nullptr;
     slc_weight *w = nullptr;
+    slc_weight *w2 = nullptr;       // dual op: the up projection (w is the gate); y = silu(x . w^T) * (x . w2^T)
+    float *dual_tmp = nullptr;      // dual op: the gate's result for the row counts that take two launches
     long long max_rows = 0;
     uint32_t flags = 0;
     int forced_kernel = SLC_KERNEL_AUTO;

@@ -67,6 +67,17 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, unsigned b
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(b) : "memory");
 }
 
+// The same for two sources of `bytes` each, landing back to back at dst, on one barrier phase.
+__device__ __forceinline__ void bulk_load2(void *dst, const void *src_a, const void *src_b, unsigned bytes, uint64_t *bar)
+{
+    const unsigned b = smem_u32(bar);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(2 * bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src_a), "r"(bytes), "r"(b) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst) + bytes), "l"(src_b), "r"(bytes), "r"(b) : "memory");
+}
+
 // Bounded wait for the phase with the given parity. Returns false when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity)
 {
@@ -99,13 +110,18 @@ cudaError_t launch_quantize(const void *x, int x_dtype, int rows, int rows_pad, 
 
 // matvec.cu: dp4a mat-vec for 1..4 activation rows (rows row0 .. row0+rows-1 of the quantized activations). dump
 // (optional) receives unsigned-code block dots [rows][n][k/32]; status: device word raised when a bounded wait runs out.
-bool matvec_fits(int rows, int k_pad);
+bool matvec_fits(int rows, int k_pad, bool dual = false);
 // exchange (optional, both kernels): the MatMul is the row-split part of a tensor-parallel group; the kernel sums the
 // partial outputs of all ranks itself (exchange.cuh) and y receives the total. Such a launch is never early.
 struct Exchange;
 cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
                           int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange = nullptr,
-                          const Epilogue *epilogue = nullptr);
+                          const Epilogue *epilogue = nullptr, const WeightView *w2 = nullptr);
+// w2 (optional, mat-vec only): a second weight of the same shape and format; y receives silu(x . W^T) * (x . W2^T).
+
+// gate.cu: y[t][n] = silu(g[t][n]) * y[t][n], the same tail for the row counts the other kernels serve.
+cudaError_t launch_gate_mul(const float *g, long long g_stride, float *y, long long y_stride, int rows, int n,
+                            cudaStream_t stream);
 
 // skinny.cu: int8 mma tiles, 1..64 activation rows per launch.
 cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,

@@ -398,15 +398,19 @@ __device__ __forceinline__ void compute_slot(const uint8_t *slot, const SmemAct 
     }
 }
 
-template <int FMT, int M, bool DUMP>
+// DUAL: two weights of one shape share the activations (the gate and up projections of a gated FFN); every ring slot
+// carries the record of each, both dots are accumulated, and the store writes silu(gate) * up -- the reference's dual
+// MatMul with the SiLU-mul group as its epilogue (src/Sharplight.Shaders/Lowering/GraphLowerer.MatMul.cs:128-198),
+// silu(v) = v / (1 + exp(-v)) as in src/Sharplight.Cpu/ScalarMath.cs:552-577.
+template <int FMT, int M, bool DUMP, bool DUAL>
 __global__ void __launch_bounds__(FV_MAX_WARPS * 32)
-matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__ y, long long y_stride, int *dump,
-              int *status, int early, const Exchange ex, const Epilogue ep)
+matvec_kernel(const WeightView w, const WeightView w2, const ActView a, int row0, float *__restrict__ y, long long y_stride,
+              int *dump, int *status, int early, const Exchange ex, const Epilogue ep)
 {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) uint64_t bars[FV_MAX_WARPS][FV_STAGES];
-    __shared__ float red[FV_MAX_WARPS][16][M];
-    constexpr int REC = record_bytes(FMT);
+    __shared__ float red[DUAL ? 2 : 1][FV_MAX_WARPS][16][M];
+    constexpr int REC1 = record_bytes(FMT), REC = DUAL ? 2 * REC1 : REC1;   // bytes of a ring slot
     const int warps = blockDim.x >> 5;
     const int nblk_pad = w.k_pad >> 5, nst = w.k_pad >> 8;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, t = lane & 3, g = lane >> 2;
@@ -425,7 +429,10 @@ matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__
         fence_mbar_init();
 #pragma unroll
         for (int s = 0; s < FV_STAGES; s++) {
-            if (s < count) bulk_load(ring + s * REC, w.record(rg, warp + s * warps), REC, &bars[warp][s]);
+            if (s < count) {
+                if (DUAL) bulk_load2(ring + s * REC, w.record(rg, warp + s * warps), w2.record(rg, warp + s * warps), REC1, &bars[warp][s]);
+                else bulk_load(ring + s * REC, w.record(rg, warp + s * warps), REC, &bars[warp][s]);
+            }
         }
     }
 
@@ -450,11 +457,16 @@ matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__
 
     const SmemAct act{ sq, sds, sisum, w.k_pad, nblk_pad };
     const DumpCtx dc{ dump, w.n, w.k, rg, g, t };
-    float acc[2][M];
+    float acc[2][M], acc2[2][M];
 #pragma unroll
     for (int r = 0; r < 2; r++)
 #pragma unroll
-        for (int m = 0; m < M; m++) acc[r][m] = 0.0f;
+        for (int m = 0; m < M; m++) { acc[r][m] = 0.0f; acc2[r][m] = 0.0f; }
+    auto refill = [&](int s, int i) {
+        const int st = warp + (i + FV_STAGES) * warps;
+        if (DUAL) bulk_load2(ring + s * REC, w.record(rg, st), w2.record(rg, st), REC1, &bars[warp][s]);
+        else bulk_load(ring + s * REC, w.record(rg, st), REC, &bars[warp][s]);
+    };
 
     bool alive = true;
     for (int i = 0; i < count; i++) {
@@ -467,19 +479,18 @@ matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__
         }
         if (alive) {
             if constexpr (FMT == FMT_Q6_K) {
-                FTile<FMT> tl;
+                FTile<FMT> tl, tl2;
                 load_tile<FMT>(tl, slot, lane);
+                if (DUAL) load_tile<FMT>(tl2, slot + REC1, lane);
                 __syncwarp();   // every lane has its copy of the record: the slot may be refilled
-                if (lane == 0 && i + FV_STAGES < count) {
-                    bulk_load(ring + s * REC, w.record(rg, warp + (i + FV_STAGES) * warps), REC, &bars[warp][s]);
-                }
+                if (lane == 0 && i + FV_STAGES < count) refill(s, i);
                 compute_tile<FMT, M, DUMP>(tl, act, warp + i * warps, t, acc, dc);
+                if (DUAL) compute_tile<FMT, M, DUMP>(tl2, act, warp + i * warps, t, acc2, dc);
             } else {
                 compute_slot<FMT, M, DUMP>(slot, act, warp + i * warps, lane, acc, dc);
+                if (DUAL) compute_slot<FMT, M, DUMP>(slot + REC1, act, warp + i * warps, lane, acc2, dc);
                 __syncwarp();   // every lane is done reading the slot: it may be refilled
-                if (lane == 0 && i + FV_STAGES < count) {
-                    bulk_load(ring + s * REC, w.record(rg, warp + (i + FV_STAGES) * warps), REC, &bars[warp][s]);
-                }
+                if (lane == 0 && i + FV_STAGES < count) refill(s, i);
             }
         }
     }
@@ -491,7 +502,13 @@ matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__
             float v = acc[r][m];
             v += __shfl_xor_sync(0xffffffffu, v, 1);
             v += __shfl_xor_sync(0xffffffffu, v, 2);
-            if (t == 0) red[warp][g + 8 * r][m] = v;
+            if (t == 0) red[0][warp][g + 8 * r][m] = v;
+            if (DUAL) {
+                float u = acc2[r][m];
+                u += __shfl_xor_sync(0xffffffffu, u, 1);
+                u += __shfl_xor_sync(0xffffffffu, u, 2);
+                if (t == 0) red[DUAL ? 1 : 0][warp][g + 8 * r][m] = u;
+            }
         }
     }
     __syncthreads();
@@ -501,7 +518,12 @@ matvec_kernel(const WeightView w, const ActView a, int row0, float *__restrict__
         const int row = blockIdx.x * 16 + rr;
         float v = 0.0f;
         if (own) {
-            for (int wi = 0; wi < warps; wi++) v += red[wi][rr][m];
+            for (int wi = 0; wi < warps; wi++) v += red[0][wi][rr][m];
+            if (DUAL) {
+                float u = 0.0f;
+                for (int wi = 0; wi < warps; wi++) u += red[DUAL ? 1 : 0][wi][rr][m];
+                v = __fdiv_rn(v, 1.0f + expf(-v)) * u;   // silu(gate) * up
+            }
         }
         if (ex.world == 0) {
             if (own && row < w.n) y[(long long)(row0 + m) * y_stride + row] = ep.apply(v, row0 + m, row);
@@ -531,42 +553,45 @@ static int matvec_warps(const WeightView &w)
     return warps < nst ? warps : nst;
 }
 
-static size_t matvec_smem(int fmt, int warps, int rows, int k_pad)
+static size_t matvec_smem(int fmt, int warps, int rows, int k_pad, bool dual = false)
 {
-    return (size_t)warps * FV_STAGES * record_bytes(fmt) + (size_t)rows * (k_pad + (k_pad >> 5) * 12);
+    return (size_t)(dual ? 2 : 1) * warps * FV_STAGES * record_bytes(fmt) + (size_t)rows * (k_pad + (k_pad >> 5) * 12);
 }
 
-bool matvec_fits(int rows, int k_pad)
+bool matvec_fits(int rows, int k_pad, bool dual)
 {
-    return rows >= 1 && rows <= 4 && matvec_smem(FMT_Q8_0, FV_MAX_WARPS, rows, k_pad) <= FV_MAX_SMEM;
+    return rows >= 1 && rows <= 4 && matvec_smem(FMT_Q8_0, FV_MAX_WARPS, rows, k_pad, dual) <= FV_MAX_SMEM;
 }
 
-template <int FMT, int M, bool DUMP>
-static cudaError_t launch_one(const WeightView &w, const ActView &a, int row0, float *y, long long y_stride, int *dump,
-                              int *status, int early, cudaStream_t stream, const Exchange &ex, const Epilogue &ep)
+template <int FMT, int M, bool DUMP, bool DUAL>
+static cudaError_t launch_one(const WeightView &w, const WeightView &w2, const ActView &a, int row0, float *y,
+                              long long y_stride, int *dump, int *status, int early, cudaStream_t stream,
+                              const Exchange &ex, const Epilogue &ep)
 {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kernel = matvec_kernel<FMT, M, DUMP>;
+    auto kernel = matvec_kernel<FMT, M, DUMP, DUAL>;
     if (dev < 64 && !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FV_MAX_SMEM);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
     const int warps = matvec_warps(w);
-    return launch_pdl(kernel, dim3(w.n_pad / 16), dim3(warps * 32), matvec_smem(FMT, warps, M, w.k_pad), stream, w, a,
-                      row0, y, y_stride, dump, status, early, ex, ep);
+    return launch_pdl(kernel, dim3(w.n_pad / 16), dim3(warps * 32), matvec_smem(FMT, warps, M, w.k_pad, DUAL), stream, w, w2,
+                      a, row0, y, y_stride, dump, status, early, ex, ep);
 }
 
 template <int FMT>
-static cudaError_t launch_fmt(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                              int *dump, int *status, int early, cudaStream_t stream, const Exchange &ex, const Epilogue &ep)
+static cudaError_t launch_fmt(const WeightView &w, const WeightView *w2, const ActView &a, int row0, int rows, float *y,
+                              long long y_stride, int *dump, int *status, int early, cudaStream_t stream,
+                              const Exchange &ex, const Epilogue &ep)
 {
 #define SLC_ROWS(MM)                                                                        \
     case MM:                                                                                \
-        return dump ? launch_one<FMT, MM, true>(w, a, row0, y, y_stride, dump, status, early, stream, ex, ep)      \
-                    : launch_one<FMT, MM, false>(w, a, row0, y, y_stride, nullptr, status, early, stream, ex, ep);
+        if (w2) return launch_one<FMT, MM, false, true>(w, *w2, a, row0, y, y_stride, nullptr, status, early, stream, ex, ep); \
+        return dump ? launch_one<FMT, MM, true, false>(w, w, a, row0, y, y_stride, dump, status, early, stream, ex, ep)      \
+                    : launch_one<FMT, MM, false, false>(w, w, a, row0, y, y_stride, nullptr, status, early, stream, ex, ep);
     switch (rows) {
         SLC_ROWS(1) SLC_ROWS(2) SLC_ROWS(3) SLC_ROWS(4)
     default: return cudaErrorInvalidValue;
@@ -577,10 +602,11 @@ static cudaError_t launch_fmt(const WeightView &w, const ActView &a, int row0, i
 // rows 1..4 starting at activation row row0; dump (optional) receives [rows][n][k/32] block dots.
 cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
                           int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange,
-                          const Epilogue *epilogue)
+                          const Epilogue *epilogue, const WeightView *w2)
 {
     if (w.n_pad == 0 || rows == 0) return cudaSuccess;
     const Epilogue ep = epilogue ? *epilogue : Epilogue{ nullptr, nullptr, 0 };
+    if (w2 && (dump || exchange || w2->fmt != w.fmt || w2->n != w.n || w2->k != w.k)) return cudaErrorInvalidValue;
     Exchange ex{};
     if (exchange) {
         ex = *exchange;
@@ -588,10 +614,10 @@ cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int r
         if (early || rows > SLC_LL_ROWS || w.n_pad > ex.n_stride) return cudaErrorInvalidValue;
     }
     switch (w.fmt) {
-    case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
-    case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
-    case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
-    case FMT_Q6_K: return launch_fmt<FMT_Q6_K>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
+    case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(w, w2, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
+    case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(w, w2, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
+    case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(w, w2, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
+    case FMT_Q6_K: return launch_fmt<FMT_Q6_K>(w, w2, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
     default: return cudaErrorInvalidValue;
     }
 }

@@ -80,6 +80,7 @@ SIGNATURES = {
     "slc_weight_shape": (_i32, [_vp, _P(_i32), _P(_i64), _P(_i64), _P(_i64)]),
     "slc_weight_free": (None, [_vp]),
     "slc_matmul_create": (_i32, [_vp, _vp, _i64, _u32, _P(_vp)]),
+    "slc_matmul_create_dual": (_i32, [_vp, _vp, _vp, _i64, _u32, _P(_vp)]),
     "slc_matmul_destroy": (None, [_vp]),
     "slc_matmul_run": (_i32, [_vp, _vp, _i32, _i64, _i64, _i32, _vp, _i64, _i32, _vp]),
     "slc_matmul_set_kernel": (_i32, [_vp, _i32]),

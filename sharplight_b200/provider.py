@@ -338,11 +338,17 @@ class MatMulOp:
     """y = x . W^T for activation rows x and a quantized weight W [N, K] (src/Sharplight.Cpu/MatMulOp.cs:88-160),
     on the integer-dot path at every row count."""
 
-    def __init__(self, device: CudaDevice, weight: DeviceWeight, max_rows: int, *, row_invariant: bool = False):
-        self.device, self.weight, self.max_rows = device, weight, max_rows
+    def __init__(self, device: CudaDevice, weight: DeviceWeight, max_rows: int, *, row_invariant: bool = False,
+                 up: Optional[DeviceWeight] = None):
+        """``up``: a second weight of the same shape; the op then computes silu(x . weight^T) * (x . up^T), the gated
+        FFN's gate / up pair as one MatMul (slc_matmul_create_dual)."""
+        self.device, self.weight, self.max_rows, self.up = device, weight, max_rows, up
         h = C.c_void_p()
         flags = N.MATMUL_ROW_INVARIANT if row_invariant else N.MATMUL_DEFAULT
-        _check(N.load().slc_matmul_create(device.handle, weight.handle, max_rows, flags, C.byref(h)))
+        if up is None:
+            _check(N.load().slc_matmul_create(device.handle, weight.handle, max_rows, flags, C.byref(h)))
+        else:
+            _check(N.load().slc_matmul_create_dual(device.handle, weight.handle, up.handle, max_rows, flags, C.byref(h)))
         self._h = h
 
     @property

@@ -63,3 +63,34 @@ def test_fused_additions_equal_separate_additions(cuda_device, type_name, n, k, 
         for p in [xd, bd, rd] + ys:
             lib.slc_buffer_free(cuda_device.handle, p)
         ex.dispose(); act.dispose(); op.dispose(); w.dispose()
+
+
+@pytest.mark.parametrize("type_name,n,k", [("Q4_K", 200, 1024), ("Q8_0", 100, 1568), ("Q6_K", 72, 512), ("Q4_0", 136, 512)])
+def test_dual_gate_up(cuda_device, type_name, n, k):
+    """slc_matmul_create_dual: y = silu(x . gate^T) * (x . up^T). One dual mat-vec launch up to two rows, the two MatMuls
+    and the element-wise tail above; both against the oracle's two MatMuls followed by the same f32 arithmetic."""
+    from helpers import FMT_OF, MAX_REL, max_rel_error, sl_oracle
+    fmt = FMT_OF[type_name]
+    gate_b, up_b = synth.weight_blocks(type_name, n, k, seed=21), synth.weight_blocks(type_name, n, k, seed=22)
+    gate, up = cuda_device.upload_weight(type_name, (n, k), gate_b), cuda_device.upload_weight(type_name, (n, k), up_b)
+    op = MatMulOp(cuda_device, gate, 100, up=up)
+    try:
+        for rows, launches in ((1, 2), (2, 2), (8, 4), (100, 4)):
+            x = synth.activations(rows, k, seed=30 + rows) * np.float32(3.0)
+            y = op.run(x)
+            g, _, _ = sl_oracle.matmul_intdot(fmt, gate_b, n, k, x)
+            u, _, _ = sl_oracle.matmul_intdot(fmt, up_b, n, k, x)
+            with np.errstate(over="ignore"):
+                ref = (g / (np.float32(1) + np.exp(-g))).astype(np.float32) * u
+            assert y.shape == (rows, n) and max_rel_error(y, ref) <= MAX_REL, (rows, op.last_kernel())
+            got = op.last_kernel()[1]                       # quantization included
+            assert got == launches if rows <= 2 else got >= launches
+        with pytest.raises(Exception):
+            op.block_dots(synth.activations(1, k, seed=1))   # no block-dot export for a pair
+        other = cuda_device.upload_weight(type_name, (n + 16, k), synth.weight_blocks(type_name, n + 16, k, seed=23))
+        with pytest.raises(ValueError):
+            MatMulOp(cuda_device, gate, 4, up=other)
+        other.dispose()
+        assert cuda_device.last_status() == 0
+    finally:
+        op.dispose(); gate.dispose(); up.dispose()
