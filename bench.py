@@ -5,7 +5,7 @@
 One JSON line on stdout (rank 0). Metric: quantized mat-vec HBM GB/s = weight bytes streamed per second, the figure the
 reference's own benchmark reports (tests/Sharplight.Cpu.Tests/BenchTests.cs:82-99 of the Sharplight tree).
 
-Workload at N = 1: BASELINE config 2, the Llama-3-8B FFN shape -- Q4_K weight [14336, 4096], f32 activations ~N(0,1),
+Workload at N = 1: benchmark configuration 2, the Llama-3-8B FFN shape -- Q4_K weight [14336, 4096], f32 activations ~N(0,1),
 M = 1 row. One step = the MatMul (8-bit activation quantization + mat-vec) over each of COPIES independent weight
 matrices of that shape (COPIES x 33 MB is far larger than the 126 MB L2, so every weight byte comes from HBM).
   value : device-resident inputs and outputs, timed with CUDA events on the launching stream.
@@ -189,7 +189,7 @@ def run_reference(args):
 
 
 def prefill_leg(device, torch, N, synth, stream, steps):
-    """BASELINE config 3: Q4_0 [4096, 4096], bf16 activations [2048, 4096] on the tcgen05 int8 GEMM.
+    """benchmark configuration 3: Q4_0 [4096, 4096], bf16 activations [2048, 4096] on the tcgen05 int8 GEMM.
     Operator time = quantization + GEMM (what the reference's published TFLOPS include,
     tests/Sharplight.Vulkan.Tests/BenchTests.cs:28-46); kernel time = the GEMM alone on quantized activations."""
     from sharplight_b200 import MatMulOp, SharedActivation
@@ -250,7 +250,7 @@ def prefill_leg(device, torch, N, synth, stream, steps):
 
 
 class TpStack:
-    """BASELINE config 5: the quantized MatMuls of a Llama-3-70B-shaped layer stack, tensor-parallel over the ranks:
+    """benchmark configuration 5: the quantized MatMuls of a Llama-3-70B-shaped layer stack, tensor-parallel over the ranks:
     q / k / v / gate / up column-split (stacked into one qkv and one gate_up MatMul per layer), o / down row-split with
     an all-reduce (sum) of the f32 partial outputs.
     Attention, norms and the activation function are not on the path: the inputs of o and down are fresh synthetic
@@ -368,7 +368,7 @@ def time_graphed(torch, dist, world, stream, fn, steps, warmup, use_graph=True):
 
 
 def decode_step_leg(args, torch, dist, device, N, synth, stream):
-    """BASELINE config 4: every quantized MatMul of one decode step of a Llama-3-8B-shaped model on one GPU, a
+    """benchmark configuration 4: every quantized MatMul of one decode step of a Llama-3-8B-shaped model on one GPU, a
     continuous batch of 32 sequences: 32 layers of Q4_K weights (qkv, o, gate_up, down) and the Q6_K lm_head
     [128256, 4096]. Attention, norms and sampling are not on the path."""
     from sharplight_b200 import MatMulOp, SharedActivation, tp

@@ -1,7 +1,7 @@
 """Extracts the golden vectors of the quantized-MatMul path from the reference's own test fixtures.
 
-Run in the build container, where the reference tree is mounted (default root: /root/reference, or the first
-argument). It reads
+Run where the reference tree is available: its root is the first argument (or the SHARPLIGHT_REFERENCE environment
+variable). It reads
   tests/Sharplight.Cpu.Tests/Fixtures/ggml_quant_ext.bin  (record layout: GgmlDequantTests.cs:26-48)
   tests/Sharplight.Cpu.Tests/Fixtures/ggml_quant.bin      (record layout: QuantTests.cs:16-43)
 and writes, beside this script, ``ggml_golden.npz`` with the records of ggml types 2 (Q4_0), 8 (Q8_0), 12 (Q4_K) and
@@ -64,7 +64,9 @@ def read_src(path):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SHARPLIGHT_REFERENCE")
+    if not root:
+        raise SystemExit("usage: make_golden.py <root of the Sharplight tree>")
     fx = os.path.join(root, "tests", "Sharplight.Cpu.Tests", "Fixtures")
     here = os.path.dirname(os.path.abspath(__file__))
     arrays = {}

@@ -397,7 +397,7 @@ def test_mmq_exact_int8_activations(cuda_device, type_name):
 
 
 def test_config3_q4_0_prefill_bf16(cuda_device):
-    """BASELINE config 3 at full size: Q4_0 [4096, 4096], bf16 activations [2048, 4096]. The oracle checks a sample of
+    """benchmark configuration 3 at full size: Q4_0 [4096, 4096], bf16 activations [2048, 4096]. The oracle checks a sample of
     the token rows (rows are independent), every weight row; the block dots of a second, smaller sample bit for bit."""
     n, k, rows = 4096, 4096, 2048
     blocks = synth.weight_blocks("Q4_0", n, k, 103)
@@ -440,13 +440,13 @@ def _check_sampled_rows(device, type_name, n, k, rows, seed, sample_n):
 
 
 def test_config4_q6_k_lm_head_batch32(cuda_device):
-    """BASELINE config 4's largest MatMul at full size: the Q6_K lm_head [128256, 4096] for a batch of 32 sequences."""
+    """benchmark configuration 4's largest MatMul at full size: the Q6_K lm_head [128256, 4096] for a batch of 32 sequences."""
     assert _check_sampled_rows(cuda_device, "Q6_K", 128256, 4096, 32, 201, 512) == N.KERNEL_SKINNY
 
 
 @pytest.mark.parametrize("n,k,rows", [(8192, 28672, 1), (8192, 28672, 64), (10240, 8192, 8), (57344, 8192, 1),
                                       (8192, 3584, 1), (1280, 8192, 64)])
 def test_config5_llama70b_shapes(cuda_device, n, k, rows):
-    """BASELINE config 5: the Q4_K MatMuls of a Llama-3-70B-shaped layer at full size, whole (down [8192, 28672],
+    """benchmark configuration 5: the Q4_K MatMuls of a Llama-3-70B-shaped layer at full size, whole (down [8192, 28672],
     stacked qkv [10240, 8192], stacked gate_up [57344, 8192]) and as 8-way tensor-parallel shards."""
     _check_sampled_rows(cuda_device, "Q4_K", n, k, rows, 300 + rows, 256)
