@@ -101,18 +101,6 @@ __device__ __forceinline__ void mq_umma_commit(uint64_t *bar)
 
 // The 32-bit results are declared as f32 registers: the values are used as floats (biased accumulators), and typing them
 // so from the start leaves no integer-to-float register moves behind.
-__device__ __forceinline__ void mq_tmem_ld32(unsigned taddr, float (&r)[32])
-{
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]),
-                   "=f"(r[8]), "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15]),
-                   "=f"(r[16]), "=f"(r[17]), "=f"(r[18]), "=f"(r[19]), "=f"(r[20]), "=f"(r[21]), "=f"(r[22]), "=f"(r[23]),
-                   "=f"(r[24]), "=f"(r[25]), "=f"(r[26]), "=f"(r[27]), "=f"(r[28]), "=f"(r[29]), "=f"(r[30]), "=f"(r[31])
-                 : "r"(taddr) : "memory");
-}
-
 __device__ __forceinline__ void mq_tmem_ld16(unsigned taddr, float (&r)[16])
 {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
