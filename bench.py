@@ -406,6 +406,27 @@ def run_tp(args, torch, dist, device, N, synth, stream, world, rank, local):
     row_counts = sorted(set([args.rows] + ([] if args.tp_main_only else [1, 8, 64, 2048])))
     stack = TpStack(device, torch, dist, N, synth, rank, world, max(row_counts), layers, arch)
     flops_per_row = 2.0 * sum(n * k for _, n, k, _, _ in stack.specs) * layers
+    check = None
+    if world > 1:
+        # the in-kernel sum against the collective library's, on the last layer's row-split outputs of one step
+        sp = stream.cuda_stream
+        check = {}
+        for rows in [r for r in (1, 8) if r <= max(row_counts)]:
+            stack.step(rows, sp, in_kernel=True)
+            torch.cuda.synchronize()
+            mine = {name: stack.y[name][:rows].clone() for name in ("o", "down")}
+            stack.step(rows, sp, in_kernel=False)
+            torch.cuda.synchronize()
+            worst, same = 0.0, True
+            for name, got in mine.items():
+                ref = stack.y[name][:rows]
+                worst = max(worst, float(((got - ref).abs().max() / ref.abs().max().clamp_min(1e-30)).item()))
+                everyone = [torch.empty_like(got) for _ in range(world)]
+                dist.all_gather(everyone, got)
+                same = same and all(torch.equal(everyone[0], e) for e in everyone[1:])
+            t = torch.tensor([worst], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            check[rows] = {"max_diff_vs_nccl_over_max_abs": float(t.item()), "bit_identical_on_all_ranks": same}
     for rows in row_counts:
         steps = max(3, min(args.steps, 20 if rows <= 64 else 5))
         ms = time_graphed(torch, dist, world, stream, lambda sp, r=rows: stack.step(r, sp), steps, 3,
@@ -423,8 +444,11 @@ def run_tp(args, torch, dist, device, N, synth, stream, world, rank, local):
             out[rows]["ms_per_step_nccl" if in_kernel else "ms_per_step_in_kernel"] = other
     stack.dispose()
     torch.cuda.synchronize()
-    return {"workload": f"configs[4]: Llama-3-70B-shaped stack, {layers} layers, Q4_K, tensor parallel x{world}",
-            "weight_bytes_per_step": tp.layer_weight_bytes(arch) * layers, "by_rows": out}
+    res = {"workload": f"configs[4]: Llama-3-70B-shaped stack, {layers} layers, Q4_K, tensor parallel x{world}",
+           "weight_bytes_per_step": tp.layer_weight_bytes(arch) * layers, "by_rows": out}
+    if check is not None:
+        res["in_kernel_allreduce_check"] = check
+    return res
 
 
 def run_ours(args):
