@@ -451,6 +451,16 @@ def run_tp(args, torch, dist, device, N, synth, stream, world, rank, local):
     return res
 
 
+def tp_roofline(per_gpu_gbs: float):
+    """The N > 1 line's roofline object: the whole step, not one kernel -- every GPU streams its shard of the weights
+    once per step, so per-GPU weight bytes over the step time against the measured HBM peak says how much of the step
+    is streaming and how much is the latency of its chain of dependent launches."""
+    peak, kind = measured_peaks()
+    return {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
+            "traffic": None, "peak_source": kind,
+            "what": "per-GPU weight bytes of one step / step time (all launches and sums of the step, not one kernel)"}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -490,6 +500,7 @@ def run_ours(args):
                                "l2": f"inputs larger than L2: {tpr['weight_bytes_per_step'] / world / 1e9:.1f} GB of weights per GPU per step",
                                "launch": "host launches" if args.no_graph else "CUDA graph replay of the step"},
                     "gpu_launches": main["launches_per_step"] * max(3, min(args.steps, 20)),
+                    "roofline": tp_roofline(main["weight_gbs"] / world),
                     "tp_stack": tpr, "clocks": clocks,
                     "e2e": {"value": main["weight_gbs"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                             "note": "activations of this workload are device-resident by construction (they come from the "
