@@ -258,6 +258,9 @@ SLC_API void slc_tp_exchange_destroy(slc_tp_exchange *exchange);
 SLC_API slc_result slc_tp_exchange_set_wait_ms(slc_tp_exchange *exchange, int32_t milliseconds);
 /* y (device, f32) = sum over ranks of (act . W^T), W being this rank's K range of the weight and act this rank's
    matching slice of the activations. Asynchronous on the stream. */
+/* The same with x not yet quantized (device, rows x k): slc_matmul_run with the sum over the ranks. */
+SLC_API slc_result slc_matmul_run_allreduce(slc_matmul *op, slc_tp_exchange *exchange, const void *x_device, int32_t x_dtype,
+                                            int64_t rows, int64_t x_stride, float *y_device, int64_t y_stride, void *stream);
 SLC_API slc_result slc_matmul_run_quantized_allreduce(slc_matmul *op, slc_activation *act, slc_tp_exchange *exchange,
                                                       float *y_device, int64_t y_stride, void *stream);
 

@@ -752,12 +752,25 @@ slc_result slc_matmul_run_quantized_allreduce(slc_matmul *op, slc_activation *ac
     return run_kernels(op, act, y, y_stride, nullptr, s, &x->view);
 }
 
-static slc_result ensure_op_buffers(slc_matmul *op, bool need_x_stage, bool need_y_stage)
+// x -> y through the op's own activation object (created at first use).
+static slc_result quantize_and_run(slc_matmul *op, const Exchange *ex, const void *x_dev, int32_t x_dtype, int64_t rows,
+                                   int64_t x_stride, float *y_dev, int64_t y_stride, cudaStream_t s)
 {
+    slc_result r;
     if (!op->act) {
-        slc_result r = slc_activation_create(op->dev, op->max_rows, op->w->k, &op->act);
+        r = slc_activation_create(op->dev, op->max_rows, op->w->k, &op->act);
         if (r != SLC_OK) return r;
     }
+    r = slc_activation_quantize(op->act, x_dev, x_dtype, rows, x_stride, s);
+    if (r != SLC_OK) return r;
+    r = run_kernels(op, op->act, y_dev, y_stride, nullptr, s, ex);
+    if (r != SLC_OK) return r;
+    op->last_launches_total = op->last_launches + 1;
+    return SLC_OK;
+}
+
+static slc_result ensure_op_buffers(slc_matmul *op, bool need_x_stage, bool need_y_stage)
+{
     if (need_x_stage && !op->x_stage) SLC_CUDA(cudaMalloc(&op->x_stage, (size_t)op->max_rows * op->w->k * 4));
     if (need_y_stage && !op->y_stage) {
         SLC_CUDA(cudaMalloc(&op->y_stage, (size_t)op->max_rows * (op->w->n > 0 ? op->w->n : 1) * 4));
@@ -792,17 +805,35 @@ slc_result slc_matmul_run(slc_matmul *op, const void *x, int32_t x_dtype, int64_
     if (n == 0) return SLC_OK;
     float *y_dev = y_is_device ? y : op->y_stage;
     const long long ys = y_is_device ? y_stride : n;
-    r = slc_activation_quantize(op->act, x_dev, x_dtype, rows, xs, s);
+    r = quantize_and_run(op, nullptr, x_dev, x_dtype, rows, xs, y_dev, ys, s);
     if (r != SLC_OK) return r;
-    r = run_kernels(op, op->act, y_dev, ys, nullptr, s);
-    if (r != SLC_OK) return r;
-    op->last_launches_total = op->last_launches + 1;
     if (!y_is_device) {
         SLC_CUDA(cudaMemcpy2DAsync(y, (size_t)y_stride * 4, y_dev, (size_t)n * 4, (size_t)n * 4, (size_t)rows,
                                    cudaMemcpyDeviceToHost, s));
         SLC_CUDA(cudaStreamSynchronize(s));
     }
     return SLC_OK;
+}
+
+slc_result slc_matmul_run_allreduce(slc_matmul *op, slc_tp_exchange *x, const void *x_device, int32_t x_dtype, int64_t rows,
+                                    int64_t x_stride, float *y, int64_t y_stride, void *stream)
+{
+    if (!op || !x) return fail(SLC_ERR_INVALID_ARGUMENT, "null op or exchange");
+    if (x->dev != op->dev) return fail(SLC_ERR_INVALID_ARGUMENT, "op and exchange live on different devices");
+    if (!x->connected) return fail(SLC_ERR_INVALID_STATE, "the exchange is not connected");
+    if (x_dtype != SLC_F32 && x_dtype != SLC_BF16) return fail(SLC_ERR_UNSUPPORTED, "activation dtype must be f32 or bf16");
+    if (rows < 0) return fail(SLC_ERR_INVALID_ARGUMENT, "rows < 0");
+    if (rows > op->max_rows) return fail(SLC_ERR_INVALID_STATE, "rows exceed the op's compiled bound");
+    if (rows > x->max_rows) return fail(SLC_ERR_UNSUPPORTED, "rows exceed the exchange's bound");
+    if (op->w->n > x->n) return fail(SLC_ERR_INVALID_ARGUMENT, "the weight has more rows than the exchange was created for");
+    if (rows == 0 || op->w->n == 0) return SLC_OK;
+    if (!x_device || x_stride < op->w->k) return fail(SLC_ERR_INVALID_ARGUMENT, "bad activation buffer or stride");
+    if (!y || y_stride < op->w->n) return fail(SLC_ERR_INVALID_ARGUMENT, "bad output buffer or stride");
+    SLC_CUDA(cudaSetDevice(op->dev->index));
+    cudaStream_t s = stream ? (cudaStream_t)stream : op->dev->stream;
+    slc_result r = ensure_op_buffers(op, false, false);
+    if (r != SLC_OK) return r;
+    return quantize_and_run(op, &x->view, x_device, x_dtype, rows, x_stride, y, y_stride, s);
 }
 
 // ---- parity exports --------------------------------------------------------------------------------------------------
@@ -859,6 +890,10 @@ slc_result slc_debug_block_dots(slc_matmul *op, const void *x, int32_t x_dtype, 
     cudaError_t e = cudaMemsetAsync(dump, 0xff, dump_bytes, d->stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(op->x_stage, x, (size_t)rows * k * esz, cudaMemcpyHostToDevice, d->stream);
     if (e != cudaSuccess) { cudaFree(dump); return cuda_fail(e, "slc_debug_block_dots"); }
+    if (!op->act) {
+        r = slc_activation_create(op->dev, op->max_rows, op->w->k, &op->act);
+        if (r != SLC_OK) { cudaFree(dump); return r; }
+    }
     r = slc_activation_quantize(op->act, op->x_stage, x_dtype, rows, k, d->stream);
     if (r == SLC_OK) r = run_kernels(op, op->act, op->y_stage, n, dump, d->stream);
     if (r == SLC_OK) {

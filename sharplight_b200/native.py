@@ -93,6 +93,7 @@ SIGNATURES = {
     "slc_tp_exchange_connect": (_i32, [_vp, _vp]),
     "slc_tp_exchange_destroy": (None, [_vp]),
     "slc_tp_exchange_set_wait_ms": (_i32, [_vp, _i32]),
+    "slc_matmul_run_allreduce": (_i32, [_vp, _vp, _vp, _i32, _i64, _i64, _vp, _i64, _vp]),
     "slc_matmul_run_quantized_allreduce": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp]),
     "slc_matmul_run_quantized_epilogue": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp]),
     "slc_matmul_run_static": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp, _i64, _vp]),

@@ -474,6 +474,12 @@ class TpExchange:
         _check(N.load().slc_matmul_run_quantized_allreduce(op.handle, act.handle, self.handle, C.c_void_p(y_device_ptr),
                                                            y_stride, C.c_void_p(stream) if stream else None))
 
+    def run(self, op: MatMulOp, x_device_ptr: int, dtype: int, rows: int, x_stride: int, y_device_ptr: int,
+            y_stride: int, stream: int = 0) -> None:
+        """y = sum over ranks of x . W^T with x not yet quantized (slc_matmul_run_allreduce)."""
+        _check(N.load().slc_matmul_run_allreduce(op.handle, self.handle, C.c_void_p(x_device_ptr), dtype, rows, x_stride,
+                                                 C.c_void_p(y_device_ptr), y_stride, C.c_void_p(stream) if stream else None))
+
     def dispose(self) -> None:
         if self._h is not None:
             N.load().slc_tp_exchange_destroy(self._h)
