@@ -52,6 +52,11 @@ def test_group_of_one_gives_the_plain_result(cuda_device, type_name, n, k):
             ex.matmul(op, act, y1.value, n)
             plain, summed = _read(lib, cuda_device, y0, (rows, n)), _read(lib, cuda_device, y1, (rows, n))
             assert np.array_equal(plain.view(np.uint32), summed.view(np.uint32)), (rows, op.last_kernel())
+            # the same from rows that have not been quantized yet (slc_matmul_run_allreduce)
+            y2 = _dev(lib, cuda_device, np.full((rows, n), np.nan, np.float32))
+            ex.run(op, xd.value, N.F32, rows, k, y2.value, n)
+            assert np.array_equal(plain.view(np.uint32), _read(lib, cuda_device, y2, (rows, n)).view(np.uint32)), rows
+            lib.slc_buffer_free(cuda_device.handle, y2)
             for p in (xd, y0, y1):
                 lib.slc_buffer_free(cuda_device.handle, p)
         assert cuda_device.last_status() == 0
