@@ -226,9 +226,11 @@ __device__ __forceinline__ void mq_store(const MqRegs<FMT> &rr, int rgl, int lan
             const unsigned wv[4] = { q.x, q.y, q.z, q.w };
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                // codes minus 8 as signed bytes: the block dot needs no offset term
-                const unsigned lo = __vsub4(wv[j] & 0x0F0F0F0Fu, 0x08080808u);
-                const unsigned hi = __vsub4((wv[j] >> 4) & 0x0F0F0F0Fu, 0x08080808u);
+                // 16 * (code - 8) as signed bytes, one logic operation per four codes: the nibble moved to (or left in)
+                // the byte's high half is 16 * code, and flipping the top bit subtracts 128. The block dot needs no
+                // offset term; the factor 16 is taken out of the scale table below (exactly: a power of two).
+                const unsigned lo = ((wv[j] << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
+                const unsigned hi = (wv[j] & 0xF0F0F0F0u) ^ 0x80808080u;
                 const int blk = 2 * i + (j >> 1);
                 uint8_t *dst = ((j & 1) ? row_hi : row_lo) + (2 * blk) * 128 + 4 * t;
                 *reinterpret_cast<unsigned *>(dst) = lo;
@@ -251,10 +253,11 @@ __device__ __forceinline__ void mq_store(const MqRegs<FMT> &rr, int rgl, int lan
     if constexpr (FMT == FMT_Q8_0 || FMT == FMT_Q4_0) {
         const unsigned w0 = t == 0 ? s0.x : t == 1 ? s0.y : t == 2 ? s0.z : s0.w;
         const unsigned w1 = t == 0 ? s1.x : t == 1 ? s1.y : t == 2 ? s1.z : s1.w;
-        dw_lo[(2 * t) * MQ_TILE_N] = mq_h2f(w0 & 0xffffu);
-        dw_lo[(2 * t + 1) * MQ_TILE_N] = mq_h2f(w0 >> 16);
-        dw_hi[(2 * t) * MQ_TILE_N] = mq_h2f(w1 & 0xffffu);
-        dw_hi[(2 * t + 1) * MQ_TILE_N] = mq_h2f(w1 >> 16);
+        constexpr float unit = FMT == FMT_Q4_0 ? 0.0625f : 1.0f;   // the Q4_0 codes are stored times 16
+        dw_lo[(2 * t) * MQ_TILE_N] = mq_h2f(w0 & 0xffffu) * unit;
+        dw_lo[(2 * t + 1) * MQ_TILE_N] = mq_h2f(w0 >> 16) * unit;
+        dw_hi[(2 * t) * MQ_TILE_N] = mq_h2f(w1 & 0xffffu) * unit;
+        dw_hi[(2 * t + 1) * MQ_TILE_N] = mq_h2f(w1 >> 16) * unit;
     } else {
         float *dm_lo = dms + rgl * 16 + g, *dm_hi = dm_lo + 8;
 #pragma unroll
@@ -432,7 +435,8 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
                         if (tok < a.rows && row < w.n && i * 32 < w.k) {
                             const int cexp = FMT == FMT_Q8_0 ? 128 : FMT == FMT_Q4_0 ? 8 : 0;
                             const int add = cexp ? cexp * __ldg(&a.isum[(long long)tok * (a.k_pad >> 5) + i]) : 0;
-                            dump[((long long)tok * w.n + row) * (w.k >> 5) + i] = __float_as_int(sv[j]) - MQ_BIAS + add;
+                            const int dot = __float_as_int(sv[j]) - MQ_BIAS;   // Q4_0: 16 times the dot, exactly
+                            dump[((long long)tok * w.n + row) * (w.k >> 5) + i] = (FMT == FMT_Q4_0 ? dot >> 4 : dot) + add;
                         }
                     }
                 }

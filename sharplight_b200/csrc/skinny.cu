@@ -102,7 +102,8 @@ struct SkCtx
     int row0, rg, g, t;
     int *dump;
 
-    __device__ __forceinline__ void export_tile(int blk, int nt, const int c[4], int c_export) const
+    // shift: the tile holds the dots times 2^shift (Q4_0 multiplies its codes by 16)
+    __device__ __forceinline__ void export_tile(int blk, int nt, const int c[4], int c_export, int shift = 0) const
     {
         if (!DUMP) return;
 #pragma unroll
@@ -112,7 +113,7 @@ struct SkCtx
             const int tok = row0 + m;
             if (row < w.n && tok < a.rows && blk * 32 < w.k) {
                 const int add = c_export ? c_export * __ldg(&a.isum[(long long)tok * (a.k_pad >> 5) + blk]) : 0;
-                dump[((long long)m * w.n + row) * (w.k >> 5) + blk] = c[e] - SK_BIAS + add;
+                dump[((long long)m * w.n + row) * (w.k >> 5) + blk] = ((c[e] - SK_BIAS) >> shift) + add;
             }
         }
     }
@@ -180,7 +181,9 @@ __device__ __forceinline__ void sk_compute(const SkRec<FMT> &rec, const SkTile<N
         const unsigned s0w[4] = { rec.s0.x, rec.s0.y, rec.s0.z, rec.s0.w }, s1w[4] = { rec.s1.x, rec.s1.y, rec.s1.z, rec.s1.w };
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            const float dw[2] = { sk_h2f((s0w[i >> 1] >> (16 * (i & 1))) & 0xffffu), sk_h2f((s1w[i >> 1] >> (16 * (i & 1))) & 0xffffu) };
+            constexpr float unit = FMT == FMT_Q4_0 ? 0.0625f : 1.0f;   // the Q4_0 codes enter the MMA times 16
+            const float dw[2] = { sk_h2f((s0w[i >> 1] >> (16 * (i & 1))) & 0xffffu) * unit,
+                                  sk_h2f((s1w[i >> 1] >> (16 * (i & 1))) & 0xffffu) * unit };
             const float cb[2] = { -SK_BIAS_F * dw[0], -SK_BIAS_F * dw[1] };   // exact: d_w has an 11-bit significand
             unsigned a0, a1, a2, a3;
             if constexpr (FMT == FMT_Q8_0) {
@@ -188,11 +191,12 @@ __device__ __forceinline__ void sk_compute(const SkRec<FMT> &rec, const SkTile<N
             } else {
                 const unsigned wg = (i & 1) ? rec.q[i >> 1].z : rec.q[i >> 1].x;
                 const unsigned wg8 = (i & 1) ? rec.q[i >> 1].w : rec.q[i >> 1].y;
-                // codes minus 8 as signed bytes: no offset term
-                a0 = __vsub4(wg & 0x0F0F0F0Fu, 0x08080808u);
-                a1 = __vsub4(wg8 & 0x0F0F0F0Fu, 0x08080808u);
-                a2 = __vsub4((wg >> 4) & 0x0F0F0F0Fu, 0x08080808u);
-                a3 = __vsub4((wg8 >> 4) & 0x0F0F0F0Fu, 0x08080808u);
+                // 16 * (code - 8) as signed bytes, one logic operation per four codes (the nibble in the byte's high
+                // half is 16 * code, flipping the top bit subtracts 128): no offset term, the 16 leaves through dw
+                a0 = ((wg << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
+                a1 = ((wg8 << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
+                a2 = (wg & 0xF0F0F0F0u) ^ 0x80808080u;
+                a3 = (wg8 & 0xF0F0F0F0u) ^ 0x80808080u;
             }
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
@@ -212,7 +216,7 @@ __device__ __forceinline__ void sk_compute(const SkRec<FMT> &rec, const SkTile<N
                 acc[nt][1] = fmaf(fmaf(__int_as_float(cc[1]), dw[0], cb[0]), ds.z, acc[nt][1]);
                 acc[nt][2] = fmaf(fmaf(__int_as_float(cc[2]), dw[1], cb[1]), ds.x, acc[nt][2]);
                 acc[nt][3] = fmaf(fmaf(__int_as_float(cc[3]), dw[1], cb[1]), ds.z, acc[nt][3]);
-                c.export_tile(st * 8 + i, nt, cc, FMT == FMT_Q8_0 ? 128 : 8);
+                c.export_tile(st * 8 + i, nt, cc, FMT == FMT_Q8_0 ? 128 : 8, FMT == FMT_Q4_0 ? 4 : 0);
             }
         }
     } else {  // Q6_K
