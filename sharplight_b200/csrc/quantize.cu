@@ -37,8 +37,15 @@ __global__ void __launch_bounds__(256) quantize_kernel(const void *__restrict__ 
                 for (int i = 0; i < 4; i++) v[i] = x[i];
             }
         } else {
-            const __nv_bfloat16 *x = (const __nv_bfloat16 *)xv + base;
-            for (int i = 0; i < 4; i++) v[i] = __bfloat162float(x[i]);  // exact widening
+            // bf16 -> f32 is exact: the 16 bits become the high half of the f32
+            const unsigned short *x = (const unsigned short *)xv + base;
+            if ((((uintptr_t)x) & 7) == 0) {
+                const uint2 u = *reinterpret_cast<const uint2 *>(x);   // four values in one 8-byte load
+                v[0] = __uint_as_float(u.x << 16); v[1] = __uint_as_float(u.x & 0xffff0000u);
+                v[2] = __uint_as_float(u.y << 16); v[3] = __uint_as_float(u.y & 0xffff0000u);
+            } else {
+                for (int i = 0; i < 4; i++) v[i] = __uint_as_float((unsigned)x[i] << 16);
+            }
         }
     }
     float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
