@@ -389,7 +389,6 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
             const float *dxs = stage_dx(s) + b * MQ_TILE_T + c0, *sxs = stage_sx(s) + b * MQ_TILE_T + c0;
             const float dwv = stage_dw(s)[b * MQ_TILE_N + r];
             const float dmv = HAS_MIN ? -stage_dm(s)[b * MQ_TILE_N + r] : 0.0f;
-            // (biased - 12582912) * d_w as one FMA: the constant -12582912 * d_w is exact when d_w comes from an f16
             const float cw = -MQ_BIAS_F * dwv;
             // the slice in two halves of 16 columns: 16 result registers live at a time
 #pragma unroll
@@ -417,13 +416,11 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
                     for (int e = 0; e < 4; e++) {
                         const float f = sv[j4 * 4 + e];
                         float v = acc[h * 16 + j4 * 4 + e];
-                        if (HAS_MIN) {
-                            // d_w = d * sc is a rounded product: keep the subtraction exact, then scale
-                            v = fmaf((f - MQ_BIAS_F) * dwv, dxv[e], v);
-                            v = fmaf(dmv, sxv[e], v);
-                        } else {
-                            v = fmaf(fmaf(f, dwv, cw), dxv[e], v);
-                        }
+                        // (f - 12582912) * d_w in one FMA: -12582912 * d_w is exact for every format here -- d_w is an
+                        // f16 (11 significant bits), or for Q4_K the product of an f16 and a 6-bit integer (17 bits,
+                        // itself exact in f32), and the constant 1.5 * 2^23 adds one bit
+                        v = fmaf(fmaf(f, dwv, cw), dxv[e], v);
+                        if (HAS_MIN) v = fmaf(dmv, sxv[e], v);
                         acc[h * 16 + j4 * 4 + e] = v;
                     }
                 }
