@@ -333,11 +333,18 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
     const long long mq_kernel_t0 = clock64();
 #endif
 
-    // Register budget: 80 per thread at launch (768 threads). The MMA issuer's warpgroup gives back all but 24; the
-    // epilogue takes 88 and the producers (two weight records in registers) 104: 4 x 88 + 104 + 24 = 6 x 80.
-    if (warp >= MQ_EPI_WARPS + MQ_PROD_WARPS) asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
-    else if (warp >= MQ_EPI_WARPS) asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
-    else asm volatile("setmaxnreg.inc.sync.aligned.u32 88;");
+    // Register budget: 80 per thread at launch (768 threads). The MMA issuer's warpgroup gives back all but 24. The
+    // producers of Q8_0 (two 4352-byte records in registers) and Q4_K (scale decoding) take 104, leaving 88 to the
+    // epilogue; Q4_0's need 72 and its epilogue gets 96 (no spills). Either way 4 x epilogue + producers + 24 = 6 x 80.
+    if (warp >= MQ_EPI_WARPS + MQ_PROD_WARPS) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
+    } else if (warp >= MQ_EPI_WARPS) {
+        if constexpr (FMT != FMT_Q4_0) asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+        else asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    } else {
+        if constexpr (FMT != FMT_Q4_0) asm volatile("setmaxnreg.inc.sync.aligned.u32 88;");
+        else asm volatile("setmaxnreg.inc.sync.aligned.u32 96;");
+    }
 
     if (warp < MQ_EPI_WARPS) {
         // ===== epilogue: 16 warps, four per scheduler; warp = (TMEM lane quarter, 32-column slice) =====
