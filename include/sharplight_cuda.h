@@ -87,7 +87,8 @@ enum
     SLC_KERNEL_AUTO = 0,
     SLC_KERNEL_MMVQ = 1,     /* dp4a mat-vec, weights streamed once for up to 8 activation rows */
     SLC_KERNEL_SKINNY = 2,   /* int8 mma tiles with the weight as the streamed operand, 9..64 rows */
-    SLC_KERNEL_MMQ = 3       /* tcgen05 / TMEM int8 GEMM for prefill */
+    SLC_KERNEL_MMQ = 3,      /* tcgen05 / TMEM int8 GEMM for prefill */
+    SLC_KERNEL_TILE = 4      /* tcgen05 / TMEM tiles on exact f16-coded integers, stream-K, 3 rows and more (the default there) */
 };
 
 typedef struct slc_device slc_device;

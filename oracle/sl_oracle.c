@@ -541,3 +541,323 @@ int slo_matmul_f64(int fmt, const uint8_t *w, int64_t n, int64_t k, const float 
     for (int i = 1; i < used; i++) pthread_join(tid[i], NULL);
     return 0;
 }
+
+/* ---- parallel loops: the reference's CpuParallel.For over its spinning pool ------------------------------------------
+ * src/Sharplight.Cpu/CpuParallel.cs:34-66 (For), CpuThreadPool.cs:48-114 (persistent workers that spin for a while after
+ * the last job, then block), CpuThreadJob.cs:14-95 (one contiguous range of items per participant, the caller being
+ * participant 0; own range first, then the others'; items claimed count / (participants * 8) at a time). */
+
+#include <stdatomic.h>
+#include <time.h>
+
+typedef void (*slo_body)(int item, void *ctx);
+
+#define POOL_MAX 256
+#define POOL_STRIDE 16   /* longs between two counters: 128 bytes */
+
+typedef struct {
+    slo_body body;
+    void *ctx;
+    int count, participants, ranges, batch;
+    _Atomic long counters[(POOL_MAX + 2) * POOL_STRIDE];   /* [(r + 1) * stride]: next item of range r; last: items done */
+} pool_job;
+
+static struct {
+    pthread_mutex_t gate;
+    pthread_cond_t wake;
+    pthread_t tid[POOL_MAX];
+    int workers;
+    _Atomic long generation;
+    pool_job *_Atomic job;
+    pthread_mutex_t busy;
+    int ready;
+} g_pool = { PTHREAD_MUTEX_INITIALIZER, PTHREAD_COND_INITIALIZER, {0}, 0, 0, NULL, PTHREAD_MUTEX_INITIALIZER, 0 };
+
+static long range_start(const pool_job *j, int r) { return (long)j->count * r / j->ranges; }
+
+static void job_work(pool_job *j, int participant)
+{
+    int own = participant % j->ranges;
+    for (int k = 0; k < j->ranges; k++) {
+        int r = (own + k) % j->ranges;
+        long end = range_start(j, r + 1);
+        _Atomic long *next = &j->counters[(r + 1) * POOL_STRIDE];
+        long start;
+        while (atomic_load(next) < end && (start = atomic_fetch_add(next, j->batch)) < end) {
+            long stop = start + j->batch < end ? start + j->batch : end;
+            for (long i = start; i < stop; i++) j->body((int)i, j->ctx);
+            atomic_fetch_add(&j->counters[(j->ranges + 1) * POOL_STRIDE], stop - start);
+        }
+    }
+}
+
+static double now_s(void)
+{
+    struct timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return ts.tv_sec + 1e-9 * ts.tv_nsec;
+}
+
+static void *pool_worker(void *arg)
+{
+    int id = (int)(intptr_t)arg;
+    long seen = 0;
+    for (;;) {
+        /* spin for a while after the last job, then block until the generation changes */
+        double start = now_s();
+        int checks = 0;
+        long gen;
+        for (;;) {
+            gen = atomic_load(&g_pool.generation);
+            if (gen != seen) break;
+            for (volatile int s = 0; s < 16; s++) { }
+            if (++checks % 64 == 0 && now_s() - start > 2e-3) {
+                pthread_mutex_lock(&g_pool.gate);
+                while ((gen = atomic_load(&g_pool.generation)) == seen) pthread_cond_wait(&g_pool.wake, &g_pool.gate);
+                pthread_mutex_unlock(&g_pool.gate);
+                break;
+            }
+        }
+        seen = gen;
+        pool_job *j = atomic_load(&g_pool.job);
+        if (j && id < j->participants) job_work(j, id + 1);
+    }
+    return NULL;
+}
+
+/* body(0 .. count-1) on the caller and up to threads - 1 pool workers. Not reentrant: callers serialize. */
+static void pool_for(int count, int threads, slo_body body, void *ctx)
+{
+    if (count <= 0) return;
+    if (threads > POOL_MAX) threads = POOL_MAX;
+    if (count == 1 || threads <= 1) {
+        for (int i = 0; i < count; i++) body(i, ctx);
+        return;
+    }
+    pthread_mutex_lock(&g_pool.busy);
+    while (g_pool.workers < threads - 1) {
+        pthread_create(&g_pool.tid[g_pool.workers], NULL, pool_worker, (void *)(intptr_t)g_pool.workers);
+        pthread_detach(g_pool.tid[g_pool.workers]);
+        g_pool.workers++;
+    }
+    int helpers = (count < threads ? count : threads) - 1;
+    static pool_job job;   /* one job at a time (busy lock) */
+    job.body = body; job.ctx = ctx; job.count = count; job.participants = helpers;
+    job.ranges = count < helpers + 1 ? count : helpers + 1;
+    if (job.ranges < 1) job.ranges = 1;
+    job.batch = count / ((helpers + 1) * 8);
+    if (job.batch < 1) job.batch = 1;
+    for (int r = 0; r < job.ranges; r++) atomic_store(&job.counters[(r + 1) * POOL_STRIDE], range_start(&job, r));
+    atomic_store(&job.counters[(job.ranges + 1) * POOL_STRIDE], 0);
+    pthread_mutex_lock(&g_pool.gate);
+    atomic_store(&g_pool.job, &job);
+    atomic_fetch_add(&g_pool.generation, 1);
+    pthread_cond_broadcast(&g_pool.wake);
+    pthread_mutex_unlock(&g_pool.gate);
+    job_work(&job, 0);
+    while (atomic_load(&job.counters[(job.ranges + 1) * POOL_STRIDE]) < count) { }
+    /* a worker that woke late may still look at the job: it finds every range exhausted and touches nothing else */
+    pthread_mutex_unlock(&g_pool.busy);
+}
+
+/* ---- the integer-dot driver with the reference's chunking (MatMulOp.RunIntDot, src/Sharplight.Cpu/MatMulOp.cs:174-213):
+ * chunks = clamp(N / 16, 1, threads * 4), rows per chunk = ceil(N / chunks), one pool item per chunk. */
+
+typedef struct {
+    intdot_job base;
+    int64_t per_chunk;
+} intdot_chunks;
+
+static void intdot_chunk_body(int c, void *ctx)
+{
+    intdot_chunks *jc = (intdot_chunks *)ctx;
+    intdot_job jb = jc->base;
+    jb.n0 = c * jc->per_chunk;
+    jb.n1 = jb.n0 + jc->per_chunk < jb.n ? jb.n0 + jc->per_chunk : jb.n;
+    if (jb.n0 < jb.n1) intdot_worker(&jb);
+}
+
+int slo_matmul_intdot_pooled(int fmt, const uint8_t *w, int64_t n, int64_t k, const float *x, int64_t m, float *y,
+                             int threads, int tier)
+{
+    int bs = slo_block_size(fmt);
+    if (bs == 0 || k <= 0 || k % bs != 0 || n < 0 || m < 0) return -1;
+    if (n == 0 || m == 0) return 0;
+    if (threads < 1) threads = 1;
+    if (threads > POOL_MAX) threads = POOL_MAX;
+    int8_t *q = (int8_t *)aligned_alloc(64, (size_t)align64(m * k));
+    float *d = (float *)aligned_alloc(64, (size_t)align64(m * (k / 32) * 4));
+    float *gs = (float *)aligned_alloc(64, (size_t)align64(m * (k / 16) * 4));
+    float *lane = (float *)aligned_alloc(64, (size_t)align64(m * (k / 4) * 4));
+    for (int64_t t = 0; t < m; t++) {
+        slo_quantize_row(x + t * k, k, q + t * k, d + t * (k / 32), gs + t * (k / 16));
+        for (int64_t i = 0; i < k / 4; i++) lane[t * (k / 4) + i] = d[t * (k / 32) + i / 8];
+    }
+    int64_t chunks = n / 16;
+    if (chunks < 1) chunks = 1;
+    if (chunks > (int64_t)threads * 4) chunks = (int64_t)threads * 4;
+    intdot_chunks jc = { { fmt, tier ? fast_tier() : 0, w, n, k, m, 0, 0, q, d, lane, gs, y, NULL, NULL }, (n + chunks - 1) / chunks };
+    pool_for((int)chunks, threads, intdot_chunk_body, &jc);
+    free(q); free(d); free(gs); free(lane);
+    return 0;
+}
+
+/* ---- the f32 GEMM path the reference takes from 32 rows (MatMulOp.RunGemm / PackBody / GemmBody,
+ * src/Sharplight.Cpu/MatMulOp.cs:218-369; micro-kernel Gemm.K8x32, src/Sharplight.Cpu/Gemm.cs:16-33,210-330):
+ * activations packed as [K][MR] tiles; per task (panel of NR weight rows x block of row tiles): for every KC = 256 slice,
+ * dequantize the panel's rows into B[k][NR], then run the MR x NR micro-kernel over the block's tiles, accumulating in y.
+ * Every output element is one chain of fused multiply-adds over k in order, whatever the tile shape. */
+
+enum { GEMM_KC = 256 };
+
+typedef struct {
+    int fmt, mr, nr;
+    const uint8_t *w;
+    int64_t n, k, m;
+    const float *x;
+    float *y, *apack;
+    int m_tiles, panels, m_blocks, tiles_per_block;
+} gemm_job;
+
+static void gemm_pack_body(int tile, void *ctx)
+{
+    gemm_job *j = (gemm_job *)ctx;
+    int mr = j->mr;
+    int64_t r0 = (int64_t)tile * mr;
+    int rows = j->m - r0 < mr ? (int)(j->m - r0) : mr;
+    float *dst = j->apack + (int64_t)tile * j->k * mr;
+    for (int64_t k = 0; k < j->k; k++)
+        for (int i = 0; i < mr; i++) dst[k * mr + i] = i < rows ? j->x[(r0 + i) * j->k + k] : 0.0f;
+}
+
+static void tile_generic(const float *a, const float *b, int ldb, float *c, int64_t ldc, int kc, int acc, int mr, int nr)
+{
+    float t[8 * 32];
+    for (int i = 0; i < mr; i++)
+        for (int jn = 0; jn < nr; jn++) t[i * nr + jn] = acc ? c[i * ldc + jn] : 0.0f;
+    for (int k = 0; k < kc; k++)
+        for (int i = 0; i < mr; i++)
+            for (int jn = 0; jn < nr; jn++) t[i * nr + jn] = fmaf(a[k * mr + i], b[k * ldb + jn], t[i * nr + jn]);
+    for (int i = 0; i < mr; i++)
+        for (int jn = 0; jn < nr; jn++) c[i * ldc + jn] = t[i * nr + jn];
+}
+
+#if defined(__x86_64__)
+#include <immintrin.h>
+__attribute__((target("avx512f,fma")))
+static void tile_8x32(const float *a, const float *b, int ldb, float *c, int64_t ldc, int kc, int acc)
+{
+    __m512 c0[8], c1[8];
+    for (int i = 0; i < 8; i++) {
+        c0[i] = acc ? _mm512_loadu_ps(c + i * ldc) : _mm512_setzero_ps();
+        c1[i] = acc ? _mm512_loadu_ps(c + i * ldc + 16) : _mm512_setzero_ps();
+    }
+    for (int k = 0; k < kc; k++) {
+        __m512 b0 = _mm512_loadu_ps(b), b1 = _mm512_loadu_ps(b + 16);
+        for (int i = 0; i < 8; i++) {
+            __m512 ai = _mm512_set1_ps(a[i]);
+            c0[i] = _mm512_fmadd_ps(ai, b0, c0[i]);
+            c1[i] = _mm512_fmadd_ps(ai, b1, c1[i]);
+        }
+        a += 8;
+        b += ldb;
+    }
+    for (int i = 0; i < 8; i++) {
+        _mm512_storeu_ps(c + i * ldc, c0[i]);
+        _mm512_storeu_ps(c + i * ldc + 16, c1[i]);
+    }
+}
+static int have_avx512(void) { return __builtin_cpu_supports("avx512f") && __builtin_cpu_supports("fma"); }
+#else
+static int have_avx512(void) { return 0; }
+#endif
+
+static void gemm_tile(const gemm_job *j, const float *a, const float *b, float *c, int kc, int acc, int rows, int cols)
+{
+    int mr = j->mr, nr = j->nr;
+    if (rows == mr && cols == nr) {
+#if defined(__x86_64__)
+        if (mr == 8 && nr == 32) { tile_8x32(a, b, nr, c, j->n, kc, acc); return; }
+#endif
+        tile_generic(a, b, nr, c, j->n, kc, acc, mr, nr);
+        return;
+    }
+    /* partial tile: through a scratch tile, valid part copied (Gemm.TileEdge, Gemm.cs:87-111) */
+    float tmp[8 * 32];
+    for (int i = 0; i < mr; i++)
+        for (int jn = 0; jn < nr; jn++) tmp[i * nr + jn] = (acc && i < rows && jn < cols) ? c[i * j->n + jn] : 0.0f;
+#if defined(__x86_64__)
+    if (mr == 8 && nr == 32) tile_8x32(a, b, nr, tmp, nr, kc, acc);
+    else
+#endif
+        tile_generic(a, b, nr, tmp, nr, kc, acc, mr, nr);
+    for (int i = 0; i < rows; i++)
+        for (int jn = 0; jn < cols; jn++) c[i * j->n + jn] = tmp[i * nr + jn];
+}
+
+static void gemm_body(int task, void *ctx)
+{
+    gemm_job *j = (gemm_job *)ctx;
+    int mr = j->mr, nr = j->nr;
+    int panel = task % j->panels, block = task / j->panels;
+    int t0 = block * j->tiles_per_block, t1 = t0 + j->tiles_per_block < j->m_tiles ? t0 + j->tiles_per_block : j->m_tiles;
+    if (t0 >= t1) return;
+    int64_t n0 = (int64_t)panel * nr;
+    int cols = j->n - n0 < nr ? (int)(j->n - n0) : nr;
+    float *bpack = (float *)aligned_alloc(64, (size_t)align64(((int64_t)GEMM_KC * nr + GEMM_KC) * 4));
+    float *row = bpack + (int64_t)GEMM_KC * nr;
+    int bs = slo_block_size(j->fmt), bb = slo_block_bytes(j->fmt);
+    int64_t row_bytes = j->k / bs * bb;
+    for (int64_t kb = 0; kb < j->k; kb += GEMM_KC) {
+        int kc = j->k - kb < GEMM_KC ? (int)(j->k - kb) : GEMM_KC;
+        for (int jn = 0; jn < nr; jn++) {
+            if (jn < cols) {
+                slo_dequantize_row(j->fmt, j->w + (n0 + jn) * row_bytes + kb / bs * bb, kc, row);
+                for (int k = 0; k < kc; k++) bpack[k * nr + jn] = row[k];
+            } else {
+                for (int k = 0; k < kc; k++) bpack[k * nr + jn] = 0.0f;
+            }
+        }
+        for (int t = t0; t < t1; t++) {
+            const float *a = j->apack + ((int64_t)t * j->k + kb) * mr;
+            float *c = j->y + (int64_t)t * mr * j->n + n0;
+            int rows = j->m - (int64_t)t * mr < mr ? (int)(j->m - (int64_t)t * mr) : mr;
+            gemm_tile(j, a, bpack, c, kc, kb > 0, rows, cols);
+        }
+    }
+    free(bpack);
+}
+
+int slo_matmul_gemm(int fmt, const uint8_t *w, int64_t n, int64_t k, const float *x, int64_t m, float *y, int threads)
+{
+    int bs = slo_block_size(fmt);
+    if (bs == 0 || k <= 0 || k % bs != 0 || n < 0 || m < 0) return -1;
+    if (n == 0 || m == 0) return 0;
+    if (threads < 1) threads = 1;
+    if (threads > POOL_MAX) threads = POOL_MAX;
+    gemm_job j;
+    j.fmt = fmt; j.w = w; j.n = n; j.k = k; j.m = m; j.x = x; j.y = y;
+    j.mr = have_avx512() ? 8 : 6;
+    j.nr = have_avx512() ? 32 : 16;
+    j.m_tiles = (int)((m + j.mr - 1) / j.mr);
+    j.apack = (float *)aligned_alloc(64, (size_t)align64((int64_t)j.m_tiles * k * j.mr * 4));
+    pool_for(j.m_tiles, threads, gemm_pack_body, &j);
+    /* split the rows into blocks only as far as needed to give every thread work: each block dequantizes the weights again */
+    j.panels = (int)((n + j.nr - 1) / j.nr);
+    j.m_blocks = 1;
+    while ((int64_t)j.panels * j.m_blocks < 2LL * threads && j.m_tiles / (j.m_blocks * 2) >= 4) j.m_blocks *= 2;
+    j.tiles_per_block = (j.m_tiles + j.m_blocks - 1) / j.m_blocks;
+    pool_for(j.panels * j.m_blocks, threads, gemm_body, &j);
+    free(j.apack);
+    return 0;
+}
+
+const char *slo_gemm_tile_name(void) { return have_avx512() ? "8x32 avx512" : "6x16 generic"; }
+
+/* The reference's MatMulOp.Run dispatch for a quantized weight with integer dots enabled (MatMulOp.cs:125-160): the f32
+ * GEMM from 32 rows, the integer-dot path below. */
+int slo_matmul_run(int fmt, const uint8_t *w, int64_t n, int64_t k, const float *x, int64_t m, float *y, int threads)
+{
+    if (m >= 32) return slo_matmul_gemm(fmt, w, n, k, x, m, y, threads);
+    return slo_matmul_intdot_pooled(fmt, w, n, k, x, m, y, threads, 1);
+}

@@ -68,6 +68,20 @@ int slo_matmul_intdot(int fmt, const uint8_t *w, int64_t n, int64_t k, const flo
 int slo_matmul_f64(int fmt, const uint8_t *w, int64_t n, int64_t k, const float *x, int64_t m, double *y64,
                    int threads);
 
+/* The same MatMul driven the way the reference drives it: chunks = clamp(n / 16, 1, threads * 4) rows ranges handed to a
+ * persistent spinning worker pool (src/Sharplight.Cpu/MatMulOp.cs:183, CpuParallel.cs:34-66, CpuThreadPool.cs:48-114). */
+int slo_matmul_intdot_pooled(int fmt, const uint8_t *w, int64_t n, int64_t k, const float *x, int64_t m, float *y,
+                             int threads, int tier);
+
+/* The f32 GEMM path the reference's CPU provider takes from 32 activation rows (src/Sharplight.Cpu/MatMulOp.cs:218-369,
+ * src/Sharplight.Cpu/Gemm.cs:16-60,210-330): weights dequantized per 256-value slice into packed panels, 8 x 32 AVX-512
+ * micro-kernel (6 x 16 in plain C otherwise); every output is one chain of fused multiply-adds over k in order. */
+int slo_matmul_gemm(int fmt, const uint8_t *w, int64_t n, int64_t k, const float *x, int64_t m, float *y, int threads);
+const char *slo_gemm_tile_name(void);
+
+/* MatMulOp.Run's row-count dispatch (src/Sharplight.Cpu/MatMulOp.cs:125-160): GEMM from 32 rows, integer dots below. */
+int slo_matmul_run(int fmt, const uint8_t *w, int64_t n, int64_t k, const float *x, int64_t m, float *y, int threads);
+
 /* Name of the vector tier slo_matmul_intdot(tier=1) uses on this host: "avx512vnni", "avx2" or "scalar". */
 const char *slo_fast_tier_name(void);
 

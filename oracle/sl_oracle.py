@@ -53,6 +53,10 @@ def lib() -> C.CDLL:
         L.slo_matmul_intdot.argtypes = [i32, vp, i64, i64, vp, i64, vp, vp, vp, i32, i32]
         L.slo_matmul_f64.argtypes = [i32, vp, i64, i64, vp, i64, vp, i32]
         L.slo_fast_tier_name.restype = C.c_char_p
+        L.slo_matmul_intdot_pooled.argtypes = [i32, vp, i64, i64, vp, i64, vp, i32, i32]
+        L.slo_matmul_gemm.argtypes = [i32, vp, i64, i64, vp, i64, vp, i32]
+        L.slo_matmul_run.argtypes = [i32, vp, i64, i64, vp, i64, vp, i32]
+        L.slo_gemm_tile_name.restype = C.c_char_p
         _lib = L
     return _lib
 
@@ -137,6 +141,43 @@ def matmul_f64(fmt: int, blocks: np.ndarray, n: int, k: int, x: np.ndarray, *, t
     rc = lib().slo_matmul_f64(fmt, _p(blocks), n, k, _p(x), m, _p(y64), threads)
     assert rc == 0
     return y64
+
+
+def matmul_intdot_pooled(fmt: int, blocks: np.ndarray, n: int, k: int, x: np.ndarray, *, threads: int = 1,
+                         tier: int = 1) -> np.ndarray:
+    """The integer-dot MatMul with the reference's chunking on its spinning worker pool (MatMulOp.cs:174-213)."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    m = x.shape[0]
+    assert x.shape[1] == k and blocks.size == n * row_bytes(fmt, k)
+    y = np.zeros((m, n), np.float32)
+    assert lib().slo_matmul_intdot_pooled(fmt, _p(blocks), n, k, _p(x), m, _p(y), threads, tier) == 0
+    return y
+
+
+def matmul_gemm(fmt: int, blocks: np.ndarray, n: int, k: int, x: np.ndarray, *, threads: int = 1) -> np.ndarray:
+    """The f32 GEMM path the reference's CPU provider takes from 32 rows (MatMulOp.cs:218-369, Gemm.cs:210-330)."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    m = x.shape[0]
+    assert x.shape[1] == k and blocks.size == n * row_bytes(fmt, k)
+    y = np.zeros((m, n), np.float32)
+    assert lib().slo_matmul_gemm(fmt, _p(blocks), n, k, _p(x), m, _p(y), threads) == 0
+    return y
+
+
+def matmul_run(fmt: int, blocks: np.ndarray, n: int, k: int, x: np.ndarray, *, threads: int = 1) -> np.ndarray:
+    """MatMulOp.Run's dispatch (MatMulOp.cs:125-160): the f32 GEMM from 32 rows, integer dots below."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    m = x.shape[0]
+    y = np.zeros((m, n), np.float32)
+    assert lib().slo_matmul_run(fmt, _p(blocks), n, k, _p(x), m, _p(y), threads) == 0
+    return y
+
+
+def gemm_tile_name() -> str:
+    return lib().slo_gemm_tile_name().decode()
 
 
 def fast_tier_name() -> str:

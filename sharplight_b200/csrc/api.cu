@@ -44,10 +44,9 @@ static slc_result cuda_fail(cudaError_t e, const char *what)
         if (e_ != cudaSuccess) return cuda_fail(e_, #call);     \
     } while (0)
 
-// Rows are padded so that every token tile a kernel touches exists: 8, 16, 32, 64, then multiples of 128.
+// Rows are padded so that every token tile a kernel touches exists: 16, 32, 64, then multiples of 128.
 static int pad_rows(long long rows)
 {
-    if (rows <= 8) return 8;
     if (rows <= 16) return 16;
     if (rows <= 32) return 32;
     if (rows <= 64) return 64;
@@ -390,8 +389,14 @@ slc_result slc_activation_create(slc_device *d, int64_t max_rows, int64_t k, slc
     const size_t cap = (size_t)a->cap_rows, kp = (size_t)a->k_pad;
     const size_t q_b = round_up(cap * kp, 256), ds_b = round_up(cap * (kp / 32) * 8, 256);
     const size_t gs_b = round_up(cap * (kp / 16) * 4, 256), is_b = round_up(cap * (kp / 32) * 4, 256);
-    const size_t qt_b = a->cap_rows > 64 ? q_b : 0;   // core-matrix copy for the tensor-core GEMM
-    a->bytes = q_b + 2 * ds_b + gs_b + is_b + qt_b;
+    const size_t qt_b = a->cap_rows > 64 ? q_b : 0;   // core-matrix copy for the int8 tensor-core GEMM
+    // the tile kernel's planes (3 rows and more): f16 codes, split offset sums, partial-tile scratch and counters
+    const bool tiles = max_rows >= 3;
+    a->tile_ctas = d->prop.multiProcessorCount;
+    const size_t ht_b = tiles ? round_up(cap * kp * 2, 1024) : 0, s2_b = tiles ? round_up(cap * (kp / 256) * 64, 1024) : 0;
+    const size_t sc_b = tiles ? round_up(umma_scratch_bytes(a->tile_ctas, a->cap_rows), 256) : 0;
+    const size_t ct_b = tiles ? round_up((size_t)a->tile_ctas * 4, 256) : 0;
+    a->bytes = q_b + 2 * ds_b + gs_b + is_b + qt_b + ht_b + s2_b + sc_b + ct_b + (tiles ? 1024 : 0);
     cudaError_t e = cudaMalloc(&a->base, a->bytes);
     if (e == cudaSuccess) e = cudaMemset(a->base, 0, a->bytes);
     if (e != cudaSuccess) {
@@ -406,6 +411,14 @@ slc_result slc_activation_create(slc_device *d, int64_t max_rows, int64_t k, slc
     a->planes.gs = reinterpret_cast<float *>(a->base + q_b + 2 * ds_b);
     a->planes.isum = reinterpret_cast<int *>(a->base + q_b + 2 * ds_b + gs_b);
     a->q_tiled = qt_b ? a->base + q_b + 2 * ds_b + gs_b + is_b : nullptr;
+    if (tiles) {
+        uint8_t *t0 = a->base + q_b + 2 * ds_b + gs_b + is_b + qt_b;   // 256-byte aligned so far; the planes want 1024
+        t0 += (1024 - (reinterpret_cast<uintptr_t>(t0) & 1023)) & 1023;
+        a->h_tiled = t0;
+        a->sx2 = t0 + ht_b;
+        a->tile_scratch = reinterpret_cast<float *>(t0 + ht_b + s2_b);
+        a->tile_counters = reinterpret_cast<int *>(t0 + ht_b + s2_b + sc_b);
+    }
     *out = a;
     return SLC_OK;
 }
@@ -433,6 +446,8 @@ slc_result slc_activation_quantize(slc_activation *a, const void *x, int32_t x_d
     SLC_CUDA(cudaSetDevice(a->dev->index));
     cudaStream_t s = stream ? (cudaStream_t)stream : a->dev->stream;
     a->planes.q_tiled = rows > 64 ? a->q_tiled : nullptr;
+    a->planes.h_tiled = rows >= 3 ? a->h_tiled : nullptr;
+    a->planes.sx2 = rows >= 3 ? a->sx2 : nullptr;
     a->reads_since_quantize = 0;
     a->quantize_stream = stream ? (cudaStream_t)stream : a->dev->stream;
     SLC_CUDA(launch_quantize(x, x_dtype, a->rows, a->rows_pad, (int)a->k, a->k_pad, x_stride, a->planes, s));
@@ -502,7 +517,10 @@ void slc_matmul_destroy(slc_matmul *op)
 slc_result slc_matmul_set_kernel(slc_matmul *op, int32_t kernel)
 {
     if (!op) return fail(SLC_ERR_INVALID_ARGUMENT, "op is null");
-    if (kernel < SLC_KERNEL_AUTO || kernel > SLC_KERNEL_MMQ) return fail(SLC_ERR_INVALID_ARGUMENT, "unknown kernel family");
+    if (kernel < SLC_KERNEL_AUTO || kernel > SLC_KERNEL_TILE) return fail(SLC_ERR_INVALID_ARGUMENT, "unknown kernel family");
+    if (kernel == SLC_KERNEL_TILE && !umma_supports(op->w->fmt)) {
+        return fail(SLC_ERR_UNSUPPORTED, "the f16 tensor-core tile kernel does not take this weight format");
+    }
     if (kernel == SLC_KERNEL_MMQ && !mmq_supports(op->w->fmt)) {
         return fail(SLC_ERR_UNSUPPORTED, "the tensor-core GEMM does not take this weight format");
     }
@@ -521,20 +539,27 @@ slc_result slc_matmul_last_kernel(slc_matmul *op, int32_t *out_kernel, int32_t *
 // Row-count dispatch. The reference's own GPU policy switches at 8 / 16 / 33 rows
 // (src/Sharplight.Shaders/Lowering/GraphLowerer.IntDot.cs:18-19, GraphLowerer.Mmq.cs:16-52 of the Sharplight tree);
 // these thresholds are the measured crossovers of this library's kernels on B200.
-static int choose_kernel(const slc_matmul *op, int rows)
+// From this row count the tile kernel is the default where it takes the format.
+static const int UMMA_MIN_ROWS = 1 << 30;
+
+static int choose_kernel(const slc_matmul *op, int rows, bool exchanging)
 {
-    if (op->forced_kernel != SLC_KERNEL_AUTO) return op->forced_kernel;
+    if (op->forced_kernel != SLC_KERNEL_AUTO && !(op->forced_kernel == SLC_KERNEL_TILE && (exchanging || rows < 3))) {
+        return op->forced_kernel;
+    }
     // the mat-vec keeps a row's quantized activations whole in shared memory; a K beyond that goes to the tiled kernel
     const bool mv = matvec_fits(1, op->w->view.k_pad, op->w2 != nullptr);
     if (mv && (op->flags & SLC_MATMUL_ROW_INVARIANT) && rows <= 8) return SLC_KERNEL_MMVQ;
     if (mv && rows <= 2) return SLC_KERNEL_MMVQ;
+    // three rows and more: the f16 tensor-core tiles; the in-kernel sum over ranks lives in the older kernels
+    if (rows >= UMMA_MIN_ROWS && umma_supports(op->w->fmt) && !exchanging) return SLC_KERNEL_TILE;
     if (rows <= 64 || !mmq_supports(op->w->fmt)) return SLC_KERNEL_SKINNY;
     return SLC_KERNEL_MMQ;
 }
 
 static slc_result run_family(slc_matmul *op, const WeightView &wv, const WeightView *w2, slc_activation *act, const ActView &av,
                              int kernel, float *y, long long y_stride, int *dump, cudaStream_t s, const Exchange *ex,
-                             const Epilogue *ep);
+                             const Epilogue *ep, bool allow_early = true);
 
 // ex (optional): the MatMul is the row-split part of a tensor-parallel group and its kernel sums over the ranks.
 // ep (optional): bias and residual added before the store.
@@ -543,7 +568,7 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
 {
     const ActView av = view_of(act);
     const int rows = act->rows;
-    const int kernel = choose_kernel(op, rows);
+    const int kernel = choose_kernel(op, rows, ex != nullptr);
     op->last_kernel = kernel;
     op->last_launches = 0;
     op->last_launches_total = 0;
@@ -552,8 +577,10 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
         // up -> y, and the element-wise tail
         if (dump || ex || ep) return fail(SLC_ERR_UNSUPPORTED, "a dual MatMul takes no block-dot export, exchange or epilogue");
         if (kernel == SLC_KERNEL_MMVQ) return run_family(op, op->w->view, &op->w2->view, act, av, kernel, y, y_stride, nullptr, s, nullptr, nullptr);
+        // the gate launch overwrites dual_tmp, which the element-wise tail of an earlier run of this op may still be
+        // reading: it waits for its predecessor like any launch that writes shared state
         const long long n = op->w->n;
-        slc_result r = run_family(op, op->w->view, nullptr, act, av, kernel, op->dual_tmp, n, nullptr, s, nullptr, nullptr);
+        slc_result r = run_family(op, op->w->view, nullptr, act, av, kernel, op->dual_tmp, n, nullptr, s, nullptr, nullptr, false);
         if (r == SLC_OK) r = run_family(op, op->w2->view, nullptr, act, av, kernel, y, y_stride, nullptr, s, nullptr, nullptr);
         if (r != SLC_OK) return r;
         SLC_CUDA(launch_gate_mul(op->dual_tmp, n, y, y_stride, rows, (int)n, s));
@@ -566,13 +593,17 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
 // The launches of one weight (two for the dual mat-vec) in the chosen kernel family.
 static slc_result run_family(slc_matmul *op, const WeightView &wv, const WeightView *w2, slc_activation *act, const ActView &av,
                              int kernel, float *y, long long y_stride, int *dump, cudaStream_t s, const Exchange *ex,
-                             const Epilogue *ep)
+                             const Epilogue *ep, bool allow_early)
 {
     const int rows = act->rows;
     const long long dump_row = (long long)wv.n * (wv.k >> 5);
     // A launch may run beside its predecessor when an earlier launch on this stream has already read these
-    // activations: they were complete before that launch started, and MatMul outputs do not alias each other.
-    auto early = [&]() { return !ex && act->reads_since_quantize > 0 ? 1 : 0; };
+    // activations: they were complete before that launch started, and MatMul outputs do not alias each other. Not so
+    // when the launch reads more than the activations -- a bias or a residual, which the predecessor may be writing
+    // (y2 = W2 x + y1 right after y1 = W1 x) -- or when it runs on another stream than the quantization did.
+    auto early = [&]() {
+        return allow_early && !ex && !ep && act->reads_since_quantize > 0 && s == act->quantize_stream ? 1 : 0;
+    };
     if (kernel == SLC_KERNEL_MMVQ) {
         // chunks of up to 4 rows; every row of a chunk is computed exactly as a single row is, so the row-invariant
         // guarantee holds for any chunking
@@ -592,6 +623,14 @@ static slc_result run_family(slc_matmul *op, const WeightView &wv, const WeightV
             act->reads_since_quantize++;
             op->last_launches++;
         }
+    } else if (kernel == SLC_KERNEL_TILE) {
+        if (ex) return fail(SLC_ERR_UNSUPPORTED, "the tile kernel does not sum over ranks");
+        if (!act->planes.h_tiled) return fail(SLC_ERR_INVALID_STATE, "the tile kernel needs an activation object created for 3 rows or more");
+        // one persistent launch; it shares the activation object's scratch with other launches, so it never runs early
+        SLC_CUDA(launch_umma(wv, av, act->planes.h_tiled, act->planes.sx2, y, y_stride, dump, op->dev->status_dev,
+                             act->tile_scratch, act->tile_counters, act->tile_ctas, s, ep));
+        act->reads_since_quantize++;
+        op->last_launches++;
     } else if (ex) {
         return fail(SLC_ERR_UNSUPPORTED, "the in-kernel all-reduce serves the mat-vec and skinny kernels (up to 64 rows)");
     } else {
@@ -904,17 +943,5 @@ slc_result slc_debug_block_dots(slc_matmul *op, const void *x, int32_t x_dtype, 
     cudaFree(dump);
     return r;
 }
-
-#ifdef MQ_TIMING
-// Measurement builds only: the cycle counters the GEMM kernel adds up behind the status word.
-__attribute__((visibility("default"))) slc_result slc_debug_timing(slc_device *d, int32_t *out48, int32_t clear)
-{
-    cudaSetDevice(d->index);
-    cudaDeviceSynchronize();
-    cudaMemcpy(out48, d->status_dev + 16, 48 * sizeof(int), cudaMemcpyDeviceToHost);
-    if (clear) cudaMemset(d->status_dev + 16, 0, 48 * sizeof(int));
-    return SLC_OK;
-}
-#endif
 
 }  // extern "C"

@@ -77,10 +77,12 @@ __device__ __forceinline__ void ex_ll_send(const Exchange &x, int slot, int epoc
     }
 }
 
-__device__ __forceinline__ float ex_ll_collect(const Exchange &x, int slot, int epoch, int m, int col, float v, bool &ok)
+// t0: ex_now() taken once by the caller before its first collect, so that all values of a thread share one deadline.
+__device__ __forceinline__ float ex_ll_collect(const Exchange &x, int slot, int epoch, int m, int col, float v, bool &ok,
+                                               unsigned long long t0)
 {
     const unsigned tag = (unsigned)epoch + 1u;
-    const unsigned long long t0 = ex_now(), limit = (unsigned long long)x.wait_ms * 1000000ull;
+    const unsigned long long limit = (unsigned long long)x.wait_ms * 1000000ull;
     float s = 0.0f;
     for (int p = 0; p < x.world; p++) {
         float val = v;
@@ -90,7 +92,7 @@ __device__ __forceinline__ float ex_ll_collect(const Exchange &x, int slot, int 
             for (;;) {
                 asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(got) : "l"(src) : "memory");
                 if ((unsigned)(got >> 32) == tag) break;
-                if (ex_now() - t0 > limit) { ok = false; break; }
+                if (!ok || ex_now() - t0 > limit) { ok = false; break; }
             }
             val = __uint_as_float((unsigned)got);
         }
@@ -149,7 +151,7 @@ __device__ __forceinline__ void ex_finish(const Exchange &x, int epoch)
     if (threadIdx.x == 0) {
         const unsigned total = gridDim.x * gridDim.y;
         if (atomicAdd(reinterpret_cast<unsigned *>(x.done), 1u) == total - 1) {
-            *reinterpret_cast<volatile int *>(x.done) = 0;
+            atomicExch(reinterpret_cast<unsigned *>(x.done), 0u);
             __threadfence();
             *reinterpret_cast<volatile int *>(x.epoch) = epoch + 1;
         }

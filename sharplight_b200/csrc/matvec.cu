@@ -513,31 +513,53 @@ matvec_kernel(const WeightView w, const WeightView w2, const ActView a, int row0
     }
     __syncthreads();
     {
-        const bool own = threadIdx.x < 16 * M;   // one thread per output value of the CTA
-        const int m = threadIdx.x / 16, rr = threadIdx.x % 16;
-        const int row = blockIdx.x * 16 + rr;
-        float v = 0.0f;
-        if (own) {
-            for (int wi = 0; wi < warps; wi++) v += red[0][wi][rr][m];
-            if (DUAL) {
-                float u = 0.0f;
-                for (int wi = 0; wi < warps; wi++) u += red[DUAL ? 1 : 0][wi][rr][m];
-                v = __fdiv_rn(v, 1.0f + expf(-v)) * u;   // silu(gate) * up
+        // The CTA's 16 * M output values are dealt out to its threads; a CTA of a single warp (K of one super-tile)
+        // has fewer threads than values for M > 2, so a thread may own two of them.
+        constexpr int OWN = (16 * M + 31) / 32;
+        float vals[OWN];
+#pragma unroll
+        for (int j = 0; j < OWN; j++) {
+            const int o = threadIdx.x + j * blockDim.x;
+            float v = 0.0f;
+            if (o < 16 * M) {
+                const int m = o / 16, rr = o % 16;
+                for (int wi = 0; wi < warps; wi++) v += red[0][wi][rr][m];
+                if (DUAL) {
+                    float u = 0.0f;
+                    for (int wi = 0; wi < warps; wi++) u += red[DUAL ? 1 : 0][wi][rr][m];
+                    v = __fdiv_rn(v, 1.0f + expf(-v)) * u;   // silu(gate) * up
+                }
             }
+            vals[j] = v;
         }
         if (ex.world == 0) {
-            if (own && row < w.n) y[(long long)(row0 + m) * y_stride + row] = ep.apply(v, row0 + m, row);
-        } else {
-            // row-split MatMul of a tensor-parallel group: v is this rank's partial value; every thread trades its own
-            // value with the peers as {value, tag} words (exchange.cuh)
-            const int epoch = ex_epoch(ex), slot = epoch & 1;
-            if (own) {
-                bool ok = true;
-                ex_ll_send(ex, slot, epoch, m, row, v);
-                const float total = ex_ll_collect(ex, slot, epoch, m, row, v, ok);
-                if (!ok) atomicExch(status, -7);
-                if (row < w.n) y[(long long)(row0 + m) * y_stride + row] = ep.apply(total, row0 + m, row);
+#pragma unroll
+            for (int j = 0; j < OWN; j++) {
+                const int o = threadIdx.x + j * blockDim.x;
+                const int m = o / 16, row = blockIdx.x * 16 + o % 16;
+                if (o < 16 * M && row < w.n) y[(long long)(row0 + m) * y_stride + row] = ep.apply(vals[j], row0 + m, row);
             }
+        } else {
+            // row-split MatMul of a tensor-parallel group: the values are this rank's partial sums; every thread trades
+            // its own with the peers as {value, tag} words (exchange.cuh), all sent before any is awaited
+            const int epoch = ex_epoch(ex), slot = epoch & 1;
+#pragma unroll
+            for (int j = 0; j < OWN; j++) {
+                const int o = threadIdx.x + j * blockDim.x;
+                if (o < 16 * M) ex_ll_send(ex, slot, epoch, o / 16, blockIdx.x * 16 + o % 16, vals[j]);
+            }
+            bool ok = true;
+            const unsigned long long wait_from = ex_now();
+#pragma unroll
+            for (int j = 0; j < OWN; j++) {
+                const int o = threadIdx.x + j * blockDim.x;
+                if (o < 16 * M) {
+                    const int m = o / 16, row = blockIdx.x * 16 + o % 16;
+                    const float total = ex_ll_collect(ex, slot, epoch, m, row, vals[j], ok, wait_from);
+                    if (row < w.n) y[(long long)(row0 + m) * y_stride + row] = ep.apply(total, row0 + m, row);
+                }
+            }
+            if (!ok) atomicExch(status, -7);
             ex_finish(ex, epoch);
         }
     }

@@ -158,16 +158,6 @@ __host__ __device__ constexpr unsigned mq_idesc(bool a_signed, int m, int n)
 
 __device__ __forceinline__ float mq_h2f(unsigned bits) { return __half2float(__ushort_as_half((unsigned short)bits)); }
 
-// Optional cycle accounting of the wait sites (a measurement build only: -DMQ_TIMING). CTA (0, 0) adds its cycles, in
-// units of 16, to status[16 + slot].
-#ifdef MQ_TIMING
-#define MQ_T0() const long long mq_t0_ = clock64()
-#define MQ_T1(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) atomicAdd(status + 16 + (slot), (int)((clock64() - mq_t0_) >> 4)); } while (0)
-#else
-#define MQ_T0() do { } while (0)
-#define MQ_T1(slot) do { } while (0)
-#endif
-
 struct MqSmem
 {
     uint64_t a_full[MQ_MAX_STAGES], b_full[MQ_MAX_STAGES], mma_done[MQ_MAX_STAGES], epi_done[MQ_MAX_STAGES];
@@ -329,9 +319,6 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
     const unsigned tmem = sh.tmem_base;
 
     pdl_enter(early);   // waits for the kernel that produced the activations unless they were complete before it
-#ifdef MQ_TIMING
-    const long long mq_kernel_t0 = clock64();
-#endif
 
     // Register budget: 80 per thread at launch (768 threads). The MMA issuer's warpgroup gives back all but 24. The
     // producers of Q8_0 (two 4352-byte records in registers) and Q4_K (scale decoding) take 104, leaving 88 to the
@@ -382,15 +369,11 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
             if (b == 0) {
                 // the stage's scale tables: weight scales come from the producers, activation scales from a bulk copy
                 const unsigned spar = (unsigned)(it / MQ_STAGES) & 1u;
-                MQ_T0();
                 if (!mq_bar_wait(&sh.a_full[s], spar) || !mq_bar_wait(&sh.b_full[s], spar)) { alive = false; break; }
-                if (warp == 0) MQ_T1(1);
             }
             const unsigned tcol = tlane + (unsigned)(buf * MQ_TILE_T);
             {
-                MQ_T0();
                 if (!mq_bar_wait(&sh.d_full[buf], (unsigned)(i / MQ_DBUF) & 1u)) { alive = false; break; }
-                if (warp == 0) MQ_T1(0);
             }
             mq_tc_fence_after();
             const float *dxs = stage_dx(s) + b * MQ_TILE_T + c0, *sxs = stage_sx(s) + b * MQ_TILE_T + c0;
@@ -403,13 +386,10 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
                 float sv[16];
                 mq_tmem_ld16(tcol + (unsigned)(h * 16), sv);
                 {
-                    MQ_T0();
                     mq_tmem_wait_ld();
-                    if (warp == 0) MQ_T1(2);
                 }
                 // these columns have been read: re-arm them with the bias (asynchronously)
                 mq_tmem_st16(tcol + (unsigned)(h * 16), bias);
-                MQ_T0();
 #pragma unroll
                 for (int j4 = 0; j4 < 4; j4++) {
                     const float4 dx = *reinterpret_cast<const float4 *>(dxs + h * 16 + j4 * 4);
@@ -431,7 +411,6 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
                         acc[h * 16 + j4 * 4 + e] = v;
                     }
                 }
-                if (warp == 0) MQ_T1(3);
                 if (DUMP) {
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
@@ -447,12 +426,10 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
             }
             // the bias stores have landed by now: hand the buffer back to the MMA issuer
             {
-                MQ_T0();
                 mq_tmem_wait_st();
                 mq_tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mq_bar_arrive(&sh.d_empty[buf]);
-                if (warp == 0) MQ_T1(6);
             }
             if (b == 7) {
                 __syncwarp();
@@ -485,14 +462,10 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
             const int s = it % MQ_STAGES;
             const unsigned par = ((unsigned)(it / MQ_STAGES) & 1u) ^ 1u;   // first use of a stage passes at once
             {
-                MQ_T0();
                 if (!mq_bar_wait(&sh.mma_done[s], par)) { alive = false; break; }
-                if (pw == 0) MQ_T1(4);
             }
             {
-                MQ_T0();
                 if (!mq_bar_wait(&sh.epi_done[s], par)) { alive = false; break; }
-                if (pw == 0) MQ_T1(5);
             }
             if (pw == 0 && lane == 0) {
                 // activation codes (already in core-matrix order) and scales of this stage, by bulk async copy
@@ -527,23 +500,17 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
                 const int s = it % MQ_STAGES;
                 const unsigned par = (unsigned)(it / MQ_STAGES) & 1u;
                 {
-                    MQ_T0();
                     if (!mq_bar_wait(&sh.a_full[s], par)) { alive = false; break; }
-                    MQ_T1(8);
                 }
                 {
-                    MQ_T0();
                     if (!mq_bar_wait(&sh.b_full[s], par)) { alive = false; break; }
-                    MQ_T1(9);
                 }
                 mq_tc_fence_after();
                 const unsigned a_addr = mq_smem(stage_a(s)), b_addr = mq_smem(stage_b(s));
                 for (int b = 0; b < 8; b++) {
                     const int i = it * 8 + b, buf = i % MQ_DBUF;
                     {
-                        MQ_T0();
                         if (!mq_bar_wait(&sh.d_empty[buf], (unsigned)(i / MQ_DBUF) & 1u)) { alive = false; break; }
-                        MQ_T1(10);
                     }
                     mq_tc_fence_after();
                     mq_umma_i8(tmem + (unsigned)(buf * MQ_TILE_T), mq_desc(a_addr + b * 256, 128, 2048),
@@ -557,9 +524,6 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
         __syncwarp();
     }
 
-#ifdef MQ_TIMING
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) atomicAdd(status + 16 + 12, (int)((clock64() - mq_kernel_t0) >> 4));
-#endif
     pdl_exit(early);
     mq_tc_fence_before();
     __syncthreads();

@@ -6,6 +6,7 @@
 #include "internal.cuh"
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 namespace slc {
 
@@ -73,6 +74,17 @@ __global__ void __launch_bounds__(256) quantize_kernel(const void *__restrict__ 
                               (row & 7) * 16 + (kk & 15);
         *reinterpret_cast<unsigned *>(out.q_tiled + off) = packed;
     }
+    if (out.h_tiled) {
+        // the same codes as f16 values (exact), in the 128-byte swizzled operand rows the f16 tensor-core tiles read:
+        // [k / 64][token / 8][token % 8][eight 16-byte chunks, chunk c stored at c ^ (token % 8)]; the tile of NT tokens
+        // x 64 K-values is then NT x 128 contiguous bytes, one bulk copy
+        const int kk = blk * 32 + sub * 4;
+        const long long off = ((long long)(kk >> 6) * (rows_pad >> 3) + (row >> 3)) * 1024 + (row & 7) * 128 +
+                              ((((kk & 63) >> 3) ^ (row & 7)) << 4) + (kk & 7) * 2;
+        const __half2 h01 = __floats2half2_rn((float)r[0], (float)r[1]), h23 = __floats2half2_rn((float)r[2], (float)r[3]);
+        *reinterpret_cast<uint2 *>(out.h_tiled + off) =
+            make_uint2(*reinterpret_cast<const unsigned *>(&h01), *reinterpret_cast<const unsigned *>(&h23));
+    }
     s += __shfl_xor_sync(0xffffffffu, s, 1);
     s += __shfl_xor_sync(0xffffffffu, s, 2);        // sum of this lane's 16-value group
     const int s_other = __shfl_xor_sync(0xffffffffu, s, 4);
@@ -86,6 +98,15 @@ __global__ void __launch_bounds__(256) quantize_kernel(const void *__restrict__ 
         out.dx[(long long)blk * rows_pad + row] = d;
         out.sx[(long long)blk * rows_pad + row] = sxv;
         out.isum[(long long)row * nblk_pad + blk] = s32;
+        if (out.sx2) {
+            // d * sum32(q) as two tf32 values (high 11 significant bits, and the rest), in 64-byte swizzled operand
+            // rows: [k / 256][token / 8][token % 8][four 16-byte chunks: hi of blocks 0-3, hi 4-7, lo 0-3, lo 4-7]
+            const float hi = __uint_as_float(__float_as_uint(sxv) & 0xFFFFE000u), lo = __fsub_rn(sxv, hi);
+            const int bq = blk & 7, sw = (row & 7) >> 1;
+            uint8_t *base = out.sx2 + ((long long)(blk >> 3) * (rows_pad >> 3) + (row >> 3)) * 512 + (row & 7) * 64 + (bq & 3) * 4;
+            *reinterpret_cast<float *>(base + (((bq >> 2) ^ sw) << 4)) = hi;
+            *reinterpret_cast<float *>(base + (((2 + (bq >> 2)) ^ sw) << 4)) = lo;
+        }
     }
 }
 

@@ -419,9 +419,10 @@ skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__
                 ex_ll_send(ex, slot, epoch, idx >> 6, col0 + (idx & 63), tile[idx]);
             }
             bool ok = true;
+            const unsigned long long wait_from = ex_now();
             for (int idx = threadIdx.x; idx < rows * 64; idx += SK_WARPS * 32) {
                 const int m = idx >> 6, col = col0 + (idx & 63);
-                const float total = ex_ll_collect(ex, slot, epoch, m, col, tile[idx], ok);
+                const float total = ex_ll_collect(ex, slot, epoch, m, col, tile[idx], ok, wait_from);
                 if (col < w.n) y[(long long)(row0 + m) * y_stride + col] = ep.apply(total, row0 + m, col);
             }
             if (!ok) atomicExch(status, -7);

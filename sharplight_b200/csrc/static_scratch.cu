@@ -7,7 +7,9 @@
 // in the library's device image, so every GPU that loads the library pays SLC_STATIC_SCRATCH_BYTES (480 KB) until the
 // process exits, whether the entry point is used or not.
 //
-// Limits, checked with a clear error: 1..4 activation rows, K up to 32768 (after padding to a multiple of 256).
+// Limits, checked with a clear error: 1..4 activation rows, K up to 32768 (after padding to a multiple of 256). Where
+// K is too long for the kernel to hold four rows of activations in shared memory (beyond 24576), the rows go in two
+// launches on the same scratch, as the ordinary path does.
 // The array is shared by every call on a device and keeps the previous call's contents; each call rewrites all of what
 // its kernels read (the quantizer writes every padded row and block), so nothing needs clearing, but two calls that
 // overlap on the GPU (different streams, or the same weight from two threads) race on it: serialise them.
@@ -17,6 +19,7 @@
 
 #include "handles.cuh"
 
+#include <atomic>
 #include <string>
 
 using namespace slc;
@@ -38,7 +41,8 @@ static_assert(NA_TOTAL == SLC_STATIC_SCRATCH_BYTES, "header and implementation d
 // comes from cudaGetSymbolAddress below and only that pointer is ever handed to a kernel.
 static __device__ __align__(256) unsigned char g_static_scratch[NA_TOTAL];
 
-unsigned char *g_scratch_ptr[64] = {};   // per device, filled at first use
+// per device, filled at first use; two host threads that race here both look the same address up and store the same value
+std::atomic<unsigned char *> g_scratch_ptr[64];
 
 thread_local std::string t_static_error;
 
@@ -63,7 +67,7 @@ slc_result slc_matmul_run_static(slc_weight *weight, const void *x_device, int32
     if (rows == 0 || weight->n == 0) return SLC_OK;
     if (rows > NA_MAX_ROWS) return na_fail(SLC_ERR_UNSUPPORTED, "slc_matmul_run_static takes at most 4 activation rows");
     const WeightView &wv = weight->view;
-    if (wv.k_pad > NA_MAX_KPAD || !matvec_fits((int)rows, wv.k_pad)) {
+    if (wv.k_pad > NA_MAX_KPAD || !matvec_fits(1, wv.k_pad)) {
         return na_fail(SLC_ERR_UNSUPPORTED, "slc_matmul_run_static: K exceeds the static scratch (32768 values)");
     }
     if (!x_device || x_stride < weight->k) return na_fail(SLC_ERR_INVALID_ARGUMENT, "bad activation pointer or stride");
@@ -74,26 +78,28 @@ slc_result slc_matmul_run_static(slc_weight *weight, const void *x_device, int32
     if (e != cudaSuccess) return na_fail(SLC_ERR_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(e));
 
     // set-up, once per device, with that device current: the symbol's address on this device
-    if (!g_scratch_ptr[dev->index]) {
+    unsigned char *base = g_scratch_ptr[dev->index].load(std::memory_order_acquire);
+    if (!base) {
         void *p = nullptr;
         e = cudaGetSymbolAddress(&p, g_static_scratch);
         if (e != cudaSuccess || !p) {
             return na_fail(SLC_ERR_CUDA, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
         }
-        g_scratch_ptr[dev->index] = static_cast<unsigned char *>(p);
+        base = static_cast<unsigned char *>(p);
+        g_scratch_ptr[dev->index].store(base, std::memory_order_release);
     }
-    unsigned char *base = g_scratch_ptr[dev->index];
 
-    const int k_pad = wv.k_pad, nblk = k_pad / 32;
+    const int k_pad = wv.k_pad;
     ActPlanes planes;
     planes.q_tiled = nullptr;
+    planes.h_tiled = nullptr;
+    planes.sx2 = nullptr;
     planes.q = reinterpret_cast<int8_t *>(base);
     planes.ds = reinterpret_cast<float2 *>(base + NA_Q);
     planes.dx = reinterpret_cast<float *>(base + NA_Q + NA_DS);
     planes.sx = reinterpret_cast<float *>(base + NA_Q + NA_DS + NA_DX);
     planes.gs = reinterpret_cast<float *>(base + NA_Q + NA_DS + NA_DX + NA_SX);
     planes.isum = reinterpret_cast<int *>(base + NA_Q + NA_DS + NA_DX + NA_SX + NA_GS);
-    (void)nblk;
 
     cudaStream_t s = stream ? (cudaStream_t)stream : dev->stream;
     e = launch_quantize(x_device, x_dtype, (int)rows, NA_ROWS_PAD, (int)weight->k, k_pad, x_stride, planes, s);
@@ -101,8 +107,15 @@ slc_result slc_matmul_run_static(slc_weight *weight, const void *x_device, int32
     ActView av;
     av.rows = (int)rows; av.rows_pad = NA_ROWS_PAD; av.k = (int)weight->k; av.k_pad = k_pad;
     av.q = planes.q; av.ds = planes.ds; av.dx = planes.dx; av.sx = planes.sx; av.gs = planes.gs; av.isum = planes.isum;
-    e = launch_matvec(wv, av, 0, (int)rows, y_device, y_stride, nullptr, dev->status_dev, 0, s);
-    if (e != cudaSuccess) return na_fail(SLC_ERR_CUDA, std::string("mat-vec: ") + cudaGetErrorString(e));
+    // the largest chunk of rows whose activations fit the kernel's shared memory at this K (every row of a chunk is
+    // computed exactly as a single row is, so the chunking does not change the result)
+    int chunk = (int)rows;
+    while (chunk > 1 && !matvec_fits(chunk, k_pad)) chunk--;
+    for (int r0 = 0; r0 < (int)rows; r0 += chunk) {
+        const int m = (int)rows - r0 < chunk ? (int)rows - r0 : chunk;
+        e = launch_matvec(wv, av, r0, m, y_device, y_stride, nullptr, dev->status_dev, r0 > 0 ? 1 : 0, s);
+        if (e != cudaSuccess) return na_fail(SLC_ERR_CUDA, std::string("mat-vec: ") + cudaGetErrorString(e));
+    }
     return SLC_OK;
 }
 

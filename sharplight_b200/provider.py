@@ -233,6 +233,7 @@ class CudaDevice:
     def __init__(self, info: DeviceInfo, options: dict):
         self.info = info
         self.options = options
+        self.allow_reduced_precision = bool(options.get("allow_reduced_precision", False))
         h = C.c_void_p()
         _check(N.load().slc_device_open(info.index, C.byref(h)))
         self._h = h
@@ -281,7 +282,16 @@ class CudaDevice:
             return OpSupport.no("activations must be f32 or bf16")
         if "int_dot" not in self.enabled_features:
             return OpSupport.no("int_dot is disabled and this provider has no float path")
+        # a node may opt out of 8-bit activations (StandardOps.cs:130-135); the reference then runs its f32-activation
+        # path unless reduced precision is allowed (GraphLowerer.IntDot.cs:61-62, CpuCompiledSegment.LowerLinear.cs:39).
+        # This provider has only the integer-dot path, so such a node goes to the placement fallback.
+        if node.f32_activations and not self.allow_reduced_precision:
+            return OpSupport.no("f32 activations requested and this provider only has the 8-bit activation path")
         return OpSupport.yes()
+
+    def _supports_ignoring_f32(self, node: "MatMulNode") -> bool:
+        import dataclasses
+        return self.supports(dataclasses.replace(node, f32_activations=False)).supported
 
     def upload_weight(self, type_name: str, shape: Sequence[int], blocks, k_slice=None) -> DeviceWeight:
         fmt = DATA_TYPES.get(type_name)
@@ -302,7 +312,8 @@ class CudaDevice:
     def compile(self, segment: GraphSegment, options: CompileOptions) -> "CudaSegment":
         for node in segment.nodes:
             s = self.supports(node)
-            if not s.supported:
+            if not s.supported and not (isinstance(node, MatMulNode) and node.f32_activations and options.allow_reduced_precision
+                                        and self._supports_ignoring_f32(node)):
                 raise NotSupportedError(f"{node.name}: {s.reason}")
         return CudaSegment(self, segment, options)
 

@@ -89,9 +89,10 @@ def test_missing_library_fails_loudly(monkeypatch):
     assert P.CudaExecutionProvider().check_availability().available is False
 
 
-def _bare_device(disabled=()):
+def _bare_device(disabled=(), allow_reduced_precision=False):
     d = object.__new__(P.CudaDevice)
     d.enabled_features = frozenset(P.FEATURES - frozenset(disabled))
+    d.allow_reduced_precision = allow_reduced_precision
     return d
 
 
@@ -107,6 +108,18 @@ def test_supports_mirrors_the_quantized_matmul_check():
     assert not d.supports(P.MatMulNode("m", "x", P.WeightInfo("Q8_0", (1, 32), blocks), "y", x_dtype="f16")).supported
     assert not d.supports("Softmax").supported
     assert not _bare_device(["int_dot"]).supports(ok).supported
+
+
+def test_supports_honours_the_f32_activation_opt_out():
+    """A MatMul node may opt out of 8-bit activations (src/Sharplight.Core/Graph/StandardOps.cs:130-135); the reference
+    then keeps f32 activations unless reduced precision is allowed (src/Sharplight.Shaders/Lowering/
+    GraphLowerer.IntDot.cs:61-62, src/Sharplight.Cpu/CpuCompiledSegment.LowerLinear.cs:39). This provider only has the
+    8-bit path: the node is refused (and goes to the placement fallback), never silently quantized."""
+    blocks = np.zeros(34, np.uint8)
+    node = P.MatMulNode("m", "x", P.WeightInfo("Q8_0", (1, 32), blocks), "y", f32_activations=True)
+    no = _bare_device().supports(node)
+    assert not no.supported and "f32 activations" in no.reason
+    assert _bare_device(allow_reduced_precision=True).supports(node).supported
 
 
 def test_bf16_helpers_round_trip():

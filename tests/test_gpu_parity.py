@@ -450,3 +450,28 @@ def test_config5_llama70b_shapes(cuda_device, n, k, rows):
     """benchmark configuration 5: the Q4_K MatMuls of a Llama-3-70B-shaped layer at full size, whole (down [8192, 28672],
     stacked qkv [10240, 8192], stacked gate_up [57344, 8192]) and as 8-way tensor-parallel shards."""
     _check_sampled_rows(cuda_device, "Q4_K", n, k, rows, 300 + rows, 256)
+
+
+# ---- short K with 3 and 4 rows on the dp4a family (a CTA of one warp owns two output values per thread) ----------------
+
+@pytest.mark.parametrize("type_name,k", [("Q8_0", 32), ("Q4_0", 64), ("Q8_0", 256), ("Q4_K", 256), ("Q6_K", 256)])
+@pytest.mark.parametrize("rows", [3, 4, 7])
+def test_mmvq_short_k_three_and_four_rows(cuda_device, type_name, k, rows):
+    check_matmul(cuda_device, type_name, 40, k, rows, seed=rows + k, kernel=N.KERNEL_MMVQ)
+
+
+@pytest.mark.parametrize("rows", [3, 4, 8])
+def test_row_invariant_short_k(cuda_device, rows):
+    blocks = synth.weight_blocks("Q4_K", 48, 256, seed=3)
+    x = synth.activations(rows, 256, seed=4)
+    w = cuda_device.upload_weight("Q4_K", (48, 256), blocks)
+    op = MatMulOp(cuda_device, w, 8, row_invariant=True)
+    try:
+        y = op.run(x)
+        singles = np.concatenate([op.run(x[i:i + 1]) for i in range(rows)], axis=0)
+        assert np.array_equal(y.view(np.uint32), singles.view(np.uint32))
+        ref, _, _ = sl_oracle.matmul_intdot(FMT_OF["Q4_K"], blocks, 48, 256, x, threads=4, want_f64=False, want_s32=False)
+        assert max_rel_error(y, ref) <= MAX_REL
+    finally:
+        op.dispose()
+        w.dispose()

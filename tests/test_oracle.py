@@ -182,3 +182,54 @@ def test_empty_and_bad_shapes():
     assert sl_oracle.lib().slo_decode_row(99, None, 32, None, None, None) == -1
     y, _, _ = sl_oracle.matmul_intdot(8, np.zeros(0, np.uint8), 0, 32, np.zeros((2, 32), np.float32))
     assert y.shape == (2, 0)
+
+
+# ---- the reference's CPU drivers: chunked integer dots on the worker pool, f32 GEMM from 32 rows ---------------------
+
+@pytest.mark.parametrize("fmt_name", ["Q8_0", "Q4_0", "Q4_K", "Q6_K"])
+def test_pooled_intdot_equals_the_plain_driver(fmt_name):
+    """Chunking and the worker pool change who computes a row, not what is computed."""
+    from sharplight_b200 import synth
+    fmt = {"Q4_0": 2, "Q8_0": 8, "Q4_K": 12, "Q6_K": 14}[fmt_name]
+    n, k, m = 203, 1024, 5
+    blocks = synth.weight_blocks(fmt_name, n, k, 11)
+    x = synth.activations(m, k, 12)
+    plain, _, _ = sl_oracle.matmul_intdot(fmt, blocks, n, k, x, threads=3, tier=1)
+    for threads in (1, 4, 7):
+        pooled = sl_oracle.matmul_intdot_pooled(fmt, blocks, n, k, x, threads=threads)
+        assert np.array_equal(plain.view(np.uint32), pooled.view(np.uint32))
+
+
+@pytest.mark.parametrize("fmt_name", ["Q8_0", "Q4_0", "Q4_K", "Q6_K"])
+@pytest.mark.parametrize("n,k,m", [(37, 512, 32), (70, 768, 45), (33, 256, 64)])
+def test_gemm_path_matches_the_exact_product(fmt_name, n, k, m):
+    """MatMulOp.RunGemm restated: within atol 2e-3 / rtol 1e-4 of the double-precision product of the dequantized weight
+    with the f32 activations (the tolerance of the reference's float MatMul tests, tests/Sharplight.Cpu.Tests/QuantTests.cs:257-265
+    compare the integer-dot result with the same product at 1e-2 relative RMS), and identical for every thread count."""
+    from sharplight_b200 import synth
+    fmt = {"Q4_0": 2, "Q8_0": 8, "Q4_K": 12, "Q6_K": 14}[fmt_name]
+    blocks = synth.weight_blocks(fmt_name, n, k, n + k)
+    x = synth.activations(m, k, m)
+    exact = sl_oracle.matmul_f64(fmt, blocks, n, k, x, threads=4)
+    y1 = sl_oracle.matmul_gemm(fmt, blocks, n, k, x, threads=1)
+    assert np.all(np.abs(y1 - exact) <= 2e-3 + 1e-4 * np.abs(exact))
+    for threads in (3, 8):
+        assert np.array_equal(y1.view(np.uint32), sl_oracle.matmul_gemm(fmt, blocks, n, k, x, threads=threads).view(np.uint32))
+    # the sequential fused multiply-add chain over k, spelled out for a few outputs
+    w = sl_oracle.dequantize(fmt, blocks, n, k)
+    for (t, r) in [(0, 0), (m - 1, n - 1), (m // 2, n // 3)]:
+        acc = np.float32(0)
+        for i in range(k):
+            acc = np.float32(np.float64(x[t, i]) * np.float64(w[r, i]) + np.float64(acc))   # exact product, one rounding
+        assert acc == y1[t, r]
+
+
+def test_run_dispatch_switches_at_32_rows():
+    from sharplight_b200 import synth
+    n, k = 48, 512
+    blocks = synth.weight_blocks("Q4_K", n, k, 5)
+    x = synth.activations(40, k, 6)
+    assert np.array_equal(sl_oracle.matmul_run(12, blocks, n, k, x[:31], threads=4),
+                          sl_oracle.matmul_intdot_pooled(12, blocks, n, k, x[:31], threads=4))
+    assert np.array_equal(sl_oracle.matmul_run(12, blocks, n, k, x[:32], threads=4),
+                          sl_oracle.matmul_gemm(12, blocks, n, k, x[:32], threads=4))

@@ -51,6 +51,34 @@ def test_static_scratch_matches_allocating_entry_point(cuda_device, type_name, n
         w.dispose()
 
 
+@pytest.mark.parametrize("n,k,rows", [(48, 28672, 4), (32, 32768, 4), (40, 256, 3), (40, 32, 4)])
+def test_static_scratch_long_and_short_k(cuda_device, n, k, rows):
+    """Four rows at a K where the kernel's shared memory holds fewer rows per launch (the rows then go in two launches on
+    the same scratch), and at a K of one super-tile or less (a one-warp CTA then owns two outputs per thread)."""
+    lib = N.load()
+    type_name = "Q4_K" if k % 256 == 0 else "Q8_0"
+    blocks = synth.weight_blocks(type_name, n, k, seed=k)
+    w = cuda_device.upload_weight(type_name, (n, k), blocks)
+    op = MatMulOp(cuda_device, w, 4)
+    op.set_kernel(N.KERNEL_MMVQ)
+    try:
+        x = synth.activations(rows, k, seed=91)
+        expected = op.run(x)
+        xd = _dev_buffer(lib, cuda_device, x)
+        y = np.full((rows, n), np.nan, np.float32)
+        yd = _dev_buffer(lib, cuda_device, y)
+        rc = lib.slc_matmul_run_static(w.handle, xd, N.F32, rows, k, yd, n, None)
+        assert rc == N.OK, lib.slc_static_last_error()
+        assert lib.slc_device_sync(cuda_device.handle) == N.OK
+        assert lib.slc_buffer_download(cuda_device.handle, y.ctypes.data_as(C.c_void_p), yd, y.nbytes) == N.OK
+        lib.slc_buffer_free(cuda_device.handle, xd)
+        lib.slc_buffer_free(cuda_device.handle, yd)
+        assert np.array_equal(y.view(np.uint32), expected.view(np.uint32))
+    finally:
+        op.dispose()
+        w.dispose()
+
+
 def test_static_scratch_rejects_what_does_not_fit(cuda_device):
     lib = N.load()
     w = cuda_device.upload_weight("Q8_0", (16, 256), synth.weight_blocks("Q8_0", 16, 256, 1))
