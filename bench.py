@@ -2,20 +2,28 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--rows M]
 
-One JSON line on stdout (rank 0). Metric: quantized mat-vec HBM GB/s = weight bytes streamed per second, the figure the
+One JSON line on stdout (rank 0). Metric: quantized MatMul weight GB/s = weight bytes streamed per second, the figure the
 reference's own benchmark reports (tests/Sharplight.Cpu.Tests/BenchTests.cs:82-99 of the Sharplight tree).
 
-Workload at N = 1: benchmark configuration 2, the Llama-3-8B FFN shape -- Q4_K weight [14336, 4096], f32 activations ~N(0,1),
-M = 1 row. One step = the MatMul (8-bit activation quantization + mat-vec) over each of COPIES independent weight
-matrices of that shape (COPIES x 33 MB is far larger than the 126 MB L2, so every weight byte comes from HBM).
-  value : device-resident inputs and outputs, timed with CUDA events on the launching stream.
-  e2e   : the same step through the provider API (a compiled segment: SetInput / Execute / GetOutput) with HOST
-          buffers: host->device copy of x, kernels, device->host copy of every y inside the timed region.
-  roofline : the mat-vec kernel alone (activations already quantized), algorithmic bytes / measured launch time.
-  cpu_baseline : the CPU restatement of the reference's integer-dot MatMul (oracle/) on the host cores, bounded sample.
+The workload is the same at every N, so the per-N values form a strong-scaling curve: benchmark configuration 5, the
+quantized MatMuls of a Llama-3-70B-shaped layer stack (80 layers, Q4_K, 38.5 GB of weights: it fits one B200), at
+decode batch M = --rows (default 1), tensor parallel over the N GPUs -- q/k/v and gate/up column-split (stacked into
+one MatMul each), o and down row-split with the f32 partial outputs summed over the ranks. One step = every MatMul of
+every layer once, activation quantization included.
+  value    : device-resident inputs and outputs, the step replayed as one CUDA graph, timed with CUDA events on the
+             launching stream, max over ranks; 38.5 GB / step time.
+  e2e      : the same step through the provider API (one compiled segment: SetInput / Execute / GetOutput) with HOST
+             buffers: host->device copy of the four activation inputs and a device->host copy of every MatMul output
+             into the caller's array, inside the timed region.
+  roofline : the dominant kernel alone -- benchmark configuration 2's Q4_K [14336, 4096] mat-vec at M = 1 on
+             pre-quantized activations -- algorithmic bytes / measured launch time against the measured HBM peak.
+  configs  : (N = 1) every other benchmark configuration: configuration 1 (Q8_0 [3072, 1024]), configuration 2 at
+             M = 1 / 4 / 16 / 64, configuration 3 (Q4_0 prefill GEMM, with its own roofline, e2e and CPU baseline),
+             configuration 4 (8B decode step at batch 32, with a per-MatMul breakdown).
+  tp_stack : the stack at M = 1 / 8 / 64 and the 2048-row prefill.
+  cpu_baseline : the CPU restatement of the reference's MatMul (oracle/) on the host cores, bounded sample.
 With --impl reference the CPU arm is the measured one (the reference's managed CPU provider cannot be built here: no
 .NET toolchain; the restatement is labelled "port").
-For N > 1 every rank streams its own COPIES matrices (weak scaling, no data-path collective for this workload).
 """
 from __future__ import annotations
 
@@ -32,22 +40,25 @@ if ROOT not in sys.path:
 
 import numpy as np  # noqa: E402
 
-TYPE, N_ROWS_W, K_COLS = "Q4_K", 14336, 4096
-COPIES = 32
-# dram__bytes_read.sum + dram__bytes_write.sum of one matvec_kernel launch on this workload at M = 1, from the ncu capture
-# summarised in profiles/matvec_q4k_m1_14336x4096.md (the algorithmic bytes are 33 092 608)
-CONFIG2_M1_DRAM_BYTES = 33062656
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+NOMINAL_INT8_TOPS = 4500.0
+KERNEL_NAMES = {1: "mmvq (dp4a)", 2: "skinny (int8 mma.sync)", 3: "mmq (tcgen05 kind::i8)", 4: "tile (tcgen05 kind::f16, stream-K)"}
+# dram__bytes_read.sum + dram__bytes_write.sum of one mat-vec launch on configuration 2 at M = 1, from one ncu capture
+# of this kernel (the algorithmic bytes are 33 092 608); quoted only while the kernel family of the run is the captured one
+CONFIG2_M1_DRAM_BYTES = 33062656
 
 
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_BF16_TFLOPS, "source": "fallback"}
     if os.path.exists(path):
         try:
-            return float(json.load(open(path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+            j = json.load(open(path))
+            out = {"hbm_gbs": float(j["hbm_gbs"]), "bf16_tflops": float(j["bf16_tflops"]), "source": "measured (MEASURED_PEAKS.json)"}
         except Exception:
             pass
-    return FALLBACK_HBM_GBS, "fallback"
+    return out
 
 
 class ClockSampler:
@@ -100,200 +111,139 @@ class ClockSampler:
         return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def cpu_arm(rows: int, seconds: float = 12.0):
-    """The reference's CPU integer-dot MatMul (restated in oracle/) on all host cores; bounded sample."""
-    from oracle import sl_oracle
-    from sharplight_b200 import synth
-    threads = os.cpu_count() or 1
-    copies = 8   # 264 MB of distinct weights, so the sample does not sit in the last-level cache
-    blocks = [synth.weight_blocks(TYPE, N_ROWS_W, K_COLS, seed=200 + i) for i in range(copies)]
-    x = synth.activations(rows, K_COLS, seed=300)
-    wbytes = synth.weight_bytes(TYPE, N_ROWS_W, K_COLS)
-    for i in range(2):
-        sl_oracle.matmul_intdot(12, blocks[i], N_ROWS_W, K_COLS, x, threads=threads, tier=1)
-    t0 = time.perf_counter()
-    done = 0
-    while True:
-        sl_oracle.matmul_intdot(12, blocks[done % copies], N_ROWS_W, K_COLS, x, threads=threads, tier=1)
-        done += 1
-        el = time.perf_counter() - t0
-        if el > seconds or done >= 4000:
+# ---- the CPU arm -----------------------------------------------------------------------------------------------------
+
+def cpu_p10(fn, budget_s: float, min_runs: int = 3, want_runs: int = 30, warmups: int = 5):
+    """The reference's timing rule (tests/Sharplight.Cpu.Tests/BenchTests.cs:82-99): warm-ups, then the 10th percentile of
+    at least 30 runs -- cut short (never below min_runs) when the time budget of this bounded sample runs out."""
+    t_w = time.perf_counter()
+    for i in range(warmups):
+        fn()
+        if time.perf_counter() - t_w > 0.25 * budget_s and i >= 1:
             break
-    return {"value": wbytes * done / el / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
-            "tier": sl_oracle.fast_tier_name(),
-            "sample": f"{done} mat-vecs of the {TYPE} [{N_ROWS_W},{K_COLS}] weight at M={rows} over {copies} rotating "
-                      f"copies, {el:.1f} s, {threads} threads"}, el / done
+    times = []
+    t0 = time.perf_counter()
+    while len(times) < want_runs:
+        a = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - a)
+        if time.perf_counter() - t0 > budget_s and len(times) >= min_runs:
+            break
+    return float(np.percentile(times, 10)), len(times)
 
 
-def cpu_arm_stack(rows: int, seconds: float):
-    """The N > 1 workload on the host cores: the four MatMuls of a Llama-3-70B-shaped layer (stacked qkv, o, stacked
-    gate_up, down), an eighth of the output rows of each (60 MB of Q4_K blocks), in rotation; weight GB/s."""
+def cpu_stack_baseline(rows: int, seconds: float):
+    """The 70B-shaped stack on the host cores: the four MatMuls of one layer (stacked qkv, o, stacked gate_up, down; 481 MB
+    of Q4_K blocks, full size), driven as the reference's CPU provider drives them -- integer dots in
+    clamp(N / 16, 1, 4 x threads) chunks on a spinning worker pool below 32 rows, the f32 GEMM from 32 rows
+    (src/Sharplight.Cpu/MatMulOp.cs:125-213) -- p10 per MatMul, summed; weight GB/s."""
     from oracle import sl_oracle
     from sharplight_b200 import synth, tp
     threads = os.cpu_count() or 1
     mats = []
     for i, (name, parts, k, _, _) in enumerate(tp.fused_layer_matmuls(tp.LLAMA70B)):
-        n = sum(parts) // 8
-        mats.append((synth.weight_blocks("Q4_K", n, k, seed=400 + i), n, k, synth.activations(rows, k, seed=410 + i)))
-    layer_bytes = sum(synth.weight_bytes("Q4_K", n, k) for _, n, k, _ in mats)
-    for b, n, k, x in mats:
-        sl_oracle.matmul_intdot(12, b, n, k, x, threads=threads, tier=1)
-    t0, done = time.perf_counter(), 0
-    while True:
-        for b, n, k, x in mats:
-            sl_oracle.matmul_intdot(12, b, n, k, x, threads=threads, tier=1)
-        done += 1
-        el = time.perf_counter() - t0
-        if el > seconds or done >= 2000:
-            break
-    gbs = layer_bytes * done / el / 1e9
-    return {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "tier": sl_oracle.fast_tier_name(),
-            "sample": f"{done} passes over one layer's four MatMuls at an eighth of their output rows "
-                      f"({layer_bytes / 1e6:.0f} MB of Q4_K blocks) at M={rows}, {el:.1f} s, {threads} threads"}, gbs
+        n = sum(parts)
+        mats.append((name, synth.weight_blocks("Q4_K", n, k, seed=400 + i), n, k, synth.activations(rows, k, seed=410 + i)))
+    layer_bytes = sum(synth.weight_bytes("Q4_K", n, k) for _, _, n, k, _ in mats)
+    total, runs = 0.0, []
+    for name, b, n, k, x in mats:
+        p10, nruns = cpu_p10(lambda: sl_oracle.matmul_run(12, b, n, k, x, threads=threads), seconds / len(mats))
+        total += p10
+        runs.append(nruns)
+    gbs = layer_bytes / total / 1e9
+    path = "f32 GEMM (" + sl_oracle.gemm_tile_name() + ")" if rows >= 32 else "integer dots (" + sl_oracle.fast_tier_name() + ")"
+    return {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "path": path,
+            "sample": f"one layer's four MatMuls at full size ({layer_bytes / 1e6:.0f} MB of Q4_K blocks) at M={rows}, p10 of "
+                      f"{min(runs)}-{max(runs)} runs each after warm-ups, {threads} threads; the stack's step time is 80 x the layer's"}, gbs
+
+
+def cpu_matmul_baseline(type_name: str, n: int, k: int, rows: int, seconds: float):
+    """One MatMul shape on the host cores through the reference's row-count dispatch; (seconds per MatMul p10, runs)."""
+    from oracle import sl_oracle
+    from sharplight_b200 import synth
+    fmt = {"Q4_0": 2, "Q8_0": 8, "Q4_K": 12, "Q6_K": 14}[type_name]
+    threads = os.cpu_count() or 1
+    b = synth.weight_blocks(type_name, n, k, seed=77)
+    x = synth.activations(rows, k, seed=78)
+    p10, runs = cpu_p10(lambda: sl_oracle.matmul_run(fmt, b, n, k, x, threads=threads), seconds)
+    return p10, runs, threads
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    seconds = max(3.0, min(60.0, 0.25 * (args.steps + args.warmup)))
-    if int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.gpus > 1:
-        # the N > 1 arm's workload: the 70B-shaped stack (the CPU has no tensor parallelism: one socket, all threads)
-        from sharplight_b200 import tp
-        base, gbs = cpu_arm_stack(args.rows, seconds)
-        total = tp.layer_weight_bytes(tp.LLAMA70B) * tp.LLAMA70B["layers"]
-        line = {"impl": "reference", "metric": "quant mat-vec HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / (gbs * 1e9) * 1e3,
-                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
-                "config": {"workload": f"configs[4]: Llama-3-70B-shaped stack, 80 layers, Q4_K, decode M={args.rows}, on the "
-                                       "host cores; bounded sample, step time extrapolated to the 38.5 GB stack"},
-                "cpu_baseline": base,
-                "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-                "note": "CPU restatement (oracle/) of the reference's Sharplight.Cpu integer-dot MatMul; the managed "
-                        "reference cannot be built here (no .NET toolchain)"}
-        print(json.dumps(line), flush=True)
-        return
-    base, per_matvec = cpu_arm(args.rows, seconds)
-    line = {"impl": "reference", "metric": "quant mat-vec HBM GB/s", "value": base["value"], "unit": "GB/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_matvec * COPIES * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int8 -> int32, f32 scales",
-            "data": "synthetic",
-            "config": {"workload": f"configs[1]: {TYPE} [{N_ROWS_W},{K_COLS}] mat-vec, M={args.rows}; bounded sample, "
-                                   f"step time extrapolated to {COPIES} matrices"},
+    from oracle import sl_oracle  # noqa: F401  (the reference arm is the one place besides the baseline leg that runs oracle/)
+    from sharplight_b200 import tp
+    seconds = max(8.0, min(60.0, 0.5 * (args.steps + args.warmup)))
+    base, gbs = cpu_stack_baseline(args.rows, seconds)
+    total = tp.layer_weight_bytes(tp.LLAMA70B) * tp.LLAMA70B["layers"]
+    line = {"impl": "reference", "metric": "quant MatMul weight GB/s", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / (gbs * 1e9) * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
+            "config": {"workload": stack_workload_name(args.rows, 1) + " -- on the host cores (the CPU has no tensor "
+                                   "parallelism: one socket, all threads); bounded sample, step time extrapolated to the 38.5 GB stack"},
             "cpu_baseline": base,
-            "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "note": "CPU restatement (oracle/) of the reference's Sharplight.Cpu integer-dot MatMul; the managed "
-                    "reference cannot be built here (no .NET toolchain)"}
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "CPU restatement (oracle/) of the reference's Sharplight.Cpu MatMul; the managed reference cannot be built "
+                    "here (no .NET toolchain)"}
     print(json.dumps(line), flush=True)
 
 
-def prefill_leg(device, torch, N, synth, stream, steps):
-    """benchmark configuration 3: Q4_0 [4096, 4096], bf16 activations [2048, 4096] on the tcgen05 int8 GEMM.
-    Operator time = quantization + GEMM (what the reference's published TFLOPS include,
-    tests/Sharplight.Vulkan.Tests/BenchTests.cs:28-46); kernel time = the GEMM alone on quantized activations."""
-    from sharplight_b200 import MatMulOp, SharedActivation
-    from sharplight_b200.provider import to_bf16_bits
-    n, k, m, copies = 4096, 4096, 2048, 8
-    base = synth.weight_blocks("Q4_0", n, k, seed=300)
-    ws = [device.upload_weight("Q4_0", (n, k), np.roll(base.reshape(n, -1), 11 * i, axis=0).reshape(-1))
-          for i in range(copies)]
-    ops = [MatMulOp(device, w, m) for w in ws]
-    x = torch.from_numpy(to_bf16_bits(synth.activations(m, k, seed=301)).view(np.int16)).cuda()
-    y = torch.empty((copies, m, n), dtype=torch.float32, device="cuda")
-    act = SharedActivation(device, m, k)
-    sp = stream.cuda_stream
+def stack_workload_name(rows: int, world: int) -> str:
+    return (f"configs[4]: Llama-3-70B-shaped layer stack, 80 layers, Q4_K (38.5 GB), decode M={rows}, tensor parallel x{world}: "
+            "column-split stacked q/k/v and gate/up, row-split o/down with the f32 partial outputs summed over the ranks")
 
-    def op_step(p=sp):
-        for i, op in enumerate(ops):
-            op.run_pointers(x.data_ptr(), N.BF16, m, k, True, y[i].data_ptr(), n, True, p)
 
-    def gemm_step(p=sp):
-        for i, op in enumerate(ops):
-            act.matmul(op, y[i].data_ptr(), n, p)
-
-    def timed(fn):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=torch.cuda.Stream()):
-            fn(torch.cuda.current_stream().cuda_stream)
-        for _ in range(3):
-            g.replay()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(steps):
-            g.replay()
-        e1.record(stream)
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) * 1e-3 / (steps * copies)
-
-    t_op = timed(op_step)
-    act.quantize(x.data_ptr(), N.BF16, m, k, sp)
-    t_gemm = timed(gemm_step)
-    family, _ = ops[0].last_kernel()
-    ops_count = 2.0 * m * n * k
-    out = {"workload": "configs[2]: Q4_0 [4096,4096] x bf16 [2048,4096], 8 rotating weight copies",
-           "operator_tops": ops_count / t_op / 1e12, "gemm_kernel_tops": ops_count / t_gemm / 1e12,
-           "operator_us": t_op * 1e6, "gemm_kernel_us": t_gemm * 1e6,
-           "frac_of_nominal_int8_4500": ops_count / t_gemm / 4.5e15,
-           "kernel_family": {1: "mmvq (dp4a)", 2: "skinny (int8 mma)", 3: "mmq (tcgen05)"}[family],
-           "block_scale_fmas": m * n * (k // 32)}
-    for op in ops:
-        op.dispose()
-    for w in ws:
-        w.dispose()
-    act.dispose()
-    return out
-
+# ---- GPU legs --------------------------------------------------------------------------------------------------------
 
 class TpStack:
-    """benchmark configuration 5: the quantized MatMuls of a Llama-3-70B-shaped layer stack, tensor-parallel over the ranks:
-    q / k / v / gate / up column-split (stacked into one qkv and one gate_up MatMul per layer), o / down row-split with
-    an all-reduce (sum) of the f32 partial outputs.
+    """benchmark configuration 5: the quantized MatMuls of a Llama-3-70B-shaped layer stack, tensor-parallel over the
+    ranks: q / k / v / gate / up column-split (stacked into one qkv and one gate_up MatMul per layer), o / down row-split
+    with an all-reduce (sum) of the f32 partial outputs.
     Attention, norms and the activation function are not on the path: the inputs of o and down are fresh synthetic
     activations of the sharded shape. One step = every MatMul of every layer once, for `rows` activation rows (any
     count up to max_rows: decode batches and the prefill run on the same stack)."""
 
+    IN_KERNEL_ROWS = 16   # measured on 8 GPUs: in-kernel sum 2.2x faster than NCCL at 1 row, 1.5x at 8, 0.9x at 64
+
     def __init__(self, device, torch, dist, N, synth, rank, world, max_rows, layers, arch, type_name="Q4_K"):
         from sharplight_b200 import MatMulOp, SharedActivation, TpExchange, tp
-        self.torch, self.dist, self.N, self.world = torch, dist, N, world
-        # the receive area of the in-kernel all-reduce (one serves o and down of every layer: same output width)
+        self.torch, self.dist, self.N, self.world, self.device = torch, dist, N, world, device
         self.exchange = None
         if world > 1:
+            # the receive area of the in-kernel all-reduce (one serves o and down of every layer: same output width)
             self.exchange = TpExchange(device, rank, world, N.TP_MAX_ROWS, arch["hidden"])
             self.exchange.connect_group(dist)
             dist.barrier()
         rows = max_rows
-        self.layers, self.arch = layers, arch
-        # q / k / v and gate / up are stacked along N (one MatMul each), as a runtime stores them
+        self.layers, self.arch, self.type_name = layers, arch, type_name
         self.specs = [(name, sum(parts), k, split, inp) for name, parts, k, split, inp in tp.fused_layer_matmuls(arch)]
         self.total_weight_bytes = tp.layer_weight_bytes(arch, type_name) * layers
-        h, f = arch["hidden"], arch["ffn"]
-        self.weights, self.ops = [], []
+        self.weights, self.ops, self.layer_weights = [], [], []
         shard_blocks = {}
         for name, parts, k, split, _ in tp.fused_layer_matmuls(arch):
             nl, kl = tp.fused_shard_shape(parts, k, split, rank, world, type_name, arch["head_dim"])
             shard_blocks[name] = (synth.weight_blocks(type_name, nl, kl, seed=500 + 7 * rank + len(shard_blocks)), nl, kl)
         for _ in range(layers):
-            layer_ops = {}
+            layer_ops, layer_w = {}, {}
             for name, (blocks, nl, kl) in shard_blocks.items():
                 w = device.upload_weight(type_name, (nl, kl), blocks)
                 self.weights.append(w)
+                layer_w[name] = w
                 layer_ops[name] = MatMulOp(device, w, rows)
             self.ops.append(layer_ops)
-        dims = {name: (nl, kl) for name, (_, nl, kl) in shard_blocks.items()}
-        self.dims = dims
+            self.layer_weights.append(layer_w)
+        self.dims = {name: (nl, kl) for name, (_, nl, kl) in shard_blocks.items()}
+        dims = self.dims
         g = torch.Generator(device="cuda").manual_seed(1234 + rank)
         mk = lambda r, c: torch.randn((r, c), generator=g, device="cuda", dtype=torch.float32)
+        h = arch["hidden"]
         self.x = {"x_attn": mk(rows, h), "x_ffn": mk(rows, h), "x_o": mk(rows, dims["o"][1]), "x_down": mk(rows, dims["down"][1])}
         self.y = {name: torch.empty((rows, dims[name][0]), device="cuda", dtype=torch.float32) for name in dims}
         self.act = {key: SharedActivation(device, rows, v.shape[1]) for key, v in self.x.items()}
         self.launches_per_step = 0
-
-    IN_KERNEL_ROWS = 16   # measured on 8 GPUs: in-kernel sum 2.2x faster than NCCL at 1 row, 1.5x at 8, 0.9x at 64
 
     def step(self, rows, sp, in_kernel=None):
         """in_kernel: row-split MatMuls sum over the ranks inside their kernel (peer stores over NVLink), possible up
@@ -320,6 +270,22 @@ class TpStack:
                             self.dist.all_reduce(y[:rows])
                     launches += layer_ops[name].last_kernel()[1]
         self.launches_per_step = launches
+
+    def segment(self, max_rows: int):
+        """The same stack as one compiled segment of the provider API, on the weights already resident: four host inputs,
+        every MatMul's output a host output; row-split nodes sum over the ranks through the stack's exchange."""
+        from sharplight_b200 import CompileOptions, GraphSegment, MatMulNode, WeightInfo
+        nodes, outputs = [], []
+        for li, layer_w in enumerate(self.layer_weights):
+            for name, _, _, split, inp in self.specs:
+                nl, kl = self.dims[name]
+                out = f"{name}{li}"
+                nodes.append(MatMulNode(out, inp, WeightInfo(self.type_name, (nl, kl), None, resident=layer_w[name]), out,
+                                        allreduce=(split == "row" and self.world > 1)))
+                outputs.append(out)
+        seg = self.device.compile(GraphSegment(nodes, ["x_attn", "x_o", "x_ffn", "x_down"], outputs),
+                                  CompileOptions(max_rows=max_rows, exchange=self.exchange))
+        return seg, outputs
 
     def dispose(self):
         if self.exchange is not None:
@@ -367,10 +333,199 @@ def time_graphed(torch, dist, world, stream, fn, steps, warmup, use_graph=True):
     return ms
 
 
-def decode_step_leg(args, torch, dist, device, N, synth, stream):
+def stack_e2e(args, torch, dist, world, stack, rows, steps):
+    """The stack's step through the provider API with host buffers: SetInput of the four activation inputs (pinned
+    staging, host->device), Execute (one quantization per input and layer, every MatMul; a captured graph from the third
+    call), GetOutput of every MatMul's result copied into the caller's array."""
+    seg, outputs = stack.segment(rows)
+    xs = {k: v[:rows].cpu().numpy() for k, v in stack.x.items()}
+    got = {}
+
+    def step_host():
+        for k, v in xs.items():
+            seg.set_input(k, v)
+        seg.execute({"T": rows})
+        for name in outputs:
+            got[name] = seg.get_output(name, copy=True)
+
+    for _ in range(4):
+        step_host()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step_host()
+    torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) * 1e3 / steps   # every step ends with a host-side wait: wall clock is the device's clock here
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    # what was timed equals the device-resident path: the last layer's outputs against the graph-replayed stack's
+    stack.step(rows, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    last = len(stack.layer_weights) - 1
+    same = bool(all(np.array_equal(got[f"{name}{last}"], stack.y[name][:rows].cpu().numpy()) for name in stack.dims))
+    h2d = sum(v.nbytes for v in xs.values())
+    d2h = sum(rows * stack.dims[name][0] * 4 for name in stack.dims) * len(stack.layer_weights)
+    seg.dispose()
+    return ms, h2d, d2h, same
+
+
+def kernel_times(torch, device, N, synth, stream, type_name, n, k, rows, copies, steps, distinct=True, kernel=None):
+    """One MatMul shape over `copies` weight matrices (distinct: rotating copies, so the weights come from HBM; else
+    the same matrix every time: L2-resident when it fits). Returns seconds per MatMul for (operator = quantize + kernel,
+    each launch waiting for its predecessor; kernel alone on shared pre-quantized activations), and the kernel family."""
+    from sharplight_b200 import MatMulOp, SharedActivation
+    base = synth.weight_blocks(type_name, n, k, seed=100 + n % 97)
+    nw = copies if distinct else 1
+    ws = [device.upload_weight(type_name, (n, k), np.roll(base.reshape(n, -1), i * 37, axis=0).reshape(-1)) for i in range(nw)]
+    ops = [MatMulOp(device, ws[i % nw], rows) for i in range(copies)]
+    if kernel is not None:
+        for op in ops:
+            op.set_kernel(kernel)
+    x = torch.randn((rows, k), device="cuda", dtype=torch.float32)
+    y = torch.empty((copies, rows, n), dtype=torch.float32, device="cuda")
+    act = SharedActivation(device, rows, k)
+
+    def op_step(sp):
+        for i, op in enumerate(ops):
+            op.run_pointers(x.data_ptr(), N.F32, rows, k, True, y[i].data_ptr(), n, True, sp)
+
+    def kern_step(sp):
+        for i, op in enumerate(ops):
+            act.matmul(op, y[i].data_ptr(), n, sp)
+
+    t_op = time_graphed(torch, None, 1, stream, op_step, steps, 3) * 1e-3 / copies
+    act.quantize(x.data_ptr(), N.F32, rows, k, stream.cuda_stream)
+    t_k = time_graphed(torch, None, 1, stream, kern_step, steps, 3) * 1e-3 / copies
+    family, launches = ops[0].last_kernel()
+    for op in ops:
+        op.dispose()
+    for w in ws:
+        w.dispose()
+    act.dispose()
+    return t_op, t_k, family, launches
+
+
+def hbm_entry(peaks, type_name, n, k, rows, t_op, t_k, family, synth):
+    wbytes = synth.weight_bytes(type_name, n, k)
+    algo = wbytes + rows * k + rows * (k // 32) * 8 + rows * n * 4
+    return {"kernel_us": t_k * 1e6, "operator_us": t_op * 1e6, "achieved": algo / t_k / 1e9, "unit": "GB/s",
+            "frac": algo / t_k / 1e9 / peaks["hbm_gbs"], "operator_frac": algo / t_op / 1e9 / peaks["hbm_gbs"],
+            "algorithmic_bytes_per_launch": algo, "kernel_family": KERNEL_NAMES.get(family, str(family))}
+
+
+def config_legs(args, torch, device, N, synth, stream, peaks):
+    """Configurations 1 and 2 (HBM-bound mat-vec / skinny shapes): kernel and operator time, achieved GB/s over the
+    algorithmic bytes, fraction of the measured HBM peak."""
+    steps = max(5, min(args.steps, 20))
+    out = {}
+    c1 = {}
+    t_op, t_k, fam, _ = kernel_times(torch, device, N, synth, stream, "Q8_0", 3072, 1024, 1, 48, steps, distinct=True)
+    c1["rotating_48_copies_160MB"] = hbm_entry(peaks, "Q8_0", 3072, 1024, 1, t_op, t_k, fam, synth)
+    t_op, t_k, fam, _ = kernel_times(torch, device, N, synth, stream, "Q8_0", 3072, 1024, 1, 48, steps, distinct=False)
+    c1["l2_resident"] = hbm_entry(peaks, "Q8_0", 3072, 1024, 1, t_op, t_k, fam, synth)
+    c1["workload"] = "configs[0]: Q8_0 [3072,1024] mat-vec, M=1; 3.3 MB of weights per launch (time floor 0.51 us at the measured peak: launch latency dominates)"
+    out["config1"] = c1
+    c2 = {"workload": "configs[1]: Q4_K [14336,4096], 32 rotating weight copies (1057 MB > L2)"}
+    for rows in (1, 4, 16, 64):
+        t_op, t_k, fam, _ = kernel_times(torch, device, N, synth, stream, "Q4_K", 14336, 4096, rows, 32, steps)
+        c2[f"M={rows}"] = hbm_entry(peaks, "Q4_K", 14336, 4096, rows, t_op, t_k, fam, synth)
+    out["config2"] = c2
+    return out
+
+
+def prefill_leg(args, device, torch, N, synth, stream, peaks, with_cpu):
+    """benchmark configuration 3: Q4_0 [4096, 4096], bf16 activations [2048, 4096], the tensor-core GEMM.
+    Operator time = quantization + GEMM (what the reference's published TFLOPS include,
+    tests/Sharplight.Vulkan.Tests/BenchTests.cs:28-46); kernel time = the GEMM alone on quantized activations; e2e = one
+    compiled segment with host bf16 activations in and host f32 results out."""
+    from sharplight_b200 import CompileOptions, GraphSegment, MatMulNode, MatMulOp, SharedActivation, WeightInfo
+    from sharplight_b200.provider import to_bf16_bits
+    n, k, m, copies = 4096, 4096, 2048, 8
+    steps = max(5, args.steps // 4)
+    base = synth.weight_blocks("Q4_0", n, k, seed=300)
+    ws = [device.upload_weight("Q4_0", (n, k), np.roll(base.reshape(n, -1), 11 * i, axis=0).reshape(-1)) for i in range(copies)]
+    ops = [MatMulOp(device, w, m) for w in ws]
+    x_bits = to_bf16_bits(synth.activations(m, k, seed=301))
+    x = torch.from_numpy(x_bits.view(np.int16)).cuda()
+    y = torch.empty((copies, m, n), dtype=torch.float32, device="cuda")
+    act = SharedActivation(device, m, k)
+
+    def op_step(sp):
+        for i, op in enumerate(ops):
+            op.run_pointers(x.data_ptr(), N.BF16, m, k, True, y[i].data_ptr(), n, True, sp)
+
+    def gemm_step(sp):
+        for i, op in enumerate(ops):
+            act.matmul(op, y[i].data_ptr(), n, sp)
+
+    t_op = time_graphed(torch, None, 1, stream, op_step, steps, 3) * 1e-3 / copies
+    act.quantize(x.data_ptr(), N.BF16, m, k, stream.cuda_stream)
+    t_gemm = time_graphed(torch, None, 1, stream, gemm_step, steps, 3) * 1e-3 / copies
+    family, _ = ops[0].last_kernel()
+    ops_count = 2.0 * m * n * k
+    tops = ops_count / t_gemm / 1e12
+    # e2e: one segment holding the eight MatMuls, host bf16 in, host f32 out
+    nodes = [MatMulNode(f"mm{i}", "x", WeightInfo("Q4_0", (n, k), None, resident=ws[i]), f"y{i}", x_dtype="bf16") for i in range(copies)]
+    seg = device.compile(GraphSegment(nodes, ["x"], [f"y{i}" for i in range(copies)]), CompileOptions(max_rows=m))
+    got = [None] * copies
+
+    def step_host():
+        seg.set_input("x", x_bits)
+        seg.execute({"T": m})
+        for i in range(copies):
+            got[i] = seg.get_output(f"y{i}", copy=True)
+
+    for _ in range(4):
+        step_host()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e_steps = max(3, steps // 2)
+    for _ in range(e_steps):
+        step_host()
+    torch.cuda.synchronize()
+    t_e2e = (time.perf_counter() - t0) / (e_steps * copies)
+    same = bool(np.array_equal(got[0], y[0].cpu().numpy()))
+    seg.dispose()
+    ceiling = 1100.0
+    out = {"workload": "configs[2]: Q4_0 [4096,4096] x bf16 [2048,4096], 8 rotating weight copies",
+           "operator_tops": ops_count / t_op / 1e12, "gemm_kernel_tops": tops,
+           "operator_us": t_op * 1e6, "gemm_kernel_us": t_gemm * 1e6,
+           "kernel_family": KERNEL_NAMES.get(family, str(family)),
+           "block_scale_fmas": m * n * (k // 32),
+           "roofline": {"bound": "tensor", "achieved": tops, "unit": "TOP/s", "peak": NOMINAL_INT8_TOPS,
+                        "frac": tops / NOMINAL_INT8_TOPS, "peak_source": "nominal dense int8 (no int8 figure in MEASURED_PEAKS.json)",
+                        "frac_of_2x_measured_bf16": tops / (2.0 * peaks["bf16_tflops"]),
+                        "ceiling_tops": ceiling, "frac_of_ceiling": tops / ceiling,
+                        "ceiling": "two f32 operations per (row, token, 32-block) on the CUDA cores -- per-block f16 weight "
+                                   "scale x f32 activation scale -- at 128 per clock per SM",
+                        "traffic": None},
+           "e2e": {"value": ops_count / t_e2e / 1e12, "unit": "TOP/s", "h2d_bytes_per_step": int(x_bits.nbytes),
+                   "d2h_bytes_per_step": copies * m * n * 4, "us_per_matmul": t_e2e * 1e6, "equals_device_path": same,
+                   "note": "host bf16 activations in (16.8 MB once per 8 MatMuls), host f32 results out (33.6 MB per MatMul): the "
+                           "copies over PCIe dominate"}}
+    if with_cpu:
+        p10, runs, threads = cpu_matmul_baseline("Q4_0", n, k, m, 12.0)
+        from oracle import sl_oracle
+        out["cpu_baseline"] = {"value": ops_count / p10 / 1e12, "unit": "TOP/s (2 M N K / t; the CPU runs them as f32 FLOPs)",
+                               "cores": threads, "kind": "port", "ms_per_matmul": p10 * 1e3,
+                               "sample": f"p10 of {runs} runs of the reference's f32 GEMM path ({sl_oracle.gemm_tile_name()} micro-kernel, "
+                                         "weights dequantized per 256-value slice) on this shape"}
+    for op in ops:
+        op.dispose()
+    for w in ws:
+        w.dispose()
+    act.dispose()
+    return out
+
+
+def decode_step_leg(args, torch, dist, device, N, synth, stream, peaks):
     """benchmark configuration 4: every quantized MatMul of one decode step of a Llama-3-8B-shaped model on one GPU, a
     continuous batch of 32 sequences: 32 layers of Q4_K weights (qkv, o, gate_up, down) and the Q6_K lm_head
-    [128256, 4096]. Attention, norms and sampling are not on the path."""
+    [128256, 4096]. Attention, norms and sampling are not on the path. With the time of every MatMul type alone."""
     from sharplight_b200 import MatMulOp, SharedActivation, tp
     arch, rows = tp.LLAMA8B, 32
     stack = TpStack(device, torch, dist, N, synth, 0, 1, rows, arch["layers"], arch)
@@ -389,82 +544,64 @@ def decode_step_leg(args, torch, dist, device, N, synth, stream):
     steps = max(3, min(args.steps, 20))
     ms = time_graphed(torch, dist, 1, stream, step, steps, 3, use_graph=not args.no_graph)
     wbytes = stack.total_weight_bytes + synth.weight_bytes("Q6_K", vocab, h)
+    # per-MatMul breakdown: the stack's own ops of one type in turn over the 32 layers (distinct weights), kernel + quantize
+    breakdown = {}
+    for name, n, k, _, inp in stack.specs:
+        def one(sp, name=name, inp=inp):
+            xx = stack.x[inp]
+            for layer_ops in stack.ops:
+                stack.act[inp].quantize(xx.data_ptr(), N.F32, rows, xx.shape[1], sp)
+                stack.act[inp].matmul(layer_ops[name], stack.y[name].data_ptr(), stack.y[name].shape[1], sp)
+        t = time_graphed(torch, dist, 1, stream, one, steps, 2) * 1e-3 / arch["layers"]
+        wb = synth.weight_bytes("Q4_K", n, k)
+        breakdown[name] = {"shape": [n, k], "operator_us": t * 1e6, "weight_gbs": wb / t / 1e9, "frac": wb / t / 1e9 / peaks["hbm_gbs"],
+                           "kernel_family": KERNEL_NAMES.get(stack.ops[0][name].last_kernel()[0])}
+
+    def head_only(sp):
+        head_act.quantize(x.data_ptr(), N.F32, rows, h, sp)
+        head_act.matmul(head, logits.data_ptr(), vocab, sp)
+    t = time_graphed(torch, dist, 1, stream, head_only, steps, 2) * 1e-3
+    wb = synth.weight_bytes("Q6_K", vocab, h)
+    breakdown["lm_head"] = {"shape": [vocab, h], "format": "Q6_K", "operator_us": t * 1e6, "weight_gbs": wb / t / 1e9,
+                            "frac": wb / t / 1e9 / peaks["hbm_gbs"], "kernel_family": KERNEL_NAMES.get(head.last_kernel()[0])}
     out = {"workload": "configs[3]: Llama-3-8B-shaped decode step, 32 layers Q4_K + Q6_K lm_head, batch 32, one GPU",
-           "ms_per_step": ms, "weight_gbs": wbytes / (ms * 1e-3) / 1e9, "weight_bytes_per_step": wbytes,
-           "sequences_per_s": rows / (ms * 1e-3), "launches_per_step": stack.launches_per_step + 2, "steps": steps}
+           "ms_per_step": ms, "weight_gbs": wbytes / (ms * 1e-3) / 1e9, "frac": wbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+           "weight_bytes_per_step": wbytes, "sequences_per_s": rows / (ms * 1e-3),
+           "launches_per_step": stack.launches_per_step + 2, "steps": steps, "per_matmul": breakdown}
     head_act.dispose(); head.dispose(); head_w.dispose(); stack.dispose()
     torch.cuda.synchronize()
     return out
 
 
-def run_tp(args, torch, dist, device, N, synth, stream, world, rank, local):
-    """The N > 1 workload (and the "tp_stack" object of the N = 1 line)."""
-    from sharplight_b200 import tp
-    arch = tp.LLAMA70B
-    layers = args.layers or arch["layers"]
-    out = {}
-    row_counts = sorted(set([args.rows] + ([] if args.tp_main_only else [1, 8, 64, 2048])))
-    stack = TpStack(device, torch, dist, N, synth, rank, world, max(row_counts), layers, arch)
-    flops_per_row = 2.0 * sum(n * k for _, n, k, _, _ in stack.specs) * layers
-    check = None
-    if world > 1:
-        # the in-kernel sum against the collective library's, on the last layer's row-split outputs of one step
-        sp = stream.cuda_stream
-        check = {}
-        for rows in [r for r in (1, 8) if r <= max(row_counts)]:
-            stack.step(rows, sp, in_kernel=True)
-            torch.cuda.synchronize()
-            mine = {name: stack.y[name][:rows].clone() for name in ("o", "down")}
-            stack.step(rows, sp, in_kernel=False)
-            torch.cuda.synchronize()
-            worst, same = 0.0, True
-            for name, got in mine.items():
-                ref = stack.y[name][:rows]
-                worst = max(worst, float(((got - ref).abs().max() / ref.abs().max().clamp_min(1e-30)).item()))
-                everyone = [torch.empty_like(got) for _ in range(world)]
-                dist.all_gather(everyone, got)
-                same = same and all(torch.equal(everyone[0], e) for e in everyone[1:])
-            t = torch.tensor([worst], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            check[rows] = {"max_diff_vs_nccl_over_max_abs": float(t.item()), "bit_identical_on_all_ranks": same}
+def allreduce_check(stack, torch, dist, world, stream, row_counts):
+    """The in-kernel sum against the collective library's, on the last layer's row-split outputs of one step, and across
+    ranks (bit-identical everywhere), at row counts on both exchange protocols (word protocol up to 16 rows, arrival
+    flags above)."""
+    sp = stream.cuda_stream
+    check = {}
     for rows in row_counts:
-        steps = max(3, min(args.steps, 20 if rows <= 64 else 5))
-        ms = time_graphed(torch, dist, world, stream, lambda sp, r=rows: stack.step(r, sp), steps, 3,
-                          use_graph=not args.no_graph)
-        in_kernel = world > 1 and rows <= TpStack.IN_KERNEL_ROWS
-        out[rows] = {"ms_per_step": ms, "weight_gbs": stack.total_weight_bytes / (ms * 1e-3) / 1e9,
-                     "tops": flops_per_row * rows / (ms * 1e-3) / 1e12, "steps": steps,
-                     "launches_per_step": stack.launches_per_step,
-                     "allreduce": "none" if world == 1 else "in the MatMul kernel (peer stores)" if in_kernel else "NCCL",
-                     "allreduces_per_step": 2 * layers if world > 1 else 0}
-        if world > 1 and rows <= N.TP_MAX_ROWS:
-            # the same step with the sum done the other way, for comparison
-            other = time_graphed(torch, dist, world, stream, lambda sp, r=rows: stack.step(r, sp, in_kernel=not in_kernel),
-                                 steps, 3, use_graph=not args.no_graph)
-            out[rows]["ms_per_step_nccl" if in_kernel else "ms_per_step_in_kernel"] = other
-    stack.dispose()
-    torch.cuda.synchronize()
-    res = {"workload": f"configs[4]: Llama-3-70B-shaped stack, {layers} layers, Q4_K, tensor parallel x{world}",
-           "weight_bytes_per_step": tp.layer_weight_bytes(arch) * layers, "by_rows": out}
-    if check is not None:
-        res["in_kernel_allreduce_check"] = check
-    return res
-
-
-def tp_roofline(per_gpu_gbs: float):
-    """The N > 1 line's roofline object: the whole step, not one kernel -- every GPU streams its shard of the weights
-    once per step, so per-GPU weight bytes over the step time against the measured HBM peak says how much of the step
-    is streaming and how much is the latency of its chain of dependent launches."""
-    peak, kind = measured_peaks()
-    return {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
-            "traffic": None, "peak_source": kind,
-            "what": "per-GPU weight bytes of one step / step time (all launches and sums of the step, not one kernel)"}
+        stack.step(rows, sp, in_kernel=True)
+        torch.cuda.synchronize()
+        mine = {name: stack.y[name][:rows].clone() for name in ("o", "down")}
+        stack.step(rows, sp, in_kernel=False)
+        torch.cuda.synchronize()
+        worst, same = 0.0, True
+        for name, got in mine.items():
+            ref = stack.y[name][:rows]
+            worst = max(worst, float(((got - ref).abs().max() / ref.abs().max().clamp_min(1e-30)).item()))
+            everyone = [torch.empty_like(got) for _ in range(world)]
+            dist.all_gather(everyone, got)
+            same = same and all(torch.equal(everyone[0], e) for e in everyone[1:])
+        t = torch.tensor([worst], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        check[rows] = {"max_diff_vs_nccl_over_max_abs": float(t.item()), "bit_identical_on_all_ranks": same}
+    return check
 
 
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from sharplight_b200 import CudaExecutionProvider, MatMulOp, SharedActivation, synth
+    from sharplight_b200 import CudaExecutionProvider, synth, tp
     from sharplight_b200 import native as N
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -478,237 +615,128 @@ def run_ours(args):
     if not av.available:
         raise RuntimeError("CUDA provider unavailable (no CPU fallback): " + av.reason)
     device = provider.open_device([d for d in provider.get_devices() if d.index == local][0])
-    rows, n, k = args.rows, N_ROWS_W, K_COLS
-    wbytes = synth.weight_bytes(TYPE, n, k)
-
-    if world > 1:
-        stream = torch.cuda.Stream()
-        torch.cuda.set_stream(stream)
-        sampler = ClockSampler(local)
-        sampler.start()
-        tpr = run_tp(args, torch, dist, device, N, synth, stream, world, rank, local)
-        clocks = sampler.stop()
-        if rank == 0:
-            main = tpr["by_rows"][rows]
-            line = {"metric": "quant mat-vec HBM GB/s", "value": main["weight_gbs"], "unit": "GB/s", "n_gpus": world,
-                    "steps": max(3, min(args.steps, 20)), "warmup": 3, "ms_per_step": main["ms_per_step"],
-                    "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                    "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
-                    "config": {"workload": tpr["workload"] + f", decode M={rows}: column-split q/k/v/gate/up, row-split "
-                                           "o/down, f32 partial outputs summed inside the MatMul kernel over NVLink peer memory "
-                                           "up to 16 rows, by an NCCL all-reduce above",
-                               "l2": f"inputs larger than L2: {tpr['weight_bytes_per_step'] / world / 1e9:.1f} GB of weights per GPU per step",
-                               "launch": "host launches" if args.no_graph else "CUDA graph replay of the step"},
-                    "gpu_launches": main["launches_per_step"] * max(3, min(args.steps, 20)),
-                    "roofline": tp_roofline(main["weight_gbs"] / world),
-                    "tp_stack": tpr, "clocks": clocks,
-                    "e2e": {"value": main["weight_gbs"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-                            "note": "activations of this workload are device-resident by construction (they come from the "
-                                    "preceding layer); the host-buffer figure is reported by the N=1 run"}}
-            print(json.dumps(line), flush=True)
-        device.dispose()
-        dist.destroy_process_group()
-        return
-
-    base_blocks = synth.weight_blocks(TYPE, n, k, seed=100 + rank)
-    weights, ops = [], []
-    for i in range(COPIES):
-        blocks = np.roll(base_blocks.reshape(n, -1), i * 37, axis=0).reshape(-1)   # distinct matrices, cheap to make
-        w = device.upload_weight(TYPE, (n, k), blocks)
-        weights.append(w)
-        ops.append(MatMulOp(device, w, max(rows, 1)))
-    x_host = torch.from_numpy(synth.activations(rows, k, seed=7)).pin_memory()
-    y_host = torch.empty((COPIES, rows, n), dtype=torch.float32).pin_memory()
-    x_dev = x_host.cuda()
-    y_dev = torch.empty((COPIES, rows, n), dtype=torch.float32, device="cuda")
+    peaks = measured_peaks()
     # an explicit (non-default) launching stream: kernels, CUDA events and graph replays all go to it
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
-    sptr = stream.cuda_stream
-    assert sptr != 0
-    act = SharedActivation(device, max(rows, 1), k)
+    rows = args.rows
+    warmup = max(args.warmup, 3)
+    arch = tp.LLAMA70B
+    layers = args.layers or arch["layers"]
+    row_counts = sorted(set([rows] + ([] if args.tp_main_only else [1, 8, 64, 2048])))
+    stack = TpStack(device, torch, dist, N, synth, rank, world, max(row_counts), layers, arch)
+    flops_per_row = 2.0 * sum(n * k for _, n, k, _, _ in stack.specs) * layers
 
-    def step_device(sp=sptr):
-        for i, op in enumerate(ops):
-            op.run_pointers(x_dev.data_ptr(), N.F32, rows, k, True, y_dev[i].data_ptr(), n, True, sp)
-
-    def step_kernel_only(sp=sptr):
-        for i, op in enumerate(ops):
-            act.matmul(op, y_dev[i].data_ptr(), n, sp)
-
-    def graphed(fn):
-        """Captures one step of fn into a CUDA graph; returns the replay callable."""
-        if args.no_graph:
-            return fn
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=torch.cuda.Stream()):
-            fn(torch.cuda.current_stream().cuda_stream)
-        graphs.append(graph)
-        return graph.replay
-
-    graphs = []
-
-    # End to end through the provider API with host buffers: one compiled segment holding the step's MatMul nodes
-    # (SetInput copies x from host memory, Execute quantizes once and runs every node, GetOutput reads the results
-    # back); the copies in both directions are inside the timed region.
-    from sharplight_b200 import CompileOptions, GraphSegment, MatMulNode, WeightInfo
-    segment = None
-    if not args.no_e2e:
-        nodes = [MatMulNode(f"mm{i}", "x", WeightInfo(TYPE, (n, k), np.roll(base_blocks.reshape(n, -1), i * 37, axis=0).reshape(-1)),
-                            f"y{i}") for i in range(COPIES)]
-        segment = device.compile(GraphSegment(nodes, ["x"], [f"y{i}" for i in range(COPIES)]), CompileOptions(max_rows=max(rows, 1)))
-    x_np = x_host.numpy()
-    e2e_out = [None] * COPIES
-    dev_stream = torch.cuda.ExternalStream(device.stream)
-
-    def step_host():
-        segment.set_input("x", x_np)
-        segment.execute({"T": rows})
-        for i in range(COPIES):
-            e2e_out[i] = segment.get_output(f"y{i}", copy=False)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps, warmup):
-        for _ in range(warmup):
-            fn()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(steps):
-            fn()
-        e1.record(stream)
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms / steps
-
-    # The step's launches are captured once into a CUDA graph (the decode loop of a real model is launch-bound on the
-    # host otherwise); the timed region replays that graph on the launching stream.
+    # ---- the headline: the stack at M = rows, exactly --steps steps after --warmup warm-ups
     sampler = ClockSampler(local)
     sampler.start()
-    ms_step = timed(graphed(step_device), args.steps, max(args.warmup, 3))
+    ms_main = time_graphed(torch, dist, world, stream, lambda sp: stack.step(rows, sp), args.steps, warmup, use_graph=not args.no_graph)
     clocks = sampler.stop()
-    kernel_family, launches_per_call = ops[0].last_kernel()   # launches of one MatMul call, quantization included
-    # kernel pass for the roofline: activations quantized once and shared (as the q/k/v or gate/up MatMuls of a layer
-    # share theirs), only the MatMul kernel in the timed loop, every launch free to run beside its predecessor
-    act.quantize(x_dev.data_ptr(), N.F32, rows, k, sptr)
-    ms_kernel_step = timed(graphed(step_kernel_only), args.steps, 3)
-    main_launches = 1 if launches_per_call == 1 else launches_per_call - 1
-    # end to end through host buffers
-    ms_e2e = float("nan")
-    same = None
-    if not args.no_e2e:
-        for _ in range(3):
-            step_host()
-        barrier()
-        e_steps = max(3, args.steps // 4)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t_wall0 = time.perf_counter()
-        e0.record(dev_stream)
-        for _ in range(e_steps):
-            step_host()
-        e1.record(dev_stream)
-        barrier()
-        wall_ms = (time.perf_counter() - t_wall0) * 1e3 / e_steps
-        ms_e2e = max(e0.elapsed_time(e1) / e_steps, wall_ms)   # the step ends with a host-side wait: take the longer clock
-        # a last correctness look at what was timed: graph-replayed device result == segment result read on the host
-        torch.cuda.synchronize()
-        yd = y_dev.cpu().numpy()
-        same = bool(all(np.array_equal(yd[i], e2e_out[i]) for i in range(COPIES)))
+    launches_main = stack.launches_per_step
+    value = stack.total_weight_bytes / (ms_main * 1e-3) / 1e9
 
-    tp_stack = None
-    if world == 1 and not args.no_tp_stack:
-        tp_stack = run_tp(args, torch, dist, device, N, synth, stream, 1, 0, local)
-    decode_step = None
-    if world == 1 and not args.no_tp_stack:
-        decode_step = decode_step_leg(args, torch, dist, device, N, synth, stream)
-    prefill = None
-    if world == 1 and not args.no_prefill:
-        prefill = prefill_leg(device, torch, N, synth, stream, max(5, args.steps // 10))
+    check = None
+    if world > 1:
+        check = allreduce_check(stack, torch, dist, world, stream, [r for r in (1, 8, 33, 64) if r <= max(row_counts)])
 
-    peak, peak_kind = measured_peaks()
-    algo_bytes = wbytes + rows * k + rows * (k // 32) * 8 + rows * n * 4
-    sec_per_launch = ms_kernel_step * 1e-3 / (COPIES * main_launches)
-    achieved = algo_bytes / sec_per_launch / 1e9
-    value = world * COPIES * wbytes / (ms_step * 1e-3) / 1e9
-    e2e = world * COPIES * wbytes / (ms_e2e * 1e-3) / 1e9
+    by_rows = {}
+    for r in row_counts:
+        steps = max(3, min(args.steps, 20 if r <= 64 else 5))
+        ms = ms_main if r == rows else time_graphed(torch, dist, world, stream, lambda sp, r=r: stack.step(r, sp), steps, 3,
+                                                    use_graph=not args.no_graph)
+        in_kernel = world > 1 and r <= TpStack.IN_KERNEL_ROWS
+        by_rows[r] = {"ms_per_step": ms, "weight_gbs": stack.total_weight_bytes / (ms * 1e-3) / 1e9,
+                      "per_gpu_frac_of_hbm_peak": stack.total_weight_bytes / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                      "tops": flops_per_row * r / (ms * 1e-3) / 1e12, "steps": args.steps if r == rows else steps,
+                      "launches_per_step": stack.launches_per_step if r != rows else launches_main,
+                      "kernel_families": {name: KERNEL_NAMES.get(stack.ops[0][name].last_kernel()[0]) for name in stack.dims},
+                      "allreduce": "none" if world == 1 else "in the MatMul kernel (peer stores)" if in_kernel else "NCCL",
+                      "allreduces_per_step": 2 * layers if world > 1 else 0}
+        if world > 1 and r <= N.TP_MAX_ROWS and not args.tp_main_only:
+            other = time_graphed(torch, dist, world, stream, lambda sp, r=r: stack.step(r, sp, in_kernel=not in_kernel),
+                                 steps, 3, use_graph=not args.no_graph)
+            by_rows[r]["ms_per_step_nccl" if in_kernel else "ms_per_step_in_kernel"] = other
 
+    # ---- end to end through the provider API with host buffers
+    e2e = None
+    if not args.no_e2e and rows <= N.TP_MAX_ROWS:
+        e_steps = max(3, args.steps // 2)
+        ms_e2e, h2d, d2h, same = stack_e2e(args, torch, dist, world, stack, rows, e_steps)
+        e2e = {"value": stack.total_weight_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e, "steps": e_steps, "equals_device_path": same,
+               "note": "one compiled segment of the provider API over the stack's MatMuls: SetInput of the four host activation "
+                       "inputs, Execute, GetOutput of every MatMul's result into the caller's array (copy included); per rank. "
+                       "The segment quantizes each input once and shares the 8-bit copy among the MatMuls that read it, as the "
+                       "reference's lowering does, whereas `value` quantizes per layer"}
+    tp_stack = {"workload": f"configs[4]: Llama-3-70B-shaped stack, {layers} layers, Q4_K, tensor parallel x{world}",
+                "weight_bytes_per_step": stack.total_weight_bytes, "by_rows": by_rows}
+    if check is not None:
+        tp_stack["in_kernel_allreduce_check"] = check
+    stack.dispose()
+    torch.cuda.synchronize()
+
+    line = None
     if rank == 0:
-        base = None
-        if world == 1 and not args.no_cpu:
-            base, _ = cpu_arm(rows)
-        line = {"metric": "quant mat-vec HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-                "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
-                "config": {"workload": f"configs[1]: {TYPE} [{n},{k}] mat-vec (quantize + kernel), M={rows}, "
-                                       f"{COPIES} weight matrices per step per GPU",
-                           "l2": f"inputs larger than L2: {COPIES * wbytes / 1e6:.0f} MB of weights per step vs 126 MB",
-                           "kernel_family": {1: "mmvq (dp4a)", 2: "skinny (int8 mma)", 3: "mmq (tcgen05)"}[kernel_family],
+        line = {"metric": "quant MatMul weight GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+                "warmup": warmup, "ms_per_step": ms_main, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
+                "config": {"workload": stack_workload_name(rows, world) +
+                                       (" (inside the MatMul kernel over NVLink peer memory up to 16 rows, by an NCCL all-reduce above)" if world > 1 else ""),
+                           "l2": f"inputs larger than L2: {stack.total_weight_bytes / world / 1e9:.1f} GB of weights per GPU per step vs 126 MB",
                            "launch": "host launches" if args.no_graph else "CUDA graph replay of the step"},
-                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                             "traffic": CONFIG2_M1_DRAM_BYTES if (rows, n, k, TYPE) == (1, 14336, 4096, "Q4_K") else None,
-                             "peak_source": peak_kind, "kernel_us": sec_per_launch * 1e6,
-                             "algorithmic_bytes_per_launch": algo_bytes, "frac_of_nominal_8000": achieved / 8000.0,
-                             "operator_us": ms_step * 1e3 / COPIES,
-                             "what": "matvec_kernel on shared, already quantized activations (overlapping launches); "
-                                     "operator_us is one whole MatMul of the main loop, quantization included, each "
-                                     "launch waiting for its predecessor"},
-                "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": rows * k * 4,
-                        "d2h_bytes_per_step": COPIES * rows * n * 4, "ms_per_step": ms_e2e,
-                        "note": "one compiled segment of the provider API: SetInput (host x), Execute, GetOutput of every "
-                                "y; x is quantized once and shared by the step's MatMuls, as the reference's lowering "
-                                "shares it, whereas `value` quantizes per MatMul"},
-                "gpu_launches": args.steps * COPIES * launches_per_call,
-                "clocks": clocks, "device_equals_host_path": same}
-        if base is not None:
+                "gpu_launches": launches_main * args.steps, "clocks": clocks, "tp_stack": tp_stack,
+                "stack_frac_of_hbm_peak": value / world / peaks["hbm_gbs"]}
+        if e2e is not None:
+            line["e2e"] = e2e
+
+    # ---- the dominant kernel's roofline, and the other benchmark configurations (one GPU)
+    if world == 1:
+        t_op, t_k, fam, _ = kernel_times(torch, device, N, synth, stream, "Q4_K", 14336, 4096, 1, 32, max(args.steps, 10))
+        wbytes = synth.weight_bytes("Q4_K", 14336, 4096)
+        algo = wbytes + 4096 + (4096 // 32) * 8 + 14336 * 4
+        achieved = algo / t_k / 1e9
+        line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                            "traffic": CONFIG2_M1_DRAM_BYTES if fam == 1 else None, "peak_source": peaks["source"],
+                            "kernel_us": t_k * 1e6, "algorithmic_bytes_per_launch": algo, "frac_of_nominal_8000": achieved / 8000.0,
+                            "operator_us": t_op * 1e6, "kernel_family": KERNEL_NAMES.get(fam),
+                            "what": "configs[1] at M=1: the mat-vec kernel on shared, already quantized activations, 32 rotating "
+                                    "weight matrices (1057 MB > L2), launches free to overlap; operator_us is one whole MatMul "
+                                    "(quantize + kernel), each launch waiting for its predecessor"}
+        if not args.no_configs:
+            configs = config_legs(args, torch, device, N, synth, stream, peaks)
+            configs["config3_prefill"] = prefill_leg(args, device, torch, N, synth, stream, peaks, with_cpu=not args.no_cpu)
+            configs["config4_decode_step_8b"] = decode_step_leg(args, torch, dist, device, N, synth, stream, peaks)
+            line["configs"] = configs
+        if not args.no_cpu:
+            base, _ = cpu_stack_baseline(rows, 12.0)
             line["cpu_baseline"] = base
-        if prefill is not None:
-            line["prefill"] = prefill
-        if tp_stack is not None:
-            line["tp_stack"] = tp_stack
-        if decode_step is not None:
-            line["decode_step_8b"] = decode_step
+    elif rank == 0:
+        per_gpu = value / world
+        line["roofline"] = {"bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": per_gpu / peaks["hbm_gbs"],
+                            "traffic": None, "peak_source": peaks["source"],
+                            "what": "per-GPU weight bytes of one step / step time (all launches and sums of the step, not one "
+                                    "kernel): how much of the step is streaming and how much the latency of its chain of dependent launches"}
+    if rank == 0:
         print(json.dumps(line), flush=True)
-    if segment is not None:
-        segment.dispose()
-    for op in ops:
-        op.dispose()
-    for w in weights:
-        w.dispose()
-    act.dispose()
     device.dispose()
     if world > 1:
         dist.destroy_process_group()
 
 
 def main():
-    global COPIES
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--rows", type=int, default=1)
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--copies", type=int, default=COPIES, help="weight matrices per step (profiling runs use fewer)")
+    ap.add_argument("--rows", type=int, default=1, help="decode batch of the headline step")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
-    ap.add_argument("--layers", type=int, default=0, help="layers of the tensor-parallel stack (default: the architecture's 80)")
-    ap.add_argument("--no-tp-stack", action="store_true", help="N=1: skip the 70B-shaped stack at tensor-parallel degree 1 and the 8B decode step")
+    ap.add_argument("--no-configs", action="store_true", help="N=1: skip the legs of configurations 1-4 (profiling runs)")
+    ap.add_argument("--layers", type=int, default=0, help="layers of the stack (default: the architecture's 80)")
     ap.add_argument("--tp-main-only", action="store_true", help="time the stack at --rows only, not at 1, 8, 64 and 2048 rows")
-    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM leg")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of a CUDA graph")
     args = ap.parse_args()
-    COPIES = args.copies
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -17,8 +17,8 @@
 // still streams through all 148 SMs; a tile whose K range is shared by several CTAs is summed by the last of them to
 // arrive, in CTA order (deterministic), through a scratch area that belongs to the activation object.
 //
-// Roles (24 warps): warp 0 issues the MMAs; warps 1-3 are bulk-copy (TMA engine) loaders for weight records, activation
-// scale tables and activation code tiles; warps 4-7 expand weight codes to f16 operand tiles (128-byte swizzled rows)
+// Roles (24 warps): warps 0 and 2 issue the MMAs (every other stage each); warps 1 and 3 are bulk-copy (TMA engine)
+// loaders for weight records and for activation scale tables and code tiles; warps 4-7 expand weight codes to f16 operand tiles (128-byte swizzled rows)
 // and decode scales; warps 8-23 read tensor memory, scale and accumulate. Every wait is bounded and raises the
 // device status word when it runs out.
 #include "internal.cuh"
@@ -52,8 +52,11 @@ struct UmCfg
     static constexpr int TM_COLS = TM_NEED <= 32 ? 32 : TM_NEED <= 64 ? 64 : TM_NEED <= 128 ? 128 : TM_NEED <= 256 ? 256 : 512;
     static constexpr int REC = record_bytes(FMT);
     static constexpr int RAW_SLOT = 8 * REC;
-    static constexpr int S = 3;                                   // operand stages (64 K-values each)
-    static constexpr int RS = (NT == 128 || FMT == FMT_Q8_0) ? 3 : 4;   // weight-record ring (units)
+    static constexpr int S = 3;                                   // weight-operand stages (64 K-values each)
+    // activation-operand stages: these tiles come from L2 by bulk copy, and enough of them must be in flight to cover
+    // that latency at the rate the tensor core consumes them
+    static constexpr int SB = NT == 128 ? 5 : NT == 64 ? 6 : 8;
+    static constexpr int RS = FMT == FMT_Q8_0 ? 2 : NT >= 32 ? 3 : 4;   // weight-record ring (units)
     static constexpr int B_STAGE = NT * 128;
     static constexpr int DX_BYTES = 8 * NT * 4;
     static constexpr int SX2_BYTES = MINS ? NT * 64 : 0;
@@ -65,7 +68,7 @@ struct UmCfg
     // offsets inside the 1024-byte aligned dynamic shared memory
     static constexpr int OFF_A = 0;
     static constexpr int OFF_B = OFF_A + S * UM_A_STAGE;
-    static constexpr int OFF_WS = OFF_B + S * B_STAGE;            // multiples of 1024 so far
+    static constexpr int OFF_WS = OFF_B + SB * B_STAGE;           // multiples of 1024 so far
     static constexpr int OFF_ACT = OFF_WS + 2 * WS_SLOT;
     static constexpr int OFF_RAW = OFF_ACT + 2 * ACT_SLOT;
     static constexpr int OFF_COMB = OFF_RAW + RS * RAW_SLOT;
@@ -79,7 +82,7 @@ struct UmBars
     uint64_t rw_full[4], rw_empty[4];
     uint64_t ua_full[2], ua_empty[2];
     uint64_t ws_full[2], ws_empty[2];
-    uint64_t a_full[3], b_full[3], ab_empty[3];
+    uint64_t a_full[3], a_empty[3], b_full[8], b_empty[8];
     uint64_t d_full[4], d_empty[4];
     uint64_t m_full[2], m_empty[2];
     uint64_t comb_full, comb_free;       // block turns of a tile meeting in shared memory
@@ -121,25 +124,21 @@ __device__ __forceinline__ void um_bulk(void *dst, const void *src, unsigned byt
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-// Bounded wait; gives up early when another role has already raised the abort flag. The probe carries no suspend-time
-// hint: a waiter is woken as soon as the phase completes (with a long hint the wake-up was measured to cost about a
-// microsecond per hand-over). The bound is wall-clock: about two seconds.
-__device__ __forceinline__ bool um_wait(uint64_t *bar, unsigned parity, volatile int *abort_flag)
+// Bounded wait (about two seconds); gives up early when another role has already raised the abort flag. Between probes
+// the warp naps for nap_ns, so that the roles that mostly wait (loaders, MMA issuer, producers) leave the issue slots
+// to the warps that have work: a tight probing loop of eight waiting warps was measured to execute more instructions
+// than the arithmetic of the kernel.
+__device__ __forceinline__ bool um_wait(uint64_t *bar, unsigned parity, volatile int *abort_flag, unsigned nap_ns = 100)
 {
     const unsigned b = smem_u32(bar);
-    unsigned long long t0 = 0;
-    for (unsigned i = 0;; i++) {
+#pragma unroll 1
+    for (unsigned i = 0; i < 20000000u; i++) {
         unsigned ok;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(ok) : "r"(b), "r"(parity) : "memory");
         if (ok) return true;
-        if ((i & 255u) == 255u) {
-            if (*abort_flag) return false;
-            unsigned long long now;
-            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > 2000000000ull) break;
-        }
+        __nanosleep(nap_ns);
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
     }
     *abort_flag = 1;
     return false;
@@ -181,9 +180,29 @@ __device__ __forceinline__ void um_ld16(unsigned taddr, unsigned (&r)[16])
                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
                    "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr) : "memory");
+                 : "r"(taddr));
 }
-__device__ __forceinline__ void um_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The same with the results typed as floats from the start (the values are used as floats: no re-typing moves).
+__device__ __forceinline__ void um_ld16f(unsigned taddr, float (&r)[16])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]),
+                   "=f"(r[8]), "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15])
+                 : "r"(taddr));
+}
+// The same 16 columns as eight packed pairs (column 2j in the low half): the form the packed f32x2 arithmetic consumes.
+__device__ __forceinline__ void um_ld16p(unsigned taddr, ull (&p)[8])
+{
+    asm volatile("{\n\t.reg .b32 t<16>;\n\t"
+                 "tcgen05.ld.sync.aligned.32x32b.x16.b32 {t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15}, [%8];\n\t"
+                 "mov.b64 %0, {t0, t1};\n\tmov.b64 %1, {t2, t3};\n\tmov.b64 %2, {t4, t5};\n\tmov.b64 %3, {t6, t7};\n\t"
+                 "mov.b64 %4, {t8, t9};\n\tmov.b64 %5, {t10, t11};\n\tmov.b64 %6, {t12, t13};\n\tmov.b64 %7, {t14, t15};\n\t}"
+                 : "=l"(p[0]), "=l"(p[1]), "=l"(p[2]), "=l"(p[3]), "=l"(p[4]), "=l"(p[5]), "=l"(p[6]), "=l"(p[7])
+                 : "r"(taddr));
+}
+// (no memory clobber on these: they touch tensor memory only, and ordinary shared-memory loads may be scheduled across them)
+__device__ __forceinline__ void um_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;"); }
 __device__ __forceinline__ void um_st16(unsigned taddr, const ull (&a)[8])
 {
     asm volatile("{\n\t.reg .b32 r<16>;\n\t"
@@ -191,6 +210,12 @@ __device__ __forceinline__ void um_st16(unsigned taddr, const ull (&a)[8])
                  "mov.b64 {r8, r9}, %5;\n\tmov.b64 {r10, r11}, %6;\n\tmov.b64 {r12, r13}, %7;\n\tmov.b64 {r14, r15}, %8;\n\t"
                  "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {r0, r1, r2, r3, r4, r5, r6, r7, r8, r9, r10, r11, r12, r13, r14, r15};\n\t}"
                  ::"r"(taddr), "l"(a[0]), "l"(a[1]), "l"(a[2]), "l"(a[3]), "l"(a[4]), "l"(a[5]), "l"(a[6]), "l"(a[7]) : "memory");
+}
+__device__ __forceinline__ void um_st16f(unsigned taddr, const float (&a)[16])
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 ::"r"(taddr), "f"(a[0]), "f"(a[1]), "f"(a[2]), "f"(a[3]), "f"(a[4]), "f"(a[5]), "f"(a[6]), "f"(a[7]),
+                   "f"(a[8]), "f"(a[9]), "f"(a[10]), "f"(a[11]), "f"(a[12]), "f"(a[13]), "f"(a[14]), "f"(a[15]) : "memory");
 }
 __device__ __forceinline__ void um_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -271,18 +296,19 @@ struct UmWork
 
 // ---- producers: one row group (16 rows) of one 64-value stage -> f16 operand rows ------------------------------------------
 
-// Q4_K header of a row -> the two f16x2 constants of stage c: (sc, sc) and (-1024 sc, -1024 sc) for sub-blocks 2c, 2c+1.
+// Q4_K: the 6-bit scales of a row's eight sub-blocks as two words of four bytes (sub-blocks 0-3, 4-7), decoded once per
+// unit (src/Sharplight.Cpu/Quant.cs:504-516 of the Sharplight tree); the export build multiplies by one instead.
 template <bool DUMP>
-__device__ __forceinline__ void um_q4k_scales(const uint4 &h, int c, unsigned (&sc2)[2], unsigned (&off2)[2])
+__device__ __forceinline__ void um_q4k_scale_bytes(const uint4 &h, unsigned &lo, unsigned &hi)
 {
-    if (DUMP) {
-        sc2[0] = sc2[1] = 0x3C003C00u;     // (1, 1): the export wants the unscaled block dot
-        off2[0] = off2[1] = 0xE400E400u;   // (-1024, -1024)
-        return;
-    }
-    // 6-bit scales of sub-blocks 0-3 / 4-7 (src/Sharplight.Cpu/Quant.cs:504-516 of the Sharplight tree)
-    const unsigned scw = c < 2 ? (h.y & 0x3F3F3F3Fu) : ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u));
-    const unsigned pair = (scw >> (16 * (c & 1))) & 0xffffu;                      // bytes: sc of 2c, sc of 2c+1
+    lo = DUMP ? 0x01010101u : (h.y & 0x3F3F3F3Fu);
+    hi = DUMP ? 0x01010101u : ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u));
+}
+
+// The two f16x2 constants of stage c from the packed scale bytes: (sc, sc) and (-1024 sc, -1024 sc) for sub-blocks 2c, 2c+1.
+__device__ __forceinline__ void um_q4k_stage_scales(unsigned lo, unsigned hi, int c, unsigned (&sc2)[2], unsigned (&off2)[2])
+{
+    const unsigned pair = ((c < 2 ? lo : hi) >> (16 * (c & 1)));                  // low two bytes: sc of 2c, sc of 2c+1
     const unsigned h1024 = um_prmt(pair, 0x64646464u, 0x5140u);                   // (1024 + sc_a, 1024 + sc_b)
     const unsigned sc = um_hadd2(h1024, 0xE400E400u);                             // (sc_a, sc_b), exact
     sc2[0] = um_prmt(sc, sc, 0x1010u);
@@ -291,22 +317,28 @@ __device__ __forceinline__ void um_q4k_scales(const uint4 &h, int c, unsigned (&
     off2[1] = um_hmul2(sc2[1], 0xE400E400u);
 }
 
-template <int FMT, bool DUMP>
-__device__ __forceinline__ void um_expand(const uint8_t *rec, int c, int rgl, int lane, uint8_t *a_stage)
+// What a producer lane keeps of a row group for the four stages of a unit.
+template <int FMT>
+struct UmRowGroup
 {
-    const int g = lane >> 2, t = lane & 3;
-    const int r_lo = rgl * 16 + g, r_hi = r_lo + 8;
+    unsigned sc_lo[2], sc_hi[2];   // Q4_K: packed sub-block scales of rows g and g + 8
+};
+
+// One 64-value stage of one row group. a_rg: the stage's operand rows of this row group (a_stage + rgl * 2048); soff: this
+// lane's byte offset of row g, chunk t (or t / 2 for Q4_0) inside it, swizzle included. A chunk further along K differs
+// only in bits 4-6 of the offset, so its address is soff ^ (chunk bits << 4); row g + 8 lies 1024 bytes on.
+template <int FMT>
+__device__ __forceinline__ void um_expand(const uint8_t *rec, int c, int lane, uint8_t *a_rg, unsigned soff, const UmRowGroup<FMT> &rg)
+{
     if constexpr (FMT == FMT_Q4_K) {
         // tile c of the record: lane (g, t) holds qs[32c + 8t .. +7] of rows g (x, y) and g + 8 (z, w); low nibbles are
         // values 8t.. of sub-block 2c (chunk t of the stage), high nibbles the same of sub-block 2c + 1 (chunk 4 + t)
         const uint4 q = reinterpret_cast<const uint4 *>(rec + c * 512)[lane];
-        const uint4 *hdr = reinterpret_cast<const uint4 *>(rec + code_bytes(FMT));
 #pragma unroll
         for (int r = 0; r < 2; r++) {
             unsigned sc2[2], off2[2];
-            um_q4k_scales<DUMP>(hdr[g + 8 * r], c, sc2, off2);
+            um_q4k_stage_scales(rg.sc_lo[r], rg.sc_hi[r], c, sc2, off2);
             const unsigned w0 = r ? q.z : q.x, w1 = r ? q.w : q.y;
-            const int row = r ? r_hi : r_lo;
 #pragma unroll
             for (int nib = 0; nib < 2; nib++) {
                 const unsigned b0 = (nib ? (w0 >> 4) : w0) & 0x0F0F0F0Fu, b1 = (nib ? (w1 >> 4) : w1) & 0x0F0F0F0Fu;
@@ -318,17 +350,17 @@ __device__ __forceinline__ void um_expand(const uint8_t *rec, int c, int rgl, in
                 um_bytes_to_h1024(b1, h01, h23);
                 o.z = um_hfma2(h01, sc2[nib], off2[nib]);
                 o.w = um_hfma2(h23, sc2[nib], off2[nib]);
-                *reinterpret_cast<uint4 *>(a_stage + um_sw128(row, 4 * nib + t)) = o;
+                *reinterpret_cast<uint4 *>(a_rg + r * 1024 + (soff ^ (unsigned)(nib << 6))) = o;
             }
         }
     } else if constexpr (FMT == FMT_Q4_0) {
         // tile c: words w0 = row g block 2c, w1 = row g+8 block 2c, w2 = row g block 2c+1, w3 = row g+8 block 2c+1, each
-        // qs[4t .. 4t+3]: low nibbles are values 4t.. of the block, high nibbles values 16 + 4t..; operand value = code - 8
+        // qs[4t .. 4t+3]: low nibbles are values 4t.. of the block, high nibbles values 16 + 4t..; operand value = code - 8.
+        // K offset inside the stage: 32 blk + 16 nib + 4t -> chunk 4 blk + 2 nib + t / 2, half t & 1 (in soff)
         const uint4 q = reinterpret_cast<const uint4 *>(rec + c * 512)[lane];
         const unsigned wv[4] = { q.x, q.y, q.z, q.w };
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            const int row = (j & 1) ? r_hi : r_lo, blk = j >> 1;
 #pragma unroll
             for (int nib = 0; nib < 2; nib++) {
                 const unsigned b = (nib ? (wv[j] >> 4) : wv[j]) & 0x0F0F0F0Fu;
@@ -337,8 +369,7 @@ __device__ __forceinline__ void um_expand(const uint8_t *rec, int c, int rgl, in
                 uint2 o;
                 o.x = um_hadd2(h01, 0xE408E408u);   // (1024 + v) - 1032 = v - 8
                 o.y = um_hadd2(h23, 0xE408E408u);
-                // K offset inside the stage: 32 * blk + 16 * nib + 4t -> chunk 4 blk + 2 nib + t / 2, half t & 1
-                *reinterpret_cast<uint2 *>(a_stage + um_sw128(row, 4 * blk + 2 * nib + (t >> 1)) + 8 * (t & 1)) = o;
+                *reinterpret_cast<uint2 *>(a_rg + (j & 1) * 1024 + (soff ^ (unsigned)((4 * (j >> 1) + 2 * nib) << 4))) = o;
             }
         }
     } else {  // Q8_0: tiles 2c and 2c + 1 (one block each); lane: q[8t .. 8t+7] of rows g (x, y) and g + 8 (z, w)
@@ -356,7 +387,7 @@ __device__ __forceinline__ void um_expand(const uint8_t *rec, int c, int rgl, in
                 um_bytes_to_h1024(w1, h01, h23);
                 o.z = um_hadd2(h01, 0xE480E480u);
                 o.w = um_hadd2(h23, 0xE480E480u);
-                *reinterpret_cast<uint4 *>(a_stage + um_sw128(r ? r_hi : r_lo, 4 * blk + t)) = o;
+                *reinterpret_cast<uint4 *>(a_rg + r * 1024 + (soff ^ (unsigned)(blk << 6))) = o;
             }
         }
     }
@@ -399,7 +430,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
 {
     using Cfg = UmCfg<FMT, NT>;
     constexpr bool MINS = Cfg::MINS;
-    constexpr int CS = Cfg::CS, BP = Cfg::BP, CW = Cfg::CW, DB = Cfg::DB, S = Cfg::S, RS = Cfg::RS;
+    constexpr int CS = Cfg::CS, BP = Cfg::BP, CW = Cfg::CW, DB = Cfg::DB, S = Cfg::S, SB = Cfg::SB, RS = Cfg::RS;
     extern __shared__ __align__(1024) unsigned char um_smem_raw[];
     __shared__ UmBars sh;
     unsigned char *smem = um_smem_raw + ((1024 - (smem_u32(um_smem_raw) & 1023)) & 1023);
@@ -413,7 +444,9 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
             mbar_init(&sh.ws_full[i], 4); mbar_init(&sh.ws_empty[i], 16);
             mbar_init(&sh.m_full[i], 1); mbar_init(&sh.m_empty[i], 4 * CS);
         }
-        for (int i = 0; i < S; i++) { mbar_init(&sh.a_full[i], 4); mbar_init(&sh.b_full[i], 1); mbar_init(&sh.ab_empty[i], 1); }
+        // (with two block-dot buffers both MMA issuers read every stage and both release it)
+        for (int i = 0; i < S; i++) { mbar_init(&sh.a_full[i], 4); mbar_init(&sh.a_empty[i], DB == 2 ? 2 : 1); }
+        for (int i = 0; i < SB; i++) { mbar_init(&sh.b_full[i], 1); mbar_init(&sh.b_empty[i], DB == 2 ? 2 : 1); }
         for (int i = 0; i < DB; i++) { mbar_init(&sh.d_full[i], 1); mbar_init(&sh.d_empty[i], 4 * CS); }
         mbar_init(&sh.comb_full, BP > 1 ? 16 - 4 * CS : 1);
         mbar_init(&sh.comb_free, 4 * CS);
@@ -450,7 +483,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
             int slot = 0;
             unsigned phase = 1;   // parity to wait on for "slot is free" (passes at once on a fresh barrier)
             for (; !wk.done(); wk.next()) {
-                if (!um_wait(&sh.rw_empty[slot], phase, abort_flag)) break;
+                if (!um_wait(&sh.rw_empty[slot], phase, abort_flag, 1000)) break;
                 const int row_tile = wk.tile / p.tok_tiles;
                 const int rg0 = row_tile * 8;
                 const int live = rg_count - rg0 < 8 ? rg_count - rg0 : 8;
@@ -463,47 +496,59 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
     } else {
         pdl_enter(0);   // everything else touches activations or writes results: wait for the preceding kernel
         wk.init(p);
-        if (warp == 0) {
-            // ===== MMA issuer (one thread; it needs only the number of units, not which tiles they belong to)
+        if (warp == 0 || warp == 2) {
+            // ===== MMA issuers: two threads (warps 0 and 2). Issuing a tcgen05 instruction, committing and probing a barrier
+            // each cost the issuing thread some tens of cycles, a dozen such steps per stage; one thread alone was the
+            // slowest stage of the pipeline. Every block-dot buffer must have ONE issuer: a parity wait tells "free again"
+            // from "not yet used" only for a thread that is at most one use ahead of the barrier. With four buffers the
+            // threads take every other 64-value stage (even stages use buffers 0-1, odd ones 2-3); with two buffers both
+            // threads visit every stage and each issues the block of its own buffer. The issuers need only the number of
+            // units, not which tiles they belong to.
             if (lane == 0) {
                 constexpr unsigned idesc = um_idesc_f16(NT), idesc_m = um_idesc_tf32(NT);
                 const unsigned a_lo0 = (smem_u32(smem + Cfg::OFF_A) >> 4) & 0x3FFFu, b_lo0 = (smem_u32(smem + Cfg::OFF_B) >> 4) & 0x3FFFu;
                 const unsigned desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);          // bits 32..63: sbo 1024, version, 128-byte swizzle
                 const unsigned desc_hi_m = (512u >> 4) | (1u << 14) | (4u << 29);         // sbo 512, version, 64-byte swizzle
                 auto mk = [](unsigned lo14, unsigned hi) { return (uint64_t)(lo14 | (1u << 16)) | ((uint64_t)hi << 32); };
-                const int n_units = (int)(wk.u_end - wk.u);
-                int stage = 0;
-                unsigned ab_phase = 0;
+                const int n_stages = (int)(wk.u_end - wk.u) * 4;
+                const int me = warp >> 1;                         // 0 or 1
+                constexpr bool BY_BLOCK = DB == 2;
+                constexpr int STEP = BY_BLOCK ? 1 : 2;
+                // ring positions of this issuer's first stage, advanced by STEP stages per iteration
+                int stage = BY_BLOCK ? 0 : me % S, stage_b = BY_BLOCK ? 0 : me % SB;
+                unsigned a_phase = 0, b_phase = 0;
                 bool ok = true;
 #pragma unroll 1
-                for (int unit = 0; unit < n_units && ok; unit++) {
-                    const int us = unit & 1;
-                    const unsigned uphase = (unsigned)(unit >> 1) & 1u;
-#pragma unroll 1
-                    for (int c = 0; c < 4 && ok; c++) {
-                        if (!um_wait(&sh.a_full[stage], ab_phase, abort_flag) || !um_wait(&sh.b_full[stage], ab_phase, abort_flag)) { ok = false; break; }
-                        um_tc_after();
-                        const unsigned a_lo = a_lo0 + (unsigned)(stage * (UM_A_STAGE >> 4)), b_lo = b_lo0 + (unsigned)(stage * (Cfg::B_STAGE >> 4));
+                for (int k = BY_BLOCK ? 0 : me; k < n_stages && ok; k += STEP) {
+                    const int unit = k >> 2, c = k & 3;
+                    if (!um_wait(&sh.a_full[stage], a_phase, abort_flag, 100) || !um_wait(&sh.b_full[stage_b], b_phase, abort_flag, 100)) { ok = false; break; }
+                    um_tc_after();
+                    const unsigned a_lo = a_lo0 + (unsigned)(stage * (UM_A_STAGE >> 4)), b_lo = b_lo0 + (unsigned)(stage_b * (Cfg::B_STAGE >> 4));
 #pragma unroll
-                        for (int bb = 0; bb < 2; bb++) {
-                            const int b = 2 * c + bb, buf = b % DB;
-                            const unsigned dphase = ((unsigned)((unit * 8 + b) / DB) & 1u) ^ 1u;
-                            if (!um_wait(&sh.d_empty[buf], dphase, abort_flag)) { ok = false; break; }
-                            um_tc_after();
-                            const unsigned d = tmem + (unsigned)(buf * NT);
-                            // K values 32 bb .. +15, then +16 .. +31: 32 bytes = 2 sixteen-byte units further along the swizzled row
-                            um_mma_f16(d, mk(a_lo + 4 * bb, desc_hi), mk(b_lo + 4 * bb, desc_hi), idesc, 0);
-                            um_mma_f16(d, mk(a_lo + 4 * bb + 2, desc_hi), mk(b_lo + 4 * bb + 2, desc_hi), idesc, 1);
-                            um_commit(&sh.d_full[buf]);
-                        }
-                        if (ok) um_commit(&sh.ab_empty[stage]);
-                        if (++stage == S) { stage = 0; ab_phase ^= 1u; }
+                    for (int bb = 0; bb < 2; bb++) {
+                        if (BY_BLOCK && bb != me) continue;
+                        const int b = 2 * c + bb, buf = b % DB;
+                        const unsigned dphase = ((unsigned)((unit * 8 + b) / DB) & 1u) ^ 1u;
+                        if (!um_wait(&sh.d_empty[buf], dphase, abort_flag, 100)) { ok = false; break; }
+                        um_tc_after();
+                        const unsigned d = tmem + (unsigned)(buf * NT);
+                        // K values 32 bb .. +15, then +16 .. +31: 32 bytes = 2 sixteen-byte units further along the swizzled row
+                        um_mma_f16(d, mk(a_lo + 4 * bb, desc_hi), mk(b_lo + 4 * bb, desc_hi), idesc, 0);
+                        um_mma_f16(d, mk(a_lo + 4 * bb + 2, desc_hi), mk(b_lo + 4 * bb + 2, desc_hi), idesc, 1);
+                        um_commit(&sh.d_full[buf]);
                     }
-                    if (MINS && ok) {
-                        // offset term of the unit: D2[n][t] = sum_b m[n,b] * (sx_hi + sx_lo)[t,b], two K = 8 steps
-                        const int mb = unit % Cfg::MB;
-                        if (!um_wait(&sh.ws_full[us], uphase, abort_flag) || !um_wait(&sh.ua_full[us], uphase, abort_flag) ||
-                            !um_wait(&sh.m_empty[mb], ((unsigned)(unit / Cfg::MB) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                    if (!ok) break;
+                    um_commit(&sh.a_empty[stage]);
+                    um_commit(&sh.b_empty[stage_b]);
+                    stage += STEP; if (stage >= S) { stage -= S; a_phase ^= 1u; }
+                    stage_b += STEP; if (stage_b >= SB) { stage_b -= SB; b_phase ^= 1u; }
+                    if (MINS && c == 3 && me == 1) {
+                        // offset term of the unit (issued by the thread that has the unit's last stage):
+                        // D2[n][t] = sum_b m[n,b] * (sx_hi + sx_lo)[t,b], two K = 8 steps
+                        const int us = unit & 1, mb = unit % Cfg::MB;
+                        const unsigned uphase = (unsigned)(unit >> 1) & 1u;
+                        if (!um_wait(&sh.ws_full[us], uphase, abort_flag, 100) || !um_wait(&sh.ua_full[us], uphase, abort_flag, 100) ||
+                            !um_wait(&sh.m_empty[mb], ((unsigned)(unit / Cfg::MB) & 1u) ^ 1u, abort_flag, 100)) { ok = false; break; }
                         um_tc_after();
                         const unsigned a2 = (smem_u32(smem + Cfg::OFF_WS + us * Cfg::WS_SLOT + Cfg::WS_TAB) >> 4) & 0x3FFFu;
                         const unsigned b2 = (smem_u32(smem + Cfg::OFF_ACT + us * Cfg::ACT_SLOT + Cfg::DX_BYTES) >> 4) & 0x3FFFu;
@@ -516,36 +561,29 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
                 if (!ok) atomicExch(p.status, -7);
             }
             __syncwarp();
-        } else if (warp == 2) {
-            // ===== activation scale tables of a unit: d_x per block and token, and (Q4_K) the split d_x * sum q tile
+        } else if (warp == 3) {
+            // ===== activation-side loader: per unit the scale tables (d_x per block and token, and for Q4_K the split
+            // d_x * sum q tile), then one bulk copy of the code tile per 64-value stage
             if (lane == 0) {
-                int unit = 0;
-                for (; !wk.done(); wk.next(), unit++) {
+                int stage = 0, unit = 0;
+                unsigned phase = 1;
+                bool ok = true;
+                for (; !wk.done() && ok; wk.next(), unit++) {
                     const int us = unit & 1;
-                    if (!um_wait(&sh.ua_empty[us], ((unsigned)(unit >> 1) & 1u) ^ 1u, abort_flag)) break;
                     const int t0 = (wk.tile % p.tok_tiles) * NT;
+                    if (!um_wait(&sh.ua_empty[us], ((unsigned)(unit >> 1) & 1u) ^ 1u, abort_flag, 500)) break;
                     unsigned char *dst = smem + Cfg::OFF_ACT + us * Cfg::ACT_SLOT;
                     um_expect_tx(&sh.ua_full[us], (unsigned)(Cfg::DX_BYTES + Cfg::SX2_BYTES));
                     for (int b = 0; b < 8; b++) {
                         um_bulk(dst + b * NT * 4, p.a.dx + (long long)(wk.st * 8 + b) * p.a.rows_pad + t0, NT * 4, &sh.ua_full[us]);
                     }
                     if (MINS) um_bulk(dst + Cfg::DX_BYTES, p.sx2 + ((long long)wk.st * tok_groups + (t0 >> 3)) * 512, Cfg::SX2_BYTES, &sh.ua_full[us]);
-                }
-            }
-        } else if (warp == 3) {
-            // ===== activation code tiles: one bulk copy per 64-value stage
-            if (lane == 0) {
-                int stage = 0;
-                unsigned phase = 1;
-                bool ok = true;
-                for (; !wk.done() && ok; wk.next()) {
-                    const int t0 = (wk.tile % p.tok_tiles) * NT;
                     for (int c = 0; c < 4; c++) {
-                        if (!um_wait(&sh.ab_empty[stage], phase, abort_flag)) { ok = false; break; }
+                        if (!um_wait(&sh.b_empty[stage], phase, abort_flag, 500)) { ok = false; break; }
                         um_expect_tx(&sh.b_full[stage], (unsigned)Cfg::B_STAGE);
                         um_bulk(smem + Cfg::OFF_B + stage * Cfg::B_STAGE,
                                 p.h_tiled + ((long long)(wk.st * 4 + c) * tok_groups + (t0 >> 3)) * 1024, Cfg::B_STAGE, &sh.b_full[stage]);
-                        if (++stage == S) { stage = 0; phase ^= 1u; }
+                        if (++stage == SB) { stage = 0; phase ^= 1u; }
                     }
                 }
             }
@@ -553,28 +591,42 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
             // ===== producers: weight codes -> f16 operand rows, scale tables
             asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(UM_REG_PROD));
             const int pw = warp - 4;
+            const int pg = lane >> 2, pt = lane & 3;
+            // this lane's byte offset of (row g, its first chunk) inside a row group's operand rows, swizzle included
+            const unsigned soff = FMT == FMT_Q4_0 ? (unsigned)(pg * 128 + ((((pt >> 1) ^ pg) & 7) << 4) + 8 * (pt & 1))
+                                                  : (unsigned)(pg * 128 + (((pt ^ pg) & 7) << 4));
             int slot = 0, stage = 0, unit = 0;
             unsigned rphase = 0, ab_phase = 1;
             bool ok = true;
             for (; !wk.done() && ok; wk.next(), unit++) {
                 const int us = unit & 1;
-                if (!um_wait(&sh.rw_full[slot], rphase, abort_flag) ||
-                    !um_wait(&sh.ws_empty[us], ((unsigned)(unit >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                if (!um_wait(&sh.rw_full[slot], rphase, abort_flag, 300) ||
+                    !um_wait(&sh.ws_empty[us], ((unsigned)(unit >> 1) & 1u) ^ 1u, abort_flag, 300)) { ok = false; break; }
                 const uint8_t *raw = smem + Cfg::OFF_RAW + slot * Cfg::RAW_SLOT;
                 const int rg0 = (wk.tile / p.tok_tiles) * 8;
                 const bool live0 = rg0 + 2 * pw < rg_count, live1 = rg0 + 2 * pw + 1 < rg_count;
+                const uint8_t *rec0 = raw + (2 * pw) * Cfg::REC, *rec1 = rec0 + Cfg::REC;
                 uint8_t *ws_slot = smem + Cfg::OFF_WS + us * Cfg::WS_SLOT;
-                if (live0) um_tables<FMT>(raw + (2 * pw) * Cfg::REC, 2 * pw, lane, ws_slot);
-                if (live1) um_tables<FMT>(raw + (2 * pw + 1) * Cfg::REC, 2 * pw + 1, lane, ws_slot);
+                if (live0) um_tables<FMT>(rec0, 2 * pw, lane, ws_slot);
+                if (live1) um_tables<FMT>(rec1, 2 * pw + 1, lane, ws_slot);
                 um_fence_async();
                 __syncwarp();
                 if (lane == 0) um_arrive(&sh.ws_full[us]);
+                UmRowGroup<FMT> rga, rgb;
+                if constexpr (FMT == FMT_Q4_K) {
+                    const uint4 *h0 = reinterpret_cast<const uint4 *>(rec0 + code_bytes(FMT)), *h1 = reinterpret_cast<const uint4 *>(rec1 + code_bytes(FMT));
+#pragma unroll
+                    for (int r = 0; r < 2; r++) {
+                        um_q4k_scale_bytes<DUMP>(h0[pg + 8 * r], rga.sc_lo[r], rga.sc_hi[r]);
+                        um_q4k_scale_bytes<DUMP>(h1[pg + 8 * r], rgb.sc_lo[r], rgb.sc_hi[r]);
+                    }
+                }
 #pragma unroll 1
                 for (int c = 0; c < 4; c++) {
-                    if (!um_wait(&sh.ab_empty[stage], ab_phase, abort_flag)) { ok = false; break; }
-                    uint8_t *a_stage = smem + Cfg::OFF_A + stage * UM_A_STAGE;
-                    if (live0) um_expand<FMT, DUMP>(raw + (2 * pw) * Cfg::REC, c, 2 * pw, lane, a_stage);
-                    if (live1) um_expand<FMT, DUMP>(raw + (2 * pw + 1) * Cfg::REC, c, 2 * pw + 1, lane, a_stage);
+                    if (!um_wait(&sh.a_empty[stage], ab_phase, abort_flag, 300)) { ok = false; break; }
+                    uint8_t *a_stage = smem + Cfg::OFF_A + stage * UM_A_STAGE + (2 * pw) * 2048;
+                    if (live0) um_expand<FMT>(rec0, c, lane, a_stage, soff, rga);
+                    if (live1) um_expand<FMT>(rec1, c, lane, a_stage + 2048, soff, rgb);
                     um_fence_async();   // generic-proxy stores -> visible to the tensor core's reads
                     __syncwarp();
                     if (lane == 0) um_arrive(&sh.a_full[stage]);
@@ -611,23 +663,34 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
                 const int us = unit & 1;
                 const unsigned uphase = (unsigned)(unit >> 1) & 1u;
                 if (!um_wait(&sh.ua_full[us], uphase, abort_flag) || !um_wait(&sh.ws_full[us], uphase, abort_flag)) { ok = false; break; }
-                const unsigned dx_s = smem_s + (unsigned)(Cfg::OFF_ACT + us * Cfg::ACT_SLOT + c0 * 4);
                 const unsigned ws_s = smem_s + (unsigned)(Cfg::OFF_WS + us * Cfg::WS_SLOT);
+                // The unit's blocks of this warp as a stream of 16-column chunks, software-pipelined: the tensor-memory load
+                // of the next chunk is in flight while the current one is scaled and accumulated, and a block's buffer goes
+                // back to the MMA issuer as soon as its last chunk has arrived in registers. The loop over blocks is a real
+                // loop (the code of all roles has to stay resident in the instruction cache).
+                constexpr int HPB = CW / 16, NBLK = 8 / BP;
+                const ulonglong2 *dx_tab = reinterpret_cast<const ulonglong2 *>(smem + Cfg::OFF_ACT + us * Cfg::ACT_SLOT) + c0 / 4;
+                if constexpr (MINS) {
 #pragma unroll
-                for (int bi = 0; bi < 8 / BP; bi++) {
+                    for (int j = 0; j < CW / 2; j++) accsb[j] = 0ull;
+                }
+#pragma unroll 1
+                for (int bi = 0; bi < NBLK; bi++) {
                     const int b = bi * BP + bp, buf = b % DB;
-                    if (!um_wait(&sh.d_full[buf], (unsigned)((unit * 8 + b) / DB) & 1u, abort_flag)) { ok = false; break; }
+                    if (!um_wait(&sh.d_full[buf], (unsigned)((unit * 8 + b) / DB) & 1u, abort_flag, 20)) { ok = false; break; }
                     um_tc_after();
-                    ull dw2 = 0ull;
-                    if (!MINS) {
-                        const float dw = um_lds_f32(ws_s + (unsigned)((b * UM_ROWS + r) * 4));
-                        dw2 = um_pkf(dw, dw);
-                    }
+                    const float dw = MINS ? 0.0f : um_lds_f32(ws_s + (unsigned)((b * UM_ROWS + r) * 4));
 #pragma unroll
-                    for (int h = 0; h < CW / 16; h++) {
+                    for (int h = 0; h < HPB; h++) {
                         unsigned v[16];
                         um_ld16(tlane + (unsigned)(buf * NT + h * 16), v);
                         um_wait_ld();
+                        if (h == HPB - 1) {
+                            // every chunk of the block is in registers: the buffer goes back to the MMA issuer
+                            um_tc_before();
+                            __syncwarp();
+                            if (lane == 0) um_arrive(&sh.d_empty[buf]);
+                        }
                         if (DUMP) {
                             const int n0 = (wk.tile / p.tok_tiles) * UM_ROWS, t0 = (wk.tile % p.tok_tiles) * NT;
 #pragma unroll
@@ -642,23 +705,21 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
                         }
 #pragma unroll
                         for (int j4 = 0; j4 < 4; j4++) {
-                            ull dx01, dx23;
-                            um_lds_2x64(dx_s + (unsigned)((b * NT + h * 16 + j4 * 4) * 4), dx01, dx23);
-                            const ull v01 = um_pk(v[4 * j4], v[4 * j4 + 1]), v23 = um_pk(v[4 * j4 + 2], v[4 * j4 + 3]);
+                            const ulonglong2 dx = dx_tab[(b * NT + h * 16) / 4 + j4];
                             const int o = h * 8 + j4 * 2;
                             if constexpr (MINS) {
                                 // the MMA already applied the integer sub-block scale: one multiply-add with d_x
-                                if (bi == 0) { accsb[o] = um_mul2(v01, dx01); accsb[o + 1] = um_mul2(v23, dx23); }
-                                else { accsb[o] = um_fma2(v01, dx01, accsb[o]); accsb[o + 1] = um_fma2(v23, dx23, accsb[o + 1]); }
+                                accsb[o] = um_fma2(um_pk(v[4 * j4], v[4 * j4 + 1]), dx.x, accsb[o]);
+                                accsb[o + 1] = um_fma2(um_pk(v[4 * j4 + 2], v[4 * j4 + 3]), dx.y, accsb[o + 1]);
                             } else {
-                                acc[o] = um_fma2(um_mul2(v01, dw2), dx01, acc[o]);
-                                acc[o + 1] = um_fma2(um_mul2(v23, dw2), dx23, acc[o + 1]);
+                                // d_w first, as two scalar multiplies whose results form a pair, then the packed multiply-add
+                                const ull t01 = um_pkf(__uint_as_float(v[4 * j4]) * dw, __uint_as_float(v[4 * j4 + 1]) * dw);
+                                const ull t23 = um_pkf(__uint_as_float(v[4 * j4 + 2]) * dw, __uint_as_float(v[4 * j4 + 3]) * dw);
+                                acc[o] = um_fma2(t01, dx.x, acc[o]);
+                                acc[o + 1] = um_fma2(t23, dx.y, acc[o + 1]);
                             }
                         }
                     }
-                    um_tc_before();
-                    __syncwarp();
-                    if (lane == 0) um_arrive(&sh.d_empty[buf]);
                 }
                 if (!ok) break;
                 if constexpr (MINS) {
@@ -673,22 +734,21 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
                     um_tc_after();
 #pragma unroll
                     for (int h = 0; h < CW / 16; h++) {
-                        ull a[8];
-                        unsigned v[16];
+                        ull a[8], v[8];
                         if (seg_fresh) {
 #pragma unroll
                             for (int j = 0; j < 8; j++) a[j] = um_mul2(accsb[h * 8 + j], d2);
                         } else {
-                            um_ld16(tacc + (unsigned)(h * 16), v);
+                            um_ld16p(tacc + (unsigned)(h * 16), v);
                             um_wait_ld();
 #pragma unroll
-                            for (int j = 0; j < 8; j++) a[j] = um_fma2(accsb[h * 8 + j], d2, um_pk(v[2 * j], v[2 * j + 1]));
+                            for (int j = 0; j < 8; j++) a[j] = um_fma2(accsb[h * 8 + j], d2, v[j]);
                         }
                         if (bp == 0) {
-                            um_ld16(tlane + (unsigned)(Cfg::TM_MINS + mb * NT + h * 16), v);
+                            um_ld16p(tlane + (unsigned)(Cfg::TM_MINS + mb * NT + h * 16), v);
                             um_wait_ld();
 #pragma unroll
-                            for (int j = 0; j < 8; j++) a[j] = um_fma2(um_pk(v[2 * j], v[2 * j + 1]), nm2, a[j]);
+                            for (int j = 0; j < 8; j++) a[j] = um_fma2(v[j], nm2, a[j]);
                         }
                         um_st16(tacc + (unsigned)(h * 16), a);
                     }
@@ -711,27 +771,21 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
                 const bool whole = seg_st0 == 0 && tile_ends;
                 float *comb = reinterpret_cast<float *>(smem + Cfg::OFF_COMB);
                 // 16 columns of this thread's running sums
-                auto chunk = [&](int h, ull (&a)[8]) {
+                auto chunk = [&](int h, float (&a)[16]) {
                     if constexpr (MINS) {
-                        unsigned v[16];
-                        um_ld16(tacc + (unsigned)(h * 16), v);
+                        um_ld16f(tacc + (unsigned)(h * 16), a);
                         um_wait_ld();
-#pragma unroll
-                        for (int j = 0; j < 8; j++) a[j] = um_pk(v[2 * j], v[2 * j + 1]);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 8; j++) { a[j] = acc[h * 8 + j]; acc[h * 8 + j] = 0ull; }
+                        for (int j = 0; j < 8; j++) { um_unpk(acc[h * 8 + j], a[2 * j], a[2 * j + 1]); acc[h * 8 + j] = 0ull; }
                     }
                 };
-                auto store_y = [&](int h, const ull (&a)[8]) {
+                auto store_y = [&](int h, const float (&a)[16]) {
                     if (row < p.w.n) {
 #pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            float lo, hi;
-                            um_unpk(a[j], lo, hi);
-                            const int tok = t0 + c0 + h * 16 + 2 * j;
-                            if (tok < p.a.rows) p.y[(long long)tok * p.y_stride + row] = p.ep.apply(lo, tok, row);
-                            if (tok + 1 < p.a.rows) p.y[(long long)(tok + 1) * p.y_stride + row] = p.ep.apply(hi, tok + 1, row);
+                        for (int j = 0; j < 16; j++) {
+                            const int tok = t0 + c0 + h * 16 + j;
+                            if (tok < p.a.rows) p.y[(long long)tok * p.y_stride + row] = p.ep.apply(a[j], tok, row);
                         }
                     }
                 };
@@ -740,15 +794,10 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
                     if (!um_wait(&sh.comb_free, ((unsigned)n_comb & 1u) ^ 1u, abort_flag)) { ok = false; break; }
 #pragma unroll
                     for (int h = 0; h < CW / 16; h++) {
-                        ull a[8];
+                        float a[16];
                         chunk(h, a);
 #pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            float lo, hi;
-                            um_unpk(a[j], lo, hi);
-                            comb[((bp - 1) * NT + c0 + h * 16 + 2 * j) * UM_ROWS + r] = lo;
-                            comb[((bp - 1) * NT + c0 + h * 16 + 2 * j + 1) * UM_ROWS + r] = hi;
-                        }
+                        for (int j = 0; j < 16; j++) comb[((bp - 1) * NT + c0 + h * 16 + j) * UM_ROWS + r] = a[j];
                     }
                     __syncwarp();
                     if (lane == 0) um_arrive(&sh.comb_full);
@@ -761,28 +810,19 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
                     float *mine = p.scratch + ((long long)blockIdx.x * 2 + my_slot) * NT * UM_ROWS;
 #pragma unroll
                     for (int h = 0; h < CW / 16; h++) {
-                        ull a[8];
+                        float a[16];
                         chunk(h, a);
                         if (BP > 1) {
 #pragma unroll
                             for (int t = 1; t < BP; t++) {
 #pragma unroll
-                                for (int j = 0; j < 8; j++) {
-                                    const float lo = comb[((t - 1) * NT + c0 + h * 16 + 2 * j) * UM_ROWS + r];
-                                    const float hi = comb[((t - 1) * NT + c0 + h * 16 + 2 * j + 1) * UM_ROWS + r];
-                                    a[j] = um_add2(a[j], um_pkf(lo, hi));
-                                }
+                                for (int j = 0; j < 16; j++) a[j] += comb[((t - 1) * NT + c0 + h * 16 + j) * UM_ROWS + r];
                             }
                         }
                         if (whole) store_y(h, a);
                         else {
 #pragma unroll
-                            for (int j = 0; j < 8; j++) {
-                                float lo, hi;
-                                um_unpk(a[j], lo, hi);
-                                __stcg(&mine[(c0 + h * 16 + 2 * j) * UM_ROWS + r], lo);
-                                __stcg(&mine[(c0 + h * 16 + 2 * j + 1) * UM_ROWS + r], hi);
-                            }
+                            for (int j = 0; j < 16; j++) __stcg(&mine[(c0 + h * 16 + j) * UM_ROWS + r], a[j]);
                         }
                     }
                     if (BP > 1) {
@@ -814,17 +854,16 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
                             __threadfence();
 #pragma unroll 1
                             for (int h = 0; h < CW / 16; h++) {
-                                ull sum[8];
+                                float sum[16];
 #pragma unroll 1
                                 for (int c = c_first; c <= c_last; c++) {
                                     const long long cu0 = (long long)c * p.units / g;
                                     const int slot_c = (cu0 / p.nst == wk.tile) ? 0 : 1;
                                     const float *part = p.scratch + ((long long)c * 2 + slot_c) * NT * UM_ROWS;
 #pragma unroll
-                                    for (int j = 0; j < 8; j++) {
-                                        const ull v = um_pkf(__ldcg(&part[(c0 + h * 16 + 2 * j) * UM_ROWS + r]),
-                                                             __ldcg(&part[(c0 + h * 16 + 2 * j + 1) * UM_ROWS + r]));
-                                        sum[j] = c == c_first ? v : um_add2(sum[j], v);
+                                    for (int j = 0; j < 16; j++) {
+                                        const float v = __ldcg(&part[(c0 + h * 16 + j) * UM_ROWS + r]);
+                                        sum[j] = c == c_first ? v : sum[j] + v;
                                     }
                                 }
                                 store_y(h, sum);

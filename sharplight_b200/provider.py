@@ -108,7 +108,8 @@ class WeightInfo:
     """A static weight as the importer describes it: type name, shape [N, K], raw ggml blocks."""
     type: str
     shape: Sequence[int]
-    blocks: np.ndarray
+    blocks: Optional[np.ndarray]
+    resident: Optional["DeviceWeight"] = None   # already on the device (a weight shared between segments): not uploaded again
 
 
 @dataclass
@@ -120,6 +121,7 @@ class MatMulNode:
     y: str                     # output value name, f32 [T, N]
     x_dtype: str = "f32"
     f32_activations: bool = False   # StandardOps.cs:130-135: the node opts out of 8-bit activations
+    allreduce: bool = False         # tensor parallelism: the node is row-split, its output is summed over the ranks
 
 
 @dataclass
@@ -137,6 +139,7 @@ class CompileOptions:
     allow_reduced_precision: bool = False
     row_invariant_rows: int = 0
     capture_steps: bool = True              # replay Execute as a captured CUDA graph from the third call per row count
+    exchange: Optional["TpExchange"] = None  # tensor parallelism: the receive area through which allreduce nodes sum
 
 
 class CudaExecutionProvider:
@@ -535,9 +538,14 @@ class CudaSegment:
         row_inv = options.row_invariant_rows > 0
         # value name -> (columns, element bytes)
         self._shape: Dict[str, tuple] = {}
+        self._reduce = {node.name for node in segment.nodes if node.allreduce}
+        if self._reduce and options.exchange is None:
+            raise ArgumentError("a segment with allreduce nodes needs CompileOptions.exchange")
         for node in segment.nodes:
-            w = device.upload_weight(node.weight.type, node.weight.shape, node.weight.blocks)
-            self._weights.append(w)
+            w = node.weight.resident
+            if w is None:
+                w = device.upload_weight(node.weight.type, node.weight.shape, node.weight.blocks)
+                self._weights.append(w)
             self._ops[node.name] = MatMulOp(device, w, mr, row_invariant=row_inv)
             self._shape.setdefault(node.x, (w.k, 2 if node.x_dtype == "bf16" else 4))
             self._shape[node.y] = (w.n, 4)
@@ -688,7 +696,11 @@ class CudaSegment:
                 dtype = N.BF16 if node.x_dtype == "bf16" else N.F32
                 self._acts[node.x].quantize(self._dev[node.x].value, dtype, rows, self._shape[node.x][0], 0)
                 continue
-            self._acts[node.x].matmul(self._ops[node.name], self._dev[node.y].value, self._shape[node.y][0], 0)
+            if node.name in self._reduce:
+                self.options.exchange.matmul(self._ops[node.name], self._acts[node.x], self._dev[node.y].value,
+                                             self._shape[node.y][0], 0)
+            else:
+                self._acts[node.x].matmul(self._ops[node.name], self._dev[node.y].value, self._shape[node.y][0], 0)
             if node.y in outputs and node.y not in self._device_only:
                 nbytes = rows * self._shape[node.y][0] * 4
                 dst = C.c_void_p(self._out_stage.ptr.value + self._out_offset[node.y])
