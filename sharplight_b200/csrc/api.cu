@@ -390,10 +390,10 @@ slc_result slc_activation_create(slc_device *d, int64_t max_rows, int64_t k, slc
     const size_t q_b = round_up(cap * kp, 256), ds_b = round_up(cap * (kp / 32) * 8, 256);
     const size_t gs_b = round_up(cap * (kp / 16) * 4, 256), is_b = round_up(cap * (kp / 32) * 4, 256);
     const size_t qt_b = a->cap_rows > 64 ? q_b : 0;   // core-matrix copy for the int8 tensor-core GEMM
-    // the tile kernel's planes (3 rows and more): f16 codes, split offset sums, partial-tile scratch and counters
+    // the tile kernel's planes (3 rows and more): swizzled codes, split offset sums, partial-tile scratch and counters
     const bool tiles = max_rows >= 3;
     a->tile_ctas = d->prop.multiProcessorCount;
-    const size_t ht_b = tiles ? round_up(cap * kp * 2, 1024) : 0, s2_b = tiles ? round_up(cap * (kp / 256) * 64, 1024) : 0;
+    const size_t ht_b = tiles ? round_up(cap * kp, 1024) : 0, s2_b = tiles ? round_up(cap * (kp / 256) * 64, 1024) : 0;
     const size_t sc_b = tiles ? round_up(umma_scratch_bytes(a->tile_ctas, a->cap_rows), 256) : 0;
     const size_t ct_b = tiles ? round_up((size_t)a->tile_ctas * 4, 256) : 0;
     a->bytes = q_b + 2 * ds_b + gs_b + is_b + qt_b + ht_b + s2_b + sc_b + ct_b + (tiles ? 1024 : 0);
@@ -414,7 +414,7 @@ slc_result slc_activation_create(slc_device *d, int64_t max_rows, int64_t k, slc
     if (tiles) {
         uint8_t *t0 = a->base + q_b + 2 * ds_b + gs_b + is_b + qt_b;   // 256-byte aligned so far; the planes want 1024
         t0 += (1024 - (reinterpret_cast<uintptr_t>(t0) & 1023)) & 1023;
-        a->h_tiled = t0;
+        a->q_sw = t0;
         a->sx2 = t0 + ht_b;
         a->tile_scratch = reinterpret_cast<float *>(t0 + ht_b + s2_b);
         a->tile_counters = reinterpret_cast<int *>(t0 + ht_b + s2_b + sc_b);
@@ -446,7 +446,7 @@ slc_result slc_activation_quantize(slc_activation *a, const void *x, int32_t x_d
     SLC_CUDA(cudaSetDevice(a->dev->index));
     cudaStream_t s = stream ? (cudaStream_t)stream : a->dev->stream;
     a->planes.q_tiled = rows > 64 ? a->q_tiled : nullptr;
-    a->planes.h_tiled = rows >= 3 ? a->h_tiled : nullptr;
+    a->planes.q_sw = rows >= 3 ? a->q_sw : nullptr;
     a->planes.sx2 = rows >= 3 ? a->sx2 : nullptr;
     a->reads_since_quantize = 0;
     a->quantize_stream = stream ? (cudaStream_t)stream : a->dev->stream;
@@ -519,7 +519,7 @@ slc_result slc_matmul_set_kernel(slc_matmul *op, int32_t kernel)
     if (!op) return fail(SLC_ERR_INVALID_ARGUMENT, "op is null");
     if (kernel < SLC_KERNEL_AUTO || kernel > SLC_KERNEL_TILE) return fail(SLC_ERR_INVALID_ARGUMENT, "unknown kernel family");
     if (kernel == SLC_KERNEL_TILE && !umma_supports(op->w->fmt)) {
-        return fail(SLC_ERR_UNSUPPORTED, "the f16 tensor-core tile kernel does not take this weight format");
+        return fail(SLC_ERR_UNSUPPORTED, "the tile kernel does not take this weight format");
     }
     if (kernel == SLC_KERNEL_MMQ && !mmq_supports(op->w->fmt)) {
         return fail(SLC_ERR_UNSUPPORTED, "the tensor-core GEMM does not take this weight format");
@@ -551,7 +551,7 @@ static int choose_kernel(const slc_matmul *op, int rows, bool exchanging)
     const bool mv = matvec_fits(1, op->w->view.k_pad, op->w2 != nullptr);
     if (mv && (op->flags & SLC_MATMUL_ROW_INVARIANT) && rows <= 8) return SLC_KERNEL_MMVQ;
     if (mv && rows <= 2) return SLC_KERNEL_MMVQ;
-    // three rows and more: the f16 tensor-core tiles; the in-kernel sum over ranks lives in the older kernels
+    // the tile kernel (stream-K, tcgen05) from UMMA_MIN_ROWS rows; the in-kernel sum over ranks lives in the older kernels
     if (rows >= UMMA_MIN_ROWS && umma_supports(op->w->fmt) && !exchanging) return SLC_KERNEL_TILE;
     if (rows <= 64 || !mmq_supports(op->w->fmt)) return SLC_KERNEL_SKINNY;
     return SLC_KERNEL_MMQ;
@@ -625,9 +625,9 @@ static slc_result run_family(slc_matmul *op, const WeightView &wv, const WeightV
         }
     } else if (kernel == SLC_KERNEL_TILE) {
         if (ex) return fail(SLC_ERR_UNSUPPORTED, "the tile kernel does not sum over ranks");
-        if (!act->planes.h_tiled) return fail(SLC_ERR_INVALID_STATE, "the tile kernel needs an activation object created for 3 rows or more");
+        if (!act->planes.q_sw) return fail(SLC_ERR_INVALID_STATE, "the tile kernel needs an activation object created for 3 rows or more");
         // one persistent launch; it shares the activation object's scratch with other launches, so it never runs early
-        SLC_CUDA(launch_umma(wv, av, act->planes.h_tiled, act->planes.sx2, y, y_stride, dump, op->dev->status_dev,
+        SLC_CUDA(launch_umma(wv, av, act->planes.q_sw, act->planes.sx2, y, y_stride, dump, op->dev->status_dev,
                              act->tile_scratch, act->tile_counters, act->tile_ctas, s, ep));
         act->reads_since_quantize++;
         op->last_launches++;

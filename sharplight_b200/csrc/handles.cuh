@@ -34,7 +34,7 @@ struct slc_activation
     size_t bytes = 0;
     slc::ActPlanes planes{};
     uint8_t *q_tiled = nullptr;   // present when the capacity allows GEMM-sized row counts
-    uint8_t *h_tiled = nullptr, *sx2 = nullptr;   // f16 operand planes of the tile kernel (capacity of 3 rows and more)
+    uint8_t *q_sw = nullptr, *sx2 = nullptr;   // operand planes of the tile kernel (capacity of 3 rows and more)
     float *tile_scratch = nullptr;                // partial tiles of K ranges shared between CTAs (umma.cu)
     int *tile_counters = nullptr;
     int tile_ctas = 0;                            // CTAs the scratch was sized for (the device's SM count)

@@ -98,8 +98,8 @@ cudaError_t launch_repack(int fmt, int n, int k, int n_pad, int k_pad, uint8_t *
 // quantize.cu: x (f32 or bf16, device) -> ActView planes. x_dtype: 0 = f32, 1 = bf16.
 struct ActPlanes
 {
-    uint8_t *h_tiled;   // optional: the codes as f16 in 128-byte swizzled operand rows (umma.cu), or null
-    uint8_t *sx2;       // optional, with h_tiled: d * sum32(q) split in two tf32 halves, 64-byte swizzled operand rows
+    uint8_t *q_sw;      // optional: a copy of the codes in 128-byte swizzled operand rows (umma.cu), or null
+    uint8_t *sx2;       // optional, with q_sw: d * sum32(q) split in two tf32 halves, 64-byte swizzled operand rows
     uint8_t *q_tiled;   // optional second copy of the codes in tensor-core core-matrix order (mmq.cu), or null
     int8_t *q;
     float2 *ds;
@@ -137,13 +137,13 @@ cudaError_t launch_mmq(const WeightView &w, const ActView &a, const uint8_t *q_t
                        int *dump, int *status, int early, cudaStream_t stream, const Epilogue *epilogue = nullptr);
 
 // umma.cu: tcgen05 kind::f16 tiles for 3 rows and more (Q4_K, Q4_0, Q8_0), stream-K over one persistent CTA per SM.
-// h_tiled / sx2: the tiled planes the quantizer wrote for these rows (rows_pad a multiple of umma_token_tile(rows));
+// q_sw / sx2: the tiled planes the quantizer wrote for these rows (rows_pad a multiple of umma_token_tile(rows));
 // scratch (umma_scratch_bytes) and counters (max_ctas ints, zero between launches) serve the tiles whose K range is
 // shared by several CTAs. Launches that use the same scratch must not overlap.
 bool umma_supports(int fmt);
 int umma_token_tile(int rows);
 size_t umma_scratch_bytes(int max_ctas, int rows_pad);
-cudaError_t launch_umma(const WeightView &w, const ActView &a, const uint8_t *h_tiled, const uint8_t *sx2, float *y,
+cudaError_t launch_umma(const WeightView &w, const ActView &a, const uint8_t *q_sw, const uint8_t *sx2, float *y,
                         long long y_stride, int *dump, int *status, float *scratch, int *counters, int max_ctas,
                         cudaStream_t stream, const Epilogue *epilogue = nullptr);
 

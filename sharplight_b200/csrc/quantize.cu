@@ -74,16 +74,14 @@ __global__ void __launch_bounds__(256) quantize_kernel(const void *__restrict__ 
                               (row & 7) * 16 + (kk & 15);
         *reinterpret_cast<unsigned *>(out.q_tiled + off) = packed;
     }
-    if (out.h_tiled) {
-        // the same codes as f16 values (exact), in the 128-byte swizzled operand rows the f16 tensor-core tiles read:
-        // [k / 64][token / 8][token % 8][eight 16-byte chunks, chunk c stored at c ^ (token % 8)]; the tile of NT tokens
-        // x 64 K-values is then NT x 128 contiguous bytes, one bulk copy
+    if (out.q_sw) {
+        // the same codes once more, in the 128-byte swizzled operand rows the tile kernel's tensor-core instructions read:
+        // [k / 128][token / 8][token % 8][eight 16-byte chunks, chunk c stored at c ^ (token % 8)]; the tile of NT tokens
+        // x 128 K-values is then NT x 128 contiguous bytes, one bulk copy
         const int kk = blk * 32 + sub * 4;
-        const long long off = ((long long)(kk >> 6) * (rows_pad >> 3) + (row >> 3)) * 1024 + (row & 7) * 128 +
-                              ((((kk & 63) >> 3) ^ (row & 7)) << 4) + (kk & 7) * 2;
-        const __half2 h01 = __floats2half2_rn((float)r[0], (float)r[1]), h23 = __floats2half2_rn((float)r[2], (float)r[3]);
-        *reinterpret_cast<uint2 *>(out.h_tiled + off) =
-            make_uint2(*reinterpret_cast<const unsigned *>(&h01), *reinterpret_cast<const unsigned *>(&h23));
+        const long long off = ((long long)(kk >> 7) * (rows_pad >> 3) + (row >> 3)) * 1024 + (row & 7) * 128 +
+                              ((((kk & 127) >> 4) ^ (row & 7)) << 4) + (kk & 15);
+        *reinterpret_cast<unsigned *>(out.q_sw + off) = packed;
     }
     s += __shfl_xor_sync(0xffffffffu, s, 1);
     s += __shfl_xor_sync(0xffffffffu, s, 2);        // sum of this lane's 16-value group

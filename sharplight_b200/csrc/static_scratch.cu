@@ -92,7 +92,7 @@ slc_result slc_matmul_run_static(slc_weight *weight, const void *x_device, int32
     const int k_pad = wv.k_pad;
     ActPlanes planes;
     planes.q_tiled = nullptr;
-    planes.h_tiled = nullptr;
+    planes.q_sw = nullptr;
     planes.sx2 = nullptr;
     planes.q = reinterpret_cast<int8_t *>(base);
     planes.ds = reinterpret_cast<float2 *>(base + NA_Q);

@@ -475,3 +475,101 @@ def test_row_invariant_short_k(cuda_device, rows):
     finally:
         op.dispose()
         w.dispose()
+
+
+# ---- the tcgen05 tile kernel (selectable family): stream-K over persistent CTAs, every token-tile width ---------------------
+
+@pytest.mark.parametrize("type_name,n,k,rows", [
+    ("Q4_0", 128, 256, 16), ("Q4_0", 96, 512, 5), ("Q8_0", 96, 512, 3), ("Q4_K", 96, 512, 8), ("Q4_K", 130, 1024, 17),
+    ("Q4_K", 300, 2048, 33), ("Q8_0", 7, 1568, 12), ("Q4_0", 7, 96, 3), ("Q4_K", 1000, 3072, 64), ("Q4_K", 384, 1024, 65),
+    ("Q4_0", 640, 2048, 130), ("Q8_0", 256, 1024, 300), ("Q4_K", 4112, 512, 40), ("Q4_K", 1000, 2816, 256),
+    ("Q8_0", 2500, 1024, 31), ("Q4_0", 19000, 256, 9)])
+def test_tile_kernel_shapes(cuda_device, type_name, n, k, rows):
+    """Ragged N and K, every token-tile width (16, 32, 64, 128), tiles split between CTAs and tiles owned by one CTA,
+    more tiles than CTAs and fewer; y against the oracle and the int32 block dots bit for bit."""
+    _, kern = check_matmul(cuda_device, type_name, n, k, rows, seed=n + k + rows, kernel=N.KERNEL_TILE)
+    assert kern[0] == N.KERNEL_TILE
+    assert cuda_device.last_status() == 0
+
+
+def test_tile_kernel_refuses_q6_k_and_short_rows(cuda_device):
+    w = cuda_device.upload_weight("Q6_K", (64, 256), synth.weight_blocks("Q6_K", 64, 256, 1))
+    op = MatMulOp(cuda_device, w, 8)
+    try:
+        with pytest.raises(Exception):
+            op.set_kernel(N.KERNEL_TILE)
+    finally:
+        op.dispose()
+        w.dispose()
+    # fewer than 3 rows: the forced family falls back to the automatic choice
+    _, kern = check_matmul(cuda_device, "Q4_K", 64, 512, 2, kernel=N.KERNEL_TILE, max_rows=8)
+    assert kern[0] != N.KERNEL_TILE
+
+
+@pytest.mark.parametrize("rows", [16, 64])
+def test_tile_kernel_config2_full_size(cuda_device, rows):
+    fmt, n, k = FMT_OF["Q4_K"], 14336, 4096
+    blocks = synth.weight_blocks("Q4_K", n, k, 77)
+    x = synth.activations(rows, k, 78 + rows)
+    w = cuda_device.upload_weight("Q4_K", (n, k), blocks)
+    op = MatMulOp(cuda_device, w, rows)
+    try:
+        op.set_kernel(N.KERNEL_TILE)
+        y = op.run(x)
+        ref, ref64, _ = sl_oracle.matmul_intdot(fmt, blocks, n, k, x, threads=8, want_f64=True)
+        assert max_rel_error(y, ref) <= MAX_REL and max_rel_error(y, ref64) <= MAX_REL
+        assert op.last_kernel()[0] == N.KERNEL_TILE and cuda_device.last_status() == 0
+    finally:
+        op.dispose()
+        w.dispose()
+
+
+# ---- prefill GEMM at full size: int32 block dots of config 3, and the 70B-shaped Q4_K MatMuls at 2048 rows -----------------
+
+@pytest.mark.parametrize("kernel", [N.KERNEL_AUTO, N.KERNEL_TILE])
+def test_config3_block_dots_sample_full_size(cuda_device, kernel):
+    """Q4_0 [4096, 4096] x [2048, 4096]: the GEMM exports every int32 block dot of the full-size problem (4.3 GB); a sample of
+    token rows is compared bit for bit with the oracle's."""
+    n, k, rows = 4096, 4096, 2048
+    blocks = synth.weight_blocks("Q4_0", n, k, 103)
+    x = synth.activations(rows, k, 105)
+    w = cuda_device.upload_weight("Q4_0", (n, k), blocks)
+    op = MatMulOp(cuda_device, w, rows)
+    try:
+        if kernel != N.KERNEL_AUTO:
+            op.set_kernel(kernel)
+        got = op.block_dots(x)
+        assert op.last_kernel()[0] == (N.KERNEL_MMQ if kernel == N.KERNEL_AUTO else kernel)
+        sample = np.sort(np.random.Generator(np.random.Philox(9)).choice(rows, 12, replace=False))
+        _, _, s32 = sl_oracle.matmul_intdot(2, blocks, n, k, x[sample], threads=8, want_f64=False, want_s32=True)
+        assert np.array_equal(got[sample], s32)
+        assert cuda_device.last_status() == 0
+    finally:
+        op.dispose()
+        w.dispose()
+
+
+@pytest.mark.parametrize("kernel", [N.KERNEL_AUTO, N.KERNEL_TILE])
+@pytest.mark.parametrize("n,k", [(8192, 8192), (1280, 8192), (8192, 3584)])
+def test_q4_k_gemm_70b_shapes_at_2048_rows(cuda_device, n, k, kernel):
+    """The Q4_K MatMuls of the 70B-shaped stack in prefill: attention output [8192, 8192], and the 8-way tensor-parallel
+    shards of stacked qkv [1280, 8192] and down [8192, 3584], 2048 token rows; a sample of weight rows against the oracle."""
+    fmt, rows, sample_n = FMT_OF["Q4_K"], 2048, 48
+    blocks = synth.weight_blocks("Q4_K", n, k, 400 + n % 97)
+    x = synth.activations(rows, k, 401)
+    w = cuda_device.upload_weight("Q4_K", (n, k), blocks)
+    op = MatMulOp(cuda_device, w, rows)
+    try:
+        if kernel != N.KERNEL_AUTO:
+            op.set_kernel(kernel)
+        y = op.run(x)
+        assert op.last_kernel()[0] == (N.KERNEL_MMQ if kernel == N.KERNEL_AUTO else kernel)
+        pick = np.sort(np.random.Generator(np.random.Philox(n + k)).choice(n, sample_n, replace=False))
+        sub = np.ascontiguousarray(blocks.reshape(n, blocks.size // n)[pick]).reshape(-1)
+        ref, ref64, _ = sl_oracle.matmul_intdot(fmt, sub, sample_n, k, x, threads=8, want_f64=True)
+        assert max_rel_error(y[:, pick], ref) <= MAX_REL
+        assert max_rel_error(y[:, pick], ref64) <= MAX_REL
+        assert cuda_device.last_status() == 0
+    finally:
+        op.dispose()
+        w.dispose()
