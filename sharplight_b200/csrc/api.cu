@@ -395,7 +395,9 @@ slc_result slc_activation_create(slc_device *d, int64_t max_rows, int64_t k, slc
     a->tile_ctas = d->prop.multiProcessorCount;
     const size_t ht_b = tiles ? round_up(cap * kp, 1024) : 0, s2_b = tiles ? round_up(cap * (kp / 256) * 64, 1024) : 0;
     const size_t sc_b = tiles ? round_up(umma_scratch_bytes(a->tile_ctas, a->cap_rows), 256) : 0;
-    const size_t ct_b = tiles ? round_up((size_t)a->tile_ctas * 4, 256) : 0;
+    a->tile_scratch_floats = sc_b / sizeof(float);
+    a->tile_counter_slots = a->tile_ctas > 4096 ? a->tile_ctas : 4096;
+    const size_t ct_b = tiles ? round_up((size_t)a->tile_counter_slots * 4, 256) : 0;
     a->bytes = q_b + 2 * ds_b + gs_b + is_b + qt_b + ht_b + s2_b + sc_b + ct_b + (tiles ? 1024 : 0);
     cudaError_t e = cudaMalloc(&a->base, a->bytes);
     if (e == cudaSuccess) e = cudaMemset(a->base, 0, a->bytes);
@@ -617,9 +619,12 @@ static slc_result run_family(slc_matmul *op, const WeightView &wv, const WeightV
             op->last_launches++;
         }
     } else if (kernel == SLC_KERNEL_SKINNY) {
+        // the activation object's scratch area (present from 3 rows of capacity) lets short-and-wide MatMuls split K
+        const SkinnySplit split{ act->tile_scratch, act->tile_counters, act->tile_scratch_floats, act->tile_counter_slots, act->tile_ctas };
         for (int r0 = 0; r0 < rows; r0 += 64) {
             const int m = rows - r0 < 64 ? rows - r0 : 64;
-            SLC_CUDA(launch_skinny(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, early(), s, ex, ep));
+            SLC_CUDA(launch_skinny(wv, av, r0, m, y, y_stride, dump ? dump + r0 * dump_row : nullptr, op->dev->status_dev, early(), s, ex, ep,
+                                   act->tile_scratch ? &split : nullptr));
             act->reads_since_quantize++;
             op->last_launches++;
         }

@@ -35,8 +35,10 @@ struct slc_activation
     slc::ActPlanes planes{};
     uint8_t *q_tiled = nullptr;   // present when the capacity allows GEMM-sized row counts
     uint8_t *q_sw = nullptr, *sx2 = nullptr;   // operand planes of the tile kernel (capacity of 3 rows and more)
-    float *tile_scratch = nullptr;                // partial tiles of K ranges shared between CTAs (umma.cu)
+    float *tile_scratch = nullptr;                // partial tiles of K ranges shared between CTAs (umma.cu, skinny.cu)
+    size_t tile_scratch_floats = 0;
     int *tile_counters = nullptr;
+    int tile_counter_slots = 0;
     int tile_ctas = 0;                            // CTAs the scratch was sized for (the device's SM count)
     int rows = 0, rows_pad = 0;   // what the last quantize call wrote
     int reads_since_quantize = 0;       // MatMul launches that have read the current contents ...

@@ -125,10 +125,20 @@ cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int r
 cudaError_t launch_gate_mul(const float *g, long long g_stride, float *y, long long y_stride, int rows, int n,
                             cudaStream_t stream);
 
-// skinny.cu: int8 mma tiles, 1..64 activation rows per launch.
+// skinny.cu: int8 mma tiles, 1..64 activation rows per launch. split (optional): a scratch area and zeroed counters that
+// let a MatMul with few weight rows and a long K spread over the machine in chunks of K (partial tiles summed by the last
+// CTA to arrive, in chunk order); launches that use it must not overlap each other -- they are never early.
+struct SkinnySplit
+{
+    float *scratch;        // scratch_floats floats
+    int *counters;         // counter_slots ints, zero between launches
+    size_t scratch_floats;
+    int counter_slots;
+    int sm_count;
+};
 cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
                           int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange = nullptr,
-                          const Epilogue *epilogue = nullptr);
+                          const Epilogue *epilogue = nullptr, const SkinnySplit *split = nullptr);
 
 // mmq.cu: tcgen05 / TMEM int8 GEMM for many rows (Q4_0, Q8_0, Q4_K). status: device word set to a negative code when
 // a bounded wait runs out.

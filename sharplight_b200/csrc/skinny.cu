@@ -286,12 +286,12 @@ __device__ __forceinline__ void sk_compute(const SkRec<FMT> &rec, const SkTile<N
 __host__ __device__ constexpr int sk_depth(int nt) { return 2; }
 // Slots of a warp's weight-record ring: one for the 64-token tile (its refill is issued as soon as the record is in
 // registers and travels during the step's arithmetic), which keeps two CTAs per SM.
-__host__ __device__ constexpr int sk_wdepth(int nt) { return nt == 8 ? 1 : sk_depth(nt); }
+__host__ __device__ constexpr int sk_wdepth(int nt) { return nt == 8 ? 1 : nt <= 2 ? 4 : sk_depth(nt); }
 
 template <int FMT, int NT, bool DUMP>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__restrict__ y, long long y_stride,
-              int *dump, int *status, int early, const Exchange ex, const Epilogue ep)
+              int *dump, int *status, int early, const Exchange ex, const Epilogue ep, float *split_scratch, int *split_counters)
 {
     extern __shared__ __align__(128) unsigned char sk_smem[];
     __shared__ __align__(8) uint64_t bars[SK_WARPS][4];
@@ -301,10 +301,16 @@ skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__
     const int rg_count = w.n_pad >> 4;
     const int rg = blockIdx.x * SK_RGS + rgl;
     const bool rg_live = rg < rg_count;
-    const int nst = w.k_pad >> 8;
+    // gridDim.y > 1: the K range is cut in gridDim.y chunks of super-tiles, one CTA each (few weight rows, long K: the row
+    // tiles alone would leave most SMs idle); the chunks' partial tiles meet in global memory at the end
+    const int nst_all = w.k_pad >> 8;
+    const int chunk = (nst_all + (int)gridDim.y - 1) / (int)gridDim.y;
+    const int sb = (int)blockIdx.y * chunk;                                   // first super-tile of this CTA
+    const int nst = nst_all - sb < chunk ? (nst_all - sb > 0 ? nst_all - sb : 0) : chunk;   // and how many
     const int per = (nst + SK_KS - 1) / SK_KS;          // super-tiles per K half; both halves take `per` steps
-    const int st0 = ks * per;
-    const int my_steps = !rg_live ? 0 : (nst - st0 < per ? (nst - st0 > 0 ? nst - st0 : 0) : per);
+    const int st0 = sb + ks * per;
+    const int left = nst - ks * per;
+    const int my_steps = !rg_live ? 0 : (left < per ? (left > 0 ? left : 0) : per);
     SkCtx<FMT, NT, DUMP> c{ w, a, row0, rg, lane >> 2, lane & 3, dump };
     unsigned char *act_ring = sk_smem;                                     // [D][SK_KS][TILE]
     uint8_t *w_ring = sk_smem + (size_t)D * SK_KS * TILE + (size_t)warp * WD * REC;   // this warp's [WD][REC]
@@ -326,8 +332,8 @@ skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__
     auto stage = [&](int b, int i) {
         if (i < per) {
             for (int h = 0; h < SK_KS; h++) {
-                const int st = h * per + i;
-                if (st >= nst) continue;
+                if (h * per + i >= nst) continue;
+                const int st = sb + h * per + i;
                 unsigned char *dst = act_ring + (b * SK_KS + h) * TILE;
                 for (int idx = threadIdx.x; idx < T * 16; idx += SK_WARPS * 32) {
                     const int tok = idx >> 4, ch = idx & 15;
@@ -383,7 +389,41 @@ skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__
             for (int e = 0; e < 4; e++) red[((rgl * NT + nt) * 4 + e) * 32 + lane] = acc[nt][e];
     }
     __syncthreads();
-    if (ex.world == 0) {
+    if (gridDim.y > 1) {
+        // K chunks: every CTA leaves its 64-column partial tile in global memory; the CTA that arrives last for these
+        // columns adds the parts in chunk order (the same order whichever CTA it is) and stores
+        __shared__ int is_last;
+        float *part = split_scratch + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * (T * 64);
+        if (ks == 0) {
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float v = acc[nt][e] + red[((rgl * NT + nt) * 4 + e) * 32 + lane];   // zero for absent row groups
+                    __stcg(&part[(nt * 8 + 2 * c.t + (e & 1)) * 64 + rgl * 16 + c.g + 8 * (e >> 1)], v);
+                }
+            }
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const int arrived = atomicAdd(&split_counters[blockIdx.x], 1);
+            is_last = arrived == (int)gridDim.y - 1;
+            if (is_last) split_counters[blockIdx.x] = 0;   // ready for the next launch
+        }
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            for (int idx = threadIdx.x; idx < rows * 64; idx += SK_WARPS * 32) {
+                const int m = idx >> 6, col = idx & 63, row = blockIdx.x * 64 + col;
+                float sum = 0.0f;
+                for (int p = 0; p < (int)gridDim.y; p++) {
+                    sum += __ldcg(split_scratch + ((size_t)p * gridDim.x + blockIdx.x) * (T * 64) + m * 64 + col);
+                }
+                if (row < w.n) y[(long long)(row0 + m) * y_stride + row] = ep.apply(sum, row0 + m, row);
+            }
+        }
+    } else if (ex.world == 0) {
         if (ks == 0 && rg_live) {
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
@@ -452,7 +492,8 @@ skinny_kernel(const WeightView w, const ActView a, int row0, int rows, float *__
 
 template <int FMT, int NT, bool DUMP>
 static cudaError_t launch_cfg(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                              int *dump, int *status, int early, cudaStream_t stream, const Exchange &ex, const Epilogue &ep)
+                              int *dump, int *status, int early, cudaStream_t stream, const Exchange &ex, const Epilogue &ep,
+                              const SkinnySplit &sp)
 {
     static bool configured[64] = {};
     int dev = 0;
@@ -468,18 +509,32 @@ static cudaError_t launch_cfg(const WeightView &w, const ActView &a, int row0, i
         configured[dev] = true;
     }
     const int rg_count = w.n_pad >> 4;
-    return launch_pdl(kernel, dim3((rg_count + SK_RGS - 1) / SK_RGS), dim3(SK_WARPS * 32), smem, stream, w, a, row0, rows,
-                      y, y_stride, dump, status, early, ex, ep);
+    const int ctas = (rg_count + SK_RGS - 1) / SK_RGS;
+    // K chunks when the row tiles alone leave CTA slots empty (4 CTAs of the small token tiles fit an SM, 2 of the large
+    // ones): at least four super-tiles per chunk, at most 8 chunks, and only while the partial tiles fit the scratch area
+    int split = 1;
+    const int slots = (NT <= 2 ? 4 : 2) * sp.sm_count;
+    if (sp.scratch && sp.counters && ex.world == 0 && ctas < sp.sm_count && ctas <= sp.counter_slots) {
+        split = slots / ctas;
+        const int nst = w.k_pad >> 8;
+        if (split > nst / 4) split = nst / 4;
+        if (split > 8) split = 8;
+        while (split > 1 && (size_t)split * ctas * (NT * 8 * 64) > sp.scratch_floats) split--;
+        if (split < 1) split = 1;
+    }
+    return launch_pdl(kernel, dim3(ctas, split), dim3(SK_WARPS * 32), smem, stream, w, a, row0, rows,
+                      y, y_stride, dump, status, split > 1 ? 0 : early, ex, ep, sp.scratch, sp.counters);
 }
 
 template <int FMT, bool DUMP>
 static cudaError_t launch_nt(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
-                             int *dump, int *status, int early, cudaStream_t stream, const Exchange &ex, const Epilogue &ep)
+                             int *dump, int *status, int early, cudaStream_t stream, const Exchange &ex, const Epilogue &ep,
+                             const SkinnySplit &sp)
 {
-    if (rows <= 8) return launch_cfg<FMT, 1, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
-    if (rows <= 16) return launch_cfg<FMT, 2, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
-    if (rows <= 32) return launch_cfg<FMT, 4, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
-    if (rows <= 64) return launch_cfg<FMT, 8, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep);
+    if (rows <= 8) return launch_cfg<FMT, 1, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep, sp);
+    if (rows <= 16) return launch_cfg<FMT, 2, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep, sp);
+    if (rows <= 32) return launch_cfg<FMT, 4, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep, sp);
+    if (rows <= 64) return launch_cfg<FMT, 8, DUMP>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep, sp);
     return cudaErrorInvalidValue;
 }
 
@@ -487,9 +542,10 @@ static cudaError_t launch_nt(const WeightView &w, const ActView &a, int row0, in
 // activations must be padded to the token tile (8, 16, 32 or 64 rows).
 cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int rows, float *y, long long y_stride,
                           int *dump, int *status, int early, cudaStream_t stream, const Exchange *exchange,
-                          const Epilogue *epilogue)
+                          const Epilogue *epilogue, const SkinnySplit *split)
 {
     if (w.n_pad == 0 || rows == 0) return cudaSuccess;
+    const SkinnySplit sp = split ? *split : SkinnySplit{ nullptr, nullptr, 0, 0, 0 };
     const Epilogue ep = epilogue ? *epilogue : Epilogue{ nullptr, nullptr, 0 };
     if (row0 & 7) return cudaErrorInvalidValue;
     Exchange ex{};
@@ -499,8 +555,8 @@ cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int r
         if (early || rows > ex.max_rows || ctas * 64 > ex.n_stride || ctas > ex.groups) return cudaErrorInvalidValue;
     }
 #define SLC_FMT(F) \
-    case F: return dump ? launch_nt<F, true>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep) \
-                        : launch_nt<F, false>(w, a, row0, rows, y, y_stride, nullptr, status, early, stream, ex, ep);
+    case F: return dump ? launch_nt<F, true>(w, a, row0, rows, y, y_stride, dump, status, early, stream, ex, ep, sp) \
+                        : launch_nt<F, false>(w, a, row0, rows, y, y_stride, nullptr, status, early, stream, ex, ep, sp);
     switch (w.fmt) {
         SLC_FMT(FMT_Q8_0) SLC_FMT(FMT_Q4_0) SLC_FMT(FMT_Q4_K) SLC_FMT(FMT_Q6_K)
     default: return cudaErrorInvalidValue;

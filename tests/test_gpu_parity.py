@@ -573,3 +573,17 @@ def test_q4_k_gemm_70b_shapes_at_2048_rows(cuda_device, n, k, kernel):
     finally:
         op.dispose()
         w.dispose()
+
+
+# ---- K chunks in the skinny kernel (few weight rows, long K) -----------------------------------------------------------
+
+@pytest.mark.parametrize("type_name,n,k,rows", [("Q4_K", 64, 8192, 8), ("Q4_K", 200, 2816, 5), ("Q8_0", 40, 8448, 16),
+                                                ("Q4_0", 1000, 4096, 33), ("Q6_K", 130, 4352, 64), ("Q4_K", 4096, 14336, 32)])
+def test_skinny_k_chunks(cuda_device, type_name, n, k, rows):
+    """Row tiles alone would fill less than the machine: the launch splits K between CTAs (2 to 8 chunks, uneven and empty
+    last chunks included); the sum over chunks must not change the result beyond rounding, the block dots not at all."""
+    dots = n * k * rows <= 1 << 28
+    _, kern = check_matmul(cuda_device, type_name, n, k, rows, seed=n + rows, kernel=N.KERNEL_SKINNY, dots=dots)
+    assert kern[0] == N.KERNEL_SKINNY and cuda_device.last_status() == 0
+    # twice in a row: the arrival counters are back at zero
+    check_matmul(cuda_device, type_name, n, k, rows, seed=n + rows + 1, kernel=N.KERNEL_SKINNY, dots=False)
