@@ -209,13 +209,16 @@ class TpStack:
     IN_KERNEL_ROWS = 16   # measured on 8 GPUs: in-kernel sum 2.2x faster than NCCL at 1 row, 1.5x at 8, 0.9x at 64
 
     def __init__(self, device, torch, dist, N, synth, rank, world, max_rows, layers, arch, type_name="Q4_K"):
-        from sharplight_b200 import MatMulOp, SharedActivation, TpExchange, tp
+        from sharplight_b200 import MatMulOp, SharedActivation, TpComm, TpExchange, tp
         self.torch, self.dist, self.N, self.world, self.device = torch, dist, N, world, device
-        self.exchange = None
+        self.exchange, self.comm = None, None
         if world > 1:
-            # the receive area of the in-kernel all-reduce (one serves o and down of every layer: same output width)
+            # the receive area of the in-kernel all-reduce (one serves o and down of every layer: same output width), and
+            # the library's own NCCL communicator for the row counts above it
             self.exchange = TpExchange(device, rank, world, N.TP_MAX_ROWS, arch["hidden"])
             self.exchange.connect_group(dist)
+            self.comm = TpComm.for_group(device, dist)
+            self.exchange.set_comm(self.comm, self.IN_KERNEL_ROWS)
             dist.barrier()
         rows = max_rows
         self.layers, self.arch, self.type_name = layers, arch, type_name
@@ -246,13 +249,13 @@ class TpStack:
         self.launches_per_step = 0
 
     def step(self, rows, sp, in_kernel=None):
-        """in_kernel: row-split MatMuls sum over the ranks inside their kernel (peer stores over NVLink), possible up
-        to 64 rows and the default up to IN_KERNEL_ROWS; otherwise the partial outputs go through an NCCL all-reduce."""
+        """Row-split MatMuls go through the exchange: the library sums over the ranks inside the MatMul kernel (peer stores
+        over NVLink) up to IN_KERNEL_ROWS rows and by its NCCL communicator above. in_kernel = True / False moves that
+        threshold to 64 / 0 rows for this step (the comparison legs)."""
         N = self.N
         launches = 0
-        if in_kernel is None:
-            in_kernel = rows <= self.IN_KERNEL_ROWS
-        in_kernel = in_kernel and self.exchange is not None and rows <= N.TP_MAX_ROWS
+        if self.exchange is not None:
+            self.exchange.set_comm(self.comm, self.IN_KERNEL_ROWS if in_kernel is None else N.TP_MAX_ROWS if in_kernel else 0)
         for layer_ops in self.ops:
             for key in ("x_attn", "x_o", "x_ffn", "x_down"):
                 x = self.x[key]
@@ -262,12 +265,10 @@ class TpStack:
                     if inp != key:
                         continue
                     y = self.y[name]
-                    if split == "row" and in_kernel:
+                    if split == "row" and self.exchange is not None:
                         self.exchange.matmul(layer_ops[name], self.act[key], y.data_ptr(), y.shape[1], sp)
                     else:
                         self.act[key].matmul(layer_ops[name], y.data_ptr(), y.shape[1], sp)
-                        if split == "row" and self.world > 1:
-                            self.dist.all_reduce(y[:rows])
                     launches += layer_ops[name].last_kernel()[1]
         self.launches_per_step = launches
 
@@ -292,6 +293,7 @@ class TpStack:
             self.torch.cuda.synchronize()
             self.dist.barrier()
             self.exchange.dispose()
+            self.comm.dispose()
         for layer_ops in self.ops:
             for op in layer_ops.values():
                 op.dispose()
@@ -637,6 +639,7 @@ def run_ours(args):
     ms_main = time_graphed(torch, dist, world, stream, lambda sp: stack.step(rows, sp), args.steps, warmup, use_graph=not args.no_graph)
     clocks = sampler.stop()
     launches_main = stack.launches_per_step
+    families_main = {name: KERNEL_NAMES.get(stack.ops[0][name].last_kernel()[0]) for name in stack.dims}
     value = stack.total_weight_bytes / (ms_main * 1e-3) / 1e9
 
     check = None
@@ -653,8 +656,9 @@ def run_ours(args):
                       "per_gpu_frac_of_hbm_peak": stack.total_weight_bytes / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                       "tops": flops_per_row * r / (ms * 1e-3) / 1e12, "steps": args.steps if r == rows else steps,
                       "launches_per_step": stack.launches_per_step if r != rows else launches_main,
-                      "kernel_families": {name: KERNEL_NAMES.get(stack.ops[0][name].last_kernel()[0]) for name in stack.dims},
-                      "allreduce": "none" if world == 1 else "in the MatMul kernel (peer stores)" if in_kernel else "NCCL",
+                      "kernel_families": families_main if r == rows else
+                                         {name: KERNEL_NAMES.get(stack.ops[0][name].last_kernel()[0]) for name in stack.dims},
+                      "allreduce": "none" if world == 1 else "in the MatMul kernel (peer stores)" if in_kernel else "ncclAllReduce issued by the library",
                       "allreduces_per_step": 2 * layers if world > 1 else 0}
         if world > 1 and r <= N.TP_MAX_ROWS and not args.tp_main_only:
             other = time_graphed(torch, dist, world, stream, lambda sp, r=r: stack.step(r, sp, in_kernel=not in_kernel),

@@ -242,7 +242,7 @@ SLC_API slc_result slc_matmul_run_quantized_epilogue(slc_matmul *op, slc_activat
         MatMul kernel itself sums the partial outputs of all ranks, through receive areas that the ranks map into each
         other's address space (CUDA IPC, plain peer stores over NVLink, bounded waits), and y receives the total, the
         bit-identical value on every rank. For up to SLC_TP_MAX_ROWS rows per call; larger row counts go through
-        slc_matmul_run_quantized and the caller's all-reduce.
+        the communicator below (slc_tp_exchange_set_comm), or slc_matmul_run_quantized and the caller's all-reduce.
         Set-up: every rank creates its exchange (same world, max_rows, n everywhere) and gets a 64-byte handle; the
         host exchanges the handles by any means and passes all of them, in rank order, to connect. All ranks must
         issue the same sequence of allreduce calls on an exchange. A peer that never arrives (it died, or its stream is
@@ -257,6 +257,20 @@ SLC_API slc_result slc_tp_exchange_connect(slc_tp_exchange *exchange, const uint
 SLC_API void slc_tp_exchange_destroy(slc_tp_exchange *exchange);
 /* How long a kernel waits for its peers before it gives up (default 1000 ms; 1..60000). */
 SLC_API slc_result slc_tp_exchange_set_wait_ms(slc_tp_exchange *exchange, int32_t milliseconds);
+/* The collective-library route for row counts the in-kernel sum does not serve. NCCL is loaded at run time
+   (libnccl.so.2; the copy already in the process, if there is one): without it these calls fail with
+   SLC_ERR_UNSUPPORTED and everything else works. Rank 0 obtains an id (slc_tp_comm_unique_id), the host hands it to all
+   ranks, every rank creates its communicator (a collective call: all ranks at the same time). Attached to an exchange,
+   it takes the sums of calls with more than in_kernel_rows rows (default 16: below that the in-kernel sum is faster)
+   or more than the exchange's max_rows: plain MatMul, ncclAllReduce in place on y, then bias / residual if given.
+   comm = null detaches. Destroy the communicator only when no rank has a launch in flight. */
+#define SLC_TP_COMM_ID_BYTES 128
+typedef struct slc_tp_comm slc_tp_comm;
+SLC_API slc_result slc_tp_comm_unique_id(uint8_t *out_id /* [SLC_TP_COMM_ID_BYTES] */);
+SLC_API slc_result slc_tp_comm_create(slc_device *device, int32_t rank, int32_t world,
+                                      const uint8_t *id /* [SLC_TP_COMM_ID_BYTES] */, slc_tp_comm **out);
+SLC_API void slc_tp_comm_destroy(slc_tp_comm *comm);
+SLC_API slc_result slc_tp_exchange_set_comm(slc_tp_exchange *exchange, slc_tp_comm *comm, int32_t in_kernel_rows);
 /* y (device, f32) = sum over ranks of (act . W^T), W being this rank's K range of the weight and act this rank's
    matching slice of the activations. Asynchronous on the stream. */
 /* The same with x not yet quantized (device, rows x k): slc_matmul_run with the sum over the ranks. */

@@ -660,6 +660,34 @@ slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act, float *
     return run_kernels(op, act, y, y_stride, nullptr, s);
 }
 
+// A row-split MatMul of a tensor-parallel group: the sum over the ranks happens inside the MatMul kernel (exchange) for
+// few rows, and by the attached communicator's all-reduce above the exchange's in_kernel_rows (or its row bound).
+static slc_result run_summed(slc_matmul *op, slc_activation *act, slc_tp_exchange *x, float *y, long long y_stride,
+                             cudaStream_t s, const Epilogue *ep)
+{
+    const int rows = act->rows;
+    if (!x->connected) return fail(SLC_ERR_INVALID_STATE, "the exchange is not connected");
+    if (op->w->n > x->n) return fail(SLC_ERR_INVALID_ARGUMENT, "the weight has more rows than the exchange was created for");
+    const bool by_comm = x->comm && x->world > 1 && (rows > x->in_kernel_rows || rows > x->max_rows);
+    if (!by_comm) {
+        if (rows > x->max_rows) return fail(SLC_ERR_UNSUPPORTED, "rows exceed the exchange's bound and no communicator is attached");
+        return run_kernels(op, act, y, y_stride, nullptr, s, &x->view, ep);
+    }
+    slc_result r = run_kernels(op, act, y, y_stride, nullptr, s, nullptr, nullptr);
+    if (r != SLC_OK) return r;
+    const int e = tp_comm_allreduce(x->comm->comm, y, rows, op->w->n, y_stride, s);
+    if (e != 0) return fail(SLC_ERR_CUDA, tp_comm_error(e));
+    op->last_launches++;
+    if (ep) {
+        SLC_CUDA(launch_add_epilogue(y, y_stride, rows, (int)op->w->n, *ep, s));
+        op->last_launches++;
+    }
+    // the all-reduce (and the additions) wrote y after the MatMul: nothing that follows may run beside them as if the
+    // activations' last reader were a MatMul of this stream
+    act->reads_since_quantize = 0;
+    return SLC_OK;
+}
+
 slc_result slc_matmul_run_quantized_epilogue(slc_matmul *op, slc_activation *act, slc_tp_exchange *x, const float *bias,
                                              const float *residual, int64_t residual_stride, float *y, int64_t y_stride,
                                              void *stream)
@@ -668,18 +696,14 @@ slc_result slc_matmul_run_quantized_epilogue(slc_matmul *op, slc_activation *act
     if (act->dev != op->dev || (x && x->dev != op->dev)) return fail(SLC_ERR_INVALID_ARGUMENT, "op, activation and exchange live on different devices");
     if (act->k != op->w->k) return fail(SLC_ERR_INVALID_ARGUMENT, "activation K differs from the weight's K");
     if (act->rows > op->max_rows) return fail(SLC_ERR_INVALID_STATE, "rows exceed the op's compiled bound");
-    if (x) {
-        if (!x->connected) return fail(SLC_ERR_INVALID_STATE, "the exchange is not connected");
-        if (act->rows > x->max_rows) return fail(SLC_ERR_UNSUPPORTED, "rows exceed the exchange's bound");
-        if (op->w->n > x->n) return fail(SLC_ERR_INVALID_ARGUMENT, "the weight has more rows than the exchange was created for");
-    }
     if (act->rows == 0 || op->w->n == 0) return SLC_OK;
     if (!y || y_stride < op->w->n) return fail(SLC_ERR_INVALID_ARGUMENT, "bad output buffer or stride");
     if (residual && residual_stride < op->w->n) return fail(SLC_ERR_INVALID_ARGUMENT, "residual_stride < N");
     SLC_CUDA(cudaSetDevice(op->dev->index));
     cudaStream_t s = stream ? (cudaStream_t)stream : op->dev->stream;
     const Epilogue ep{ bias, residual, residual_stride };
-    return run_kernels(op, act, y, y_stride, nullptr, s, x ? &x->view : nullptr, (bias || residual) ? &ep : nullptr);
+    if (x) return run_summed(op, act, x, y, y_stride, s, (bias || residual) ? &ep : nullptr);
+    return run_kernels(op, act, y, y_stride, nullptr, s, nullptr, (bias || residual) ? &ep : nullptr);
 }
 
 // ---- tensor-parallel exchange ---------------------------------------------------------------------------------------
@@ -779,25 +803,75 @@ void slc_tp_exchange_destroy(slc_tp_exchange *x)
     delete x;
 }
 
+// ---- tensor-parallel communicator (NCCL, loaded at run time) -------------------------------------------------------------
+
+slc_result slc_tp_comm_unique_id(uint8_t *out_id)
+{
+    if (!out_id) return fail(SLC_ERR_INVALID_ARGUMENT, "out_id is null");
+    if (const char *why = tp_comm_unavailable()) return fail(SLC_ERR_UNSUPPORTED, std::string("NCCL is not available: ") + why);
+    const int e = tp_comm_unique_id(out_id);
+    if (e != 0) return fail(SLC_ERR_CUDA, tp_comm_error(e));
+    return SLC_OK;
+}
+
+slc_result slc_tp_comm_create(slc_device *d, int32_t rank, int32_t world, const uint8_t *id, slc_tp_comm **out)
+{
+    if (!out) return fail(SLC_ERR_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    if (!d || !id || world < 1 || world > SLC_TP_MAX_RANKS || rank < 0 || rank >= world) {
+        return fail(SLC_ERR_INVALID_ARGUMENT, "communicator: 1 <= world <= 8, 0 <= rank < world, id from slc_tp_comm_unique_id");
+    }
+    if (const char *why = tp_comm_unavailable()) return fail(SLC_ERR_UNSUPPORTED, std::string("NCCL is not available: ") + why);
+    SLC_CUDA(cudaSetDevice(d->index));
+    slc_tp_comm *c = new (std::nothrow) slc_tp_comm();
+    if (!c) return fail(SLC_ERR_OUT_OF_MEMORY, "host allocation failed");
+    c->dev = d; c->rank = rank; c->world = world;
+    const int e = tp_comm_init(&c->comm, world, id, rank);
+    if (e != 0) {
+        delete c;
+        return fail(SLC_ERR_CUDA, tp_comm_error(e));
+    }
+    *out = c;
+    return SLC_OK;
+}
+
+void slc_tp_comm_destroy(slc_tp_comm *c)
+{
+    if (!c) return;
+    cudaSetDevice(c->dev->index);
+    cudaDeviceSynchronize();
+    if (c->comm) tp_comm_destroy(c->comm);
+    delete c;
+}
+
+slc_result slc_tp_exchange_set_comm(slc_tp_exchange *x, slc_tp_comm *comm, int32_t in_kernel_rows)
+{
+    if (!x) return fail(SLC_ERR_INVALID_ARGUMENT, "exchange is null");
+    if (comm && (comm->dev != x->dev || comm->world != x->world || comm->rank != x->rank)) {
+        return fail(SLC_ERR_INVALID_ARGUMENT, "the communicator belongs to another device, rank or group size");
+    }
+    if (in_kernel_rows < 0 || in_kernel_rows > SLC_TP_MAX_ROWS) return fail(SLC_ERR_INVALID_ARGUMENT, "in_kernel_rows: 0..64");
+    x->comm = comm;
+    x->in_kernel_rows = in_kernel_rows;
+    return SLC_OK;
+}
+
 slc_result slc_matmul_run_quantized_allreduce(slc_matmul *op, slc_activation *act, slc_tp_exchange *x, float *y,
                                               int64_t y_stride, void *stream)
 {
     if (!op || !act || !x) return fail(SLC_ERR_INVALID_ARGUMENT, "null op, activation or exchange");
     if (act->dev != op->dev || x->dev != op->dev) return fail(SLC_ERR_INVALID_ARGUMENT, "op, activation and exchange live on different devices");
-    if (!x->connected) return fail(SLC_ERR_INVALID_STATE, "the exchange is not connected");
     if (act->k != op->w->k) return fail(SLC_ERR_INVALID_ARGUMENT, "activation K differs from the weight's K");
     if (act->rows > op->max_rows) return fail(SLC_ERR_INVALID_STATE, "rows exceed the op's compiled bound");
-    if (act->rows > x->max_rows) return fail(SLC_ERR_UNSUPPORTED, "rows exceed the exchange's bound");
-    if (op->w->n > x->n) return fail(SLC_ERR_INVALID_ARGUMENT, "the weight has more rows than the exchange was created for");
     if (act->rows == 0 || op->w->n == 0) return SLC_OK;
     if (!y || y_stride < op->w->n) return fail(SLC_ERR_INVALID_ARGUMENT, "bad output buffer or stride");
     SLC_CUDA(cudaSetDevice(op->dev->index));
     cudaStream_t s = stream ? (cudaStream_t)stream : op->dev->stream;
-    return run_kernels(op, act, y, y_stride, nullptr, s, &x->view);
+    return run_summed(op, act, x, y, y_stride, s, nullptr);
 }
 
 // x -> y through the op's own activation object (created at first use).
-static slc_result quantize_and_run(slc_matmul *op, const Exchange *ex, const void *x_dev, int32_t x_dtype, int64_t rows,
+static slc_result quantize_and_run(slc_matmul *op, slc_tp_exchange *ex, const void *x_dev, int32_t x_dtype, int64_t rows,
                                    int64_t x_stride, float *y_dev, int64_t y_stride, cudaStream_t s)
 {
     slc_result r;
@@ -807,7 +881,7 @@ static slc_result quantize_and_run(slc_matmul *op, const Exchange *ex, const voi
     }
     r = slc_activation_quantize(op->act, x_dev, x_dtype, rows, x_stride, s);
     if (r != SLC_OK) return r;
-    r = run_kernels(op, op->act, y_dev, y_stride, nullptr, s, ex);
+    r = ex ? run_summed(op, op->act, ex, y_dev, y_stride, s, nullptr) : run_kernels(op, op->act, y_dev, y_stride, nullptr, s);
     if (r != SLC_OK) return r;
     op->last_launches_total = op->last_launches + 1;
     return SLC_OK;
@@ -864,12 +938,10 @@ slc_result slc_matmul_run_allreduce(slc_matmul *op, slc_tp_exchange *x, const vo
 {
     if (!op || !x) return fail(SLC_ERR_INVALID_ARGUMENT, "null op or exchange");
     if (x->dev != op->dev) return fail(SLC_ERR_INVALID_ARGUMENT, "op and exchange live on different devices");
-    if (!x->connected) return fail(SLC_ERR_INVALID_STATE, "the exchange is not connected");
     if (x_dtype != SLC_F32 && x_dtype != SLC_BF16) return fail(SLC_ERR_UNSUPPORTED, "activation dtype must be f32 or bf16");
     if (rows < 0) return fail(SLC_ERR_INVALID_ARGUMENT, "rows < 0");
     if (rows > op->max_rows) return fail(SLC_ERR_INVALID_STATE, "rows exceed the op's compiled bound");
-    if (rows > x->max_rows) return fail(SLC_ERR_UNSUPPORTED, "rows exceed the exchange's bound");
-    if (op->w->n > x->n) return fail(SLC_ERR_INVALID_ARGUMENT, "the weight has more rows than the exchange was created for");
+    if (rows > x->max_rows && !x->comm) return fail(SLC_ERR_UNSUPPORTED, "rows exceed the exchange's bound and no communicator is attached");
     if (rows == 0 || op->w->n == 0) return SLC_OK;
     if (!x_device || x_stride < op->w->k) return fail(SLC_ERR_INVALID_ARGUMENT, "bad activation buffer or stride");
     if (!y || y_stride < op->w->n) return fail(SLC_ERR_INVALID_ARGUMENT, "bad output buffer or stride");
@@ -877,7 +949,7 @@ slc_result slc_matmul_run_allreduce(slc_matmul *op, slc_tp_exchange *x, const vo
     cudaStream_t s = stream ? (cudaStream_t)stream : op->dev->stream;
     slc_result r = ensure_op_buffers(op, false, false);
     if (r != SLC_OK) return r;
-    return quantize_and_run(op, &x->view, x_device, x_dtype, rows, x_stride, y, y_stride, s);
+    return quantize_and_run(op, x, x_device, x_dtype, rows, x_stride, y, y_stride, s);
 }
 
 // ---- parity exports --------------------------------------------------------------------------------------------------

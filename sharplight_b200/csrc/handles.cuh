@@ -62,9 +62,18 @@ struct slc_matmul
 };
 
 
+struct slc_tp_comm
+{
+    slc_device *dev = nullptr;
+    int rank = 0, world = 0;
+    void *comm = nullptr;   // ncclComm_t
+};
+
 struct slc_tp_exchange
 {
     slc_device *dev = nullptr;
+    slc_tp_comm *comm = nullptr;          // optional: row counts above in_kernel_rows are summed by ncclAllReduce
+    int in_kernel_rows = 16;
     int rank = 0, world = 0;
     long long max_rows = 0, n = 0;
     uint8_t *base = nullptr;              // this rank's receive area, arrival words and counters (one allocation)

@@ -1,6 +1,9 @@
 // Launchers shared between the translation units of libsharplight_cuda.
 #pragma once
 
+#include <string>
+#include <string.h>
+
 #include "layout.cuh"
 
 namespace slc {
@@ -124,6 +127,16 @@ cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int r
 // gate.cu: y[t][n] = silu(g[t][n]) * y[t][n], the same tail for the row counts the other kernels serve.
 cudaError_t launch_gate_mul(const float *g, long long g_stride, float *y, long long y_stride, int rows, int n,
                             cudaStream_t stream);
+
+// tp_comm.cu: NCCL, loaded at run time, for the sums over ranks the in-kernel exchange does not serve.
+struct NcclId { char bytes[128]; };
+const char *tp_comm_unavailable();   // null when NCCL is loaded, else the reason
+std::string tp_comm_error(int code);
+int tp_comm_unique_id(uint8_t *out);
+int tp_comm_init(void **comm, int world, const uint8_t *id, int rank);
+int tp_comm_destroy(void *comm);
+int tp_comm_allreduce(void *comm, float *y, long long rows, long long n, long long y_stride, cudaStream_t stream);
+cudaError_t launch_add_epilogue(float *y, long long y_stride, int rows, int n, const Epilogue &ep, cudaStream_t stream);
 
 // skinny.cu: int8 mma tiles, 1..64 activation rows per launch. split (optional): a scratch area and zeroed counters that
 // let a MatMul with few weight rows and a long K spread over the machine in chunks of K (partial tiles summed by the last

@@ -22,7 +22,7 @@ FMT_Q4_0, FMT_Q8_0, FMT_Q4_K, FMT_Q6_K = 2, 8, 12, 14
 F32, BF16 = 0, 1
 MATMUL_DEFAULT, MATMUL_ROW_INVARIANT = 0, 1
 KERNEL_AUTO, KERNEL_MMVQ, KERNEL_SKINNY, KERNEL_MMQ, KERNEL_TILE = 0, 1, 2, 3, 4
-TP_MAX_RANKS, TP_MAX_ROWS, TP_HANDLE_BYTES = 8, 64, 64
+TP_MAX_RANKS, TP_MAX_ROWS, TP_HANDLE_BYTES, TP_COMM_ID_BYTES = 8, 64, 64, 128
 
 BLOCK = {FMT_Q4_0: (32, 18), FMT_Q8_0: (32, 34), FMT_Q4_K: (256, 144), FMT_Q6_K: (256, 210)}
 
@@ -93,6 +93,10 @@ SIGNATURES = {
     "slc_tp_exchange_connect": (_i32, [_vp, _vp]),
     "slc_tp_exchange_destroy": (None, [_vp]),
     "slc_tp_exchange_set_wait_ms": (_i32, [_vp, _i32]),
+    "slc_tp_comm_unique_id": (_i32, [_vp]),
+    "slc_tp_comm_create": (_i32, [_vp, _i32, _i32, _vp, _P(_vp)]),
+    "slc_tp_comm_destroy": (None, [_vp]),
+    "slc_tp_exchange_set_comm": (_i32, [_vp, _vp, _i32]),
     "slc_matmul_run_allreduce": (_i32, [_vp, _vp, _vp, _i32, _i64, _i64, _vp, _i64, _vp]),
     "slc_matmul_run_quantized_allreduce": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp]),
     "slc_matmul_run_quantized_epilogue": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp]),

@@ -449,6 +449,44 @@ class SharedActivation:
             self._h = None
 
 
+class TpComm:
+    """The collective-library communicator of a tensor-parallel group (slc_tp_comm: NCCL, loaded by the native library
+    at run time). Rank 0 makes the id, the host hands it to every rank, all ranks create at the same time."""
+
+    def __init__(self, device: CudaDevice, rank: int, world: int, unique_id: bytes):
+        if len(unique_id) != N.TP_COMM_ID_BYTES:
+            raise ArgumentError("unique_id must be the 128 bytes of TpComm.unique_id()")
+        self.device, self.rank, self.world = device, rank, world
+        h = C.c_void_p()
+        buf = (C.c_uint8 * N.TP_COMM_ID_BYTES).from_buffer_copy(unique_id)
+        _check(N.load().slc_tp_comm_create(device.handle, rank, world, buf, C.byref(h)))
+        self._h = h
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = (C.c_uint8 * N.TP_COMM_ID_BYTES)()
+        _check(N.load().slc_tp_comm_unique_id(buf))
+        return bytes(buf)
+
+    @classmethod
+    def for_group(cls, device: CudaDevice, dist) -> "TpComm":
+        """Creates the communicator over an initialised torch.distributed group (the id travels by broadcast)."""
+        box = [cls.unique_id() if dist.get_rank() == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        return cls(device, dist.get_rank(), dist.get_world_size(), box[0])
+
+    @property
+    def handle(self):
+        if self._h is None:
+            raise ObjectDisposedError("TpComm")
+        return self._h
+
+    def dispose(self) -> None:
+        if self._h is not None:
+            N.load().slc_tp_comm_destroy(self._h)
+            self._h = None
+
+
 class TpExchange:
     """The receive area through which a row-split MatMul's kernel sums its output over the ranks of a tensor-parallel
     group (slc_tp_exchange). One per rank; ``handle_bytes`` of every rank, in rank order, go to ``connect``."""
@@ -476,6 +514,11 @@ class TpExchange:
     def set_wait_ms(self, milliseconds: int) -> None:
         """How long a kernel waits for its peers before it raises the device status to ERR_TIMEOUT."""
         _check(N.load().slc_tp_exchange_set_wait_ms(self.handle, milliseconds))
+
+    def set_comm(self, comm: Optional["TpComm"], in_kernel_rows: int = 16) -> None:
+        """Calls with more than ``in_kernel_rows`` rows (or more than this exchange's max_rows) are summed by the
+        communicator's all-reduce instead of inside the MatMul kernel; None detaches."""
+        _check(N.load().slc_tp_exchange_set_comm(self.handle, comm.handle if comm is not None else None, in_kernel_rows))
 
     def connect_group(self, dist) -> None:
         """Exchanges the handles over an initialised torch.distributed group and connects."""

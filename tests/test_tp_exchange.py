@@ -51,11 +51,16 @@ def test_group_of_one_gives_the_plain_result(cuda_device, type_name, n, k):
             act.matmul(op, y0.value, n)
             ex.matmul(op, act, y1.value, n)
             plain, summed = _read(lib, cuda_device, y0, (rows, n)), _read(lib, cuda_device, y1, (rows, n))
-            assert np.array_equal(plain.view(np.uint32), summed.view(np.uint32)), (rows, op.last_kernel())
+            if rows <= 2:
+                assert np.array_equal(plain.view(np.uint32), summed.view(np.uint32)), (rows, op.last_kernel())
+            else:
+                # from 3 rows the plain launch may cut K in chunks between CTAs (few weight rows): another order of the
+                # same f32 sums
+                assert np.max(np.abs(plain - summed)) <= 1e-5 * np.max(np.abs(plain)), (rows, op.last_kernel())
             # the same from rows that have not been quantized yet (slc_matmul_run_allreduce)
             y2 = _dev(lib, cuda_device, np.full((rows, n), np.nan, np.float32))
             ex.run(op, xd.value, N.F32, rows, k, y2.value, n)
-            assert np.array_equal(plain.view(np.uint32), _read(lib, cuda_device, y2, (rows, n)).view(np.uint32)), rows
+            assert np.array_equal(summed.view(np.uint32), _read(lib, cuda_device, y2, (rows, n)).view(np.uint32)), rows
             lib.slc_buffer_free(cuda_device.handle, y2)
             for p in (xd, y0, y1):
                 lib.slc_buffer_free(cuda_device.handle, p)
@@ -108,7 +113,7 @@ def _free_port():
 def _two_gpu_worker(rank, world, port, out):
     import torch
     import torch.distributed as dist
-    from sharplight_b200 import CudaExecutionProvider
+    from sharplight_b200 import CudaExecutionProvider, TpComm
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -146,7 +151,8 @@ def _two_gpu_worker(rank, world, port, out):
                 mine = y_sum.cpu().numpy()
                 if max_rel_error(mine, ref) > MAX_REL:
                     failures.append(f"{type_name} rows={rows}: differs from the oracle by {max_rel_error(mine, ref):.2e}")
-                if max_rel_error(mine, y_part.cpu().numpy()) > 1e-5:
+                # (the plain launch may sum K in chunks between CTAs, the exchanging one does not: f32 rounding apart)
+                if max_rel_error(mine, y_part.cpu().numpy()) > 1e-4:
                     failures.append(f"{type_name} rows={rows}: differs from the NCCL all-reduce")
                 both = [torch.empty_like(y_sum) for _ in range(world)]
                 dist.all_gather(both, y_sum)
@@ -157,6 +163,37 @@ def _two_gpu_worker(rank, world, port, out):
                 failures.append(f"{type_name}: device status {status}")
             dist.barrier()
             torch.cuda.synchronize()
+            if type_name == "Q4_K":
+                # the library's own NCCL communicator takes the sums above in_kernel_rows and above the exchange's bound
+                comm = TpComm.for_group(device, dist)
+                ex.set_comm(comm, 16)
+                op_big = MatMulOp(device, w, 256)
+                act_big = SharedActivation(device, 256, sk)
+                for call, rows in enumerate((8, 17, 64, 200)):
+                    x_full = synth.activations(rows, k, seed=170 + call)
+                    ref, _, _ = sl_oracle.matmul_intdot(fmt, blocks, n, k, x_full)
+                    x = torch.from_numpy(np.ascontiguousarray(x_full[:, k0:k0 + sk])).cuda()
+                    y_sum = torch.full((rows, n + 8), float("nan"), device="cuda")      # a row stride wider than n
+                    torch.cuda.synchronize()
+                    act_big.quantize(x.data_ptr(), N.F32, rows, sk, sp)
+                    ex.matmul(op_big, act_big, y_sum.data_ptr(), n + 8, sp)
+                    stream.synchronize()
+                    mine = y_sum[:, :n].cpu().numpy()
+                    if max_rel_error(mine, ref) > MAX_REL:
+                        failures.append(f"comm rows={rows}: differs from the oracle by {max_rel_error(mine, ref):.2e}")
+                    if not bool(torch.isnan(y_sum[:, n:]).all()):
+                        failures.append(f"comm rows={rows}: wrote beyond n")
+                    launches = op_big.last_kernel()[1]
+                    if (rows > 16) != (launches >= 2):
+                        failures.append(f"comm rows={rows}: {launches} launches (the sum went the wrong way)")
+                    both = [torch.empty_like(y_sum) for _ in range(world)]
+                    dist.all_gather(both, y_sum.nan_to_num())
+                    if not all(torch.equal(both[0], b) for b in both[1:]):
+                        failures.append(f"comm rows={rows}: the ranks hold different sums")
+                ex.set_comm(None, 16)
+                torch.cuda.synchronize()
+                dist.barrier()
+                act_big.dispose(); op_big.dispose(); comm.dispose()
             if type_name == "Q8_0":
                 # A peer that never shows up: rank 1 sits this exchange out (it has nothing in flight), rank 0's
                 # kernel gives up after the limit, reports through the status word and leaves the context usable.
