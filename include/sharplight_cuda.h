@@ -219,6 +219,25 @@ SLC_API void slc_activation_destroy(slc_activation *act);
    from zero (src/Sharplight.Cpu/IntDot.cs:92-126). Asynchronous on the stream. */
 SLC_API slc_result slc_activation_quantize(slc_activation *act, const void *x_device, int32_t x_dtype, int64_t rows,
                                            int64_t x_stride, void *stream);
+/* Producers: the operation in front of a MatMul writes the 8-bit activations itself, in the same pass (the reference
+   lets its norm kernels write the copy the next MatMul reads, src/Sharplight.Shaders/Lowering/GraphLowerer.IntDot.cs:146-184).
+   Both fill `act` exactly as slc_activation_quantize would from the f32 values they compute; y (optional, device) also
+   receives those f32 values (the residual stream needs the norm's input, not its output, so y is usually null).
+   rmsnorm: v = (x * 1 / sqrt(sum x^2 / K + eps)) * weight (src/Sharplight.Cpu/RowOp.cs:63-76), weight f32 [K] or null.
+   silu_mul: v = silu(gate) * up, silu(g) = g / (1 + exp(-g)) (src/Sharplight.Cpu/ScalarMath.cs:552-577): the gated-FFN
+   tail in front of the down projection; gate and up may be the two halves of one stacked gate/up output (strides). */
+SLC_API slc_result slc_activation_quantize_rmsnorm(slc_activation *act, const void *x_device, int32_t x_dtype, int64_t rows,
+                                                   int64_t x_stride, const float *weight_device, float eps,
+                                                   float *y_device, int64_t y_stride, void *stream);
+SLC_API slc_result slc_activation_quantize_silu_mul(slc_activation *act, const float *gate_device, int64_t gate_stride,
+                                                    const float *up_device, int64_t up_stride, int64_t rows,
+                                                    float *y_device, int64_t y_stride, void *stream);
+/* The sampling head behind the lm_head MatMul: out_index_device[t] = index of the first maximum of row t of y (NaN never
+   beats a number; src/Sharplight.Cpu/RowOp.cs:174-189), so one int32 per sequence leaves the device instead of the row
+   of logits. */
+SLC_API slc_result slc_argmax_rows(slc_device *device, const float *y_device, int64_t rows, int64_t n, int64_t y_stride,
+                                   int32_t *out_index_device, void *stream);
+
 /* y (device, f32) = act . W^T with the rows last quantized into act. Asynchronous on the stream. Consecutive calls that
    read the same quantized rows may execute side by side on the device: their outputs must not overlap in memory. */
 SLC_API slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act, float *y_device, int64_t y_stride,
@@ -247,7 +266,10 @@ SLC_API slc_result slc_matmul_run_quantized_epilogue(slc_matmul *op, slc_activat
         host exchanges the handles by any means and passes all of them, in rank order, to connect. All ranks must
         issue the same sequence of allreduce calls on an exchange. A peer that never arrives (it died, or its stream is
         stuck) ends the wait after about a second: the call's kernel raises the device status to SLC_ERR_TIMEOUT
-        (slc_last_status) and y is not meaningful. Destroy only when no rank has a launch in flight. */
+        (slc_last_status) and y is not meaningful. The device and every other handle stay usable after that, the
+        exchange itself does not: the ranks' call counts no longer agree (the rank that gave up counted its call, the
+        one that never launched did not), so every later call on it would time out as well. Destroy it on all ranks
+        and create and connect a new one. Destroy only when no rank has a launch in flight. */
 #define SLC_TP_MAX_RANKS 8
 #define SLC_TP_MAX_ROWS 64
 #define SLC_TP_HANDLE_BYTES 64

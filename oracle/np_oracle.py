@@ -126,3 +126,42 @@ def matmul_intdot_f64(fmt: int, blocks: np.ndarray, n: int, k: int, x: np.ndarra
     d16 = np.repeat(d, 2, axis=1).astype(np.float64)
     return (s * a.astype(np.float64)[None] * d16[:, None, :]).sum(-1) + \
         (b.astype(np.float64)[None] * (d16 * sq)[:, None, :]).sum(-1)
+
+
+# ---- the operations on either side of the MatMul that the CUDA path fuses with the activation quantization ---------------
+
+def rms_norm(x: np.ndarray, weight, eps: float) -> np.ndarray:
+    """RmsNorm as the reference's CPU row op computes it (src/Sharplight.Cpu/RowOp.cs:63-76, Simd.cs:464-483):
+    scale = 1 / sqrt(sum(x^2) / n + eps); y = (x * scale) * w, every step in f32. The reference's sum of squares runs
+    in an ISA-dependent order (Simd.cs:274-310); here it is accumulated in f64 and rounded once, which every such order
+    matches to a few ulp."""
+    x = np.asarray(x, np.float32)
+    n = x.shape[-1]
+    sumsq = np.sum(x.astype(np.float64) ** 2, axis=-1, keepdims=True).astype(np.float32)
+    scale = (np.float32(1.0) / np.sqrt(sumsq / np.float32(n) + np.float32(eps))).astype(np.float32)
+    y = (x * scale).astype(np.float32)
+    if weight is not None:
+        y = (y * np.asarray(weight, np.float32)).astype(np.float32)
+    return y
+
+
+def silu_mul(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """silu(gate) * up with silu(v) = v / (1 + exp(-v)) (src/Sharplight.Cpu/ScalarMath.cs:552-577), in f32."""
+    g = np.asarray(gate, np.float32)
+    with np.errstate(over="ignore"):
+        s = (g / (np.float32(1.0) + np.exp(-g).astype(np.float32))).astype(np.float32)
+    return (s * np.asarray(up, np.float32)).astype(np.float32)
+
+
+def argmax_first(y: np.ndarray) -> np.ndarray:
+    """Index of the first maximum per row as the reference's sequential scan finds it (src/Sharplight.Cpu/RowOp.cs:174-189):
+    best = 0; x[i] > x[best] replaces it -- so NaN never beats a number, and a row that starts with NaN answers 0."""
+    y = np.asarray(y, np.float32)
+    out = np.zeros(y.shape[0], np.int32)
+    for r in range(y.shape[0]):
+        row = y[r]
+        if row.size == 0 or np.isnan(row[0]):
+            continue
+        masked = np.where(np.isnan(row), -np.inf, row)
+        out[r] = int(np.argmax(masked))      # numpy's argmax is the first maximum too
+    return out

@@ -433,26 +433,82 @@ void slc_activation_destroy(slc_activation *a)
     delete a;
 }
 
+// What every way of filling an activation object does first: bounds, padded row count, which optional planes this row
+// count needs, and the bookkeeping that decides whether later MatMul launches may run beside each other.
+static slc_result begin_fill(slc_activation *a, int64_t rows, void *stream, cudaStream_t *s)
+{
+    if (rows < 0) return fail(SLC_ERR_INVALID_ARGUMENT, "rows < 0");
+    if (rows > a->max_rows) return fail(SLC_ERR_INVALID_STATE, "rows exceed the bound the activation was created with");
+    a->rows = (int)rows;
+    a->rows_pad = rows > 0 ? pad_rows(rows) : 0;
+    if (rows == 0) return SLC_OK;
+    SLC_CUDA(cudaSetDevice(a->dev->index));
+    *s = stream ? (cudaStream_t)stream : a->dev->stream;
+    a->planes.q_tiled = rows > 64 ? a->q_tiled : nullptr;
+    a->planes.q_sw = rows >= 3 ? a->q_sw : nullptr;
+    a->planes.sx2 = rows >= 3 ? a->sx2 : nullptr;
+    a->reads_since_quantize = 0;
+    a->quantize_stream = *s;
+    return SLC_OK;
+}
+
 slc_result slc_activation_quantize(slc_activation *a, const void *x, int32_t x_dtype, int64_t rows, int64_t x_stride,
                                    void *stream)
 {
     if (!a) return fail(SLC_ERR_INVALID_ARGUMENT, "activation is null");
     if (x_dtype != SLC_F32 && x_dtype != SLC_BF16) return fail(SLC_ERR_UNSUPPORTED, "activation dtype must be f32 or bf16");
-    if (rows < 0) return fail(SLC_ERR_INVALID_ARGUMENT, "rows < 0");
-    if (rows > a->max_rows) return fail(SLC_ERR_INVALID_STATE, "rows exceed the bound the activation was created with");
     if (rows > 0 && !x) return fail(SLC_ERR_INVALID_ARGUMENT, "x is null");
     if (rows > 0 && x_stride < a->k) return fail(SLC_ERR_INVALID_ARGUMENT, "x_stride < K");
-    a->rows = (int)rows;
-    a->rows_pad = rows > 0 ? pad_rows(rows) : 0;
-    if (rows == 0) return SLC_OK;
-    SLC_CUDA(cudaSetDevice(a->dev->index));
-    cudaStream_t s = stream ? (cudaStream_t)stream : a->dev->stream;
-    a->planes.q_tiled = rows > 64 ? a->q_tiled : nullptr;
-    a->planes.q_sw = rows >= 3 ? a->q_sw : nullptr;
-    a->planes.sx2 = rows >= 3 ? a->sx2 : nullptr;
-    a->reads_since_quantize = 0;
-    a->quantize_stream = stream ? (cudaStream_t)stream : a->dev->stream;
+    cudaStream_t s = nullptr;
+    slc_result r = begin_fill(a, rows, stream, &s);
+    if (r != SLC_OK || rows == 0) return r;
     SLC_CUDA(launch_quantize(x, x_dtype, a->rows, a->rows_pad, (int)a->k, a->k_pad, x_stride, a->planes, s));
+    return SLC_OK;
+}
+
+slc_result slc_activation_quantize_rmsnorm(slc_activation *a, const void *x, int32_t x_dtype, int64_t rows, int64_t x_stride,
+                                           const float *weight, float eps, float *y, int64_t y_stride, void *stream)
+{
+    if (!a) return fail(SLC_ERR_INVALID_ARGUMENT, "activation is null");
+    if (x_dtype != SLC_F32 && x_dtype != SLC_BF16) return fail(SLC_ERR_UNSUPPORTED, "activation dtype must be f32 or bf16");
+    if (rows > 0 && !x) return fail(SLC_ERR_INVALID_ARGUMENT, "x is null");
+    if (rows > 0 && x_stride < a->k) return fail(SLC_ERR_INVALID_ARGUMENT, "x_stride < K");
+    if (y && (y_stride < a->k || (y_stride & 3) || (reinterpret_cast<uintptr_t>(y) & 15))) {
+        return fail(SLC_ERR_INVALID_ARGUMENT, "y: 16-byte aligned, y_stride >= K and a multiple of 4");
+    }
+    if (weight && (reinterpret_cast<uintptr_t>(weight) & 15)) return fail(SLC_ERR_INVALID_ARGUMENT, "weight must be 16-byte aligned");
+    if (!(eps >= 0.0f)) return fail(SLC_ERR_INVALID_ARGUMENT, "eps must be >= 0");
+    cudaStream_t s = nullptr;
+    slc_result r = begin_fill(a, rows, stream, &s);
+    if (r != SLC_OK || rows == 0) return r;
+    SLC_CUDA(launch_rmsnorm_quantize(x, x_dtype, a->rows, a->rows_pad, (int)a->k, a->k_pad, x_stride, weight, eps, y, y_stride,
+                                     a->planes, s));
+    return SLC_OK;
+}
+
+slc_result slc_activation_quantize_silu_mul(slc_activation *a, const float *gate, int64_t gate_stride, const float *up,
+                                            int64_t up_stride, int64_t rows, float *y, int64_t y_stride, void *stream)
+{
+    if (!a) return fail(SLC_ERR_INVALID_ARGUMENT, "activation is null");
+    if (rows > 0 && (!gate || !up)) return fail(SLC_ERR_INVALID_ARGUMENT, "gate or up is null");
+    if (rows > 0 && (gate_stride < a->k || up_stride < a->k)) return fail(SLC_ERR_INVALID_ARGUMENT, "gate_stride / up_stride < K");
+    if (y && y_stride < a->k) return fail(SLC_ERR_INVALID_ARGUMENT, "y_stride < K");
+    cudaStream_t s = nullptr;
+    slc_result r = begin_fill(a, rows, stream, &s);
+    if (r != SLC_OK || rows == 0) return r;
+    SLC_CUDA(launch_silu_mul_quantize(gate, gate_stride, up, up_stride, a->rows, a->rows_pad, (int)a->k, a->k_pad, y, y_stride,
+                                      a->planes, s));
+    return SLC_OK;
+}
+
+slc_result slc_argmax_rows(slc_device *d, const float *y, int64_t rows, int64_t n, int64_t y_stride, int32_t *out_index, void *stream)
+{
+    if (!d) return fail(SLC_ERR_INVALID_ARGUMENT, "device is null");
+    if (rows < 0 || n < 1 || n > (1ll << 30) || rows > (1 << 24)) return fail(SLC_ERR_INVALID_ARGUMENT, "rows >= 0, 1 <= n <= 2^30");
+    if (rows == 0) return SLC_OK;
+    if (!y || !out_index || y_stride < n) return fail(SLC_ERR_INVALID_ARGUMENT, "bad buffers or stride");
+    SLC_CUDA(cudaSetDevice(d->index));
+    SLC_CUDA(launch_argmax_rows(y, y_stride, (int)rows, (int)n, out_index, stream ? (cudaStream_t)stream : d->stream));
     return SLC_OK;
 }
 

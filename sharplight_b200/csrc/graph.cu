@@ -73,9 +73,17 @@ slc_result slc_stream_wait(slc_device *d, void *waiter, void *signal)
     cudaEvent_t ev = nullptr;
     r = g_cuda(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreateWithFlags");
     if (r != SLC_OK) return r;
-    d->events.push_back(ev);   // kept until the device closes: a capture may still refer to it
+    // Inside a capture the event becomes part of the graph being built: it is kept until the device closes. Outside,
+    // it has done its work once the wait is enqueued (destroying an event that streams still wait on is safe: the
+    // resources go when the work completes), so a long-running host does not accumulate events.
+    cudaStreamCaptureStatus cap_w = cudaStreamCaptureStatusNone, cap_s = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(w, &cap_w);
+    cudaStreamIsCapturing(s, &cap_s);
+    const bool capturing = cap_w != cudaStreamCaptureStatusNone || cap_s != cudaStreamCaptureStatusNone;
     cudaError_t e = cudaEventRecord(ev, s);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(w, ev, 0);
+    if (capturing) d->events.push_back(ev);
+    else cudaEventDestroy(ev);
     return g_cuda(e, "cudaEventRecord / cudaStreamWaitEvent");
 }
 

@@ -128,6 +128,14 @@ cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int r
 cudaError_t launch_gate_mul(const float *g, long long g_stride, float *y, long long y_stride, int rows, int n,
                             cudaStream_t stream);
 
+// producers.cu: kernels that produce the quantized activations in the same pass as the operation in front of the MatMul
+// (y, optional: the f32 result as well), and the arg-max behind the lm_head.
+cudaError_t launch_rmsnorm_quantize(const void *x, int x_dtype, int rows, int rows_pad, int k, int k_pad, long long x_stride,
+                                    const float *weight, float eps, float *y, long long y_stride, ActPlanes out, cudaStream_t stream);
+cudaError_t launch_silu_mul_quantize(const float *gate, long long gate_stride, const float *up, long long up_stride, int rows,
+                                     int rows_pad, int k, int k_pad, float *y, long long y_stride, ActPlanes out, cudaStream_t stream);
+cudaError_t launch_argmax_rows(const float *y, long long y_stride, int rows, int n, int *out, cudaStream_t stream);
+
 // tp_comm.cu: NCCL, loaded at run time, for the sums over ranks the in-kernel exchange does not serve.
 struct NcclId { char bytes[128]; };
 const char *tp_comm_unavailable();   // null when NCCL is loaded, else the reason

@@ -263,6 +263,11 @@ class CudaDevice:
     def synchronize(self) -> None:
         _check(N.load().slc_device_sync(self.handle))
 
+    def argmax_rows(self, y_device_ptr: int, rows: int, n: int, y_stride: int, out_index_ptr: int, stream: int = 0) -> None:
+        """out[t] = index of the first maximum of row t (slc_argmax_rows): the sampling head behind the lm_head."""
+        _check(N.load().slc_argmax_rows(self.handle, C.c_void_p(y_device_ptr), rows, n, y_stride, C.c_void_p(out_index_ptr),
+                                        C.c_void_p(stream) if stream else None))
+
     def last_status(self) -> int:
         v = C.c_int32(0)
         _check(N.load().slc_last_status(self.handle, C.byref(v)))
@@ -430,6 +435,20 @@ class SharedActivation:
     def quantize(self, x_device_ptr: int, dtype: int, rows: int, x_stride: int, stream: int = 0) -> None:
         _check(N.load().slc_activation_quantize(self.handle, C.c_void_p(x_device_ptr), dtype, rows, x_stride,
                                                 C.c_void_p(stream) if stream else None))
+
+    def quantize_rmsnorm(self, x_device_ptr: int, dtype: int, rows: int, x_stride: int, weight_ptr: int, eps: float,
+                         y_device_ptr: int = 0, y_stride: int = 0, stream: int = 0) -> None:
+        """RmsNorm and quantization in one pass (slc_activation_quantize_rmsnorm); y (optional) also gets the f32 values."""
+        _check(N.load().slc_activation_quantize_rmsnorm(
+            self.handle, C.c_void_p(x_device_ptr), dtype, rows, x_stride, C.c_void_p(weight_ptr) if weight_ptr else None,
+            C.c_float(eps), C.c_void_p(y_device_ptr) if y_device_ptr else None, y_stride, C.c_void_p(stream) if stream else None))
+
+    def quantize_silu_mul(self, gate_ptr: int, gate_stride: int, up_ptr: int, up_stride: int, rows: int,
+                          y_device_ptr: int = 0, y_stride: int = 0, stream: int = 0) -> None:
+        """silu(gate) * up and quantization in one pass (slc_activation_quantize_silu_mul)."""
+        _check(N.load().slc_activation_quantize_silu_mul(
+            self.handle, C.c_void_p(gate_ptr), gate_stride, C.c_void_p(up_ptr), up_stride, rows,
+            C.c_void_p(y_device_ptr) if y_device_ptr else None, y_stride, C.c_void_p(stream) if stream else None))
 
     def matmul(self, op: MatMulOp, y_device_ptr: int, y_stride: int, stream: int = 0) -> None:
         _check(N.load().slc_matmul_run_quantized(op.handle, self.handle, C.c_void_p(y_device_ptr), y_stride,
