@@ -78,7 +78,13 @@ enum
     /* every activation row is computed exactly as a single row would be, so a 2-4 row verification step gives the
        logits of one-row decoding bit for bit (CompileOptions.RowInvariantRows, src/Sharplight.Core/Runtime/
        CompileOptions.cs:52-60; src/Sharplight.Cpu/MatMulOp.cs:36-41) */
-    SLC_MATMUL_ROW_INVARIANT = 1
+    SLC_MATMUL_ROW_INVARIANT = 1,
+    /* the node keeps f32 activation math (StandardOps' f32-activations attribute, src/Sharplight.Core/Graph/
+       StandardOps.cs:130-135): the activations are never quantized; slc_matmul_run serves the op with the dequant-fused
+       f32 mat-vec (GPU form in the reference: src/Sharplight.Shaders/Kernels/matmul.slang:148-226), up to 4 rows per
+       pass over the weights. Meant for decode-sized row counts; K up to 49 152. Such an op refuses the entry points
+       that take quantized activations. */
+    SLC_MATMUL_F32_ACTIVATIONS = 2
 };
 
 /* Kernel families, for slc_matmul_set_kernel / slc_matmul_last_kernel. */
@@ -88,7 +94,9 @@ enum
     SLC_KERNEL_MMVQ = 1,     /* dp4a mat-vec, weights streamed once for up to 8 activation rows */
     SLC_KERNEL_SKINNY = 2,   /* int8 mma tiles with the weight as the streamed operand, 9..64 rows */
     SLC_KERNEL_MMQ = 3,      /* tcgen05 / TMEM int8 GEMM for prefill */
-    SLC_KERNEL_TILE = 4      /* tcgen05 / TMEM tiles on exact f16-coded integers, stream-K, 3 rows and more (the default there) */
+    SLC_KERNEL_TILE = 4,     /* tcgen05 kind::i8 / TMEM tiles with the weights as the M operand, stream-K over persistent
+                                CTAs, 3 rows and more; selectable, not chosen automatically */
+    SLC_KERNEL_F32 = 5       /* dequant-fused f32 mat-vec of SLC_MATMUL_F32_ACTIVATIONS ops (reported, not selectable) */
 };
 
 typedef struct slc_device slc_device;

@@ -530,7 +530,10 @@ slc_result slc_matmul_create(slc_device *d, slc_weight *w, int64_t max_rows, uin
     if (!d || !w) return fail(SLC_ERR_INVALID_ARGUMENT, "null device or weight");
     if (w->dev != d) return fail(SLC_ERR_INVALID_ARGUMENT, "the weight lives on another device");
     if (max_rows < 1 || max_rows > (1 << 24)) return fail(SLC_ERR_INVALID_ARGUMENT, "max_rows out of range");
-    if (flags & ~(uint32_t)SLC_MATMUL_ROW_INVARIANT) return fail(SLC_ERR_INVALID_ARGUMENT, "unknown flags");
+    if (flags & ~(uint32_t)(SLC_MATMUL_ROW_INVARIANT | SLC_MATMUL_F32_ACTIVATIONS)) return fail(SLC_ERR_INVALID_ARGUMENT, "unknown flags");
+    if ((flags & SLC_MATMUL_F32_ACTIVATIONS) && matvec_f32_rows(w->view.k_pad) == 0) {
+        return fail(SLC_ERR_UNSUPPORTED, "K is too long for the f32-activation mat-vec's shared memory");
+    }
     slc_matmul *op = new (std::nothrow) slc_matmul();
     if (!op) return fail(SLC_ERR_OUT_OF_MEMORY, "host allocation failed");
     op->dev = d; op->w = w; op->max_rows = max_rows; op->flags = flags;
@@ -575,7 +578,7 @@ void slc_matmul_destroy(slc_matmul *op)
 slc_result slc_matmul_set_kernel(slc_matmul *op, int32_t kernel)
 {
     if (!op) return fail(SLC_ERR_INVALID_ARGUMENT, "op is null");
-    if (kernel < SLC_KERNEL_AUTO || kernel > SLC_KERNEL_TILE) return fail(SLC_ERR_INVALID_ARGUMENT, "unknown kernel family");
+    if (kernel < SLC_KERNEL_AUTO || kernel > SLC_KERNEL_TILE) return fail(SLC_ERR_INVALID_ARGUMENT, "unknown or not selectable kernel family");
     if (kernel == SLC_KERNEL_TILE && !umma_supports(op->w->fmt)) {
         return fail(SLC_ERR_UNSUPPORTED, "the tile kernel does not take this weight format");
     }
@@ -624,6 +627,7 @@ static slc_result run_family(slc_matmul *op, const WeightView &wv, const WeightV
 static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, long long y_stride, int *dump,
                               cudaStream_t s, const Exchange *ex = nullptr, const Epilogue *ep = nullptr)
 {
+    if (op->flags & SLC_MATMUL_F32_ACTIVATIONS) return fail(SLC_ERR_INVALID_STATE, "this op keeps f32 activations: it takes no quantized ones");
     const ActView av = view_of(act);
     const int rows = act->rows;
     const int kernel = choose_kernel(op, rows, ex != nullptr);
@@ -706,6 +710,7 @@ static slc_result run_family(slc_matmul *op, const WeightView &wv, const WeightV
 slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act, float *y, int64_t y_stride, void *stream)
 {
     if (!op || !act) return fail(SLC_ERR_INVALID_ARGUMENT, "null op or activation");
+    if (op->flags & SLC_MATMUL_F32_ACTIVATIONS) return fail(SLC_ERR_INVALID_STATE, "this op keeps f32 activations: it takes no quantized ones and does not sum over ranks");
     if (act->dev != op->dev) return fail(SLC_ERR_INVALID_ARGUMENT, "the activation lives on another device");
     if (act->k != op->w->k) return fail(SLC_ERR_INVALID_ARGUMENT, "activation K differs from the weight's K");
     if (act->rows > op->max_rows) return fail(SLC_ERR_INVALID_STATE, "rows exceed the op's compiled bound");
@@ -749,6 +754,7 @@ slc_result slc_matmul_run_quantized_epilogue(slc_matmul *op, slc_activation *act
                                              void *stream)
 {
     if (!op || !act) return fail(SLC_ERR_INVALID_ARGUMENT, "null op or activation");
+    if (op->flags & SLC_MATMUL_F32_ACTIVATIONS) return fail(SLC_ERR_INVALID_STATE, "this op keeps f32 activations: it takes no quantized ones and does not sum over ranks");
     if (act->dev != op->dev || (x && x->dev != op->dev)) return fail(SLC_ERR_INVALID_ARGUMENT, "op, activation and exchange live on different devices");
     if (act->k != op->w->k) return fail(SLC_ERR_INVALID_ARGUMENT, "activation K differs from the weight's K");
     if (act->rows > op->max_rows) return fail(SLC_ERR_INVALID_STATE, "rows exceed the op's compiled bound");
@@ -916,6 +922,7 @@ slc_result slc_matmul_run_quantized_allreduce(slc_matmul *op, slc_activation *ac
                                               int64_t y_stride, void *stream)
 {
     if (!op || !act || !x) return fail(SLC_ERR_INVALID_ARGUMENT, "null op, activation or exchange");
+    if (op->flags & SLC_MATMUL_F32_ACTIVATIONS) return fail(SLC_ERR_INVALID_STATE, "this op keeps f32 activations: it takes no quantized ones and does not sum over ranks");
     if (act->dev != op->dev || x->dev != op->dev) return fail(SLC_ERR_INVALID_ARGUMENT, "op, activation and exchange live on different devices");
     if (act->k != op->w->k) return fail(SLC_ERR_INVALID_ARGUMENT, "activation K differs from the weight's K");
     if (act->rows > op->max_rows) return fail(SLC_ERR_INVALID_STATE, "rows exceed the op's compiled bound");
@@ -979,8 +986,22 @@ slc_result slc_matmul_run(slc_matmul *op, const void *x, int32_t x_dtype, int64_
     if (n == 0) return SLC_OK;
     float *y_dev = y_is_device ? y : op->y_stage;
     const long long ys = y_is_device ? y_stride : n;
-    r = quantize_and_run(op, nullptr, x_dev, x_dtype, rows, xs, y_dev, ys, s);
-    if (r != SLC_OK) return r;
+    if (op->flags & SLC_MATMUL_F32_ACTIVATIONS) {
+        // the node keeps f32 activation math: no quantization, the dequant-fused f32 mat-vec in chunks of rows (every row
+        // is computed the same way whatever the chunking)
+        const int chunk = matvec_f32_rows(op->w->view.k_pad);
+        op->last_kernel = SLC_KERNEL_F32;
+        op->last_launches = 0;
+        for (int64_t r0 = 0; r0 < rows; r0 += chunk) {
+            const int m = (int)(rows - r0 < chunk ? rows - r0 : chunk);
+            SLC_CUDA(launch_matvec_f32(op->w->view, x_dev, x_dtype, xs, (int)r0, m, y_dev, ys, s, nullptr));
+            op->last_launches++;
+        }
+        op->last_launches_total = op->last_launches;
+    } else {
+        r = quantize_and_run(op, nullptr, x_dev, x_dtype, rows, xs, y_dev, ys, s);
+        if (r != SLC_OK) return r;
+    }
     if (!y_is_device) {
         SLC_CUDA(cudaMemcpy2DAsync(y, (size_t)y_stride * 4, y_dev, (size_t)n * 4, (size_t)n * 4, (size_t)rows,
                                    cudaMemcpyDeviceToHost, s));
@@ -993,6 +1014,7 @@ slc_result slc_matmul_run_allreduce(slc_matmul *op, slc_tp_exchange *x, const vo
                                     int64_t x_stride, float *y, int64_t y_stride, void *stream)
 {
     if (!op || !x) return fail(SLC_ERR_INVALID_ARGUMENT, "null op or exchange");
+    if (op->flags & SLC_MATMUL_F32_ACTIVATIONS) return fail(SLC_ERR_INVALID_STATE, "this op keeps f32 activations: it takes no quantized ones and does not sum over ranks");
     if (x->dev != op->dev) return fail(SLC_ERR_INVALID_ARGUMENT, "op and exchange live on different devices");
     if (x_dtype != SLC_F32 && x_dtype != SLC_BF16) return fail(SLC_ERR_UNSUPPORTED, "activation dtype must be f32 or bf16");
     if (rows < 0) return fail(SLC_ERR_INVALID_ARGUMENT, "rows < 0");

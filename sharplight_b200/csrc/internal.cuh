@@ -128,6 +128,11 @@ cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int r
 cudaError_t launch_gate_mul(const float *g, long long g_stride, float *y, long long y_stride, int rows, int n,
                             cudaStream_t stream);
 
+// matvec_f32.cu: dequant-fused f32 mat-vec for ops that keep f32 activation math; rows: 1 .. matvec_f32_rows(k_pad).
+int matvec_f32_rows(int k_pad);
+cudaError_t launch_matvec_f32(const WeightView &w, const void *x, int x_dtype, long long x_stride, int row0, int rows, float *y,
+                              long long y_stride, cudaStream_t stream, const Epilogue *epilogue = nullptr);
+
 // producers.cu: kernels that produce the quantized activations in the same pass as the operation in front of the MatMul
 // (y, optional: the f32 result as well), and the arg-max behind the lm_head.
 cudaError_t launch_rmsnorm_quantize(const void *x, int x_dtype, int rows, int rows_pad, int k, int k_pad, long long x_stride,

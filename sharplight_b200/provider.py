@@ -292,9 +292,10 @@ class CudaDevice:
             return OpSupport.no("int_dot is disabled and this provider has no float path")
         # a node may opt out of 8-bit activations (StandardOps.cs:130-135); the reference then runs its f32-activation
         # path unless reduced precision is allowed (GraphLowerer.IntDot.cs:61-62, CpuCompiledSegment.LowerLinear.cs:39).
-        # This provider has only the integer-dot path, so such a node goes to the placement fallback.
-        if node.f32_activations and not self.allow_reduced_precision:
-            return OpSupport.no("f32 activations requested and this provider only has the 8-bit activation path")
+        # Here such a node runs the dequant-fused f32 mat-vec (never silently quantized), which keeps one activation row
+        # of K f32 values in shared memory: K beyond that goes to the placement fallback.
+        if node.f32_activations and not self.allow_reduced_precision and node.weight.shape[1] > F32_ACTIVATIONS_MAX_K:
+            return OpSupport.no(f"f32 activations requested and K={node.weight.shape[1]} exceeds the f32 mat-vec's {F32_ACTIVATIONS_MAX_K}")
         return OpSupport.yes()
 
     def _supports_ignoring_f32(self, node: "MatMulNode") -> bool:
@@ -353,17 +354,21 @@ def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
     return (b.astype(np.uint32) << 16).view(np.float32)
 
 
+F32_ACTIVATIONS_MAX_K = 49152   # one f32 activation row in 200 KB of shared memory (matvec_f32.cu), less the reduction area
+
+
 class MatMulOp:
     """y = x . W^T for activation rows x and a quantized weight W [N, K] (src/Sharplight.Cpu/MatMulOp.cs:88-160),
     on the integer-dot path at every row count."""
 
     def __init__(self, device: CudaDevice, weight: DeviceWeight, max_rows: int, *, row_invariant: bool = False,
-                 up: Optional[DeviceWeight] = None):
+                 up: Optional[DeviceWeight] = None, f32_activations: bool = False):
         """``up``: a second weight of the same shape; the op then computes silu(x . weight^T) * (x . up^T), the gated
-        FFN's gate / up pair as one MatMul (slc_matmul_create_dual)."""
+        FFN's gate / up pair as one MatMul (slc_matmul_create_dual). ``f32_activations``: the activations are never
+        quantized; ``run`` / ``run_pointers`` use the dequant-fused f32 mat-vec (SLC_MATMUL_F32_ACTIVATIONS)."""
         self.device, self.weight, self.max_rows, self.up = device, weight, max_rows, up
         h = C.c_void_p()
-        flags = N.MATMUL_ROW_INVARIANT if row_invariant else N.MATMUL_DEFAULT
+        flags = (N.MATMUL_ROW_INVARIANT if row_invariant else N.MATMUL_DEFAULT) | (N.MATMUL_F32_ACTIVATIONS if f32_activations else 0)
         if up is None:
             _check(N.load().slc_matmul_create(device.handle, weight.handle, max_rows, flags, C.byref(h)))
         else:
@@ -595,6 +600,7 @@ class CudaSegment:
         self._rows: Dict[str, int] = {}
         self._ops: Dict[str, MatMulOp] = {}
         self._weights: List[DeviceWeight] = []
+        self._f32_nodes: set = set()   # nodes that keep f32 activation math (never quantized)
         lib = N.load()
         mr = options.max_rows
         row_inv = options.row_invariant_rows > 0
@@ -608,7 +614,10 @@ class CudaSegment:
             if w is None:
                 w = device.upload_weight(node.weight.type, node.weight.shape, node.weight.blocks)
                 self._weights.append(w)
-            self._ops[node.name] = MatMulOp(device, w, mr, row_invariant=row_inv)
+            f32 = node.f32_activations and not (device.allow_reduced_precision or options.allow_reduced_precision)
+            self._ops[node.name] = MatMulOp(device, w, mr, row_invariant=row_inv and not f32, f32_activations=f32)
+            if f32:
+                self._f32_nodes.add(node.name)
             self._shape.setdefault(node.x, (w.k, 2 if node.x_dtype == "bf16" else 4))
             self._shape[node.y] = (w.n, 4)
         # device buffers for every value; page-locked staging for inputs and outputs
@@ -623,7 +632,8 @@ class CudaSegment:
             self._out_offset[v] = off
             off += mr * self._shape[v][0] * 4
         self._out_stage = _Pinned(off)
-        self._acts = {v: SharedActivation(device, mr, self._shape[v][0]) for v in {n.x for n in segment.nodes}}
+        self._acts = {v: SharedActivation(device, mr, self._shape[v][0])
+                      for v in {n.x for n in segment.nodes if n.name not in self._f32_nodes}}
         # output copies travel on a second stream beside the kernels; per row-count signature: None -> issued once
         # from the host, 1 -> issued twice (every kernel configured), then the captured graph
         self._copy_stream = C.c_void_p()
@@ -718,10 +728,13 @@ class CudaSegment:
             if node.x not in rows_of:
                 raise InvalidOperationError(f"input '{node.x}' was never set")
             rows = rows_of[node.x] if t is None else min(t, rows_of[node.x])
-            if node.x not in quantized:
-                plan.append(("quantize", node, rows))
-                quantized.add(node.x)
-            plan.append(("matmul", node, rows))
+            if node.name in self._f32_nodes:
+                plan.append(("matmul_f32", node, rows))
+            else:
+                if node.x not in quantized:
+                    plan.append(("quantize", node, rows))
+                    quantized.add(node.x)
+                plan.append(("matmul", node, rows))
             rows_of[node.y] = rows
             quantized.discard(node.y)
         self._out_rows = {v: rows_of[v] for v in self.segment.outputs}
@@ -758,7 +771,13 @@ class CudaSegment:
                 dtype = N.BF16 if node.x_dtype == "bf16" else N.F32
                 self._acts[node.x].quantize(self._dev[node.x].value, dtype, rows, self._shape[node.x][0], 0)
                 continue
-            if node.name in self._reduce:
+            if kind == "matmul_f32":
+                if node.name in self._reduce:
+                    raise NotSupportedError("an f32-activation MatMul does not sum over ranks")
+                dtype = N.BF16 if node.x_dtype == "bf16" else N.F32
+                self._ops[node.name].run_pointers(self._dev[node.x].value, dtype, rows, self._shape[node.x][0], True,
+                                                  self._dev[node.y].value, self._shape[node.y][0], True, 0)
+            elif node.name in self._reduce:
                 self.options.exchange.matmul(self._ops[node.name], self._acts[node.x], self._dev[node.y].value,
                                              self._shape[node.y][0], 0)
             else:

@@ -113,13 +113,16 @@ def test_supports_mirrors_the_quantized_matmul_check():
 def test_supports_honours_the_f32_activation_opt_out():
     """A MatMul node may opt out of 8-bit activations (src/Sharplight.Core/Graph/StandardOps.cs:130-135); the reference
     then keeps f32 activations unless reduced precision is allowed (src/Sharplight.Shaders/Lowering/
-    GraphLowerer.IntDot.cs:61-62, src/Sharplight.Cpu/CpuCompiledSegment.LowerLinear.cs:39). This provider only has the
-    8-bit path: the node is refused (and goes to the placement fallback), never silently quantized."""
+    GraphLowerer.IntDot.cs:61-62, src/Sharplight.Cpu/CpuCompiledSegment.LowerLinear.cs:39). Such a node is taken for the
+    dequant-fused f32 mat-vec (never silently quantized), as long as one f32 activation row fits that kernel's shared
+    memory; beyond that it is refused and goes to the placement fallback."""
     blocks = np.zeros(34, np.uint8)
     node = P.MatMulNode("m", "x", P.WeightInfo("Q8_0", (1, 32), blocks), "y", f32_activations=True)
-    no = _bare_device().supports(node)
+    assert _bare_device().supports(node).supported
+    long_k = P.MatMulNode("m", "x", P.WeightInfo("Q8_0", (1, 65536), None), "y", f32_activations=True)
+    no = _bare_device().supports(long_k)
     assert not no.supported and "f32 activations" in no.reason
-    assert _bare_device(allow_reduced_precision=True).supports(node).supported
+    assert _bare_device(allow_reduced_precision=True).supports(long_k).supported
 
 
 def test_bf16_helpers_round_trip():

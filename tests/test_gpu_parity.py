@@ -11,7 +11,7 @@ import pytest
 
 from helpers import FMT_OF, MAX_REL, max_rel_error, relative_rms, sl_oracle
 from sharplight_b200 import (ArgumentError, CompileOptions, GraphSegment, InvalidOperationError, MatMulNode, MatMulOp,
-                             NotSupportedError, ObjectDisposedError, WeightInfo, synth)
+                             NotSupportedError, ObjectDisposedError, SharedActivation, WeightInfo, synth)
 from sharplight_b200 import native as N
 from sharplight_b200.provider import bf16_bits_to_f32, to_bf16_bits
 from test_oracle import quantize_kat
@@ -587,3 +587,58 @@ def test_skinny_k_chunks(cuda_device, type_name, n, k, rows):
     assert kern[0] == N.KERNEL_SKINNY and cuda_device.last_status() == 0
     # twice in a row: the arrival counters are back at zero
     check_matmul(cuda_device, type_name, n, k, rows, seed=n + rows + 1, kernel=N.KERNEL_SKINNY, dots=False)
+
+
+# ---- f32 activations kept: the dequant-fused f32 mat-vec ---------------------------------------------------------------
+
+@pytest.mark.parametrize("type_name", TYPES)
+@pytest.mark.parametrize("n,k,rows", [(40, 256, 1), (100, 1024, 3), (33, 4096, 4), (7, 2560, 9), (4112, 512, 2)])
+def test_f32_activation_matvec(cuda_device, type_name, n, k, rows):
+    """An op that keeps f32 activation math against the exact product of the dequantized weight (the oracle's f64
+    MatMul), at the tolerance the reference holds its f32 paths to (atol 2e-3, rtol 1e-4,
+    tests/Sharplight.Cpu.Tests/QuantTests.cs:257-265) -- far tighter than 8-bit activations could meet."""
+    blocks = synth.weight_blocks(type_name, n, k, seed=n + k)
+    x = synth.activations(rows, k, seed=rows + k)
+    w = cuda_device.upload_weight(type_name, (n, k), blocks)
+    op = MatMulOp(cuda_device, w, rows, f32_activations=True)
+    try:
+        y = op.run(x)
+        exact = sl_oracle.matmul_f64(FMT_OF[type_name], blocks, n, k, x, threads=4)
+        assert np.all(np.abs(y - exact) <= 2e-3 + 1e-4 * np.abs(exact)), float(np.max(np.abs(y - exact)))
+        assert op.last_kernel()[0] == N.KERNEL_F32
+        bits = to_bf16_bits(x)
+        yb = op.run(bits, N.BF16)
+        exact_b = sl_oracle.matmul_f64(FMT_OF[type_name], blocks, n, k, bf16_bits_to_f32(bits), threads=4)
+        assert np.all(np.abs(yb - exact_b) <= 2e-3 + 1e-4 * np.abs(exact_b))
+        # such an op takes no quantized activations
+        act = SharedActivation(cuda_device, rows, k)
+        try:
+            with pytest.raises(Exception):
+                act.matmul(op, 0, n)
+        finally:
+            act.dispose()
+    finally:
+        op.dispose()
+        w.dispose()
+
+
+def test_f32_activation_node_in_a_segment(cuda_device):
+    """A segment with one node that keeps f32 activations and one that does not, reading the same input."""
+    from sharplight_b200 import CompileOptions, GraphSegment, MatMulNode, WeightInfo
+    n, k, rows = 64, 1024, 3
+    b1, b2 = synth.weight_blocks("Q4_K", n, k, 1), synth.weight_blocks("Q8_0", n, k, 2)
+    x = synth.activations(rows, k, 3)
+    nodes = [MatMulNode("a", "x", WeightInfo("Q4_K", (n, k), b1), "ya", f32_activations=True),
+             MatMulNode("b", "x", WeightInfo("Q8_0", (n, k), b2), "yb")]
+    seg = cuda_device.compile(GraphSegment(nodes, ["x"], ["ya", "yb"]), CompileOptions(max_rows=4))
+    try:
+        for _ in range(4):      # direct launches, then the captured graph
+            seg.set_input("x", x)
+            seg.execute({"T": rows})
+            ya, yb = seg.get_output("ya"), seg.get_output("yb")
+            exact = sl_oracle.matmul_f64(FMT_OF["Q4_K"], b1, n, k, x, threads=4)
+            assert np.all(np.abs(ya - exact) <= 2e-3 + 1e-4 * np.abs(exact))
+            ref, _, _ = sl_oracle.matmul_intdot(FMT_OF["Q8_0"], b2, n, k, x, threads=4)
+            assert max_rel_error(yb, ref) <= MAX_REL
+    finally:
+        seg.dispose()
