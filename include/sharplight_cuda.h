@@ -158,6 +158,13 @@ SLC_API slc_result slc_host_alloc(int64_t bytes, void **out_host_ptr);
 SLC_API void slc_host_free(void *host_ptr);
 SLC_API slc_result slc_buffer_copy_async(slc_device *device, void *dst, const void *src, int64_t bytes, int32_t direction,
                                          void *stream);
+/* A strided device view made dense: dst[z][r][c] = src[z * batch_stride + r * row_stride + c * col_stride] (strides in
+   elements of elem_bytes = 2 or 4; dst is [batch][rows][cols], contiguous). slc_matmul_run and slc_activation_quantize take rows that are x_stride apart and start at any element, so a
+   Slice or a row-splitting Reshape in front of a MatMul is only a pointer and a stride; a Permute's rows are not
+   contiguous and come through here first (src/Sharplight.Shaders/Lowering/GraphLowerer.MatMul.cs:117-126). */
+SLC_API slc_result slc_buffer_densify(slc_device *device, void *dst_device, const void *src_device, int64_t batch, int64_t rows,
+                                      int64_t cols, int64_t batch_stride, int64_t row_stride, int64_t col_stride,
+                                      int32_t elem_bytes, void *stream);
 
 /* ---- side streams and captured step graphs: a segment's Execute captured once per row count and replayed with one
         call, its output copies on a second stream beside the kernels (the CUDA form of a command buffer that is

@@ -2,8 +2,8 @@
 over the C ABI of libsharplight_cuda.so. Build the library with ``python -m sharplight_b200.build``."""
 from .provider import (ArgumentError, CompileOptions, CudaDevice, CudaExecutionProvider, CudaSegment, DeviceInfo,
                        DeviceWeight, GraphSegment, InvalidOperationError, MatMulNode, MatMulOp, NotSupportedError,
-                       ObjectDisposedError, OpSupport, SharedActivation, TpComm, TpExchange, WeightInfo)
+                       ObjectDisposedError, OpSupport, SharedActivation, TpComm, TpExchange, ViewNode, WeightInfo)
 
 __all__ = ["ArgumentError", "CompileOptions", "CudaDevice", "CudaExecutionProvider", "CudaSegment", "DeviceInfo",
            "DeviceWeight", "GraphSegment", "InvalidOperationError", "MatMulNode", "MatMulOp", "NotSupportedError",
-           "ObjectDisposedError", "OpSupport", "SharedActivation", "TpComm", "TpExchange", "WeightInfo"]
+           "ObjectDisposedError", "OpSupport", "SharedActivation", "TpComm", "TpExchange", "ViewNode", "WeightInfo"]

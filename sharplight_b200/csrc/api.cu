@@ -261,6 +261,21 @@ slc_result slc_buffer_copy_async(slc_device *d, void *dst, const void *src, int6
     return SLC_OK;
 }
 
+slc_result slc_buffer_densify(slc_device *d, void *dst, const void *src, int64_t batch, int64_t rows, int64_t cols,
+                              int64_t batch_stride, int64_t row_stride, int64_t col_stride, int32_t elem_bytes, void *stream)
+{
+    if (!d || batch < 0 || batch > 65535 || rows < 0 || cols < 0 || rows > (1 << 24) || cols > (1 << 30)) {
+        return fail(SLC_ERR_INVALID_ARGUMENT, "bad densify request (batch <= 65535)");
+    }
+    if (elem_bytes != 2 && elem_bytes != 4) return fail(SLC_ERR_UNSUPPORTED, "elements of 2 or 4 bytes");
+    if (batch == 0 || rows == 0 || cols == 0) return SLC_OK;
+    if (!dst || !src || batch_stride < 0 || row_stride < 0 || col_stride < 0) return fail(SLC_ERR_INVALID_ARGUMENT, "null pointer or negative stride");
+    SLC_CUDA(cudaSetDevice(d->index));
+    SLC_CUDA(launch_densify(dst, src, (int)batch, (int)rows, (int)cols, batch_stride, row_stride, col_stride, elem_bytes,
+                            stream ? (cudaStream_t)stream : d->stream));
+    return SLC_OK;
+}
+
 // ---- weights ---------------------------------------------------------------------------------------------------------
 
 static slc_result check_weight_args(slc_device *d, int32_t fmt, int64_t n, int64_t k, const void *blocks, int64_t bytes)

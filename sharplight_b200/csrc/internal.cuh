@@ -128,6 +128,10 @@ cudaError_t launch_matvec(const WeightView &w, const ActView &a, int row0, int r
 cudaError_t launch_gate_mul(const float *g, long long g_stride, float *y, long long y_stride, int rows, int n,
                             cudaStream_t stream);
 
+// gate.cu: dst[z][r][c] = src[z * batch_stride + r * row_stride + c * col_stride], dense, elements of 2 or 4 bytes.
+cudaError_t launch_densify(void *dst, const void *src, int batch, int rows, int cols, long long batch_stride, long long row_stride,
+                           long long col_stride, int elem_bytes, cudaStream_t stream);
+
 // matvec_f32.cu: dequant-fused f32 mat-vec for ops that keep f32 activation math; rows: 1 .. matvec_f32_rows(k_pad).
 int matvec_f32_rows(int k_pad);
 cudaError_t launch_matvec_f32(const WeightView &w, const void *x, int x_dtype, long long x_stride, int row0, int rows, float *y,

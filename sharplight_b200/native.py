@@ -90,6 +90,7 @@ SIGNATURES = {
     "slc_activation_quantize": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp]),
     "slc_activation_quantize_rmsnorm": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp, C.c_float, _vp, _i64, _vp]),
     "slc_activation_quantize_silu_mul": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _vp]),
+    "slc_buffer_densify": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "slc_argmax_rows": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "slc_matmul_run_quantized": (_i32, [_vp, _vp, _vp, _i64, _vp]),
     "slc_tp_exchange_create": (_i32, [_vp, _i32, _i32, _i64, _i64, _P(_vp), _vp]),

@@ -125,8 +125,31 @@ class MatMulNode:
 
 
 @dataclass
+class ViewNode:
+    """A node of OpCategory.View in front of a MatMul (Reshape, Slice, Permute: src/Sharplight.Core/Graph/StandardOps.cs:61,68,89).
+    The placement planner does not ask providers about such nodes, they stay on their group's device
+    (src/Sharplight.Core/Runtime/PlacementPlanner.cs:238), so the segment has to take them. x is a [T, x_cols] value.
+      kind "slice":   y = x[:, start : start + length]                      -- a pointer and a row stride, nothing moves
+      kind "reshape": y = x seen as [T * split, x_cols / split]             -- the same bytes, more and shorter rows
+      kind "permute": y[t] = x[t] seen as [a, b] and transposed to [b, a]   -- rows are no longer runs of memory: gathered
+                      into a dense buffer first, as the reference's lowering densifies such an input
+                      (src/Sharplight.Shaders/Lowering/GraphLowerer.MatMul.cs:117-126)"""
+    name: str
+    x: str
+    y: str
+    kind: str
+    x_cols: int
+    dtype: str = "f32"
+    start: int = 0
+    length: int = 0
+    split: int = 1
+    a: int = 0
+    b: int = 0
+
+
+@dataclass
 class GraphSegment:
-    nodes: List[MatMulNode]
+    nodes: List[object]          # MatMulNode and ViewNode, in execution order
     inputs: List[str]
     outputs: List[str]
 
@@ -320,6 +343,8 @@ class CudaDevice:
 
     def compile(self, segment: GraphSegment, options: CompileOptions) -> "CudaSegment":
         for node in segment.nodes:
+            if isinstance(node, ViewNode):
+                continue
             s = self.supports(node)
             if not s.supported and not (isinstance(node, MatMulNode) and node.f32_activations and options.allow_reduced_precision
                                         and self._supports_ignoring_f32(node)):
@@ -606,34 +631,50 @@ class CudaSegment:
         row_inv = options.row_invariant_rows > 0
         # value name -> (columns, element bytes)
         self._shape: Dict[str, tuple] = {}
-        self._reduce = {node.name for node in segment.nodes if node.allreduce}
+        self._reduce = {node.name for node in segment.nodes if isinstance(node, MatMulNode) and node.allreduce}
         if self._reduce and options.exchange is None:
             raise ArgumentError("a segment with allreduce nodes needs CompileOptions.exchange")
+        # views: value -> (the value whose buffer it lives in, element offset, row stride in elements, rows per T)
+        self._alias: Dict[str, tuple] = {}
+        self._row_mult: Dict[str, int] = {}
         for node in segment.nodes:
+            if isinstance(node, ViewNode):
+                self._lower_view(node)
+                continue
             w = node.weight.resident
             if w is None:
                 w = device.upload_weight(node.weight.type, node.weight.shape, node.weight.blocks)
                 self._weights.append(w)
             f32 = node.f32_activations and not (device.allow_reduced_precision or options.allow_reduced_precision)
-            self._ops[node.name] = MatMulOp(device, w, mr, row_invariant=row_inv and not f32, f32_activations=f32)
+            mult = self._row_mult.get(node.x, 1)
+            self._ops[node.name] = MatMulOp(device, w, mr * mult, row_invariant=row_inv and not f32, f32_activations=f32)
             if f32:
                 self._f32_nodes.add(node.name)
-            self._shape.setdefault(node.x, (w.k, 2 if node.x_dtype == "bf16" else 4))
+            esz = 2 if node.x_dtype == "bf16" else 4
+            if node.x in self._shape and self._shape[node.x] != (w.k, esz):
+                raise ArgumentError(f"{node.name}: input '{node.x}' is [T, {self._shape[node.x][0]}], the weight wants K={w.k}")
+            self._shape.setdefault(node.x, (w.k, esz))
             self._shape[node.y] = (w.n, 4)
-        # device buffers for every value; page-locked staging for inputs and outputs
+            self._row_mult[node.y] = mult
+        for v in segment.outputs:
+            if v in self._alias:
+                raise NotSupportedError(f"output '{v}' is a view of another value: read that value instead")
+        # device buffers for every value that owns its bytes; page-locked staging for inputs and outputs
         self._dev: Dict[str, C.c_void_p] = {}
         for name, (cols, esz) in self._shape.items():
+            if name in self._alias:
+                continue
             p = C.c_void_p()
-            _check(lib.slc_buffer_alloc(device.handle, mr * cols * esz, C.byref(p)))
+            _check(lib.slc_buffer_alloc(device.handle, mr * self._row_mult.get(name, 1) * cols * esz, C.byref(p)))
             self._dev[name] = p
         self._in_stage = {v: _Pinned(mr * self._shape[v][0] * self._shape[v][1]) for v in segment.inputs}
         self._out_offset, off = {}, 0
         for v in segment.outputs:
             self._out_offset[v] = off
-            off += mr * self._shape[v][0] * 4
+            off += mr * self._row_mult.get(v, 1) * self._shape[v][0] * 4
         self._out_stage = _Pinned(off)
-        self._acts = {v: SharedActivation(device, mr, self._shape[v][0])
-                      for v in {n.x for n in segment.nodes if n.name not in self._f32_nodes}}
+        self._acts = {v: SharedActivation(device, mr * self._row_mult.get(v, 1), self._shape[v][0])
+                      for v in {n.x for n in segment.nodes if isinstance(n, MatMulNode) and n.name not in self._f32_nodes}}
         # output copies travel on a second stream beside the kernels; per row-count signature: None -> issued once
         # from the host, 1 -> issued twice (every kernel configured), then the captured graph
         self._copy_stream = C.c_void_p()
@@ -643,10 +684,47 @@ class CudaSegment:
         self._forward: Dict[str, "CudaSegment"] = {}   # input value -> the segment whose output it is read from
         self._device_only: set = set()                 # outputs nobody reads on the host: not copied back
 
+    def _lower_view(self, node: "ViewNode") -> None:
+        esz = 2 if node.dtype == "bf16" else 4
+        if node.x in self._shape and self._shape[node.x] != (node.x_cols, esz):
+            raise ArgumentError(f"{node.name}: '{node.x}' is [T, {self._shape[node.x][0]}], not [T, {node.x_cols}]")
+        self._shape.setdefault(node.x, (node.x_cols, esz))
+        self._row_mult.setdefault(node.x, 1)
+        root, off, stride, mult = self._alias.get(node.x, (node.x, 0, node.x_cols, self._row_mult[node.x]))
+        if node.kind == "slice":
+            if node.start < 0 or node.length < 1 or node.start + node.length > node.x_cols:
+                raise ArgumentError(f"{node.name}: slice [{node.start}, {node.start + node.length}) of {node.x_cols} columns")
+            self._alias[node.y] = (root, off + node.start, stride, mult)
+            self._shape[node.y] = (node.length, esz)
+            self._row_mult[node.y] = mult
+        elif node.kind == "reshape":
+            if node.split < 1 or node.x_cols % node.split != 0:
+                raise ArgumentError(f"{node.name}: {node.x_cols} columns do not split in {node.split} rows")
+            if stride != node.x_cols:
+                raise NotSupportedError(f"{node.name}: a row-splitting reshape of a column slice (rows are not contiguous)")
+            cols = node.x_cols // node.split
+            self._alias[node.y] = (root, off, cols, mult * node.split)
+            self._shape[node.y] = (cols, esz)
+            self._row_mult[node.y] = mult * node.split
+        elif node.kind == "permute":
+            if node.a < 1 or node.b < 1 or node.a * node.b != node.x_cols:
+                raise ArgumentError(f"{node.name}: [{node.a}, {node.b}] is not {node.x_cols} columns")
+            self._shape[node.y] = (node.x_cols, esz)      # a buffer of its own, filled by the gather
+            self._row_mult[node.y] = mult
+        else:
+            raise NotSupportedError(f"{node.name}: view kind '{node.kind}'")
+
+    def _where(self, value: str):
+        """(device address, row stride in elements) of a value: its own buffer, or the place inside another one."""
+        if value in self._alias:
+            root, off, stride, _ = self._alias[value]
+            return self._dev[root].value + off * self._shape[value][1], stride
+        return self._dev[value].value, self._shape[value][0]
+
     @property
     def device_memory_bytes(self) -> int:
         return sum(w.device_bytes for w in self._weights) + \
-            sum(self.options.max_rows * c * e for c, e in self._shape.values())
+            sum(self.options.max_rows * self._row_mult.get(n, 1) * c * e for n, (c, e) in self._shape.items() if n not in self._alias)
 
     def _live(self):
         if self._disposed:
@@ -727,7 +805,14 @@ class CudaSegment:
         for node in self.segment.nodes:
             if node.x not in rows_of:
                 raise InvalidOperationError(f"input '{node.x}' was never set")
-            rows = rows_of[node.x] if t is None else min(t, rows_of[node.x])
+            if isinstance(node, ViewNode):
+                rows_of[node.y] = rows_of[node.x] * (node.split if node.kind == "reshape" else 1)
+                if node.kind == "permute":
+                    plan.append(("densify", node, rows_of[node.x] if t is None else min(t * self._row_mult[node.x], rows_of[node.x])))
+                    quantized.discard(node.y)
+                continue
+            mult = self._row_mult.get(node.x, 1)
+            rows = rows_of[node.x] if t is None else min(t * mult, rows_of[node.x])
             if node.name in self._f32_nodes:
                 plan.append(("matmul_f32", node, rows))
             else:
@@ -767,15 +852,22 @@ class CudaSegment:
         outputs = set(self.segment.outputs)
         copied = False
         for kind, node, rows in plan:
+            if kind == "densify":
+                src, stride = self._where(node.x)
+                _check(lib.slc_buffer_densify(self.device.handle, self._dev[node.y], C.c_void_p(src), rows, node.b, node.a,
+                                              stride, 1, node.b, self._shape[node.y][1], None))
+                continue
             if kind == "quantize":
                 dtype = N.BF16 if node.x_dtype == "bf16" else N.F32
-                self._acts[node.x].quantize(self._dev[node.x].value, dtype, rows, self._shape[node.x][0], 0)
+                src, stride = self._where(node.x)
+                self._acts[node.x].quantize(src, dtype, rows, stride, 0)
                 continue
             if kind == "matmul_f32":
                 if node.name in self._reduce:
                     raise NotSupportedError("an f32-activation MatMul does not sum over ranks")
                 dtype = N.BF16 if node.x_dtype == "bf16" else N.F32
-                self._ops[node.name].run_pointers(self._dev[node.x].value, dtype, rows, self._shape[node.x][0], True,
+                src, stride = self._where(node.x)
+                self._ops[node.name].run_pointers(src, dtype, rows, stride, True,
                                                   self._dev[node.y].value, self._shape[node.y][0], True, 0)
             elif node.name in self._reduce:
                 self.options.exchange.matmul(self._ops[node.name], self._acts[node.x], self._dev[node.y].value,

@@ -642,3 +642,44 @@ def test_f32_activation_node_in_a_segment(cuda_device):
             assert max_rel_error(yb, ref) <= MAX_REL
     finally:
         seg.dispose()
+
+
+# ---- view nodes in front of a MatMul: Slice and Reshape are a pointer and a stride, Permute is gathered first -------------
+
+def test_views_in_front_of_matmuls(cuda_device):
+    from sharplight_b200 import ViewNode
+    rows = 5
+    x = synth.activations(rows, 3074, 11)          # sliced at an odd column: rows that start at any element
+    z = synth.activations(rows, 1024, 12)
+    w1 = synth.weight_blocks("Q4_K", 48, 2048, 1)
+    w2 = synth.weight_blocks("Q8_0", 40, 1024, 2)
+    w3 = synth.weight_blocks("Q6_K", 24, 1024, 3)
+    nodes = [ViewNode("v1", "x", "xs", "slice", 3074, start=1025, length=2048),
+             MatMulNode("m1", "xs", WeightInfo("Q4_K", (48, 2048), w1), "y1"),
+             ViewNode("v2", "z", "zr", "reshape", 1024, split=4),
+             ViewNode("v3", "z", "zp", "permute", 1024, a=4, b=256),
+             MatMulNode("m2", "zp", WeightInfo("Q8_0", (40, 1024), w2), "y2"),
+             MatMulNode("m3", "z", WeightInfo("Q6_K", (24, 1024), w3), "y3")]
+    w4 = synth.weight_blocks("Q4_0", 16, 256, 4)
+    nodes.append(MatMulNode("m4", "zr", WeightInfo("Q4_0", (16, 256), w4), "y4"))      # [4 T, 256] rows out of [T, 1024]
+    seg = cuda_device.compile(GraphSegment(nodes, ["x", "z"], ["y1", "y2", "y3", "y4"]), CompileOptions(max_rows=8))
+    try:
+        for _ in range(4):          # direct launches, then the captured graph
+            seg.set_input("x", x)
+            seg.set_input("z", z)
+            seg.execute({"T": rows})
+            ref, _, _ = sl_oracle.matmul_intdot(FMT_OF["Q4_K"], w1, 48, 2048, np.ascontiguousarray(x[:, 1025:3073]), threads=4)
+            assert max_rel_error(seg.get_output("y1"), ref) <= MAX_REL
+            zp = np.ascontiguousarray(z.reshape(rows, 4, 256).transpose(0, 2, 1).reshape(rows, 1024))
+            ref, _, _ = sl_oracle.matmul_intdot(FMT_OF["Q8_0"], w2, 40, 1024, zp, threads=4)
+            assert max_rel_error(seg.get_output("y2"), ref) <= MAX_REL
+            ref, _, _ = sl_oracle.matmul_intdot(FMT_OF["Q6_K"], w3, 24, 1024, z, threads=4)
+            assert max_rel_error(seg.get_output("y3"), ref) <= MAX_REL
+            ref, _, _ = sl_oracle.matmul_intdot(FMT_OF["Q4_0"], w4, 16, 256, z.reshape(rows * 4, 256), threads=4)
+            y4 = seg.get_output("y4")
+            assert y4.shape == (rows * 4, 16) and max_rel_error(y4, ref) <= MAX_REL
+    finally:
+        seg.dispose()
+    with pytest.raises(Exception):
+        cuda_device.compile(GraphSegment([ViewNode("v", "x", "xs", "slice", 1024, start=1000, length=100)], ["x"], []),
+                            CompileOptions(max_rows=2))
