@@ -180,7 +180,7 @@ cudaError_t launch_mmq(const WeightView &w, const ActView &a, const uint8_t *q_t
 // q_sw / sx2: the tiled planes the quantizer wrote for these rows (rows_pad a multiple of umma_token_tile(rows));
 // scratch (umma_scratch_bytes) and counters (max_ctas ints, zero between launches) serve the tiles whose K range is
 // shared by several CTAs. Launches that use the same scratch must not overlap.
-bool umma_supports(int fmt);
+bool umma_supports(int fmt, int rows);   // Q6_K: more than 64 rows only
 int umma_token_tile(int rows);
 size_t umma_scratch_bytes(int max_ctas, int rows_pad);
 cudaError_t launch_umma(const WeightView &w, const ActView &a, const uint8_t *q_sw, const uint8_t *sx2, float *y,

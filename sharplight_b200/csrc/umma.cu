@@ -41,17 +41,23 @@ template <int FMT, int NT>
 struct UmCfg
 {
     static constexpr bool MINS = FMT == FMT_Q4_K;
+    // Q6_K changes its scale every 16 values: a 32-value block is two MMAs on two copies of the weight rows, one with the
+    // upper and one with the lower sixteen values zero (the same activation codes both times), into two buffers with a
+    // weight scale each (the reference's GEMM does the same, src/Sharplight.Shaders/Kernels/mmq.slang:235-239)
+    static constexpr int GPB = FMT == FMT_Q6_K ? 2 : 1;           // MMAs (scale groups) per 32-value block
+    static constexpr int NB = 8 * GPB;                            // block-dot buffers' worth of work per unit
+    static_assert(FMT != FMT_Q6_K || NT == 128, "Q6_K is served at the 128-token tile only");
     static constexpr int PW = NT <= 32 ? 8 : 4;                   // producer warps (warps 4 .. 4 + PW)
     static constexpr int EG = NT <= 32 ? 2 : 4;                   // epilogue groups of four warps (one warp per 32 rows)
     static constexpr int EPI0 = 4 + PW;                           // first epilogue warp
     static constexpr int CS = NT >= 128 ? 4 : NT == 64 ? 2 : 1;   // column slices of the token tile
     static constexpr int BP = EG / CS;                            // epilogue groups taking blocks in turn
     static constexpr int CW = NT / CS;                            // columns per epilogue warp
-    static constexpr int DB = NT == 128 ? (MINS ? 2 : 4) : NT == 64 ? 4 : 8;   // tensor-memory buffers for block dots
+    static constexpr int DB = NT == 128 ? (MINS ? 2 : 4) : NT == 64 ? 4 : 8;   // tensor-memory buffers for block dots (NB % DB == 0)
     static constexpr int MB = NT == 128 ? 1 : 2;                  // offset-term buffers (Q4_K)
     static constexpr int TM_MINS = DB * NT;                       // first column of the offset-term buffers
     static constexpr int TM_NEED = DB * NT + (MINS ? MB * NT : 0);
-    static_assert(TM_NEED <= 512 && DB % 2 == 0 && 8 % DB == 0, "tensor memory budget; one issuer per buffer");
+    static_assert(TM_NEED <= 512 && DB % 2 == 0 && NB % DB == 0, "tensor memory budget; one issuer per buffer");
     static constexpr int TM_COLS = TM_NEED <= 32 ? 32 : TM_NEED <= 64 ? 64 : TM_NEED <= 128 ? 128 : TM_NEED <= 256 ? 256 : 512;
     // registers per thread after the roles have split; the CTA's pool is 6 warpgroups x 80
     static constexpr int REG_PROD = PW == 8 ? 64 : 56, REG_EPI = EG == 2 ? 136 : 96;
@@ -61,11 +67,12 @@ struct UmCfg
     static constexpr int RAW_SLOT = 8 * REC;
     static constexpr int S = NT == 128 ? 3 : 4;                   // operand stages (128 K-values each: weight rows + code tile)
     static constexpr int B_STAGE = NT * 128;
-    static constexpr int STAGE = UM_A_STAGE + B_STAGE;
+    static constexpr int A_BYTES = GPB * UM_A_STAGE;               // weight rows of a stage (Q6_K: the two half-masked copies)
+    static constexpr int STAGE = A_BYTES + B_STAGE;
     static constexpr int DX_BYTES = 8 * NT * 4;
     static constexpr int SX2_BYTES = MINS ? NT * 64 : 0;
     static constexpr int ACT_SLOT = (DX_BYTES + SX2_BYTES + 511) / 512 * 512;
-    static constexpr int WS_DW = 8 * UM_ROWS * 4;                 // d_w per block and row
+    static constexpr int WS_DW = NB * UM_ROWS * 4;                // d_w per block (Q6_K: per 16-value group) and row
     static constexpr int WS_ND = MINS ? UM_ROWS * 4 : 0;          // -dmin per row
     static constexpr int WS_A2 = MINS ? UM_ROWS * 64 : 0;         // mins as a tf32 operand tile
     static constexpr int WS_SLOT = WS_DW + WS_ND + WS_A2;
@@ -319,6 +326,33 @@ __device__ __forceinline__ void um_expand(const uint8_t *rec, int c, int lane, u
             *reinterpret_cast<uint2 *>(row_g + ch) = make_uint2(q.x, q.y);
             *reinterpret_cast<uint2 *>(row_g + 1024 + ch) = make_uint2(q.z, q.w);
         }
+    } else if constexpr (FMT == FMT_Q6_K) {
+        // Stage c = half c of the super-block: planes 3c (row g) and 3c + 1 (row g + 8) hold L[l0..+3], L[32+l0..+3],
+        // L[l1..+3], L[32+l1..+3] with l0 = 4t, l1 = 16 + 4t; plane 3c + 2 holds H[l0..+3], H[l1..+3] of row g, then of
+        // row g + 8. Quarter v (0..3) of the half is block v of the stage: values l of it are
+        // (low or high nibble of L[l] or L[32 + l]) | (bits 2v, 2v+1 of H[l]) << 4, minus 32. Its lower sixteen values
+        // (l0 part) go to chunk 2v of the first copy, its upper sixteen (l1 part) to chunk 2v + 1 of the second copy;
+        // the other halves of both copies stay zero. Four bytes per store, eight rows on eight chunk positions.
+        const uint4 L[2] = { tiles[(3 * c) * 32 + lane], tiles[(3 * c + 1) * 32 + lane] };
+        const uint4 H = tiles[(3 * c + 2) * 32 + lane];
+        uint8_t *row_g = a_rg + g * 128 + 4 * t;
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+#pragma unroll
+            for (int li = 0; li < 2; li++) {
+                const unsigned lw = li ? L[r].z : L[r].x, lw32 = li ? L[r].w : L[r].y;
+                const unsigned hw = r ? (li ? H.w : H.z) : (li ? H.y : H.x);
+#pragma unroll
+                for (int v = 0; v < 4; v++) {
+                    const unsigned lsrc = (v & 1) ? lw32 : lw;
+                    const unsigned lo4 = ((v & 2) ? (lsrc >> 4) : lsrc) & 0x0F0F0F0Fu;
+                    const unsigned u = lo4 | (((hw >> (2 * v)) & 0x03030303u) << 4);       // 0..63
+                    const unsigned x = u ^ 0x20202020u;                                     // six-bit two's complement of u - 32
+                    const unsigned code = x | ((x & 0x20202020u) * 6u);                     // sign bit copied to bits 6, 7
+                    *reinterpret_cast<unsigned *>(row_g + li * UM_A_STAGE + r * 1024 + (((2 * v + li) ^ g) << 4)) = code;
+                }
+            }
+        }
     } else {
         // Q4_0, record tile i (two blocks): words x = row g block 2i, y = row g+8 block 2i, z = row g block 2i+1,
         // w = row g+8 block 2i+1, each qs[4t .. 4t+3]: low nibbles are values 4t.. of the block, high nibbles values
@@ -368,6 +402,13 @@ __device__ __forceinline__ void um_tables(const uint8_t *rec, int rgl, int lane,
             uint8_t *a2 = ws_slot + Cfg::WS_DW + Cfg::WS_ND;
             *reinterpret_cast<float2 *>(a2 + um_sw64(row, t >> 1) + 8 * (t & 1)) = mn;
             *reinterpret_cast<float2 *>(a2 + um_sw64(row, 2 + (t >> 1)) + 8 * (t & 1)) = mn;
+        } else if constexpr (FMT == FMT_Q6_K) {
+            // i8 scales of the 16-value groups 4t .. 4t + 3, times the row's f16 d
+            const unsigned short *dp = reinterpret_cast<const unsigned short *>(rec + code_bytes(FMT) + 256);
+            const float d = um_h2f(dp[g + 8 * r]);
+            const unsigned scw = t == 0 ? h.x : t == 1 ? h.y : t == 2 ? h.z : h.w;
+#pragma unroll
+            for (int i = 0; i < 4; i++) dw[(4 * t + i) * UM_ROWS + row] = d * (float)(int)(signed char)((scw >> (8 * i)) & 0xffu);
         } else {
             // f16 scale of blocks 2t and 2t + 1
             const unsigned wsc = t == 0 ? h.x : t == 1 ? h.y : t == 2 ? h.z : h.w;
@@ -386,6 +427,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
     using Cfg = UmCfg<FMT, NT>;
     constexpr bool MINS = Cfg::MINS;
     constexpr int CS = Cfg::CS, BP = Cfg::BP, CW = Cfg::CW, DB = Cfg::DB, S = Cfg::S, RS = Cfg::RS, PW = Cfg::PW, EG = Cfg::EG;
+    constexpr int GPB = Cfg::GPB, NB = Cfg::NB;
     extern __shared__ __align__(1024) unsigned char um_smem_raw[];
     __shared__ UmBars sh;
     unsigned char *smem = um_smem_raw + ((1024 - (smem_u32(um_smem_raw) & 1023)) & 1023);
@@ -454,8 +496,9 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
         pdl_enter(0);   // everything else touches activations or writes results: wait for the preceding kernel
         wk.init(p);
         if (warp == 0 || warp == 2) {
-            // ===== MMA issuers: two threads (warps 0 and 2). Both visit every stage; a stage holds four blocks, block j
-            // goes to buffer (4c + j) % DB, and issuer `me` takes the blocks with j % 2 == me. Every block-dot buffer so has
+            // ===== MMA issuers: two threads (warps 0 and 2). Both visit every stage; a stage holds four blocks (Q6_K: eight
+            // 16-value groups), the i-th of them goes to buffer (first of the stage + i) % DB, and issuer `me` takes those
+            // with i % 2 == me. Every block-dot buffer so has
             // ONE issuer: a parity wait tells "free again" from "not yet used" only for a thread that is at most one use
             // ahead of the barrier. The issuers need only the number of units, not which tiles they belong to.
             if (lane == 0) {
@@ -474,15 +517,18 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
                     const int unit = k >> 1, c = k & 1;
                     if (!um_wait(&sh.full[stage], phase, abort_flag, NAP * 100)) { ok = false; break; }
                     um_tc_after();
-                    const unsigned a_lo = st_lo0 + (unsigned)(stage * (Cfg::STAGE >> 4)), b_lo = a_lo + (unsigned)(UM_A_STAGE >> 4);
+                    const unsigned a_lo = st_lo0 + (unsigned)(stage * (Cfg::STAGE >> 4)), b_lo = a_lo + (unsigned)(Cfg::A_BYTES >> 4);
 #pragma unroll
-                    for (int jj = 0; jj < 2; jj++) {
-                        const int j = me + 2 * jj, b = 4 * c + j, buf = b % DB;
-                        const unsigned dphase = ((unsigned)((unit * 8 + b) / DB) & 1u) ^ 1u;
+                    for (int ii = 0; ii < 2 * GPB; ii++) {
+                        const int i = me + 2 * ii;                       // this issuer's MMAs of the stage
+                        const int j = i / GPB, half = i % GPB;           // block of the stage; Q6_K: which sixteen values
+                        const int b = 4 * GPB * c + i, buf = b % DB;
+                        const unsigned dphase = ((unsigned)((unit * NB + b) / DB) & 1u) ^ 1u;
                         if (!um_wait(&sh.d_empty[buf], dphase, abort_flag, NAP * 100)) { ok = false; break; }
                         um_tc_after();
                         // K values 32 j .. 32 j + 31: 32 bytes = 2 sixteen-byte units along the swizzled row
-                        um_mma_i8(tmem + (unsigned)(buf * NT), mk(a_lo + 2 * j, desc_hi), mk(b_lo + 2 * j, desc_hi), idesc, 0);
+                        um_mma_i8(tmem + (unsigned)(buf * NT), mk(a_lo + (unsigned)(half * (UM_A_STAGE >> 4)) + 2 * j, desc_hi),
+                                  mk(b_lo + 2 * j, desc_hi), idesc, 0);
                         um_commit(&sh.d_full[buf]);
                     }
                     if (!ok) break;
@@ -526,7 +572,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
                     for (int c = 0; c < 2; c++) {
                         if (!um_wait(&sh.empty[stage], phase, abort_flag, NAP * 500)) { ok = false; break; }
                         um_expect_tx(&sh.full[stage], (unsigned)Cfg::B_STAGE);
-                        um_bulk(smem + Cfg::OFF_STAGE + stage * Cfg::STAGE + UM_A_STAGE,
+                        um_bulk(smem + Cfg::OFF_STAGE + stage * Cfg::STAGE + Cfg::A_BYTES,
                                 p.q_sw + ((long long)(wk.st * 2 + c) * tok_groups + (t0 >> 3)) * 1024, Cfg::B_STAGE, &sh.full[stage]);
                         if (++stage == S) { stage = 0; phase ^= 1u; }
                     }
@@ -540,6 +586,15 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
             int slot = 0, stage = 0, unit = 0;
             unsigned rphase = 0, sphase = 1;
             bool ok = true;
+            if constexpr (GPB == 2) {
+                // the zero halves of the two masked copies never change: written once, for every stage
+                for (int st = 0; st < S; st++) {
+                    uint4 *z = reinterpret_cast<uint4 *>(smem + Cfg::OFF_STAGE + st * Cfg::STAGE);
+                    for (int i = pw * 32 + lane; i < Cfg::A_BYTES / 16; i += PW * 32) z[i] = make_uint4(0u, 0u, 0u, 0u);
+                }
+                um_fence_async();
+                asm volatile("bar.sync 1, %0;" ::"n"(PW * 32) : "memory");   // (the producer warps only; passed once, at the start)
+            }
             for (; !wk.done() && ok; wk.next(), unit++) {
                 const int us = unit & 1;
                 if (!um_wait(&sh.rw_full[slot], rphase, abort_flag, NAP * 300) ||
@@ -599,12 +654,12 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
                 // The unit's blocks of this warp as 16-column chunks; a block's buffer goes back to its MMA issuer as soon
                 // as the last chunk has arrived in registers. The loop over blocks is a real loop (the code of all roles
                 // has to stay resident in the instruction cache).
-                constexpr int HPB = CW / 16, NBLK = 8 / BP;
+                constexpr int HPB = CW / 16, NBLK = NB / BP;
                 const ulonglong2 *dx_tab = reinterpret_cast<const ulonglong2 *>(smem + Cfg::OFF_ACT + us * Cfg::ACT_SLOT) + c0 / 4;
 #pragma unroll 1
                 for (int bi = 0; bi < NBLK; bi++) {
                     const int b = bi * BP + bp, buf = b % DB;
-                    if (!um_wait(&sh.d_full[buf], (unsigned)((unit * 8 + b) / DB) & 1u, abort_flag, NAP * 20)) { ok = false; break; }
+                    if (!um_wait(&sh.d_full[buf], (unsigned)((unit * NB + b) / DB) & 1u, abort_flag, NAP * 20)) { ok = false; break; }
                     um_tc_after();
                     const float dw = um_lds_f32(ws_s + (unsigned)((b * UM_ROWS + r) * 4));
                     const ull dw2 = um_pkf(dw, dw);
@@ -623,20 +678,23 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
                             const int n0 = (wk.tile / p.tok_tiles) * UM_ROWS, t0 = (wk.tile % p.tok_tiles) * NT;
 #pragma unroll
                             for (int j = 0; j < 16; j++) {
-                                const int tok = t0 + c0 + h * 16 + j, row = n0 + r, blk = wk.st * 8 + b;
+                                const int tok = t0 + c0 + h * 16 + j, row = n0 + r, blk = wk.st * 8 + b / GPB;
                                 if (tok < p.a.rows && row < p.w.n && blk * 32 < p.w.k) {
-                                    // the reference's block dot has unsigned weight codes (code + 128, nibble): add the
-                                    // offset times the block's activation sum
-                                    const int cexp = FMT == FMT_Q8_0 ? 128 : FMT == FMT_Q4_0 ? 8 : 0;
+                                    // the reference's block dot has unsigned weight codes (code + 128, nibble, 6-bit value):
+                                    // add the offset times the block's activation sum
+                                    const int cexp = FMT == FMT_Q8_0 ? 128 : FMT == FMT_Q4_0 ? 8 : FMT == FMT_Q6_K ? 32 : 0;
                                     const int add = cexp ? cexp * __ldg(&p.a.isum[(long long)tok * (p.a.k_pad >> 5) + blk]) : 0;
                                     const int dot = FMT == FMT_Q4_0 ? ((int)v[j] >> 4) : (int)v[j];
-                                    p.dump[((long long)tok * p.w.n + row) * (p.w.k >> 5) + blk] = dot + add;
+                                    int *dst = &p.dump[((long long)tok * p.w.n + row) * (p.w.k >> 5) + blk];
+                                    // Q6_K: the block's two groups come one after the other to this same thread
+                                    if (GPB == 1 || (b & 1) == 0) *dst = dot + add;
+                                    else *dst += dot;
                                 }
                             }
                         }
 #pragma unroll
                         for (int j4 = 0; j4 < 4; j4++) {
-                            const ulonglong2 dx = dx_tab[(b * NT + h * 16) / 4 + j4];
+                            const ulonglong2 dx = dx_tab[((b / GPB) * NT + h * 16) / 4 + j4];
                             const int o = h * 8 + j4 * 2;
                             const ull t01 = um_mul2(um_i2f2(v[4 * j4], v[4 * j4 + 1]), dw2);
                             const ull t23 = um_mul2(um_i2f2(v[4 * j4 + 2], v[4 * j4 + 3]), dw2);
@@ -791,7 +849,8 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
 
 // ---- host side --------------------------------------------------------------------------------------------------------
 
-bool umma_supports(int fmt) { return fmt == FMT_Q4_K || fmt == FMT_Q4_0 || fmt == FMT_Q8_0; }
+// Q6_K at the 128-token tile only (more than 64 rows)
+bool umma_supports(int fmt, int rows) { return fmt == FMT_Q4_K || fmt == FMT_Q4_0 || fmt == FMT_Q8_0 || (fmt == FMT_Q6_K && rows > 64); }
 
 int umma_token_tile(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : 128; }
 
@@ -820,12 +879,16 @@ static cudaError_t um_launch(const UmParams &p, int ctas, cudaStream_t stream)
 template <int FMT, bool DUMP>
 static cudaError_t um_launch_nt(const UmParams &p, int nt, int ctas, cudaStream_t stream)
 {
-    switch (nt) {
-    case 16: return um_launch<FMT, 16, DUMP>(p, ctas, stream);
-    case 32: return um_launch<FMT, 32, DUMP>(p, ctas, stream);
-    case 64: return um_launch<FMT, 64, DUMP>(p, ctas, stream);
-    case 128: return um_launch<FMT, 128, DUMP>(p, ctas, stream);
-    default: return cudaErrorInvalidValue;
+    if constexpr (FMT == FMT_Q6_K) {
+        return nt == 128 ? um_launch<FMT, 128, DUMP>(p, ctas, stream) : cudaErrorInvalidValue;
+    } else {
+        switch (nt) {
+        case 16: return um_launch<FMT, 16, DUMP>(p, ctas, stream);
+        case 32: return um_launch<FMT, 32, DUMP>(p, ctas, stream);
+        case 64: return um_launch<FMT, 64, DUMP>(p, ctas, stream);
+        case 128: return um_launch<FMT, 128, DUMP>(p, ctas, stream);
+        default: return cudaErrorInvalidValue;
+        }
     }
 }
 
@@ -851,7 +914,7 @@ cudaError_t launch_umma(const WeightView &w, const ActView &a, const uint8_t *q_
 #define SLC_FMT(F)                                                                   \
     case F: return dump ? um_launch_nt<F, true>(p, nt, ctas, stream) : um_launch_nt<F, false>(p, nt, ctas, stream);
     switch (w.fmt) {
-        SLC_FMT(FMT_Q4_K) SLC_FMT(FMT_Q4_0) SLC_FMT(FMT_Q8_0)
+        SLC_FMT(FMT_Q4_K) SLC_FMT(FMT_Q4_0) SLC_FMT(FMT_Q8_0) SLC_FMT(FMT_Q6_K)
     default: return cudaErrorInvalidValue;
     }
 #undef SLC_FMT

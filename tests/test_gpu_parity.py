@@ -483,7 +483,8 @@ def test_row_invariant_short_k(cuda_device, rows):
     ("Q4_0", 128, 256, 16), ("Q4_0", 96, 512, 5), ("Q8_0", 96, 512, 3), ("Q4_K", 96, 512, 8), ("Q4_K", 130, 1024, 17),
     ("Q4_K", 300, 2048, 33), ("Q8_0", 7, 1568, 12), ("Q4_0", 7, 96, 3), ("Q4_K", 1000, 3072, 64), ("Q4_K", 384, 1024, 65),
     ("Q4_0", 640, 2048, 130), ("Q8_0", 256, 1024, 300), ("Q4_K", 4112, 512, 40), ("Q4_K", 1000, 2816, 256),
-    ("Q8_0", 2500, 1024, 31), ("Q4_0", 19000, 256, 9)])
+    ("Q8_0", 2500, 1024, 31), ("Q4_0", 19000, 256, 9), ("Q6_K", 128, 256, 65), ("Q6_K", 1000, 2816, 300),
+    ("Q6_K", 7, 512, 70), ("Q6_K", 520, 1024, 129)])
 def test_tile_kernel_shapes(cuda_device, type_name, n, k, rows):
     """Ragged N and K, every token-tile width (16, 32, 64, 128), tiles split between CTAs and tiles owned by one CTA,
     more tiles than CTAs and fewer; y against the oracle and the int32 block dots bit for bit."""
@@ -492,18 +493,22 @@ def test_tile_kernel_shapes(cuda_device, type_name, n, k, rows):
     assert cuda_device.last_status() == 0
 
 
-def test_tile_kernel_refuses_q6_k_and_short_rows(cuda_device):
-    w = cuda_device.upload_weight("Q6_K", (64, 256), synth.weight_blocks("Q6_K", 64, 256, 1))
-    op = MatMulOp(cuda_device, w, 8)
-    try:
-        with pytest.raises(Exception):
-            op.set_kernel(N.KERNEL_TILE)
-    finally:
-        op.dispose()
-        w.dispose()
-    # fewer than 3 rows: the forced family falls back to the automatic choice
+def test_tile_kernel_falls_back_where_it_does_not_serve(cuda_device):
+    # Q6_K is served at the 128-token tile only: up to 64 rows the forced family falls back to the automatic choice
+    _, kern = check_matmul(cuda_device, "Q6_K", 64, 256, 8, kernel=N.KERNEL_TILE)
+    assert kern[0] != N.KERNEL_TILE
+    # and so do fewer than 3 rows of any format
     _, kern = check_matmul(cuda_device, "Q4_K", 64, 512, 2, kernel=N.KERNEL_TILE, max_rows=8)
     assert kern[0] != N.KERNEL_TILE
+
+
+def test_q6_k_prefill_takes_the_tile_kernel(cuda_device):
+    """More than 64 rows of a Q6_K weight with few rows: two half-masked tensor-core instructions per block instead of
+    64-row chunks of the skinny kernel (the reference's GEMM serves Q6_K the same way,
+    src/Sharplight.Shaders/Kernels/mmq.slang:235-239)."""
+    _, kern = check_matmul(cuda_device, "Q6_K", 640, 1024, 200, seed=9)
+    assert kern[0] == N.KERNEL_TILE
+    assert _check_sampled_rows(cuda_device, "Q6_K", 4096, 4096, 2048, 210, 32) == N.KERNEL_TILE
 
 
 @pytest.mark.parametrize("rows", [16, 64])
