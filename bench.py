@@ -43,7 +43,7 @@ import numpy as np  # noqa: E402
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 NOMINAL_INT8_TOPS = 4500.0
-KERNEL_NAMES = {1: "mmvq (dp4a)", 2: "skinny (int8 mma.sync)", 3: "mmq (tcgen05 kind::i8)", 4: "tile (tcgen05 kind::f16, stream-K)"}
+KERNEL_NAMES = {1: "mmvq (dp4a)", 2: "skinny (int8 mma.sync)", 3: "mmq (tcgen05 kind::i8)", 4: "tile (tcgen05 kind::i8, stream-K)"}
 # dram__bytes_read.sum + dram__bytes_write.sum of one mat-vec launch on configuration 2 at M = 1, from one ncu capture
 # of this kernel (the algorithmic bytes are 33 092 608); quoted only while the kernel family of the run is the captured one
 CONFIG2_M1_DRAM_BYTES = 33062656
@@ -375,7 +375,7 @@ def stack_e2e(args, torch, dist, world, stack, rows, steps):
     return ms, h2d, d2h, same
 
 
-def kernel_times(torch, device, N, synth, stream, type_name, n, k, rows, copies, steps, distinct=True, kernel=None):
+def kernel_times(torch, device, N, synth, stream, type_name, n, k, rows, copies, steps, distinct=True, kernel=None, use_graph=True):
     """One MatMul shape over `copies` weight matrices (distinct: rotating copies, so the weights come from HBM; else
     the same matrix every time: L2-resident when it fits). Returns seconds per MatMul for (operator = quantize + kernel,
     each launch waiting for its predecessor; kernel: the step quantizes once and the `copies` MatMuls share that one
@@ -404,8 +404,8 @@ def kernel_times(torch, device, N, synth, stream, type_name, n, k, rows, copies,
         for i, op in enumerate(ops):
             act.matmul(op, y[i].data_ptr(), n, sp)
 
-    t_op = time_graphed(torch, None, 1, stream, op_step, steps, 3) * 1e-3 / copies
-    t_k = time_graphed(torch, None, 1, stream, kern_step, steps, 3) * 1e-3 / copies
+    t_op = time_graphed(torch, None, 1, stream, op_step, steps, 3, use_graph=use_graph) * 1e-3 / copies
+    t_k = time_graphed(torch, None, 1, stream, kern_step, steps, 3, use_graph=use_graph) * 1e-3 / copies
     family, launches = ops[0].last_kernel()
     for op in ops:
         op.dispose()
@@ -731,6 +731,32 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_shape(args):
+    """--shape TYPE,N,K,ROWS[,FAMILY]: one MatMul shape over --copies rotating weight matrices, kernel and operator time
+    (the probe behind the per-kernel profiles: small enough to capture under a profiler). FAMILY: auto, mmvq, skinny, mmq,
+    tile."""
+    import torch
+    from sharplight_b200 import CudaExecutionProvider, synth
+    from sharplight_b200 import native as N
+    parts = args.shape.split(",")
+    type_name, n, k, rows = parts[0], int(parts[1]), int(parts[2]), int(parts[3])
+    family = {"auto": None, "mmvq": N.KERNEL_MMVQ, "skinny": N.KERNEL_SKINNY, "mmq": N.KERNEL_MMQ, "tile": N.KERNEL_TILE}[
+        parts[4] if len(parts) > 4 else "auto"]
+    torch.cuda.set_device(0)
+    provider = CudaExecutionProvider()
+    device = provider.open_device(provider.get_devices()[0])
+    peaks = measured_peaks()
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    t_op, t_k, fam, launches = kernel_times(torch, device, N, synth, stream, type_name, n, k, rows, args.copies, max(args.steps, 1),
+                                            kernel=family, use_graph=not args.no_graph)
+    entry = hbm_entry(peaks, type_name, n, k, rows, t_op, t_k, fam, synth)
+    entry.update({"shape": [type_name, n, k, rows], "copies": args.copies, "launches_per_matmul": launches,
+                  "kernel_tops": 2.0 * rows * n * k / t_k / 1e12, "status": device.last_status()})
+    print(json.dumps({"probe": entry}), flush=True)
+    device.dispose()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -744,9 +770,13 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="layers of the stack (default: the architecture's 80)")
     ap.add_argument("--tp-main-only", action="store_true", help="time the stack at --rows only, not at 1, 8, 64 and 2048 rows")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of a CUDA graph")
+    ap.add_argument("--shape", default="", help="TYPE,N,K,ROWS[,FAMILY]: time this one MatMul shape and nothing else")
+    ap.add_argument("--copies", type=int, default=8, help="--shape: rotating weight matrices")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.shape:
+        run_shape(args)
     else:
         run_ours(args)
 
