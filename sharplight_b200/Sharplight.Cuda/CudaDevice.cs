@@ -89,11 +89,12 @@ internal sealed class CudaDevice : IComputeDevice
             return OpSupport.No("int_dot is disabled and this provider has no float path");
         }
 
-        // StandardOps.F32ActivationsAttribute: the node keeps f32 activation math unless reduced precision is allowed; this
-        // provider only has the 8-bit activation path, so such a node is not taken (never silently quantized)
-        if (node.Attributes.Get(StandardOps.F32ActivationsAttribute, false))
+        // StandardOps.F32ActivationsAttribute: the node keeps f32 activation math unless reduced precision is allowed. Such
+        // a node is never silently quantized: it runs the dequant-fused f32 mat-vec (SLC_MATMUL_F32_ACTIVATIONS), which
+        // keeps one f32 activation row in shared memory; a longer K goes to the placement fallback.
+        if (node.Attributes.Get(StandardOps.F32ActivationsAttribute, false) && k > Slc.F32ActivationsMaxK)
         {
-            return OpSupport.No("f32 activations requested and this provider only has the 8-bit activation path");
+            return OpSupport.No($"f32 activations requested and K={k} exceeds the f32 mat-vec's {Slc.F32ActivationsMaxK}");
         }
 
         return OpSupport.Yes;

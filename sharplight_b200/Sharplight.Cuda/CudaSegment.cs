@@ -31,7 +31,7 @@ internal sealed unsafe class CudaSegment : ICompiledSegment, IDeviceForwardingSe
     private readonly long _maxRows;
     private readonly Dictionary<Value, Slot> _slots = new();
     private readonly Dictionary<Value, nint> _activations = new();          // one 8-bit copy per distinct MatMul input
-    private readonly List<(Node Node, nint Op, Value X, Value Y)> _steps = new();
+    private readonly List<(Node Node, nint Op, Value X, Value Y, bool F32)> _steps = new();
     private readonly List<nint> _weights = new();
     private long _weightBytes;
     private bool _executed;
@@ -76,18 +76,21 @@ internal sealed unsafe class CudaSegment : ICompiledSegment, IDeviceForwardingSe
                 Check.Ok(NativeMethods.slc_weight_shape(weight, out _, out _, out _, out long bytes));
                 _weightBytes += bytes;
 
-                uint flags = options.Deterministic ? Slc.MatMulRowInvariant : 0u;
+                // a node that keeps f32 activation math (StandardOps.F32ActivationsAttribute) is never quantized, unless the
+                // compile options allow reduced precision (src/Sharplight.Cpu/CpuCompiledSegment.LowerLinear.cs:39)
+                bool f32 = node.Attributes.Get(StandardOps.F32ActivationsAttribute, false) && !options.AllowReducedPrecision;
+                uint flags = f32 ? Slc.MatMulF32Activations : options.Deterministic ? Slc.MatMulRowInvariant : 0u;
                 Check.Ok(NativeMethods.slc_matmul_create(device.Handle, weight, _maxRows, flags, out nint op));
                 Slot xs = SlotOf(x, k, x.Type == DataType.BF16 ? 2 : 4, x.Type == DataType.BF16 ? Slc.Bf16 : Slc.F32);
                 SlotOf(y, n, 4, Slc.F32);
-                if (!_activations.ContainsKey(x))
+                if (!f32 && !_activations.ContainsKey(x))
                 {
                     Check.Ok(NativeMethods.slc_activation_create(device.Handle, _maxRows, k, out nint act));
                     _activations[x] = act;
                 }
 
                 _ = xs;
-                _steps.Add((node, op, x, y));
+                _steps.Add((node, op, x, y, f32));
             }
 
             foreach (Value v in segment.Inputs.Concat(segment.Outputs))
@@ -177,9 +180,16 @@ internal sealed unsafe class CudaSegment : ICompiledSegment, IDeviceForwardingSe
         }
 
         var quantized = new HashSet<Value>();
-        foreach ((Node _, nint op, Value x, Value y) in _steps)
+        foreach ((Node _, nint op, Value x, Value y, bool f32) in _steps)
         {
             Slot xs = _slots[x], ys = _slots[y];
+            if (f32)
+            {
+                Check.Ok(NativeMethods.slc_matmul_run(op, (void*)xs.Device, xs.Dtype, rows, xs.Columns, 1, (float*)ys.Device, ys.Columns, 1, 0));
+                ys.Rows = rows;
+                continue;
+            }
+
             nint act = _activations[x];
             if (quantized.Add(x))
             {
@@ -296,7 +306,7 @@ internal sealed unsafe class CudaSegment : ICompiledSegment, IDeviceForwardingSe
 
         _disposed = true;
         _ = NativeMethods.slc_device_sync(_device.Handle);
-        foreach ((Node _, nint op, Value _, Value _) in _steps)
+        foreach ((Node _, nint op, Value _, Value _, bool _) in _steps)
         {
             NativeMethods.slc_matmul_destroy(op);
         }

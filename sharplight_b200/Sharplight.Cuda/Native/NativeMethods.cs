@@ -33,6 +33,7 @@ internal static unsafe partial class NativeMethods
     [LibraryImport(Library)] public static partial int slc_host_alloc(long bytes, out nint hostPtr);
     [LibraryImport(Library)] public static partial void slc_host_free(nint hostPtr);
     [LibraryImport(Library)] public static partial int slc_buffer_copy_async(nint device, nint dst, nint src, long bytes, int direction, nint stream);
+    [LibraryImport(Library)] public static partial int slc_buffer_densify(nint device, nint dst, nint src, long batch, long rows, long cols, long batchStride, long rowStride, long colStride, int elemBytes, nint stream);
 
     [LibraryImport(Library)] public static partial int slc_stream_create(nint device, out nint stream);
     [LibraryImport(Library)] public static partial void slc_stream_destroy(nint device, nint stream);
@@ -59,6 +60,9 @@ internal static unsafe partial class NativeMethods
     [LibraryImport(Library)] public static partial int slc_activation_create(nint device, long maxRows, long k, out nint act);
     [LibraryImport(Library)] public static partial void slc_activation_destroy(nint act);
     [LibraryImport(Library)] public static partial int slc_activation_quantize(nint act, nint xDevice, int xDtype, long rows, long xStride, nint stream);
+    [LibraryImport(Library)] public static partial int slc_activation_quantize_rmsnorm(nint act, nint xDevice, int xDtype, long rows, long xStride, nint weightDevice, float eps, nint yDevice, long yStride, nint stream);
+    [LibraryImport(Library)] public static partial int slc_activation_quantize_silu_mul(nint act, nint gateDevice, long gateStride, nint upDevice, long upStride, long rows, nint yDevice, long yStride, nint stream);
+    [LibraryImport(Library)] public static partial int slc_argmax_rows(nint device, nint yDevice, long rows, long n, long yStride, nint outIndexDevice, nint stream);
     [LibraryImport(Library)] public static partial int slc_matmul_run_quantized(nint op, nint act, nint yDevice, long yStride, nint stream);
     [LibraryImport(Library)] public static partial int slc_matmul_run_quantized_epilogue(nint op, nint act, nint exchange, nint bias, nint residual, long residualStride, nint y, long yStride, nint stream);
 
@@ -66,6 +70,10 @@ internal static unsafe partial class NativeMethods
     [LibraryImport(Library)] public static partial int slc_tp_exchange_connect(nint exchange, ReadOnlySpan<byte> handles);
     [LibraryImport(Library)] public static partial void slc_tp_exchange_destroy(nint exchange);
     [LibraryImport(Library)] public static partial int slc_tp_exchange_set_wait_ms(nint exchange, int milliseconds);
+    [LibraryImport(Library)] public static partial int slc_tp_comm_unique_id(Span<byte> id128);
+    [LibraryImport(Library)] public static partial int slc_tp_comm_create(nint device, int rank, int world, ReadOnlySpan<byte> id128, out nint comm);
+    [LibraryImport(Library)] public static partial void slc_tp_comm_destroy(nint comm);
+    [LibraryImport(Library)] public static partial int slc_tp_exchange_set_comm(nint exchange, nint comm, int inKernelRows);
     [LibraryImport(Library)] public static partial int slc_matmul_run_allreduce(nint op, nint exchange, nint x, int xDtype, long rows, long xStride, nint y, long yStride, nint stream);
     [LibraryImport(Library)] public static partial int slc_matmul_run_quantized_allreduce(nint op, nint act, nint exchange, nint y, long yStride, nint stream);
 
@@ -100,7 +108,8 @@ internal static class Slc
 {
     public const int FormatQ4_0 = 2, FormatQ8_0 = 8, FormatQ4_K = 12, FormatQ6_K = 14;
     public const int F32 = 0, Bf16 = 1;
-    public const uint MatMulRowInvariant = 1;
+    public const uint MatMulRowInvariant = 1, MatMulF32Activations = 2;
+    public const long F32ActivationsMaxK = 49152;
     public const int HostToDevice = 0, DeviceToHost = 1, DeviceToDevice = 2;
     public const int ErrTimeout = -7;
 }

@@ -131,3 +131,15 @@ def test_bf16_helpers_round_trip():
     back = P.bf16_bits_to_f32(b)
     assert np.all(np.abs(back - x) <= np.abs(x) * 2.0 ** -8)
     assert np.array_equal(P.to_bf16_bits(back), b)
+
+
+def test_managed_pinvoke_list_covers_the_header():
+    """Every export of include/sharplight_cuda.h has its [LibraryImport] in the managed provider's NativeMethods.cs (the
+    C# sources are not compiled in this image: this at least keeps the list complete and free of stale names)."""
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    header = open(os.path.join(root, "include", "sharplight_cuda.h")).read()
+    managed = open(os.path.join(root, "sharplight_b200", "Sharplight.Cuda", "Native", "NativeMethods.cs")).read()
+    exported = set(re.findall(r"SLC_API\s+[\w\s\*]+?\b(slc_[a-z0-9_]+)\s*\(", header))
+    imported = set(re.findall(r"static partial [\w\*]+ (slc_[a-z0-9_]+)\(", managed))
+    assert exported and exported == imported, (sorted(exported - imported), sorted(imported - exported))
