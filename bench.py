@@ -579,6 +579,54 @@ def decode_step_leg(args, torch, dist, device, N, synth, stream, peaks):
     return out
 
 
+def extras_leg(args, torch, device, N, synth, stream, peaks):
+    """The kernels on either side of the MatMul (producers of the 8-bit activations, arg-max) and the f32-activation
+    mat-vec: microseconds per launch inside a replayed graph of 32 launches."""
+    from sharplight_b200 import MatMulOp, SharedActivation
+    steps = max(5, min(args.steps, 20))
+    reps = 32
+    out = {}
+
+    def timed(fn):
+        return time_graphed(torch, None, 1, stream, lambda sp: [fn(sp) for _ in range(reps)], steps, 3) * 1e3 / reps
+
+    for rows, k in ((1, 8192), (32, 4096)):
+        x = torch.randn((rows, k), device="cuda")
+        w = torch.ones((k,), device="cuda")
+        act = SharedActivation(device, rows, k)
+        out[f"quantize_{rows}x{k}_us"] = timed(lambda sp: act.quantize(x.data_ptr(), N.F32, rows, k, sp))
+        out[f"rmsnorm_quantize_{rows}x{k}_us"] = timed(lambda sp: act.quantize_rmsnorm(x.data_ptr(), N.F32, rows, k, w.data_ptr(), 1e-5, 0, 0, sp))
+        act.dispose()
+    for rows, k in ((1, 28672), (32, 14336)):
+        gu = torch.randn((rows, 2 * k), device="cuda")
+        act = SharedActivation(device, rows, k)
+        out[f"silu_mul_quantize_{rows}x{k}_us"] = timed(
+            lambda sp: act.quantize_silu_mul(gu.data_ptr(), 2 * k, gu.data_ptr() + 4 * k, 2 * k, rows, 0, 0, sp))
+        act.dispose()
+    logits = torch.randn((32, 128256), device="cuda")
+    idx = torch.empty((32,), dtype=torch.int32, device="cuda")
+    out["argmax_32x128256_us"] = timed(lambda sp: device.argmax_rows(logits.data_ptr(), 32, 128256, 128256, idx.data_ptr(), sp))
+    # f32-activation mat-vec on config 2's shape, 16 rotating weights
+    n, k, copies = 14336, 4096, 16
+    base = synth.weight_blocks("Q4_K", n, k, seed=77)
+    ws = [device.upload_weight("Q4_K", (n, k), np.roll(base.reshape(n, -1), i * 37, axis=0).reshape(-1)) for i in range(copies)]
+    wbytes = synth.weight_bytes("Q4_K", n, k)
+    for rows in (1, 4):
+        ops = [MatMulOp(device, wt, rows, f32_activations=True) for wt in ws]
+        x = torch.randn((rows, k), device="cuda")
+        y = torch.empty((copies, rows, n), device="cuda")
+        ms = time_graphed(torch, None, 1, stream,
+                          lambda sp: [op.run_pointers(x.data_ptr(), N.F32, rows, k, True, y[i].data_ptr(), n, True, sp) for i, op in enumerate(ops)],
+                          steps, 3)
+        us = ms * 1e3 / copies
+        out[f"matvec_f32_q4k_14336x4096_M{rows}"] = {"us": us, "weight_gbs": wbytes / us / 1e3, "frac": wbytes / us / 1e3 / peaks["hbm_gbs"]}
+        for op in ops:
+            op.dispose()
+    for wt in ws:
+        wt.dispose()
+    return out
+
+
 def allreduce_check(stack, torch, dist, world, stream, row_counts):
     """The in-kernel sum against the collective library's, on the last layer's row-split outputs of one step, and across
     ranks (bit-identical everywhere), at row counts on both exchange protocols (word protocol up to 16 rows, arrival
@@ -714,6 +762,7 @@ def run_ours(args):
             configs = config_legs(args, torch, device, N, synth, stream, peaks)
             configs["config3_prefill"] = prefill_leg(args, device, torch, N, synth, stream, peaks, with_cpu=not args.no_cpu)
             configs["config4_decode_step_8b"] = decode_step_leg(args, torch, dist, device, N, synth, stream, peaks)
+            configs["either_side_of_the_matmul"] = extras_leg(args, torch, device, N, synth, stream, peaks)
             line["configs"] = configs
         if not args.no_cpu:
             base, _ = cpu_stack_baseline(rows, 12.0)
