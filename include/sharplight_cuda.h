@@ -197,6 +197,13 @@ SLC_API slc_result slc_weight_upload_kslice(slc_device *device, int32_t format, 
                                             slc_weight **out);
 /* Writes the weight back as raw ggml blocks (inverse of the device layout; for verification). */
 SLC_API slc_result slc_weight_download(slc_weight *weight, void *blocks, int64_t bytes);
+/* The device layout as an artefact (the reference's providers name artefact tiers a model package may carry for them,
+   src/Sharplight.Core/Runtime/IComputeDevice.cs:47-52): export writes a 56-byte header (magic, version, format, shape)
+   and the re-laid-out records; import uploads them as they are, without the re-layout pass and without the raw blocks.
+   An artefact of another layout version is refused with SLC_ERR_UNSUPPORTED: fall back to slc_weight_upload. */
+SLC_API slc_result slc_weight_layout_bytes(slc_weight *weight, int64_t *out_bytes);
+SLC_API slc_result slc_weight_export_layout(slc_weight *weight, void *out_host, int64_t bytes);
+SLC_API slc_result slc_weight_import_layout(slc_device *device, const void *artefact_host, int64_t bytes, slc_weight **out);
 SLC_API slc_result slc_weight_shape(slc_weight *weight, int32_t *format, int64_t *n, int64_t *k, int64_t *device_bytes);
 SLC_API void slc_weight_free(slc_weight *weight);
 

@@ -48,6 +48,9 @@ internal static unsafe partial class NativeMethods
     [LibraryImport(Library)] public static partial int slc_weight_upload_kslice(nint device, int format, long n, long k, void* blocks, long bytes, long k0, long k1, out nint weight);
     [LibraryImport(Library)] public static partial int slc_weight_download(nint weight, void* blocks, long bytes);
     [LibraryImport(Library)] public static partial int slc_weight_shape(nint weight, out int format, out long n, out long k, out long deviceBytes);
+    [LibraryImport(Library)] public static partial int slc_weight_layout_bytes(nint weight, out long bytes);
+    [LibraryImport(Library)] public static partial int slc_weight_export_layout(nint weight, void* outHost, long bytes);
+    [LibraryImport(Library)] public static partial int slc_weight_import_layout(nint device, void* artefactHost, long bytes, out nint weight);
     [LibraryImport(Library)] public static partial void slc_weight_free(nint weight);
 
     [LibraryImport(Library)] public static partial int slc_matmul_create(nint device, nint weight, long maxRows, uint flags, out nint op);

@@ -368,6 +368,74 @@ slc_result slc_weight_download(slc_weight *w, void *blocks, int64_t bytes)
     return SLC_OK;
 }
 
+// ---- the device layout as an artefact: written once, loaded without the re-layout pass ---------------------------------
+
+static const uint32_t SLC_LAYOUT_MAGIC = 0x4C434C53u;   // "SLCL"
+static const uint32_t SLC_LAYOUT_VERSION = 1;
+
+struct LayoutHeader
+{
+    uint32_t magic, version;
+    int32_t fmt, reserved;
+    int64_t n, k, n_pad, k_pad, payload;
+};
+
+slc_result slc_weight_layout_bytes(slc_weight *w, int64_t *out_bytes)
+{
+    if (!w || !out_bytes) return fail(SLC_ERR_INVALID_ARGUMENT, "weight or out is null");
+    *out_bytes = (int64_t)(sizeof(LayoutHeader) + weight_bytes(w->fmt, w->view.n_pad, w->view.k_pad));
+    return SLC_OK;
+}
+
+slc_result slc_weight_export_layout(slc_weight *w, void *out, int64_t bytes)
+{
+    if (!w || !out) return fail(SLC_ERR_INVALID_ARGUMENT, "weight or out is null");
+    const size_t payload = weight_bytes(w->fmt, w->view.n_pad, w->view.k_pad);
+    if (bytes != (int64_t)(sizeof(LayoutHeader) + payload)) return fail(SLC_ERR_BUFFER_TOO_SMALL, "bytes != slc_weight_layout_bytes");
+    LayoutHeader h{ SLC_LAYOUT_MAGIC, SLC_LAYOUT_VERSION, w->fmt, 0, w->n, w->k, w->view.n_pad, w->view.k_pad, (int64_t)payload };
+    memcpy(out, &h, sizeof h);
+    SLC_CUDA(cudaSetDevice(w->dev->index));
+    SLC_CUDA(cudaMemcpy(static_cast<uint8_t *>(out) + sizeof h, w->base, payload, cudaMemcpyDeviceToHost));
+    return SLC_OK;
+}
+
+slc_result slc_weight_import_layout(slc_device *d, const void *artefact, int64_t bytes, slc_weight **out)
+{
+    if (!out) return fail(SLC_ERR_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    if (!d || !artefact || bytes < (int64_t)sizeof(LayoutHeader)) return fail(SLC_ERR_INVALID_ARGUMENT, "device or artefact is null, or too short");
+    LayoutHeader h;
+    memcpy(&h, artefact, sizeof h);
+    if (h.magic != SLC_LAYOUT_MAGIC) return fail(SLC_ERR_INVALID_ARGUMENT, "not a weight-layout artefact");
+    if (h.version != SLC_LAYOUT_VERSION) return fail(SLC_ERR_UNSUPPORTED, "weight-layout artefact of another version: upload the raw blocks again");
+    const int bs = block_size(h.fmt);
+    if (bs == 0 || h.n < 0 || h.k <= 0 || h.k % bs != 0 || h.n_pad != (int64_t)round_up((size_t)h.n, 16) ||
+        h.k_pad != (int64_t)round_up((size_t)h.k, 256) || h.payload != (int64_t)weight_bytes(h.fmt, (int)h.n_pad, (int)h.k_pad) ||
+        bytes != (int64_t)sizeof(LayoutHeader) + h.payload) {
+        return fail(SLC_ERR_INVALID_ARGUMENT, "weight-layout artefact: inconsistent header");
+    }
+    SLC_CUDA(cudaSetDevice(d->index));
+    slc_weight *w = new (std::nothrow) slc_weight();
+    if (!w) return fail(SLC_ERR_OUT_OF_MEMORY, "host allocation failed");
+    w->dev = d; w->fmt = h.fmt; w->n = h.n; w->k = h.k;
+    w->bytes = round_up((size_t)h.payload, 256) + 256;
+    cudaError_t e = cudaMalloc(&w->base, w->bytes);
+    if (e == cudaSuccess) e = cudaMemsetAsync(w->base, 0, w->bytes, d->stream);
+    if (e == cudaSuccess && h.payload > 0) {
+        e = cudaMemcpyAsync(w->base, static_cast<const uint8_t *>(artefact) + sizeof h, (size_t)h.payload, cudaMemcpyHostToDevice, d->stream);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);
+    if (e != cudaSuccess) {
+        if (w->base) cudaFree(w->base);
+        delete w;
+        return cuda_fail(e, "slc_weight_import_layout");
+    }
+    w->view.fmt = h.fmt; w->view.n = (int)h.n; w->view.k = (int)h.k; w->view.n_pad = (int)h.n_pad; w->view.k_pad = (int)h.k_pad;
+    w->view.data = w->base;
+    *out = w;
+    return SLC_OK;
+}
+
 slc_result slc_weight_shape(slc_weight *w, int32_t *format, int64_t *n, int64_t *k, int64_t *device_bytes)
 {
     if (!w) return fail(SLC_ERR_INVALID_ARGUMENT, "weight is null");

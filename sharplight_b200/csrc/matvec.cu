@@ -600,6 +600,15 @@ static cudaError_t launch_one(const WeightView &w, const WeightView &w2, const A
         configured[dev] = true;
     }
     const int warps = matvec_warps(w);
+    if (ex.world > 1) {
+        // a CTA that exchanges waits for the peers' CTAs of the same index: every CTA of the grid must be able to be
+        // resident at once, or a wait could depend on a CTA that has not started (it would time out, not hang; refused)
+        int per_sm = 0, sms = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, warps * 32, matvec_smem(FMT, warps, M, w.k_pad, DUAL));
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+        if (w.n_pad / 16 > per_sm * sms) return cudaErrorLaunchOutOfResources;
+    }
     return launch_pdl(kernel, dim3(w.n_pad / 16), dim3(warps * 32), matvec_smem(FMT, warps, M, w.k_pad, DUAL), stream, w, w2,
                       a, row0, y, y_stride, dump, status, early, ex, ep);
 }

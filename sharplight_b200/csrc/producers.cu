@@ -38,13 +38,14 @@ __device__ __forceinline__ void load4(const void *xv, long long base, bool live,
     }
 }
 
-// One CTA per (padded) row: sum of squares over K, then the row is read again (from L1 / L2), scaled and quantized.
+// One CTA of 1024 threads per (padded) row: sum of squares over K, then the row is read again (from L1 / L2), scaled and
+// quantized.
 template <int DTYPE>
-__global__ void __launch_bounds__(256) rmsnorm_quantize_kernel(const void *__restrict__ xv, int rows, int rows_pad, int k, int k_pad,
+__global__ void __launch_bounds__(1024) rmsnorm_quantize_kernel(const void *__restrict__ xv, int rows, int rows_pad, int k, int k_pad,
                                                                long long x_stride, const float *__restrict__ weight, float eps,
                                                                float *y, long long y_stride, ActPlanes out)
 {
-    __shared__ float warp_sums[8];
+    __shared__ float warp_sums[32];
     __shared__ float scale_s;
     const int row = blockIdx.x;
     const bool row_live = row < rows;
@@ -53,7 +54,7 @@ __global__ void __launch_bounds__(256) rmsnorm_quantize_kernel(const void *__res
 
     float sum = 0.0f;
     if (row_live) {
-        for (int i = threadIdx.x * 4; i < k; i += 256 * 4) {
+        for (int i = threadIdx.x * 4; i < k; i += 1024 * 4) {
             float v[4];
             load4<DTYPE>(xv, (long long)row * x_stride + i, true, v);
             sum = fmaf(v[0], v[0], sum); sum = fmaf(v[1], v[1], sum); sum = fmaf(v[2], v[2], sum); sum = fmaf(v[3], v[3], sum);
@@ -64,7 +65,7 @@ __global__ void __launch_bounds__(256) rmsnorm_quantize_kernel(const void *__res
     __syncthreads();
     if (threadIdx.x == 0) {
         float t = 0.0f;
-        for (int i = 0; i < 8; i++) t += warp_sums[i];
+        for (int i = 0; i < 32; i++) t += warp_sums[i];
         scale_s = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)k), eps)));
     }
     __syncthreads();
@@ -72,7 +73,7 @@ __global__ void __launch_bounds__(256) rmsnorm_quantize_kernel(const void *__res
 
     // blocks of 32 values, eight lanes each; k_pad is a multiple of 256, so whole warps stay together
     const int sub = threadIdx.x & 7;
-    for (int blk = threadIdx.x >> 3; blk < (k_pad >> 5); blk += 32) {
+    for (int blk = threadIdx.x >> 3; blk < (k_pad >> 5); blk += 128) {
         const bool live = row_live && blk * 32 < k;
         float v[4];
         load4<DTYPE>(xv, (long long)row * x_stride + blk * 32 + sub * 4, live, v);
@@ -154,10 +155,10 @@ cudaError_t launch_rmsnorm_quantize(const void *x, int x_dtype, int rows, int ro
 {
     if (rows_pad == 0) return cudaSuccess;
     if (x_dtype == 0) {
-        return launch_pdl(rmsnorm_quantize_kernel<0>, dim3(rows_pad), dim3(256), 0, stream, x, rows, rows_pad, k, k_pad, x_stride,
+        return launch_pdl(rmsnorm_quantize_kernel<0>, dim3(rows_pad), dim3(1024), 0, stream, x, rows, rows_pad, k, k_pad, x_stride,
                           weight, eps, y, y_stride, out);
     }
-    return launch_pdl(rmsnorm_quantize_kernel<1>, dim3(rows_pad), dim3(256), 0, stream, x, rows, rows_pad, k, k_pad, x_stride,
+    return launch_pdl(rmsnorm_quantize_kernel<1>, dim3(rows_pad), dim3(1024), 0, stream, x, rows, rows_pad, k, k_pad, x_stride,
                       weight, eps, y, y_stride, out);
 }
 

@@ -510,6 +510,14 @@ static cudaError_t launch_cfg(const WeightView &w, const ActView &a, int row0, i
     }
     const int rg_count = w.n_pad >> 4;
     const int ctas = (rg_count + SK_RGS - 1) / SK_RGS;
+    if (ex.world > 1) {
+        // as in the mat-vec: an exchanging grid must fit the machine at once
+        int per_sm = 0, sms = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, SK_WARPS * 32, smem);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+        if (ctas > per_sm * sms) return cudaErrorLaunchOutOfResources;
+    }
     // K chunks when the row tiles alone leave CTA slots empty (4 CTAs of the small token tiles fit an SM, 2 of the large
     // ones): at least four super-tiles per chunk, at most 8 chunks, and only while the partial tiles fit the scratch area
     int split = 1;

@@ -78,6 +78,9 @@ SIGNATURES = {
     "slc_weight_upload_kslice": (_i32, [_vp, _i32, _i64, _i64, _vp, _i64, _i64, _i64, _P(_vp)]),
     "slc_weight_download": (_i32, [_vp, _vp, _i64]),
     "slc_weight_shape": (_i32, [_vp, _P(_i32), _P(_i64), _P(_i64), _P(_i64)]),
+    "slc_weight_layout_bytes": (_i32, [_vp, _P(_i64)]),
+    "slc_weight_export_layout": (_i32, [_vp, _vp, _i64]),
+    "slc_weight_import_layout": (_i32, [_vp, _vp, _i64, _P(_vp)]),
     "slc_weight_free": (None, [_vp]),
     "slc_matmul_create": (_i32, [_vp, _vp, _i64, _u32, _P(_vp)]),
     "slc_matmul_create_dual": (_i32, [_vp, _vp, _vp, _i64, _u32, _P(_vp)]),

@@ -247,6 +247,14 @@ class DeviceWeight:
         _check(N.load().slc_weight_download(self.handle, out.ctypes.data_as(C.c_void_p), out.size))
         return out
 
+    def export_layout(self) -> np.ndarray:
+        """The device layout as an artefact (header + re-laid-out records) for CudaDevice.import_weight_layout."""
+        b = C.c_int64(0)
+        _check(N.load().slc_weight_layout_bytes(self.handle, C.byref(b)))
+        out = np.empty(b.value, np.uint8)
+        _check(N.load().slc_weight_export_layout(self.handle, out.ctypes.data_as(C.c_void_p), out.size))
+        return out
+
     def dispose(self) -> None:
         if self._h is not None:
             N.load().slc_weight_free(self._h)
@@ -340,6 +348,15 @@ class CudaDevice:
             _check(N.load().slc_weight_upload_kslice(self.handle, fmt, n, k, ptr, blocks.size, k0, k1, C.byref(h)))
             k = k1 - k0
         return DeviceWeight(self, fmt, n, k, h.value)
+
+    def import_weight_layout(self, artefact) -> DeviceWeight:
+        """Uploads an artefact written by DeviceWeight.export_layout: no raw blocks, no re-layout pass."""
+        artefact = np.ascontiguousarray(artefact, np.uint8).reshape(-1)
+        h = C.c_void_p()
+        _check(N.load().slc_weight_import_layout(self.handle, artefact.ctypes.data_as(C.c_void_p), artefact.size, C.byref(h)))
+        fmt, n, k = C.c_int32(0), C.c_int64(0), C.c_int64(0)
+        _check(N.load().slc_weight_shape(h, C.byref(fmt), C.byref(n), C.byref(k), None))
+        return DeviceWeight(self, fmt.value, n.value, k.value, h.value)
 
     def compile(self, segment: GraphSegment, options: CompileOptions) -> "CudaSegment":
         for node in segment.nodes:

@@ -688,3 +688,31 @@ def test_views_in_front_of_matmuls(cuda_device):
     with pytest.raises(Exception):
         cuda_device.compile(GraphSegment([ViewNode("v", "x", "xs", "slice", 1024, start=1000, length=100)], ["x"], []),
                             CompileOptions(max_rows=2))
+
+
+# ---- the device layout as an artefact ---------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("type_name,n,k", [("Q4_K", 100, 1024), ("Q8_0", 37, 1568), ("Q6_K", 4112, 512), ("Q4_0", 7, 96)])
+def test_weight_layout_artefact_round_trip(cuda_device, type_name, n, k):
+    """Export the re-laid-out records, import them on the device without the raw blocks: the same weight (raw blocks
+    come back byte for byte) and the same MatMul bits; a damaged or foreign artefact is refused."""
+    blocks = synth.weight_blocks(type_name, n, k, seed=n)
+    x = synth.activations(5, k, seed=k)
+    w = cuda_device.upload_weight(type_name, (n, k), blocks)
+    art = w.export_layout()
+    w2 = cuda_device.import_weight_layout(art)
+    op, op2 = MatMulOp(cuda_device, w, 5), MatMulOp(cuda_device, w2, 5)
+    try:
+        assert (w2.n, w2.k, w2.format) == (n, k, FMT_OF[type_name])
+        assert np.array_equal(w2.download(), blocks)
+        assert np.array_equal(op.run(x).view(np.uint32), op2.run(x).view(np.uint32))
+        bad = art.copy(); bad[0] ^= 0xFF
+        with pytest.raises(Exception):
+            cuda_device.import_weight_layout(bad)
+        with pytest.raises(Exception):
+            cuda_device.import_weight_layout(art[:-16])
+        newer = art.copy(); newer[4] = 99
+        with pytest.raises(NotSupportedError):
+            cuda_device.import_weight_layout(newer)
+    finally:
+        op.dispose(); op2.dispose(); w.dispose(); w2.dispose()
