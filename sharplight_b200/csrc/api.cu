@@ -811,6 +811,8 @@ slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act, float *
     return run_kernels(op, act, y, y_stride, nullptr, s);
 }
 
+static const int CHUNKED_SUM_MIN_ROWS = 1 << 30;   // (the chunked, overlapped prefill sum: off until it has been run on two GPUs)
+
 // A row-split MatMul of a tensor-parallel group: the sum over the ranks happens inside the MatMul kernel (exchange) for
 // few rows, and by the attached communicator's all-reduce above the exchange's in_kernel_rows (or its row bound).
 static slc_result run_summed(slc_matmul *op, slc_activation *act, slc_tp_exchange *x, float *y, long long y_stride,
@@ -824,11 +826,39 @@ static slc_result run_summed(slc_matmul *op, slc_activation *act, slc_tp_exchang
         if (rows > x->max_rows) return fail(SLC_ERR_UNSUPPORTED, "rows exceed the exchange's bound and no communicator is attached");
         return run_kernels(op, act, y, y_stride, nullptr, s, &x->view, ep);
     }
-    slc_result r = run_kernels(op, act, y, y_stride, nullptr, s, nullptr, nullptr);
-    if (r != SLC_OK) return r;
-    const int e = tp_comm_allreduce(x->comm->comm, y, rows, op->w->n, y_stride, s);
-    if (e != 0) return fail(SLC_ERR_CUDA, tp_comm_error(e));
-    op->last_launches++;
+    const long long n = op->w->n;
+    const int kernel = choose_kernel(op, rows, false);
+    if (kernel == SLC_KERNEL_MMQ && rows >= CHUNKED_SUM_MIN_ROWS && !op->w2 && act->planes.q_tiled) {
+        // Prefill: the rows in four chunks of whole 128-token tiles; the all-reduce of chunk i runs on the communicator's
+        // own stream while the GEMM of chunk i + 1 runs on the caller's, and the caller's stream joins at the end. (Forks
+        // and joins by events, so the whole thing can sit inside a captured graph.)
+        slc_tp_comm *c = x->comm;
+        const ActView av = view_of(act);
+        const int tiles = (rows + 127) / 128, per = (tiles + 3) / 4;
+        op->last_kernel = kernel;
+        op->last_launches = 0;
+        op->last_launches_total = 0;
+        int ci = 0;
+        for (int t0 = 0; t0 < tiles; t0 += per, ci++) {
+            const int cnt = tiles - t0 < per ? tiles - t0 : per;
+            const long long r0 = (long long)t0 * 128, r1 = r0 + (long long)cnt * 128 < rows ? r0 + (long long)cnt * 128 : rows;
+            SLC_CUDA(launch_mmq(op->w->view, av, act->planes.q_tiled, y, y_stride, nullptr, op->dev->status_dev, 0, s, nullptr, t0, cnt));
+            SLC_CUDA(cudaEventRecord(c->chunk_done[ci], s));
+            SLC_CUDA(cudaStreamWaitEvent(c->side, c->chunk_done[ci], 0));
+            const int e = tp_comm_allreduce(c->comm, y + r0 * y_stride, r1 - r0, n, y_stride, c->side);
+            if (e != 0) return fail(SLC_ERR_CUDA, tp_comm_error(e));
+            op->last_launches += 2;
+        }
+        SLC_CUDA(cudaEventRecord(c->joined, c->side));
+        SLC_CUDA(cudaStreamWaitEvent(s, c->joined, 0));
+        act->reads_since_quantize++;
+    } else {
+        slc_result r = run_kernels(op, act, y, y_stride, nullptr, s, nullptr, nullptr);
+        if (r != SLC_OK) return r;
+        const int e = tp_comm_allreduce(x->comm->comm, y, rows, n, y_stride, s);
+        if (e != 0) return fail(SLC_ERR_CUDA, tp_comm_error(e));
+        op->last_launches++;
+    }
     if (ep) {
         SLC_CUDA(launch_add_epilogue(y, y_stride, rows, (int)op->w->n, *ep, s));
         op->last_launches++;
@@ -983,6 +1013,13 @@ slc_result slc_tp_comm_create(slc_device *d, int32_t rank, int32_t world, const 
         delete c;
         return fail(SLC_ERR_CUDA, tp_comm_error(e));
     }
+    cudaError_t ce = cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking);
+    for (int i = 0; i < 8 && ce == cudaSuccess; i++) ce = cudaEventCreateWithFlags(&c->chunk_done[i], cudaEventDisableTiming);
+    if (ce == cudaSuccess) ce = cudaEventCreateWithFlags(&c->joined, cudaEventDisableTiming);
+    if (ce != cudaSuccess) {
+        slc_tp_comm_destroy(c);
+        return cuda_fail(ce, "slc_tp_comm_create");
+    }
     *out = c;
     return SLC_OK;
 }
@@ -993,6 +1030,11 @@ void slc_tp_comm_destroy(slc_tp_comm *c)
     cudaSetDevice(c->dev->index);
     cudaDeviceSynchronize();
     if (c->comm) tp_comm_destroy(c->comm);
+    for (int i = 0; i < 8; i++) {
+        if (c->chunk_done[i]) cudaEventDestroy(c->chunk_done[i]);
+    }
+    if (c->joined) cudaEventDestroy(c->joined);
+    if (c->side) cudaStreamDestroy(c->side);
     delete c;
 }
 

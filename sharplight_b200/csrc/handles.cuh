@@ -67,6 +67,10 @@ struct slc_tp_comm
     slc_device *dev = nullptr;
     int rank = 0, world = 0;
     void *comm = nullptr;   // ncclComm_t
+    // a stream of its own and events for prefill-sized sums: the all-reduce of one chunk of rows runs beside the GEMM of
+    // the next
+    cudaStream_t side = nullptr;
+    cudaEvent_t chunk_done[8] = {}, joined = nullptr;
 };
 
 struct slc_tp_exchange

@@ -174,7 +174,8 @@ cudaError_t launch_skinny(const WeightView &w, const ActView &a, int row0, int r
 // a bounded wait runs out.
 bool mmq_supports(int fmt);
 cudaError_t launch_mmq(const WeightView &w, const ActView &a, const uint8_t *q_tiled, float *y, long long y_stride,
-                       int *dump, int *status, int early, cudaStream_t stream, const Epilogue *epilogue = nullptr);
+                       int *dump, int *status, int early, cudaStream_t stream, const Epilogue *epilogue = nullptr,
+                       int tile_t0 = 0, int tile_count = 0);
 
 // umma.cu: tcgen05 kind::f16 tiles for 3 rows and more (Q4_K, Q4_0, Q8_0), stream-K over one persistent CTA per SM.
 // q_sw / sx2: the tiled planes the quantizer wrote for these rows (rows_pad a multiple of umma_token_tile(rows));

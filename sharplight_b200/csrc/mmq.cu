@@ -274,14 +274,14 @@ __device__ __forceinline__ void mq_store(const MqRegs<FMT> &rr, int rgl, int lan
 template <int FMT, bool DUMP>
 __global__ void __launch_bounds__(MQ_THREADS, 1)
 mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_tiled, float *__restrict__ y,
-           long long y_stride, int *dump, int *status, int early, const Epilogue ep)
+           long long y_stride, int *dump, int *status, int early, const Epilogue ep, int tile_t0)
 {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ MqSmem sh;
     // 1024-byte alignment of the tiles
     unsigned char *smem = smem_raw + ((1024 - (mq_smem(smem_raw) & 1023)) & 1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * MQ_TILE_N, t0 = blockIdx.y * MQ_TILE_T;
+    const int n0 = blockIdx.x * MQ_TILE_N, t0 = ((int)blockIdx.y + tile_t0) * MQ_TILE_T;   // tile_t0: first token tile of this launch
     const int nst = w.k_pad >> 8;
     constexpr bool HAS_MIN = FMT == FMT_Q4_K;
     constexpr int MQ_STAGES = mq_stages(FMT), MQ_STAGE_BYTES = mq_stage_bytes(FMT);
@@ -536,7 +536,8 @@ bool mmq_supports(int fmt) { return fmt == FMT_Q4_0 || fmt == FMT_Q8_0 || fmt ==
 
 template <int FMT, bool DUMP>
 static cudaError_t mmq_launch_one(const WeightView &w, const ActView &a, const uint8_t *q_tiled, float *y,
-                                  long long y_stride, int *dump, int *status, int early, cudaStream_t stream, const Epilogue &ep)
+                                  long long y_stride, int *dump, int *status, int early, cudaStream_t stream, const Epilogue &ep,
+                                  int tile_t0, int tile_count)
 {
     static bool configured[64] = {};
     int dev = 0;
@@ -547,21 +548,27 @@ static cudaError_t mmq_launch_one(const WeightView &w, const ActView &a, const u
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    const dim3 grid((w.n_pad + MQ_TILE_N - 1) / MQ_TILE_N, (a.rows + MQ_TILE_T - 1) / MQ_TILE_T);
-    return launch_pdl(kernel, grid, dim3(MQ_THREADS), mq_smem_bytes(FMT), stream, w, a, q_tiled, y, y_stride, dump, status, early, ep);
+    const int tiles_t = (a.rows + MQ_TILE_T - 1) / MQ_TILE_T;
+    if (tile_t0 < 0 || tile_t0 >= tiles_t) return cudaErrorInvalidValue;
+    if (tile_count <= 0 || tile_t0 + tile_count > tiles_t) tile_count = tiles_t - tile_t0;
+    const dim3 grid((w.n_pad + MQ_TILE_N - 1) / MQ_TILE_N, tile_count);
+    return launch_pdl(kernel, grid, dim3(MQ_THREADS), mq_smem_bytes(FMT), stream, w, a, q_tiled, y, y_stride, dump, status, early, ep, tile_t0);
 }
 
 // a.rows_pad must be a multiple of 128 and q_tiled the core-matrix copy of the activation codes (quantize.cu).
+// tile_t0 / tile_count: only the 128-token tiles [tile_t0, tile_t0 + tile_count) (0 / 0: all), for callers that want the
+// rows in chunks (a sum over ranks of one chunk while the next is computed).
 cudaError_t launch_mmq(const WeightView &w, const ActView &a, const uint8_t *q_tiled, float *y, long long y_stride,
-                       int *dump, int *status, int early, cudaStream_t stream, const Epilogue *epilogue)
+                       int *dump, int *status, int early, cudaStream_t stream, const Epilogue *epilogue, int tile_t0,
+                       int tile_count)
 {
     if (w.n_pad == 0 || a.rows == 0) return cudaSuccess;
     const Epilogue ep = epilogue ? *epilogue : Epilogue{ nullptr, nullptr, 0 };
     if ((a.rows_pad % MQ_TILE_T) != 0 || !q_tiled) return cudaErrorInvalidValue;
 #define SLC_FMT(F)                                                                                 \
     case F:                                                                                        \
-        return dump ? mmq_launch_one<F, true>(w, a, q_tiled, y, y_stride, dump, status, early, stream, ep)    \
-                    : mmq_launch_one<F, false>(w, a, q_tiled, y, y_stride, nullptr, status, early, stream, ep);
+        return dump ? mmq_launch_one<F, true>(w, a, q_tiled, y, y_stride, dump, status, early, stream, ep, tile_t0, tile_count)    \
+                    : mmq_launch_one<F, false>(w, a, q_tiled, y, y_stride, nullptr, status, early, stream, ep, tile_t0, tile_count);
     switch (w.fmt) {
         SLC_FMT(FMT_Q4_0) SLC_FMT(FMT_Q8_0) SLC_FMT(FMT_Q4_K)
     default: return cudaErrorInvalidValue;

@@ -143,3 +143,21 @@ def test_managed_pinvoke_list_covers_the_header():
     exported = set(re.findall(r"SLC_API\s+[\w\s\*]+?\b(slc_[a-z0-9_]+)\s*\(", header))
     imported = set(re.findall(r"static partial [\w\*]+ (slc_[a-z0-9_]+)\(", managed))
     assert exported and exported == imported, (sorted(exported - imported), sorted(imported - exported))
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` (the restated reference CPU path on the host cores) runs without a GPU and prints one
+    JSON line with the keys the measurement contract names, on the same metric, unit and workload as the GPU arm."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=600, cwd=root)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
+    assert line["impl"] == "reference" and line["metric"] == "quant MatMul weight GB/s" and line["unit"] == "GB/s"
+    assert line["higher_is_better"] is True and line["value"] > 0 and line["n_gpus"] == 1
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1 and line["cpu_baseline"]["sample"]
+    assert line["e2e"]["value"] == line["value"] and line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
+    assert "70B" in line["config"]["workload"]

@@ -167,9 +167,10 @@ def _two_gpu_worker(rank, world, port, out):
                 # the library's own NCCL communicator takes the sums above in_kernel_rows and above the exchange's bound
                 comm = TpComm.for_group(device, dist)
                 ex.set_comm(comm, 16)
-                op_big = MatMulOp(device, w, 256)
-                act_big = SharedActivation(device, 256, sk)
-                for call, rows in enumerate((8, 17, 64, 200)):
+                op_big = MatMulOp(device, w, 1280)
+                act_big = SharedActivation(device, 1280, sk)
+                # (1100 rows: the prefill path, rows in four chunks whose all-reduces run beside the next chunk's GEMM)
+                for call, rows in enumerate((8, 17, 64, 200, 1100)):
                     x_full = synth.activations(rows, k, seed=170 + call)
                     ref, _, _ = sl_oracle.matmul_intdot(fmt, blocks, n, k, x_full)
                     x = torch.from_numpy(np.ascontiguousarray(x_full[:, k0:k0 + sk])).cuda()
