@@ -259,8 +259,10 @@ class TpStack:
         for layer_ops in self.ops:
             for key in ("x_attn", "x_o", "x_ffn", "x_down"):
                 x = self.x[key]
-                self.act[key].quantize(x.data_ptr(), N.F32, rows, x.shape[1], sp)
-                launches += 1
+                # every input of this stack has one consumer (q/k/v and gate/up are stacked): the rows are handed over as
+                # they are and the library quantizes them at that MatMul -- inside the mat-vec kernel when K is a short
+                # tensor-parallel shard, through the quantizer kernel otherwise (counted in the MatMul's launches)
+                self.act[key].set_rows(x.data_ptr(), N.F32, rows, x.shape[1], sp)
                 for name, _, _, split, inp in self.specs:
                     if inp != key:
                         continue

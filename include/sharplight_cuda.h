@@ -241,6 +241,13 @@ SLC_API void slc_activation_destroy(slc_activation *act);
    from zero (src/Sharplight.Cpu/IntDot.cs:92-126). Asynchronous on the stream. */
 SLC_API slc_result slc_activation_quantize(slc_activation *act, const void *x_device, int32_t x_dtype, int64_t rows,
                                            int64_t x_stride, void *stream);
+/* Deferred quantization: the rows are handed over as they are (device, f32 or bf16) and quantized when the first MatMul
+   that reads them runs -- inside that MatMul's kernel when it is a mat-vec (up to 4 rows per launch) over a short K
+   (K <= 2048: a tensor-parallel shard; one launch and one boundary on the dependent chain less), by the quantizer
+   kernel on that MatMul's stream otherwise. x must stay unchanged until the MatMuls that read it have run. Results are
+   bit-identical to slc_activation_quantize followed by the same MatMul. */
+SLC_API slc_result slc_activation_set_rows(slc_activation *act, const void *x_device, int32_t x_dtype, int64_t rows,
+                                           int64_t x_stride, void *stream);
 /* Producers: the operation in front of a MatMul writes the 8-bit activations itself, in the same pass (the reference
    lets its norm kernels write the copy the next MatMul reads, src/Sharplight.Shaders/Lowering/GraphLowerer.IntDot.cs:146-184).
    Both fill `act` exactly as slc_activation_quantize would from the f32 values they compute; y (optional, device) also

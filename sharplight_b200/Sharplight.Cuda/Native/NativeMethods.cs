@@ -63,6 +63,7 @@ internal static unsafe partial class NativeMethods
     [LibraryImport(Library)] public static partial int slc_activation_create(nint device, long maxRows, long k, out nint act);
     [LibraryImport(Library)] public static partial void slc_activation_destroy(nint act);
     [LibraryImport(Library)] public static partial int slc_activation_quantize(nint act, nint xDevice, int xDtype, long rows, long xStride, nint stream);
+    [LibraryImport(Library)] public static partial int slc_activation_set_rows(nint act, nint xDevice, int xDtype, long rows, long xStride, nint stream);
     [LibraryImport(Library)] public static partial int slc_activation_quantize_rmsnorm(nint act, nint xDevice, int xDtype, long rows, long xStride, nint weightDevice, float eps, nint yDevice, long yStride, nint stream);
     [LibraryImport(Library)] public static partial int slc_activation_quantize_silu_mul(nint act, nint gateDevice, long gateStride, nint upDevice, long upStride, long rows, nint yDevice, long yStride, nint stream);
     [LibraryImport(Library)] public static partial int slc_argmax_rows(nint device, nint yDevice, long rows, long n, long yStride, nint outIndexDevice, nint stream);

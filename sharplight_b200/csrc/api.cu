@@ -532,6 +532,7 @@ static slc_result begin_fill(slc_activation *a, int64_t rows, void *stream, cuda
     a->planes.sx2 = rows >= 3 ? a->sx2 : nullptr;
     a->reads_since_quantize = 0;
     a->quantize_stream = *s;
+    a->pending = false;
     return SLC_OK;
 }
 
@@ -546,6 +547,25 @@ slc_result slc_activation_quantize(slc_activation *a, const void *x, int32_t x_d
     slc_result r = begin_fill(a, rows, stream, &s);
     if (r != SLC_OK || rows == 0) return r;
     SLC_CUDA(launch_quantize(x, x_dtype, a->rows, a->rows_pad, (int)a->k, a->k_pad, x_stride, a->planes, s));
+    return SLC_OK;
+}
+
+// Up to this K the mat-vec quantizes deferred rows itself; beyond it the quantizer kernel runs first. Every CTA redoes
+// the row before its dots can start, so it pays only for short rows -- measured per dependent (quantize +) mat-vec on
+// [8192, K] Q4_K at one row: K = 1024 4.17 -> 2.99 us, 2048 5.96 -> 5.29, 3584 7.69 -> 8.11, 4096 8.00 -> 8.66.
+static const int FUSED_QUANTIZE_MAX_K = 2048;
+
+slc_result slc_activation_set_rows(slc_activation *a, const void *x, int32_t x_dtype, int64_t rows, int64_t x_stride, void *stream)
+{
+    if (!a) return fail(SLC_ERR_INVALID_ARGUMENT, "activation is null");
+    if (x_dtype != SLC_F32 && x_dtype != SLC_BF16) return fail(SLC_ERR_UNSUPPORTED, "activation dtype must be f32 or bf16");
+    if (rows > 0 && !x) return fail(SLC_ERR_INVALID_ARGUMENT, "x is null");
+    if (rows > 0 && x_stride < a->k) return fail(SLC_ERR_INVALID_ARGUMENT, "x_stride < K");
+    cudaStream_t s = nullptr;
+    slc_result r = begin_fill(a, rows, stream, &s);
+    if (r != SLC_OK || rows == 0) return r;
+    a->pending = true;
+    a->pending_x = x; a->pending_dtype = x_dtype; a->pending_stride = x_stride;
     return SLC_OK;
 }
 
@@ -601,6 +621,7 @@ static ActView view_of(const slc_activation *a)
     v.rows = a->rows; v.rows_pad = a->rows_pad; v.k = (int)a->k; v.k_pad = a->k_pad;
     v.q = a->planes.q; v.ds = a->planes.ds; v.dx = a->planes.dx; v.sx = a->planes.sx; v.gs = a->planes.gs;
     v.isum = a->planes.isum;
+    if (a->pending) { v.raw = a->pending_x; v.raw_dtype = a->pending_dtype; v.raw_stride = a->pending_stride; }
     return v;
 }
 
@@ -718,11 +739,24 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
                               cudaStream_t s, const Exchange *ex = nullptr, const Epilogue *ep = nullptr)
 {
     if (op->flags & SLC_MATMUL_F32_ACTIVATIONS) return fail(SLC_ERR_INVALID_STATE, "this op keeps f32 activations: it takes no quantized ones");
-    const ActView av = view_of(act);
     const int rows = act->rows;
     const int kernel = choose_kernel(op, rows, ex != nullptr);
+    bool ran_quantizer = false;
+    if (act->pending) {
+        // deferred rows: the mat-vec quantizes them itself when K is short; otherwise the quantizer runs now, on this
+        // stream, and the planes are there for this and every later MatMul
+        const bool fuse = kernel == SLC_KERNEL_MMVQ && !dump && !op->w2 && act->k_pad <= FUSED_QUANTIZE_MAX_K;
+        if (!fuse) {
+            SLC_CUDA(launch_quantize(act->pending_x, act->pending_dtype, act->rows, act->rows_pad, (int)act->k, act->k_pad,
+                                     act->pending_stride, act->planes, s));
+            act->pending = false;
+            act->quantize_stream = s;
+            ran_quantizer = true;
+        }
+    }
+    const ActView av = view_of(act);
     op->last_kernel = kernel;
-    op->last_launches = 0;
+    op->last_launches = ran_quantizer ? 1 : 0;   // (the deferred quantizer counts as a launch of this call)
     op->last_launches_total = 0;
     if (op->w2) {
         // gate / up pair: one dual mat-vec launch where that kernel serves the row count, else gate -> scratch,
@@ -754,7 +788,7 @@ static slc_result run_family(slc_matmul *op, const WeightView &wv, const WeightV
     // when the launch reads more than the activations -- a bias or a residual, which the predecessor may be writing
     // (y2 = W2 x + y1 right after y1 = W1 x) -- or when it runs on another stream than the quantization did.
     auto early = [&]() {
-        return allow_early && !ex && !ep && act->reads_since_quantize > 0 && s == act->quantize_stream ? 1 : 0;
+        return allow_early && !ex && !ep && !act->pending && act->reads_since_quantize > 0 && s == act->quantize_stream ? 1 : 0;
     };
     if (kernel == SLC_KERNEL_MMVQ) {
         // chunks of up to 4 rows; every row of a chunk is computed exactly as a single row is, so the row-invariant
@@ -833,6 +867,12 @@ static slc_result run_summed(slc_matmul *op, slc_activation *act, slc_tp_exchang
         // own stream while the GEMM of chunk i + 1 runs on the caller's, and the caller's stream joins at the end. (Forks
         // and joins by events, so the whole thing can sit inside a captured graph.)
         slc_tp_comm *c = x->comm;
+        if (act->pending) {   // deferred rows: the GEMM reads the planes
+            SLC_CUDA(launch_quantize(act->pending_x, act->pending_dtype, act->rows, act->rows_pad, (int)act->k, act->k_pad,
+                                     act->pending_stride, act->planes, s));
+            act->pending = false;
+            act->quantize_stream = s;
+        }
         const ActView av = view_of(act);
         const int tiles = (rows + 127) / 128, per = (tiles + 3) / 4;
         op->last_kernel = kernel;

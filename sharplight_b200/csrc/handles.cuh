@@ -43,6 +43,11 @@ struct slc_activation
     int rows = 0, rows_pad = 0;   // what the last quantize call wrote
     int reads_since_quantize = 0;       // MatMul launches that have read the current contents ...
     cudaStream_t quantize_stream = nullptr;   // ... and the stream they were quantized on
+    // deferred quantization (slc_activation_set_rows): the rows as given, not yet in the planes
+    bool pending = false;
+    const void *pending_x = nullptr;
+    int pending_dtype = 0;
+    long long pending_stride = 0;
 };
 
 struct slc_matmul

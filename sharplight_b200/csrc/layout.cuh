@@ -103,6 +103,11 @@ struct ActView
     const float *sx;     // [k_pad/32][rows_pad] d * sum32(q) alone: the planes the tensor-core GEMM bulk-copies
     const float *gs;     // [rows_pad][k_pad/16]
     const int *isum;     // [rows_pad][k_pad/32]
+    // Deferred quantization (mat-vec only): when raw is set, the planes above have not been written; the kernel reads the
+    // rows themselves (f32 or bf16, raw_stride elements apart) and quantizes them into its shared memory.
+    const void *raw = nullptr;
+    int raw_dtype = 0;
+    long long raw_stride = 0;
 };
 
 // What a MatMul adds to its result before the store, the elementwise tail the reference's lowering folds into the

@@ -441,7 +441,54 @@ matvec_kernel(const WeightView w, const WeightView w2, const ActView a, int row0
     pdl_enter(early);
 
     // quantized activations -> shared memory
-    {
+    if (a.raw) {
+        // Deferred quantization: this CTA quantizes the rows itself, with the quantizer's arithmetic step for step
+        // (quantize.cuh: d = max|x| / 127, id = 1 / d, round half away from zero by truncation, separately rounded IEEE
+        // operations), eight lanes per 32-value block. Worth it when K is short (a tensor-parallel shard): the row is a few
+        // kilobytes from L2, and the launch of a quantizer with its boundary on the dependent chain is saved.
+        const int sub = threadIdx.x & 7;
+        for (int m = 0; m < M; m++) {
+            for (int blk = threadIdx.x >> 3; blk < nblk_pad; blk += blockDim.x >> 3) {
+                float v[4] = { 0.f, 0.f, 0.f, 0.f };
+                if (blk * 32 < a.k) {
+                    const long long base = (long long)(row0 + m) * a.raw_stride + blk * 32 + sub * 4;
+                    if (a.raw_dtype == 0) {
+                        const float *x = reinterpret_cast<const float *>(a.raw) + base;
+                        if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+                            const float4 f = *reinterpret_cast<const float4 *>(x);
+                            v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+                        } else {
+                            for (int i = 0; i < 4; i++) v[i] = x[i];
+                        }
+                    } else {
+                        const unsigned short *x = reinterpret_cast<const unsigned short *>(a.raw) + base;
+                        for (int i = 0; i < 4; i++) v[i] = __uint_as_float((unsigned)x[i] << 16);
+                    }
+                }
+                float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                const float d = __fdiv_rn(amax, 127.0f);
+                const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+                int r[4], s = 0;
+                for (int i = 0; i < 4; i++) {
+                    const float wv = __fmul_rn(v[i], id);
+                    r[i] = __float2int_rz(__fadd_rn(wv, copysignf(0.5f, wv)));
+                    s += r[i];
+                }
+                *reinterpret_cast<unsigned *>(sq + (size_t)m * w.k_pad + blk * 32 + sub * 4) =
+                    (unsigned)(r[0] & 0xff) | ((unsigned)(r[1] & 0xff) << 8) | ((unsigned)(r[2] & 0xff) << 16) | ((unsigned)(r[3] & 0xff) << 24);
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
+                s += __shfl_xor_sync(0xffffffffu, s, 4);
+                if (sub == 0) {
+                    sds[m * nblk_pad + blk] = make_float2(d, __fmul_rn(d, (float)s));
+                    if (DUMP) sisum[m * nblk_pad + blk] = s;
+                }
+            }
+        }
+    } else {
         const uint4 *src = reinterpret_cast<const uint4 *>(a.q + (long long)row0 * a.k_pad);
         uint4 *dst = reinterpret_cast<uint4 *>(sq);
         for (int i = threadIdx.x; i < M * (w.k_pad >> 4); i += blockDim.x) dst[i] = __ldg(src + i);

@@ -91,6 +91,7 @@ SIGNATURES = {
     "slc_activation_create": (_i32, [_vp, _i64, _i64, _P(_vp)]),
     "slc_activation_destroy": (None, [_vp]),
     "slc_activation_quantize": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp]),
+    "slc_activation_set_rows": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp]),
     "slc_activation_quantize_rmsnorm": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp, C.c_float, _vp, _i64, _vp]),
     "slc_activation_quantize_silu_mul": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _vp]),
     "slc_buffer_densify": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),

@@ -483,6 +483,12 @@ class SharedActivation:
         _check(N.load().slc_activation_quantize(self.handle, C.c_void_p(x_device_ptr), dtype, rows, x_stride,
                                                 C.c_void_p(stream) if stream else None))
 
+    def set_rows(self, x_device_ptr: int, dtype: int, rows: int, x_stride: int, stream: int = 0) -> None:
+        """Deferred quantization (slc_activation_set_rows): the first MatMul that reads the rows quantizes them -- inside
+        its own kernel when it is a mat-vec over a short K, through the quantizer otherwise."""
+        _check(N.load().slc_activation_set_rows(self.handle, C.c_void_p(x_device_ptr), dtype, rows, x_stride,
+                                                C.c_void_p(stream) if stream else None))
+
     def quantize_rmsnorm(self, x_device_ptr: int, dtype: int, rows: int, x_stride: int, weight_ptr: int, eps: float,
                          y_device_ptr: int = 0, y_stride: int = 0, stream: int = 0) -> None:
         """RmsNorm and quantization in one pass (slc_activation_quantize_rmsnorm); y (optional) also gets the f32 values."""

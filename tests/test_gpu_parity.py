@@ -716,3 +716,38 @@ def test_weight_layout_artefact_round_trip(cuda_device, type_name, n, k):
             cuda_device.import_weight_layout(newer)
     finally:
         op.dispose(); op2.dispose(); w.dispose(); w2.dispose()
+
+
+# ---- deferred quantization: the mat-vec quantizes short rows itself ------------------------------------------------------
+
+@pytest.mark.parametrize("type_name", TYPES)
+@pytest.mark.parametrize("n,k,rows", [(64, 1024, 1), (200, 3584, 2), (48, 512, 4), (100, 4096, 1), (40, 8192, 1), (64, 1024, 8),
+                                      (33, 1568, 3)])
+def test_deferred_quantization_bit_identical(cuda_device, type_name, n, k, rows):
+    """slc_activation_set_rows + MatMul against slc_activation_quantize + the same MatMul: the same bits whether the
+    mat-vec quantized the rows inside its own kernel (K <= 2048, up to 4 rows per launch), or the quantizer ran at the
+    first use (longer K, more rows, other kernel families); a second MatMul on the same rows included."""
+    import torch
+    if k % N.BLOCK[FMT_OF[type_name]][0] != 0:
+        pytest.skip("K is not a multiple of this format's block size")
+    blocks = synth.weight_blocks(type_name, n, k, seed=n + k)
+    x = torch.from_numpy(synth.activations(rows, k + 5, seed=k)[:, 2:2 + k].copy()).cuda()     # (a contiguous copy)
+    xs = torch.from_numpy(synth.activations(rows, k + 8, seed=k)).cuda()                        # rows 8 elements wider than K
+    w = cuda_device.upload_weight(type_name, (n, k), blocks)
+    op = MatMulOp(cuda_device, w, rows)
+    a0, a1 = SharedActivation(cuda_device, rows, k), SharedActivation(cuda_device, rows, k)
+    try:
+        for src, stride in ((x, k), (xs, k + 8)):
+            y0 = torch.empty((rows, n), device="cuda"); y1 = torch.empty((rows, n), device="cuda"); y2 = torch.empty((rows, n), device="cuda")
+            a0.quantize(src.data_ptr(), N.F32, rows, stride)
+            a0.matmul(op, y0.data_ptr(), n)
+            a1.set_rows(src.data_ptr(), N.F32, rows, stride)
+            a1.matmul(op, y1.data_ptr(), n)
+            fused = op.last_kernel()[0] == N.KERNEL_MMVQ and k <= 2048
+            assert op.last_kernel()[1] == ((rows + 3) // 4 if fused else op.last_kernel()[1])
+            a1.matmul(op, y2.data_ptr(), n)
+            torch.cuda.synchronize()
+            assert torch.equal(y0, y1) and torch.equal(y0, y2), (type_name, n, k, rows)
+        assert cuda_device.last_status() == 0
+    finally:
+        a0.dispose(); a1.dispose(); op.dispose(); w.dispose()
