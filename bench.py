@@ -46,7 +46,7 @@ NOMINAL_INT8_TOPS = 4500.0
 KERNEL_NAMES = {1: "mmvq (dp4a)", 2: "skinny (int8 mma.sync)", 3: "mmq (tcgen05 kind::i8)", 4: "tile (tcgen05 kind::i8, stream-K)"}
 # dram__bytes_read.sum + dram__bytes_write.sum of one mat-vec launch on configuration 2 at M = 1, from one ncu capture
 # of this kernel (the algorithmic bytes are 33 092 608); quoted only while the kernel family of the run is the captured one
-CONFIG2_M1_DRAM_BYTES = 33062656
+CONFIG2_M1_DRAM_BYTES = 33071872
 
 
 def measured_peaks():
@@ -710,6 +710,15 @@ def run_ours(args):
                                          {name: KERNEL_NAMES.get(stack.ops[0][name].last_kernel()[0]) for name in stack.dims},
                       "allreduce": "none" if world == 1 else "in the MatMul kernel (peer stores)" if in_kernel else "ncclAllReduce issued by the library",
                       "allreduces_per_step": 2 * layers if world > 1 else 0}
+        if world > 1 and r >= 1024 and not args.tp_main_only:
+            # prefill: the sum over ranks in chunks beside the GEMM (the library's default from four ranks) against the
+            # unchunked form (its default on two)
+            chunked_by_default = world >= 4
+            stack.comm.set_chunking((1 << 30) if chunked_by_default else 1024)
+            other = time_graphed(torch, dist, world, stream, lambda sp, r=r: stack.step(r, sp), steps, 3, use_graph=not args.no_graph)
+            stack.comm.set_chunking(0)
+            by_rows[r]["prefill_sum"] = "in four chunks beside the GEMM" if chunked_by_default else "after the GEMM"
+            by_rows[r]["ms_per_step_unchunked" if chunked_by_default else "ms_per_step_chunked"] = other
         if world > 1 and r <= N.TP_MAX_ROWS and not args.tp_main_only:
             other = time_graphed(torch, dist, world, stream, lambda sp, r=r: stack.step(r, sp, in_kernel=not in_kernel),
                                  steps, 3, use_graph=not args.no_graph)

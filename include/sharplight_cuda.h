@@ -322,6 +322,10 @@ SLC_API slc_result slc_tp_comm_create(slc_device *device, int32_t rank, int32_t 
                                       const uint8_t *id /* [SLC_TP_COMM_ID_BYTES] */, slc_tp_comm **out);
 SLC_API void slc_tp_comm_destroy(slc_tp_comm *comm);
 SLC_API slc_result slc_tp_exchange_set_comm(slc_tp_exchange *exchange, slc_tp_comm *comm, int32_t in_kernel_rows);
+/* Prefill-sized sums run in four chunks of rows, the all-reduce of one chunk beside the GEMM of the next (the
+   communicator's own stream, joined back into the call's stream at the end). By default from 1024 rows in groups of four
+   ranks and more; min_rows > 0 makes it "from min_rows rows, whatever the group size", 0 restores the default. */
+SLC_API slc_result slc_tp_comm_set_chunking(slc_tp_comm *comm, int32_t min_rows);
 /* y (device, f32) = sum over ranks of (act . W^T), W being this rank's K range of the weight and act this rank's
    matching slice of the activations. Asynchronous on the stream. */
 /* The same with x not yet quantized (device, rows x k): slc_matmul_run with the sum over the ranks. */

@@ -77,6 +77,7 @@ internal static unsafe partial class NativeMethods
     [LibraryImport(Library)] public static partial int slc_tp_comm_unique_id(Span<byte> id128);
     [LibraryImport(Library)] public static partial int slc_tp_comm_create(nint device, int rank, int world, ReadOnlySpan<byte> id128, out nint comm);
     [LibraryImport(Library)] public static partial void slc_tp_comm_destroy(nint comm);
+    [LibraryImport(Library)] public static partial int slc_tp_comm_set_chunking(nint comm, int minRows);
     [LibraryImport(Library)] public static partial int slc_tp_exchange_set_comm(nint exchange, nint comm, int inKernelRows);
     [LibraryImport(Library)] public static partial int slc_matmul_run_allreduce(nint op, nint exchange, nint x, int xDtype, long rows, long xStride, nint y, long yStride, nint stream);
     [LibraryImport(Library)] public static partial int slc_matmul_run_quantized_allreduce(nint op, nint act, nint exchange, nint y, long yStride, nint stream);

@@ -845,7 +845,9 @@ slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act, float *
     return run_kernels(op, act, y, y_stride, nullptr, s);
 }
 
-static const int CHUNKED_SUM_MIN_ROWS = 1 << 30;   // (the chunked, overlapped prefill sum: off until it has been run on two GPUs)
+static const int CHUNKED_SUM_MIN_ROWS = 1024;   // from here the prefill sum over ranks runs in chunks beside the GEMM ...
+static const int CHUNKED_SUM_MIN_RANKS = 4;     // ... in groups of four ranks and more (on two ranks the sum is too short to
+                                                // pay for four smaller GEMM launches: 650 against 637 ms on the 70B stack)
 
 // A row-split MatMul of a tensor-parallel group: the sum over the ranks happens inside the MatMul kernel (exchange) for
 // few rows, and by the attached communicator's all-reduce above the exchange's in_kernel_rows (or its row bound).
@@ -862,7 +864,9 @@ static slc_result run_summed(slc_matmul *op, slc_activation *act, slc_tp_exchang
     }
     const long long n = op->w->n;
     const int kernel = choose_kernel(op, rows, false);
-    if (kernel == SLC_KERNEL_MMQ && rows >= CHUNKED_SUM_MIN_ROWS && !op->w2 && act->planes.q_tiled) {
+    const bool chunked = x->comm->chunk_min_rows > 0 ? rows >= x->comm->chunk_min_rows
+                                                     : rows >= CHUNKED_SUM_MIN_ROWS && x->world >= CHUNKED_SUM_MIN_RANKS;
+    if (kernel == SLC_KERNEL_MMQ && chunked && rows > 128 && !op->w2 && act->planes.q_tiled) {
         // Prefill: the rows in four chunks of whole 128-token tiles; the all-reduce of chunk i runs on the communicator's
         // own stream while the GEMM of chunk i + 1 runs on the caller's, and the caller's stream joins at the end. (Forks
         // and joins by events, so the whole thing can sit inside a captured graph.)
@@ -1076,6 +1080,14 @@ void slc_tp_comm_destroy(slc_tp_comm *c)
     if (c->joined) cudaEventDestroy(c->joined);
     if (c->side) cudaStreamDestroy(c->side);
     delete c;
+}
+
+slc_result slc_tp_comm_set_chunking(slc_tp_comm *c, int32_t min_rows)
+{
+    if (!c) return fail(SLC_ERR_INVALID_ARGUMENT, "communicator is null");
+    if (min_rows < 0) return fail(SLC_ERR_INVALID_ARGUMENT, "min_rows >= 0");
+    c->chunk_min_rows = min_rows;
+    return SLC_OK;
 }
 
 slc_result slc_tp_exchange_set_comm(slc_tp_exchange *x, slc_tp_comm *comm, int32_t in_kernel_rows)

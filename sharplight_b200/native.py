@@ -104,6 +104,7 @@ SIGNATURES = {
     "slc_tp_comm_unique_id": (_i32, [_vp]),
     "slc_tp_comm_create": (_i32, [_vp, _i32, _i32, _vp, _P(_vp)]),
     "slc_tp_comm_destroy": (None, [_vp]),
+    "slc_tp_comm_set_chunking": (_i32, [_vp, _i32]),
     "slc_tp_exchange_set_comm": (_i32, [_vp, _vp, _i32]),
     "slc_matmul_run_allreduce": (_i32, [_vp, _vp, _vp, _i32, _i64, _i64, _vp, _i64, _vp]),
     "slc_matmul_run_quantized_allreduce": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp]),

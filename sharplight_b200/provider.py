@@ -534,6 +534,10 @@ class TpComm:
         _check(N.load().slc_tp_comm_create(device.handle, rank, world, buf, C.byref(h)))
         self._h = h
 
+    def set_chunking(self, min_rows: int) -> None:
+        """Prefill sums in chunks beside the GEMM from ``min_rows`` rows whatever the group size; 0: the default policy."""
+        _check(N.load().slc_tp_comm_set_chunking(self.handle, min_rows))
+
     @staticmethod
     def unique_id() -> bytes:
         buf = (C.c_uint8 * N.TP_COMM_ID_BYTES)()

@@ -166,6 +166,7 @@ def _two_gpu_worker(rank, world, port, out):
             if type_name == "Q4_K":
                 # the library's own NCCL communicator takes the sums above in_kernel_rows and above the exchange's bound
                 comm = TpComm.for_group(device, dist)
+                comm.set_chunking(1024)          # two ranks are below the default policy's group size
                 ex.set_comm(comm, 16)
                 op_big = MatMulOp(device, w, 1280)
                 act_big = SharedActivation(device, 1280, sk)
