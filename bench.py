@@ -711,14 +711,12 @@ def run_ours(args):
                       "allreduce": "none" if world == 1 else "in the MatMul kernel (peer stores)" if in_kernel else "ncclAllReduce issued by the library",
                       "allreduces_per_step": 2 * layers if world > 1 else 0}
         if world > 1 and r >= 1024 and not args.tp_main_only:
-            # prefill: the sum over ranks in chunks beside the GEMM (the library's default from four ranks) against the
-            # unchunked form (its default on two)
-            chunked_by_default = world >= 4
-            stack.comm.set_chunking((1 << 30) if chunked_by_default else 1024)
+            # prefill: the library's option of summing over ranks in chunks beside the GEMM, against its default (after it)
+            stack.comm.set_chunking(1024)
             other = time_graphed(torch, dist, world, stream, lambda sp, r=r: stack.step(r, sp), steps, 3, use_graph=not args.no_graph)
             stack.comm.set_chunking(0)
-            by_rows[r]["prefill_sum"] = "in four chunks beside the GEMM" if chunked_by_default else "after the GEMM"
-            by_rows[r]["ms_per_step_unchunked" if chunked_by_default else "ms_per_step_chunked"] = other
+            by_rows[r]["prefill_sum"] = "after the GEMM"
+            by_rows[r]["ms_per_step_chunked"] = other
         if world > 1 and r <= N.TP_MAX_ROWS and not args.tp_main_only:
             other = time_graphed(torch, dist, world, stream, lambda sp, r=r: stack.step(r, sp, in_kernel=not in_kernel),
                                  steps, 3, use_graph=not args.no_graph)

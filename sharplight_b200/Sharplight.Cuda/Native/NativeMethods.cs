@@ -48,6 +48,13 @@ internal static unsafe partial class NativeMethods
     [LibraryImport(Library)] public static partial int slc_weight_upload_kslice(nint device, int format, long n, long k, void* blocks, long bytes, long k0, long k1, out nint weight);
     [LibraryImport(Library)] public static partial int slc_weight_download(nint weight, void* blocks, long bytes);
     [LibraryImport(Library)] public static partial int slc_weight_shape(nint weight, out int format, out long n, out long k, out long deviceBytes);
+    [LibraryImport(Library, StringMarshalling = StringMarshalling.Utf8)] public static partial int slc_gguf_open(string path, out nint file);
+    [LibraryImport(Library)] public static partial void slc_gguf_close(nint file);
+    [LibraryImport(Library)] public static partial int slc_gguf_tensor_count(nint file, out long count);
+    [LibraryImport(Library)] public static partial int slc_gguf_tensor_info(nint file, long index, byte* nameOut, int nameCapacity, out int format, out int rank, out long n, out long k, out long bytes);
+    [LibraryImport(Library, StringMarshalling = StringMarshalling.Utf8)] public static partial int slc_gguf_find(nint file, string name, out long index);
+    [LibraryImport(Library)] public static partial int slc_weight_upload_gguf(nint device, nint file, long index, out nint weight);
+    [LibraryImport(Library)] public static partial nint slc_gguf_last_error();
     [LibraryImport(Library)] public static partial int slc_weight_layout_bytes(nint weight, out long bytes);
     [LibraryImport(Library)] public static partial int slc_weight_export_layout(nint weight, void* outHost, long bytes);
     [LibraryImport(Library)] public static partial int slc_weight_import_layout(nint device, void* artefactHost, long bytes, out nint weight);

@@ -845,9 +845,9 @@ slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act, float *
     return run_kernels(op, act, y, y_stride, nullptr, s);
 }
 
-static const int CHUNKED_SUM_MIN_ROWS = 1024;   // from here the prefill sum over ranks runs in chunks beside the GEMM ...
-static const int CHUNKED_SUM_MIN_RANKS = 4;     // ... in groups of four ranks and more (on two ranks the sum is too short to
-                                                // pay for four smaller GEMM launches: 650 against 637 ms on the 70B stack)
+// The prefill sum over ranks in chunks beside the GEMM is an option (slc_tp_comm_set_chunking), not the default: on the
+// 70B-shaped stack at 2048 rows it measured 650 against 637 ms on two GPUs and 372 against 356 ms on four -- four smaller
+// GEMM launches and NCCL's kernels sharing the SMs with the GEMM cost more than hiding the all-reduce gains.
 
 // A row-split MatMul of a tensor-parallel group: the sum over the ranks happens inside the MatMul kernel (exchange) for
 // few rows, and by the attached communicator's all-reduce above the exchange's in_kernel_rows (or its row bound).
@@ -864,8 +864,7 @@ static slc_result run_summed(slc_matmul *op, slc_activation *act, slc_tp_exchang
     }
     const long long n = op->w->n;
     const int kernel = choose_kernel(op, rows, false);
-    const bool chunked = x->comm->chunk_min_rows > 0 ? rows >= x->comm->chunk_min_rows
-                                                     : rows >= CHUNKED_SUM_MIN_ROWS && x->world >= CHUNKED_SUM_MIN_RANKS;
+    const bool chunked = x->comm->chunk_min_rows > 0 && rows >= x->comm->chunk_min_rows;
     if (kernel == SLC_KERNEL_MMQ && chunked && rows > 128 && !op->w2 && act->planes.q_tiled) {
         // Prefill: the rows in four chunks of whole 128-token tiles; the all-reduce of chunk i runs on the communicator's
         // own stream while the GEMM of chunk i + 1 runs on the caller's, and the caller's stream joins at the end. (Forks

@@ -72,7 +72,7 @@ struct slc_tp_comm
     slc_device *dev = nullptr;
     int rank = 0, world = 0;
     void *comm = nullptr;   // ncclComm_t
-    int chunk_min_rows = 0;  // 0: the default policy (1024 rows, four ranks and more); > 0: chunk from this row count
+    int chunk_min_rows = 0;  // > 0: prefill sums from this row count run in chunks beside the GEMM; 0 (default): after it
     // a stream of its own and events for prefill-sized sums: the all-reduce of one chunk of rows runs beside the GEMM of
     // the next
     cudaStream_t side = nullptr;

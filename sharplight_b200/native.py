@@ -78,6 +78,13 @@ SIGNATURES = {
     "slc_weight_upload_kslice": (_i32, [_vp, _i32, _i64, _i64, _vp, _i64, _i64, _i64, _P(_vp)]),
     "slc_weight_download": (_i32, [_vp, _vp, _i64]),
     "slc_weight_shape": (_i32, [_vp, _P(_i32), _P(_i64), _P(_i64), _P(_i64)]),
+    "slc_gguf_open": (_i32, [C.c_char_p, _P(_vp)]),
+    "slc_gguf_close": (None, [_vp]),
+    "slc_gguf_tensor_count": (_i32, [_vp, _P(_i64)]),
+    "slc_gguf_tensor_info": (_i32, [_vp, _i64, C.c_char_p, _i32, _P(_i32), _P(_i32), _P(_i64), _P(_i64), _P(_i64)]),
+    "slc_gguf_find": (_i32, [_vp, C.c_char_p, _P(_i64)]),
+    "slc_weight_upload_gguf": (_i32, [_vp, _vp, _i64, _P(_vp)]),
+    "slc_gguf_last_error": (C.c_char_p, []),
     "slc_weight_layout_bytes": (_i32, [_vp, _P(_i64)]),
     "slc_weight_export_layout": (_i32, [_vp, _vp, _i64]),
     "slc_weight_import_layout": (_i32, [_vp, _vp, _i64, _P(_vp)]),
