@@ -45,6 +45,15 @@ __device__ __forceinline__ void mma_s8s8_k16(int c[4], unsigned a0, unsigned a1,
                  : "r"(a0), "r"(a1), "r"(b0), "r"(SK_BIAS));
 }
 
+// C[16 x 8] += A[16 x 8] * B[8 x 8] in tf32 (f32 accumulate): the Q4_K offset term, whose factors (6-bit mins, and
+// d_x * sum q split in a tf32 high part and the rest) lose nothing that matters in tf32.
+__device__ __forceinline__ void mma_tf32_k8(float c[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
@@ -88,6 +97,11 @@ struct SkTile
     static constexpr int BYTES = T * SK_XROW + 8 * T * 8;
     const unsigned char *base;
     __device__ __forceinline__ const int8_t *x(int tok, int koff) const { return reinterpret_cast<const int8_t *>(base + tok * SK_XROW + koff); }
+    // d_x * sum q of (block, token) alone
+    __device__ __forceinline__ float sx(int blk, int tok) const
+    {
+        return *reinterpret_cast<const float *>(base + T * SK_XROW + (blk * T + tok) * 8 + 4);
+    }
     __device__ __forceinline__ float4 ds2(int blk, int tok) const
     {
         return *reinterpret_cast<const float4 *>(base + T * SK_XROW + (blk * T + tok) * 8);
@@ -143,17 +157,31 @@ __device__ __forceinline__ void sk_compute(const SkRec<FMT> &rec, const SkTile<N
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
             for (int e = 0; e < 4; e++) { part[nt][e] = 0.f; mpart[nt][e] = 0.f; }
+        // The offset term of the whole super-block is one small product, mins [16 rows x 8 sub-blocks] times
+        // (d_x * sum q) [8 sub-blocks x 8 tokens]: two tf32 tensor-core instructions per token group (the second for what
+        // the tf32 rounding of d_x * sum q leaves over) instead of four multiply-adds per sub-block and token group. The
+        // accumulator comes back in the same (row, token) arrangement as the int8 tiles'.
+        {
+            const unsigned ma0 = __float_as_uint((float)((mn[0][0] >> (8 * t)) & 0xffu)), ma1 = __float_as_uint((float)((mn[1][0] >> (8 * t)) & 0xffu));
+            const unsigned ma2 = __float_as_uint((float)((mn[0][1] >> (8 * t)) & 0xffu)), ma3 = __float_as_uint((float)((mn[1][1] >> (8 * t)) & 0xffu));
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const float s0 = tile.sx(t, nt * 8 + g), s1 = tile.sx(t + 4, nt * 8 + g);
+                const unsigned h0 = __float_as_uint(s0) & 0xFFFFE000u, h1 = __float_as_uint(s1) & 0xFFFFE000u;
+                mma_tf32_k8(mpart[nt], ma0, ma1, ma2, ma3, h0, h1);
+                mma_tf32_k8(mpart[nt], ma0, ma1, ma2, ma3, __float_as_uint(s0 - __uint_as_float(h0)), __float_as_uint(s1 - __uint_as_float(h1)));
+            }
+        }
 #pragma unroll
         for (int sb = 0; sb < 8; sb++) {
             const int ch = sb >> 1, sh = 4 * (sb & 1);
             const unsigned a0 = (rec.q[ch].x >> sh) & 0x0F0F0F0Fu, a2 = (rec.q[ch].y >> sh) & 0x0F0F0F0Fu;
             const unsigned a1 = (rec.q[ch].z >> sh) & 0x0F0F0F0Fu, a3 = (rec.q[ch].w >> sh) & 0x0F0F0F0Fu;
-            float scf[2], scb[2], mnf[2];
+            float scf[2], scb[2];
 #pragma unroll
             for (int r = 0; r < 2; r++) {
                 scf[r] = (float)((sc[r][sb >> 2] >> (8 * (sb & 3))) & 0xffu);
                 scb[r] = -SK_BIAS_F * scf[r];   // exact: 1.5 * 2^23 * (6-bit integer)
-                mnf[r] = (float)((mn[r][sb >> 2] >> (8 * (sb & 3))) & 0xffu);
             }
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
@@ -166,10 +194,6 @@ __device__ __forceinline__ void sk_compute(const SkRec<FMT> &rec, const SkTile<N
                 part[nt][1] = fmaf(fmaf(__int_as_float(cc[1]), scf[0], scb[0]), ds.z, part[nt][1]);
                 part[nt][2] = fmaf(fmaf(__int_as_float(cc[2]), scf[1], scb[1]), ds.x, part[nt][2]);
                 part[nt][3] = fmaf(fmaf(__int_as_float(cc[3]), scf[1], scb[1]), ds.z, part[nt][3]);
-                mpart[nt][0] = fmaf(mnf[0], ds.y, mpart[nt][0]);
-                mpart[nt][1] = fmaf(mnf[0], ds.w, mpart[nt][1]);
-                mpart[nt][2] = fmaf(mnf[1], ds.y, mpart[nt][2]);
-                mpart[nt][3] = fmaf(mnf[1], ds.w, mpart[nt][3]);
                 c.export_tile(st * 8 + sb, nt, cc, 0);
             }
         }
