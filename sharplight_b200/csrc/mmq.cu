@@ -121,21 +121,28 @@ constexpr float MQ_BIAS_F = 12582912.0f;
 // per block, as many instructions as half the scaling itself); an array that is opaque to it stays in place.
 struct MqBias16
 {
-    int v[16];
-    __device__ __forceinline__ void init()
+    int v[8];
+    __device__ __forceinline__ void init(const int *word)   // word: shared memory holding MQ_BIAS
     {
+        const unsigned addr = (unsigned)__cvta_generic_to_shared(word);
 #pragma unroll
-        for (int j = 0; j < 16; j++) asm volatile("mov.b32 %0, %1;" : "=r"(v[j]) : "r"(MQ_BIAS));
+#ifdef SLC_BIAS_MOV
+        for (int j = 0; j < 8; j++) asm volatile("mov.b32 %0, %1;" : "=r"(v[j]) : "r"(MQ_BIAS));
+#else
+        for (int j = 0; j < 8; j++) asm volatile("ld.volatile.shared.b32 %0, [%1];" : "=r"(v[j]) : "r"(addr) : "memory");
+#endif
     }
 };
 
+__device__ __forceinline__ void mq_tmem_st8(unsigned taddr, const MqBias16 &b)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "r"(b.v[0]), "r"(b.v[1]), "r"(b.v[2]), "r"(b.v[3]), "r"(b.v[4]), "r"(b.v[5]), "r"(b.v[6]), "r"(b.v[7]) : "memory");
+}
 __device__ __forceinline__ void mq_tmem_st16(unsigned taddr, const MqBias16 &b)
 {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-                 ::"r"(taddr), "r"(b.v[0]), "r"(b.v[1]), "r"(b.v[2]), "r"(b.v[3]), "r"(b.v[4]), "r"(b.v[5]), "r"(b.v[6]),
-                   "r"(b.v[7]), "r"(b.v[8]), "r"(b.v[9]), "r"(b.v[10]), "r"(b.v[11]), "r"(b.v[12]), "r"(b.v[13]),
-                   "r"(b.v[14]), "r"(b.v[15]) : "memory");
+    mq_tmem_st8(taddr, b);
+    mq_tmem_st8(taddr + 8u, b);
 }
 
 __device__ __forceinline__ void mq_tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -164,6 +171,7 @@ struct MqSmem
     uint64_t d_full[MQ_DBUF], d_empty[MQ_DBUF];
     unsigned tmem_base;
     int abort;
+    int bias_word;
 };
 
 // ---- producer: one row group (16 rows) of one stage -> int8 codes in the A tile, scales in the tables ------------------
@@ -306,6 +314,7 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
             mq_bar_init(&sh.d_empty[b], MQ_EPI_WARPS);
         }
         sh.abort = 0;
+        sh.bias_word = MQ_BIAS;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == MQ_EPI_WARPS + MQ_PROD_WARPS) {
@@ -326,10 +335,10 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
     if (warp >= MQ_EPI_WARPS + MQ_PROD_WARPS) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
     } else if (warp >= MQ_EPI_WARPS) {
-        if constexpr (FMT != FMT_Q4_0) asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+        if constexpr (FMT != FMT_Q4_0 || true) asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
         else asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     } else {
-        if constexpr (FMT != FMT_Q4_0) asm volatile("setmaxnreg.inc.sync.aligned.u32 88;");
+        if constexpr (FMT != FMT_Q4_0 || true) asm volatile("setmaxnreg.inc.sync.aligned.u32 88;");
         else asm volatile("setmaxnreg.inc.sync.aligned.u32 96;");
     }
 
@@ -346,9 +355,8 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
 #pragma unroll
         for (int j = 0; j < 32; j++) acc[j] = 0.0f;
         bool alive = true;
-        const int total = nst * 8;
         MqBias16 bias;
-        bias.init();
+        bias.init(&sh.bias_word);
 
         // arm this warp's part of every accumulator buffer with the bias, then open the buffers for the MMA issuer
 #pragma unroll
@@ -364,21 +372,32 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
             for (int buf = 0; buf < MQ_DBUF; buf++) mq_bar_arrive(&sh.d_empty[buf]);
         }
 
-        for (int i = 0; i < total && alive; i++) {
-            const int it = i >> 3, b = i & 7, s = it % MQ_STAGES, buf = i % MQ_DBUF;
-            if (b == 0) {
-                // the stage's scale tables: weight scales come from the producers, activation scales from a bulk copy
-                const unsigned spar = (unsigned)(it / MQ_STAGES) & 1u;
-                if (!mq_bar_wait(&sh.a_full[s], spar) || !mq_bar_wait(&sh.b_full[s], spar)) { alive = false; break; }
-            }
+        // Stage loop outside, the stage's eight blocks unrolled inside: 8 is a multiple of the buffer count, so the buffer
+        // of block b, the parity of its barrier and every table offset are constants of the unrolled body.
+        static_assert(8 % MQ_DBUF == 0, "buffer index and parity must not depend on the stage");
+        int s = 0;
+        unsigned spar = 0;
+        for (int it = 0; it < nst && alive; it++) {
+            // the stage's scale tables: weight scales come from the producers, activation scales from a bulk copy
+            if (!mq_bar_wait(&sh.a_full[s], spar) || !mq_bar_wait(&sh.b_full[s], spar)) { alive = false; break; }
+            // two walking pointers per stage: the per-token tables at this warp's columns, the per-row tables at this
+            // lane's row; the d_x * sum q table and the mins table (Q4_K) lie a fixed distance behind them
+            const float *tok_tab = stage_dx(s) + c0, *row_tab = stage_dw(s) + r;
+            constexpr int SECOND = 8 * MQ_TILE_T + MQ_TILE_N * 8;   // floats from d_x to d_x * sum q, and from d_w to the mins
+            {
+#pragma unroll 1
+            for (int b = 0; b < 8; b++) {
+            const int buf = b % MQ_DBUF, hb = b / MQ_DBUF, i = it * 8 + b;
             const unsigned tcol = tlane + (unsigned)(buf * MQ_TILE_T);
             {
-                if (!mq_bar_wait(&sh.d_full[buf], (unsigned)(i / MQ_DBUF) & 1u)) { alive = false; break; }
+                if (!mq_bar_wait(&sh.d_full[buf], (unsigned)hb & 1u)) { alive = false; break; }
             }
             mq_tc_fence_after();
-            const float *dxs = stage_dx(s) + b * MQ_TILE_T + c0, *sxs = stage_sx(s) + b * MQ_TILE_T + c0;
-            const float dwv = stage_dw(s)[b * MQ_TILE_N + r];
-            const float dmv = HAS_MIN ? -stage_dm(s)[b * MQ_TILE_N + r] : 0.0f;
+            const float *dxs = tok_tab, *sxs = tok_tab + SECOND;
+            const float dwv = row_tab[0];
+            const float dmv = HAS_MIN ? -row_tab[SECOND] : 0.0f;
+            tok_tab += MQ_TILE_T;
+            row_tab += MQ_TILE_N;
             const float cw = -MQ_BIAS_F * dwv;
             // the slice in two halves of 16 columns: 16 result registers live at a time
 #pragma unroll
@@ -431,10 +450,12 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
                 __syncwarp();
                 if (lane == 0) mq_bar_arrive(&sh.d_empty[buf]);
             }
-            if (b == 7) {
-                __syncwarp();
-                if (lane == 0) mq_bar_arrive(&sh.epi_done[s]);   // the stage's scale tables are free
             }
+            }
+            if (!alive) break;
+            __syncwarp();
+            if (lane == 0) mq_bar_arrive(&sh.epi_done[s]);   // the stage's scale tables are free
+            if (++s == MQ_STAGES) { s = 0; spar ^= 1u; }
         }
         if (!alive) {
             if (lane == 0) atomicExch(status, -7);
