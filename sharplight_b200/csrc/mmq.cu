@@ -116,9 +116,10 @@ __device__ __forceinline__ void mq_tmem_ld16(unsigned taddr, float (&r)[16])
 constexpr int MQ_BIAS = 0x4B400000;
 constexpr float MQ_BIAS_F = 12582912.0f;
 
-// Sixteen registers that hold the bias pattern for the whole kernel. tcgen05.st takes sixteen distinct registers: fed
-// from one value, the compiler copies it into sixteen registers before every store (one move per accumulator column
-// per block, as many instructions as half the scaling itself); an array that is opaque to it stays in place.
+// Eight registers that hold the bias pattern for the whole kernel; tcgen05.st .x8 takes eight distinct registers. They
+// are read from shared memory with volatile loads so that the compiler cannot re-create them from the constant before
+// every store. Eight rather than sixteen (with .x16 stores): the epilogue's 88 registers then hold everything without
+// spilling, which was worth 12 % of the kernel's time.
 struct MqBias16
 {
     int v[8];
@@ -126,11 +127,7 @@ struct MqBias16
     {
         const unsigned addr = (unsigned)__cvta_generic_to_shared(word);
 #pragma unroll
-#ifdef SLC_BIAS_MOV
-        for (int j = 0; j < 8; j++) asm volatile("mov.b32 %0, %1;" : "=r"(v[j]) : "r"(MQ_BIAS));
-#else
         for (int j = 0; j < 8; j++) asm volatile("ld.volatile.shared.b32 %0, [%1];" : "=r"(v[j]) : "r"(addr) : "memory");
-#endif
     }
 };
 
@@ -329,17 +326,15 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
 
     pdl_enter(early);   // waits for the kernel that produced the activations unless they were complete before it
 
-    // Register budget: 80 per thread at launch (768 threads). The MMA issuer's warpgroup gives back all but 24. The
-    // producers of Q8_0 (two 4352-byte records in registers) and Q4_K (scale decoding) take 104, leaving 88 to the
-    // epilogue; Q4_0's need 72 and its epilogue gets 96 (no spills). Either way 4 x epilogue + producers + 24 = 6 x 80.
+    // Register budget: 80 per thread at launch (768 threads). The MMA issuer's warpgroup gives back all but 24, the
+    // producers (two records in registers, scale decoding) take 104, the epilogue 88: 4 x 88 + 104 + 24 = 6 x 80. No
+    // instantiation spills.
     if (warp >= MQ_EPI_WARPS + MQ_PROD_WARPS) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
     } else if (warp >= MQ_EPI_WARPS) {
-        if constexpr (FMT != FMT_Q4_0 || true) asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
-        else asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     } else {
-        if constexpr (FMT != FMT_Q4_0 || true) asm volatile("setmaxnreg.inc.sync.aligned.u32 88;");
-        else asm volatile("setmaxnreg.inc.sync.aligned.u32 96;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 88;");
     }
 
     if (warp < MQ_EPI_WARPS) {
@@ -372,8 +367,9 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
             for (int buf = 0; buf < MQ_DBUF; buf++) mq_bar_arrive(&sh.d_empty[buf]);
         }
 
-        // Stage loop outside, the stage's eight blocks unrolled inside: 8 is a multiple of the buffer count, so the buffer
-        // of block b, the parity of its barrier and every table offset are constants of the unrolled body.
+        // Stage loop outside, the stage's eight blocks inside: 8 is a multiple of the buffer count, so the buffer of block b
+        // and the parity of its barrier depend on b alone, and the tables are walked with two pointers. (Unrolling the
+        // inner loop, by 8 or by the buffer count, spills at this register budget and was measured 40-60 % slower.)
         static_assert(8 % MQ_DBUF == 0, "buffer index and parity must not depend on the stage");
         int s = 0;
         unsigned spar = 0;
@@ -389,16 +385,18 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
             for (int b = 0; b < 8; b++) {
             const int buf = b % MQ_DBUF, hb = b / MQ_DBUF, i = it * 8 + b;
             const unsigned tcol = tlane + (unsigned)(buf * MQ_TILE_T);
-            {
-                if (!mq_bar_wait(&sh.d_full[buf], (unsigned)hb & 1u)) { alive = false; break; }
-            }
-            mq_tc_fence_after();
+            // the row's scales first: they come from the stage's tables, not from the accumulator, and their latency
+            // then lies under the wait
             const float *dxs = tok_tab, *sxs = tok_tab + SECOND;
             const float dwv = row_tab[0];
             const float dmv = HAS_MIN ? -row_tab[SECOND] : 0.0f;
             tok_tab += MQ_TILE_T;
             row_tab += MQ_TILE_N;
             const float cw = -MQ_BIAS_F * dwv;
+            {
+                if (!mq_bar_wait(&sh.d_full[buf], (unsigned)hb & 1u)) { alive = false; break; }
+            }
+            mq_tc_fence_after();
             // the slice in two halves of 16 columns: 16 result registers live at a time
 #pragma unroll
             for (int h = 0; h < 2; h++) {
