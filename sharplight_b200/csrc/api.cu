@@ -719,12 +719,9 @@ static int choose_kernel(const slc_matmul *op, int rows, bool exchanging)
     if (mv && rows <= 2) return SLC_KERNEL_MMVQ;
     // the tile kernel (stream-K, tcgen05) from UMMA_MIN_ROWS rows; the in-kernel sum over ranks lives in the older kernels
     if (rows >= UMMA_MIN_ROWS && umma_supports(op->w->fmt, rows) && !exchanging) return SLC_KERNEL_TILE;
-    // Q6_K prefill: the tile kernel (two half-masked MMAs per block, stream-K) unless the weight has so many rows that
-    // the skinny kernel's 64-row chunks fill the machine by themselves (measured: [4096, 4096] x 2048 rows 550 against
-    // 919 us, [32064, 4096] 4220 against 3287 us)
-    if (op->w->fmt == FMT_Q6_K && rows > 64 && !exchanging && (op->w->view.n_pad >> 6) < 2 * op->dev->prop.multiProcessorCount) {
-        return SLC_KERNEL_TILE;
-    }
+    // more than 64 rows: the tensor-core GEMM for every format (Q6_K included: two half-masked MMAs per block; on
+    // [4096, 4096] x 2048 rows 394 us against 554 of the tile kernel and 919 of 64-row chunks of the skinny kernel, on
+    // [32064, 4096] 3058 against 4241 and 3287)
     if (rows <= 64 || !mmq_supports(op->w->fmt)) return SLC_KERNEL_SKINNY;
     return SLC_KERNEL_MMQ;
 }

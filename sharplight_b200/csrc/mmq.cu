@@ -6,15 +6,16 @@
 // One CTA computes a 128 (weight rows) x 128 (tokens) tile. Roles, warp-specialised:
 //   warps 0-15  epilogue, four per scheduler: read each block's tile from tensor memory (tcgen05.ld, 16 columns at a
 //               time), scale, accumulate in f32 registers; warp w owns TMEM lanes 32*(w%4).. and columns 32*(w/4)..
-//   warps 16-19 producers: stream the weight records (layout.cuh) with 128-bit loads, expand 4-bit codes to int8 in
+//   warps 16-19 producers: stream the weight records (layout.cuh) with 128-bit loads, expand 4- and 6-bit codes to int8 in
 //               registers and store them in the K-major core-matrix layout the tensor core reads; lane 0 of warp 16
 //               also starts the bulk async copies (TMA engine) of the activation tile, which the quantizer already
 //               wrote in that layout, and of the activation scales
 //   warp 20     allocates tensor memory; its lane 0 issues tcgen05.mma kind::i8 (M=128, N=128, K=32: one quantization
 //               block per instruction, each into its own accumulator buffer: per-block scales forbid accumulating
-//               across blocks in int32) and commits to mbarriers
-// Pipelines: 3 shared-memory stages of 256 K-values (8 blocks), 4 TMEM accumulator buffers of 128 columns; the
-// producers keep the next stage's weight records in registers while the current one is expanded.
+//               across blocks in int32; Q6_K, whose scale changes every 16 values: two instructions per block on two
+//               half-masked copies of the weight rows) and commits to mbarriers
+// Pipelines: 3 shared-memory stages of 256 K-values (8 blocks; 2 stages for Q4_K and Q6_K), 4 TMEM accumulator buffers of
+// 128 columns; the producers keep the next stage's weight records in registers while the current one is expanded.
 // Every mbarrier wait is bounded; when one runs out the kernel raises the device status word, and every role leaves
 // through the common exit that frees tensor memory.
 #include "internal.cuh"
@@ -23,8 +24,12 @@ namespace slc {
 
 constexpr int MQ_TILE_N = 128;     // weight rows per CTA (UMMA M)
 constexpr int MQ_TILE_T = 128;     // tokens per CTA (UMMA N)
-// shared-memory stages: three, or two for the format with an offset table (Q4_K), whose stage is 8 KB larger
-__host__ __device__ constexpr int mq_stages(int fmt) { return fmt == FMT_Q4_K ? 2 : 3; }
+// Q6_K changes its scale every 16 values: a 32-value block is two MMAs on two copies of the weight rows, one with the
+// upper and one with the lower sixteen values zero (the same activation codes both times), into two accumulator buffers
+// with a weight scale each (the reference's GEMM does the same, src/Sharplight.Shaders/Kernels/mmq.slang:235-239)
+__host__ __device__ constexpr int mq_gpb(int fmt) { return fmt == FMT_Q6_K ? 2 : 1; }   // MMAs (scale groups) per block
+// shared-memory stages: three, or two for the formats with a larger stage (Q4_K: offset tables; Q6_K: two weight copies)
+__host__ __device__ constexpr int mq_stages(int fmt) { return fmt == FMT_Q4_K || fmt == FMT_Q6_K ? 2 : 3; }
 constexpr int MQ_MAX_STAGES = 3;
 constexpr int MQ_DBUF = 4;
 constexpr int MQ_EPI_WARPS = 16, MQ_PROD_WARPS = 4;
@@ -33,13 +38,13 @@ constexpr int MQ_THREADS = 768;   // warps 0-15 epilogue, 16-19 producers, 20 MM
 // epilogue needs; 100000 attempts bound it at about two seconds
 constexpr unsigned MQ_WAIT_LIMIT = 100000;
 
-constexpr int MQ_A_BYTES = MQ_TILE_N * 256;          // int8 codes of one stage
+constexpr int MQ_A_BYTES = MQ_TILE_N * 256;          // int8 codes of one stage (one copy)
 constexpr int MQ_B_BYTES = MQ_TILE_T * 256;
 constexpr int MQ_DX_BYTES = 8 * MQ_TILE_T * 4;       // d per block and token (a second table of d * sum32(q) for Q4_K)
 constexpr int MQ_DW_BYTES = MQ_TILE_N * 8 * 4;       // weight scale per row and block (a second table of mins for Q4_K)
 __host__ __device__ constexpr int mq_stage_bytes(int fmt)
 {
-    return MQ_A_BYTES + MQ_B_BYTES + (fmt == FMT_Q4_K ? 2 : 1) * (MQ_DX_BYTES + MQ_DW_BYTES);
+    return mq_gpb(fmt) * MQ_A_BYTES + MQ_B_BYTES + (fmt == FMT_Q4_K ? 2 : 1) * MQ_DX_BYTES + (fmt == FMT_Q4_K ? 2 : mq_gpb(fmt)) * MQ_DW_BYTES;
 }
 __host__ __device__ constexpr int mq_smem_bytes(int fmt) { return mq_stages(fmt) * mq_stage_bytes(fmt) + 1024; }
 
@@ -178,6 +183,7 @@ struct MqRegs
 {
     uint4 q[code_units(FMT) / 32];
     uint4 s0, s1;
+    unsigned d01;   // Q6_K: the f16 super-block scales of rows g (low half) and g + 8
 };
 
 // The record of (rg, st) into registers (zeros for row groups beyond the weight).
@@ -194,6 +200,10 @@ __device__ __forceinline__ void mq_load(MqRegs<FMT> &rr, const WeightView &w, in
     const uint4 *sp = reinterpret_cast<const uint4 *>(rec + code_bytes(FMT));
     rr.s0 = live ? ld_stream(sp + g) : zero;
     rr.s1 = live ? ld_stream(sp + g + 8) : zero;
+    if constexpr (FMT == FMT_Q6_K) {
+        const unsigned short *dp = reinterpret_cast<const unsigned short *>(rec + code_bytes(FMT) + 256);
+        rr.d01 = live ? (unsigned)__ldg(dp + g) | ((unsigned)__ldg(dp + g + 8) << 16) : 0u;
+    }
 }
 
 // Registers -> int8 codes in the A tile (rows rgl*16 .. +15), scales in the tables.
@@ -232,6 +242,36 @@ __device__ __forceinline__ void mq_store(const MqRegs<FMT> &rr, int rgl, int lan
                 *reinterpret_cast<unsigned *>(dst + 128) = hi;
             }
         }
+    } else if constexpr (FMT == FMT_Q6_K) {
+        // Half c of the super-block: planes 3c (row g) and 3c + 1 (row g + 8) hold L[l0..+3], L[32+l0..+3], L[l1..+3],
+        // L[32+l1..+3] with l0 = 4t, l1 = 16 + 4t; plane 3c + 2 holds H[l0..+3], H[l1..+3] of row g, then of row g + 8.
+        // Quarter v of the half is block 4c + v of the stage: its values l are (low or high nibble of L[l] or L[32 + l])
+        // | (bits 2v, 2v+1 of H[l]) << 4, minus 32. Its lower sixteen values go to the first 16-byte chunk of the block
+        // in the first copy, its upper sixteen to the second chunk in the second copy; the other chunks of both copies
+        // stay zero (written once when the kernel starts).
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+            const uint4 L[2] = { rr.q[3 * c], rr.q[3 * c + 1] };
+            const uint4 H = rr.q[3 * c + 2];
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+#pragma unroll
+                for (int li = 0; li < 2; li++) {
+                    const unsigned lw = li ? L[r].z : L[r].x, lw32 = li ? L[r].w : L[r].y;
+                    const unsigned hw = r ? (li ? H.w : H.z) : (li ? H.y : H.x);
+                    uint8_t *dst = (r ? row_hi : row_lo) + li * MQ_A_BYTES + 4 * t;
+#pragma unroll
+                    for (int v = 0; v < 4; v++) {
+                        const unsigned lsrc = (v & 1) ? lw32 : lw;
+                        const unsigned lo4 = ((v & 2) ? (lsrc >> 4) : lsrc) & 0x0F0F0F0Fu;
+                        const unsigned u = lo4 | (((hw >> (2 * v)) & 0x03030303u) << 4);       // 0..63
+                        const unsigned x = u ^ 0x20202020u;                                     // six-bit two's complement of u - 32
+                        const unsigned code = x | ((x & 0x20202020u) * 6u);                     // sign bit copied to bits 6, 7
+                        *reinterpret_cast<unsigned *>(dst + (2 * (4 * c + v) + li) * 128) = code;
+                    }
+                }
+            }
+        }
     } else {  // Q4_K: unsigned nibbles, the mins go through the offset table
 #pragma unroll
         for (int c = 0; c < 4; c++) {
@@ -253,6 +293,16 @@ __device__ __forceinline__ void mq_store(const MqRegs<FMT> &rr, int rgl, int lan
         dw_lo[(2 * t + 1) * MQ_TILE_N] = mq_h2f(w0 >> 16) * unit;
         dw_hi[(2 * t) * MQ_TILE_N] = mq_h2f(w1 & 0xffffu) * unit;
         dw_hi[(2 * t + 1) * MQ_TILE_N] = mq_h2f(w1 >> 16) * unit;
+    } else if constexpr (FMT == FMT_Q6_K) {
+        // i8 scales of the 16-value groups 4t .. 4t + 3 (group 2b + li is copy li of block b), times the row's f16 d
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const uint4 h = r ? s1 : s0;
+            const float d = mq_h2f(r ? rr.d01 >> 16 : rr.d01 & 0xffffu);
+            const unsigned scw = t == 0 ? h.x : t == 1 ? h.y : t == 2 ? h.z : h.w;
+#pragma unroll
+            for (int i = 0; i < 4; i++) (r ? dw_hi : dw_lo)[(4 * t + i) * MQ_TILE_N] = d * (float)(int)(signed char)((scw >> (8 * i)) & 0xffu);
+        }
     } else {
         float *dm_lo = dms + rgl * 16 + g, *dm_hi = dm_lo + 8;
 #pragma unroll
@@ -293,8 +343,9 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
 
     // stage layout: A codes, B codes, d_x table, d_w table, then (Q4_K) the d_x * sum q table and the mins table
     auto stage_a = [&](int s) { return smem + s * MQ_STAGE_BYTES; };
-    auto stage_b = [&](int s) { return smem + s * MQ_STAGE_BYTES + MQ_A_BYTES; };
-    auto stage_dx = [&](int s) { return reinterpret_cast<float *>(smem + s * MQ_STAGE_BYTES + MQ_A_BYTES + MQ_B_BYTES); };
+    constexpr int GPB = mq_gpb(FMT), A_ALL = GPB * MQ_A_BYTES;   // Q6_K: two half-masked copies of the weight rows
+    auto stage_b = [&](int s) { return smem + s * MQ_STAGE_BYTES + A_ALL; };
+    auto stage_dx = [&](int s) { return reinterpret_cast<float *>(smem + s * MQ_STAGE_BYTES + A_ALL + MQ_B_BYTES); };
     auto stage_dw = [&](int s) { return stage_dx(s) + 8 * MQ_TILE_T; };
     auto stage_sx = [&](int s) { return stage_dw(s) + MQ_TILE_N * 8; };
     auto stage_dm = [&](int s) { return stage_sx(s) + 8 * MQ_TILE_T; };
@@ -313,6 +364,14 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
         sh.abort = 0;
         sh.bias_word = MQ_BIAS;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if constexpr (GPB > 1) {
+        // the halves of the two weight copies that no producer ever writes
+        for (int st = 0; st < MQ_STAGES; st++) {
+            uint4 *z = reinterpret_cast<uint4 *>(stage_a(st));
+            for (int j = threadIdx.x; j < A_ALL / 16; j += MQ_THREADS) z[j] = make_uint4(0, 0, 0, 0);
+        }
+        mq_fence_proxy_async();
     }
     if (warp == MQ_EPI_WARPS + MQ_PROD_WARPS) {
         // all 512 columns: four 128-column accumulators (one CTA per SM: the shared-memory footprint guarantees it)
@@ -371,6 +430,7 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
         // and the parity of its barrier depend on b alone, and the tables are walked with two pointers. (Unrolling the
         // inner loop, by 8 or by the buffer count, spills at this register budget and was measured 40-60 % slower.)
         static_assert(8 % MQ_DBUF == 0, "buffer index and parity must not depend on the stage");
+        constexpr int NBLK = 8 * GPB;   // accumulator buffers' worth of work per stage
         int s = 0;
         unsigned spar = 0;
         for (int it = 0; it < nst && alive; it++) {
@@ -382,15 +442,15 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
             constexpr int SECOND = 8 * MQ_TILE_T + MQ_TILE_N * 8;   // floats from d_x to d_x * sum q, and from d_w to the mins
             {
 #pragma unroll 1
-            for (int b = 0; b < 8; b++) {
-            const int buf = b % MQ_DBUF, hb = b / MQ_DBUF, i = it * 8 + b;
+            for (int b = 0; b < NBLK; b++) {
+            const int buf = b % MQ_DBUF, hb = b / MQ_DBUF, i = it * 8 + b / GPB;   // i: the 32-value block
             const unsigned tcol = tlane + (unsigned)(buf * MQ_TILE_T);
             // the row's scales first: they come from the stage's tables, not from the accumulator, and their latency
             // then lies under the wait
             const float *dxs = tok_tab, *sxs = tok_tab + SECOND;
             const float dwv = row_tab[0];
             const float dmv = HAS_MIN ? -row_tab[SECOND] : 0.0f;
-            tok_tab += MQ_TILE_T;
+            if (GPB == 1 || (b & 1)) tok_tab += MQ_TILE_T;   // activation scales are per 32-value block
             row_tab += MQ_TILE_N;
             const float cw = -MQ_BIAS_F * dwv;
             {
@@ -433,10 +493,14 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
                     for (int j = 0; j < 16; j++) {
                         const int tok = t0 + c0 + h * 16 + j, row = n0 + r;
                         if (tok < a.rows && row < w.n && i * 32 < w.k) {
-                            const int cexp = FMT == FMT_Q8_0 ? 128 : FMT == FMT_Q4_0 ? 8 : 0;
+                            // the reference's block dot has unsigned weight codes: add the offset times the block's
+                            // activation sum; Q6_K: the block's two groups come one after the other to this thread
+                            const int cexp = FMT == FMT_Q8_0 ? 128 : FMT == FMT_Q4_0 ? 8 : FMT == FMT_Q6_K ? 32 : 0;
                             const int add = cexp ? cexp * __ldg(&a.isum[(long long)tok * (a.k_pad >> 5) + i]) : 0;
                             const int dot = __float_as_int(sv[j]) - MQ_BIAS;   // Q4_0: 16 times the dot, exactly
-                            dump[((long long)tok * w.n + row) * (w.k >> 5) + i] = (FMT == FMT_Q4_0 ? dot >> 4 : dot) + add;
+                            int *dst = &dump[((long long)tok * w.n + row) * (w.k >> 5) + i];
+                            if (GPB == 1 || (b & 1) == 0) *dst = (FMT == FMT_Q4_0 ? dot >> 4 : dot) + add;
+                            else *dst += dot;
                         }
                     }
                 }
@@ -526,14 +590,15 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
                 }
                 mq_tc_fence_after();
                 const unsigned a_addr = mq_smem(stage_a(s)), b_addr = mq_smem(stage_b(s));
-                for (int b = 0; b < 8; b++) {
-                    const int i = it * 8 + b, buf = i % MQ_DBUF;
+                for (int b = 0; b < 8 * GPB; b++) {
+                    const int i = it * 8 * GPB + b, buf = i % MQ_DBUF;
                     {
                         if (!mq_bar_wait(&sh.d_empty[buf], (unsigned)(i / MQ_DBUF) & 1u)) { alive = false; break; }
                     }
                     mq_tc_fence_after();
-                    mq_umma_i8(tmem + (unsigned)(buf * MQ_TILE_T), mq_desc(a_addr + b * 256, 128, 2048),
-                               mq_desc(b_addr + b * 256, 128, 2048), idesc);
+                    // block b / GPB of the stage; Q6_K: copy b % 2 of the weight rows, the same activation codes
+                    mq_umma_i8(tmem + (unsigned)(buf * MQ_TILE_T), mq_desc(a_addr + (b % GPB) * MQ_A_BYTES + (b / GPB) * 256, 128, 2048),
+                               mq_desc(b_addr + (b / GPB) * 256, 128, 2048), idesc);
                     mq_umma_commit(&sh.d_full[buf]);
                 }
                 if (alive) mq_umma_commit(&sh.mma_done[s]);
@@ -551,7 +616,7 @@ mmq_kernel(const WeightView w, const ActView a, const uint8_t *__restrict__ q_ti
     }
 }
 
-bool mmq_supports(int fmt) { return fmt == FMT_Q4_0 || fmt == FMT_Q8_0 || fmt == FMT_Q4_K; }
+bool mmq_supports(int fmt) { return fmt == FMT_Q4_0 || fmt == FMT_Q8_0 || fmt == FMT_Q4_K || fmt == FMT_Q6_K; }
 
 template <int FMT, bool DUMP>
 static cudaError_t mmq_launch_one(const WeightView &w, const ActView &a, const uint8_t *q_tiled, float *y,
@@ -589,7 +654,7 @@ cudaError_t launch_mmq(const WeightView &w, const ActView &a, const uint8_t *q_t
         return dump ? mmq_launch_one<F, true>(w, a, q_tiled, y, y_stride, dump, status, early, stream, ep, tile_t0, tile_count)    \
                     : mmq_launch_one<F, false>(w, a, q_tiled, y, y_stride, nullptr, status, early, stream, ep, tile_t0, tile_count);
     switch (w.fmt) {
-        SLC_FMT(FMT_Q4_0) SLC_FMT(FMT_Q8_0) SLC_FMT(FMT_Q4_K)
+        SLC_FMT(FMT_Q4_0) SLC_FMT(FMT_Q8_0) SLC_FMT(FMT_Q4_K) SLC_FMT(FMT_Q6_K)
     default: return cudaErrorInvalidValue;
     }
 #undef SLC_FMT

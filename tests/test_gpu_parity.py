@@ -375,7 +375,7 @@ def test_intdot_stays_close_to_exact_product_at_full_size(cuda_device):
 
 # ---- prefill: the tensor-core GEMM ------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("type_name", ["Q4_0", "Q8_0", "Q4_K"])
+@pytest.mark.parametrize("type_name", ["Q4_0", "Q8_0", "Q4_K", "Q6_K"])
 @pytest.mark.parametrize("rows,n,k", [(65, 96, 512), (200, 100, 512), (300, 520, 512), (129, 128, 256), (1000, 3000, 256)])
 def test_mmq_shapes(cuda_device, type_name, rows, n, k):
     """MmqTests (tests/Sharplight.Vulkan.Tests/MmqTests.cs:21-98): (T, N) in {(65, 96), (200, 100), (300, 520)} at
@@ -385,7 +385,7 @@ def test_mmq_shapes(cuda_device, type_name, rows, n, k):
     assert used == N.KERNEL_MMQ and launches >= 1
 
 
-@pytest.mark.parametrize("type_name", ["Q4_0", "Q8_0", "Q4_K"])
+@pytest.mark.parametrize("type_name", ["Q4_0", "Q8_0", "Q4_K", "Q6_K"])
 def test_mmq_exact_int8_activations(cuda_device, type_name):
     """MmqTests' exact-activation case (K = 1024): atol 2e-3, rtol 1e-3 against the product with the dequantized weight."""
     n, k, rows = 520, 1024, 300
@@ -502,13 +502,18 @@ def test_tile_kernel_falls_back_where_it_does_not_serve(cuda_device):
     assert kern[0] != N.KERNEL_TILE
 
 
-def test_q6_k_prefill_takes_the_tile_kernel(cuda_device):
-    """More than 64 rows of a Q6_K weight with few rows: two half-masked tensor-core instructions per block instead of
-    64-row chunks of the skinny kernel (the reference's GEMM serves Q6_K the same way,
-    src/Sharplight.Shaders/Kernels/mmq.slang:235-239)."""
+def test_q6_k_prefill_takes_the_gemm(cuda_device):
+    """More than 64 rows of a Q6_K weight: two half-masked tensor-core instructions per block instead of 64-row chunks of
+    the skinny kernel (the reference's GEMM serves Q6_K the same way, src/Sharplight.Shaders/Kernels/mmq.slang:235-239);
+    ragged N and K, block dots bit for bit, then a full-size case against a sample of the weight rows."""
     _, kern = check_matmul(cuda_device, "Q6_K", 640, 1024, 200, seed=9)
-    assert kern[0] == N.KERNEL_TILE
-    assert _check_sampled_rows(cuda_device, "Q6_K", 4096, 4096, 2048, 210, 32) == N.KERNEL_TILE
+    assert kern[0] == N.KERNEL_MMQ
+    _, kern = check_matmul(cuda_device, "Q6_K", 1000, 2816, 300, seed=10)
+    assert kern[0] == N.KERNEL_MMQ
+    _, kern = check_matmul(cuda_device, "Q6_K", 7, 512, 70, seed=11)
+    assert kern[0] == N.KERNEL_MMQ
+    assert _check_sampled_rows(cuda_device, "Q6_K", 4096, 4096, 2048, 210, 32) == N.KERNEL_MMQ
+    assert _check_sampled_rows(cuda_device, "Q6_K", 32064, 4096, 300, 211, 48) == N.KERNEL_MMQ
 
 
 @pytest.mark.parametrize("rows", [16, 64])
