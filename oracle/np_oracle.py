@@ -9,8 +9,10 @@ from __future__ import annotations
 
 import numpy as np
 
-Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
-BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}
+Q4_0, Q5_0, Q8_0, Q4_K, Q6_K, IQ4_NL = 2, 6, 8, 12, 14, 20
+BLOCK = {Q4_0: (32, 18), Q5_0: (32, 22), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210), IQ4_NL: (32, 18)}
+# IQ4_NL's non-linear codebook (src/Sharplight.Cpu/Quant.cs:409)
+IQ4NL_VALUES = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.int32)
 
 
 def _f16(b: np.ndarray) -> np.ndarray:
@@ -51,6 +53,22 @@ def codes(fmt: int, blocks: np.ndarray, n: int, k: int):
         u = np.concatenate([qs & 15, qs >> 4], axis=-1).reshape(n, k)
         a = np.repeat(d, 2, axis=1)
         b = np.float32(-8.0) * a
+    elif fmt == Q5_0:
+        # { f16 d; u32 qh; u8 qs[16] }: bit j of qh is the fifth bit of value j (IntDot.Decode.cs:101-123)
+        d = _f16(blk[..., 0:2])
+        qh = np.ascontiguousarray(blk[..., 2:6]).view("<u4")[..., 0].astype(np.int64)
+        hi = ((qh[..., None] >> np.arange(32)) & 1).astype(np.int32) << 4
+        qs = blk[..., 6:22].astype(np.int32)
+        u = (np.concatenate([qs & 15, qs >> 4], axis=-1) | hi).reshape(n, k)
+        a = np.repeat(d, 2, axis=1)
+        b = np.float32(-16.0) * a
+    elif fmt == IQ4_NL:
+        # { f16 d; u8 qs[16] }: u = codebook value + 128 (IntDot.Decode.cs:225-238)
+        d = _f16(blk[..., 0:2])
+        qs = blk[..., 2:18].astype(np.int32)
+        u = (IQ4NL_VALUES[np.concatenate([qs & 15, qs >> 4], axis=-1)] + 128).reshape(n, k)
+        a = np.repeat(d, 2, axis=1)
+        b = np.float32(-128.0) * a
     elif fmt == Q4_K:
         d = _f16(blk[..., 0:2])
         dmin = _f16(blk[..., 2:4])
@@ -83,7 +101,7 @@ def dequantize(fmt: int, blocks: np.ndarray, n: int, k: int) -> np.ndarray:
     """w = fma(code, a, b) per value with the reference's signed code for Q8_0 (offset 0)."""
     u, a, b = codes(fmt, blocks, n, k)
     a16 = np.repeat(a, 16, axis=1)
-    if fmt == Q8_0:
+    if fmt == Q8_0 or fmt == IQ4_NL:   # a plain product of the signed code and d
         return _fma((u - 128).astype(np.float32), a16, np.zeros_like(a16))
     return _fma(u.astype(np.float32), a16, np.repeat(b, 16, axis=1))
 

@@ -19,7 +19,7 @@
 int slo_block_size(int fmt)
 {
     switch (fmt) {
-    case SLO_Q4_0: case SLO_Q8_0: return 32;
+    case SLO_Q4_0: case SLO_Q8_0: case SLO_Q5_0: case SLO_IQ4_NL: return 32;
     case SLO_Q4_K: case SLO_Q6_K: return 256;
     default: return 0;
     }
@@ -29,6 +29,8 @@ int slo_block_bytes(int fmt)
 {
     switch (fmt) {
     case SLO_Q4_0: return 18;
+    case SLO_Q5_0: return 22;
+    case SLO_IQ4_NL: return 18;
     case SLO_Q8_0: return 34;
     case SLO_Q4_K: return 144;
     case SLO_Q6_K: return 210;
@@ -81,6 +83,9 @@ static void scale_min(int j, const uint8_t *s, int *sc, int *m)
 
 /* ---- dequantization, one FMA per value: src/Sharplight.Cpu/Quant.cs:384-405,519-545,585-618; Simd.cs:699-753 ------- */
 
+/* the non-linear 4-bit codebook of IQ4_NL (ggml's kvalues_iq4nl; Quant.cs:409) */
+static const int8_t iq4nl_values[16] = { -127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113 };
+
 static void store16_u8(const uint8_t *v, float scale, float offset, float *dst)
 {
     for (int i = 0; i < 16; i++) {
@@ -113,6 +118,29 @@ int slo_dequantize_row(int fmt, const uint8_t *p, int64_t k, float *dst)
             store16_u8(v, d, off, dst);
             for (int i = 0; i < 16; i++) v[i] = p[2 + i] >> 4;
             store16_u8(v, d, off, dst + 16);
+        }
+        return 0;
+    case SLO_Q5_0:
+        /* Quant.cs:463-480: { f16 d; u32 qh; u8 qs[16] }, value j = (nibble | bit j of qh << 4) * d - 16 d (FMA form) */
+        for (int64_t b = 0; b < nb; b++, p += 22, dst += 32) {
+            float d = h_at(p);
+            float off = -16.0f * d;
+            uint32_t qh;
+            memcpy(&qh, p + 2, 4);
+            for (int i = 0; i < 16; i++) v[i] = (uint8_t)((p[6 + i] & 15) | (((qh >> i) & 1u) << 4));
+            store16_u8(v, d, off, dst);
+            for (int i = 0; i < 16; i++) v[i] = (uint8_t)((p[6 + i] >> 4) | (((qh >> (i + 16)) & 1u) << 4));
+            store16_u8(v, d, off, dst + 16);
+        }
+        return 0;
+    case SLO_IQ4_NL:
+        /* Quant.cs:409-423: { f16 d; u8 qs[16] }, value = d * kvalues[nibble] (a plain product) */
+        for (int64_t b = 0; b < nb; b++, p += 18, dst += 32) {
+            float d = h_at(p);
+            for (int i = 0; i < 16; i++) {
+                dst[i] = d * (float)iq4nl_values[p[2 + i] & 15];
+                dst[16 + i] = d * (float)iq4nl_values[p[2 + i] >> 4];
+            }
         }
         return 0;
     case SLO_Q4_K:
@@ -221,6 +249,30 @@ int slo_decode_row(int fmt, const uint8_t *p, int64_t k, uint8_t *u, float *a, f
                 u[16 + i] = p[2 + i] >> 4;
             }
             set_block(a, b, d, -8.0f * d);
+        }
+        return 0;
+    case SLO_Q5_0:
+        /* IntDot.Decode.cs:101-123: u = the 5-bit code, a = d, b = -16 d */
+        for (int64_t blk = 0; blk < nb; blk++, p += 22, u += 32, a += 2, b += 2) {
+            float d = h_at(p);
+            uint32_t qh;
+            memcpy(&qh, p + 2, 4);
+            for (int i = 0; i < 16; i++) {
+                u[i] = (uint8_t)((p[6 + i] & 15) | (((qh >> i) & 1u) << 4));
+                u[16 + i] = (uint8_t)((p[6 + i] >> 4) | (((qh >> (i + 16)) & 1u) << 4));
+            }
+            set_block(a, b, d, -16.0f * d);
+        }
+        return 0;
+    case SLO_IQ4_NL:
+        /* IntDot.Decode.cs:225-238: u = kvalues[nibble] + 128, a = d, b = -128 d */
+        for (int64_t blk = 0; blk < nb; blk++, p += 18, u += 32, a += 2, b += 2) {
+            float d = h_at(p);
+            for (int i = 0; i < 16; i++) {
+                u[i] = (uint8_t)(iq4nl_values[p[2 + i] & 15] + 128);
+                u[16 + i] = (uint8_t)(iq4nl_values[p[2 + i] >> 4] + 128);
+            }
+            set_block(a, b, d, -128.0f * d);
         }
         return 0;
     case SLO_Q4_K:

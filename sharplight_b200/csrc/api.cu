@@ -281,8 +281,8 @@ slc_result slc_buffer_densify(slc_device *d, void *dst, const void *src, int64_t
 static slc_result check_weight_args(slc_device *d, int32_t fmt, int64_t n, int64_t k, const void *blocks, int64_t bytes)
 {
     if (!d) return fail(SLC_ERR_INVALID_ARGUMENT, "device is null");
-    const int bs = block_size(fmt);
-    if (bs == 0) return fail(SLC_ERR_UNSUPPORTED, "weight format is not one of Q4_0, Q8_0, Q4_K, Q6_K");
+    const int bs = source_block_size(fmt);
+    if (bs == 0) return fail(SLC_ERR_UNSUPPORTED, "weight format is not one of Q4_0, Q8_0, Q4_K, Q6_K, Q5_0, IQ4_NL");
     if (n < 0 || k <= 0) return fail(SLC_ERR_INVALID_ARGUMENT, "bad weight shape");
     if (k % bs != 0) {
         char msg[96];
@@ -290,7 +290,7 @@ static slc_result check_weight_args(slc_device *d, int32_t fmt, int64_t n, int64
         return fail(SLC_ERR_INVALID_ARGUMENT, msg);
     }
     if (n > (1 << 30) || k > (1 << 30)) return fail(SLC_ERR_UNSUPPORTED, "weight dimension too large");
-    if (bytes != n * (k / bs) * block_bytes(fmt)) return fail(SLC_ERR_INVALID_ARGUMENT, "bytes != n * k / block_size * block_bytes");
+    if (bytes != n * (k / bs) * source_block_bytes(fmt)) return fail(SLC_ERR_INVALID_ARGUMENT, "bytes != n * k / block_size * block_bytes");
     if (bytes > 0 && !blocks) return fail(SLC_ERR_INVALID_ARGUMENT, "blocks is null");
     return SLC_OK;
 }
@@ -305,22 +305,30 @@ slc_result slc_weight_upload(slc_device *d, int32_t fmt, int64_t n, int64_t k, c
     SLC_CUDA(cudaSetDevice(d->index));
     slc_weight *w = new (std::nothrow) slc_weight();
     if (!w) return fail(SLC_ERR_OUT_OF_MEMORY, "host allocation failed");
-    w->dev = d; w->fmt = fmt; w->n = n; w->k = k;
+    // Q5_0 and IQ4_NL are rewritten as Q8_0 blocks on the device first (exactly); the kernels see a Q8_0 weight
+    const int dev_fmt = device_format(fmt);
+    w->dev = d; w->fmt = dev_fmt; w->src_fmt = fmt; w->n = n; w->k = k;
     const int n_pad = (int)round_up((size_t)n, 16), k_pad = (int)round_up((size_t)k, 256);
-    w->bytes = round_up(weight_bytes(fmt, n_pad, k_pad), 256) + 256;
-    uint8_t *raw = nullptr;
+    w->bytes = round_up(weight_bytes(dev_fmt, n_pad, k_pad), 256) + 256;
+    uint8_t *raw = nullptr, *converted = nullptr;
+    const long long src_blocks = n * (k / source_block_size(fmt));
     cudaError_t e = cudaMalloc(&w->base, w->bytes);
     if (e == cudaSuccess && bytes > 0) e = cudaMalloc(&raw, (size_t)bytes);
     if (e == cudaSuccess && bytes > 0) e = cudaMemcpyAsync(raw, blocks, (size_t)bytes, cudaMemcpyHostToDevice, d->stream);
-    if (e == cudaSuccess) e = launch_repack(fmt, (int)n, (int)k, n_pad, k_pad, raw, w->base, false, d->stream);
+    if (e == cudaSuccess && bytes > 0 && dev_fmt != fmt) {
+        e = cudaMalloc(&converted, (size_t)src_blocks * block_bytes(dev_fmt));
+        if (e == cudaSuccess) e = launch_convert_to_q8_0(fmt, raw, converted, src_blocks, d->stream);
+    }
+    if (e == cudaSuccess) e = launch_repack(dev_fmt, (int)n, (int)k, n_pad, k_pad, converted ? converted : raw, w->base, false, d->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);
     if (raw) cudaFree(raw);
+    if (converted) cudaFree(converted);
     if (e != cudaSuccess) {
         if (w->base) cudaFree(w->base);
         delete w;
         return cuda_fail(e, "slc_weight_upload");
     }
-    w->view.fmt = fmt; w->view.n = (int)n; w->view.k = (int)k; w->view.n_pad = n_pad; w->view.k_pad = k_pad;
+    w->view.fmt = dev_fmt; w->view.n = (int)n; w->view.k = (int)k; w->view.n_pad = n_pad; w->view.k_pad = k_pad;
     w->view.data = w->base;
     *out = w;
     return SLC_OK;
@@ -333,7 +341,7 @@ slc_result slc_weight_upload_kslice(slc_device *d, int32_t fmt, int64_t n, int64
     *out = nullptr;
     slc_result r = check_weight_args(d, fmt, n, k, blocks, bytes);
     if (r != SLC_OK) return r;
-    const int bs = block_size(fmt), bb = block_bytes(fmt);
+    const int bs = source_block_size(fmt), bb = source_block_bytes(fmt);
     if (k0 < 0 || k1 <= k0 || k1 > k || k0 % bs != 0 || k1 % bs != 0) {
         return fail(SLC_ERR_INVALID_ARGUMENT, "K slice must be non-empty and aligned to the block size");
     }
@@ -349,6 +357,7 @@ slc_result slc_weight_upload_kslice(slc_device *d, int32_t fmt, int64_t n, int64
 slc_result slc_weight_download(slc_weight *w, void *blocks, int64_t bytes)
 {
     if (!w) return fail(SLC_ERR_INVALID_ARGUMENT, "weight is null");
+    if (w->src_fmt != w->fmt) return fail(SLC_ERR_UNSUPPORTED, "a weight converted at upload (Q5_0, IQ4_NL) keeps no raw blocks of its format");
     const long long want = w->n * (w->k / block_size(w->fmt)) * block_bytes(w->fmt);
     if (bytes != want) return fail(SLC_ERR_BUFFER_TOO_SMALL, "bytes != n * k / block_size * block_bytes");
     if (bytes == 0) return SLC_OK;
@@ -376,7 +385,7 @@ static const uint32_t SLC_LAYOUT_VERSION = 1;
 struct LayoutHeader
 {
     uint32_t magic, version;
-    int32_t fmt, reserved;
+    int32_t fmt, src_fmt;   // src_fmt: 0, or the uploaded format of a weight whose records are Q8_0 after conversion
     int64_t n, k, n_pad, k_pad, payload;
 };
 
@@ -392,7 +401,8 @@ slc_result slc_weight_export_layout(slc_weight *w, void *out, int64_t bytes)
     if (!w || !out) return fail(SLC_ERR_INVALID_ARGUMENT, "weight or out is null");
     const size_t payload = weight_bytes(w->fmt, w->view.n_pad, w->view.k_pad);
     if (bytes != (int64_t)(sizeof(LayoutHeader) + payload)) return fail(SLC_ERR_BUFFER_TOO_SMALL, "bytes != slc_weight_layout_bytes");
-    LayoutHeader h{ SLC_LAYOUT_MAGIC, SLC_LAYOUT_VERSION, w->fmt, 0, w->n, w->k, w->view.n_pad, w->view.k_pad, (int64_t)payload };
+    // (the second format field: what was uploaded, when the records are of another format -- Q5_0, IQ4_NL; else 0)
+    LayoutHeader h{ SLC_LAYOUT_MAGIC, SLC_LAYOUT_VERSION, w->fmt, w->src_fmt != w->fmt ? w->src_fmt : 0, w->n, w->k, w->view.n_pad, w->view.k_pad, (int64_t)payload };
     memcpy(out, &h, sizeof h);
     SLC_CUDA(cudaSetDevice(w->dev->index));
     SLC_CUDA(cudaMemcpy(static_cast<uint8_t *>(out) + sizeof h, w->base, payload, cudaMemcpyDeviceToHost));
@@ -411,13 +421,13 @@ slc_result slc_weight_import_layout(slc_device *d, const void *artefact, int64_t
     const int bs = block_size(h.fmt);
     if (bs == 0 || h.n < 0 || h.k <= 0 || h.k % bs != 0 || h.n_pad != (int64_t)round_up((size_t)h.n, 16) ||
         h.k_pad != (int64_t)round_up((size_t)h.k, 256) || h.payload != (int64_t)weight_bytes(h.fmt, (int)h.n_pad, (int)h.k_pad) ||
-        bytes != (int64_t)sizeof(LayoutHeader) + h.payload) {
+        bytes != (int64_t)sizeof(LayoutHeader) + h.payload || (h.src_fmt != 0 && (device_format(h.src_fmt) != h.fmt || h.src_fmt == h.fmt))) {
         return fail(SLC_ERR_INVALID_ARGUMENT, "weight-layout artefact: inconsistent header");
     }
     SLC_CUDA(cudaSetDevice(d->index));
     slc_weight *w = new (std::nothrow) slc_weight();
     if (!w) return fail(SLC_ERR_OUT_OF_MEMORY, "host allocation failed");
-    w->dev = d; w->fmt = h.fmt; w->n = h.n; w->k = h.k;
+    w->dev = d; w->fmt = h.fmt; w->src_fmt = h.src_fmt ? h.src_fmt : h.fmt; w->n = h.n; w->k = h.k;
     w->bytes = round_up((size_t)h.payload, 256) + 256;
     cudaError_t e = cudaMalloc(&w->base, w->bytes);
     if (e == cudaSuccess) e = cudaMemsetAsync(w->base, 0, w->bytes, d->stream);
@@ -439,7 +449,7 @@ slc_result slc_weight_import_layout(slc_device *d, const void *artefact, int64_t
 slc_result slc_weight_shape(slc_weight *w, int32_t *format, int64_t *n, int64_t *k, int64_t *device_bytes)
 {
     if (!w) return fail(SLC_ERR_INVALID_ARGUMENT, "weight is null");
-    if (format) *format = w->fmt;
+    if (format) *format = w->src_fmt;   // the format that was uploaded
     if (n) *n = w->n;
     if (k) *k = w->k;
     if (device_bytes) *device_bytes = (int64_t)w->bytes;
@@ -1276,6 +1286,22 @@ slc_result slc_debug_block_dots(slc_matmul *op, const void *x, int32_t x_dtype, 
         if (e != cudaSuccess) r = cuda_fail(e, "slc_debug_block_dots");
     }
     cudaFree(dump);
+    // A weight converted at upload: the kernels exported the dots with the device format's unsigned-code offset (Q8_0: 128);
+    // the reference's decoder for the uploaded format uses another (Q5_0: 16). The difference times the block's
+    // activation sum puts them right (host side: this is the parity export, not the data path).
+    const int delta = unsigned_code_offset(op->w->src_fmt) - unsigned_code_offset(op->w->fmt);
+    if (r == SLC_OK && delta != 0) {
+        const long long kb = k / 32, kbp = op->act->k_pad / 32;
+        std::vector<int> isum;
+        try { isum.resize((size_t)rows * kbp); } catch (...) { return fail(SLC_ERR_OUT_OF_MEMORY, "host allocation failed"); }
+        SLC_CUDA(cudaMemcpy(isum.data(), op->act->planes.isum, isum.size() * sizeof(int), cudaMemcpyDeviceToHost));
+        for (long long t = 0; t < rows; t++) {
+            for (long long row = 0; row < n; row++) {
+                int32_t *o = s32 + (t * n + row) * kb;
+                for (long long b = 0; b < kb; b++) o[b] += delta * isum[(size_t)(t * kbp + b)];
+            }
+        }
+    }
     return r;
 }
 

@@ -190,7 +190,7 @@ slc_result slc_gguf_tensor_count(slc_gguf *g, int64_t *count)
 // bytes of the tensor when it is a 2-D tensor of a served format; 0 otherwise
 static uint64_t served_bytes(const GgufTensor &t)
 {
-    const int bs = block_size((int)t.type), bb = block_bytes((int)t.type);
+    const int bs = source_block_size((int)t.type), bb = source_block_bytes((int)t.type);
     if (bs == 0 || t.rank != 2 || t.dims[0] == 0 || t.dims[0] % bs != 0 || t.dims[1] > (1ull << 31) || t.dims[0] > (1ull << 31)) return 0;
     return t.dims[1] * (t.dims[0] / bs) * bb;
 }
@@ -208,7 +208,7 @@ slc_result slc_gguf_tensor_info(slc_gguf *g, int64_t index, char *name_out, int3
     if (rank) *rank = t.rank;
     if (k) *k = (int64_t)t.dims[0];                         // innermost dimension
     if (n) *n = t.rank >= 2 ? (int64_t)t.dims[1] : 1;
-    if (bytes) *bytes = (int64_t)served_bytes(t);           // 0: not a 2-D tensor of Q4_0 / Q8_0 / Q4_K / Q6_K
+    if (bytes) *bytes = (int64_t)served_bytes(t);           // 0: not a 2-D tensor of a served format
     return SLC_OK;
 }
 
@@ -229,7 +229,7 @@ slc_result slc_weight_upload_gguf(slc_device *d, slc_gguf *g, int64_t index, slc
     if (!d || !g || index < 0 || index >= (int64_t)g->tensors.size()) return g_fail(SLC_ERR_INVALID_ARGUMENT, "null argument or index out of range");
     const GgufTensor &t = g->tensors[(size_t)index];
     const uint64_t bytes = served_bytes(t);
-    if (bytes == 0) return g_fail(SLC_ERR_UNSUPPORTED, "'" + t.name + "' is not a 2-D tensor of Q4_0, Q8_0, Q4_K or Q6_K");
+    if (bytes == 0) return g_fail(SLC_ERR_UNSUPPORTED, "'" + t.name + "' is not a 2-D tensor of Q4_0, Q8_0, Q4_K, Q6_K, Q5_0 or IQ4_NL");
     const uint64_t start = g->data_offset + t.offset;
     if (t.offset % g->alignment != 0 || start > g->length || bytes > g->length - start) {
         return g_fail(SLC_ERR_INVALID_ARGUMENT, "'" + t.name + "': data outside the file or misaligned");

@@ -18,7 +18,8 @@ struct slc_device
 struct slc_weight
 {
     slc_device *dev = nullptr;
-    int fmt = 0;
+    int fmt = 0;       // the format of the device records (what the kernels see)
+    int src_fmt = 0;   // the format that was uploaded (differs for the formats converted at upload: Q5_0, IQ4_NL -> Q8_0)
     long long n = 0, k = 0;
     uint8_t *base = nullptr;
     size_t bytes = 0;

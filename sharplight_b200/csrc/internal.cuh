@@ -98,6 +98,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity)
 cudaError_t launch_repack(int fmt, int n, int k, int n_pad, int k_pad, uint8_t *raw, uint8_t *data, bool to_raw,
                           cudaStream_t stream);
 
+// convert.cu: raw Q5_0 / IQ4_NL blocks -> raw Q8_0 blocks (34 bytes each), exactly.
+cudaError_t launch_convert_to_q8_0(int src_fmt, const uint8_t *src, uint8_t *dst, long long blocks, cudaStream_t stream);
+
 // quantize.cu: x (f32 or bf16, device) -> ActView planes. x_dtype: 0 = f32, 1 = bf16.
 struct ActPlanes
 {

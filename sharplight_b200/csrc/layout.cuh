@@ -65,6 +65,28 @@ __host__ __device__ inline int block_bytes(int fmt)
     return fmt == FMT_Q4_0 ? 18 : fmt == FMT_Q8_0 ? 34 : fmt == FMT_Q4_K ? 144 : fmt == FMT_Q6_K ? 210 : 0;
 }
 
+// Formats that are accepted at upload and turned into the Q8_0 device layout, exactly: Q5_0 { f16 d; u32 qh; u8 qs[16] }
+// (value d * (q - 16): the signed code q - 16 fits a byte) and IQ4_NL { f16 d; u8 qs[16] } (value d * codebook[nibble], the
+// codebook entry being the signed byte). The reference's integer-dot path treats them the same way: unsigned code, the
+// block's f16 d, an offset of -16 d or -128 d (src/Sharplight.Cpu/IntDot.Decode.cs:101-123, 225-238). They cost 34 bytes
+// per 32 values on the device instead of 22 / 18.
+enum : int { FMT_Q5_0 = 6, FMT_IQ4_NL = 20 };
+
+// The format the kernels see for an uploaded format (0: not served).
+__host__ __device__ inline int device_format(int fmt)
+{
+    return (fmt == FMT_Q5_0 || fmt == FMT_IQ4_NL) ? FMT_Q8_0 : block_size(fmt) ? fmt : 0;
+}
+// Values and bytes per block of the format as the host hands it over.
+__host__ __device__ inline int source_block_size(int fmt) { return (fmt == FMT_Q5_0 || fmt == FMT_IQ4_NL) ? 32 : block_size(fmt); }
+__host__ __device__ inline int source_block_bytes(int fmt) { return fmt == FMT_Q5_0 ? 22 : fmt == FMT_IQ4_NL ? 18 : block_bytes(fmt); }
+// What the reference's unsigned code adds to the signed code the kernels multiply (block-dot export): Q8_0 and IQ4_NL
+// 128, Q4_0 8, Q6_K 32, Q4_K 0, Q5_0 16.
+__host__ __device__ inline int unsigned_code_offset(int fmt)
+{
+    return fmt == FMT_Q8_0 || fmt == FMT_IQ4_NL ? 128 : fmt == FMT_Q4_0 ? 8 : fmt == FMT_Q6_K ? 32 : fmt == FMT_Q5_0 ? 16 : 0;
+}
+
 // 16-byte units of codes per record (all formats: a multiple of 32 lanes).
 __host__ __device__ constexpr int code_units(int fmt)
 {

@@ -39,10 +39,11 @@ def write_gguf(path, tensors, alignment=64, version=3):
 def gguf_file(tmp_path):
     w1 = synth.weight_blocks("Q4_K", 48, 512, seed=1)
     w2 = synth.weight_blocks("Q8_0", 20, 96, seed=2)
+    w3 = synth.weight_blocks("Q5_0", 24, 128, seed=3)
     norm = np.arange(96, dtype=np.float32).tobytes()
     path = str(tmp_path / "tiny.gguf")
     write_gguf(path, [("blk.0.ffn_down.weight", 12, [512, 48], w1.tobytes()), ("output_norm.weight", 0, [96], norm),
-                      ("blk.0.attn_q.weight", 8, [96, 20], w2.tobytes())])
+                      ("blk.0.attn_q.weight", 8, [96, 20], w2.tobytes()), ("blk.0.attn_k.weight", 6, [128, 24], w3.tobytes())])
     return path, w1, w2
 
 
@@ -65,10 +66,11 @@ def test_gguf_table_is_parsed(gguf_file):
     h = _open(lib, path)
     try:
         count = C.c_int64()
-        assert lib.slc_gguf_tensor_count(h, C.byref(count)) == N.OK and count.value == 3
+        assert lib.slc_gguf_tensor_count(h, C.byref(count)) == N.OK and count.value == 4
         assert _info(lib, h, 0) == ("blk.0.ffn_down.weight", 12, 2, 48, 512, w1.size)
         assert _info(lib, h, 1) == ("output_norm.weight", 0, 1, 1, 96, 0)          # f32, 1-D: not a served weight
         assert _info(lib, h, 2) == ("blk.0.attn_q.weight", 8, 2, 20, 96, w2.size)
+        assert _info(lib, h, 3) == ("blk.0.attn_k.weight", 6, 2, 24, 128, 24 * 4 * 22)   # Q5_0: served through the Q8_0 layout
         idx = C.c_int64()
         assert lib.slc_gguf_find(h, b"blk.0.attn_q.weight", C.byref(idx)) == N.OK and idx.value == 2
         assert lib.slc_gguf_find(h, b"nope", C.byref(idx)) != N.OK and idx.value == -1
@@ -113,6 +115,17 @@ def test_gguf_upload_equals_upload_of_the_same_blocks(cuda_device, gguf_file):
                 assert np.array_equal(a.run(x).view(np.uint32), b.run(x).view(np.uint32))
             finally:
                 a.dispose(); b.dispose(); w.dispose(); ref.dispose()
+        # the Q5_0 tensor: converted at upload, results equal to an upload of the same blocks
+        wh = C.c_void_p()
+        assert lib.slc_weight_upload_gguf(cuda_device.handle, h, 3, C.byref(wh)) == N.OK, lib.slc_gguf_last_error()
+        w = DeviceWeight(cuda_device, N.FMT_Q5_0, 24, 128, wh.value)
+        ref = cuda_device.upload_weight("Q5_0", (24, 128), synth.weight_blocks("Q5_0", 24, 128, seed=3))
+        x = synth.activations(3, 128, seed=5)
+        a, b = MatMulOp(cuda_device, w, 3), MatMulOp(cuda_device, ref, 3)
+        try:
+            assert np.array_equal(a.run(x).view(np.uint32), b.run(x).view(np.uint32))
+        finally:
+            a.dispose(); b.dispose(); w.dispose(); ref.dispose()
         wh = C.c_void_p()
         assert lib.slc_weight_upload_gguf(cuda_device.handle, h, 1, C.byref(wh)) == N.ERR_UNSUPPORTED      # the f32 norm vector
     finally:

@@ -6,6 +6,8 @@ floor used for outputs that cancel to nothing). Shapes follow the reference's ow
 (tests/Sharplight.Cpu.Tests/QuantTests.cs:119-128, tests/Sharplight.Vulkan.Tests/MatMulTests.cs:7-48, MmqTests.cs:21-98,
 SkinnyGemmTests.cs:29-39 of the Sharplight tree).
 """
+import ctypes as C
+
 import numpy as np
 import pytest
 
@@ -756,3 +758,76 @@ def test_deferred_quantization_bit_identical(cuda_device, type_name, n, k, rows)
         assert cuda_device.last_status() == 0
     finally:
         a0.dispose(); a1.dispose(); op.dispose(); w.dispose()
+
+
+# ---- formats rewritten at upload as Q8_0 device records: Q5_0, IQ4_NL ---------------------------------------------------
+
+CONVERTED = ["Q5_0", "IQ4_NL"]
+
+
+@pytest.mark.parametrize("type_name", CONVERTED)
+@pytest.mark.parametrize("n,k,rows", [(48, 256, 1), (100, 1568, 3), (7, 96, 4), (300, 1024, 16), (520, 512, 64), (100, 512, 200),
+                                      (1000, 768, 129)])
+def test_converted_formats_every_kernel_family(cuda_device, type_name, n, k, rows):
+    """Q5_0 and IQ4_NL weights (src/Sharplight.Cpu/IntDot.Decode.cs:101-123, 225-238) through the mat-vec, the skinny
+    kernel and the GEMM: y against the oracle's integer-dot MatMul of the uploaded format, and the int32 block dots -- in the
+    reference's unsigned-code convention for that format -- bit for bit."""
+    _, kern = check_matmul(cuda_device, type_name, n, k, rows, seed=n + k + rows)
+    assert kern[0] == (N.KERNEL_MMVQ if rows <= 2 else N.KERNEL_MMQ if rows > 64 else kern[0])
+    assert cuda_device.last_status() == 0
+
+
+@pytest.mark.parametrize("type_name", CONVERTED)
+def test_converted_formats_f32_activations_and_shape(cuda_device, type_name):
+    """The f32-activation mat-vec on a converted weight against the exact product of the dequantized weight (atol 2e-3,
+    rtol 1e-4); the handle reports the uploaded format and refuses a download."""
+    n, k, rows = 100, 1024, 3
+    blocks = synth.weight_blocks(type_name, n, k, seed=77)
+    x = synth.activations(rows, k, seed=78)
+    w = cuda_device.upload_weight(type_name, (n, k), blocks)
+    op = MatMulOp(cuda_device, w, rows, f32_activations=True)
+    try:
+        y = op.run(x)
+        exact = sl_oracle.matmul_f64(FMT_OF[type_name], blocks, n, k, x, threads=4)
+        assert np.all(np.abs(y - exact) <= 2e-3 + 1e-4 * np.abs(exact)), float(np.max(np.abs(y - exact)))
+        fmt = C.c_int32(0)
+        assert N.load().slc_weight_shape(w.handle, C.byref(fmt), None, None, None) == N.OK
+        assert fmt.value == FMT_OF[type_name]
+        with pytest.raises(Exception):
+            w.download()
+    finally:
+        op.dispose()
+        w.dispose()
+
+
+@pytest.mark.parametrize("type_name", CONVERTED)
+def test_converted_formats_kslice_and_layout_artefact(cuda_device, type_name):
+    """The K-slice upload of a row-split shard and the layout artefact of a converted weight: both give the results of a
+    plain upload of the same blocks, bit for bit, block dots included (the artefact remembers the uploaded format)."""
+    n, k, rows = 64, 1024, 5
+    blocks = synth.weight_blocks(type_name, n, k, seed=5)
+    x = synth.activations(rows, k, seed=6)
+    bs, bb = N.BLOCK[FMT_OF[type_name]]
+    k0, k1 = 256, 768
+    sliced = np.ascontiguousarray(blocks.reshape(n, k // bs, bb)[:, k0 // bs:k1 // bs]).reshape(-1)
+    wh = C.c_void_p()
+    assert N.load().slc_weight_upload_kslice(cuda_device.handle, FMT_OF[type_name], n, k, blocks.ctypes.data_as(C.c_void_p),
+                                             blocks.size, k0, k1, C.byref(wh)) == N.OK
+    from sharplight_b200.provider import DeviceWeight
+    ws = DeviceWeight(cuda_device, FMT_OF[type_name], n, k1 - k0, wh.value)
+    wr = cuda_device.upload_weight(type_name, (n, k1 - k0), sliced)
+    wa = cuda_device.import_weight_layout(wr.export_layout())
+    ops = [MatMulOp(cuda_device, w, rows) for w in (ws, wr, wa)]
+    try:
+        xs = np.ascontiguousarray(x[:, k0:k1])
+        ys = [op.run(xs) for op in ops]
+        assert np.array_equal(ys[0].view(np.uint32), ys[1].view(np.uint32))
+        assert np.array_equal(ys[2].view(np.uint32), ys[1].view(np.uint32))
+        _, _, s32 = sl_oracle.matmul_intdot(FMT_OF[type_name], sliced, n, k1 - k0, xs, threads=4, want_s32=True)
+        for op in ops:
+            assert np.array_equal(op.block_dots(xs), s32)
+    finally:
+        for op in ops:
+            op.dispose()
+        for w in (ws, wr, wa):
+            w.dispose()

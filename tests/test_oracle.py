@@ -9,7 +9,8 @@ import pytest
 from helpers import FMT_OF, TYPE_OF, np_oracle, relative_rms, same_floats, sl_oracle
 from sharplight_b200 import synth
 
-RECORDS = [f"ext_{t}_{kind}" for t in (2, 8, 12, 14) for kind in ("ggml", "random")] + [f"src_{t}" for t in (2, 8, 12, 14)]
+RECORDS = ([f"ext_{t}_{kind}" for t in (2, 6, 8, 12, 14, 20) for kind in ("ggml", "random")] +
+           [f"src_{t}" for t in (2, 6, 8, 12, 14)])
 
 
 def _record(golden, name):
@@ -36,7 +37,7 @@ def test_decode_matches_dequantize(golden, name):
     formats stay below 128."""
     tid, rows, cols, blocks, expected = _record(golden, name)
     u, a, b = sl_oracle.decode(tid, blocks, rows, cols)
-    if tid != 8:
+    if tid not in (8, 20):
         assert u.max() < 128
     actual = np.repeat(a, 16, axis=1) * u.astype(np.float32) + np.repeat(b, 16, axis=1)
     assert np.all(np.abs(expected - actual) <= 1e-6 * np.abs(expected) + 1e-7)
