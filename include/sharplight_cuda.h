@@ -55,16 +55,21 @@ enum
 };
 
 /* Weight formats, numbered like ggml (src/Sharplight.Import.Gguf/GgmlTypes.cs:51-92); block sizes and bytes as in
-   src/Sharplight.Core/Tensors/DataType.cs:102,106,110,116,120,124. Q5_0 and IQ4_NL are rewritten at upload, exactly, as
-   Q8_0 device records (their values are a signed byte times the block's f16 d, which is how the reference's integer-dot
-   decoder treats them too, src/Sharplight.Cpu/IntDot.Decode.cs:101-123,225-238): they cost 34 bytes per 32 values on
-   the device, run through the Q8_0 kernels, and have no slc_weight_download. */
+   src/Sharplight.Core/Tensors/DataType.cs:102,106,110,116,118,120,124. Q5_0 and IQ4_NL are rewritten at upload, exactly,
+   as Q8_0 device records (their values are a signed byte times the block's f16 d, which is how the reference's
+   integer-dot decoder treats them too, src/Sharplight.Cpu/IntDot.Decode.cs:101-123,225-238): they cost 34 bytes per 32
+   values on the device and run through the Q8_0 kernels. Q5_K is split at upload, exactly, into two Q4_K weights -- the
+   block without its fifth bits, and the fifth bits as nibbles with d' = 16 d, dmin' = 0 -- and every MatMul runs both,
+   the second adding onto the first: 288 bytes per 256 values and two launches. An upload whose 16 d is not an f16
+   returns SLC_ERR_UNSUPPORTED. Converted weights have no slc_weight_download; Q5_K has no layout artefact and takes no
+   part in a dual MatMul. */
 typedef enum slc_format
 {
     SLC_FMT_Q4_0 = 2,   /* 32 values, 18 bytes: f16 d; u8 qs[16] */
     SLC_FMT_Q5_0 = 6,   /* 32 values, 22 bytes: f16 d; u32 qh; u8 qs[16] (converted at upload) */
     SLC_FMT_Q8_0 = 8,   /* 32 values, 34 bytes: f16 d; i8 q[32] */
     SLC_FMT_Q4_K = 12,  /* 256 values, 144 bytes: f16 d; f16 dmin; u8 scales[12]; u8 qs[128] */
+    SLC_FMT_Q5_K = 13,  /* 256 values, 176 bytes: f16 d; f16 dmin; u8 scales[12]; u8 qh[32]; u8 qs[128] (split at upload) */
     SLC_FMT_Q6_K = 14,  /* 256 values, 210 bytes: u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d */
     SLC_FMT_IQ4_NL = 20 /* 32 values, 18 bytes: f16 d; u8 qs[16], nibbles index a 16-entry codebook (converted at upload) */
 } slc_format;
@@ -201,7 +206,7 @@ SLC_API slc_result slc_weight_upload_kslice(slc_device *device, int32_t format, 
                                             const void *blocks, int64_t bytes, int64_t k0, int64_t k1,
                                             slc_weight **out);
 /* Writes the weight back as raw ggml blocks (inverse of the device layout; for verification). SLC_ERR_UNSUPPORTED for a
-   weight that was converted at upload (Q5_0, IQ4_NL). */
+   weight that was converted at upload (Q5_0, IQ4_NL, Q5_K). */
 SLC_API slc_result slc_weight_download(slc_weight *weight, void *blocks, int64_t bytes);
 /* The device layout as an artefact (the reference's providers name artefact tiers a model package may carry for them,
    src/Sharplight.Core/Runtime/IComputeDevice.cs:47-52): export writes a 56-byte header (magic, version, format, shape)

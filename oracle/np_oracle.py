@@ -9,8 +9,8 @@ from __future__ import annotations
 
 import numpy as np
 
-Q4_0, Q5_0, Q8_0, Q4_K, Q6_K, IQ4_NL = 2, 6, 8, 12, 14, 20
-BLOCK = {Q4_0: (32, 18), Q5_0: (32, 22), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210), IQ4_NL: (32, 18)}
+Q4_0, Q5_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL = 2, 6, 8, 12, 13, 14, 20
+BLOCK = {Q4_0: (32, 18), Q5_0: (32, 22), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ4_NL: (32, 18)}
 # IQ4_NL's non-linear codebook (src/Sharplight.Cpu/Quant.cs:409)
 IQ4NL_VALUES = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.int32)
 
@@ -75,6 +75,21 @@ def codes(fmt: int, blocks: np.ndarray, n: int, k: int):
         sc, m = scale_min(blk[..., 4:16])
         qs = blk[..., 16:144].astype(np.int32).reshape(n, nb, 4, 32)
         u = np.concatenate([qs & 15, qs >> 4], axis=-1).reshape(n, k)
+        a8 = d[..., None] * sc.astype(np.float32)
+        b8 = -dmin[..., None] * m.astype(np.float32)
+        a = np.repeat(a8.reshape(n, nb * 8), 2, axis=1)
+        b = np.repeat(b8.reshape(n, nb * 8), 2, axis=1)
+    elif fmt == Q5_K:
+        # Q4_K plus a fifth bit: bit 2j / 2j + 1 of qh[l] for value l of the low- / high-nibble sub-block of chunk j
+        d = _f16(blk[..., 0:2])
+        dmin = _f16(blk[..., 2:4])
+        sc, m = scale_min(blk[..., 4:16])
+        qh = blk[..., 16:48].astype(np.int32)[:, :, None, :]                       # [n, nb, 1, 32]
+        qs = blk[..., 48:176].astype(np.int32).reshape(n, nb, 4, 32)
+        sh = (2 * np.arange(4))[None, None, :, None]
+        lo = (qs & 15) | (((qh >> sh) & 1) << 4)
+        hi = (qs >> 4) | (((qh >> (sh + 1)) & 1) << 4)
+        u = np.concatenate([lo, hi], axis=-1).reshape(n, k)
         a8 = d[..., None] * sc.astype(np.float32)
         b8 = -dmin[..., None] * m.astype(np.float32)
         a = np.repeat(a8.reshape(n, nb * 8), 2, axis=1)

@@ -20,7 +20,7 @@ int slo_block_size(int fmt)
 {
     switch (fmt) {
     case SLO_Q4_0: case SLO_Q8_0: case SLO_Q5_0: case SLO_IQ4_NL: return 32;
-    case SLO_Q4_K: case SLO_Q6_K: return 256;
+    case SLO_Q4_K: case SLO_Q5_K: case SLO_Q6_K: return 256;
     default: return 0;
     }
 }
@@ -33,6 +33,7 @@ int slo_block_bytes(int fmt)
     case SLO_IQ4_NL: return 18;
     case SLO_Q8_0: return 34;
     case SLO_Q4_K: return 144;
+    case SLO_Q5_K: return 176;
     case SLO_Q6_K: return 210;
     default: return 0;
     }
@@ -165,6 +166,30 @@ int slo_dequantize_row(int fmt, const uint8_t *p, int64_t k, float *dst)
             }
         }
         return 0;
+    case SLO_Q5_K:
+        /* Quant.cs:548-582: { f16 d; f16 dmin; u8 scales[12]; u8 qh[32]; u8 qs[128] }: Q4_K with a fifth bit per value,
+           bit 2j (2j + 1) of qh[l] for value l of the low-nibble (high-nibble) sub-block of chunk j */
+        for (int64_t b = 0; b < nb; b++, p += 176, dst += 256) {
+            float d = h_at(p), dmin = h_at(p + 2);
+            const uint8_t *scales = p + 4, *qh = p + 16, *qs = p + 48;
+            for (int j = 0; j < 4; j++, qs += 32) {
+                int sc1, m1, sc2, m2;
+                scale_min(2 * j, scales, &sc1, &m1);
+                scale_min(2 * j + 1, scales, &sc2, &m2);
+                float d1 = d * (float)sc1, mm1 = dmin * (float)m1;
+                float d2 = d * (float)sc2, mm2 = dmin * (float)m2;
+                float *o = dst + 64 * j;
+                for (int i = 0; i < 16; i++) v[i] = (uint8_t)((qs[i] & 15) | (((qh[i] >> (2 * j)) & 1) << 4));
+                store16_u8(v, d1, -mm1, o);
+                for (int i = 0; i < 16; i++) v[i] = (uint8_t)((qs[16 + i] & 15) | (((qh[16 + i] >> (2 * j)) & 1) << 4));
+                store16_u8(v, d1, -mm1, o + 16);
+                for (int i = 0; i < 16; i++) v[i] = (uint8_t)((qs[i] >> 4) | (((qh[i] >> (2 * j + 1)) & 1) << 4));
+                store16_u8(v, d2, -mm2, o + 32);
+                for (int i = 0; i < 16; i++) v[i] = (uint8_t)((qs[16 + i] >> 4) | (((qh[16 + i] >> (2 * j + 1)) & 1) << 4));
+                store16_u8(v, d2, -mm2, o + 48);
+            }
+        }
+        return 0;
     case SLO_Q6_K:
         for (int64_t b = 0; b < nb; b++, p += 210, dst += 256) {
             float d = h_at(p + 208);
@@ -284,6 +309,25 @@ int slo_decode_row(int fmt, const uint8_t *p, int64_t k, uint8_t *u, float *a, f
                 for (int i = 0; i < 32; i++) {
                     uj[i] = qs[32 * j + i] & 15;
                     uj[32 + i] = qs[32 * j + i] >> 4;
+                }
+            }
+            for (int j = 0; j < 8; j++) {
+                int sc, m;
+                scale_min(j, p + 4, &sc, &m);
+                set_block(a + 2 * j, b + 2 * j, d * (float)sc, -dmin * (float)m);
+            }
+        }
+        return 0;
+    case SLO_Q5_K:
+        /* IntDot.Decode.cs:150-176: the 5-bit codes, a = d * sc, b = -dmin * m per 32-value sub-block */
+        for (int64_t blk = 0; blk < nb; blk++, p += 176, u += 256, a += 16, b += 16) {
+            float d = h_at(p), dmin = h_at(p + 2);
+            const uint8_t *qh = p + 16, *qs = p + 48;
+            for (int j = 0; j < 4; j++) {
+                uint8_t *uj = u + 64 * j;
+                for (int i = 0; i < 32; i++) {
+                    uj[i] = (uint8_t)((qs[32 * j + i] & 15) | (((qh[i] >> (2 * j)) & 1) << 4));
+                    uj[32 + i] = (uint8_t)((qs[32 * j + i] >> 4) | (((qh[i] >> (2 * j + 1)) & 1) << 4));
                 }
             }
             for (int j = 0; j < 8; j++) {

@@ -5,14 +5,14 @@
  *
  * It restates, in plain C, the arithmetic of the reference's managed CPU provider (paths are relative to the
  * Sharplight source tree):
- *   - src/Sharplight.Cpu/Quant.cs            half decode, Q8_0 / Q4_0 / Q4_K / Q6_K / Q5_0 / IQ4_NL dequantization
+ *   - src/Sharplight.Cpu/Quant.cs            half decode, Q8_0 / Q4_0 / Q4_K / Q5_K / Q6_K / Q5_0 / IQ4_NL dequantization
  *   - src/Sharplight.Cpu/IntDot.cs           8-bit activation quantization (32-value blocks, 16-value group sums)
  *   - src/Sharplight.Cpu/IntDot.Decode.cs    weight rows -> unsigned codes u, multiplier a, offset b per 16 values
  *   - src/Sharplight.Cpu/IntDot.Kernels.cs   the scalar dot kernel (the specification of the float order)
  *   - src/Sharplight.Cpu/MatMulOp.cs         the integer-dot MatMul driver
  *
  * Parity pins: the dequantizers and decoders reproduce the ggml golden fixtures of the reference's own test suite
- * (tests/Sharplight.Cpu.Tests/Fixtures/ggml_quant_ext.bin and ggml_quant.bin, the records of ggml types 2, 6, 8, 12, 14, 20);
+ * (tests/Sharplight.Cpu.Tests/Fixtures/ggml_quant_ext.bin and ggml_quant.bin, the records of ggml types 2, 6, 8, 12, 13, 14, 20);
  * the quantizer reproduces the analytic known-answer cases of IntDotTests.QuantizeMatchesReference. No reference test
  * stores int32 block dots or int-dot outputs, so those are pinned through this restatement.
  */
@@ -26,7 +26,7 @@ extern "C" {
 #endif
 
 /* ggml type ids, as mapped by src/Sharplight.Import.Gguf/GgmlTypes.cs:51-92 */
-enum { SLO_Q4_0 = 2, SLO_Q5_0 = 6, SLO_Q8_0 = 8, SLO_Q4_K = 12, SLO_Q6_K = 14, SLO_IQ4_NL = 20 };
+enum { SLO_Q4_0 = 2, SLO_Q5_0 = 6, SLO_Q8_0 = 8, SLO_Q4_K = 12, SLO_Q5_K = 13, SLO_Q6_K = 14, SLO_IQ4_NL = 20 };
 
 int slo_block_size(int fmt);   /* values per block, 0 if unknown */
 int slo_block_bytes(int fmt);  /* bytes per block, 0 if unknown */

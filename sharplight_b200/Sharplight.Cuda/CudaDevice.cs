@@ -42,12 +42,13 @@ internal sealed class CudaDevice : IComputeDevice
     internal static int FormatOf(DataType type)
         => type == DataType.Q4_0 ? Slc.FormatQ4_0 : type == DataType.Q8_0 ? Slc.FormatQ8_0
          : type == DataType.Q4_K ? Slc.FormatQ4_K : type == DataType.Q6_K ? Slc.FormatQ6_K
-         : type == DataType.Q5_0 ? Slc.FormatQ5_0 : type == DataType.IQ4_NL ? Slc.FormatIQ4_NL : 0;   // the last two: Q8_0 records after upload
+         : type == DataType.Q5_0 ? Slc.FormatQ5_0 : type == DataType.IQ4_NL ? Slc.FormatIQ4_NL   // Q8_0 records after upload
+         : type == DataType.Q5_K ? Slc.FormatQ5_K : 0;                                               // two Q4_K weights after upload
 
-    internal static int BlockSize(int format) => format is Slc.FormatQ4_K or Slc.FormatQ6_K ? 256 : 32;
+    internal static int BlockSize(int format) => format is Slc.FormatQ4_K or Slc.FormatQ5_K or Slc.FormatQ6_K ? 256 : 32;
 
     /// <summary>
-    /// Yes only for MatMul with a static Q8_0 / Q4_0 / Q4_K / Q6_K / Q5_0 / IQ4_NL weight whose K is a multiple of the block size, f32 or bf16
+    /// Yes only for MatMul with a static Q8_0 / Q4_0 / Q4_K / Q6_K / Q5_0 / Q5_K / IQ4_NL weight whose K is a multiple of the block size, f32 or bf16
     /// activations, and activations that may be quantized to 8 bits -- the mirror of CpuOpSupport.CheckQuantizedMatMul
     /// (src/Sharplight.Cpu/CpuOpSupport.Linear.cs:21-53). Everything else goes to PlacementOptions.Fallback
     /// (PlacementPlanner.cs:238-248). View nodes (Reshape / Slice / Permute) are not asked: they stay on their group's device

@@ -120,6 +120,7 @@ internal static class Slc
 {
     public const int FormatQ4_0 = 2, FormatQ8_0 = 8, FormatQ4_K = 12, FormatQ6_K = 14;
     public const int FormatQ5_0 = 6, FormatIQ4_NL = 20;   // rewritten at upload as Q8_0 device records
+    public const int FormatQ5_K = 13;                     // split at upload into two Q4_K weights
     public const int F32 = 0, Bf16 = 1;
     public const uint MatMulRowInvariant = 1, MatMulF32Activations = 2;
     public const long F32ActivationsMaxK = 49152;

@@ -282,7 +282,7 @@ static slc_result check_weight_args(slc_device *d, int32_t fmt, int64_t n, int64
 {
     if (!d) return fail(SLC_ERR_INVALID_ARGUMENT, "device is null");
     const int bs = source_block_size(fmt);
-    if (bs == 0) return fail(SLC_ERR_UNSUPPORTED, "weight format is not one of Q4_0, Q8_0, Q4_K, Q6_K, Q5_0, IQ4_NL");
+    if (bs == 0) return fail(SLC_ERR_UNSUPPORTED, "weight format is not one of Q4_0, Q8_0, Q4_K, Q6_K, Q5_0, Q5_K, IQ4_NL");
     if (n < 0 || k <= 0) return fail(SLC_ERR_INVALID_ARGUMENT, "bad weight shape");
     if (k % bs != 0) {
         char msg[96];
@@ -295,6 +295,29 @@ static slc_result check_weight_args(slc_device *d, int32_t fmt, int64_t n, int64
     return SLC_OK;
 }
 
+// A device weight of a format the kernels serve, from raw blocks of that format already on the device (no synchronize).
+static cudaError_t weight_from_device_blocks(slc_device *d, int dev_fmt, int src_fmt, long long n, long long k, uint8_t *raw,
+                                             slc_weight **out)
+{
+    *out = nullptr;
+    slc_weight *w = new (std::nothrow) slc_weight();
+    if (!w) return cudaErrorMemoryAllocation;
+    w->dev = d; w->fmt = dev_fmt; w->src_fmt = src_fmt; w->n = n; w->k = k;
+    const int n_pad = (int)round_up((size_t)n, 16), k_pad = (int)round_up((size_t)k, 256);
+    w->bytes = round_up(weight_bytes(dev_fmt, n_pad, k_pad), 256) + 256;
+    cudaError_t e = cudaMalloc(&w->base, w->bytes);
+    if (e == cudaSuccess) e = launch_repack(dev_fmt, (int)n, (int)k, n_pad, k_pad, raw, w->base, false, d->stream);
+    if (e != cudaSuccess) {
+        if (w->base) cudaFree(w->base);
+        delete w;
+        return e;
+    }
+    w->view.fmt = dev_fmt; w->view.n = (int)n; w->view.k = (int)k; w->view.n_pad = n_pad; w->view.k_pad = k_pad;
+    w->view.data = w->base;
+    *out = w;
+    return cudaSuccess;
+}
+
 slc_result slc_weight_upload(slc_device *d, int32_t fmt, int64_t n, int64_t k, const void *blocks, int64_t bytes,
                              slc_weight **out)
 {
@@ -303,33 +326,44 @@ slc_result slc_weight_upload(slc_device *d, int32_t fmt, int64_t n, int64_t k, c
     slc_result r = check_weight_args(d, fmt, n, k, blocks, bytes);
     if (r != SLC_OK) return r;
     SLC_CUDA(cudaSetDevice(d->index));
-    slc_weight *w = new (std::nothrow) slc_weight();
-    if (!w) return fail(SLC_ERR_OUT_OF_MEMORY, "host allocation failed");
-    // Q5_0 and IQ4_NL are rewritten as Q8_0 blocks on the device first (exactly); the kernels see a Q8_0 weight
+    // Q5_0 and IQ4_NL are rewritten as Q8_0 blocks on the device first, Q5_K is split into two Q4_K weights (both exactly;
+    // layout.cuh): the kernels only ever see the four formats they have decoders for
     const int dev_fmt = device_format(fmt);
-    w->dev = d; w->fmt = dev_fmt; w->src_fmt = fmt; w->n = n; w->k = k;
-    const int n_pad = (int)round_up((size_t)n, 16), k_pad = (int)round_up((size_t)k, 256);
-    w->bytes = round_up(weight_bytes(dev_fmt, n_pad, k_pad), 256) + 256;
-    uint8_t *raw = nullptr, *converted = nullptr;
     const long long src_blocks = n * (k / source_block_size(fmt));
-    cudaError_t e = cudaMalloc(&w->base, w->bytes);
-    if (e == cudaSuccess && bytes > 0) e = cudaMalloc(&raw, (size_t)bytes);
+    const size_t dev_raw_bytes = (size_t)src_blocks * block_bytes(dev_fmt);
+    uint8_t *raw = nullptr, *conv = nullptr, *conv2 = nullptr;
+    int *overflow = nullptr;
+    slc_weight *w = nullptr, *high = nullptr;
+    int overflowed = 0;
+    cudaError_t e = cudaSuccess;
+    if (bytes > 0) e = cudaMalloc(&raw, (size_t)bytes);
     if (e == cudaSuccess && bytes > 0) e = cudaMemcpyAsync(raw, blocks, (size_t)bytes, cudaMemcpyHostToDevice, d->stream);
     if (e == cudaSuccess && bytes > 0 && dev_fmt != fmt) {
-        e = cudaMalloc(&converted, (size_t)src_blocks * block_bytes(dev_fmt));
-        if (e == cudaSuccess) e = launch_convert_to_q8_0(fmt, raw, converted, src_blocks, d->stream);
+        e = cudaMalloc(&conv, dev_raw_bytes);
+        if (e == cudaSuccess && fmt == FMT_Q5_K) {
+            e = cudaMalloc(&conv2, dev_raw_bytes);
+            if (e == cudaSuccess) e = cudaMalloc(&overflow, sizeof(int));
+            if (e == cudaSuccess) e = cudaMemsetAsync(overflow, 0, sizeof(int), d->stream);
+            if (e == cudaSuccess) e = launch_split_q5_k(raw, conv, conv2, src_blocks, overflow, d->stream);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(&overflowed, overflow, sizeof(int), cudaMemcpyDeviceToHost, d->stream);
+        } else if (e == cudaSuccess) {
+            e = launch_convert_to_q8_0(fmt, raw, conv, src_blocks, d->stream);
+        }
     }
-    if (e == cudaSuccess) e = launch_repack(dev_fmt, (int)n, (int)k, n_pad, k_pad, converted ? converted : raw, w->base, false, d->stream);
+    if (e == cudaSuccess) e = weight_from_device_blocks(d, dev_fmt, fmt, n, k, conv ? conv : raw, &w);
+    if (e == cudaSuccess && fmt == FMT_Q5_K) e = weight_from_device_blocks(d, dev_fmt, fmt, n, k, conv2, &high);
     if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);
     if (raw) cudaFree(raw);
-    if (converted) cudaFree(converted);
-    if (e != cudaSuccess) {
-        if (w->base) cudaFree(w->base);
-        delete w;
-        return cuda_fail(e, "slc_weight_upload");
+    if (conv) cudaFree(conv);
+    if (conv2) cudaFree(conv2);
+    if (overflow) cudaFree(overflow);
+    if (e != cudaSuccess || overflowed) {
+        if (w) { cudaFree(w->base); delete w; }
+        if (high) { cudaFree(high->base); delete high; }
+        if (e != cudaSuccess) return cuda_fail(e, "slc_weight_upload");
+        return fail(SLC_ERR_UNSUPPORTED, "Q5_K block with a scale whose sixteenfold is not an f16: the split into two Q4_K weights would not be exact");
     }
-    w->view.fmt = dev_fmt; w->view.n = (int)n; w->view.k = (int)k; w->view.n_pad = n_pad; w->view.k_pad = k_pad;
-    w->view.data = w->base;
+    w->high = high;
     *out = w;
     return SLC_OK;
 }
@@ -357,7 +391,7 @@ slc_result slc_weight_upload_kslice(slc_device *d, int32_t fmt, int64_t n, int64
 slc_result slc_weight_download(slc_weight *w, void *blocks, int64_t bytes)
 {
     if (!w) return fail(SLC_ERR_INVALID_ARGUMENT, "weight is null");
-    if (w->src_fmt != w->fmt) return fail(SLC_ERR_UNSUPPORTED, "a weight converted at upload (Q5_0, IQ4_NL) keeps no raw blocks of its format");
+    if (w->src_fmt != w->fmt) return fail(SLC_ERR_UNSUPPORTED, "a weight converted at upload (Q5_0, IQ4_NL, Q5_K) keeps no raw blocks of its format");
     const long long want = w->n * (w->k / block_size(w->fmt)) * block_bytes(w->fmt);
     if (bytes != want) return fail(SLC_ERR_BUFFER_TOO_SMALL, "bytes != n * k / block_size * block_bytes");
     if (bytes == 0) return SLC_OK;
@@ -392,6 +426,7 @@ struct LayoutHeader
 slc_result slc_weight_layout_bytes(slc_weight *w, int64_t *out_bytes)
 {
     if (!w || !out_bytes) return fail(SLC_ERR_INVALID_ARGUMENT, "weight or out is null");
+    if (w->high) return fail(SLC_ERR_UNSUPPORTED, "a Q5_K weight (two Q4_K weights on the device) has no single-layout artefact");
     *out_bytes = (int64_t)(sizeof(LayoutHeader) + weight_bytes(w->fmt, w->view.n_pad, w->view.k_pad));
     return SLC_OK;
 }
@@ -399,6 +434,7 @@ slc_result slc_weight_layout_bytes(slc_weight *w, int64_t *out_bytes)
 slc_result slc_weight_export_layout(slc_weight *w, void *out, int64_t bytes)
 {
     if (!w || !out) return fail(SLC_ERR_INVALID_ARGUMENT, "weight or out is null");
+    if (w->high) return fail(SLC_ERR_UNSUPPORTED, "a Q5_K weight (two Q4_K weights on the device) has no single-layout artefact");
     const size_t payload = weight_bytes(w->fmt, w->view.n_pad, w->view.k_pad);
     if (bytes != (int64_t)(sizeof(LayoutHeader) + payload)) return fail(SLC_ERR_BUFFER_TOO_SMALL, "bytes != slc_weight_layout_bytes");
     // (the second format field: what was uploaded, when the records are of another format -- Q5_0, IQ4_NL; else 0)
@@ -421,7 +457,7 @@ slc_result slc_weight_import_layout(slc_device *d, const void *artefact, int64_t
     const int bs = block_size(h.fmt);
     if (bs == 0 || h.n < 0 || h.k <= 0 || h.k % bs != 0 || h.n_pad != (int64_t)round_up((size_t)h.n, 16) ||
         h.k_pad != (int64_t)round_up((size_t)h.k, 256) || h.payload != (int64_t)weight_bytes(h.fmt, (int)h.n_pad, (int)h.k_pad) ||
-        bytes != (int64_t)sizeof(LayoutHeader) + h.payload || (h.src_fmt != 0 && (device_format(h.src_fmt) != h.fmt || h.src_fmt == h.fmt))) {
+        bytes != (int64_t)sizeof(LayoutHeader) + h.payload || (h.src_fmt != 0 && (device_format(h.src_fmt) != h.fmt || h.src_fmt == h.fmt || h.src_fmt == FMT_Q5_K))) {
         return fail(SLC_ERR_INVALID_ARGUMENT, "weight-layout artefact: inconsistent header");
     }
     SLC_CUDA(cudaSetDevice(d->index));
@@ -452,7 +488,7 @@ slc_result slc_weight_shape(slc_weight *w, int32_t *format, int64_t *n, int64_t 
     if (format) *format = w->src_fmt;   // the format that was uploaded
     if (n) *n = w->n;
     if (k) *k = w->k;
-    if (device_bytes) *device_bytes = (int64_t)w->bytes;
+    if (device_bytes) *device_bytes = (int64_t)(w->bytes + (w->high ? w->high->bytes : 0));
     return SLC_OK;
 }
 
@@ -460,6 +496,7 @@ void slc_weight_free(slc_weight *w)
 {
     if (!w) return;
     cudaSetDevice(w->dev->index);
+    if (w->high) { cudaFree(w->high->base); delete w->high; }
     cudaFree(w->base);
     delete w;
 }
@@ -664,6 +701,7 @@ slc_result slc_matmul_create_dual(slc_device *d, slc_weight *gate, slc_weight *u
     if (gate->dev != up->dev || gate->fmt != up->fmt || gate->n != up->n || gate->k != up->k) {
         return fail(SLC_ERR_INVALID_ARGUMENT, "gate and up must share device, format and shape");
     }
+    if (gate->high || up->high) return fail(SLC_ERR_UNSUPPORTED, "a dual MatMul takes no Q5_K weights (two passes each): run gate and up as two MatMuls");
     slc_matmul *op = nullptr;
     slc_result r = slc_matmul_create(d, gate, max_rows, flags, &op);
     if (r != SLC_OK) return r;
@@ -780,7 +818,15 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
         op->last_launches++;
         return SLC_OK;
     }
-    return run_family(op, op->w->view, nullptr, act, av, kernel, y, y_stride, dump, s, ex, ep);
+    slc_result r = run_family(op, op->w->view, nullptr, act, av, kernel, y, y_stride, dump, s, ex, ep);
+    if (r == SLC_OK && op->w->high) {
+        // Q5_K: the fifth bits are a second Q4_K weight whose product is added onto the first (in place: every output is
+        // read and rewritten by the thread that owns it; a launch with an epilogue never runs beside its predecessor)
+        if (dump) return fail(SLC_ERR_UNSUPPORTED, "block-dot export of a Q5_K weight goes through slc_debug_block_dots");
+        const Epilogue add{ nullptr, y, y_stride };
+        r = run_family(op, op->w->high->view, nullptr, act, av, kernel, y, y_stride, nullptr, s, ex, &add);
+    }
+    return r;
 }
 
 // The launches of one weight (two for the dual mat-vec) in the chosen kernel family.
@@ -872,7 +918,7 @@ static slc_result run_summed(slc_matmul *op, slc_activation *act, slc_tp_exchang
     const long long n = op->w->n;
     const int kernel = choose_kernel(op, rows, false);
     const bool chunked = x->comm->chunk_min_rows > 0 && rows >= x->comm->chunk_min_rows;
-    if (kernel == SLC_KERNEL_MMQ && chunked && rows > 128 && !op->w2 && act->planes.q_tiled) {
+    if (kernel == SLC_KERNEL_MMQ && chunked && rows > 128 && !op->w2 && !op->w->high && act->planes.q_tiled) {
         // Prefill: the rows in four chunks of whole 128-token tiles; the all-reduce of chunk i runs on the communicator's
         // own stream while the GEMM of chunk i + 1 runs on the caller's, and the caller's stream joins at the end. (Forks
         // and joins by events, so the whole thing can sit inside a captured graph.)
@@ -1186,6 +1232,11 @@ slc_result slc_matmul_run(slc_matmul *op, const void *x, int32_t x_dtype, int64_
             const int m = (int)(rows - r0 < chunk ? rows - r0 : chunk);
             SLC_CUDA(launch_matvec_f32(op->w->view, x_dev, x_dtype, xs, (int)r0, m, y_dev, ys, s, nullptr));
             op->last_launches++;
+            if (op->w->high) {   // Q5_K: the fifth bits, added onto the rows just written
+                const Epilogue add{ nullptr, y_dev, ys };
+                SLC_CUDA(launch_matvec_f32(op->w->high->view, x_dev, x_dtype, xs, (int)r0, m, y_dev, ys, s, &add));
+                op->last_launches++;
+            }
         }
         op->last_launches_total = op->last_launches;
     } else {
@@ -1279,12 +1330,33 @@ slc_result slc_debug_block_dots(slc_matmul *op, const void *x, int32_t x_dtype, 
         if (r != SLC_OK) { cudaFree(dump); return r; }
     }
     r = slc_activation_quantize(op->act, op->x_stage, x_dtype, rows, k, d->stream);
+    // Q5_K (two Q4_K weights): the dots of the nibbles, then 16 times the dots of the fifth bits
+    slc_weight *const whole = op->w, *const high = whole->high;
+    whole->high = nullptr;
     if (r == SLC_OK) r = run_kernels(op, op->act, op->y_stage, n, dump, d->stream);
     if (r == SLC_OK) {
         e = cudaMemcpyAsync(s32, dump, dump_bytes, cudaMemcpyDeviceToHost, d->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);
         if (e != cudaSuccess) r = cuda_fail(e, "slc_debug_block_dots");
     }
+    if (r == SLC_OK && high) {
+        std::vector<int32_t> bits;
+        try { bits.resize(dump_bytes / 4); } catch (...) { r = fail(SLC_ERR_OUT_OF_MEMORY, "host allocation failed"); }
+        if (r == SLC_OK) {
+            op->w = high;
+            r = run_kernels(op, op->act, op->y_stage, n, dump, d->stream);
+            op->w = whole;
+        }
+        if (r == SLC_OK) {
+            e = cudaMemcpyAsync(bits.data(), dump, dump_bytes, cudaMemcpyDeviceToHost, d->stream);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);
+            if (e != cudaSuccess) r = cuda_fail(e, "slc_debug_block_dots");
+        }
+        if (r == SLC_OK) {
+            for (size_t i = 0; i < bits.size(); i++) s32[i] += 16 * bits[i];
+        }
+    }
+    whole->high = high;
     cudaFree(dump);
     // A weight converted at upload: the kernels exported the dots with the device format's unsigned-code offset (Q8_0: 128);
     // the reference's decoder for the uploaded format uses another (Q5_0: 16). The difference times the block's

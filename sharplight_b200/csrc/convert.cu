@@ -1,8 +1,11 @@
-// Upload-time conversion of the formats that are served through the Q8_0 device layout: one thread rewrites one 32-value
+// Upload-time conversion of the formats that are served through another format's device layout. Q5_0 / IQ4_NL -> Q8_0:
+// one thread rewrites one 32-value
 // block as { f16 d; i8 q[32] }. Exact: Q5_0's value is d * (q5 - 16) and IQ4_NL's is d * codebook[nibble], both a signed
 // byte times the block's own f16 scale (src/Sharplight.Cpu/Quant.cs:409-423, 463-480 of the Sharplight tree); value j < 16
 // of a block comes from the low nibble of qs[j], value j + 16 from the high nibble.
 #include "internal.cuh"
+
+#include <cuda_fp16.h>
 
 namespace slc {
 
@@ -29,6 +32,42 @@ __global__ void convert_to_q8_0_kernel(int src_fmt, const uint8_t *__restrict__ 
             o[18 + j] = (uint8_t)c_iq4nl_values[p[2 + j] >> 4];
         }
     }
+}
+
+// Q5_K -> two Q4_K blocks (layout.cuh). One thread per 256-value block. A block whose 16 * d leaves the f16 range raises
+// *overflow (the upload is then refused: the split would not be exact).
+__global__ void split_q5_k_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ low, uint8_t *__restrict__ high,
+                                  long long blocks, int *overflow)
+{
+    const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= blocks) return;
+    const uint8_t *p = src + b * 176;
+    uint8_t *lo = low + b * 144, *hi = high + b * 144;
+    for (int i = 0; i < 16; i++) lo[i] = p[i];                 // d, dmin, scales
+    for (int i = 0; i < 128; i++) lo[16 + i] = p[48 + i];      // the nibbles
+    const unsigned short dbits = (unsigned short)(p[0] | (p[1] << 8));
+    const float d = __half2float(__ushort_as_half(dbits));
+    const __half d16 = __float2half_rn(16.0f * d);
+    if (!(__half2float(d16) == 16.0f * d)) atomicExch(overflow, 1);   // also catches NaN
+    const unsigned short hbits = __half_as_ushort(d16);
+    hi[0] = (uint8_t)(hbits & 0xff);
+    hi[1] = (uint8_t)(hbits >> 8);
+    hi[2] = 0;
+    hi[3] = 0;                                                  // dmin' = 0: the mins are not counted twice
+    for (int i = 0; i < 12; i++) hi[4 + i] = p[4 + i];
+    const uint8_t *qh = p + 16;
+    for (int j = 0; j < 4; j++) {
+        for (int l = 0; l < 32; l++) hi[16 + 32 * j + l] = (uint8_t)(((qh[l] >> (2 * j)) & 1) | (((qh[l] >> (2 * j + 1)) & 1) << 4));
+    }
+}
+
+cudaError_t launch_split_q5_k(const uint8_t *src, uint8_t *low, uint8_t *high, long long blocks, int *overflow, cudaStream_t stream)
+{
+    if (blocks <= 0) return cudaSuccess;
+    const long long grid = (blocks + 127) / 128;
+    if (grid > 0x7fffffffLL) return cudaErrorInvalidValue;
+    split_q5_k_kernel<<<(unsigned)grid, 128, 0, stream>>>(src, low, high, blocks, overflow);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_convert_to_q8_0(int src_fmt, const uint8_t *src, uint8_t *dst, long long blocks, cudaStream_t stream)

@@ -229,7 +229,7 @@ slc_result slc_weight_upload_gguf(slc_device *d, slc_gguf *g, int64_t index, slc
     if (!d || !g || index < 0 || index >= (int64_t)g->tensors.size()) return g_fail(SLC_ERR_INVALID_ARGUMENT, "null argument or index out of range");
     const GgufTensor &t = g->tensors[(size_t)index];
     const uint64_t bytes = served_bytes(t);
-    if (bytes == 0) return g_fail(SLC_ERR_UNSUPPORTED, "'" + t.name + "' is not a 2-D tensor of Q4_0, Q8_0, Q4_K, Q6_K, Q5_0 or IQ4_NL");
+    if (bytes == 0) return g_fail(SLC_ERR_UNSUPPORTED, "'" + t.name + "' is not a 2-D tensor of Q4_0, Q8_0, Q4_K, Q6_K, Q5_0, Q5_K or IQ4_NL");
     const uint64_t start = g->data_offset + t.offset;
     if (t.offset % g->alignment != 0 || start > g->length || bytes > g->length - start) {
         return g_fail(SLC_ERR_INVALID_ARGUMENT, "'" + t.name + "': data outside the file or misaligned");

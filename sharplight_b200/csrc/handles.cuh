@@ -19,7 +19,9 @@ struct slc_weight
 {
     slc_device *dev = nullptr;
     int fmt = 0;       // the format of the device records (what the kernels see)
-    int src_fmt = 0;   // the format that was uploaded (differs for the formats converted at upload: Q5_0, IQ4_NL -> Q8_0)
+    int src_fmt = 0;   // the format that was uploaded (differs for the formats converted at upload: Q5_0, IQ4_NL -> Q8_0,
+                       // Q5_K -> two Q4_K weights)
+    slc_weight *high = nullptr;   // Q5_K: the second Q4_K weight (the fifth bits, d' = 16 d); a MatMul adds it onto the first
     long long n = 0, k = 0;
     uint8_t *base = nullptr;
     size_t bytes = 0;

@@ -100,6 +100,9 @@ cudaError_t launch_repack(int fmt, int n, int k, int n_pad, int k_pad, uint8_t *
 
 // convert.cu: raw Q5_0 / IQ4_NL blocks -> raw Q8_0 blocks (34 bytes each), exactly.
 cudaError_t launch_convert_to_q8_0(int src_fmt, const uint8_t *src, uint8_t *dst, long long blocks, cudaStream_t stream);
+// raw Q5_K blocks -> two arrays of raw Q4_K blocks (144 bytes each): the block without its fifth bits, and the fifth bits
+// as a Q4_K block with d' = 16 d, dmin' = 0. *overflow (device int, zero before) is set when a 16 d is not an f16.
+cudaError_t launch_split_q5_k(const uint8_t *src, uint8_t *low, uint8_t *high, long long blocks, int *overflow, cudaStream_t stream);
 
 // quantize.cu: x (f32 or bf16, device) -> ActView planes. x_dtype: 0 = f32, 1 = bf16.
 struct ActPlanes

@@ -70,16 +70,27 @@ __host__ __device__ inline int block_bytes(int fmt)
 // codebook entry being the signed byte). The reference's integer-dot path treats them the same way: unsigned code, the
 // block's f16 d, an offset of -16 d or -128 d (src/Sharplight.Cpu/IntDot.Decode.cs:101-123, 225-238). They cost 34 bytes
 // per 32 values on the device instead of 22 / 18.
-enum : int { FMT_Q5_0 = 6, FMT_IQ4_NL = 20 };
+//
+// Q5_K { f16 d; f16 dmin; u8 scales[12]; u8 qh[32]; u8 qs[128] } is Q4_K with a fifth bit per value: d * sc * (q4 + 16 h)
+// - dmin * m = [d * sc * q4 - dmin * m] + [(16 d) * sc * h]. It is split at upload, exactly, into two Q4_K weights -- the
+// block without qh, and a block with d' = 16 d (a power of two: exact in f16), dmin' = 0, the same scales and the high
+// bits as nibbles -- and a MatMul runs both, the second adding onto the first. 288 instead of 176 bytes per 256 values.
+enum : int { FMT_Q5_0 = 6, FMT_Q5_K = 13, FMT_IQ4_NL = 20 };
 
 // The format the kernels see for an uploaded format (0: not served).
 __host__ __device__ inline int device_format(int fmt)
 {
-    return (fmt == FMT_Q5_0 || fmt == FMT_IQ4_NL) ? FMT_Q8_0 : block_size(fmt) ? fmt : 0;
+    return (fmt == FMT_Q5_0 || fmt == FMT_IQ4_NL) ? FMT_Q8_0 : fmt == FMT_Q5_K ? FMT_Q4_K : block_size(fmt) ? fmt : 0;
 }
 // Values and bytes per block of the format as the host hands it over.
-__host__ __device__ inline int source_block_size(int fmt) { return (fmt == FMT_Q5_0 || fmt == FMT_IQ4_NL) ? 32 : block_size(fmt); }
-__host__ __device__ inline int source_block_bytes(int fmt) { return fmt == FMT_Q5_0 ? 22 : fmt == FMT_IQ4_NL ? 18 : block_bytes(fmt); }
+__host__ __device__ inline int source_block_size(int fmt)
+{
+    return (fmt == FMT_Q5_0 || fmt == FMT_IQ4_NL) ? 32 : fmt == FMT_Q5_K ? 256 : block_size(fmt);
+}
+__host__ __device__ inline int source_block_bytes(int fmt)
+{
+    return fmt == FMT_Q5_0 ? 22 : fmt == FMT_IQ4_NL ? 18 : fmt == FMT_Q5_K ? 176 : block_bytes(fmt);
+}
 // What the reference's unsigned code adds to the signed code the kernels multiply (block-dot export): Q8_0 and IQ4_NL
 // 128, Q4_0 8, Q6_K 32, Q4_K 0, Q5_0 16.
 __host__ __device__ inline int unsigned_code_offset(int fmt)

@@ -116,6 +116,16 @@ slc_result slc_matmul_run_static(slc_weight *weight, const void *x_device, int32
         e = launch_matvec(wv, av, r0, m, y_device, y_stride, nullptr, dev->status_dev, r0 > 0 ? 1 : 0, s);
         if (e != cudaSuccess) return na_fail(SLC_ERR_CUDA, std::string("mat-vec: ") + cudaGetErrorString(e));
     }
+    if (weight->high) {
+        // Q5_K: the fifth bits are a second Q4_K weight, added onto the rows just written (a launch with an epilogue waits
+        // for its predecessor)
+        const Epilogue add{ nullptr, y_device, y_stride };
+        for (int r0 = 0; r0 < (int)rows; r0 += chunk) {
+            const int m = (int)rows - r0 < chunk ? (int)rows - r0 : chunk;
+            e = launch_matvec(weight->high->view, av, r0, m, y_device, y_stride, nullptr, dev->status_dev, 0, s, nullptr, &add);
+            if (e != cudaSuccess) return na_fail(SLC_ERR_CUDA, std::string("mat-vec: ") + cudaGetErrorString(e));
+        }
+    }
     return SLC_OK;
 }
 

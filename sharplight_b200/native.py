@@ -20,12 +20,14 @@ ERR_CUDA, ERR_INVALID_STATE, ERR_TIMEOUT, ERR_BUFFER_TOO_SMALL = -5, -6, -7, -8
 
 FMT_Q4_0, FMT_Q8_0, FMT_Q4_K, FMT_Q6_K = 2, 8, 12, 14
 FMT_Q5_0, FMT_IQ4_NL = 6, 20   # rewritten at upload as Q8_0 device records (exactly)
+FMT_Q5_K = 13                  # split at upload into two Q4_K weights (exactly)
 F32, BF16 = 0, 1
 MATMUL_DEFAULT, MATMUL_ROW_INVARIANT, MATMUL_F32_ACTIVATIONS = 0, 1, 2
 KERNEL_AUTO, KERNEL_MMVQ, KERNEL_SKINNY, KERNEL_MMQ, KERNEL_TILE, KERNEL_F32 = 0, 1, 2, 3, 4, 5
 TP_MAX_RANKS, TP_MAX_ROWS, TP_HANDLE_BYTES, TP_COMM_ID_BYTES = 8, 64, 64, 128
 
-BLOCK = {FMT_Q4_0: (32, 18), FMT_Q8_0: (32, 34), FMT_Q4_K: (256, 144), FMT_Q6_K: (256, 210), FMT_Q5_0: (32, 22), FMT_IQ4_NL: (32, 18)}
+BLOCK = {FMT_Q4_0: (32, 18), FMT_Q8_0: (32, 34), FMT_Q4_K: (256, 144), FMT_Q6_K: (256, 210), FMT_Q5_0: (32, 22), FMT_IQ4_NL: (32, 18),
+         FMT_Q5_K: (256, 176)}
 
 
 class DeviceInfoStruct(C.Structure):

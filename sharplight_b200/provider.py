@@ -61,7 +61,7 @@ def _check(code: int) -> None:
 
 
 DATA_TYPES = {"Q4_0": N.FMT_Q4_0, "Q8_0": N.FMT_Q8_0, "Q4_K": N.FMT_Q4_K, "Q6_K": N.FMT_Q6_K, "Q5_0": N.FMT_Q5_0,
-              "IQ4_NL": N.FMT_IQ4_NL}
+              "IQ4_NL": N.FMT_IQ4_NL, "Q5_K": N.FMT_Q5_K}
 
 # DeviceFeatures names the device reports (src/Sharplight.Core/Runtime/DeviceFeatures.cs:28,54)
 FEATURES = frozenset({"int_dot", "matrix_int8", "subgroup_ops", "fp16", "bf16"})
@@ -306,7 +306,7 @@ class CudaDevice:
         return v.value
 
     def supports(self, node) -> OpSupport:
-        """Yes only for MatMul with a static Q8_0 / Q4_0 / Q4_K / Q6_K / Q5_0 / IQ4_NL weight whose K is a multiple of the block size
+        """Yes only for MatMul with a static Q8_0 / Q4_0 / Q4_K / Q6_K / Q5_0 / Q5_K / IQ4_NL weight whose K is a multiple of the block size
         and activations that may be quantized to 8 bits (mirrors CpuOpSupport.CheckQuantizedMatMul,
         src/Sharplight.Cpu/CpuOpSupport.Linear.cs:21-53); everything else goes to the placement fallback."""
         if not isinstance(node, MatMulNode):

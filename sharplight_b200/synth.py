@@ -7,7 +7,8 @@ from __future__ import annotations
 
 import numpy as np
 
-BLOCK = {"Q4_0": (32, 18), "Q8_0": (32, 34), "Q4_K": (256, 144), "Q6_K": (256, 210), "Q5_0": (32, 22), "IQ4_NL": (32, 18)}
+BLOCK = {"Q4_0": (32, 18), "Q8_0": (32, 34), "Q4_K": (256, 144), "Q6_K": (256, 210), "Q5_0": (32, 22), "IQ4_NL": (32, 18),
+         "Q5_K": (256, 176)}
 
 
 def _rng(seed: int) -> np.random.Generator:
@@ -24,6 +25,7 @@ def weight_blocks(type_name: str, n: int, k: int, seed: int, scale_sigma: float 
     Q8_0: codes uniform in [-127, 127], d = |N(0, 0.02)| / 127.   Q4_0: nibbles uniform, d = |N(0, 0.02)| / 8.
     Q4_K: 6-bit scales / mins uniform (12 uniform bytes), d, dmin = |N(0, 0.01)|, nibbles uniform.
     Q6_K: ql / qh uniform bits, int8 sub-block scales uniform, d = |N(0, 0.01)|.
+    Q5_K: like Q4_K plus 32 uniform bytes of fifth bits.
     Q5_0: nibbles and the 32 high bits uniform, d = |N(0, 0.02)| / 16.   IQ4_NL: nibbles uniform, d = |N(0, 0.02)| / 127.
     """
     bs, bb = BLOCK[type_name]
@@ -52,6 +54,11 @@ def weight_blocks(type_name: str, n: int, k: int, seed: int, scale_sigma: float 
         out[:, 0:2] = _f16_bytes(np.abs(g.normal(0.0, sigma, nb)))
         out[:, 2:4] = _f16_bytes(np.abs(g.normal(0.0, sigma, nb)))
         out[:, 4:144] = g.integers(0, 256, (nb, 140), dtype=np.uint8)
+    elif type_name == "Q5_K":
+        sigma = 0.01 if scale_sigma is None else scale_sigma
+        out[:, 0:2] = _f16_bytes(np.abs(g.normal(0.0, sigma, nb)))
+        out[:, 2:4] = _f16_bytes(np.abs(g.normal(0.0, sigma, nb)))
+        out[:, 4:176] = g.integers(0, 256, (nb, 172), dtype=np.uint8)
     elif type_name == "Q6_K":
         sigma = 0.01 if scale_sigma is None else scale_sigma
         out[:, 0:208] = g.integers(0, 256, (nb, 208), dtype=np.uint8)

@@ -19,7 +19,8 @@ from typing import Tuple
 
 import numpy as np
 
-BLOCK = {"Q4_0": (32, 18), "Q8_0": (32, 34), "Q4_K": (256, 144), "Q6_K": (256, 210), "Q5_0": (32, 22), "IQ4_NL": (32, 18)}
+BLOCK = {"Q4_0": (32, 18), "Q8_0": (32, 34), "Q4_K": (256, 144), "Q6_K": (256, 210), "Q5_0": (32, 22), "IQ4_NL": (32, 18),
+         "Q5_K": (256, 176)}
 
 
 def shard_range(total: int, rank: int, tp: int, align: int = 1) -> Tuple[int, int]:

@@ -4,7 +4,7 @@ Run where the reference tree is available: its root is the first argument (or th
 variable). It reads
   tests/Sharplight.Cpu.Tests/Fixtures/ggml_quant_ext.bin  (record layout: GgmlDequantTests.cs:26-48)
   tests/Sharplight.Cpu.Tests/Fixtures/ggml_quant.bin      (record layout: QuantTests.cs:16-43)
-and writes, beside this script, ``ggml_golden.npz`` with the records of ggml types 2 (Q4_0), 6 (Q5_0), 8 (Q8_0), 12 (Q4_K), 20 (IQ4_NL) and
+and writes, beside this script, ``ggml_golden.npz`` with the records of ggml types 2 (Q4_0), 6 (Q5_0), 8 (Q8_0), 12 (Q4_K), 13 (Q5_K), 20 (IQ4_NL) and
 14 (Q6_K): raw blocks, the floats ggml's own decoder produced, and (second file) the f32 source the blocks were
 quantized from. Nothing is recomputed here: the arrays are byte-for-byte slices of the fixture files.
 """
@@ -20,7 +20,7 @@ TYPES = {2: (32, 18), 3: (32, 20), 6: (32, 22), 7: (32, 24), 8: (32, 34), 10: (2
          12: (256, 144), 13: (256, 176), 14: (256, 210), 16: (256, 66), 17: (256, 74), 18: (256, 98),
          19: (256, 50), 20: (32, 18), 21: (256, 110), 22: (256, 82), 23: (256, 136), 29: (256, 56),
          34: (256, 54), 35: (256, 66), 39: (32, 17), 40: (64, 36)}
-KEEP = (2, 6, 8, 12, 14, 20)
+KEEP = (2, 6, 8, 12, 13, 14, 20)
 
 
 def read_ext(path):

@@ -5,7 +5,7 @@ import numpy as np
 
 from oracle import np_oracle, sl_oracle  # noqa: F401  (re-exported for the tests)
 
-TYPE_OF = {2: "Q4_0", 6: "Q5_0", 8: "Q8_0", 12: "Q4_K", 14: "Q6_K", 20: "IQ4_NL"}
+TYPE_OF = {2: "Q4_0", 6: "Q5_0", 8: "Q8_0", 12: "Q4_K", 13: "Q5_K", 14: "Q6_K", 20: "IQ4_NL"}
 FMT_OF = {v: k for k, v in TYPE_OF.items()}
 
 # fp32 outputs: max relative error 1e-3 against the oracle's integer-dot result on the same quantized inputs.

@@ -102,7 +102,7 @@ def test_supports_mirrors_the_quantized_matmul_check():
     blocks = np.zeros(34, np.uint8)
     ok = P.MatMulNode("m", "x", P.WeightInfo("Q8_0", (1, 32), blocks), "y")
     assert d.supports(ok).supported
-    assert not d.supports(P.MatMulNode("m", "x", P.WeightInfo("Q5_K", (1, 256), blocks), "y")).supported
+    assert not d.supports(P.MatMulNode("m", "x", P.WeightInfo("Q4_1", (1, 256), blocks), "y")).supported
     bad_k = d.supports(P.MatMulNode("m", "x", P.WeightInfo("Q4_K", (1, 288), blocks), "y"))
     assert not bad_k.supported and "multiple" in bad_k.reason
     assert not d.supports(P.MatMulNode("m", "x", P.WeightInfo("Q8_0", (1, 32), blocks), "y", x_dtype="f16")).supported

@@ -94,3 +94,38 @@ def test_dual_gate_up(cuda_device, type_name, n, k):
         assert cuda_device.last_status() == 0
     finally:
         op.dispose(); gate.dispose(); up.dispose()
+
+
+@pytest.mark.parametrize("rows", [1, 8, 130])
+def test_q5_k_epilogue_counts_bias_and_residual_once(cuda_device, rows):
+    """A Q5_K weight is two Q4_K weights on the device, the second product added onto the first: bias and residual belong
+    to the first pass only. (The order of the f32 additions differs from plain + bias + residual, hence a tolerance.)"""
+    lib = N.load()
+    n, k = 136, 512
+    rng = np.random.Generator(np.random.Philox(78))
+    w = cuda_device.upload_weight("Q5_K", (n, k), synth.weight_blocks("Q5_K", n, k, seed=5))
+    op = MatMulOp(cuda_device, w, rows)
+    act = SharedActivation(cuda_device, rows, k)
+    ex = TpExchange(cuda_device, 0, 1, 64, n)
+    x = synth.activations(rows, k, seed=6)
+    bias = rng.standard_normal(n).astype(np.float32)
+    res = rng.standard_normal((rows, n + 5)).astype(np.float32)
+    xd, bd, rd = _dev(lib, cuda_device, x), _dev(lib, cuda_device, bias), _dev(lib, cuda_device, res)
+    ys = [_dev(lib, cuda_device, np.full((rows, n), np.nan, np.float32)) for _ in range(3)]
+    try:
+        act.quantize(xd.value, N.F32, rows, k)
+        act.matmul(op, ys[0].value, n)
+        act.matmul_epilogue(op, ys[1].value, n, bias_ptr=bd.value, residual_ptr=rd.value, residual_stride=n + 5)
+        plain = _read(lib, cuda_device, ys[0], (rows, n))
+        want = plain + bias[None, :] + res[:, :n]
+        got = _read(lib, cuda_device, ys[1], (rows, n))
+        assert np.all(np.abs(got - want) <= 1e-5 * np.maximum(1.0, np.abs(want)))
+        if rows <= 64:
+            act.matmul_epilogue(op, ys[2].value, n, bias_ptr=bd.value, residual_ptr=rd.value, residual_stride=n + 5, exchange=ex)
+            got = _read(lib, cuda_device, ys[2], (rows, n))
+            assert np.all(np.abs(got - want) <= 1e-5 * np.maximum(1.0, np.abs(want)))
+        assert cuda_device.last_status() == 0
+    finally:
+        for p in [xd, bd, rd] + ys:
+            lib.slc_buffer_free(cuda_device.handle, p)
+        ex.dispose(); act.dispose(); op.dispose(); w.dispose()

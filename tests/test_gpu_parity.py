@@ -111,7 +111,7 @@ def test_upload_rejects_bad_shapes(cuda_device):
     with pytest.raises(ArgumentError):
         cuda_device.upload_weight("Q8_0", (4, 64), np.zeros(10, np.uint8))            # byte count
     with pytest.raises(NotSupportedError):
-        cuda_device.upload_weight("Q5_K", (4, 256), np.zeros(4 * 176, np.uint8))
+        cuda_device.upload_weight("Q5_1", (4, 256), np.zeros(4 * 8 * 24, np.uint8))   # a format without kernels
 
 
 # ---- the operator ---------------------------------------------------------------------------------------------------
@@ -272,7 +272,7 @@ def test_segment_contract(cuda_device):
     with pytest.raises(ObjectDisposedError):
         compiled.execute({"T": 1})
     with pytest.raises(NotSupportedError):
-        cuda_device.compile(GraphSegment([MatMulNode("m", "x", WeightInfo("Q5_K", (4, 256), np.zeros(704, np.uint8)),
+        cuda_device.compile(GraphSegment([MatMulNode("m", "x", WeightInfo("Q5_1", (4, 256), np.zeros(768, np.uint8)),
                                                      "y")], ["x"], ["y"]), CompileOptions())
 
 
@@ -831,3 +831,66 @@ def test_converted_formats_kslice_and_layout_artefact(cuda_device, type_name):
             op.dispose()
         for w in (ws, wr, wa):
             w.dispose()
+
+
+# ---- Q5_K: split at upload into two Q4_K weights (nibbles; fifth bits with d' = 16 d), the second product added ----------
+
+@pytest.mark.parametrize("n,k,rows", [(48, 256, 1), (100, 1536, 3), (7, 512, 4), (300, 1024, 16), (520, 512, 64), (100, 512, 200),
+                                      (1000, 768, 129), (4112, 512, 2), (64, 14336, 32)])
+def test_q5_k_every_kernel_family(cuda_device, n, k, rows):
+    """Q5_K (src/Sharplight.Cpu/IntDot.Decode.cs:150-176) through the mat-vec, the skinny kernel (K chunks included) and
+    the GEMM: y against the oracle's integer-dot MatMul of the Q5_K blocks, the int32 block dots of the 5-bit codes bit for
+    bit (dots of the nibbles + 16 x dots of the fifth bits)."""
+    _, kern = check_matmul(cuda_device, "Q5_K", n, k, rows, seed=n + k + rows)
+    assert kern[0] == (N.KERNEL_MMVQ if rows <= 2 else N.KERNEL_MMQ if rows > 64 else kern[0])
+    assert cuda_device.last_status() == 0
+
+
+def test_q5_k_other_entry_points(cuda_device):
+    """The f32-activation mat-vec, an epilogue (bias and residual stay counted once), a K-slice shard, the no-allocation
+    entry point and the refusals (download, layout artefact, dual MatMul) on a Q5_K weight."""
+    n, k, rows = 96, 1024, 3
+    fmt = FMT_OF["Q5_K"]
+    blocks = synth.weight_blocks("Q5_K", n, k, seed=31)
+    x = synth.activations(rows, k, seed=32)
+    w = cuda_device.upload_weight("Q5_K", (n, k), blocks)
+    opf = MatMulOp(cuda_device, w, rows, f32_activations=True)
+    op = MatMulOp(cuda_device, w, rows)
+    try:
+        exact = sl_oracle.matmul_f64(fmt, blocks, n, k, x, threads=4)
+        yf = opf.run(x)
+        assert np.all(np.abs(yf - exact) <= 2e-3 + 1e-4 * np.abs(exact)), float(np.max(np.abs(yf - exact)))
+        ref, _, _ = sl_oracle.matmul_intdot(fmt, blocks, n, k, x, threads=4)
+        y = op.run(x)
+        assert max_rel_error(y, ref) <= MAX_REL
+        # the no-allocation entry point gives the same rows
+        import torch
+        xd = torch.from_numpy(x).cuda()
+        yd = torch.zeros((rows, n), device="cuda", dtype=torch.float32)
+        assert N.load().slc_matmul_run_static(w.handle, C.c_void_p(xd.data_ptr()), N.F32, rows, k, C.c_void_p(yd.data_ptr()), n,
+                                              None) == N.OK
+        torch.cuda.synchronize()
+        assert max_rel_error(yd.cpu().numpy(), ref) <= MAX_REL
+        # K-slice shard == upload of the sliced blocks
+        k0, k1 = 256, 768
+        sliced = np.ascontiguousarray(blocks.reshape(n, k // 256, 176)[:, k0 // 256:k1 // 256]).reshape(-1)
+        wh = C.c_void_p()
+        assert N.load().slc_weight_upload_kslice(cuda_device.handle, fmt, n, k, blocks.ctypes.data_as(C.c_void_p), blocks.size,
+                                                 k0, k1, C.byref(wh)) == N.OK
+        from sharplight_b200.provider import DeviceWeight
+        ws = DeviceWeight(cuda_device, fmt, n, k1 - k0, wh.value)
+        wr = cuda_device.upload_weight("Q5_K", (n, k1 - k0), sliced)
+        a, b = MatMulOp(cuda_device, ws, rows), MatMulOp(cuda_device, wr, rows)
+        try:
+            xs = np.ascontiguousarray(x[:, k0:k1])
+            assert np.array_equal(a.run(xs).view(np.uint32), b.run(xs).view(np.uint32))
+        finally:
+            a.dispose(); b.dispose(); ws.dispose(); wr.dispose()
+        with pytest.raises(Exception):
+            w.download()
+        with pytest.raises(Exception):
+            w.export_layout()
+    finally:
+        op.dispose()
+        opf.dispose()
+        w.dispose()

@@ -9,8 +9,8 @@ import pytest
 from helpers import FMT_OF, TYPE_OF, np_oracle, relative_rms, same_floats, sl_oracle
 from sharplight_b200 import synth
 
-RECORDS = ([f"ext_{t}_{kind}" for t in (2, 6, 8, 12, 14, 20) for kind in ("ggml", "random")] +
-           [f"src_{t}" for t in (2, 6, 8, 12, 14)])
+RECORDS = ([f"ext_{t}_{kind}" for t in (2, 6, 8, 12, 13, 14, 20) for kind in ("ggml", "random")] +
+           [f"src_{t}" for t in (2, 6, 8, 12, 13, 14)])
 
 
 def _record(golden, name):
