@@ -790,7 +790,7 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
     if (act->pending) {
         // deferred rows: the mat-vec quantizes them itself when K is short; otherwise the quantizer runs now, on this
         // stream, and the planes are there for this and every later MatMul
-        const bool fuse = kernel == SLC_KERNEL_MMVQ && !dump && !op->w2 && act->k_pad <= FUSED_QUANTIZE_MAX_K;
+        const bool fuse = kernel == SLC_KERNEL_MMVQ && !dump && !op->w2 && !op->w->high && act->k_pad <= FUSED_QUANTIZE_MAX_K;   // (Q5_K: two passes read the rows)
         if (!fuse) {
             SLC_CUDA(launch_quantize(act->pending_x, act->pending_dtype, act->rows, act->rows_pad, (int)act->k, act->k_pad,
                                      act->pending_stride, act->planes, s));

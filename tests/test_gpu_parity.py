@@ -727,7 +727,7 @@ def test_weight_layout_artefact_round_trip(cuda_device, type_name, n, k):
 
 # ---- deferred quantization: the mat-vec quantizes short rows itself ------------------------------------------------------
 
-@pytest.mark.parametrize("type_name", TYPES)
+@pytest.mark.parametrize("type_name", TYPES + ["Q5_K", "Q5_0"])
 @pytest.mark.parametrize("n,k,rows", [(64, 1024, 1), (200, 3584, 2), (48, 512, 4), (100, 4096, 1), (40, 8192, 1), (64, 1024, 8),
                                       (33, 1568, 3)])
 def test_deferred_quantization_bit_identical(cuda_device, type_name, n, k, rows):
@@ -750,7 +750,7 @@ def test_deferred_quantization_bit_identical(cuda_device, type_name, n, k, rows)
             a0.matmul(op, y0.data_ptr(), n)
             a1.set_rows(src.data_ptr(), N.F32, rows, stride)
             a1.matmul(op, y1.data_ptr(), n)
-            fused = op.last_kernel()[0] == N.KERNEL_MMVQ and k <= 2048
+            fused = op.last_kernel()[0] == N.KERNEL_MMVQ and k <= 2048 and type_name != "Q5_K"   # (two passes: quantized once)
             assert op.last_kernel()[1] == ((rows + 3) // 4 if fused else op.last_kernel()[1])
             a1.matmul(op, y2.data_ptr(), n)
             torch.cuda.synchronize()
