@@ -112,6 +112,12 @@ def test_upload_rejects_bad_shapes(cuda_device):
         cuda_device.upload_weight("Q8_0", (4, 64), np.zeros(10, np.uint8))            # byte count
     with pytest.raises(NotSupportedError):
         cuda_device.upload_weight("Q5_1", (4, 256), np.zeros(4 * 8 * 24, np.uint8))   # a format without kernels
+    # Q5_K is split into two Q4_K weights, one of them with 16 d as its f16 scale: a d whose sixteenfold is no f16 is refused
+    huge = synth.weight_blocks("Q5_K", 4, 256, seed=1).reshape(4, 176)
+    huge[2, 0:2] = np.array([0xFF, 0x7B], np.uint8)                                   # d = 65504
+    with pytest.raises(NotSupportedError):
+        cuda_device.upload_weight("Q5_K", (4, 256), huge.reshape(-1))
+    assert cuda_device.last_status() == 0
 
 
 # ---- the operator ---------------------------------------------------------------------------------------------------
