@@ -626,6 +626,27 @@ def extras_leg(args, torch, device, N, synth, stream, peaks):
             op.dispose()
     for wt in ws:
         wt.dispose()
+    # the other served formats on the same shape at one row (MatMul launches only, one shared quantization): Q6_K natively;
+    # Q5_0 / IQ4_NL as Q8_0 device records, Q5_K as two Q4_K weights (converted at upload)
+    x = torch.randn((1, k), device="cuda")
+    y = torch.empty((copies, 1, n), device="cuda")
+    act = SharedActivation(device, 1, k)
+    act.quantize(x.data_ptr(), N.F32, 1, k, stream.cuda_stream)
+    more = {}
+    for type_name in ("Q6_K", "Q5_K", "Q5_0", "IQ4_NL"):
+        base = synth.weight_blocks(type_name, n, k, seed=78)
+        ws = [device.upload_weight(type_name, (n, k), np.roll(base.reshape(n, -1), i * 37, axis=0).reshape(-1)) for i in range(copies)]
+        ops = [MatMulOp(device, wt, 1) for wt in ws]
+        ms = time_graphed(torch, None, 1, stream, lambda sp: [act.matmul(op, y[i].data_ptr(), n, sp) for i, op in enumerate(ops)], steps, 3)
+        us = ms * 1e3 / copies
+        src = synth.weight_bytes(type_name, n, k)
+        more[type_name] = {"us": us, "file_format_gbs": src / us / 1e3, "device_bytes": ws[0].device_bytes, "launches": ops[0].last_kernel()[1]}
+        for op in ops:
+            op.dispose()
+        for wt in ws:
+            wt.dispose()
+    act.dispose()
+    out["more_formats_14336x4096_M1"] = more
     return out
 
 
