@@ -352,6 +352,7 @@ slc_result slc_weight_upload(slc_device *d, int32_t fmt, int64_t n, int64_t k, c
     }
     if (e == cudaSuccess) e = weight_from_device_blocks(d, dev_fmt, fmt, n, k, conv ? conv : raw, &w);
     if (e == cudaSuccess && fmt == FMT_Q5_K) e = weight_from_device_blocks(d, dev_fmt, fmt, n, k, conv2, &high);
+    if (high) high->view.pair_sum = 1;   // in a two-weight mat-vec launch its product is added to the first weight's
     if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);
     if (raw) cudaFree(raw);
     if (conv) cudaFree(conv);
@@ -817,6 +818,10 @@ static slc_result run_kernels(slc_matmul *op, slc_activation *act, float *y, lon
         SLC_CUDA(launch_gate_mul(op->dual_tmp, n, y, y_stride, rows, (int)n, s));
         op->last_launches++;
         return SLC_OK;
+    }
+    if (op->w->high && kernel == SLC_KERNEL_MMVQ && !dump && !ex && matvec_fits(1, op->w->view.k_pad, true)) {
+        // Q5_K on the mat-vec: both Q4_K halves stream through one launch (the two-weight form of the kernel, products added)
+        return run_family(op, op->w->view, &op->w->high->view, act, av, kernel, y, y_stride, nullptr, s, nullptr, ep);
     }
     slc_result r = run_family(op, op->w->view, nullptr, act, av, kernel, y, y_stride, dump, s, ex, ep);
     if (r == SLC_OK && op->w->high) {

@@ -119,6 +119,8 @@ struct WeightView
     int n, k;          // logical shape
     int n_pad, k_pad;  // multiples of 16 / 256
     const uint8_t *data;  // records: [n_pad/16][k_pad/256][record_bytes(fmt)]
+    int pair_sum = 0;     // as the second weight of a two-weight mat-vec launch: 1 = the two products are added (the two
+                          // halves of a Q5_K weight), 0 = silu(first) * second (gate / up)
 
     __host__ __device__ const uint8_t *record(int rg, int st) const
     {

@@ -574,7 +574,8 @@ matvec_kernel(const WeightView w, const WeightView w2, const ActView a, int row0
                 if (DUAL) {
                     float u = 0.0f;
                     for (int wi = 0; wi < warps; wi++) u += red[DUAL ? 1 : 0][wi][rr][m];
-                    v = __fdiv_rn(v, 1.0f + expf(-v)) * u;   // silu(gate) * up
+                    v = w2.pair_sum ? __fadd_rn(v, u)                        // the two halves of one weight (Q5_K)
+                                    : __fdiv_rn(v, 1.0f + expf(-v)) * u;    // silu(gate) * up
                 }
             }
             vals[j] = v;

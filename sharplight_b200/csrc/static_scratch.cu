@@ -109,22 +109,15 @@ slc_result slc_matmul_run_static(slc_weight *weight, const void *x_device, int32
     av.q = planes.q; av.ds = planes.ds; av.dx = planes.dx; av.sx = planes.sx; av.gs = planes.gs; av.isum = planes.isum;
     // the largest chunk of rows whose activations fit the kernel's shared memory at this K (every row of a chunk is
     // computed exactly as a single row is, so the chunking does not change the result)
+    // (a Q5_K weight is two Q4_K weights: both stream through one launch of the kernel's two-weight form, products added)
+    const WeightView *second = weight->high ? &weight->high->view : nullptr;
+    if (second && !matvec_fits(1, k_pad, true)) return na_fail(SLC_ERR_UNSUPPORTED, "slc_matmul_run_static: K of this Q5_K weight exceeds the two-weight mat-vec's shared memory");
     int chunk = (int)rows;
-    while (chunk > 1 && !matvec_fits(chunk, k_pad)) chunk--;
+    while (chunk > 1 && !matvec_fits(chunk, k_pad, second != nullptr)) chunk--;
     for (int r0 = 0; r0 < (int)rows; r0 += chunk) {
         const int m = (int)rows - r0 < chunk ? (int)rows - r0 : chunk;
-        e = launch_matvec(wv, av, r0, m, y_device, y_stride, nullptr, dev->status_dev, r0 > 0 ? 1 : 0, s);
+        e = launch_matvec(wv, av, r0, m, y_device, y_stride, nullptr, dev->status_dev, r0 > 0 ? 1 : 0, s, nullptr, nullptr, second);
         if (e != cudaSuccess) return na_fail(SLC_ERR_CUDA, std::string("mat-vec: ") + cudaGetErrorString(e));
-    }
-    if (weight->high) {
-        // Q5_K: the fifth bits are a second Q4_K weight, added onto the rows just written (a launch with an epilogue waits
-        // for its predecessor)
-        const Epilogue add{ nullptr, y_device, y_stride };
-        for (int r0 = 0; r0 < (int)rows; r0 += chunk) {
-            const int m = (int)rows - r0 < chunk ? (int)rows - r0 : chunk;
-            e = launch_matvec(weight->high->view, av, r0, m, y_device, y_stride, nullptr, dev->status_dev, 0, s, nullptr, &add);
-            if (e != cudaSuccess) return na_fail(SLC_ERR_CUDA, std::string("mat-vec: ") + cudaGetErrorString(e));
-        }
     }
     return SLC_OK;
 }
