@@ -60,8 +60,8 @@ enum
    integer-dot decoder treats them too, src/Sharplight.Cpu/IntDot.Decode.cs:101-123,225-238): they cost 34 bytes per 32
    values on the device and run through the Q8_0 kernels. Q5_K is split at upload, exactly, into two Q4_K weights -- the
    block without its fifth bits, and the fifth bits as nibbles with d' = 16 d, dmin' = 0 -- and every MatMul runs both
-   (one two-weight launch on the mat-vec; elsewhere the second launch adds onto the first): 288 bytes per 256 values. An upload whose 16 d is not an f16
-   returns SLC_ERR_UNSUPPORTED. Converted weights have no slc_weight_download; Q5_K has no layout artefact and takes no
+   (one two-weight launch on the mat-vec; elsewhere the second launch adds onto the first): 288 bytes per 256 values.
+   An upload whose 16 d is not an f16 returns SLC_ERR_UNSUPPORTED. Converted weights have no slc_weight_download; Q5_K has no layout artefact and takes no
    part in a dual MatMul. */
 typedef enum slc_format
 {
