@@ -842,7 +842,8 @@ def test_converted_formats_kslice_and_layout_artefact(cuda_device, type_name):
 # ---- Q5_K: split at upload into two Q4_K weights (nibbles; fifth bits with d' = 16 d), the second product added ----------
 
 @pytest.mark.parametrize("n,k,rows", [(48, 256, 1), (100, 1536, 3), (7, 512, 4), (300, 1024, 16), (520, 512, 64), (100, 512, 200),
-                                      (1000, 768, 129), (4112, 512, 2), (64, 14336, 32)])
+                                      (1000, 768, 129), (4112, 512, 2), (64, 14336, 32), (40, 28672, 2), (24, 65536, 1),
+                                      (24, 98304, 2)])
 def test_q5_k_every_kernel_family(cuda_device, n, k, rows):
     """Q5_K (src/Sharplight.Cpu/IntDot.Decode.cs:150-176) through the mat-vec, the skinny kernel (K chunks included) and
     the GEMM: y against the oracle's integer-dot MatMul of the Q5_K blocks, the int32 block dots of the 5-bit codes bit for
