@@ -126,7 +126,7 @@ def _two_gpu_worker(rank, world, port, out):
         stream = torch.cuda.Stream()
         torch.cuda.set_stream(stream)
         sp = stream.cuda_stream
-        for type_name, n, k in (("Q4_K", 520, 4096), ("Q8_0", 136, 1024)):
+        for type_name, n, k in (("Q4_K", 520, 4096), ("Q8_0", 136, 1024), ("Q5_K", 136, 2048), ("Q5_0", 72, 1024)):
             fmt = FMT_OF[type_name]
             blocks = synth.weight_blocks(type_name, n, k, seed=61)
             sb, sn, sk, k0 = tp.row_shard(blocks, type_name, n, k, rank, world)
