@@ -293,6 +293,17 @@ SLC_API slc_result slc_activation_quantize_silu_mul(slc_activation *act, const f
 SLC_API slc_result slc_argmax_rows(slc_device *device, const float *y_device, int64_t rows, int64_t n, int64_t y_stride,
                                    int32_t *out_index_device, void *stream);
 
+/* ---- MatMulId, the expert-indexed MatMul of mixture-of-experts layers (src/Sharplight.Core/Graph/StandardOps.Moe.cs:8-40):
+        y[t, s] = W[ids[t, s]] . x[t]   (per_slot == 0, x: [tokens, K])   or   W[ids[t, s]] . x[t, s]   (per_slot != 0,
+        x: [tokens * slots, K]). weight: the experts' [N, K] matrices uploaded as one [experts * N, K] weight, N a multiple
+        of 16; ids: device int32 [tokens * slots]; y: device f32, tokens * slots rows of N values, y_stride apart. The
+        arithmetic is the reference CPU operator's (src/Sharplight.Cpu/MatMulIdOp.cs): f32 activations against the
+        dequantized weight, every item computed as a single row is. An id outside [0, experts) leaves its row untouched
+        and raises the device status word (slc_last_status: -1), where the reference throws. Asynchronous on the stream. */
+SLC_API slc_result slc_matmul_id_run(slc_weight *weight, int32_t experts, const void *x_device, int32_t x_dtype, int64_t x_stride,
+                                     const int32_t *ids_device, int64_t tokens, int64_t slots, int32_t per_slot,
+                                     float *y_device, int64_t y_stride, void *stream);
+
 /* y (device, f32) = act . W^T with the rows last quantized into act. Asynchronous on the stream. Consecutive calls that
    read the same quantized rows may execute side by side on the device: their outputs must not overlap in memory. */
 SLC_API slc_result slc_matmul_run_quantized(slc_matmul *op, slc_activation *act, float *y_device, int64_t y_stride,

@@ -74,6 +74,7 @@ internal static unsafe partial class NativeMethods
     [LibraryImport(Library)] public static partial int slc_activation_quantize_rmsnorm(nint act, nint xDevice, int xDtype, long rows, long xStride, nint weightDevice, float eps, nint yDevice, long yStride, nint stream);
     [LibraryImport(Library)] public static partial int slc_activation_quantize_silu_mul(nint act, nint gateDevice, long gateStride, nint upDevice, long upStride, long rows, nint yDevice, long yStride, nint stream);
     [LibraryImport(Library)] public static partial int slc_argmax_rows(nint device, nint yDevice, long rows, long n, long yStride, nint outIndexDevice, nint stream);
+    [LibraryImport(Library)] public static partial int slc_matmul_id_run(nint weight, int experts, nint xDevice, int xDtype, long xStride, nint idsDevice, long tokens, long slots, int perSlot, nint yDevice, long yStride, nint stream);
     [LibraryImport(Library)] public static partial int slc_matmul_run_quantized(nint op, nint act, nint yDevice, long yStride, nint stream);
     [LibraryImport(Library)] public static partial int slc_matmul_run_quantized_epilogue(nint op, nint act, nint exchange, nint bias, nint residual, long residualStride, nint y, long yStride, nint stream);
 

@@ -663,6 +663,26 @@ slc_result slc_argmax_rows(slc_device *d, const float *y, int64_t rows, int64_t 
     return SLC_OK;
 }
 
+slc_result slc_matmul_id_run(slc_weight *w, int32_t experts, const void *x, int32_t x_dtype, int64_t x_stride, const int32_t *ids,
+                             int64_t tokens, int64_t slots, int32_t per_slot, float *y, int64_t y_stride, void *stream)
+{
+    if (!w) return fail(SLC_ERR_INVALID_ARGUMENT, "weight is null");
+    if (x_dtype != SLC_F32 && x_dtype != SLC_BF16) return fail(SLC_ERR_UNSUPPORTED, "activation dtype must be f32 or bf16");
+    if (experts < 1 || w->n % experts != 0) return fail(SLC_ERR_INVALID_ARGUMENT, "the weight's rows are not a multiple of the expert count");
+    const long long n = w->n / experts;
+    if (n % 16 != 0) return fail(SLC_ERR_UNSUPPORTED, "MatMulId: rows per expert must be a multiple of 16 (an expert starts on a row group)");
+    if (w->high) return fail(SLC_ERR_UNSUPPORTED, "MatMulId takes no Q5_K weight (two passes)");
+    if (tokens < 0 || slots < 1 || slots > 65535 || tokens > (1 << 24)) return fail(SLC_ERR_INVALID_ARGUMENT, "tokens >= 0, 1 <= slots <= 65535");
+    if (tokens == 0 || n == 0) return SLC_OK;
+    if (!x || !ids || !y || x_stride < w->k || y_stride < n) return fail(SLC_ERR_INVALID_ARGUMENT, "bad buffers or strides");
+    if (matvec_f32_rows(w->view.k_pad) == 0) return fail(SLC_ERR_UNSUPPORTED, "K is too long for the f32 mat-vec's shared memory");
+    slc_device *d = w->dev;
+    SLC_CUDA(cudaSetDevice(d->index));
+    SLC_CUDA(launch_matvec_f32_id(w->view, experts, x, x_dtype, x_stride, ids, tokens, (int)slots, per_slot ? 1 : 0, y, y_stride,
+                                  d->status_dev, stream ? (cudaStream_t)stream : d->stream));
+    return SLC_OK;
+}
+
 static ActView view_of(const slc_activation *a)
 {
     ActView v;

@@ -142,6 +142,12 @@ cudaError_t launch_densify(void *dst, const void *src, int batch, int rows, int 
 int matvec_f32_rows(int k_pad);
 cudaError_t launch_matvec_f32(const WeightView &w, const void *x, int x_dtype, long long x_stride, int row0, int rows, float *y,
                               long long y_stride, cudaStream_t stream, const Epilogue *epilogue = nullptr);
+// The expert-indexed form (MatMulId): w holds `experts` matrices of N = w.n / experts rows (N % 16 == 0); item t * slots + s
+// multiplies expert ids[item] with activation row item (per_slot) or t and writes output row item. status: device word,
+// set to -1 by an id outside [0, experts).
+cudaError_t launch_matvec_f32_id(const WeightView &w, int experts, const void *x, int x_dtype, long long x_stride, const int *ids,
+                                 long long tokens, int slots, int per_slot, float *y, long long y_stride, int *status,
+                                 cudaStream_t stream);
 
 // producers.cu: kernels that produce the quantized activations in the same pass as the operation in front of the MatMul
 // (y, optional: the f32 result as well), and the arg-max behind the lm_head.

@@ -202,6 +202,58 @@ __global__ void __launch_bounds__(F32V_WARPS * 32) matvec_f32_kernel(const Weigh
     }
 }
 
+// Expert-indexed form (the reference's MatMulId, src/Sharplight.Core/Graph/StandardOps.Moe.cs:8-40, CPU arithmetic as
+// src/Sharplight.Cpu/MatMulIdOp.cs: f32 activations, each item computed as a single row is): the weight holds the E
+// expert matrices one after the other ([E * N, K], N a multiple of 16 so that an expert starts on a row group);
+// item = t * S + s multiplies the rows of expert ids[item] with activation row item (per_slot) or t, and writes output
+// row item. Grid: (N / 16, items). The ids come from the kernel in front (top-k routing), so nothing is read before the
+// dependency wait. An id outside [0, E) raises the device status word (-1) and leaves the item's row untouched.
+template <int FMT>
+__global__ void __launch_bounds__(F32V_WARPS * 32) matvec_f32_id_kernel(const WeightView w, int rg_per_expert, int n_expert, int experts,
+                                                                        const void *__restrict__ xv, int x_dtype, long long x_stride,
+                                                                        const int *__restrict__ ids, int slots, int per_slot,
+                                                                        float *__restrict__ y, long long y_stride, int *status)
+{
+    extern __shared__ __align__(16) unsigned char f32v_smem[];
+    float *xs = reinterpret_cast<float *>(f32v_smem);          // [k_pad]
+    float *red = xs + w.k_pad;                                  // [warps][16]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int item = blockIdx.y;
+    pdl_enter(0);
+    const int e = ids[item];
+    if (e < 0 || e >= experts) {
+        if (threadIdx.x == 0 && blockIdx.x == 0) atomicExch(status, -1);
+        return;
+    }
+    const long long xrow = per_slot ? item : item / slots;
+    for (int kk = threadIdx.x; kk < w.k_pad; kk += F32V_WARPS * 32) {
+        float v = 0.0f;
+        if (kk < w.k) {
+            v = x_dtype == 0 ? reinterpret_cast<const float *>(xv)[xrow * x_stride + kk]
+                             : __uint_as_float((unsigned)reinterpret_cast<const unsigned short *>(xv)[xrow * x_stride + kk] << 16);
+        }
+        xs[kk] = v;
+    }
+    __syncthreads();
+    float acc[1][2] = { { 0.f, 0.f } };
+    const int rg = e * rg_per_expert + (int)blockIdx.x, nst = w.k_pad >> 8;
+    for (int st = warp; st < nst; st += F32V_WARPS) f32v_record<FMT, 1>(w.record(rg, st), lane, xs + st * 256, w.k_pad, acc);
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        float v = acc[0][r];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        if ((lane & 3) == 0) red[warp * 16 + (lane >> 2) + 8 * r] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < 16) {
+        float v = 0.f;
+        for (int wi = 0; wi < F32V_WARPS; wi++) v += red[wi * 16 + threadIdx.x];
+        const int row = (int)blockIdx.x * 16 + threadIdx.x;
+        if (row < n_expert) y[(long long)item * y_stride + row] = v;
+    }
+}
+
 static size_t f32v_smem_bytes(int m, int k_pad) { return (size_t)m * k_pad * 4 + (size_t)F32V_WARPS * m * 16 * 4; }
 
 // rows per launch that fit the shared memory (0: K is too long even for one row)
@@ -245,6 +297,54 @@ cudaError_t launch_matvec_f32(const WeightView &w, const void *x, int x_dtype, l
 #undef SLC_FMT
 #undef SLC_M
     return cudaErrorInvalidValue;
+}
+
+template <int FMT>
+static cudaError_t f32v_id_launch(const WeightView &w, int experts, const void *x, int x_dtype, long long x_stride, const int *ids,
+                                  long long items, int slots, int per_slot, float *y, long long y_stride, int *status,
+                                  cudaStream_t stream)
+{
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto kernel = matvec_f32_id_kernel<FMT>;
+    if (dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F32V_MAX_SMEM);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    const int n_expert = w.n / experts, rg_per_expert = n_expert >> 4;
+    cudaError_t e = cudaSuccess;
+    // the grid's second dimension holds at most 65535 items: launches of whole tokens
+    const long long per_launch = slots <= 65535 ? (65535 / slots) * (long long)slots : 0;
+    if (per_launch == 0) return cudaErrorInvalidValue;
+    const size_t esz = x_dtype == 0 ? 4 : 2;
+    for (long long i0 = 0; i0 < items && e == cudaSuccess; i0 += per_launch) {
+        const long long cnt = items - i0 < per_launch ? items - i0 : per_launch;
+        const long long xrow0 = per_slot ? i0 : i0 / slots;   // the activation row of this launch's first item
+        const void *xi = static_cast<const char *>(x) + (size_t)xrow0 * (size_t)x_stride * esz;
+        e = launch_pdl(kernel, dim3(rg_per_expert, (unsigned)cnt), dim3(F32V_WARPS * 32), f32v_smem_bytes(1, w.k_pad), stream, w,
+                       rg_per_expert, n_expert, experts, xi, x_dtype, x_stride, ids + i0, slots, per_slot, y + i0 * y_stride, y_stride, status);
+    }
+    return e;
+}
+
+// w: [experts * N, K] with N % 16 == 0; ids: device, items = tokens * slots entries; y: items rows, y_stride apart.
+cudaError_t launch_matvec_f32_id(const WeightView &w, int experts, const void *x, int x_dtype, long long x_stride, const int *ids,
+                                 long long tokens, int slots, int per_slot, float *y, long long y_stride, int *status,
+                                 cudaStream_t stream)
+{
+    if (experts < 1 || w.n % experts != 0 || ((w.n / experts) & 15) != 0 || slots < 1) return cudaErrorInvalidValue;
+    if (tokens <= 0 || w.n == 0) return cudaSuccess;
+    if (f32v_smem_bytes(1, w.k_pad) > (size_t)F32V_MAX_SMEM) return cudaErrorInvalidValue;
+    const long long items = tokens * slots;
+    switch (w.fmt) {
+    case FMT_Q8_0: return f32v_id_launch<FMT_Q8_0>(w, experts, x, x_dtype, x_stride, ids, items, slots, per_slot, y, y_stride, status, stream);
+    case FMT_Q4_0: return f32v_id_launch<FMT_Q4_0>(w, experts, x, x_dtype, x_stride, ids, items, slots, per_slot, y, y_stride, status, stream);
+    case FMT_Q4_K: return f32v_id_launch<FMT_Q4_K>(w, experts, x, x_dtype, x_stride, ids, items, slots, per_slot, y, y_stride, status, stream);
+    case FMT_Q6_K: return f32v_id_launch<FMT_Q6_K>(w, experts, x, x_dtype, x_stride, ids, items, slots, per_slot, y, y_stride, status, stream);
+    default: return cudaErrorInvalidValue;
+    }
 }
 
 }  // namespace slc

@@ -120,6 +120,7 @@ SIGNATURES = {
     "slc_matmul_run_quantized_allreduce": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp]),
     "slc_matmul_run_quantized_epilogue": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp]),
     "slc_matmul_run_static": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp, _i64, _vp]),
+    "slc_matmul_id_run": (_i32, [_vp, _i32, _vp, _i32, _i64, _vp, _i64, _i64, _i32, _vp, _i64, _vp]),
     "slc_static_last_error": (C.c_char_p, []),
     "slc_debug_quantize": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp, _vp, _vp]),
     "slc_debug_block_dots": (_i32, [_vp, _vp, _i32, _i64, _vp]),

@@ -300,6 +300,14 @@ class CudaDevice:
         _check(N.load().slc_argmax_rows(self.handle, C.c_void_p(y_device_ptr), rows, n, y_stride, C.c_void_p(out_index_ptr),
                                         C.c_void_p(stream) if stream else None))
 
+    def matmul_id(self, weight: "DeviceWeight", experts: int, x_device_ptr: int, x_dtype: int, x_stride: int, ids_device_ptr: int,
+                  tokens: int, slots: int, per_slot: bool, y_device_ptr: int, y_stride: int, stream: int = 0) -> None:
+        """MatMulId (slc_matmul_id_run): y[t, s] = W[ids[t, s]] . x[t (, s)] with the experts' matrices uploaded as one
+        [experts * N, K] weight; device pointers, asynchronous on the stream."""
+        _check(N.load().slc_matmul_id_run(weight.handle, experts, C.c_void_p(x_device_ptr), x_dtype, x_stride,
+                                          C.c_void_p(ids_device_ptr), tokens, slots, 1 if per_slot else 0,
+                                          C.c_void_p(y_device_ptr), y_stride, C.c_void_p(stream) if stream else None))
+
     def last_status(self) -> int:
         v = C.c_int32(0)
         _check(N.load().slc_last_status(self.handle, C.byref(v)))
