@@ -805,8 +805,8 @@ __global__ void __launch_bounds__(UM_THREADS, 1) umma_kernel(const UmParams p)
                                 um_arrive(&sh.fx_decided);
                             }
                         }
-                        // (a warp reads the flag of this round before it can arrive for the next one, and the flag is
-                        // rewritten only after all warps have arrived for that next round)
+                        // (a warp reads the flag of this fix-up before it can arrive for the next one, and the flag is
+                        // rewritten only after all warps have arrived for that next one)
                         if (!um_wait(&sh.fx_decided, (unsigned)n_fix & 1u, abort_flag, NAP * 100)) { ok = false; break; }
                         n_fix++;
                         if (*reinterpret_cast<volatile int *>(&sh.last_flag)) {
